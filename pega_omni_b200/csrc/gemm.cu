@@ -1,0 +1,393 @@
+// The two GEMM paths of the token loop (see gemm.h).
+#include "gemm.h"
+
+#include <algorithm>
+#include <cstdio>
+
+#include "sm100.cuh"
+
+namespace omni {
+
+__device__ __forceinline__ bf16 finish(float acc, int n, const bf16* bias, int kind) {
+  float t = bf16_round(acc);
+  if (kind != kEpiNone) {
+    t = bf16_round(t + __bfloat162float(bias[n]));
+    if (kind == kEpiBiasSilu) t = t / (1.f + __expf(-t));
+  }
+  return __float2bfloat16(t);
+}
+
+// ---------------------------------------------------------------------------
+// Vector GEMV: a warp owns an output column, lanes stride the weight row in
+// 16-byte pieces, up to R input rows ride along in registers, the R x K input
+// slab sits in shared memory. Weight bytes are read once per R rows.
+
+constexpr int kGemvWarps = 8;
+
+template <int R>
+__global__ void __launch_bounds__(kGemvWarps * 32) gemv_kernel(const bf16* __restrict__ w, int N, int K,
+                                                                const bf16* __restrict__ x, int rows,
+                                                                bf16* __restrict__ y, int ldy, const bf16* bias,
+                                                                int kind, int cols_per_warp) {
+  extern __shared__ __align__(16) unsigned char gemv_smem[];
+  bf16* xs = reinterpret_cast<bf16*>(gemv_smem);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int col0 = (blockIdx.x * kGemvWarps + warp) * cols_per_warp;
+  for (int r0 = 0; r0 < rows; r0 += R) {
+    __syncthreads();
+    for (int i = threadIdx.x; i < R * K / 8; i += blockDim.x) {
+      const int r = i / (K / 8), c = i % (K / 8) * 8;
+      Pack8 p;
+      if (r0 + r < rows)
+        p = *reinterpret_cast<const Pack8*>(x + (int64_t)(r0 + r) * K + c);
+      else
+        memset(&p, 0, sizeof(p));
+      *reinterpret_cast<Pack8*>(xs + r * K + c) = p;
+    }
+    __syncthreads();
+    for (int j = 0; j < cols_per_warp; ++j) {
+      const int n = col0 + j;
+      if (n >= N) break;
+      const bf16* wr = w + (int64_t)n * K;
+      float acc[R];
+#pragma unroll
+      for (int r = 0; r < R; ++r) acc[r] = 0.f;
+#pragma unroll 4
+      for (int c = lane * 8; c < K; c += 256) {
+        float wv[8];
+        ld8(wr + c, wv);
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+          float xv[8];
+          ld8(xs + r * K + c, xv);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) acc[r] = fmaf(wv[e], xv[e], acc[r]);
+        }
+      }
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        const float s = warp_add(acc[r]);
+        if (lane == 0 && r0 + r < rows) y[(int64_t)(r0 + r) * ldy + n] = finish(s, n, bias, kind);
+      }
+    }
+  }
+}
+
+template <int R>
+static cudaError_t gemv_launch_r(const bf16* w, int N, int K, const bf16* x, int rows, bf16* y, int ldy, Epilogue epi,
+                                 int sm_count, cudaStream_t stream) {
+  const size_t smem = (size_t)R * K * sizeof(bf16);  // tc_configure() has raised the limit to 200 KB
+  // enough warps to cover the machine a few times over, at most 4 columns per warp
+  int cpw = N / (kGemvWarps * sm_count * 4);
+  cpw = std::max(1, std::min(cpw, 4));
+  const int blocks = (N + kGemvWarps * cpw - 1) / (kGemvWarps * cpw);
+  gemv_kernel<R><<<blocks, kGemvWarps * 32, smem, stream>>>(w, N, K, x, rows, y, ldy, epi.bias, epi.kind, cpw);
+  return cudaGetLastError();
+}
+
+cudaError_t gemv_launch(const bf16* w, int N, int K, const bf16* x, int rows, bf16* y, int ldy, Epilogue epi,
+                        int sm_count, cudaStream_t stream) {
+  if (K % 8 != 0) return cudaErrorInvalidValue;
+  // the slab must fit in shared memory: fewer rows per pass for very wide K
+  int r = rows >= 8 ? 8 : rows > 2 ? 4 : rows;
+  while (r > 1 && (size_t)r * K * 2 > 200 * 1024) r >>= 1;
+  switch (r) {
+    case 1: return gemv_launch_r<1>(w, N, K, x, rows, y, ldy, epi, sm_count, stream);
+    case 2: return gemv_launch_r<2>(w, N, K, x, rows, y, ldy, epi, sm_count, stream);
+    case 4: return gemv_launch_r<4>(w, N, K, x, rows, y, ldy, epi, sm_count, stream);
+    default: return gemv_launch_r<8>(w, N, K, x, rows, y, ldy, epi, sm_count, stream);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Tensor-core tiles. One CTA = one 128-row slab of W (the MMA M dimension)
+// times one tile of BN input rows (the MMA N dimension) over one K split.
+//   warp 0 / lane 0: TMA producer, a ring of kStages {W tile, X tile} buffers
+//   warp 1 / lane 0: issues tcgen05.mma (K = 16 per instruction, 4 per 64-wide
+//                    K block), commits each stage back to the producer
+//   all four warps:  epilogue, each reading its 32 TMEM lanes
+// The accumulator D[128, BN] f32 lives in BN TMEM columns.
+// With splits > 1 each split stores its f32 tile to scratch; the last CTA to
+// arrive at the tile's counter sums the splits in index order (so the result
+// does not depend on arrival order) and writes the output.
+
+constexpr int kTileW = 128;  // weight rows per CTA
+constexpr int kTileK = 64;   // K elements per stage: one 128-byte swizzle row
+
+template <int BN>
+struct TcShape {
+  static constexpr int kStageBytes = kTileW * kTileK * 2 + BN * kTileK * 2;
+  static constexpr int kStages = (200 * 1024 / kStageBytes) > 8 ? 8 : (200 * 1024 / kStageBytes);
+  static constexpr int kTmemCols = BN < 32 ? 32 : BN;
+  static constexpr size_t kSmemBytes = (size_t)kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+};
+
+template <int BN>
+__global__ void __launch_bounds__(128, 1)
+    gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap xmap,
+                   bf16* __restrict__ y, int ldy, int N, int K, int rows, int splits, float* __restrict__ partials,
+                   uint32_t* __restrict__ counters, const bf16* bias, int kind, uint32_t* err) {
+  using S = TcShape<BN>;
+  using namespace sm100;
+  if (*reinterpret_cast<volatile uint32_t*>(err) != 0) return;  // an earlier kernel failed: do not wait on hardware
+
+  extern __shared__ unsigned char tc_smem_raw[];
+  const uint32_t raw = smem_addr(tc_smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  unsigned char* base_ptr = tc_smem_raw + (base - raw);
+  const uint32_t bars = base + S::kStages * S::kStageBytes;
+  // barrier words: full[kStages], empty[kStages], acc, then the TMEM base slot
+  auto full_bar = [&](int s) { return bars + 8u * s; };
+  auto empty_bar = [&](int s) { return bars + 8u * (S::kStages + s); };
+  const uint32_t acc_bar = bars + 8u * (2 * S::kStages);
+  const uint32_t tmem_slot = acc_bar + 8u;
+  volatile uint32_t* tmem_slot_ptr =
+      reinterpret_cast<volatile uint32_t*>(base_ptr + S::kStages * S::kStageBytes + 8 * (2 * S::kStages) + 8);
+  __shared__ int is_last;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tile = blockIdx.x, split = blockIdx.y, row_tile = blockIdx.z;
+  const int nkb = K / kTileK;
+  const int kb_begin = (int)((int64_t)nkb * split / splits), kb_end = (int)((int64_t)nkb * (split + 1) / splits);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S::kStages; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    mbar_init(acc_bar, 1);
+    mbar_init_fence();
+    prefetch_tensormap(&wmap);
+    prefetch_tensormap(&xmap);
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, S::kTmemCols);
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot_ptr;
+
+  bool ok = true;
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int kb = kb_begin; kb < kb_end; ++kb) {
+        if (!mbar_wait(empty_bar(stage), phase ^ 1u, err)) break;
+        const uint32_t a_dst = base + stage * S::kStageBytes, b_dst = a_dst + kTileW * kTileK * 2;
+        mbar_expect_tx(full_bar(stage), S::kStageBytes);
+        tma_load_2d(a_dst, &wmap, full_bar(stage), kb * kTileK, tile * kTileW, kEvictFirst);
+        tma_load_2d(b_dst, &xmap, full_bar(stage), kb * kTileK, row_tile * BN, kEvictLast);
+        if (++stage == S::kStages) {
+          stage = 0;
+          phase ^= 1u;
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = idesc_bf16_f32(kTileW, BN);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool alive = true;
+      for (int kb = kb_begin; kb < kb_end && alive; ++kb) {
+        alive = mbar_wait(full_bar(stage), phase, err);
+        if (!alive) break;
+        tc_fence_after_sync();
+        const uint32_t a_src = base + stage * S::kStageBytes, b_src = a_src + kTileW * kTileK * 2;
+        const uint64_t adesc = kmajor_sw128_desc(a_src), bdesc = kmajor_sw128_desc(b_src);
+#pragma unroll
+        for (int k = 0; k < kTileK / 16; ++k)
+          mma_bf16(tmem_base, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2), idesc,
+                   (kb > kb_begin || k > 0) ? 1u : 0u);
+        mma_commit(empty_bar(stage));  // frees the stage once these MMAs have read it
+        if (++stage == S::kStages) {
+          stage = 0;
+          phase ^= 1u;
+        }
+      }
+      if (alive) mma_commit(acc_bar);
+    }
+    __syncwarp();
+  }
+
+  ok = mbar_wait(acc_bar, 0, err);
+  tc_fence_after_sync();
+  const int n = tile * kTileW + warp * 32 + lane;  // this thread's weight row = output column
+  const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
+  const int n_pad = gridDim.x * kTileW;
+  if (ok) {
+    if (splits == 1) {
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 16) {
+        float v[16];
+        tmem_ld16(lane_addr + c0, v);
+        if (n < N) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int m = row_tile * BN + c0 + j;
+            if (m < rows) y[(int64_t)m * ldy + n] = finish(v[j], n, bias, kind);
+          }
+        }
+      }
+    } else {
+      float* mine = partials + (((size_t)row_tile * splits + split) * n_pad + n) * BN;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 16) {
+        float v[16];
+        tmem_ld16(lane_addr + c0, v);
+#pragma unroll
+        for (int j = 0; j < 16; j += 4)
+          *reinterpret_cast<float4*>(mine + c0 + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+      }
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, S::kTmemCols);
+
+  if (splits > 1) {
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      const uint32_t slot = row_tile * gridDim.x + tile;
+      const uint32_t prev = atomicAdd(&counters[slot], 1u);
+      is_last = prev == (uint32_t)(splits - 1);
+      if (is_last) counters[slot] = 0;  // every split has arrived; ready for the next launch
+    }
+    __syncthreads();
+    if (is_last) {
+      __threadfence();
+      const float* first = partials + (((size_t)row_tile * splits) * n_pad + n) * BN;
+      const size_t split_stride = (size_t)n_pad * BN;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 16) {
+        float acc[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) acc[j] = 0.f;
+        for (int s = 0; s < splits; ++s) {
+          const float* p = first + s * split_stride + c0;
+#pragma unroll
+          for (int j = 0; j < 16; j += 4) {
+            const float4 f = __ldcg(reinterpret_cast<const float4*>(p + j));
+            acc[j] += f.x;
+            acc[j + 1] += f.y;
+            acc[j + 2] += f.z;
+            acc[j + 3] += f.w;
+          }
+        }
+        if (n < N) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int m = row_tile * BN + c0 + j;
+            if (m < rows) y[(int64_t)m * ldy + n] = finish(acc[j], n, bias, kind);
+          }
+        }
+      }
+    }
+  }
+}
+
+// --- host side ----------------------------------------------------------------
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn g_encode = nullptr;
+
+int tc_init() {
+  if (g_encode) return 0;
+  void* fn = nullptr;
+  cudaDriverEntryPointQueryResult q;
+  cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q);
+  if (e != cudaSuccess || q != cudaDriverEntryPointSuccess || !fn) return -1;
+  g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+  return 0;
+}
+
+static int encode_kmajor(CUtensorMap* map, const bf16* base, int rows, int K, int box_rows) {
+  const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)K * sizeof(bf16)};
+  const cuuint32_t box[2] = {(cuuint32_t)kTileK, (cuuint32_t)box_rows};
+  const cuuint32_t elem[2] = {1, 1};
+  const CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<bf16*>(base), dims, strides, box,
+                              elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -1;
+}
+
+bool tc_supports(int N, int K, int rows) {
+  return K % kTileK == 0 && K >= kTileK && N >= 1 && rows >= 1;
+}
+
+static int pick_bn(int rows) {
+  if (rows <= 16) return 16;
+  if (rows <= 32) return 32;
+  if (rows <= 64) return 64;
+  if (rows <= 128) return 128;
+  return 256;
+}
+
+int tc_plan(TcGemmPlan* plan, const bf16* w, int N, int K, const bf16* x, int rows, bf16* y, int ldy, Epilogue epi,
+            int sm_count, int force_splits) {
+  if (tc_init() != 0) return -1;
+  if (!tc_supports(N, K, rows)) return -2;
+  if ((reinterpret_cast<uintptr_t>(w) & 15) || (reinterpret_cast<uintptr_t>(x) & 15)) return -3;
+  TcGemmPlan& p = *plan;
+  p.N = N;
+  p.K = K;
+  p.rows = rows;
+  p.BN = pick_bn(rows);
+  p.row_tiles = (rows + p.BN - 1) / p.BN;
+  p.y = y;
+  p.ldy = ldy;
+  p.epi = epi;
+  const int nkb = K / kTileK, ctas = p.tiles_n() * p.row_tiles;
+  int splits = force_splits > 0 ? force_splits : std::max(1, sm_count / ctas);
+  // keep at least two K blocks per split so the pipeline has something to overlap
+  splits = std::max(1, std::min(splits, nkb / 2));
+  p.splits = splits;
+  if (encode_kmajor(&p.wmap, w, N, K, kTileW) != 0) return -4;
+  if (encode_kmajor(&p.xmap, x, rows, K, p.BN) != 0) return -4;
+  return 0;
+}
+
+template <int BN>
+static cudaError_t tc_launch_bn(const TcGemmPlan& p, const GemmScratch& s, uint32_t* err, cudaStream_t stream) {
+  using S = TcShape<BN>;
+  const dim3 grid(p.tiles_n(), p.splits, p.row_tiles);
+  gemm_tc_kernel<BN><<<grid, 128, S::kSmemBytes, stream>>>(p.wmap, p.xmap, p.y, p.ldy, p.N, p.K, p.rows, p.splits,
+                                                           s.partials, s.counters, p.epi.bias, p.epi.kind, err);
+  return cudaGetLastError();
+}
+
+// Raises the dynamic shared-memory limit of every instantiation up front, so no
+// attribute call falls inside a stream capture.
+void tc_configure() {
+  cudaFuncSetAttribute(gemm_tc_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TcShape<16>::kSmemBytes);
+  cudaFuncSetAttribute(gemm_tc_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TcShape<32>::kSmemBytes);
+  cudaFuncSetAttribute(gemm_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TcShape<64>::kSmemBytes);
+  cudaFuncSetAttribute(gemm_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TcShape<128>::kSmemBytes);
+  cudaFuncSetAttribute(gemm_tc_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TcShape<256>::kSmemBytes);
+  cudaFuncSetAttribute(gemv_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+  cudaFuncSetAttribute(gemv_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+  cudaFuncSetAttribute(gemv_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+  cudaFuncSetAttribute(gemv_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+}
+
+cudaError_t tc_launch(const TcGemmPlan& p, const GemmScratch& s, uint32_t* err, cudaStream_t stream) {
+  if (p.splits > 1) {
+    if (p.partial_floats() > s.partial_floats || p.tiles_n() * p.row_tiles > s.counter_slots)
+      return cudaErrorInvalidValue;
+  }
+  switch (p.BN) {
+    case 16: return tc_launch_bn<16>(p, s, err, stream);
+    case 32: return tc_launch_bn<32>(p, s, err, stream);
+    case 64: return tc_launch_bn<64>(p, s, err, stream);
+    case 128: return tc_launch_bn<128>(p, s, err, stream);
+    case 256: return tc_launch_bn<256>(p, s, err, stream);
+  }
+  return cudaErrorInvalidValue;
+}
+
+}  // namespace omni

@@ -1,0 +1,190 @@
+// Operator-level C ABI (include/omni_b200_ops.h): each kernel as a plain call
+// over caller-owned device buffers.
+#include <cstdarg>
+#include <cstdio>
+#include <string>
+
+#include "../../include/omni_b200.h"
+#include "../../include/omni_b200_ops.h"
+#include "gemm.h"
+#include "kernels.h"
+
+using namespace omni;
+
+struct omni_ops {
+  int device = 0, sm_count = 148;
+  cudaStream_t stream = nullptr;
+  cudaEvent_t ev[2] = {nullptr, nullptr};
+  GemmScratch scratch;
+  uint32_t* err = nullptr;
+  std::string error;
+  int fail(int code, const char* fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof(buf), fmt, ap);
+    va_end(ap);
+    error = buf;
+    return code;
+  }
+};
+
+#define OPS_CUDA(ctx, expr)                                                                       \
+  do {                                                                                            \
+    cudaError_t e_ = (expr);                                                                      \
+    if (e_ != cudaSuccess) return (ctx)->fail(OMNI_ERR_CUDA, "%s: %s", #expr, cudaGetErrorString(e_)); \
+  } while (0)
+
+extern "C" {
+
+int32_t omni_ops_create(int32_t device, omni_ops** out) {
+  if (!out) return OMNI_ERR_INVALID;
+  omni_ops* c = new omni_ops();
+  *out = c;
+  c->device = device;
+  OPS_CUDA(c, cudaSetDevice(device));
+  cudaDeviceProp prop;
+  OPS_CUDA(c, cudaGetDeviceProperties(&prop, device));
+  if (prop.major != 10) return c->fail(OMNI_ERR_UNSUPPORTED, "device is sm_%d%d; this library is sm_100a only", prop.major, prop.minor);
+  c->sm_count = prop.multiProcessorCount;
+  OPS_CUDA(c, cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking));
+  OPS_CUDA(c, cudaEventCreate(&c->ev[0]));
+  OPS_CUDA(c, cudaEventCreate(&c->ev[1]));
+  if (tc_init() != 0) return c->fail(OMNI_ERR_CUDA, "cuTensorMapEncodeTiled entry point not found");
+  tc_configure();
+  c->scratch.partial_floats = (size_t)64 << 20;  // 256 MB of f32 partials: any test shape
+  c->scratch.counter_slots = 1 << 16;
+  OPS_CUDA(c, cudaMalloc((void**)&c->scratch.partials, c->scratch.partial_floats * 4));
+  OPS_CUDA(c, cudaMalloc((void**)&c->scratch.counters, (size_t)c->scratch.counter_slots * 4));
+  OPS_CUDA(c, cudaMemset(c->scratch.counters, 0, (size_t)c->scratch.counter_slots * 4));
+  OPS_CUDA(c, cudaMalloc((void**)&c->err, 256));
+  OPS_CUDA(c, cudaMemset(c->err, 0, 256));
+  return OMNI_OK;
+}
+
+void omni_ops_destroy(omni_ops* c) {
+  if (!c) return;
+  cudaSetDevice(c->device);
+  if (c->stream) cudaStreamSynchronize(c->stream);
+  cudaFree(c->scratch.partials);
+  cudaFree(c->scratch.counters);
+  cudaFree(c->err);
+  if (c->ev[0]) cudaEventDestroy(c->ev[0]);
+  if (c->ev[1]) cudaEventDestroy(c->ev[1]);
+  if (c->stream) cudaStreamDestroy(c->stream);
+  delete c;
+}
+
+const char* omni_ops_last_error(const omni_ops* c) { return c ? c->error.c_str() : "null context"; }
+
+int32_t omni_ops_sync(omni_ops* c, uint32_t* word) {
+  if (!c) return OMNI_ERR_INVALID;
+  OPS_CUDA(c, cudaStreamSynchronize(c->stream));
+  uint32_t w = 0;
+  OPS_CUDA(c, cudaMemcpy(&w, c->err, 4, cudaMemcpyDeviceToHost));
+  if (word) *word = w;
+  if (w != 0) {
+    cudaMemset(c->err, 0, 4);
+    return c->fail(OMNI_ERR_DEVICE, "device error word 0x%x", w);
+  }
+  return OMNI_OK;
+}
+
+int32_t omni_ops_mark(omni_ops* c, int32_t which) {
+  if (!c || which < 0 || which > 1) return OMNI_ERR_INVALID;
+  OPS_CUDA(c, cudaEventRecord(c->ev[which], c->stream));
+  return OMNI_OK;
+}
+
+int32_t omni_ops_elapsed_ms(omni_ops* c, float* ms) {
+  if (!c || !ms) return OMNI_ERR_INVALID;
+  OPS_CUDA(c, cudaEventSynchronize(c->ev[1]));
+  OPS_CUDA(c, cudaEventElapsedTime(ms, c->ev[0], c->ev[1]));
+  return OMNI_OK;
+}
+
+int32_t omni_op_gemm(omni_ops* c, const void* w, int32_t N, int32_t K, const void* x, int32_t rows, void* y,
+                     int32_t ldy, int32_t path, int32_t splits, const void* bias, int32_t epilogue) {
+  if (!c || !w || !x || !y || N < 1 || K < 8 || rows < 1) return OMNI_ERR_INVALID;
+  if (epilogue != OMNI_EPI_NONE && !bias) return c->fail(OMNI_ERR_INVALID, "epilogue %d needs a bias", epilogue);
+  Epilogue epi;
+  epi.bias = static_cast<const bf16*>(bias);
+  epi.kind = epilogue;
+  const bool tensor = path == OMNI_GEMM_TENSOR || (path == OMNI_GEMM_AUTO && rows > 8 && tc_supports(N, K, rows));
+  if (!tensor) {
+    OPS_CUDA(c, gemv_launch((const bf16*)w, N, K, (const bf16*)x, rows, (bf16*)y, ldy, epi, c->sm_count, c->stream));
+    return OMNI_OK;
+  }
+  if (!tc_supports(N, K, rows)) return c->fail(OMNI_ERR_UNSUPPORTED, "tensor path needs K %% 64 == 0");
+  TcGemmPlan plan;
+  const int rc = tc_plan(&plan, (const bf16*)w, N, K, (const bf16*)x, rows, (bf16*)y, ldy, epi, c->sm_count, splits);
+  if (rc != 0) return c->fail(OMNI_ERR_CUDA, "tensor-map encode failed (%d)", rc);
+  OPS_CUDA(c, tc_launch(plan, c->scratch, c->err, c->stream));
+  return OMNI_OK;
+}
+
+int32_t omni_op_norm_copy(omni_ops* c, const void* x, const void* w, void* out, void* res, int32_t rows, int32_t dim,
+                          float eps) {
+  if (!c) return OMNI_ERR_INVALID;
+  OPS_CUDA(c, launch_norm_copy((const bf16*)x, (const bf16*)w, (bf16*)out, (bf16*)res, rows, dim, eps, c->stream));
+  return OMNI_OK;
+}
+
+int32_t omni_op_add_norm(omni_ops* c, const void* x, void* res, const void* w, void* out, int32_t rows, int32_t dim,
+                         float eps, int32_t every, int32_t which) {
+  if (!c || every < 1 || which < 0 || which >= every) return OMNI_ERR_INVALID;
+  OPS_CUDA(c, launch_add_norm((const bf16*)x, (bf16*)res, (const bf16*)w, (bf16*)out, rows, dim, eps, every, which,
+                              c->stream));
+  return OMNI_OK;
+}
+
+int32_t omni_op_silu_mul(omni_ops* c, const void* gate_up, void* act, int32_t rows, int32_t inter) {
+  if (!c || inter % 8) return OMNI_ERR_INVALID;
+  OPS_CUDA(c, launch_silu_mul((const bf16*)gate_up, (bf16*)act, rows, inter, c->stream));
+  return OMNI_OK;
+}
+
+int32_t omni_op_rope_attend(omni_ops* c, void* qkv, const void* q_norm, const void* k_norm, void* kv,
+                            int32_t kv_pages, const int32_t* pos, const int32_t* slot, const int32_t* seq,
+                            const int32_t* indptr, const int32_t* pages, int32_t rows, int32_t q_heads,
+                            int32_t kv_heads, int32_t head_dim, float eps, float theta, void* out) {
+  if (!c || !pos || !slot || !indptr || !pages) return OMNI_ERR_INVALID;
+  RowMap map;
+  map.pos = pos;
+  map.slot = slot;
+  map.seq = seq;
+  map.indptr = indptr;
+  map.pages = pages;
+  const AttnShape a{q_heads, kv_heads, head_dim, eps, theta};
+  OPS_CUDA(c, launch_rope_kv((bf16*)qkv, (const bf16*)q_norm, (const bf16*)k_norm, (bf16*)kv, map, rows, a, kv_pages,
+                             c->err, c->stream));
+  OPS_CUDA(c, launch_attend((const bf16*)qkv, (const bf16*)kv, (bf16*)out, map, rows, a, c->err, c->stream));
+  return OMNI_OK;
+}
+
+int32_t omni_op_sample(omni_ops* c, const void* logits, int32_t vocab, float temperature, int32_t top_k, float top_p,
+                       float penalty, int32_t suppress_lo, int32_t suppress_hi, int32_t exempt, int32_t min_frames,
+                       const int32_t* frames, const float* uniforms, const int32_t* force, void* state,
+                       const int32_t* lines, int64_t stride, int32_t penalize, int32_t philox, int32_t* codes,
+                       int32_t group, int32_t rows) {
+  if (!c || group < 0 || group >= OMNI_GROUPS) return OMNI_ERR_INVALID;
+  SampleParams p{};
+  p.vocab = vocab;
+  p.temperature = temperature;
+  p.top_k = top_k;
+  p.top_p = top_p;
+  p.penalty = penalty;
+  p.suppress_lo = suppress_lo;
+  p.suppress_hi = suppress_hi;
+  p.exempt = exempt;
+  p.min_frames = min_frames;
+  p.penalize = penalize;
+  p.group = group;
+  p.philox = philox;
+  p.seen_words = (vocab + 31) / 32;
+  OPS_CUDA(c, launch_sample((const bf16*)logits, p, frames, uniforms, force, SlotState{state, lines, stride}, codes,
+                            rows, c->stream));
+  return OMNI_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,330 @@
+// Decoder-stack kernels that are not GEMMs: RMSNorm with the residual stream,
+// SwiGLU, per-head q/k norm + rotary embedding + KV write, and decode attention
+// over the paged KV. Rounding points follow the reference's kernels
+// (crates/omni-qwen3/kernels/qwen3.cu, crates/omni-kern/kernels/common.cuh):
+// every tensor that crosses HBM is bf16, arithmetic is f32.
+#include "kernels.h"
+
+namespace omni {
+
+// ---- RMSNorm + residual ------------------------------------------------------
+
+// One block of dim/8 threads per row. Semantics of `qwen3_norm_copy`
+// (qwen3.cu:18-31).
+__global__ void norm_copy_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, bf16* __restrict__ out,
+                                 bf16* __restrict__ res, int dim, float eps) {
+  __shared__ float scratch[32];
+  const int64_t at = (int64_t)blockIdx.x * dim + threadIdx.x * 8;
+  float v[8], g[8];
+  ld8(x + at, v);
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < 8; ++k) ss += v[k] * v[k];
+  const float r = rsqrtf(block_add(ss, scratch) / dim + eps);
+  st8(res + at, v);
+  ld8(w + threadIdx.x * 8, g);
+#pragma unroll
+  for (int k = 0; k < 8; ++k) v[k] = v[k] * r * g[k];
+  st8(out + at, v);
+}
+
+// Semantics of `qwen3_add_norm` (qwen3.cu:37-57): the residual is stored
+// rounded, the norm is taken over the unrounded sum.
+__global__ void add_norm_kernel(const bf16* __restrict__ x, bf16* __restrict__ res, const bf16* __restrict__ w,
+                                bf16* __restrict__ out, int dim, float eps, int every, int which) {
+  __shared__ float scratch[32];
+  const int n = blockIdx.x;
+  const int64_t at = (int64_t)n * dim + threadIdx.x * 8;
+  float v[8], rv[8], g[8];
+  ld8(x + at, v);
+  ld8(res + at, rv);
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    v[k] += rv[k];
+    ss += v[k] * v[k];
+  }
+  const float r = rsqrtf(block_add(ss, scratch) / dim + eps);
+  st8(res + at, v);
+  if (n % every != which) return;
+  ld8(w + threadIdx.x * 8, g);
+#pragma unroll
+  for (int k = 0; k < 8; ++k) v[k] = v[k] * r * g[k];
+  st8(out + (int64_t)(n / every) * dim + threadIdx.x * 8, v);
+}
+
+// `silu_mul` (common.cuh:66-76).
+__global__ void silu_mul_kernel(const bf16* __restrict__ gate_up, bf16* __restrict__ act, int inter, int total) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const int64_t n = i / (inter / 8), c = i % (inter / 8) * 8;
+  float g[8], u[8];
+  ld8(gate_up + n * 2 * inter + c, g);
+  ld8(gate_up + n * 2 * inter + inter + c, u);
+#pragma unroll
+  for (int k = 0; k < 8; ++k) g[k] = bf16_round(g[k] / (1.f + __expf(-g[k]))) * u[k];
+  st8(act + (int64_t)i * 8, g);
+}
+
+cudaError_t launch_norm_copy(const bf16* x, const bf16* w, bf16* out, bf16* res, int rows, int dim, float eps,
+                             cudaStream_t s) {
+  if (dim % 8 || dim / 8 > 1024) return cudaErrorInvalidValue;
+  norm_copy_kernel<<<rows, dim / 8, 0, s>>>(x, w, out, res, dim, eps);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_add_norm(const bf16* x, bf16* res, const bf16* w, bf16* out, int rows, int dim, float eps,
+                            int every, int which, cudaStream_t s) {
+  if (dim % 8 || dim / 8 > 1024) return cudaErrorInvalidValue;
+  add_norm_kernel<<<rows, dim / 8, 0, s>>>(x, res, w, out, dim, eps, every, which);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_silu_mul(const bf16* gate_up, bf16* act, int rows, int inter, cudaStream_t s) {
+  const int total = rows * (inter / 8);
+  silu_mul_kernel<<<(total + 255) / 256, 256, 0, s>>>(gate_up, act, inter, total);
+  return cudaGetLastError();
+}
+
+// ---- row -> (sequence, position, page) -----------------------------------------
+
+struct RowAt {
+  int seq, pos;
+  int64_t slot;            // page * 16 + pos % 16 of the row's own token
+  const int32_t* pages;    // the sequence's page list, or nullptr when dense
+};
+
+__device__ __forceinline__ RowAt locate(const RowMap& m, int n) {
+  RowAt r;
+  if (m.pages) {
+    r.seq = m.seq ? m.seq[n] : n;
+    r.pos = m.pos[n];
+    r.slot = m.slot ? m.slot[n] : 0;
+    r.pages = m.pages + m.indptr[r.seq];
+  } else {
+    r.seq = n / m.per;
+    r.pos = m.base + n % m.per;
+    r.slot = (int64_t)r.seq * 16 + r.pos;
+    r.pages = nullptr;
+  }
+  return r;
+}
+
+// Element offset of (page, head, K or V, token-in-page) in a layer's KV buffer.
+template <int D>
+__device__ __forceinline__ int64_t kv_offset(int64_t page, int hk, int head, int which, int tok) {
+  return (((page * hk + head) * 2 + which) * 16 + tok) * D;
+}
+
+// ---- q/k norm + RoPE + KV write -------------------------------------------------
+
+// One warp per (row, head) over the q, k and v heads of the fused qkv row.
+// Semantics of `rope_kv` (qwen3.cu:66-107): RMSNorm over the head, the
+// normalised value rounded to bf16 before the gain, half-rotation rotary
+// embedding with inv_freq = theta^(-2i/D); q stays in place, k and v go to the
+// row's slot.
+template <int D>
+__global__ void __launch_bounds__(256) rope_kv_kernel(bf16* __restrict__ qkv, const bf16* __restrict__ q_norm,
+                                                      const bf16* __restrict__ k_norm, bf16* __restrict__ kv,
+                                                      RowMap map, int hq, int hk, float eps, float theta,
+                                                      int kv_pages, uint32_t* err) {
+  constexpr int E = D / 64;  // elements of each half a lane owns
+  const int n = blockIdx.x;
+  const int head = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (head >= hq + 2 * hk) return;
+  const RowAt at = locate(map, n);
+  const int64_t page = at.slot >> 4;
+  const int tok = (int)(at.slot & 15);
+  if (page < 0 || page >= kv_pages) {
+    if (lane == 0) raise(err, kErrBadIndex);
+    return;
+  }
+  bf16* row = qkv + ((int64_t)n * (hq + 2 * hk) + head) * D;
+  if (head >= hq + hk) {  // V: a plain copy
+    bf16* dst = kv + kv_offset<D>(page, hk, head - hq - hk, 1, tok);
+    for (int i = lane; i < D; i += 32) dst[i] = row[i];
+    return;
+  }
+  const bool is_q = head < hq;
+  const bf16* w = is_q ? q_norm : k_norm;
+  bf16* dst = is_q ? row : kv + kv_offset<D>(page, hk, head - hq, 0, tok);
+  float lo[E], hi[E], ss = 0.f;
+#pragma unroll
+  for (int e = 0; e < E; ++e) {
+    lo[e] = __bfloat162float(row[lane * E + e]);
+    hi[e] = __bfloat162float(row[D / 2 + lane * E + e]);
+    ss += lo[e] * lo[e] + hi[e] * hi[e];
+  }
+  const float r = rsqrtf(warp_add(ss) / D + eps);
+#pragma unroll
+  for (int e = 0; e < E; ++e) {
+    const int i = lane * E + e;
+    const float a = bf16_round(lo[e] * r) * __bfloat162float(w[i]);
+    const float b = bf16_round(hi[e] * r) * __bfloat162float(w[D / 2 + i]);
+    const float inv_freq = 1.f / powf(theta, (float)(2 * i) / D);
+    float sn, cs;
+    sincosf((float)at.pos * inv_freq, &sn, &cs);
+    dst[i] = __float2bfloat16(a * cs - b * sn);
+    dst[D / 2 + i] = __float2bfloat16(b * cs + a * sn);
+  }
+}
+
+cudaError_t launch_rope_kv(bf16* qkv, const bf16* q_norm, const bf16* k_norm, bf16* kv, const RowMap& map, int rows,
+                           const AttnShape& a, int kv_pages, uint32_t* err, cudaStream_t s) {
+  const int heads = a.q_heads + 2 * a.kv_heads;
+  const dim3 grid(rows, (heads + 7) / 8);
+  if (a.head_dim == 128)
+    rope_kv_kernel<128><<<grid, 256, 0, s>>>(qkv, q_norm, k_norm, kv, map, a.q_heads, a.kv_heads, a.rms_eps,
+                                             a.rope_theta, kv_pages, err);
+  else if (a.head_dim == 64)
+    rope_kv_kernel<64><<<grid, 256, 0, s>>>(qkv, q_norm, k_norm, kv, map, a.q_heads, a.kv_heads, a.rms_eps,
+                                            a.rope_theta, kv_pages, err);
+  else
+    return cudaErrorInvalidValue;
+  return cudaGetLastError();
+}
+
+// ---- decode attention -------------------------------------------------------------
+
+constexpr int kAttnWarps = 4;
+
+// One CTA per (row, kv head); its G query heads share the K/V stream. Warps
+// take pages round-robin. Within a page the two half-warps split the head
+// dimension for q.k (lane & 15 = key), then every lane owns D/32 output dims
+// for p.v. Each warp keeps an online-softmax state per query head; the four
+// states merge through shared memory. Value semantics of `attend`
+// (qwen3.cu:123-207): f32 scores and accumulation, __expf, bf16 output.
+template <int D, int G>
+__global__ void __launch_bounds__(kAttnWarps * 32) attend_kernel(const bf16* __restrict__ qkv,
+                                                                 const bf16* __restrict__ kv, bf16* __restrict__ out,
+                                                                 RowMap map, int hq, int hk, float scale) {
+  constexpr int PV = D / 32;    // output dims per lane
+  constexpr int HALF = D / 2;   // q.k dims per half-warp
+  const int n = blockIdx.x, kh = blockIdx.y;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int key = lane & 15, half = lane >> 4;
+  __shared__ float qs[G][D];
+  __shared__ float ms[kAttnWarps][G], ls[kAttnWarps][G];
+  __shared__ float os[kAttnWarps][G][D];
+  const RowAt at = locate(map, n);
+  const int len = at.pos + 1;
+  const bf16* q = qkv + ((int64_t)n * (hq + 2 * hk) + kh * G) * D;
+  for (int i = threadIdx.x; i < G * D; i += blockDim.x) qs[i / D][i % D] = __bfloat162float(q[i]);
+  __syncthreads();
+
+  float m[G], l[G], acc[G][PV];
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    m[g] = -INFINITY;
+    l[g] = 0.f;
+#pragma unroll
+    for (int d = 0; d < PV; ++d) acc[g][d] = 0.f;
+  }
+  const int npages = (len + 15) >> 4;
+  for (int pi = warp; pi < npages; pi += kAttnWarps) {
+    const int64_t page = at.pages ? at.pages[pi] : at.seq;
+    const int ntok = min(16, len - pi * 16);
+    const bf16* kpage = kv + kv_offset<D>(page, hk, kh, 0, 0);
+    const bf16* vpage = kpage + 16 * D;
+    float sc[G];
+#pragma unroll
+    for (int g = 0; g < G; ++g) sc[g] = 0.f;
+    const bf16* krow = kpage + key * D + half * HALF;
+#pragma unroll
+    for (int c = 0; c < HALF; c += 8) {
+      float kf[8];
+      ld8(krow + c, kf);
+#pragma unroll
+      for (int g = 0; g < G; ++g)
+#pragma unroll
+        for (int e = 0; e < 8; ++e) sc[g] = fmaf(qs[g][half * HALF + c + e], kf[e], sc[g]);
+    }
+    float p[G];
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      float s = sc[g] + __shfl_xor_sync(0xffffffffu, sc[g], 16);
+      s = key < ntok ? s * scale : -INFINITY;
+      const float m2 = fmaxf(m[g], warp_fmax(s));
+      const float corr = __expf(m[g] - m2);
+      p[g] = __expf(s - m2);
+      float ps = p[g];  // sum over the 16 keys (both half-warps hold the same values)
+#pragma unroll
+      for (int o = 8; o > 0; o >>= 1) ps += __shfl_xor_sync(0xffffffffu, ps, o);
+      l[g] = l[g] * corr + ps;
+#pragma unroll
+      for (int d = 0; d < PV; ++d) acc[g][d] *= corr;
+      m[g] = m2;
+    }
+    for (int j = 0; j < ntok; ++j) {
+      float vf[PV];
+      if (PV == 4) {
+        const uint2 u = *reinterpret_cast<const uint2*>(vpage + j * D + lane * 4);
+        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.x));
+        const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.y));
+        vf[0] = a.x, vf[1] = a.y, vf[PV - 2] = b.x, vf[PV - 1] = b.y;
+      } else {
+        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(vpage + j * D + lane * 2));
+        vf[0] = a.x, vf[1] = a.y;
+      }
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+        const float pj = __shfl_sync(0xffffffffu, p[g], j);
+#pragma unroll
+        for (int d = 0; d < PV; ++d) acc[g][d] = fmaf(pj, vf[d], acc[g][d]);
+      }
+    }
+  }
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    if (lane == 0) {
+      ms[warp][g] = m[g];
+      ls[warp][g] = l[g];
+    }
+#pragma unroll
+    for (int d = 0; d < PV; ++d) os[warp][g][lane * PV + d] = acc[g][d];
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < G * D; i += blockDim.x) {
+    const int g = i / D, d = i % D;
+    float top = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kAttnWarps; ++w) top = fmaxf(top, ms[w][g]);
+    float num = 0.f, den = 0.f;
+#pragma unroll
+    for (int w = 0; w < kAttnWarps; ++w) {
+      const float e = __expf(ms[w][g] - top);
+      num += os[w][g][d] * e;
+      den += ls[w][g] * e;
+    }
+    out[((int64_t)n * hq + kh * G + g) * D + d] = __float2bfloat16(num / den);
+  }
+}
+
+template <int D>
+static cudaError_t launch_attend_d(const bf16* qkv, const bf16* kv, bf16* out, const RowMap& map, int rows,
+                                   const AttnShape& a, cudaStream_t s) {
+  const dim3 grid(rows, a.kv_heads);
+  const float scale = 1.f / sqrtf((float)D);
+  const int hq = a.q_heads, hk = a.kv_heads;
+  switch (hq / hk) {
+    case 1: attend_kernel<D, 1><<<grid, kAttnWarps * 32, 0, s>>>(qkv, kv, out, map, hq, hk, scale); break;
+    case 2: attend_kernel<D, 2><<<grid, kAttnWarps * 32, 0, s>>>(qkv, kv, out, map, hq, hk, scale); break;
+    case 4: attend_kernel<D, 4><<<grid, kAttnWarps * 32, 0, s>>>(qkv, kv, out, map, hq, hk, scale); break;
+    case 5: attend_kernel<D, 5><<<grid, kAttnWarps * 32, 0, s>>>(qkv, kv, out, map, hq, hk, scale); break;
+    case 8: attend_kernel<D, 8><<<grid, kAttnWarps * 32, 0, s>>>(qkv, kv, out, map, hq, hk, scale); break;
+    default: return cudaErrorInvalidValue;
+  }
+  return cudaGetLastError();
+}
+
+cudaError_t launch_attend(const bf16* qkv, const bf16* kv, bf16* out, const RowMap& map, int rows, const AttnShape& a,
+                          uint32_t* err, cudaStream_t s) {
+  (void)err;
+  if (a.q_heads % a.kv_heads) return cudaErrorInvalidValue;
+  if (a.head_dim == 128) return launch_attend_d<128>(qkv, kv, out, map, rows, a, s);
+  if (a.head_dim == 64) return launch_attend_d<64>(qkv, kv, out, map, rows, a, s);
+  return cudaErrorInvalidValue;
+}
+
+}  // namespace omni

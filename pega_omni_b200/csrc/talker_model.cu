@@ -1,0 +1,1001 @@
+// Host runtime of the talker token loop and its C ABI (include/omni_b200.h).
+//
+// Mirrors the reference's model shell (crates/omni-qwen3-tts/src/model.rs) and
+// what kern-runtime provides underneath it: weights fused at load, a paged KV
+// pool with leases, per-sequence state slots, batch buckets with a padding
+// lease, host inputs staged in one block, one CUDA graph per (program, bucket),
+// synchronous read-back of the frame.
+#include <algorithm>
+#include <cmath>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <map>
+#include <memory>
+#include <string>
+#include <tuple>
+#include <unordered_map>
+#include <vector>
+
+#include "../../include/omni_b200.h"
+#include "gemm.h"
+#include "kernels.h"
+
+namespace omni {
+
+namespace {
+
+const int kBuckets[] = {1, 2, 4, 8, 12, 16, 24, 32, 48, 64, 96, 128};
+
+int bucket_of(int n) {
+  for (int b : kBuckets)
+    if (b >= n) return b;
+  return (n + 63) / 64 * 64;  // beyond the reference's largest bucket: multiples of 64
+}
+
+__global__ void f32_to_bf16_kernel(const float* __restrict__ src, bf16* __restrict__ dst, int64_t n) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) dst[i] = __float2bfloat16(src[i]);
+}
+
+uint16_t host_f2bf(float f) {
+  uint32_t u;
+  memcpy(&u, &f, 4);
+  if ((u & 0x7fffffffu) > 0x7f800000u) return (uint16_t)((u >> 16) | 0x40);
+  u += 0x7fffu + ((u >> 16) & 1u);
+  return (uint16_t)(u >> 16);
+}
+
+struct StackW {
+  omni_stack_config cfg;
+  struct Layer {
+    bf16 *ln1, *qkv, *q_norm, *k_norm, *o, *ln2, *gate_up, *down;
+  };
+  std::vector<Layer> layers;
+  bf16* norm = nullptr;
+  int qkv_width() const { return (cfg.q_heads + 2 * cfg.kv_heads) * cfg.head_dim; }
+  size_t kv_page_elems() const { return (size_t)cfg.kv_heads * 2 * OMNI_PAGE * cfg.head_dim; }
+  AttnShape attn() const { return AttnShape{cfg.q_heads, cfg.kv_heads, cfg.head_dim, cfg.rms_eps, cfg.rope_theta}; }
+};
+
+struct Scratch {
+  bf16 *x, *res, *qkv, *attn, *gate_up, *act;
+};
+
+}  // namespace
+}  // namespace omni
+
+using namespace omni;
+
+struct omni_seq {
+  std::vector<int32_t> pages;
+  int32_t line = -1;
+  int32_t prompt = 0, frames = 0, cap = 0;
+  uint64_t seed = 0;
+  bool live = false;
+};
+
+struct omni_talker {
+  omni_talker_config cfg;
+  int device = 0, sm_count = 148;
+  cudaStream_t stream = nullptr;
+  cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+  std::string error;
+  std::vector<void*> allocations;
+  int64_t weight_bytes = 0, kv_bytes = 0;
+
+  // weights
+  StackW talker, pred;
+  bf16 *text_emb = nullptr, *codec_emb = nullptr, *codec_head = nullptr;
+  bf16 *fc1_w = nullptr, *fc1_b = nullptr, *fc2_w = nullptr, *fc2_b = nullptr, *mtp_w = nullptr, *mtp_b = nullptr;
+  bf16 *p_emb = nullptr, *lm_heads = nullptr;
+  int text_vocab = 0;
+
+  // pools
+  int max_seqs = 0, max_rows = 0, pages_total = 0, page_table = 0;
+  std::vector<bf16*> kv, pkv;  // per layer
+  std::vector<int32_t> free_pages;
+  std::vector<int32_t> free_lines;
+  int pages_used = 0;
+  char* seq_state = nullptr;
+  int64_t seq_stride = 0;
+  int seen_words = 0;
+  omni_seq pad;
+  std::vector<std::unique_ptr<omni_seq>> seqs;
+
+  // staged inputs: one host (pinned) block mirrored on the device
+  struct Inputs {
+    size_t lines, pos, force, uniforms, indptr, d_pos, d_slot, pages;  // front block: every graph call
+    size_t t_ids, t_codec, t_pos, t_slot, t_seq, last_row;             // prefill only
+    size_t front_fixed_bytes, total_bytes;
+  } in;
+  char* in_host = nullptr;
+  char* in_dev = nullptr;
+  template <typename T>
+  T* hin(size_t off) { return reinterpret_cast<T*>(in_host + off); }
+  template <typename T>
+  T* din(size_t off) { return reinterpret_cast<T*>(in_dev + off); }
+
+  // activations and outputs
+  Scratch T, P;
+  bf16 *t_e = nullptr, *t_p = nullptr, *embeds = nullptr, *hidden = nullptr, *pad_embed = nullptr;
+  bf16 *p_in = nullptr, *p_h = nullptr, *p_last = nullptr;
+  bf16 *logits = nullptr, *p_logits = nullptr;
+  int32_t* codes = nullptr;  // [max_seqs * 16] then the device error word
+  uint32_t* err = nullptr;
+  int32_t* out_host = nullptr;  // pinned mirror of `codes` + error word
+  GemmScratch gemm_scratch;
+
+  std::map<std::tuple<const void*, const void*, const void*, int, int>, TcGemmPlan> plans;
+  std::map<std::pair<int, int>, cudaGraphExec_t> graphs;  // (program, bucket)
+  std::map<std::pair<int, int>, int> graph_nodes;           // kernel nodes of each captured graph
+  int launches = 0;
+  omni_stats stats{};
+  int last_n = 0;
+
+  int fail(int code, const char* fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof(buf), fmt, ap);
+    va_end(ap);
+    error = buf;
+    return code;
+  }
+};
+
+namespace {
+
+#define CUDA_TRY(m, expr)                                                                      \
+  do {                                                                                         \
+    cudaError_t e_ = (expr);                                                                   \
+    if (e_ != cudaSuccess) return (m)->fail(OMNI_ERR_CUDA, "%s: %s", #expr, cudaGetErrorString(e_)); \
+  } while (0)
+
+template <typename T>
+int dev_alloc(omni_talker* m, T** out, size_t count, bool zero = false) {
+  void* p = nullptr;
+  const size_t bytes = std::max<size_t>(count * sizeof(T), 256);
+  cudaError_t e = cudaMalloc(&p, bytes);
+  if (e != cudaSuccess) return m->fail(OMNI_ERR_CUDA, "cudaMalloc(%zu): %s", bytes, cudaGetErrorString(e));
+  if (zero) cudaMemset(p, 0, bytes);
+  m->allocations.push_back(p);
+  *out = static_cast<T*>(p);
+  return OMNI_OK;
+}
+
+struct TensorIndex {
+  std::unordered_map<std::string, const omni_tensor*> by_name;
+  const omni_tensor* find(const std::string& n) const {
+    auto it = by_name.find(n);
+    return it == by_name.end() ? nullptr : it->second;
+  }
+};
+
+// Copies one checkpoint tensor (rounded to bf16) to `dst`; shape must match.
+int upload(omni_talker* m, const TensorIndex& idx, const std::string& name, std::initializer_list<int64_t> shape,
+           bf16* dst) {
+  const omni_tensor* t = idx.find(name);
+  if (!t) return m->fail(OMNI_ERR_MISSING_TENSOR, "missing tensor %s", name.c_str());
+  if (t->ndim != (int)shape.size()) return m->fail(OMNI_ERR_MISSING_TENSOR, "%s: rank %d", name.c_str(), t->ndim);
+  int64_t count = 1;
+  int d = 0;
+  for (int64_t s : shape) {
+    if (t->shape[d] != s)
+      return m->fail(OMNI_ERR_MISSING_TENSOR, "%s: dim %d is %lld, expected %lld", name.c_str(), d,
+                     (long long)t->shape[d], (long long)s);
+    count *= s;
+    ++d;
+  }
+  if (t->location == OMNI_DEVICE) {
+    if (t->dtype == OMNI_BF16) {
+      CUDA_TRY(m, cudaMemcpyAsync(dst, t->data, count * 2, cudaMemcpyDeviceToDevice, m->stream));
+    } else {
+      f32_to_bf16_kernel<<<(unsigned)((count + 255) / 256), 256, 0, m->stream>>>((const float*)t->data, dst, count);
+      CUDA_TRY(m, cudaGetLastError());
+    }
+  } else if (t->dtype == OMNI_BF16) {
+    CUDA_TRY(m, cudaMemcpy(dst, t->data, count * 2, cudaMemcpyHostToDevice));
+  } else {
+    std::vector<uint16_t> tmp(count);
+    const float* src = (const float*)t->data;
+    for (int64_t i = 0; i < count; ++i) tmp[i] = host_f2bf(src[i]);
+    CUDA_TRY(m, cudaMemcpy(dst, tmp.data(), count * 2, cudaMemcpyHostToDevice));
+  }
+  m->weight_bytes += count * 2;
+  return OMNI_OK;
+}
+
+#define TRY(expr)              \
+  do {                         \
+    int rc_ = (expr);          \
+    if (rc_ != OMNI_OK) return rc_; \
+  } while (0)
+
+// `Stack::load` (crates/omni-qwen3/src/stack.rs:93-141): Q|K|V rows and
+// gate|up rows fused into one weight each.
+int load_stack(omni_talker* m, const TensorIndex& idx, const std::string& prefix, const omni_stack_config& c,
+               StackW* out) {
+  out->cfg = c;
+  const int64_t h = c.hidden, d = c.head_dim, q = (int64_t)c.q_heads * d, kv = (int64_t)c.kv_heads * d, I = c.inter;
+  out->layers.resize(c.layers);
+  for (int i = 0; i < c.layers; ++i) {
+    const std::string p = prefix + ".layers." + std::to_string(i) + ".";
+    StackW::Layer& L = out->layers[i];
+    TRY(dev_alloc(m, &L.ln1, h));
+    TRY(dev_alloc(m, &L.qkv, (q + 2 * kv) * h));
+    TRY(dev_alloc(m, &L.q_norm, d));
+    TRY(dev_alloc(m, &L.k_norm, d));
+    TRY(dev_alloc(m, &L.o, h * q));
+    TRY(dev_alloc(m, &L.ln2, h));
+    TRY(dev_alloc(m, &L.gate_up, 2 * I * h));
+    TRY(dev_alloc(m, &L.down, h * I));
+    TRY(upload(m, idx, p + "input_layernorm.weight", {h}, L.ln1));
+    TRY(upload(m, idx, p + "self_attn.q_proj.weight", {q, h}, L.qkv));
+    TRY(upload(m, idx, p + "self_attn.k_proj.weight", {kv, h}, L.qkv + q * h));
+    TRY(upload(m, idx, p + "self_attn.v_proj.weight", {kv, h}, L.qkv + (q + kv) * h));
+    TRY(upload(m, idx, p + "self_attn.q_norm.weight", {d}, L.q_norm));
+    TRY(upload(m, idx, p + "self_attn.k_norm.weight", {d}, L.k_norm));
+    TRY(upload(m, idx, p + "self_attn.o_proj.weight", {h, q}, L.o));
+    TRY(upload(m, idx, p + "post_attention_layernorm.weight", {h}, L.ln2));
+    TRY(upload(m, idx, p + "mlp.gate_proj.weight", {I, h}, L.gate_up));
+    TRY(upload(m, idx, p + "mlp.up_proj.weight", {I, h}, L.gate_up + I * h));
+    TRY(upload(m, idx, p + "mlp.down_proj.weight", {h, I}, L.down));
+  }
+  TRY(dev_alloc(m, &out->norm, h));
+  TRY(upload(m, idx, prefix + ".norm.weight", {h}, out->norm));
+  return OMNI_OK;
+}
+
+int alloc_scratch(omni_talker* m, const StackW& s, int rows, Scratch* out) {
+  const omni_stack_config& c = s.cfg;
+  TRY(dev_alloc(m, &out->x, (size_t)rows * c.hidden));
+  TRY(dev_alloc(m, &out->res, (size_t)rows * c.hidden));
+  TRY(dev_alloc(m, &out->qkv, (size_t)rows * s.qkv_width()));
+  TRY(dev_alloc(m, &out->attn, (size_t)rows * c.q_heads * c.head_dim));
+  TRY(dev_alloc(m, &out->gate_up, (size_t)rows * 2 * c.inter));
+  TRY(dev_alloc(m, &out->act, (size_t)rows * c.inter));
+  return OMNI_OK;
+}
+
+// ---- launching ---------------------------------------------------------------------
+
+#define LAUNCH(m, expr)                                                                        \
+  do {                                                                                         \
+    cudaError_t e_ = (expr);                                                                   \
+    ++(m)->launches;                                                                           \
+    if (e_ != cudaSuccess) return (m)->fail(OMNI_ERR_CUDA, "%s: %s", #expr, cudaGetErrorString(e_)); \
+  } while (0)
+
+// y[rows, N] = x[rows, K] . w[N, K]^T on the path the row count calls for.
+int gemm(omni_talker* m, const bf16* w, int N, int K, const bf16* x, int rows, bf16* y, int ldy, Epilogue epi = {}) {
+  const bool vector_path = m->cfg.gemm_path == 1 || rows <= 8 || !tc_supports(N, K, rows);
+  if (vector_path) {
+    LAUNCH(m, gemv_launch(w, N, K, x, rows, y, ldy, epi, m->sm_count, m->stream));
+    return OMNI_OK;
+  }
+  const auto key = std::make_tuple((const void*)w, (const void*)x, (const void*)y, rows, epi.kind);
+  auto it = m->plans.find(key);
+  if (it == m->plans.end()) {
+    TcGemmPlan plan;
+    const int rc = tc_plan(&plan, w, N, K, x, rows, y, ldy, epi, m->sm_count);
+    if (rc != 0) return m->fail(OMNI_ERR_CUDA, "tensor-map encode failed (%d) for N=%d K=%d rows=%d", rc, N, K, rows);
+    if (plan.partial_floats() > m->gemm_scratch.partial_floats ||
+        plan.tiles_n() * plan.row_tiles > m->gemm_scratch.counter_slots)
+      return m->fail(OMNI_ERR_UNSUPPORTED, "split-K scratch too small for N=%d K=%d rows=%d", N, K, rows);
+    it = m->plans.emplace(key, plan).first;
+  }
+  LAUNCH(m, tc_launch(it->second, m->gemm_scratch, m->err, m->stream));
+  return OMNI_OK;
+}
+
+// One pass of a decoder stack: op order of `Stack::forward`
+// (crates/omni-qwen3/src/stack.rs:152-203).
+int stack_forward(omni_talker* m, const StackW& S, const Scratch& s, const bf16* input, int rows, const RowMap& map,
+                  const std::vector<bf16*>& kv, int kv_pages, bf16* keep_out, int every, int which) {
+  const omni_stack_config& c = S.cfg;
+  const int h = c.hidden, I = c.inter, qd = c.q_heads * c.head_dim;
+  const AttnShape a = S.attn();
+  LAUNCH(m, launch_norm_copy(input, S.layers[0].ln1, s.x, s.res, rows, h, c.rms_eps, m->stream));
+  for (int i = 0; i < c.layers; ++i) {
+    const StackW::Layer& L = S.layers[i];
+    TRY(gemm(m, L.qkv, S.qkv_width(), h, s.x, rows, s.qkv, S.qkv_width()));
+    LAUNCH(m, launch_rope_kv(s.qkv, L.q_norm, L.k_norm, kv[i], map, rows, a, kv_pages, m->err, m->stream));
+    LAUNCH(m, launch_attend(s.qkv, kv[i], s.attn, map, rows, a, m->err, m->stream));
+    TRY(gemm(m, L.o, h, qd, s.attn, rows, s.x, h));
+    LAUNCH(m, launch_add_norm(s.x, s.res, L.ln2, s.x, rows, h, c.rms_eps, 1, 0, m->stream));
+    TRY(gemm(m, L.gate_up, 2 * I, h, s.x, rows, s.gate_up, 2 * I));
+    LAUNCH(m, launch_silu_mul(s.gate_up, s.act, rows, I, m->stream));
+    TRY(gemm(m, L.down, h, I, s.act, rows, s.x, h));
+    if (i + 1 < c.layers)
+      LAUNCH(m, launch_add_norm(s.x, s.res, S.layers[i + 1].ln1, s.x, rows, h, c.rms_eps, 1, 0, m->stream));
+    else
+      LAUNCH(m, launch_add_norm(s.x, s.res, S.norm, keep_out, rows, h, c.rms_eps, every, which, m->stream));
+  }
+  return OMNI_OK;
+}
+
+SlotState slots(omni_talker* m) { return SlotState{m->seq_state, m->din<int32_t>(m->in.lines), m->seq_stride}; }
+
+// `Talker::sample` (crates/omni-qwen3-tts/src/talker.rs:254-290).
+int sample(omni_talker* m, int group, const bf16* logits, int rows) {
+  const omni_talker_config& c = m->cfg;
+  SampleParams p{};
+  p.group = group;
+  p.top_p = c.top_p;
+  p.philox = c.sampler == OMNI_SAMPLER_PHILOX;
+  p.seen_words = m->seen_words;
+  if (group == 0) {
+    p.vocab = c.talker.vocab;
+    p.temperature = c.temperature;
+    p.top_k = c.top_k;
+    p.penalty = c.repetition_penalty;
+    p.suppress_lo = c.talker.vocab - c.control_tokens;
+    p.suppress_hi = c.talker.vocab;
+    p.exempt = c.codec_eos_token_id;
+    p.min_frames = c.min_frames;
+    p.penalize = 1;
+  } else {
+    p.vocab = c.predictor.vocab;
+    p.temperature = c.sub_temperature;
+    p.top_k = c.sub_top_k;
+    p.penalty = 1.f;
+    p.suppress_lo = p.suppress_hi = 0;
+    p.exempt = -1;
+    p.min_frames = 0;
+    p.penalize = 0;
+  }
+  LAUNCH(m, launch_sample(logits, p, m->din<int32_t>(m->in.pos), m->din<float>(m->in.uniforms),
+                          m->din<int32_t>(m->in.force), slots(m), m->codes, rows, m->stream));
+  return OMNI_OK;
+}
+
+// `Talker::advance` (talker.rs:224-251): the last frame's embedding through the talker.
+int enqueue_advance(omni_talker* m, int b) {
+  const omni_talker_config& c = m->cfg;
+  const int h = c.talker.hidden;
+  LAUNCH(m, launch_frame_embed(slots(m), m->pad_embed, m->codec_emb, c.talker.vocab, m->p_emb, c.predictor.vocab,
+                               c.groups, m->t_e, b, h, m->err, m->stream));
+  RowMap map;
+  map.pos = m->din<int32_t>(m->in.d_pos);
+  map.slot = m->din<int32_t>(m->in.d_slot);
+  map.seq = nullptr;
+  map.indptr = m->din<int32_t>(m->in.indptr);
+  map.pages = m->din<int32_t>(m->in.pages);
+  return stack_forward(m, m->talker, m->T, m->t_e, b, map, m->kv, m->pages_total, m->hidden, 1, 0);
+}
+
+// `Talker::tail` (talker.rs:293-356).
+int enqueue_tail(omni_talker* m, int b) {
+  const omni_talker_config& c = m->cfg;
+  const int h = c.talker.hidden, p = c.predictor.hidden, V = c.talker.vocab, PV = c.predictor.vocab;
+  TRY(gemm(m, m->codec_head, V, h, m->hidden, b, m->logits, V));
+  TRY(sample(m, 0, m->logits, b));
+  LAUNCH(m, launch_pred_input(m->hidden, m->codec_emb, V, m->codes, m->p_in, b, h, m->err, m->stream));
+  Epilogue bias;
+  bias.bias = m->mtp_b;
+  bias.kind = kEpiBias;
+  for (int g = 1; g < c.groups; ++g) {
+    const int per = g == 1 ? 2 : 1, rows = b * per;
+    if (g > 1)
+      LAUNCH(m, launch_gather(m->codes + (g - 1), OMNI_GROUPS, m->p_emb + (size_t)(g - 2) * PV * h, PV, m->p_in, b, h,
+                              m->err, m->stream));
+    TRY(gemm(m, m->mtp_w, p, h, m->p_in, rows, m->p_h, p, bias));
+    RowMap map;
+    map.per = per;
+    map.base = g == 1 ? 0 : g;
+    TRY(stack_forward(m, m->pred, m->P, m->p_h, rows, map, m->pkv, m->max_seqs, m->p_last, per, per - 1));
+    bf16* lg = m->p_logits + (size_t)(g - 1) * m->max_seqs * PV;
+    TRY(gemm(m, m->lm_heads + (size_t)(g - 1) * PV * p, PV, p, m->p_last, b, lg, PV));
+    TRY(sample(m, g, lg, b));
+  }
+  return OMNI_OK;
+}
+
+enum Program { kFirst = 0, kDecode = 1 };
+
+int enqueue_program(omni_talker* m, int program, int b) {
+  if (program == kDecode) TRY(enqueue_advance(m, b));
+  return enqueue_tail(m, b);
+}
+
+// Runs a graph program at bucket b: replay of its captured graph, or eager launches.
+int run_program(omni_talker* m, int program, int b) {
+  m->launches = 0;
+  if (!m->cfg.use_graphs) return enqueue_program(m, program, b);
+  auto key = std::make_pair(program, b);
+  auto it = m->graphs.find(key);
+  if (it == m->graphs.end()) {
+    CUDA_TRY(m, cudaStreamBeginCapture(m->stream, cudaStreamCaptureModeThreadLocal));
+    const int rc = enqueue_program(m, program, b);
+    cudaGraph_t graph = nullptr;
+    cudaError_t e = cudaStreamEndCapture(m->stream, &graph);
+    if (rc != OMNI_OK) {
+      if (graph) cudaGraphDestroy(graph);
+      return rc;
+    }
+    if (e != cudaSuccess) return m->fail(OMNI_ERR_CUDA, "graph capture: %s", cudaGetErrorString(e));
+    cudaGraphExec_t exec = nullptr;
+    e = cudaGraphInstantiate(&exec, graph, 0);
+    cudaGraphDestroy(graph);
+    if (e != cudaSuccess) return m->fail(OMNI_ERR_CUDA, "graph instantiate: %s", cudaGetErrorString(e));
+    it = m->graphs.emplace(key, exec).first;
+    m->stats.bucket = b;
+    m->graph_nodes[key] = m->launches;
+  }
+  m->launches = m->graph_nodes[key];
+  CUDA_TRY(m, cudaGraphLaunch(it->second, m->stream));
+  return OMNI_OK;
+}
+
+}  // namespace
+
+namespace {
+
+size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+// Offsets of the staged inputs (names of crates/omni-qwen3-tts/src/model.rs:266-303,348-359).
+void layout_inputs(omni_talker* m) {
+  auto& in = m->in;
+  const size_t B = m->max_seqs, T = m->max_rows;
+  size_t at = 0;
+  auto take = [&](size_t bytes) {
+    const size_t here = at;
+    at = align_up(at + bytes, 16);
+    return here;
+  };
+  in.lines = take(B * 4);
+  in.pos = take(B * 4);
+  in.force = take(B * OMNI_GROUPS * 4);
+  in.uniforms = take(B * OMNI_GROUPS * 4);
+  in.indptr = take((B + 1) * 4);
+  in.d_pos = take(B * 4);
+  in.d_slot = take(B * 4);
+  in.front_fixed_bytes = at;
+  in.pages = take((size_t)m->page_table * 4);
+  in.t_ids = take(T * 4);
+  in.t_codec = take(T * 4);
+  in.t_pos = take(T * 4);
+  in.t_slot = take(T * 4);
+  in.t_seq = take(T * 4);
+  in.last_row = take(B * 4);
+  in.total_bytes = at;
+}
+
+int32_t slot_of_seq(const omni_seq& s, int pos) { return s.pages[pos / OMNI_PAGE] * OMNI_PAGE + pos % OMNI_PAGE; }
+
+struct FrameRow {
+  const omni_seq* seq;
+  int position;  // talker position the last frame goes in
+  int frame;     // index of the frame this call draws
+  const omni_draw* draw;
+};
+
+// `Model::graph_inputs` (model.rs:197-218): per-sequence inputs of a graph call
+// padded to its bucket with the pad lease; returns the bytes of the front
+// block (fixed part + the page lists) to copy.
+size_t stage_graph_inputs(omni_talker* m, char* host, const std::vector<FrameRow>& rows, int b, bool talker) {
+  auto& in = m->in;
+  int32_t* lines = reinterpret_cast<int32_t*>(host + in.lines);
+  int32_t* pos = reinterpret_cast<int32_t*>(host + in.pos);
+  int32_t* force = reinterpret_cast<int32_t*>(host + in.force);
+  float* uniforms = reinterpret_cast<float*>(host + in.uniforms);
+  int32_t* indptr = reinterpret_cast<int32_t*>(host + in.indptr);
+  int32_t* d_pos = reinterpret_cast<int32_t*>(host + in.d_pos);
+  int32_t* d_slot = reinterpret_cast<int32_t*>(host + in.d_slot);
+  int32_t* pages = reinterpret_cast<int32_t*>(host + in.pages);
+  int np = 0;
+  indptr[0] = 0;
+  for (int s = 0; s < b; ++s) {
+    const bool real = s < (int)rows.size();
+    const omni_seq& q = real ? *rows[s].seq : m->pad;
+    lines[s] = q.line;
+    pos[s] = real ? rows[s].frame : 0;
+    for (int g = 0; g < OMNI_GROUPS; ++g) {
+      uniforms[s * OMNI_GROUPS + g] = real ? rows[s].draw->uniforms[g] : 0.5f;
+      force[s * OMNI_GROUPS + g] = real ? rows[s].draw->force[g] : -1;
+    }
+    const int position = real ? rows[s].position : 0;
+    d_pos[s] = position;
+    d_slot[s] = slot_of_seq(q, position);
+    if (talker) {
+      // only the pages up to the row's position are read
+      const int used = position / OMNI_PAGE + 1;
+      for (int i = 0; i < used; ++i) pages[np++] = q.pages[i];
+    }
+    indptr[s + 1] = np;
+  }
+  return in.pages + (size_t)np * 4;
+}
+
+int finish_call(omni_talker* m, int n, int32_t* codes, float* wav) {
+  CUDA_TRY(m, cudaMemcpyAsync(m->out_host, m->codes, ((size_t)m->max_seqs * OMNI_GROUPS + 1) * 4,
+                              cudaMemcpyDeviceToHost, m->stream));
+  CUDA_TRY(m, cudaEventRecord(m->ev1, m->stream));
+  CUDA_TRY(m, cudaStreamSynchronize(m->stream));
+  cudaEventElapsedTime(&m->stats.last_call_gpu_ms, m->ev0, m->ev1);
+  m->stats.last_call_launches = m->launches;
+  const uint32_t err = (uint32_t)m->out_host[(size_t)m->max_seqs * OMNI_GROUPS];
+  if (err != 0) {
+    cudaMemsetAsync(m->err, 0, 4, m->stream);
+    cudaStreamSynchronize(m->stream);
+    return m->fail(OMNI_ERR_DEVICE, "device error word 0x%x (1: barrier wait ran out, 2: index out of range)", err);
+  }
+  memcpy(codes, m->out_host, (size_t)n * OMNI_GROUPS * 4);
+  if (wav) memset(wav, 0, (size_t)n * 1920 * sizeof(float));
+  m->last_n = n;
+  return OMNI_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* omni_version(void) { return "omni_b200 0.1 (sm_100a)"; }
+
+int32_t omni_bucket(int32_t n) { return bucket_of(n); }
+
+const char* omni_talker_last_error(const omni_talker* m) { return m ? m->error.c_str() : "null model"; }
+
+void omni_talker_destroy(omni_talker* m) {
+  if (!m) return;
+  cudaSetDevice(m->device);
+  if (m->stream) cudaStreamSynchronize(m->stream);
+  for (auto& g : m->graphs) cudaGraphExecDestroy(g.second);
+  for (void* p : m->allocations) cudaFree(p);
+  if (m->in_host) cudaFreeHost(m->in_host);
+  if (m->out_host) cudaFreeHost(m->out_host);
+  if (m->ev0) cudaEventDestroy(m->ev0);
+  if (m->ev1) cudaEventDestroy(m->ev1);
+  if (m->stream) cudaStreamDestroy(m->stream);
+  delete m;
+}
+
+static int create_impl(omni_talker* m, const omni_tensor* tensors, int32_t n_tensors) {
+  const omni_talker_config& c = m->cfg;
+  const omni_stack_config &t = c.talker, &pc = c.predictor;
+  if (c.groups < 2 || c.groups > OMNI_GROUPS) return m->fail(OMNI_ERR_UNSUPPORTED, "groups %d", c.groups);
+  if (t.vocab > 4096 || pc.vocab > 4096) return m->fail(OMNI_ERR_UNSUPPORTED, "the sampler takes vocabularies up to 4096");
+  for (const omni_stack_config* s : {&t, &pc}) {
+    if (s->head_dim != 64 && s->head_dim != 128) return m->fail(OMNI_ERR_UNSUPPORTED, "head_dim %d", s->head_dim);
+    if (s->hidden % 8 || s->hidden > 8192 || s->inter % 8) return m->fail(OMNI_ERR_UNSUPPORTED, "hidden %d", s->hidden);
+    const int g = s->kv_heads > 0 ? s->q_heads / s->kv_heads : 0;
+    if (g * s->kv_heads != s->q_heads || !(g == 1 || g == 2 || g == 4 || g == 5 || g == 8))
+      return m->fail(OMNI_ERR_UNSUPPORTED, "%d query heads over %d key heads", s->q_heads, s->kv_heads);
+  }
+  if (c.max_batch < 1 || c.max_tokens < 1) return m->fail(OMNI_ERR_INVALID, "limits");
+  if (c.top_p < 1.f && (c.top_k <= 0 || c.top_k > 512 || c.sub_top_k <= 0 || c.sub_top_k > 512))
+    return m->fail(OMNI_ERR_UNSUPPORTED, "top_p < 1 needs 0 < top_k <= 512");
+
+  CUDA_TRY(m, cudaSetDevice(m->device));
+  cudaDeviceProp prop;
+  CUDA_TRY(m, cudaGetDeviceProperties(&prop, m->device));
+  if (prop.major != 10) return m->fail(OMNI_ERR_UNSUPPORTED, "device %d is sm_%d%d; this library is sm_100a only", m->device, prop.major, prop.minor);
+  m->sm_count = prop.multiProcessorCount;
+  CUDA_TRY(m, cudaStreamCreateWithFlags(&m->stream, cudaStreamNonBlocking));
+  CUDA_TRY(m, cudaEventCreate(&m->ev0));
+  CUDA_TRY(m, cudaEventCreate(&m->ev1));
+  if (tc_init() != 0) return m->fail(OMNI_ERR_CUDA, "cuTensorMapEncodeTiled entry point not found");
+  tc_configure();
+
+  TensorIndex idx;
+  for (int i = 0; i < n_tensors; ++i) idx.by_name[tensors[i].name] = &tensors[i];
+  const int64_t h = t.hidden, p = pc.hidden, V = t.vocab, PV = pc.vocab, G = c.groups;
+  const omni_tensor* te = idx.find("talker.model.text_embedding.weight");
+  if (!te || te->ndim != 2) return m->fail(OMNI_ERR_MISSING_TENSOR, "missing tensor talker.model.text_embedding.weight");
+  m->text_vocab = (int)te->shape[0];
+  if (c.tts_pad_token_id < 0 || c.tts_pad_token_id >= m->text_vocab) return m->fail(OMNI_ERR_INVALID, "tts_pad_token_id");
+
+  TRY(dev_alloc(m, &m->text_emb, (size_t)m->text_vocab * h));
+  TRY(upload(m, idx, "talker.model.text_embedding.weight", {m->text_vocab, h}, m->text_emb));
+  TRY(dev_alloc(m, &m->codec_emb, V * h));
+  TRY(upload(m, idx, "talker.model.codec_embedding.weight", {V, h}, m->codec_emb));
+  TRY(dev_alloc(m, &m->codec_head, V * h));
+  TRY(upload(m, idx, "talker.codec_head.weight", {V, h}, m->codec_head));
+  TRY(dev_alloc(m, &m->fc1_w, h * h));
+  TRY(dev_alloc(m, &m->fc1_b, h));
+  TRY(dev_alloc(m, &m->fc2_w, h * h));
+  TRY(dev_alloc(m, &m->fc2_b, h));
+  TRY(upload(m, idx, "talker.text_projection.linear_fc1.weight", {h, h}, m->fc1_w));
+  TRY(upload(m, idx, "talker.text_projection.linear_fc1.bias", {h}, m->fc1_b));
+  TRY(upload(m, idx, "talker.text_projection.linear_fc2.weight", {h, h}, m->fc2_w));
+  TRY(upload(m, idx, "talker.text_projection.linear_fc2.bias", {h}, m->fc2_b));
+  TRY(dev_alloc(m, &m->mtp_w, p * h));
+  TRY(dev_alloc(m, &m->mtp_b, p));
+  TRY(upload(m, idx, "talker.code_predictor.small_to_mtp_projection.weight", {p, h}, m->mtp_w));
+  TRY(upload(m, idx, "talker.code_predictor.small_to_mtp_projection.bias", {p}, m->mtp_b));
+  // the predictor's G-1 embedding tables and heads stacked (talker.rs:85-93,119-130)
+  TRY(dev_alloc(m, &m->p_emb, (G - 1) * PV * h));
+  TRY(dev_alloc(m, &m->lm_heads, (G - 1) * PV * p));
+  for (int g = 0; g < G - 1; ++g) {
+    TRY(upload(m, idx, "talker.code_predictor.model.codec_embedding." + std::to_string(g) + ".weight", {PV, h},
+               m->p_emb + (size_t)g * PV * h));
+    TRY(upload(m, idx, "talker.code_predictor.lm_head." + std::to_string(g) + ".weight", {PV, p},
+               m->lm_heads + (size_t)g * PV * p));
+  }
+  TRY(load_stack(m, idx, "talker.model", t, &m->talker));
+  TRY(load_stack(m, idx, "talker.code_predictor.model", pc, &m->pred));
+
+  // pools (model.rs:111-131,306-309)
+  m->max_seqs = bucket_of(c.max_batch);
+  m->max_rows = std::max(c.max_tokens, 2 * m->max_seqs);
+  const size_t kv_token_bytes = (size_t)t.layers * 2 * t.kv_heads * t.head_dim * 2;
+  const size_t kv_tokens = (size_t)(c.kv_gib * (double)(1ull << 30)) / kv_token_bytes;
+  m->pages_total = (int)((kv_tokens + OMNI_PAGE - 1) / OMNI_PAGE) + 1;
+  m->page_table = m->pages_total + m->max_seqs;
+  m->kv.resize(t.layers);
+  for (int i = 0; i < t.layers; ++i) TRY(dev_alloc(m, &m->kv[i], (size_t)m->pages_total * m->talker.kv_page_elems(), true));
+  m->kv_bytes = (int64_t)t.layers * m->pages_total * m->talker.kv_page_elems() * 2;
+  m->pkv.resize(pc.layers);
+  for (int i = 0; i < pc.layers; ++i) TRY(dev_alloc(m, &m->pkv[i], (size_t)m->max_seqs * m->pred.kv_page_elems(), true));
+  for (int i = m->pages_total - 1; i >= 0; --i) m->free_pages.push_back(i);
+  // per-sequence slot: last frame, repetition bitmap, Philox seed
+  m->seen_words = (int)((V + 31) / 32);
+  m->seq_stride = (int64_t)align_up(4 * (OMNI_GROUPS + m->seen_words + (m->seen_words & 1)) + 8, 256);
+  const int lines = c.max_batch + 1;
+  TRY(dev_alloc(m, &m->seq_state, (size_t)lines * m->seq_stride, true));
+  for (int i = lines - 1; i >= 0; --i) m->free_lines.push_back(i);
+
+  layout_inputs(m);
+  CUDA_TRY(m, cudaHostAlloc((void**)&m->in_host, m->in.total_bytes, cudaHostAllocDefault));
+  memset(m->in_host, 0, m->in.total_bytes);
+  TRY(dev_alloc(m, &m->in_dev, m->in.total_bytes, true));
+  CUDA_TRY(m, cudaHostAlloc((void**)&m->out_host, ((size_t)m->max_seqs * OMNI_GROUPS + 1) * 4, cudaHostAllocDefault));
+
+  TRY(alloc_scratch(m, m->talker, m->max_rows, &m->T));
+  TRY(alloc_scratch(m, m->pred, 2 * m->max_seqs, &m->P));
+  TRY(dev_alloc(m, &m->t_e, (size_t)m->max_rows * h));
+  TRY(dev_alloc(m, &m->t_p, (size_t)m->max_rows * h));
+  TRY(dev_alloc(m, &m->embeds, (size_t)m->max_rows * h));
+  TRY(dev_alloc(m, &m->hidden, (size_t)m->max_seqs * h, true));
+  TRY(dev_alloc(m, &m->pad_embed, h));
+  TRY(dev_alloc(m, &m->p_in, (size_t)2 * m->max_seqs * h));
+  TRY(dev_alloc(m, &m->p_h, (size_t)2 * m->max_seqs * p));
+  TRY(dev_alloc(m, &m->p_last, (size_t)m->max_seqs * p));
+  TRY(dev_alloc(m, &m->logits, (size_t)m->max_seqs * V, true));
+  TRY(dev_alloc(m, &m->p_logits, (size_t)(G - 1) * m->max_seqs * PV, true));
+  TRY(dev_alloc(m, &m->codes, (size_t)m->max_seqs * OMNI_GROUPS + 1, true));
+  m->err = reinterpret_cast<uint32_t*>(m->codes + (size_t)m->max_seqs * OMNI_GROUPS);
+  // split-K scratch: the widest N the loop multiplies times the tallest row tile, with headroom for splits
+  {
+    const size_t widest = std::max<size_t>({(size_t)m->talker.qkv_width(), (size_t)2 * t.inter, (size_t)h, (size_t)V,
+                                            (size_t)2 * pc.inter, (size_t)m->pred.qkv_width(), (size_t)PV});
+    m->gemm_scratch.partial_floats = (size_t)(widest + 128) * 256 * 16;
+    m->gemm_scratch.counter_slots = 4096;
+    TRY(dev_alloc(m, &m->gemm_scratch.partials, m->gemm_scratch.partial_floats));
+    TRY(dev_alloc(m, &m->gemm_scratch.counters, (size_t)m->gemm_scratch.counter_slots, true));
+  }
+
+  // the pad lease: one page, one slot (model.rs:130)
+  m->pad.pages = {m->free_pages.back()};
+  m->free_pages.pop_back();
+  m->pad.line = m->free_lines.back();
+  m->free_lines.pop_back();
+  m->pad.live = true;
+  m->pad.cap = OMNI_PAGE;
+  m->pages_used = 1;
+
+  // `Talker::init` (talker.rs:169-183): the <tts_pad> embedding through the text projection
+  {
+    int32_t* ids = m->hin<int32_t>(m->in.t_ids);
+    ids[0] = c.tts_pad_token_id;
+    CUDA_TRY(m, cudaMemcpyAsync(m->din<int32_t>(m->in.t_ids), ids, 4, cudaMemcpyHostToDevice, m->stream));
+    LAUNCH(m, launch_gather(m->din<int32_t>(m->in.t_ids), 1, m->text_emb, m->text_vocab, m->t_e, 1, (int)h, m->err,
+                            m->stream));
+    Epilogue e1, e2;
+    e1.bias = m->fc1_b, e1.kind = kEpiBiasSilu;
+    e2.bias = m->fc2_b, e2.kind = kEpiBias;
+    TRY(gemm(m, m->fc1_w, (int)h, (int)h, m->t_e, 1, m->t_p, (int)h, e1));
+    TRY(gemm(m, m->fc2_w, (int)h, (int)h, m->t_p, 1, m->pad_embed, (int)h, e2));
+    CUDA_TRY(m, cudaStreamSynchronize(m->stream));
+  }
+  return OMNI_OK;
+}
+
+int32_t omni_talker_create(const omni_talker_config* cfg, const omni_tensor* tensors, int32_t n_tensors,
+                           int32_t device, omni_talker** out) {
+  if (!cfg || !tensors || !out) return OMNI_ERR_INVALID;
+  omni_talker* m = new omni_talker();
+  m->cfg = *cfg;
+  m->device = device;
+  const int rc = create_impl(m, tensors, n_tensors);
+  *out = m;  // returned even on failure so the caller can read the error; destroy() frees it
+  return rc;
+}
+
+int32_t omni_talker_open(omni_talker* m, int32_t prompt_tokens, int32_t max_frames, omni_seq** out) {
+  if (!m || !out || prompt_tokens < 1 || max_frames < 1) return OMNI_ERR_INVALID;
+  *out = nullptr;
+  const int need = (prompt_tokens + max_frames + OMNI_PAGE - 1) / OMNI_PAGE;
+  // model.rs:141-144: a request that could never fit beside the pad lease is refused for good
+  if (need + (int)m->pad.pages.size() > m->pages_total) return OMNI_DENIED_EXCEEDS_POOL;
+  if (need > (int)m->free_pages.size() || m->free_lines.empty()) return OMNI_DENIED_BUSY;
+  auto s = std::make_unique<omni_seq>();
+  for (int i = 0; i < need; ++i) {
+    s->pages.push_back(m->free_pages.back());
+    m->free_pages.pop_back();
+  }
+  s->line = m->free_lines.back();
+  m->free_lines.pop_back();
+  s->prompt = prompt_tokens;
+  s->cap = prompt_tokens + max_frames;
+  s->live = true;
+  m->pages_used += need;
+  // a fresh slot starts zeroed: empty repetition bitmap, frame of zeros, seed 0
+  cudaSetDevice(m->device);
+  CUDA_TRY(m, cudaMemsetAsync(m->seq_state + (size_t)s->line * m->seq_stride, 0, m->seq_stride, m->stream));
+  *out = s.get();
+  m->seqs.push_back(std::move(s));
+  return OMNI_OK;
+}
+
+int32_t omni_talker_close(omni_talker* m, omni_seq* seq) {
+  if (!m || !seq || !seq->live) return OMNI_ERR_INVALID;
+  for (size_t i = 0; i < m->seqs.size(); ++i) {
+    if (m->seqs[i].get() != seq) continue;
+    for (int32_t p : seq->pages) m->free_pages.push_back(p);
+    m->free_lines.push_back(seq->line);
+    m->pages_used -= (int)seq->pages.size();
+    m->seqs.erase(m->seqs.begin() + i);
+    return OMNI_OK;
+  }
+  return OMNI_ERR_INVALID;
+}
+
+int32_t omni_talker_seq_seed(omni_talker* m, omni_seq* seq, uint64_t seed) {
+  if (!m || !seq || !seq->live) return OMNI_ERR_INVALID;
+  seq->seed = seed;
+  const size_t off = (size_t)seq->line * m->seq_stride + 4 * (OMNI_GROUPS + m->seen_words + (m->seen_words & 1));
+  CUDA_TRY(m, cudaMemcpyAsync(m->seq_state + off, &seq->seed, 8, cudaMemcpyHostToDevice, m->stream));
+  CUDA_TRY(m, cudaStreamSynchronize(m->stream));
+  return OMNI_OK;
+}
+
+int32_t omni_talker_seq_frames(const omni_seq* seq) { return seq ? seq->frames : -1; }
+
+int32_t omni_talker_is_end(const omni_talker* m, const int32_t* frame) {
+  return m && frame && frame[0] == m->cfg.codec_eos_token_id;
+}
+
+int32_t omni_talker_start(omni_talker* m, int32_t n, omni_seq* const* seqs, const int32_t* text_ids,
+                          const int32_t* codec_ids, const int32_t* prompt_lens, const omni_draw* draws,
+                          int32_t* codes, float* wav) {
+  if (!m || !seqs || !text_ids || !codec_ids || !prompt_lens || !draws || !codes) return OMNI_ERR_INVALID;
+  const omni_talker_config& c = m->cfg;
+  if (n < 1 || n > c.max_batch) return m->fail(OMNI_ERR_INVALID, "%d sequences in one call", n);
+  int64_t tokens = 0;
+  for (int s = 0; s < n; ++s) {
+    if (!seqs[s] || !seqs[s]->live || seqs[s]->frames != 0 || prompt_lens[s] != seqs[s]->prompt)
+      return m->fail(OMNI_ERR_INVALID, "sequence %d is not fresh", s);
+    for (int r = 0; r < s; ++r)
+      if (seqs[r] == seqs[s]) return m->fail(OMNI_ERR_INVALID, "sequence %d listed twice", s);
+    tokens += prompt_lens[s];
+  }
+  if (tokens > c.max_tokens) return m->fail(OMNI_ERR_INVALID, "%lld prompt tokens exceed %d", (long long)tokens, c.max_tokens);
+  for (int64_t r = 0; r < tokens; ++r) {
+    if (text_ids[r] < 0 || text_ids[r] >= m->text_vocab) return m->fail(OMNI_ERR_INVALID, "text id %d at row %lld", text_ids[r], (long long)r);
+    if (codec_ids[r] < -1 || codec_ids[r] >= c.talker.vocab) return m->fail(OMNI_ERR_INVALID, "codec id %d at row %lld", codec_ids[r], (long long)r);
+  }
+  for (int s = 0; s < n; ++s)
+    for (int g = 0; g < OMNI_GROUPS; ++g)
+      if (draws[s].force[g] >= (g == 0 ? c.talker.vocab : c.predictor.vocab))
+        return m->fail(OMNI_ERR_INVALID, "forced code %d of group %d", draws[s].force[g], g);
+  CUDA_TRY(m, cudaSetDevice(m->device));
+
+  // `Rows::push_seq` (model.rs:278-289): one row per prompt token
+  auto& in = m->in;
+  int32_t *t_ids = m->hin<int32_t>(in.t_ids), *t_codec = m->hin<int32_t>(in.t_codec), *t_pos = m->hin<int32_t>(in.t_pos),
+          *t_slot = m->hin<int32_t>(in.t_slot), *t_seq = m->hin<int32_t>(in.t_seq), *last_row = m->hin<int32_t>(in.last_row),
+          *indptr = m->hin<int32_t>(in.indptr), *pages = m->hin<int32_t>(in.pages);
+  int row = 0, np = 0;
+  indptr[0] = 0;
+  for (int s = 0; s < n; ++s) {
+    const omni_seq& q = *seqs[s];
+    for (int t = 0; t < q.prompt; ++t, ++row) {
+      t_ids[row] = text_ids[row];
+      t_codec[row] = codec_ids[row];
+      t_pos[row] = t;
+      t_slot[row] = slot_of_seq(q, t);
+      t_seq[row] = s;
+    }
+    last_row[s] = row - 1;
+    for (int32_t p : q.pages) pages[np++] = p;
+    indptr[s + 1] = np;
+  }
+  const int T = (int)tokens, h = c.talker.hidden;
+  CUDA_TRY(m, cudaEventRecord(m->ev0, m->stream));
+  CUDA_TRY(m, cudaMemcpyAsync(m->in_dev, m->in_host, in.total_bytes, cudaMemcpyHostToDevice, m->stream));
+  m->launches = 0;
+  // `Talker::prefill` (talker.rs:186-221)
+  LAUNCH(m, launch_gather(m->din<int32_t>(in.t_ids), 1, m->text_emb, m->text_vocab, m->t_e, T, h, m->err, m->stream));
+  Epilogue e1;
+  e1.bias = m->fc1_b, e1.kind = kEpiBiasSilu;
+  TRY(gemm(m, m->fc1_w, h, h, m->t_e, T, m->t_p, h, e1));
+  TRY(gemm(m, m->fc2_w, h, h, m->t_p, T, m->embeds, h));
+  LAUNCH(m, launch_prompt_codec(m->embeds, m->fc2_b, m->codec_emb, c.talker.vocab, m->din<int32_t>(in.t_codec), T, h,
+                                m->err, m->stream));
+  RowMap map;
+  map.pos = m->din<int32_t>(in.t_pos);
+  map.slot = m->din<int32_t>(in.t_slot);
+  map.seq = m->din<int32_t>(in.t_seq);
+  map.indptr = m->din<int32_t>(in.indptr);
+  map.pages = m->din<int32_t>(in.pages);
+  TRY(stack_forward(m, m->talker, m->T, m->embeds, T, map, m->kv, m->pages_total, m->T.x, 1, 0));
+  LAUNCH(m, launch_gather(m->din<int32_t>(in.last_row), 1, m->T.x, T, m->hidden, n, h, m->err, m->stream));
+  const int prefill_launches = m->launches;
+  // the staging block is reused below: let the copy above and the prefill finish first
+  CUDA_TRY(m, cudaStreamSynchronize(m->stream));
+
+  // the `first` program on the prompt's last hidden state (model.rs:171-175)
+  std::vector<FrameRow> rows(n);
+  for (int s = 0; s < n; ++s) rows[s] = FrameRow{seqs[s], 0, 0, &draws[s]};
+  const int b = bucket_of(n);
+  const size_t bytes = stage_graph_inputs(m, m->in_host, rows, b, false);
+  CUDA_TRY(m, cudaMemcpyAsync(m->in_dev, m->in_host, bytes, cudaMemcpyHostToDevice, m->stream));
+  TRY(run_program(m, kFirst, b));
+  m->launches += prefill_launches;
+  m->stats.bucket = b;
+  TRY(finish_call(m, n, codes, wav));
+  for (int s = 0; s < n; ++s) seqs[s]->frames = 1;
+  return OMNI_OK;
+}
+
+static int check_step(omni_talker* m, int n, omni_seq* const* seqs, const omni_draw* draws, int ticks) {
+  const omni_talker_config& c = m->cfg;
+  if (n < 1 || n > c.max_batch) return m->fail(OMNI_ERR_INVALID, "%d sequences in one call", n);
+  for (int s = 0; s < n; ++s) {
+    if (!seqs[s] || !seqs[s]->live || seqs[s]->frames < 1) return m->fail(OMNI_ERR_INVALID, "sequence %d has not started", s);
+    for (int r = 0; r < s; ++r)
+      if (seqs[r] == seqs[s]) return m->fail(OMNI_ERR_INVALID, "sequence %d listed twice", s);
+    if (seqs[s]->prompt + seqs[s]->frames - 1 + ticks > seqs[s]->cap)
+      return m->fail(OMNI_ERR_INVALID, "sequence %d is at its frame cap", s);
+  }
+  for (int64_t i = 0; i < (int64_t)n * ticks; ++i)
+    for (int g = 0; g < OMNI_GROUPS; ++g)
+      if (draws[i].force[g] >= (g == 0 ? c.talker.vocab : c.predictor.vocab))
+        return m->fail(OMNI_ERR_INVALID, "forced code %d of group %d", draws[i].force[g], g);
+  return OMNI_OK;
+}
+
+int32_t omni_talker_step(omni_talker* m, int32_t n, omni_seq* const* seqs, const omni_draw* draws, int32_t* codes,
+                         float* wav) {
+  if (!m || !seqs || !draws || !codes) return OMNI_ERR_INVALID;
+  TRY(check_step(m, n, seqs, draws, 1));
+  CUDA_TRY(m, cudaSetDevice(m->device));
+  std::vector<FrameRow> rows(n);
+  for (int s = 0; s < n; ++s) rows[s] = FrameRow{seqs[s], seqs[s]->prompt + seqs[s]->frames - 1, seqs[s]->frames, &draws[s]};
+  const int b = bucket_of(n);
+  const size_t bytes = stage_graph_inputs(m, m->in_host, rows, b, true);
+  CUDA_TRY(m, cudaEventRecord(m->ev0, m->stream));
+  CUDA_TRY(m, cudaMemcpyAsync(m->in_dev, m->in_host, bytes, cudaMemcpyHostToDevice, m->stream));
+  TRY(run_program(m, kDecode, b));
+  m->stats.bucket = b;
+  TRY(finish_call(m, n, codes, wav));
+  for (int s = 0; s < n; ++s) seqs[s]->frames += 1;
+  return OMNI_OK;
+}
+
+int32_t omni_talker_run_ticks(omni_talker* m, int32_t n, omni_seq* const* seqs, int32_t ticks, const omni_draw* draws,
+                              int32_t* codes, float* tick_ms) {
+  if (!m || !seqs || !draws || ticks < 1) return OMNI_ERR_INVALID;
+  TRY(check_step(m, n, seqs, draws, ticks));
+  CUDA_TRY(m, cudaSetDevice(m->device));
+  const int b = bucket_of(n);
+  // every tick's front block, built on the host, staged on the device before the first tick
+  size_t block = 0;
+  std::vector<char> host;
+  std::vector<FrameRow> rows(n);
+  std::vector<size_t> used(ticks);
+  {
+    // the last tick reads the most pages; size every block for it
+    for (int s = 0; s < n; ++s) rows[s] = FrameRow{seqs[s], seqs[s]->prompt + seqs[s]->frames - 2 + ticks, 0, &draws[s]};
+    std::vector<char> probe(m->in.total_bytes);
+    block = align_up(stage_graph_inputs(m, probe.data(), rows, b, true), 256);
+  }
+  host.resize(block * ticks);
+  for (int t = 0; t < ticks; ++t) {
+    for (int s = 0; s < n; ++s)
+      rows[s] = FrameRow{seqs[s], seqs[s]->prompt + seqs[s]->frames - 1 + t, seqs[s]->frames + t, &draws[(size_t)t * n + s]};
+    std::vector<char> tmp(m->in.total_bytes);
+    used[t] = stage_graph_inputs(m, tmp.data(), rows, b, true);
+    memcpy(host.data() + block * t, tmp.data(), used[t]);
+  }
+  char* staged = nullptr;
+  int32_t* codes_dev = nullptr;
+  cudaError_t e = cudaMalloc((void**)&staged, block * ticks);
+  if (e != cudaSuccess) return m->fail(OMNI_ERR_CUDA, "cudaMalloc staged inputs: %s", cudaGetErrorString(e));
+  const size_t frame_bytes = (size_t)n * OMNI_GROUPS * 4;
+  e = cudaMalloc((void**)&codes_dev, frame_bytes * ticks);
+  if (e != cudaSuccess) {
+    cudaFree(staged);
+    return m->fail(OMNI_ERR_CUDA, "cudaMalloc codes: %s", cudaGetErrorString(e));
+  }
+  std::vector<cudaEvent_t> ev(ticks + 1);
+  for (auto& x : ev) cudaEventCreate(&x);
+  int rc = OMNI_OK;
+  auto body = [&]() -> int {
+    CUDA_TRY(m, cudaMemcpyAsync(staged, host.data(), block * ticks, cudaMemcpyHostToDevice, m->stream));
+    CUDA_TRY(m, cudaStreamSynchronize(m->stream));
+    CUDA_TRY(m, cudaEventRecord(ev[0], m->stream));
+    for (int t = 0; t < ticks; ++t) {
+      CUDA_TRY(m, cudaMemcpyAsync(m->in_dev, staged + block * t, used[t], cudaMemcpyDeviceToDevice, m->stream));
+      TRY(run_program(m, kDecode, b));
+      CUDA_TRY(m, cudaMemcpyAsync(codes_dev + (size_t)t * n * OMNI_GROUPS, m->codes, frame_bytes,
+                                  cudaMemcpyDeviceToDevice, m->stream));
+      CUDA_TRY(m, cudaEventRecord(ev[t + 1], m->stream));
+    }
+    CUDA_TRY(m, cudaStreamSynchronize(m->stream));
+    uint32_t err = 0;
+    CUDA_TRY(m, cudaMemcpy(&err, m->err, 4, cudaMemcpyDeviceToHost));
+    if (err != 0) {
+      cudaMemset(m->err, 0, 4);
+      return m->fail(OMNI_ERR_DEVICE, "device error word 0x%x", err);
+    }
+    if (codes) CUDA_TRY(m, cudaMemcpy(codes, codes_dev, frame_bytes * ticks, cudaMemcpyDeviceToHost));
+    float total = 0.f;
+    for (int t = 0; t < ticks; ++t) {
+      float ms = 0.f;
+      cudaEventElapsedTime(&ms, ev[t], ev[t + 1]);
+      if (tick_ms) tick_ms[t] = ms;
+      total += ms;
+    }
+    m->stats.last_call_gpu_ms = total;
+    m->stats.last_call_launches = m->launches * ticks;
+    m->stats.bucket = b;
+    return OMNI_OK;
+  };
+  rc = body();
+  for (auto& x : ev) cudaEventDestroy(x);
+  cudaFree(staged);
+  cudaFree(codes_dev);
+  if (rc == OMNI_OK) {
+    for (int s = 0; s < n; ++s) seqs[s]->frames += ticks;
+    m->last_n = n;
+  }
+  return rc;
+}
+
+int32_t omni_talker_read(omni_talker* m, int32_t buffer, int32_t s, void* dst, size_t bytes) {
+  if (!m || !dst) return OMNI_ERR_INVALID;
+  const omni_talker_config& c = m->cfg;
+  CUDA_TRY(m, cudaSetDevice(m->device));
+  CUDA_TRY(m, cudaStreamSynchronize(m->stream));
+  const size_t V = c.talker.vocab, PV = c.predictor.vocab, h = c.talker.hidden;
+  switch (buffer) {
+    case OMNI_BUF_LOGITS:
+      if (s < 0 || s >= m->max_seqs || bytes != V * 2) return m->fail(OMNI_ERR_INVALID, "logits read");
+      CUDA_TRY(m, cudaMemcpy(dst, m->logits + (size_t)s * V, bytes, cudaMemcpyDeviceToHost));
+      return OMNI_OK;
+    case OMNI_BUF_P_LOGITS:
+      if (s < 0 || s >= m->max_seqs || bytes != (size_t)(c.groups - 1) * PV * 2) return m->fail(OMNI_ERR_INVALID, "p_logits read");
+      for (int g = 0; g < c.groups - 1; ++g)  // row (g, s) sits at g * max_seqs + s (talker.rs:347)
+        CUDA_TRY(m, cudaMemcpy((char*)dst + (size_t)g * PV * 2, m->p_logits + ((size_t)g * m->max_seqs + s) * PV, PV * 2,
+                               cudaMemcpyDeviceToHost));
+      return OMNI_OK;
+    case OMNI_BUF_EMBEDS:
+      if (bytes > (size_t)m->max_rows * h * 2) return m->fail(OMNI_ERR_INVALID, "embeds read");
+      CUDA_TRY(m, cudaMemcpy(dst, m->embeds, bytes, cudaMemcpyDeviceToHost));
+      return OMNI_OK;
+    case OMNI_BUF_HIDDEN:
+      if (s < 0 || s >= m->max_seqs || bytes != h * 2) return m->fail(OMNI_ERR_INVALID, "hidden read");
+      CUDA_TRY(m, cudaMemcpy(dst, m->hidden + (size_t)s * h, bytes, cudaMemcpyDeviceToHost));
+      return OMNI_OK;
+    case OMNI_BUF_PAD_EMBED:
+      if (bytes != h * 2) return m->fail(OMNI_ERR_INVALID, "pad_embed read");
+      CUDA_TRY(m, cudaMemcpy(dst, m->pad_embed, bytes, cudaMemcpyDeviceToHost));
+      return OMNI_OK;
+  }
+  return m->fail(OMNI_ERR_INVALID, "unknown buffer %d", buffer);
+}
+
+int32_t omni_talker_stats(omni_talker* m, omni_stats* out) {
+  if (!m || !out) return OMNI_ERR_INVALID;
+  m->stats.pages_total = m->pages_total;
+  m->stats.pages_used = m->pages_used;
+  m->stats.weight_bytes = m->weight_bytes;
+  m->stats.kv_bytes = m->kv_bytes;
+  *out = m->stats;
+  return OMNI_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,86 @@
+// Device helpers shared by every kernel of the library: bf16 packing, warp and
+// block reductions, the device error word.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace omni {
+
+typedef __nv_bfloat16 bf16;
+
+// Device error word: kernels OR a code into it instead of trapping, the host
+// reads it after the call. Kernels that wait on hardware barriers return early
+// once it is non-zero so one failure cannot stall a whole graph.
+enum DeviceError : uint32_t {
+  kErrNone = 0,
+  kErrBarrierTimeout = 1u << 0,  // a bounded mbarrier wait ran out
+  kErrBadIndex = 1u << 1,        // an id / page / slot outside its table
+  kErrBadShape = 1u << 2,
+};
+
+__device__ __forceinline__ void raise(uint32_t* err, uint32_t code) { atomicOr(err, code); }
+
+__device__ __forceinline__ float bf16_round(float x) { return __bfloat162float(__float2bfloat16(x)); }
+
+struct alignas(16) Pack8 {
+  __nv_bfloat162 h[4];
+};
+
+// Eight bf16 (one 16-byte access) widened to f32.
+__device__ __forceinline__ void unpack8(const Pack8& p, float* v) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = __bfloat1622float2(p.h[i]);
+    v[2 * i] = f.x;
+    v[2 * i + 1] = f.y;
+  }
+}
+
+__device__ __forceinline__ Pack8 pack8(const float* v) {
+  Pack8 p;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) p.h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+  return p;
+}
+
+__device__ __forceinline__ void ld8(const bf16* src, float* v) { unpack8(*reinterpret_cast<const Pack8*>(src), v); }
+__device__ __forceinline__ void st8(bf16* dst, const float* v) { *reinterpret_cast<Pack8*>(dst) = pack8(v); }
+
+__device__ __forceinline__ float warp_add(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+__device__ __forceinline__ float warp_fmax(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Sum over the block; `scratch` is 32 floats of shared memory. Ends with a
+// barrier so `scratch` can be reused at once.
+__device__ __forceinline__ float block_add(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+  v = warp_add(v);
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  v = lane < nwarps ? scratch[lane] : 0.f;
+  v = warp_add(v);
+  __syncthreads();
+  return v;
+}
+
+__device__ __forceinline__ float block_fmax(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+  v = warp_fmax(v);
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  v = lane < nwarps ? scratch[lane] : -INFINITY;
+  v = warp_fmax(v);
+  __syncthreads();
+  return v;
+}
+
+}  // namespace omni

@@ -1,0 +1,83 @@
+"""Operator-level calls (include/omni_b200_ops.h) over torch CUDA tensors, for parity tests and micro-benchmarks."""
+from __future__ import annotations
+
+import ctypes as C
+
+from . import lib as L
+
+
+class OpsError(RuntimeError):
+    pass
+
+
+def _p(t):
+    return None if t is None else C.c_void_p(t.data_ptr())
+
+
+class Ops:
+    def __init__(self, device: int = 0):
+        self._lib = L.load()
+        h = C.c_void_p()
+        rc = self._lib.omni_ops_create(device, C.byref(h))
+        self._h = h
+        if rc != L.OK:
+            msg = self._lib.omni_ops_last_error(h).decode() if h else "create failed"
+            raise OpsError(f"status {rc}: {msg}")
+
+    def close(self):
+        if self._h:
+            self._lib.omni_ops_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def _check(self, rc):
+        if rc != L.OK:
+            raise OpsError(f"status {rc}: {self._lib.omni_ops_last_error(self._h).decode()}")
+
+    def sync(self):
+        word = C.c_uint32(0)
+        self._check(self._lib.omni_ops_sync(self._h, C.byref(word)))
+
+    def mark(self, which: int):
+        self._check(self._lib.omni_ops_mark(self._h, which))
+
+    def elapsed_ms(self) -> float:
+        ms = C.c_float(0)
+        self._check(self._lib.omni_ops_elapsed_ms(self._h, C.byref(ms)))
+        return ms.value
+
+    def gemm(self, w, x, y, path=0, splits=0, bias=None, epilogue=0):
+        n, k = w.shape
+        rows = x.shape[0]
+        assert x.shape[1] == k and y.shape[0] >= rows
+        self._check(self._lib.omni_op_gemm(self._h, _p(w), n, k, _p(x), rows, _p(y), y.stride(0), path, splits,
+                                           _p(bias), epilogue))
+
+    def norm_copy(self, x, w, out, res, eps):
+        self._check(self._lib.omni_op_norm_copy(self._h, _p(x), _p(w), _p(out), _p(res), x.shape[0], x.shape[1], eps))
+
+    def add_norm(self, x, res, w, out, eps, every=1, which=0):
+        self._check(self._lib.omni_op_add_norm(self._h, _p(x), _p(res), _p(w), _p(out), x.shape[0], x.shape[1], eps,
+                                               every, which))
+
+    def silu_mul(self, gate_up, act):
+        self._check(self._lib.omni_op_silu_mul(self._h, _p(gate_up), _p(act), gate_up.shape[0], act.shape[1]))
+
+    def rope_attend(self, qkv, q_norm, k_norm, kv, kv_pages, pos, slot, seq, indptr, pages, hq, hk, d, eps, theta,
+                    out):
+        self._check(self._lib.omni_op_rope_attend(self._h, _p(qkv), _p(q_norm), _p(k_norm), _p(kv), kv_pages, _p(pos),
+                                                  _p(slot), _p(seq), _p(indptr), _p(pages), qkv.shape[0], hq, hk, d,
+                                                  eps, theta, _p(out)))
+
+    def sample(self, logits, temperature, top_k, top_p, penalty, suppress_lo, suppress_hi, exempt, min_frames, frames,
+               uniforms, force, state, lines, stride, penalize, philox, codes, group):
+        rows, vocab = logits.shape
+        self._check(self._lib.omni_op_sample(self._h, _p(logits), vocab, temperature, top_k, top_p, penalty,
+                                             suppress_lo, suppress_hi, exempt, min_frames, _p(frames), _p(uniforms),
+                                             _p(force), _p(state), _p(lines), stride, penalize, philox, _p(codes),
+                                             group, rows))
