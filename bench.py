@@ -1,0 +1,329 @@
+"""Benchmark of the codec-frame token loop: Qwen3-TTS-1.7B talker architecture, random bf16 weights,
+64 concurrent sessions per GPU, one decode tick (talker step + 15 code-predictor sub-steps) per step.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Prints ONE JSON line (rank 0). `value`: codec frames/s over all GPUs with every tick's inputs already in HBM
+(`omni_talker_run_ticks`), timed per tick with CUDA events on the model's stream, max over ranks. `e2e`: the same
+metric through the public `Model.step` call with host draws (H2D staging and D2H frame read-back inside each step).
+`--impl reference` times the CPU restatement of the reference's path (the reference's implementation of this path is
+CUDA-only and needs an un-vendored Rust runtime, so the CPU arm is the oracle port) on a bounded sample.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+METRIC = "codec frames/sec at 64 sessions per GPU (Qwen3-TTS talker)"
+UNIT = "frames/s"
+
+
+def measured_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return float(d["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *exc):
+        if self.proc:
+            self.proc.terminate()  # the exact child started above
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            try:
+                sm.append(float(r[1]))
+                mx.append(float(r[2]))
+            except (ValueError, IndexError):
+                continue
+            for name, v in zip(names, r[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": float(np.median(sm)), "sm_max_mhz": float(max(mx)), "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def workload(cfg, sessions, prompt_len, seed):
+    from pega_omni_b200.model import Prompt
+    rng = np.random.default_rng(seed)
+    # 128-token prompts, uniform text ids, no codec-track tokens (NO_CODEC on every row)
+    return [Prompt(list(rng.integers(0, cfg.text_vocab_size, prompt_len)), [-1] * prompt_len) for _ in range(sessions)]
+
+
+def draws_for(ticks, sessions, seed):
+    from pega_omni_b200.model import Draw
+    rng = np.random.default_rng(seed)
+    u = rng.random((ticks, sessions, 16)).astype(np.float32)
+    return [[Draw(list(u[t, s])) for s in range(sessions)] for t in range(ticks)]
+
+
+def kernel_roofline(cfg, rows, peak_gbs, peak_kind, launches=56):
+    """The dominant kernel alone: the tensor-core GEMM on the talker's gate|up shape, over enough distinct
+    weight matrices that nothing is served from L2, timed with CUDA events on the stream it is launched on."""
+    import torch
+    from pega_omni_b200.ops import Ops
+    t = cfg.talker
+    n, k = 2 * t.intermediate_size, t.hidden_size
+    ops = Ops(torch.cuda.current_device())
+    copies = max(4, int(1.5e9 // (n * k * 2)))  # >= 1.5 GB of weights in rotation (L2 is 126 MB)
+    w = [(torch.randn((n, k), device="cuda") * 0.02).to(torch.bfloat16) for _ in range(copies)]
+    x = torch.randn((rows, k), device="cuda").to(torch.bfloat16)
+    y = torch.zeros((rows, n), device="cuda", dtype=torch.bfloat16)
+    torch.cuda.synchronize()
+    for i in range(8):
+        ops.gemm(w[i % copies], x, y, path=0)
+    ops.sync()
+    ops.mark(0)
+    for i in range(launches):
+        ops.gemm(w[i % copies], x, y, path=0)
+    ops.mark(1)
+    ops.sync()
+    ms = ops.elapsed_ms() / launches
+    ops.close()
+    algorithmic = (n * k + rows * k + rows * n) * 2  # weight tile stream + input rows + output rows, bf16
+    achieved = algorithmic / (ms * 1e-3) / 1e9
+    return {"bound": "hbm", "kernel": "gemm_tc_kernel<64> gate|up [12288 x 2048] x 64 rows", "achieved": achieved,
+            "peak": peak_gbs, "unit": "GB/s", "frac": achieved / peak_gbs, "peak_source": f"of {peak_kind}",
+            "us_per_launch": ms * 1e3, "bytes_per_launch": algorithmic, "traffic": None}
+
+
+def cpu_baseline(cfg, ck_host, threads=None, sessions=4, prompt_len=16, warmup=1, ticks=4, seed=0):
+    """The CPU oracle (a port of the reference's arithmetic) timed on a bounded sample of the same architecture:
+    `sessions` sessions, short prompts, `ticks` decode ticks. Returns frames/s, cores used, per-tick seconds."""
+    from oracle import cpu as orc
+    lib = orc.load()
+    if threads:
+        lib.orc_set_threads(threads)
+    cores = lib.orc_max_threads()
+    o = orc.CpuOracle(cfg, ck_host)
+    prompts = workload(cfg, sessions, prompt_len, seed)
+    sids = [o.open(prompt_len, warmup + ticks + 2) for _ in range(sessions)]
+    d = draws_for(warmup + ticks + 1, sessions, seed)
+    o.start(sids, prompts, d[0])
+    for t in range(warmup):
+        o.step(sids, d[1 + t])
+    per_tick = []
+    for t in range(ticks):
+        t0 = time.perf_counter()
+        o.step(sids, d[1 + warmup + t])
+        per_tick.append(time.perf_counter() - t0)
+    o.close()
+    total = sum(per_tick)
+    return {"value": sessions * ticks / total, "unit": UNIT, "cores": cores, "kind": "port",
+            "sample": f"{sessions} sessions x {ticks} decode ticks of the same architecture, {prompt_len}-token "
+                      f"prompts (the GPU workload runs 64 sessions x 128-token prompts)"}, per_tick
+
+
+def run_reference(args, rank):
+    """CPU arm: the oracle port on all host cores. Rank 0 only."""
+    if rank != 0:
+        return
+    import torch
+    from pega_omni_b200.config import presets
+    from pega_omni_b200.synthetic import random_checkpoint
+    cfg = presets["qwen3-tts-1.7b"]()
+    ck = random_checkpoint(cfg, seed=0, device="cuda" if torch.cuda.is_available() else "cpu")
+    ck = {k: v.cpu() for k, v in ck.items()}
+    sessions = 4
+    base, per_tick = cpu_baseline(cfg, ck, sessions=sessions, warmup=max(0, min(args.warmup, 3)),
+                                  ticks=max(1, min(args.steps, 24)))
+    ms = 1e3 * float(np.mean(per_tick))
+    line = {"impl": "reference", "metric": METRIC, "value": base["value"], "unit": UNIT, "n_gpus": args.gpus,
+            "steps": len(per_tick), "warmup": max(0, min(args.warmup, 3)), "ms_per_step": ms,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "Qwen3-TTS-12Hz-1.7B talker architecture, decode tick = talker step + 15 "
+                                   "code-predictor sub-steps; CPU arm on a bounded sample", "sessions": sessions,
+                       "note": "requested steps/warmup are clamped (24/3) so the CPU run ends in minutes"},
+            "cpu_baseline": base,
+            "e2e": {"value": base["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=64)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--sessions", type=int, default=64, help="sessions per GPU")
+    ap.add_argument("--prompt", type=int, default=128)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-graphs", action="store_true")
+    args = ap.parse_args()
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+
+    import torch
+    import torch.distributed as dist
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: there is no CPU path")
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+
+    from pega_omni_b200 import replicas
+    from pega_omni_b200.config import presets
+    from pega_omni_b200.model import Limits, Model
+    from pega_omni_b200.synthetic import random_checkpoint
+
+    W, K = max(3, args.warmup), args.steps
+    cfg = presets["qwen3-tts-1.7b"]()
+    ck = random_checkpoint(cfg, seed=0, device="cuda")
+    frames_cap = 2 * (W + K) + 8
+    kv_gib = max(1.0, 1.25 * args.sessions * (args.prompt + frames_cap + 16) * cfg.talker.kv_bytes_per_token() / 2 ** 30)
+    model = Model.load(local, ck, cfg, Limits(args.sessions, args.sessions * args.prompt, kv_gib),
+                       use_graphs=not args.no_graphs)
+    ck_host = None
+    if rank == 0 and not args.no_cpu_baseline:
+        ck_host = {k: v.cpu() for k, v in ck.items()}
+    del ck
+    torch.cuda.empty_cache()
+
+    # this rank's share of the global sessions (round-robin), a full replica per GPU
+    mine = replicas.local_sessions(args.sessions * world, rank, world)
+    n = len(mine)
+    prompts = workload(cfg, n, args.prompt, seed=1000 + rank)
+    seqs = [model.open(args.prompt, frames_cap) for _ in range(n)]
+    d0 = draws_for(1, n, seed=rank)[0]
+    model.start(list(zip(seqs, prompts, d0)))
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    # ---- device-resident arm: W warm-up ticks, then exactly K timed ticks ----
+    model.run_ticks(seqs, draws_for(W, n, seed=10 + rank))
+    draws = draws_for(K, n, seed=20 + rank)
+    first_frame = seqs[0].frames
+    barrier()
+    with ClockSampler(local) as clocks:
+        _, tick_ms = model.run_ticks(seqs, draws)
+        barrier()
+    launches_per_tick = model.stats().last_call_launches // K
+    elapsed = float(tick_ms.sum()) * 1e-3
+    lens = [args.prompt + first_frame - 1 + t for t in range(K)]  # the position every session's row sits at
+    t_el = torch.tensor([elapsed], device="cuda", dtype=torch.float64)
+    t_p99 = torch.tensor([float(np.percentile(tick_ms, 99))], device="cuda", dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t_el, op=dist.ReduceOp.MAX)
+        dist.all_reduce(t_p99, op=dist.ReduceOp.MAX)
+    elapsed_max = float(t_el.item())
+    value = args.sessions * world * K / elapsed_max
+
+    # ---- end-to-end arm: Model.step with host draws, staging and read-back inside every step ----
+    e2e_draws = draws_for(W + K, n, seed=30 + rank)
+    for t in range(min(W, 8)):
+        model.step(list(zip(seqs, e2e_draws[t])))
+    barrier()
+    t0 = time.perf_counter()
+    dev_ms = 0.0
+    for t in range(K):
+        model.step(list(zip(seqs, e2e_draws[W + t])))
+        dev_ms += model.stats().last_call_gpu_ms
+    torch.cuda.synchronize()
+    e2e_s = time.perf_counter() - t0
+    t_e2e = torch.tensor([e2e_s], device="cuda", dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t_e2e, op=dist.ReduceOp.MAX)
+    e2e_value = args.sessions * world * K / float(t_e2e.item())
+    bucket = model.stats().bucket
+    pages_per_seq = (lens[-1] + K) // 16 + 1
+    h2d = 4 * (bucket * (1 + 1 + 16 + 16 + 1 + 1) + bucket + 1) + 4 * n * pages_per_seq  # staged front block (approx.)
+    d2h = 4 * (bucket * 16 + 1)
+
+    if rank == 0:
+        peak, peak_kind = measured_peaks()
+        mean_len = float(np.mean(lens)) + 1
+        tick_bytes = cfg.tick_weight_bytes() + cfg.talker.kv_bytes_per_token() * n * (mean_len + 1)
+        tick_s = elapsed / K
+        roof = kernel_roofline(cfg, bucket, peak, peak_kind)
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
+            "ms_per_step": 1e3 * elapsed_max / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "configs[1]: Qwen3-TTS-12Hz-1.7B talker (28L h2048 16q/8kv d128 i6144, head 3072) + "
+                                   "code predictor (5L h1024, 15 codebooks x 2048), random bf16 weights N(0,0.02)",
+                       "sessions_per_gpu": args.sessions, "prompt_tokens": args.prompt, "kv_page": 16,
+                       "sampling": "top-k 50, T 0.9, repetition penalty 1.05, host uniforms (reference sampler)",
+                       "step": "one decode tick = 64 frames per GPU", "positions": [lens[0], lens[-1]],
+                       "parallelism": f"{world} replica(s), sessions round-robin, no collective",
+                       "l2": "each tick streams 5.3 GB of weights, far larger than the 126 MB L2",
+                       "graphs": not args.no_graphs},
+            "tick_p99_ms": float(t_p99.item()), "tick_p50_ms": float(np.percentile(tick_ms, 50)),
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
+                    "timing": "wall clock around K Model.step calls (each waits for its frame), max over ranks",
+                    "device_ms_per_step": dev_ms / K},
+            "gpu_launches": int(launches_per_tick * K),
+            "launches_per_tick": int(launches_per_tick),
+            "clocks": clocks.summary(),
+            "roofline": roof,
+            "tick_roofline": {"bound": "hbm", "achieved": tick_bytes / tick_s / 1e9, "peak": peak, "unit": "GB/s",
+                              "frac": tick_bytes / tick_s / 1e9 / peak, "peak_source": f"of {peak_kind}",
+                              "bytes_per_tick": int(tick_bytes), "mean_kv_len": mean_len},
+        }
+        if ck_host is not None:
+            base, _ = cpu_baseline(cfg, ck_host)
+            line["cpu_baseline"] = base
+        print(json.dumps(line), flush=True)
+    model.close()
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -53,8 +53,9 @@ def tensor_shapes(cfg: TalkerConfig):
 
 
 def random_checkpoint(cfg: TalkerConfig, seed: int = 0, std: float = 0.02, device: str | torch.device = "cpu",
-                      embed_std: float | None = None) -> dict[str, torch.Tensor]:
-    """name -> bf16 tensor on `device`. Norm gains are ones; everything else N(0, std)."""
+                      embed_std: float | None = None, head_std: float | None = None) -> dict[str, torch.Tensor]:
+    """name -> bf16 tensor on `device`. Norm gains are ones; everything else N(0, std). `head_std` widens the
+    output heads so logits are peaked like a trained model's instead of nearly flat."""
     device = torch.device(device)
     out: dict[str, torch.Tensor] = {}
     for name, shape in tensor_shapes(cfg):
@@ -66,6 +67,8 @@ def random_checkpoint(cfg: TalkerConfig, seed: int = 0, std: float = 0.02, devic
         s = std
         if embed_std is not None and ("embedding" in name):
             s = embed_std
+        if head_std is not None and ("codec_head" in name or "lm_head" in name):
+            s = head_std
         n = 1
         for d in shape:
             n *= d
