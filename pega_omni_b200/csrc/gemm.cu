@@ -213,32 +213,29 @@ __global__ void __launch_bounds__(128, 1)
 
   ok = mbar_wait(acc_bar, 0, err);
   tc_fence_after_sync();
-  const int n = tile * kTileW + warp * 32 + lane;  // this thread's weight row = output column
+  const int tl = warp * 32 + lane;        // row of the W tile = TMEM lane
+  const int n = tile * kTileW + tl;       // this thread's weight row = output column
   const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
-  const int n_pad = gridDim.x * kTileW;
+  // Once the accumulator is complete every TMA write has landed and every MMA has read its operands, so the
+  // pipeline buffers are free: the finished bf16 tile is staged there as [BN][128] and stored row by row.
+  bf16* stage = reinterpret_cast<bf16*>(base_ptr);
+  const size_t tile_floats = (size_t)BN * kTileW;
+  // split-K partials: [row_tile][split][tile][column][128 lanes], so a warp stores 128 contiguous bytes
+  float* partial0 = partials + (((size_t)row_tile * splits) * gridDim.x + tile) * tile_floats;
+  const size_t split_stride = (size_t)gridDim.x * tile_floats;
   if (ok) {
-    if (splits == 1) {
 #pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 16) {
-        float v[16];
-        tmem_ld16(lane_addr + c0, v);
-        if (n < N) {
+    for (int c0 = 0; c0 < BN; c0 += 16) {
+      float v[16];
+      tmem_ld16(lane_addr + c0, v);
+      if (splits == 1) {
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const int m = row_tile * BN + c0 + j;
-            if (m < rows) y[(int64_t)m * ldy + n] = finish(v[j], n, bias, kind);
-          }
-        }
-      }
-    } else {
-      float* mine = partials + (((size_t)row_tile * splits + split) * n_pad + n) * BN;
-#pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 16) {
-        float v[16];
-        tmem_ld16(lane_addr + c0, v);
+        for (int j = 0; j < 16; ++j)
+          stage[(c0 + j) * kTileW + tl] = n < N ? finish(v[j], n, bias, kind) : __float2bfloat16(0.f);
+      } else {
+        float* mine = partial0 + split * split_stride + (size_t)c0 * kTileW + tl;
 #pragma unroll
-        for (int j = 0; j < 16; j += 4)
-          *reinterpret_cast<float4*>(mine + c0 + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+        for (int j = 0; j < 16; ++j) mine[j * kTileW] = v[j];
       }
     }
   }
@@ -246,6 +243,7 @@ __global__ void __launch_bounds__(128, 1)
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem_base, S::kTmemCols);
 
+  bool write_out = ok && splits == 1;
   if (splits > 1) {
     __threadfence();
     __syncthreads();
@@ -258,31 +256,43 @@ __global__ void __launch_bounds__(128, 1)
     __syncthreads();
     if (is_last) {
       __threadfence();
-      const float* first = partials + (((size_t)row_tile * splits) * n_pad + n) * BN;
-      const size_t split_stride = (size_t)n_pad * BN;
+      // sum the splits in index order: the result does not depend on which CTA arrived last
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 16) {
         float acc[16];
 #pragma unroll
         for (int j = 0; j < 16; ++j) acc[j] = 0.f;
+#pragma unroll 2
         for (int s = 0; s < splits; ++s) {
-          const float* p = first + s * split_stride + c0;
+          const float* p = partial0 + s * split_stride + (size_t)c0 * kTileW + tl;
+          float f[16];
 #pragma unroll
-          for (int j = 0; j < 16; j += 4) {
-            const float4 f = __ldcg(reinterpret_cast<const float4*>(p + j));
-            acc[j] += f.x;
-            acc[j + 1] += f.y;
-            acc[j + 2] += f.z;
-            acc[j + 3] += f.w;
-          }
-        }
-        if (n < N) {
+          for (int j = 0; j < 16; ++j) f[j] = __ldcg(p + j * kTileW);
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const int m = row_tile * BN + c0 + j;
-            if (m < rows) y[(int64_t)m * ldy + n] = finish(acc[j], n, bias, kind);
-          }
+          for (int j = 0; j < 16; ++j) acc[j] += f[j];
         }
+#pragma unroll
+        for (int j = 0; j < 16; ++j)
+          stage[(c0 + j) * kTileW + tl] = n < N ? finish(acc[j], n, bias, kind) : __float2bfloat16(0.f);
+      }
+      write_out = true;
+    }
+  }
+  if (write_out) {  // uniform across the block
+    __syncthreads();
+    const int m0 = row_tile * BN, n0 = tile * kTileW;
+    const bool vec = (ldy % 8 == 0) && (N % 8 == 0) && ((reinterpret_cast<uintptr_t>(y) & 15) == 0);
+    if (vec) {
+      for (int idx = threadIdx.x; idx < BN * (kTileW / 8); idx += blockDim.x) {
+        const int m = idx / (kTileW / 8), ch = idx % (kTileW / 8);
+        if (m0 + m < rows && n0 + ch * 8 < N)
+          *reinterpret_cast<uint4*>(y + (int64_t)(m0 + m) * ldy + n0 + ch * 8) =
+              *reinterpret_cast<const uint4*>(stage + m * kTileW + ch * 8);
+      }
+    } else {
+      for (int idx = threadIdx.x; idx < BN * kTileW; idx += blockDim.x) {
+        const int m = idx / kTileW, c = idx % kTileW;
+        if (m0 + m < rows && n0 + c < N) y[(int64_t)(m0 + m) * ldy + n0 + c] = stage[m * kTileW + c];
       }
     }
   }
@@ -344,8 +354,8 @@ int tc_plan(TcGemmPlan* plan, const bf16* w, int N, int K, const bf16* x, int ro
   p.epi = epi;
   const int nkb = K / kTileK, ctas = p.tiles_n() * p.row_tiles;
   int splits = force_splits > 0 ? force_splits : std::max(1, sm_count / ctas);
-  // keep at least two K blocks per split so the pipeline has something to overlap
-  splits = std::max(1, std::min(splits, nkb / 2));
+  // at least four K blocks per split (two when forced): below that the reduction costs more than it spreads
+  splits = std::max(1, std::min(splits, force_splits > 0 ? nkb / 2 : nkb / 4));
   p.splits = splits;
   if (encode_kmajor(&p.wmap, w, N, K, kTileW) != 0) return -4;
   if (encode_kmajor(&p.xmap, x, rows, K, p.BN) != 0) return -4;

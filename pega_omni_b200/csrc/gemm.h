@@ -44,7 +44,7 @@ struct TcGemmPlan {
   int ldy = 0;
   Epilogue epi;
   size_t partial_floats() const { return splits > 1 ? (size_t)splits * row_tiles * tiles_n() * 128 * BN : 0; }
-  int tiles_n() const { return (N + 127) / 128; }
+  int tiles_n() const { return (N + 127) / 128; }  // partial_floats() matches the kernel's [row_tile][split][tile][BN][128]
 };
 
 // Raises the shared-memory limits of the GEMM kernels; call once per process before any launch.

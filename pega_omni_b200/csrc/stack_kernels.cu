@@ -227,6 +227,15 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attend_kernel(const bf16* __r
     const int ntok = min(16, len - pi * 16);
     const bf16* kpage = kv + kv_offset<D>(page, hk, kh, 0, 0);
     const bf16* vpage = kpage + 16 * D;
+    // issue the page's value loads first so they fly while q.k is computed
+    uint2 vraw[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      if constexpr (PV == 4)
+        vraw[j] = *reinterpret_cast<const uint2*>(vpage + j * D + lane * 4);
+      else
+        vraw[j] = make_uint2(*reinterpret_cast<const uint32_t*>(vpage + j * D + lane * 2), 0u);
+    }
     float sc[G];
 #pragma unroll
     for (int g = 0; g < G; ++g) sc[g] = 0.f;
@@ -256,22 +265,24 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attend_kernel(const bf16* __r
       for (int d = 0; d < PV; ++d) acc[g][d] *= corr;
       m[g] = m2;
     }
-    for (int j = 0; j < ntok; ++j) {
+    // every token's value slice was fetched up front (vraw); tokens past the sequence end contribute nothing
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
       float vf[PV];
-      if (PV == 4) {
-        const uint2 u = *reinterpret_cast<const uint2*>(vpage + j * D + lane * 4);
-        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.x));
-        const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.y));
-        vf[0] = a.x, vf[1] = a.y, vf[PV - 2] = b.x, vf[PV - 1] = b.y;
+      if constexpr (PV == 4) {
+        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&vraw[j].x));
+        const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&vraw[j].y));
+        vf[0] = a.x, vf[1] = a.y, vf[2] = b.x, vf[3] = b.y;
       } else {
-        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(vpage + j * D + lane * 2));
+        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&vraw[j].x));
         vf[0] = a.x, vf[1] = a.y;
       }
+      const bool live = j < ntok;
 #pragma unroll
       for (int g = 0; g < G; ++g) {
         const float pj = __shfl_sync(0xffffffffu, p[g], j);
 #pragma unroll
-        for (int d = 0; d < PV; ++d) acc[g][d] = fmaf(pj, vf[d], acc[g][d]);
+        for (int d = 0; d < PV; ++d) acc[g][d] = live ? fmaf(pj, vf[d], acc[g][d]) : acc[g][d];
       }
     }
   }

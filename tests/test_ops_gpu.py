@@ -85,7 +85,9 @@ def test_gemm_bias_epilogues(ops, oracle_lib, path, epi):
     t = oracle_lib.bf16_round(oracle_lib.gemm(to_f32(x), to_bits(w)) + to_f32(b)[None])
     if epi == 2:
         t = oracle_lib.bf16_round(t / (1.0 + np.exp(-t)))
-    close_bf16(to_f32(y), t, ulps=4.0 if epi == 2 else 2.0)  # __expf vs exp can move the SiLU by one more step
+    # the accumulator (|a| ~ 1) may round one step apart on the two sides; after the bias and the SiLU that step is
+    # an absolute error, so the floor is the accumulator's scale, not the output's
+    close_bf16(to_f32(y), t, ulps=2.0, floor=0.5)
 
 
 def test_gemm_strided_output(ops, oracle_lib):
@@ -178,12 +180,12 @@ def test_rope_attend_ragged_paged(ops, oracle_lib, hq, hk, d):
                 a = (hq + h) * d
                 kvrows[t, h * d:(h + 1) * d] = oracle_lib.rope_head(row[a:a + d], to_bits(kn), t, eps, theta)
             kvrows[t, hk * d:] = row[(hq + hk) * d:]
-        close_bf16(got_q[r:r + n, :hq * d], qrows, ulps=2.0, floor=2e-2)
+        close_bf16(got_q[r:r + n, :hq * d], qrows, ulps=2.0, floor=0.5)  # a*cos - b*sin cancels: absolute scale of a, b
         bits = oracle_lib.bf16_bits(kvrows)
         for t in range(n):
             want[r + t] = oracle_lib.attend(qrows[t], bits[:t + 1], hq, hk, d)
         r += n
-    close_bf16(to_f32(out), want, ulps=3.0, floor=2e-2)
+    close_bf16(to_f32(out), want, ulps=3.0, floor=0.25)  # averages of O(1) values: absolute scale
 
 
 def _slots(rows, vocab):
