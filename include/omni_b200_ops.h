@@ -66,6 +66,30 @@ int32_t omni_op_sample(omni_ops* ctx, const void* logits, int32_t vocab, float t
                        void* state, const int32_t* lines, int64_t stride, int32_t penalize, int32_t philox,
                        int32_t* codes, int32_t group, int32_t rows);
 
+/* The tensor-core GEMM of omni_op_gemm for callers that cannot allocate device memory. It has no counterpart in the
+ * reference. Two kinds of caller are meant: a serving process that handed every free byte of HBM to its KV pool at
+ * start-up, where a later cudaMalloc simply fails; and an engine thread in the middle of a live tick, where
+ * cudaMalloc / cudaFree would synchronise the whole device and stall every other session's stream. This entry
+ * point needs no context object and calls no cudaMalloc, cudaFree or allocating library routine: the split-K
+ * scratch (f32 partial tiles, tile counters, the error word) is a fixed array inside the library image, present on
+ * every GPU that loads the library for as long as the process lives.
+ *
+ *  - Inputs and outputs are the caller's device buffers, as for omni_op_gemm (tensor-core path only: K a
+ *    multiple of 64, operands 16-byte aligned). `stream` is a cudaStream_t (NULL = the default stream).
+ *  - Limits: splits * row_tiles * ceil(N/128) * 128 * BN <= 4 Mi floats (BN = rows rounded up to 16/32/64/128/256)
+ *    and row_tiles * ceil(N/128) <= 2048. Larger problems are refused with OMNI_ERR_UNSUPPORTED and a message
+ *    naming the sizes; nothing is launched.
+ *  - The first call on each device looks up the arrays' device addresses (with that device current) and raises the
+ *    kernels' shared-memory limits. Make that first call before starting any stream capture on that device.
+ *  - All calls share the one array and it keeps the previous call's contents; the counters and the error word are
+ *    cleared on the stream before each launch. Two calls whose kernels overlap on the GPU (different streams or
+ *    threads) race on it: serialise them.
+ *  - The call waits for its kernel and returns 0, or a negative omni_status with a human-readable reason in
+ *    `message` (caller-owned, may be NULL). */
+int32_t omni_op_gemm_noalloc(const void* w, int32_t N, int32_t K, const void* x, int32_t rows, void* y, int32_t ldy,
+                             int32_t splits, const void* bias, int32_t epilogue, void* stream, char* message,
+                             size_t message_len);
+
 #ifdef __cplusplus
 }
 #endif

@@ -2,6 +2,7 @@
 #include "gemm.h"
 
 #include <algorithm>
+#include <cstdarg>
 #include <cstdio>
 
 #include "sm100.cuh"
@@ -400,4 +401,133 @@ cudaError_t tc_launch(const TcGemmPlan& p, const GemmScratch& s, uint32_t* err, 
   return cudaErrorInvalidValue;
 }
 
+// ---------------------------------------------------------------------------
+// The split-K tensor-core GEMM for callers that must not allocate.
+//
+// The split-K path needs scratch in global memory: one f32 tile per split and
+// an arrival counter per output tile. Everywhere else in this library that
+// scratch comes from cudaMalloc. Here it is a fixed array inside the loaded
+// module instead, so the call never asks the driver for memory.
+
+namespace {
+constexpr size_t kStaticPartialFloats = (size_t)4 << 20;  // 16 MiB of f32 partial tiles
+constexpr int kStaticCounterSlots = 2048;
+
+// Reserved on every GPU that loads this library, from load until the process exits.
+static __device__ __align__(256) float g_static_partials[kStaticPartialFloats];
+static __device__ __align__(256) uint32_t g_static_counters[kStaticCounterSlots];
+static __device__ __align__(256) uint32_t g_static_error[64];
+
+// In host code the three names above are only handles to the device arrays; the
+// device addresses a kernel can use are looked up once per device, with that
+// device current, and kept here.
+struct StaticScratch {
+  bool ready = false;
+  float* partials = nullptr;
+  uint32_t* counters = nullptr;
+  uint32_t* error = nullptr;
+};
+StaticScratch g_static[64];
+
+void say(char* buf, size_t len, const char* fmt, ...) {
+  if (!buf || len == 0) return;
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, len, fmt, ap);
+  va_end(ap);
+}
+}  // namespace
+
 }  // namespace omni
+
+extern "C" int32_t omni_op_gemm_noalloc(const void* w, int32_t N, int32_t K, const void* x, int32_t rows, void* y,
+                                        int32_t ldy, int32_t splits, const void* bias, int32_t epilogue, void* stream,
+                                        char* message, size_t message_len) {
+  using namespace omni;
+  const int32_t kInvalid = -1, kCuda = -2, kDevice = -3, kUnsupported = -5;  // enum omni_status
+  if (message && message_len) message[0] = 0;
+  if (!w || !x || !y || N < 1 || rows < 1 || K < 64 || K % 64 || ldy < N) {
+    say(message, message_len, "bad argument: need w, x, y, N >= 1, rows >= 1, K a multiple of 64, ldy >= N");
+    return kInvalid;
+  }
+  if (epilogue != kEpiNone && !bias) {
+    say(message, message_len, "epilogue %d needs a bias", epilogue);
+    return kInvalid;
+  }
+  int device = -1;
+  cudaError_t e = cudaGetDevice(&device);
+  if (e != cudaSuccess || device < 0 || device >= 64) {
+    say(message, message_len, "cudaGetDevice: %s", cudaGetErrorString(e));
+    return kCuda;
+  }
+  StaticScratch& sc = g_static[device];
+  if (!sc.ready) {  // first call on this device: resolve the arrays' device addresses
+    cudaDeviceProp prop;
+    if ((e = cudaGetDeviceProperties(&prop, device)) != cudaSuccess || prop.major != 10) {
+      say(message, message_len, "device %d is not sm_100 (%s)", device, cudaGetErrorString(e));
+      return e != cudaSuccess ? kCuda : kUnsupported;
+    }
+    if (tc_init() != 0) {
+      say(message, message_len, "cuTensorMapEncodeTiled entry point not found");
+      return kCuda;
+    }
+    tc_configure();
+    void *p = nullptr, *c = nullptr, *r = nullptr;
+    if ((e = cudaGetSymbolAddress(&p, g_static_partials)) != cudaSuccess ||
+        (e = cudaGetSymbolAddress(&c, g_static_counters)) != cudaSuccess ||
+        (e = cudaGetSymbolAddress(&r, g_static_error)) != cudaSuccess) {
+      say(message, message_len, "cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+      return kCuda;
+    }
+    sc.partials = static_cast<float*>(p);
+    sc.counters = static_cast<uint32_t*>(c);
+    sc.error = static_cast<uint32_t*>(r);
+    sc.ready = true;
+  }
+  int sm_count = 148;
+  if (cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) sm_count = 148;
+  Epilogue epi;
+  epi.bias = static_cast<const bf16*>(bias);
+  epi.kind = epilogue;
+  TcGemmPlan plan;
+  const int rc = tc_plan(&plan, static_cast<const bf16*>(w), N, K, static_cast<const bf16*>(x), rows,
+                         static_cast<bf16*>(y), ldy, epi, sm_count, splits);
+  if (rc != 0) {
+    say(message, message_len, "tensor-map encode failed (%d): operands must be 16-byte aligned", rc);
+    return kInvalid;
+  }
+  if (plan.partial_floats() > kStaticPartialFloats || plan.tiles_n() * plan.row_tiles > kStaticCounterSlots) {
+    say(message, message_len,
+        "too large for the built-in scratch: needs %zu partial floats (limit %zu) and %d tile counters (limit %d); "
+        "use omni_op_gemm, whose context allocates its scratch",
+        plan.partial_floats(), kStaticPartialFloats, plan.tiles_n() * plan.row_tiles, kStaticCounterSlots);
+    return kUnsupported;
+  }
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // the arrays keep whatever the previous call left: counters and the error word must start at zero
+  if ((e = cudaMemsetAsync(sc.counters, 0, sizeof(uint32_t) * kStaticCounterSlots, s)) != cudaSuccess ||
+      (e = cudaMemsetAsync(sc.error, 0, sizeof(uint32_t), s)) != cudaSuccess) {
+    say(message, message_len, "cudaMemsetAsync: %s", cudaGetErrorString(e));
+    return kCuda;
+  }
+  GemmScratch scratch;
+  scratch.partials = sc.partials;
+  scratch.partial_floats = kStaticPartialFloats;
+  scratch.counters = sc.counters;
+  scratch.counter_slots = kStaticCounterSlots;
+  if ((e = tc_launch(plan, scratch, sc.error, s)) != cudaSuccess) {
+    say(message, message_len, "launch: %s", cudaGetErrorString(e));
+    return kCuda;
+  }
+  uint32_t word = 0;
+  if ((e = cudaMemcpyAsync(&word, sc.error, sizeof(word), cudaMemcpyDeviceToHost, s)) != cudaSuccess ||
+      (e = cudaStreamSynchronize(s)) != cudaSuccess) {
+    say(message, message_len, "wait: %s", cudaGetErrorString(e));
+    return kCuda;
+  }
+  if (word != 0) {
+    say(message, message_len, "device error word 0x%x (1: a bounded barrier wait ran out)", word);
+    return kDevice;
+  }
+  return 0;
+}

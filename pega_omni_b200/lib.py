@@ -83,6 +83,7 @@ SYMBOLS = {
                                   C.c_float, VP]),
     "omni_op_sample": (I32, [VP, VP, I32, C.c_float, I32, C.c_float, C.c_float, I32, I32, I32, I32, VP, VP, VP, VP,
                              VP, C.c_int64, I32, I32, VP, I32, I32]),
+    "omni_op_gemm_noalloc": (I32, [VP, I32, I32, VP, I32, VP, I32, I32, VP, I32, VP, C.c_char_p, C.c_size_t]),
 }
 
 _lib = None

@@ -81,3 +81,16 @@ class Ops:
                                              suppress_lo, suppress_hi, exempt, min_frames, _p(frames), _p(uniforms),
                                              _p(force), _p(state), _p(lines), stride, penalize, philox, _p(codes),
                                              group, rows))
+
+
+def gemm_noalloc(w, x, y, splits=0, bias=None, epilogue=0, stream=None):
+    """`omni_op_gemm_noalloc`: the tensor-core GEMM with its split-K scratch inside the library image, for callers
+    that cannot allocate device memory (no context object, no cudaMalloc). Waits for the result; raises OpsError
+    with the library's message on refusal."""
+    lib = L.load()
+    n, k = w.shape
+    msg = C.create_string_buffer(512)
+    rc = lib.omni_op_gemm_noalloc(_p(w), n, k, _p(x), x.shape[0], _p(y), y.stride(0), splits, _p(bias), epilogue,
+                                  C.c_void_p(stream) if stream else None, msg, len(msg))
+    if rc != L.OK:
+        raise OpsError(f"status {rc}: {msg.value.decode()}")
