@@ -90,6 +90,9 @@ typedef struct omni_talker_config {
   double kv_gib;          /* Limits::kv_gib: talker KV pool size */
   int32_t use_graphs;     /* 1: one CUDA graph per batch bucket per program; 0: eager launches */
   int32_t gemm_path;      /* 0: auto (vector GEMV for few rows, tcgen05 tiles otherwise); 1: GEMV only */
+  int32_t tick_kernel;    /* 1: run each graph program as ONE persistent cooperative kernel (phase list with grid
+                             barriers, weights streamed across phase boundaries) when the shapes allow it;
+                             0: one kernel per op */
 } omni_talker_config;
 
 /* `Draw` (model.rs:75-79): a uniform per codebook, or the frame to take

@@ -1,0 +1,137 @@
+// Decode attention of one (row, kv head) by a team of four warps over the paged KV
+//   kv[page][kv_head][K | V][16 tokens][D]   (bf16)
+// shared by the stand-alone attention kernel and the persistent tick kernel.
+// Value semantics of `attend` (crates/omni-qwen3/kernels/qwen3.cu:123-207): f32 scores and
+// accumulation, __expf, per-warp online softmax states merged at the end, bf16 output.
+#pragma once
+#include "util.cuh"
+
+namespace omni {
+
+constexpr int kAttnWarps = 4;
+
+// Element offset of (page, head, K or V, token-in-page) in a layer's KV buffer.
+template <int D>
+__device__ __forceinline__ int64_t kv_offset(int64_t page, int hk, int head, int which, int tok) {
+  return (((page * hk + head) * 2 + which) * 16 + tok) * D;
+}
+
+template <int D, int G>
+struct AttnShared {
+  float qs[G][D];  // the G query heads sharing this kv head, f32, filled by the caller
+  float ms[kAttnWarps][G], ls[kAttnWarps][G];
+  float os[kAttnWarps][G][D];
+};
+
+// `pages`: the sequence's page list, or nullptr when the sequence owns page `seq_page` alone (the code
+// predictor's per-frame KV). `len` keys. `out`: G heads of D, contiguous. tid: 0..127 within the team.
+// Warps take pages round-robin; within a page the two half-warps split the head dimension for q.k
+// (lane & 15 = key), then every lane owns D/32 output dims for p.v. The page's value slices are loaded
+// before the score math so their latency overlaps it. Ends with a team barrier (sh may be reused).
+template <int D, int G, typename TeamSync>
+__device__ __forceinline__ void attend_pages(AttnShared<D, G>& sh, const bf16* __restrict__ kv,
+                                             const int32_t* __restrict__ pages, int seq_page, int len, int hk, int kh,
+                                             float scale, bf16* __restrict__ out, int tid, const TeamSync& team) {
+  constexpr int PV = D / 32;   // output dims per lane
+  constexpr int HALF = D / 2;  // q.k dims per half-warp
+  const int lane = tid & 31, warp = tid >> 5;
+  const int key = lane & 15, half = lane >> 4;
+  float m[G], l[G], acc[G][PV];
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    m[g] = -INFINITY;
+    l[g] = 0.f;
+#pragma unroll
+    for (int d = 0; d < PV; ++d) acc[g][d] = 0.f;
+  }
+  const int npages = (len + 15) >> 4;
+  for (int pi = warp; pi < npages; pi += kAttnWarps) {
+    const int64_t page = pages ? pages[pi] : seq_page;
+    const int ntok = min(16, len - pi * 16);
+    const bf16* kpage = kv + kv_offset<D>(page, hk, kh, 0, 0);
+    const bf16* vpage = kpage + 16 * D;
+    uint2 vraw[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      if constexpr (PV == 4)
+        vraw[j] = *reinterpret_cast<const uint2*>(vpage + j * D + lane * 4);
+      else
+        vraw[j] = make_uint2(*reinterpret_cast<const uint32_t*>(vpage + j * D + lane * 2), 0u);
+    }
+    float sc[G];
+#pragma unroll
+    for (int g = 0; g < G; ++g) sc[g] = 0.f;
+    const bf16* krow = kpage + key * D + half * HALF;
+#pragma unroll
+    for (int c = 0; c < HALF; c += 8) {
+      float kf[8];
+      ld8(krow + c, kf);
+#pragma unroll
+      for (int g = 0; g < G; ++g)
+#pragma unroll
+        for (int e = 0; e < 8; ++e) sc[g] = fmaf(sh.qs[g][half * HALF + c + e], kf[e], sc[g]);
+    }
+    float p[G];
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      float s = sc[g] + __shfl_xor_sync(0xffffffffu, sc[g], 16);
+      s = key < ntok ? s * scale : -INFINITY;
+      const float m2 = fmaxf(m[g], warp_fmax(s));
+      const float corr = __expf(m[g] - m2);
+      p[g] = __expf(s - m2);
+      float ps = p[g];  // sum over the 16 keys (both half-warps hold the same values)
+#pragma unroll
+      for (int o = 8; o > 0; o >>= 1) ps += __shfl_xor_sync(0xffffffffu, ps, o);
+      l[g] = l[g] * corr + ps;
+#pragma unroll
+      for (int d = 0; d < PV; ++d) acc[g][d] *= corr;
+      m[g] = m2;
+    }
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      float vf[PV];
+      if constexpr (PV == 4) {
+        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&vraw[j].x));
+        const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&vraw[j].y));
+        vf[0] = a.x, vf[1] = a.y, vf[2] = b.x, vf[3] = b.y;
+      } else {
+        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&vraw[j].x));
+        vf[0] = a.x, vf[1] = a.y;
+      }
+      const bool live = j < ntok;  // tokens past the sequence end contribute nothing
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+        const float pj = __shfl_sync(0xffffffffu, p[g], j);
+#pragma unroll
+        for (int d = 0; d < PV; ++d) acc[g][d] = live ? fmaf(pj, vf[d], acc[g][d]) : acc[g][d];
+      }
+    }
+  }
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    if (lane == 0) {
+      sh.ms[warp][g] = m[g];
+      sh.ls[warp][g] = l[g];
+    }
+#pragma unroll
+    for (int d = 0; d < PV; ++d) sh.os[warp][g][lane * PV + d] = acc[g][d];
+  }
+  team.sync();
+  for (int i = tid; i < G * D; i += kAttnWarps * 32) {
+    const int g = i / D, d = i % D;
+    float top = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kAttnWarps; ++w) top = fmaxf(top, sh.ms[w][g]);
+    float num = 0.f, den = 0.f;
+#pragma unroll
+    for (int w = 0; w < kAttnWarps; ++w) {
+      const float e = __expf(sh.ms[w][g] - top);
+      num += sh.os[w][g][d] * e;
+      den += sh.ls[w][g] * e;
+    }
+    out[(int64_t)g * D + d] = __float2bfloat16(num / den);
+  }
+  team.sync();
+}
+
+}  // namespace omni

@@ -119,7 +119,10 @@ template <int BN>
 struct TcShape {
   static constexpr int kStageBytes = kTileW * kTileK * 2 + BN * kTileK * 2;
   static constexpr int kStages = (200 * 1024 / kStageBytes) > 8 ? 8 : (200 * 1024 / kStageBytes);
-  static constexpr int kTmemCols = BN < 32 ? 32 : BN;
+  // One accumulator: a tcgen05.mma occupies the tensor pipe for a fixed ~140 cycles whatever its shape
+  // (measured), so rotating accumulators buys nothing.
+  static constexpr int kAccs = 1;
+  static constexpr int kTmemCols = BN * kAccs < 32 ? 32 : BN * kAccs;
   static constexpr size_t kSmemBytes = (size_t)kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
 };
 
@@ -199,8 +202,8 @@ __global__ void __launch_bounds__(128, 1)
         const uint64_t adesc = kmajor_sw128_desc(a_src), bdesc = kmajor_sw128_desc(b_src);
 #pragma unroll
         for (int k = 0; k < kTileK / 16; ++k)
-          mma_bf16(tmem_base, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2), idesc,
-                   (kb > kb_begin || k > 0) ? 1u : 0u);
+          mma_bf16(tmem_base + (uint32_t)((k % S::kAccs) * BN), adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2),
+                   idesc, (kb > kb_begin || k >= S::kAccs) ? 1u : 0u);
         mma_commit(empty_bar(stage));  // frees the stage once these MMAs have read it
         if (++stage == S::kStages) {
           stage = 0;
@@ -229,6 +232,13 @@ __global__ void __launch_bounds__(128, 1)
     for (int c0 = 0; c0 < BN; c0 += 16) {
       float v[16];
       tmem_ld16(lane_addr + c0, v);
+#pragma unroll
+      for (int a = 1; a < S::kAccs; ++a) {  // fixed order: ((acc0 + acc1) + acc2) + acc3
+        float w[16];
+        tmem_ld16(lane_addr + a * BN + c0, w);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) v[j] += w[j];
+      }
       if (splits == 1) {
 #pragma unroll
         for (int j = 0; j < 16; ++j)

@@ -140,7 +140,7 @@ int32_t omni_op_add_norm(omni_ops* c, const void* x, void* res, const void* w, v
 
 int32_t omni_op_silu_mul(omni_ops* c, const void* gate_up, void* act, int32_t rows, int32_t inter) {
   if (!c || inter % 8) return OMNI_ERR_INVALID;
-  OPS_CUDA(c, launch_silu_mul((const bf16*)gate_up, (bf16*)act, rows, inter, c->stream));
+  OPS_CUDA(c, launch_silu_mul((const bf16*)gate_up, (bf16*)act, rows, inter, 0, c->stream));
   return OMNI_OK;
 }
 

@@ -1,0 +1,331 @@
+// Token selection for one row by a team of THREADS threads (a whole CTA, or the worker warps of the
+// persistent tick kernel). Vocabulary at most 4096.
+//
+// The chain is the one of crates/omni-qwen3-tts/kernels/talker.cu:108-293: repetition penalty and
+// suppression on the raw logits, temperature, top-k with ties kept (the k-th largest found by a radix
+// select over order-preserving integer keys), softmax numerators with __expf, and an inverse-CDF walk
+// in vocabulary order against one uniform. The reference runs 1024 threads with four consecutive
+// logits each, and the association order of its block scan decides which token a uniform lands on.
+// That order is reproduced here for any team size by scanning 1024 *virtual* threads: per-virtual-
+// thread sum of four, a Hillis-Steele inclusive scan over each group of 32 virtual lanes, the same
+// scan over the 32 group totals, exclusive prefix formed as (group_before + inclusive) - own.
+// Not in the reference: top_p < 1 (nucleus filter after top-k) and uniforms from Philox4x32-10.
+#pragma once
+#include "util.cuh"
+
+namespace omni {
+namespace sampler {
+
+constexpr int kVocabMax = 4096;
+constexpr int kVirtualThreads = 1024;  // the reference's block size
+constexpr int kVirtualPer = 4;         // logits per virtual thread
+constexpr int kMaxNucleus = 1024;
+
+struct CtaSync {
+  static __device__ __forceinline__ void sync() { __syncthreads(); }
+};
+
+template <int ID, int COUNT>
+struct NamedSync {
+  static __device__ __forceinline__ void sync() { asm volatile("bar.sync %0, %1;" ::"n"(ID), "n"(COUNT) : "memory"); }
+};
+
+__device__ __forceinline__ uint32_t order_key(float v) {
+  const uint32_t u = __float_as_uint(v);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
+// Philox4x32-10, counter (frame, group, 0, 0), key = the sequence's seed; first word -> [0, 1) with 24 bits.
+__device__ __forceinline__ float philox_uniform(uint64_t seed, uint32_t frame, uint32_t group) {
+  uint32_t c0 = frame, c1 = group, c2 = 0u, c3 = 0u;
+  uint32_t k0 = (uint32_t)seed, k1 = (uint32_t)(seed >> 32);
+#pragma unroll
+  for (int r = 0; r < 10; ++r) {
+    const uint32_t h0 = __umulhi(0xD2511F53u, c0), l0 = 0xD2511F53u * c0;
+    const uint32_t h1 = __umulhi(0xCD9E8D57u, c2), l1 = 0xCD9E8D57u * c2;
+    const uint32_t n0 = h1 ^ c1 ^ k0, n2 = h0 ^ c3 ^ k1;
+    c0 = n0, c1 = l1, c2 = n2, c3 = l0;
+    k0 += 0x9E3779B9u;
+    k1 += 0xBB67AE85u;
+  }
+  return (float)(c0 >> 8) * (1.0f / 16777216.0f);
+}
+
+struct Shared {
+  uint32_t hist[256];
+  float red[32];
+  float wtot[32];
+  float vscan[kVirtualThreads];
+  uint32_t sel_prefix, sel_left;
+  int token, last;
+  unsigned long long best;
+  int n_cand;
+  int cand_idx[kMaxNucleus];
+  float cand_p[kMaxNucleus];
+  int sorted_idx[kMaxNucleus];
+  float sorted_p[kMaxNucleus];
+  uint32_t drop[kVocabMax / 32];
+};
+
+struct Params {
+  int vocab;
+  float temperature;
+  int top_k;
+  float top_p;
+  float penalty;
+  int suppress_lo, suppress_hi, exempt, min_frames;
+  int penalize;
+  int group;
+  int philox;
+  int seen_words;
+};
+
+// Team thread `tid` owns the PER = 4096 / THREADS consecutive logits starting at tid * PER.
+template <int THREADS, typename Sync>
+struct Team {
+  static constexpr int PER = kVocabMax / THREADS;
+  static constexpr int VPT = kVirtualThreads / THREADS;  // virtual threads per team thread
+  static_assert(PER % kVirtualPer == 0 && THREADS >= 32 && THREADS <= kVirtualThreads, "team size");
+
+  static __device__ float team_max(float v, int tid, Shared& sh) {
+    v = warp_fmax(v);
+    if ((tid & 31) == 0) sh.red[tid >> 5] = v;
+    Sync::sync();
+    float m = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < THREADS / 32; ++w) m = fmaxf(m, sh.red[w]);
+    Sync::sync();
+    return m;
+  }
+
+  // The k-th largest key of the row (ties share it): four 8-bit digits from the top, each pass
+  // histogramming the keys that match the digits fixed so far.
+  static __device__ uint32_t kth_largest_key(const uint32_t* key, int vocab, uint32_t k, int tid, Shared& sh) {
+    uint32_t prefix = 0, left = k;
+    for (int shift = 24; shift >= 0; shift -= 8) {
+      for (int i = tid; i < 256; i += THREADS) sh.hist[i] = 0;
+      Sync::sync();
+      const uint32_t fixed = shift == 24 ? 0u : 0xffffffffu << (shift + 8);
+#pragma unroll
+      for (int j = 0; j < PER; ++j)
+        if (tid * PER + j < vocab && ((key[j] ^ prefix) & fixed) == 0)
+          atomicAdd(&sh.hist[(key[j] >> shift) & 255], 1u);
+      Sync::sync();
+      if (tid < 32) {
+        // lane t holds digits 8t..8t+7; keys in strictly higher lanes via a suffix scan
+        uint32_t c[8], mine = 0;
+#pragma unroll
+        for (int b = 0; b < 8; ++b) mine += c[b] = sh.hist[tid * 8 + b];
+        uint32_t suffix = mine;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+          const uint32_t other = __shfl_down_sync(0xffffffffu, suffix, o);
+          if (tid + o < 32) suffix += other;
+        }
+        uint32_t above = suffix - mine;
+#pragma unroll
+        for (int b = 7; b >= 0; --b) {
+          if (above < left && above + c[b] >= left) {
+            sh.sel_prefix = prefix | (uint32_t)(tid * 8 + b) << shift;
+            sh.sel_left = left - above;
+          }
+          above += c[b];
+        }
+      }
+      Sync::sync();
+      prefix = sh.sel_prefix;
+      left = sh.sel_left;
+    }
+    return prefix;
+  }
+
+  // v: this thread's PER processed logits (-inf beyond the vocabulary).
+  static __device__ int draw(const float* v, int vocab, float temperature, int top_k, float top_p, float u, int tid,
+                             Shared& sh) {
+    if (temperature <= 0.f) {  // argmax, lowest index on ties (talker.cu:177-188)
+      if (tid == 0) sh.best = 0ull;
+      Sync::sync();
+#pragma unroll
+      for (int j = 0; j < PER; ++j) {
+        const int i = tid * PER + j;
+        if (i < vocab) atomicMax(&sh.best, (unsigned long long)order_key(v[j]) << 32 | (uint32_t)(4095 - i));
+      }
+      Sync::sync();
+      const int token = 4095 - (int)(sh.best & 0xffffffffull);
+      Sync::sync();
+      return token;
+    }
+    float x[PER];
+    uint32_t key[PER];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+      x[j] = v[j] / temperature;
+      key[j] = order_key(x[j]);
+      mx = fmaxf(mx, x[j]);
+    }
+    const int keep = top_k > 0 && top_k < vocab ? top_k : vocab;
+    const uint32_t threshold = keep < vocab ? kth_largest_key(key, vocab, (uint32_t)keep, tid, sh) : 0u;
+    const float m = team_max(mx, tid, sh);
+    float p[PER];
+#pragma unroll
+    for (int j = 0; j < PER; ++j) p[j] = tid * PER + j < vocab && key[j] >= threshold ? __expf(x[j] - m) : 0.f;
+
+    if (top_p < 1.f) {
+      // compact the survivors, rank them by (probability desc, index asc), walk the ranking once
+      // and drop every token whose preceding mass already reaches top_p
+      if (tid == 0) sh.n_cand = 0;
+      for (int i = tid; i < kVocabMax / 32; i += THREADS) sh.drop[i] = 0u;
+      Sync::sync();
+#pragma unroll
+      for (int j = 0; j < PER; ++j)
+        if (p[j] > 0.f) {
+          const int at = atomicAdd(&sh.n_cand, 1);
+          if (at < kMaxNucleus) {
+            sh.cand_idx[at] = tid * PER + j;
+            sh.cand_p[at] = p[j];
+          }
+        }
+      Sync::sync();
+      const int nc = min(sh.n_cand, kMaxNucleus);
+      for (int a = tid; a < nc; a += THREADS) {
+        const float pa = sh.cand_p[a];
+        const int ia = sh.cand_idx[a];
+        int rank = 0;
+        for (int b = 0; b < nc; ++b) {
+          const float pb = sh.cand_p[b];
+          rank += (pb > pa) || (pb == pa && sh.cand_idx[b] < ia);
+        }
+        sh.sorted_idx[rank] = ia;
+        sh.sorted_p[rank] = pa;
+      }
+      Sync::sync();
+      if (tid == 0) {
+        float tot = 0.f;
+        for (int r = 0; r < nc; ++r) tot += sh.sorted_p[r];
+        float before = 0.f;
+        for (int r = 0; r < nc; ++r) {
+          const float mine = sh.sorted_p[r];
+          if (r > 0 && before >= top_p * tot) {
+            const int idx = sh.sorted_idx[r];
+            sh.drop[idx >> 5] |= 1u << (idx & 31);
+          }
+          before += mine;
+        }
+      }
+      Sync::sync();
+#pragma unroll
+      for (int j = 0; j < PER; ++j) {
+        const int i = tid * PER + j;
+        if (sh.drop[i >> 5] >> (i & 31) & 1u) p[j] = 0.f;
+      }
+    }
+
+    // --- the reference's block scan over 1024 virtual threads (talker.cu:136-169) ---
+    float own[VPT], incl[VPT];
+#pragma unroll
+    for (int q = 0; q < VPT; ++q) {
+      float o = 0.f;
+#pragma unroll
+      for (int e = 0; e < kVirtualPer; ++e) o += p[q * kVirtualPer + e];
+      own[q] = incl[q] = o;
+      sh.vscan[tid * VPT + q] = o;
+    }
+    if (tid == 0) {
+      sh.token = -1;
+      sh.last = 0;
+    }
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      Sync::sync();
+      float up[VPT];
+#pragma unroll
+      for (int q = 0; q < VPT; ++q) {
+        const int vt = tid * VPT + q;
+        up[q] = (vt & 31) >= o ? sh.vscan[vt - o] : 0.f;
+      }
+      Sync::sync();
+#pragma unroll
+      for (int q = 0; q < VPT; ++q) {
+        const int vt = tid * VPT + q;
+        if ((vt & 31) >= o) incl[q] += up[q];
+        sh.vscan[vt] = incl[q];
+      }
+    }
+    Sync::sync();
+    if (tid < 32) {  // the same scan over the 32 group totals
+      float wsum = sh.vscan[tid * 32 + 31];
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const float up = __shfl_up_sync(0xffffffffu, wsum, o);
+        if (tid >= o) wsum += up;
+      }
+      sh.wtot[tid] = wsum;
+    }
+    Sync::sync();
+    const float total = sh.wtot[31];
+    const float target = u * total;
+#pragma unroll
+    for (int q = 0; q < VPT; ++q) {
+      const int vt = tid * VPT + q, vw = vt >> 5;
+      const float before = vw > 0 ? sh.wtot[vw - 1] : 0.f;
+      float run = before + incl[q] - own[q];
+#pragma unroll
+      for (int e = 0; e < kVirtualPer; ++e) {
+        const float pe = p[q * kVirtualPer + e];
+        const int i = vt * kVirtualPer + e;
+        if (pe > 0.f) {
+          atomicMax(&sh.last, i);
+          if (run <= target && target < run + pe) atomicMax(&sh.token, i);
+        }
+        run += pe;
+      }
+    }
+    Sync::sync();
+    const int token = sh.token >= 0 ? sh.token : sh.last;
+    Sync::sync();
+    return token;
+  }
+
+  // `talker_sample` (talker.cu:259-293) for one row. `load(i, j)` returns logit i = tid * PER + j as f32 (already rounded
+  // to bf16 by the caller). slot: i32 last_frame[16] | u32 seen[seen_words] | u64 seed (8-byte aligned).
+  // Returns the token (identical in every team thread); thread 0 writes codes, the slot and the bitmap.
+  template <typename Load>
+  static __device__ int sample_row(Load load, const Params& prm, int frame, float uniform, int forced, int32_t* slot,
+                                   int32_t* code_out, int tid, Shared& sh) {
+    uint32_t* seen = reinterpret_cast<uint32_t*>(slot + 16);
+    int token = forced;
+    if (forced < 0) {
+      const bool exempt_blocked = frame < prm.min_frames;
+      float v[PER];
+#pragma unroll
+      for (int j = 0; j < PER; ++j) {
+        const int i = tid * PER + j;
+        float x = -INFINITY;
+        if (i < prm.vocab) {
+          x = load(i, j);
+          if (prm.penalize && (seen[i / 32] >> (i % 32) & 1u)) x = x > 0.f ? x / prm.penalty : x * prm.penalty;
+          const bool in_range = i >= prm.suppress_lo && i < prm.suppress_hi;
+          if ((in_range && i != prm.exempt) || (i == prm.exempt && exempt_blocked)) x = -INFINITY;
+        }
+        v[j] = x;
+      }
+      float u = uniform;
+      if (prm.philox) {
+        const uint64_t seed = *reinterpret_cast<const uint64_t*>(seen + prm.seen_words + (prm.seen_words & 1));
+        u = philox_uniform(seed, (uint32_t)frame, (uint32_t)prm.group);
+      }
+      token = min(max(draw(v, prm.vocab, prm.temperature, prm.top_k, prm.top_p, u, tid, sh), 0), prm.vocab - 1);
+    }
+    Sync::sync();  // every thread has read the bitmap before it changes
+    if (tid == 0) {
+      *code_out = token;
+      slot[prm.group] = token;
+      if (prm.penalize) seen[token / 32] |= 1u << (token % 32);
+    }
+    return token;
+  }
+};
+
+}  // namespace sampler
+}  // namespace omni

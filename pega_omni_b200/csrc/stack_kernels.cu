@@ -3,7 +3,9 @@
 // over the paged KV. Rounding points follow the reference's kernels
 // (crates/omni-qwen3/kernels/qwen3.cu, crates/omni-kern/kernels/common.cuh):
 // every tensor that crosses HBM is bf16, arithmetic is f32.
+#include "attend.cuh"
 #include "kernels.h"
+#include "sampler.cuh"
 
 namespace omni {
 
@@ -53,14 +55,18 @@ __global__ void add_norm_kernel(const bf16* __restrict__ x, bf16* __restrict__ r
   st8(out + (int64_t)(n / every) * dim + threadIdx.x * 8, v);
 }
 
-// `silu_mul` (common.cuh:66-76).
-__global__ void silu_mul_kernel(const bf16* __restrict__ gate_up, bf16* __restrict__ act, int inter, int total) {
+// `silu_mul` (common.cuh:66-76). With `interleaved`, the fused row alternates 16 gate channels and the matching
+// 16 up channels (the weight layout the tensor-core SwiGLU epilogue wants) instead of [all gate | all up].
+__global__ void silu_mul_kernel(const bf16* __restrict__ gate_up, bf16* __restrict__ act, int inter, int total,
+                                int interleaved) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= total) return;
   const int64_t n = i / (inter / 8), c = i % (inter / 8) * 8;
   float g[8], u[8];
-  ld8(gate_up + n * 2 * inter + c, g);
-  ld8(gate_up + n * 2 * inter + inter + c, u);
+  const int64_t g_at = interleaved ? (c / 16) * 32 + c % 16 : c;
+  const int64_t u_at = interleaved ? g_at + 16 : inter + c;
+  ld8(gate_up + n * 2 * inter + g_at, g);
+  ld8(gate_up + n * 2 * inter + u_at, u);
 #pragma unroll
   for (int k = 0; k < 8; ++k) g[k] = bf16_round(g[k] / (1.f + __expf(-g[k]))) * u[k];
   st8(act + (int64_t)i * 8, g);
@@ -80,9 +86,10 @@ cudaError_t launch_add_norm(const bf16* x, bf16* res, const bf16* w, bf16* out, 
   return cudaGetLastError();
 }
 
-cudaError_t launch_silu_mul(const bf16* gate_up, bf16* act, int rows, int inter, cudaStream_t s) {
+cudaError_t launch_silu_mul(const bf16* gate_up, bf16* act, int rows, int inter, int interleaved, cudaStream_t s) {
   const int total = rows * (inter / 8);
-  silu_mul_kernel<<<(total + 255) / 256, 256, 0, s>>>(gate_up, act, inter, total);
+  if (interleaved && inter % 16) return cudaErrorInvalidValue;
+  silu_mul_kernel<<<(total + 255) / 256, 256, 0, s>>>(gate_up, act, inter, total, interleaved);
   return cudaGetLastError();
 }
 
@@ -108,12 +115,6 @@ __device__ __forceinline__ RowAt locate(const RowMap& m, int n) {
     r.pages = nullptr;
   }
   return r;
-}
-
-// Element offset of (page, head, K or V, token-in-page) in a layer's KV buffer.
-template <int D>
-__device__ __forceinline__ int64_t kv_offset(int64_t page, int hk, int head, int which, int tok) {
-  return (((page * hk + head) * 2 + which) * 16 + tok) * D;
 }
 
 // ---- q/k norm + RoPE + KV write -------------------------------------------------
@@ -186,130 +187,20 @@ cudaError_t launch_rope_kv(bf16* qkv, const bf16* q_norm, const bf16* k_norm, bf
 }
 
 // ---- decode attention -------------------------------------------------------------
+// The page loop lives in attend.cuh; here one CTA of four warps handles one (row, kv head).
 
-constexpr int kAttnWarps = 4;
-
-// One CTA per (row, kv head); its G query heads share the K/V stream. Warps
-// take pages round-robin. Within a page the two half-warps split the head
-// dimension for q.k (lane & 15 = key), then every lane owns D/32 output dims
-// for p.v. Each warp keeps an online-softmax state per query head; the four
-// states merge through shared memory. Value semantics of `attend`
-// (qwen3.cu:123-207): f32 scores and accumulation, __expf, bf16 output.
 template <int D, int G>
 __global__ void __launch_bounds__(kAttnWarps * 32) attend_kernel(const bf16* __restrict__ qkv,
                                                                  const bf16* __restrict__ kv, bf16* __restrict__ out,
                                                                  RowMap map, int hq, int hk, float scale) {
-  constexpr int PV = D / 32;    // output dims per lane
-  constexpr int HALF = D / 2;   // q.k dims per half-warp
+  __shared__ AttnShared<D, G> sh;
   const int n = blockIdx.x, kh = blockIdx.y;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int key = lane & 15, half = lane >> 4;
-  __shared__ float qs[G][D];
-  __shared__ float ms[kAttnWarps][G], ls[kAttnWarps][G];
-  __shared__ float os[kAttnWarps][G][D];
   const RowAt at = locate(map, n);
-  const int len = at.pos + 1;
   const bf16* q = qkv + ((int64_t)n * (hq + 2 * hk) + kh * G) * D;
-  for (int i = threadIdx.x; i < G * D; i += blockDim.x) qs[i / D][i % D] = __bfloat162float(q[i]);
+  for (int i = threadIdx.x; i < G * D; i += blockDim.x) sh.qs[i / D][i % D] = __bfloat162float(q[i]);
   __syncthreads();
-
-  float m[G], l[G], acc[G][PV];
-#pragma unroll
-  for (int g = 0; g < G; ++g) {
-    m[g] = -INFINITY;
-    l[g] = 0.f;
-#pragma unroll
-    for (int d = 0; d < PV; ++d) acc[g][d] = 0.f;
-  }
-  const int npages = (len + 15) >> 4;
-  for (int pi = warp; pi < npages; pi += kAttnWarps) {
-    const int64_t page = at.pages ? at.pages[pi] : at.seq;
-    const int ntok = min(16, len - pi * 16);
-    const bf16* kpage = kv + kv_offset<D>(page, hk, kh, 0, 0);
-    const bf16* vpage = kpage + 16 * D;
-    // issue the page's value loads first so they fly while q.k is computed
-    uint2 vraw[16];
-#pragma unroll
-    for (int j = 0; j < 16; ++j) {
-      if constexpr (PV == 4)
-        vraw[j] = *reinterpret_cast<const uint2*>(vpage + j * D + lane * 4);
-      else
-        vraw[j] = make_uint2(*reinterpret_cast<const uint32_t*>(vpage + j * D + lane * 2), 0u);
-    }
-    float sc[G];
-#pragma unroll
-    for (int g = 0; g < G; ++g) sc[g] = 0.f;
-    const bf16* krow = kpage + key * D + half * HALF;
-#pragma unroll
-    for (int c = 0; c < HALF; c += 8) {
-      float kf[8];
-      ld8(krow + c, kf);
-#pragma unroll
-      for (int g = 0; g < G; ++g)
-#pragma unroll
-        for (int e = 0; e < 8; ++e) sc[g] = fmaf(qs[g][half * HALF + c + e], kf[e], sc[g]);
-    }
-    float p[G];
-#pragma unroll
-    for (int g = 0; g < G; ++g) {
-      float s = sc[g] + __shfl_xor_sync(0xffffffffu, sc[g], 16);
-      s = key < ntok ? s * scale : -INFINITY;
-      const float m2 = fmaxf(m[g], warp_fmax(s));
-      const float corr = __expf(m[g] - m2);
-      p[g] = __expf(s - m2);
-      float ps = p[g];  // sum over the 16 keys (both half-warps hold the same values)
-#pragma unroll
-      for (int o = 8; o > 0; o >>= 1) ps += __shfl_xor_sync(0xffffffffu, ps, o);
-      l[g] = l[g] * corr + ps;
-#pragma unroll
-      for (int d = 0; d < PV; ++d) acc[g][d] *= corr;
-      m[g] = m2;
-    }
-    // every token's value slice was fetched up front (vraw); tokens past the sequence end contribute nothing
-#pragma unroll
-    for (int j = 0; j < 16; ++j) {
-      float vf[PV];
-      if constexpr (PV == 4) {
-        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&vraw[j].x));
-        const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&vraw[j].y));
-        vf[0] = a.x, vf[1] = a.y, vf[2] = b.x, vf[3] = b.y;
-      } else {
-        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&vraw[j].x));
-        vf[0] = a.x, vf[1] = a.y;
-      }
-      const bool live = j < ntok;
-#pragma unroll
-      for (int g = 0; g < G; ++g) {
-        const float pj = __shfl_sync(0xffffffffu, p[g], j);
-#pragma unroll
-        for (int d = 0; d < PV; ++d) acc[g][d] = live ? fmaf(pj, vf[d], acc[g][d]) : acc[g][d];
-      }
-    }
-  }
-#pragma unroll
-  for (int g = 0; g < G; ++g) {
-    if (lane == 0) {
-      ms[warp][g] = m[g];
-      ls[warp][g] = l[g];
-    }
-#pragma unroll
-    for (int d = 0; d < PV; ++d) os[warp][g][lane * PV + d] = acc[g][d];
-  }
-  __syncthreads();
-  for (int i = threadIdx.x; i < G * D; i += blockDim.x) {
-    const int g = i / D, d = i % D;
-    float top = -INFINITY;
-#pragma unroll
-    for (int w = 0; w < kAttnWarps; ++w) top = fmaxf(top, ms[w][g]);
-    float num = 0.f, den = 0.f;
-#pragma unroll
-    for (int w = 0; w < kAttnWarps; ++w) {
-      const float e = __expf(ms[w][g] - top);
-      num += os[w][g][d] * e;
-      den += ls[w][g] * e;
-    }
-    out[((int64_t)n * hq + kh * G + g) * D + d] = __float2bfloat16(num / den);
-  }
+  attend_pages<D, G>(sh, kv, at.pages, at.seq, at.pos + 1, hk, kh, scale, out + ((int64_t)n * hq + kh * G) * D,
+                     threadIdx.x, sampler::CtaSync());
 }
 
 template <int D>

@@ -9,6 +9,7 @@
 #include <cmath>
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <map>
 #include <memory>
@@ -20,6 +21,7 @@
 #include "../../include/omni_b200.h"
 #include "gemm.h"
 #include "kernels.h"
+#include "tick.h"
 
 namespace omni {
 
@@ -36,6 +38,19 @@ int bucket_of(int n) {
 __global__ void f32_to_bf16_kernel(const float* __restrict__ src, bf16* __restrict__ dst, int64_t n) {
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) dst[i] = __float2bfloat16(src[i]);
+}
+
+// dst = the fused [gate; up] rows of src regrouped as 16 gate rows, the matching 16 up rows, 16 gate rows, ...:
+// the layout that puts a gate channel and its up channel 16 TMEM lanes apart in one tensor-core tile.
+__global__ void interleave_gate_up_kernel(const bf16* __restrict__ src, bf16* __restrict__ dst, int inter, int k) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;  // one 16-byte piece
+  const int64_t per_row = k / 8, total = (int64_t)2 * inter * per_row;
+  if (i >= total) return;
+  const int64_t row = i / per_row, piece = i % per_row;
+  const bool up = row >= inter;
+  const int64_t c = up ? row - inter : row;
+  const int64_t out_row = (c / 16) * 32 + (up ? 16 : 0) + c % 16;
+  *reinterpret_cast<Pack8*>(dst + out_row * k + piece * 8) = *reinterpret_cast<const Pack8*>(src + row * k + piece * 8);
 }
 
 uint16_t host_f2bf(float f) {
@@ -129,7 +144,16 @@ struct omni_talker {
   std::map<std::tuple<const void*, const void*, const void*, int, int>, TcGemmPlan> plans;
   std::map<std::pair<int, int>, cudaGraphExec_t> graphs;  // (program, bucket)
   std::map<std::pair<int, int>, int> graph_nodes;           // kernel nodes of each captured graph
-  int launches = 0;
+  // the persistent tick kernel: one compiled phase list per (program, bucket)
+  bool tick_ok = false;
+  int tick_ctas = 0;
+  uint32_t* tick_barrier = nullptr;
+  std::map<std::pair<int, int>, TickProgram> tick_programs;
+  int launches = 0, tick_phases = 0;
+  std::string trace_path;
+  bool trace_checked = false;
+  unsigned long long* trace = nullptr;
+  const TickProgram* trace_program = nullptr;
   omni_stats stats{};
   int last_n = 0;
 
@@ -238,8 +262,19 @@ int load_stack(omni_talker* m, const TensorIndex& idx, const std::string& prefix
     TRY(upload(m, idx, p + "self_attn.k_norm.weight", {d}, L.k_norm));
     TRY(upload(m, idx, p + "self_attn.o_proj.weight", {h, q}, L.o));
     TRY(upload(m, idx, p + "post_attention_layernorm.weight", {h}, L.ln2));
-    TRY(upload(m, idx, p + "mlp.gate_proj.weight", {I, h}, L.gate_up));
-    TRY(upload(m, idx, p + "mlp.up_proj.weight", {I, h}, L.gate_up + I * h));
+    {
+      bf16* fused = nullptr;  // [gate; up] as in the checkpoint, then regrouped 16 by 16 (see interleave_gate_up_kernel)
+      CUDA_TRY(m, cudaMalloc((void**)&fused, (size_t)2 * I * h * sizeof(bf16)));
+      int rc = upload(m, idx, p + "mlp.gate_proj.weight", {I, h}, fused);
+      if (rc == OMNI_OK) rc = upload(m, idx, p + "mlp.up_proj.weight", {I, h}, fused + I * h);
+      if (rc == OMNI_OK) {
+        const int64_t pieces = 2 * I * (h / 8);
+        interleave_gate_up_kernel<<<(unsigned)((pieces + 255) / 256), 256, 0, m->stream>>>(fused, L.gate_up, (int)I, (int)h);
+        if (cudaStreamSynchronize(m->stream) != cudaSuccess) rc = m->fail(OMNI_ERR_CUDA, "gate|up regroup failed");
+      }
+      cudaFree(fused);
+      TRY(rc);
+    }
     TRY(upload(m, idx, p + "mlp.down_proj.weight", {h, I}, L.down));
   }
   TRY(dev_alloc(m, &out->norm, h));
@@ -305,7 +340,7 @@ int stack_forward(omni_talker* m, const StackW& S, const Scratch& s, const bf16*
     TRY(gemm(m, L.o, h, qd, s.attn, rows, s.x, h));
     LAUNCH(m, launch_add_norm(s.x, s.res, L.ln2, s.x, rows, h, c.rms_eps, 1, 0, m->stream));
     TRY(gemm(m, L.gate_up, 2 * I, h, s.x, rows, s.gate_up, 2 * I));
-    LAUNCH(m, launch_silu_mul(s.gate_up, s.act, rows, I, m->stream));
+    LAUNCH(m, launch_silu_mul(s.gate_up, s.act, rows, I, 1, m->stream));
     TRY(gemm(m, L.down, h, I, s.act, rows, s.x, h));
     if (i + 1 < c.layers)
       LAUNCH(m, launch_add_norm(s.x, s.res, S.layers[i + 1].ln1, s.x, rows, h, c.rms_eps, 1, 0, m->stream));
@@ -399,9 +434,219 @@ int enqueue_program(omni_talker* m, int program, int b) {
   return enqueue_tail(m, b);
 }
 
-// Runs a graph program at bucket b: replay of its captured graph, or eager launches.
+
+// ---- the persistent tick kernel's phase list ------------------------------------------------------------------
+
+int pick_bn(int rows) { return rows <= 16 ? 16 : rows <= 32 ? 32 : rows <= 64 ? 64 : rows <= 128 ? 128 : 256; }
+
+struct TickBuilder {
+  omni_talker* m;
+  TickProgram* prog;
+  int ctas;
+  int offset = 0;  // CTA the next phase's first item lands on, so consecutive phases load different SMs first
+  std::map<std::tuple<const void*, int, int, int>, int> map_cache;
+  bool failed = false;
+
+  int map_of(const bf16* base, int rows, int K, int box) {
+    const auto key = std::make_tuple((const void*)base, rows, K, box);
+    auto it = map_cache.find(key);
+    if (it != map_cache.end()) return it->second;
+    const int idx = tick_add_map(prog, base, rows, K, box);
+    if (idx < 0) failed = true;
+    map_cache[key] = idx;
+    return idx;
+  }
+
+  Phase blank(int type, int rows) {
+    Phase ph;
+    memset(&ph, 0, sizeof(ph));
+    ph.type = type;
+    ph.rows = rows;
+    ph.cta_offset = offset;
+    return ph;
+  }
+
+  // y = x . w^T as f32 partial tiles (or SwiGLU activations); returns {tiles, splits, bn} for the consumer.
+  Phase gemm(const bf16* w, int N, int K, const bf16* x, int rows, int mode = kGemmPartials, bf16* act = nullptr,
+             int inter = 0) {
+    Phase ph = blank(kPhGemm, rows);
+    ph.N = N;
+    ph.K = K;
+    ph.bn = pick_bn(rows);
+    ph.tiles = (N + 127) / 128;
+    const int nkb = K / 64;
+    int splits = mode == kGemmSwiglu ? 1 : std::max(1, std::min(ctas / ph.tiles, nkb / 4));
+    ph.splits = splits;
+    ph.mode = mode;
+    ph.wmap = map_of(w, N, K, 128);
+    ph.xmap = map_of(x, rows, K, ph.bn);
+    ph.dst0 = act;
+    ph.i0 = inter;
+    prog->phases.push_back(ph);
+    prog->max_bn = std::max(prog->max_bn, ph.bn);
+    if (mode == kGemmPartials)
+      prog->partial_floats = std::max(prog->partial_floats, (size_t)splits * ph.tiles * ph.bn * 128);
+    offset = (offset + ph.tiles * splits) % ctas;
+    return ph;
+  }
+
+  void row_phase(int type, const Phase& src, int rows, int dim, const bf16* bias, const bf16* gain, bf16* res, bf16* out,
+                 float eps, int every = 1, int which = 0) {
+    Phase ph = blank(type, rows);
+    ph.N = dim;
+    ph.tiles = src.tiles;
+    ph.splits = src.splits;
+    ph.bn = src.bn;
+    ph.src0 = bias;
+    ph.src3 = gain;
+    ph.dst0 = res;
+    ph.dst1 = out;
+    ph.f0 = eps;
+    ph.i0 = every;
+    ph.i1 = which;
+    prog->phases.push_back(ph);
+  }
+
+  // One pass of a decoder stack over rows whose normalised input is already in s.x and residual in s.res:
+  // `Stack::forward` (crates/omni-qwen3/src/stack.rs:152-203) with the reduce of every split-K GEMM folded into its
+  // consumer and SiLU*up folded into the gate|up GEMM.
+  void stack_pass(const StackW& S, const Scratch& s, int rows, bool paged, int per, int base,
+                  const std::vector<bf16*>& kv, int kv_pages, bf16* keep_out, int every, int which) {
+    const omni_stack_config& c = S.cfg;
+    const int h = c.hidden, I = c.inter, qd = c.q_heads * c.head_dim;
+    for (int i = 0; i < c.layers; ++i) {
+      const StackW::Layer& L = S.layers[i];
+      const Phase qkv = gemm(L.qkv, S.qkv_width(), h, s.x, rows);
+      Phase at = blank(kPhRopeAttn, rows);
+      at.tiles = qkv.tiles, at.splits = qkv.splits, at.bn = qkv.bn;
+      at.i0 = c.q_heads, at.i1 = c.kv_heads, at.i2 = c.head_dim, at.i3 = per, at.i4 = base, at.i5 = paged, at.i6 = kv_pages;
+      at.src0 = L.q_norm, at.src1 = L.k_norm;
+      at.dst0 = kv[i], at.dst1 = s.attn;
+      at.f0 = c.rms_eps, at.f1 = c.rope_theta;
+      prog->phases.push_back(at);
+      const Phase o = gemm(L.o, h, qd, s.attn, rows);
+      row_phase(kPhAddNorm, o, rows, h, nullptr, L.ln2, s.res, s.x, c.rms_eps);
+      gemm(L.gate_up, 2 * I, h, s.x, rows, kGemmSwiglu, s.act, I);
+      const Phase down = gemm(L.down, h, I, s.act, rows);
+      if (i + 1 < c.layers)
+        row_phase(kPhAddNorm, down, rows, h, nullptr, S.layers[i + 1].ln1, s.res, s.x, c.rms_eps);
+      else
+        row_phase(kPhAddNorm, down, rows, h, nullptr, S.norm, s.res, keep_out, c.rms_eps, every, which);
+    }
+  }
+
+  void sample(const Phase& head, int group, int rows, bf16* logits_out, int ldl, int next, const bf16* table,
+              const bf16* hidden, bf16* p_in, int dim) {
+    const omni_talker_config& c = m->cfg;
+    Phase ph = blank(kPhSample, rows);
+    ph.tiles = head.tiles, ph.splits = head.splits, ph.bn = head.bn;
+    ph.dst0 = logits_out;
+    ph.i0 = ldl;
+    ph.f1 = c.top_p;
+    ph.i7 = group;
+    ph.i10 = c.sampler == OMNI_SAMPLER_PHILOX;
+    if (group == 0) {
+      ph.N = c.talker.vocab;
+      ph.f0 = c.temperature, ph.f2 = c.repetition_penalty;
+      ph.i1 = c.top_k, ph.i2 = c.talker.vocab - c.control_tokens, ph.i3 = c.talker.vocab;
+      ph.i4 = c.codec_eos_token_id, ph.i5 = c.min_frames, ph.i6 = 1;
+    } else {
+      ph.N = c.predictor.vocab;
+      ph.f0 = c.sub_temperature, ph.f2 = 1.f;
+      ph.i1 = c.sub_top_k, ph.i2 = 0, ph.i3 = 0, ph.i4 = -1, ph.i5 = 0, ph.i6 = 0;
+    }
+    ph.i8 = next;
+    ph.src0 = table;
+    ph.src1 = hidden;
+    ph.dst1 = p_in;
+    ph.i9 = dim;
+    prog->phases.push_back(ph);
+    offset = (offset + rows) % ctas;
+  }
+
+  // `Talker::advance` + `Talker::tail` (talker.rs:224-251, 293-356) at bucket b.
+  void build(int program, int b) {
+    const omni_talker_config& c = m->cfg;
+    const int h = c.talker.hidden, p = c.predictor.hidden, V = c.talker.vocab, PV = c.predictor.vocab;
+    if (program == kDecode) {
+      Phase e = blank(kPhEmbedNorm, b);
+      e.N = h;
+      e.src0 = m->pad_embed, e.src1 = m->codec_emb, e.src2 = m->p_emb, e.src3 = m->talker.layers[0].ln1;
+      e.dst0 = m->T.res, e.dst1 = m->T.x;
+      e.i0 = V, e.i1 = PV, e.i2 = c.groups;
+      e.f0 = c.talker.rms_eps;
+      prog->phases.push_back(e);
+      stack_pass(m->talker, m->T, b, true, 1, 0, m->kv, m->pages_total, m->hidden, 1, 0);
+    }
+    const Phase head = gemm(m->codec_head, V, h, m->hidden, b);
+    sample(head, 0, b, m->logits, V, kNextHiddenAndCode, m->codec_emb, m->hidden, m->p_in, h);
+    for (int g = 1; g < c.groups; ++g) {
+      const int per = g == 1 ? 2 : 1, rows = b * per;
+      const Phase mtp = gemm(m->mtp_w, p, h, m->p_in, rows);
+      row_phase(kPhReduceNorm, mtp, rows, p, m->mtp_b, m->pred.layers[0].ln1, m->P.res, m->P.x, c.predictor.rms_eps);
+      stack_pass(m->pred, m->P, rows, false, per, g == 1 ? 0 : g, m->pkv, m->max_seqs, m->p_last, per, per - 1);
+      const Phase ph = gemm(m->lm_heads + (size_t)(g - 1) * PV * p, PV, p, m->p_last, b);
+      const bool more = g + 1 < c.groups;
+      sample(ph, g, b, m->p_logits + (size_t)(g - 1) * m->max_seqs * PV, PV, more ? kNextCode : kNextNone,
+             more ? m->p_emb + (size_t)(g - 1) * PV * h : nullptr, nullptr, m->p_in, h);
+    }
+  }
+};
+
+bool tick_usable(const omni_talker* m, int b) {
+  if (!m->tick_ok) return false;
+  const omni_stack_config &t = m->cfg.talker, &p = m->cfg.predictor;
+  auto ok = [&](const omni_stack_config& s) {
+    return tick_supports(s.hidden, s.head_dim, s.q_heads, s.kv_heads, 2 * b) && s.inter % 64 == 0 && s.hidden % 64 == 0 &&
+           (s.q_heads * s.head_dim) % 64 == 0;
+  };
+  return ok(t) && ok(p);
+}
+
+int run_tick_program(omni_talker* m, int program, int b) {
+  auto key = std::make_pair(program, b);
+  auto it = m->tick_programs.find(key);
+  if (it == m->tick_programs.end()) {
+    TickProgram prog;
+    TickBuilder builder{m, &prog, m->tick_ctas};
+    builder.build(program, b);
+    if (builder.failed) return m->fail(OMNI_ERR_CUDA, "tensor-map encode failed while compiling the tick program");
+    if (prog.partial_floats > m->gemm_scratch.partial_floats)
+      return m->fail(OMNI_ERR_UNSUPPORTED, "split-K scratch too small for the tick program");
+    if (tick_upload(&prog) != 0) return m->fail(OMNI_ERR_CUDA, "uploading the tick program failed");
+    it = m->tick_programs.emplace(key, prog).first;
+  }
+  TickIo io;
+  io.lines = m->din<int32_t>(m->in.lines);
+  io.frames = m->din<int32_t>(m->in.pos);
+  io.uniforms = m->din<float>(m->in.uniforms);
+  io.force = m->din<int32_t>(m->in.force);
+  io.d_pos = m->din<int32_t>(m->in.d_pos);
+  io.d_slot = m->din<int32_t>(m->in.d_slot);
+  io.indptr = m->din<int32_t>(m->in.indptr);
+  io.pages = m->din<int32_t>(m->in.pages);
+  io.state = m->seq_state;
+  io.stride = m->seq_stride;
+  io.codes = m->codes;
+  io.seen_words = m->seen_words;
+  m->tick_phases = (int)it->second.phases.size();
+  // OMNI_TICK_TRACE=<file>: per-phase device timestamps of the last tick are written there (a profiling aid)
+  if (m->trace_path.empty() && !m->trace_checked) {
+    m->trace_checked = true;
+    if (const char* path = getenv("OMNI_TICK_TRACE")) m->trace_path = path;
+  }
+  if (!m->trace_path.empty() && !m->trace) TRY(dev_alloc(m, &m->trace, 8192, true));
+  if (m->trace && m->tick_phases <= 8192) m->trace_program = &it->second;
+  LAUNCH(m, tick_launch(it->second, io, m->gemm_scratch.partials, m->tick_barrier, m->err, m->tick_ctas, m->stream,
+                        m->trace && m->tick_phases <= 8192 ? m->trace : nullptr));
+  return OMNI_OK;
+}
+
+// Runs a graph program at bucket b: the persistent tick kernel when the shapes allow it, else the per-op kernels
+// as a replay of their captured graph (or eager launches).
 int run_program(omni_talker* m, int program, int b) {
   m->launches = 0;
+  if (m->cfg.tick_kernel && tick_usable(m, b)) return run_tick_program(m, program, b);
   if (!m->cfg.use_graphs) return enqueue_program(m, program, b);
   auto key = std::make_pair(program, b);
   auto it = m->graphs.find(key);
@@ -508,6 +753,24 @@ size_t stage_graph_inputs(omni_talker* m, char* host, const std::vector<FrameRow
   return in.pages + (size_t)np * 4;
 }
 
+
+// Writes "index type N K tiles splits bn rows ns" for every phase of the last traced tick.
+void dump_trace(omni_talker* m) {
+  if (!m->trace || !m->trace_program || m->trace_path.empty()) return;
+  const TickProgram& prog = *m->trace_program;
+  std::vector<unsigned long long> t(prog.phases.size());
+  if (cudaMemcpy(t.data(), m->trace, t.size() * 8, cudaMemcpyDeviceToHost) != cudaSuccess) return;
+  FILE* f = fopen(m->trace_path.c_str(), "w");
+  if (!f) return;
+  fprintf(f, "phase type N K tiles splits bn rows ns_since_previous\n");
+  for (size_t i = 0; i < t.size(); ++i) {
+    const Phase& ph = prog.phases[i];
+    fprintf(f, "%zu %d %d %d %d %d %d %d %lld\n", i, ph.type, ph.N, ph.K, ph.tiles, ph.splits, ph.bn, ph.rows,
+            i == 0 ? 0ll : (long long)(t[i] - t[i - 1]));
+  }
+  fclose(f);
+}
+
 int finish_call(omni_talker* m, int n, int32_t* codes, float* wav) {
   CUDA_TRY(m, cudaMemcpyAsync(m->out_host, m->codes, ((size_t)m->max_seqs * OMNI_GROUPS + 1) * 4,
                               cudaMemcpyDeviceToHost, m->stream));
@@ -542,6 +805,7 @@ void omni_talker_destroy(omni_talker* m) {
   cudaSetDevice(m->device);
   if (m->stream) cudaStreamSynchronize(m->stream);
   for (auto& g : m->graphs) cudaGraphExecDestroy(g.second);
+  for (auto& t : m->tick_programs) tick_free(&t.second);
   for (void* p : m->allocations) cudaFree(p);
   if (m->in_host) cudaFreeHost(m->in_host);
   if (m->out_host) cudaFreeHost(m->out_host);
@@ -558,7 +822,7 @@ static int create_impl(omni_talker* m, const omni_tensor* tensors, int32_t n_ten
   if (t.vocab > 4096 || pc.vocab > 4096) return m->fail(OMNI_ERR_UNSUPPORTED, "the sampler takes vocabularies up to 4096");
   for (const omni_stack_config* s : {&t, &pc}) {
     if (s->head_dim != 64 && s->head_dim != 128) return m->fail(OMNI_ERR_UNSUPPORTED, "head_dim %d", s->head_dim);
-    if (s->hidden % 8 || s->hidden > 8192 || s->inter % 8) return m->fail(OMNI_ERR_UNSUPPORTED, "hidden %d", s->hidden);
+    if (s->hidden % 8 || s->hidden > 8192 || s->inter % 16) return m->fail(OMNI_ERR_UNSUPPORTED, "hidden %d", s->hidden);
     const int g = s->kv_heads > 0 ? s->q_heads / s->kv_heads : 0;
     if (g * s->kv_heads != s->q_heads || !(g == 1 || g == 2 || g == 4 || g == 5 || g == 8))
       return m->fail(OMNI_ERR_UNSUPPORTED, "%d query heads over %d key heads", s->q_heads, s->kv_heads);
@@ -664,6 +928,12 @@ static int create_impl(omni_talker* m, const omni_tensor* tensors, int32_t n_ten
     m->gemm_scratch.counter_slots = 4096;
     TRY(dev_alloc(m, &m->gemm_scratch.partials, m->gemm_scratch.partial_floats));
     TRY(dev_alloc(m, &m->gemm_scratch.counters, (size_t)m->gemm_scratch.counter_slots, true));
+  }
+
+  if (c.tick_kernel) {
+    m->tick_ctas = tick_configure(m->device);
+    m->tick_ok = m->tick_ctas > 0;
+    TRY(dev_alloc(m, &m->tick_barrier, 64, true));
   }
 
   // the pad lease: one page, one slot (model.rs:130)
@@ -942,6 +1212,7 @@ int32_t omni_talker_run_ticks(omni_talker* m, int32_t n, omni_seq* const* seqs, 
     m->stats.last_call_gpu_ms = total;
     m->stats.last_call_launches = m->launches * ticks;
     m->stats.bucket = b;
+    dump_trace(m);
     return OMNI_OK;
   };
   rc = body();

@@ -35,7 +35,7 @@ class TalkerCfg(C.Structure):
                 ("sub_temperature", C.c_float), ("sub_top_k", C.c_int32), ("top_p", C.c_float),
                 ("sampler", C.c_int32), ("min_frames", C.c_int32), ("control_tokens", C.c_int32),
                 ("max_batch", C.c_int32), ("max_tokens", C.c_int32), ("kv_gib", C.c_double),
-                ("use_graphs", C.c_int32), ("gemm_path", C.c_int32)]
+                ("use_graphs", C.c_int32), ("gemm_path", C.c_int32), ("tick_kernel", C.c_int32)]
 
 
 class Draw(C.Structure):

@@ -77,13 +77,15 @@ def _stack_cfg(c) -> L.StackCfg:
                       c.num_key_value_heads, c.head_dim, c.vocab_size, c.rms_norm_eps, c.rope_theta)
 
 
-def c_config(cfg: TalkerConfig, limits: Limits, use_graphs: bool = True, gemm_path: int = 0) -> L.TalkerCfg:
+def c_config(cfg: TalkerConfig, limits: Limits, use_graphs: bool = True, gemm_path: int = 0,
+             tick_kernel: bool = True) -> L.TalkerCfg:
     g = cfg.generation
     return L.TalkerCfg(_stack_cfg(cfg.talker), _stack_cfg(cfg.predictor), cfg.num_code_groups,
                        cfg.tts_pad_token_id, cfg.codec_eos_token_id, g.temperature, g.top_k,
                        g.repetition_penalty, g.subtalker_temperature, g.subtalker_top_k, g.top_p,
                        1 if g.sampler == "philox" else 0, cfg.min_frames, cfg.control_tokens,
-                       limits.max_batch, limits.max_tokens, limits.kv_gib, int(use_graphs), gemm_path)
+                       limits.max_batch, limits.max_tokens, limits.kv_gib, int(use_graphs), gemm_path,
+                       int(tick_kernel))
 
 
 def c_tensors(checkpoint: dict):
@@ -123,9 +125,9 @@ class Model:
     # -- Model::load (model.rs:111-131) --
     @classmethod
     def load(cls, device: int, checkpoint: dict, config: TalkerConfig, limits: Limits = Limits(),
-             use_graphs: bool = True, gemm_path: int = 0) -> "Model":
+             use_graphs: bool = True, gemm_path: int = 0, tick_kernel: bool = True) -> "Model":
         lib = L.load()
-        cfg = c_config(config, limits, use_graphs, gemm_path)
+        cfg = c_config(config, limits, use_graphs, gemm_path, tick_kernel)
         tensors, keep = c_tensors(checkpoint)
         h = C.c_void_p()
         rc = lib.omni_talker_create(C.byref(cfg), tensors, len(checkpoint), device, C.byref(h))

@@ -42,10 +42,18 @@ def forced_frames(cfg, frames, n, seed=0):
     return f
 
 
-@pytest.mark.parametrize("preset,gemm_path", [("tiny128", 0), ("tiny64", 0), ("mid", 0), ("tiny128", 1)])
-def test_teacher_forced_logits_match_oracle(built_lib, oracle_lib, preset, gemm_path):
+ENGINES = {
+    "tick": dict(tick_kernel=True),                    # one persistent kernel per program
+    "ops": dict(tick_kernel=False),                    # one kernel per op, tensor-core GEMMs where rows allow
+    "ops-gemv": dict(tick_kernel=False, gemm_path=1),  # one kernel per op, vector GEMV everywhere
+}
+
+
+@pytest.mark.parametrize("preset,engine", [("tiny128", "tick"), ("tiny64", "tick"), ("mid", "tick"), ("tiny128", "ops"),
+                                           ("mid", "ops"), ("tiny128", "ops-gemv")])
+def test_teacher_forced_logits_match_oracle(built_lib, oracle_lib, preset, engine):
     from pega_omni_b200.model import Draw
-    cfg, ck, m = make(preset, gemm_path=gemm_path)
+    cfg, ck, m = make(preset, **ENGINES[engine])
     o = oracle_lib.CpuOracle(cfg, ck)
     lens, frames = [9, 33, 17], 6
     ps = prompts_for(cfg, lens)
@@ -202,7 +210,7 @@ def test_graph_replay_equals_eager(built_lib):
     from pega_omni_b200.model import Draw
     outs = []
     for graphs in (True, False):
-        cfg, ck, m = make("tiny128", use_graphs=graphs)
+        cfg, ck, m = make("tiny128", use_graphs=graphs, tick_kernel=False)
         ps = prompts_for(cfg, [8, 30], seed=6)
         rng = np.random.default_rng(6)
         seqs = [m.open(len(p), 10) for p in ps]
@@ -217,6 +225,33 @@ def test_graph_replay_equals_eager(built_lib):
         outs.append((np.stack(codes), np.stack(logits)))
         m.close()
     assert np.array_equal(outs[0][0], outs[1][0]) and np.array_equal(outs[0][1], outs[1][1])
+
+
+def test_tick_kernel_agrees_with_per_op_kernels(built_lib):
+    """The persistent kernel and the per-op kernels are two schedules of the same arithmetic (same rounding points,
+    different K splits): forced frames give logits within tolerance, and each path's own draws are reproducible."""
+    from pega_omni_b200.model import Draw
+    got = {}
+    for engine in ("tick", "ops"):
+        cfg, ck, m = make("mid", **ENGINES[engine])
+        ps = prompts_for(cfg, [14, 37, 22, 9, 30], seed=11)
+        forced = forced_frames(cfg, 5, len(ps), seed=11)
+        seqs = [m.open(len(p), 8) for p in ps]
+        logits = []
+        for t in range(5):
+            draws = [Draw([0.5] * 16, list(forced[t, s])) for s in range(len(ps))]
+            out = m.start(list(zip(seqs, ps, draws))) if t == 0 else m.step(list(zip(seqs, draws)))
+            assert (out.codes == forced[t]).all()
+            logits.append(np.stack([np.concatenate([m.talker_logits(s), m.predictor_logits(s).ravel()])
+                                    for s in range(len(ps))]))
+        assert m.stats().last_call_launches == (1 if engine == "tick" else m.stats().last_call_launches)
+        got[engine] = np.stack(logits)
+        m.close()
+    a, b = got["tick"], got["ops"]
+    assert np.abs(a - b).max() <= 2e-2, np.abs(a - b).max()
+    for t in range(a.shape[0]):
+        for s in range(a.shape[1]):
+            assert cosine(a[t, s], b[t, s]) >= 0.9999
 
 
 def test_run_ticks_equals_steps(built_lib):
