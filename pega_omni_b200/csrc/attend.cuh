@@ -1,4 +1,5 @@
-// Decode attention of one (row, kv head) by a team of four warps over the paged KV
+// Decode attention of one (row, kv head) by a team of W warps (four for long paged sequences, one for the code
+// predictor's single-page frames) over the paged KV
 //   kv[page][kv_head][K | V][16 tokens][D]   (bf16)
 // shared by the stand-alone attention kernel and the persistent tick kernel.
 // Value semantics of `attend` (crates/omni-qwen3/kernels/qwen3.cu:123-207): f32 scores and
@@ -16,26 +17,29 @@ __device__ __forceinline__ int64_t kv_offset(int64_t page, int hk, int head, int
   return (((page * hk + head) * 2 + which) * 16 + tok) * D;
 }
 
-template <int D, int G>
+template <int D, int G, int W = kAttnWarps>
 struct AttnShared {
   float qs[G][D];  // the G query heads sharing this kv head, f32, filled by the caller
-  float ms[kAttnWarps][G], ls[kAttnWarps][G];
-  float os[kAttnWarps][G][D];
+  float ms[W][G], ls[W][G];
+  float os[W][G][D];
 };
 
+struct WarpSync {  // team barrier of a one-warp team
+  __device__ __forceinline__ void sync() const { __syncwarp(); }
+};
+
+// tid: 0 .. 32*W-1 within the team.
 // `pages`: the sequence's page list, or nullptr when the sequence owns page `seq_page` alone (the code
 // predictor's per-frame KV). `len` keys. `out`: G heads of D, contiguous. tid: 0..127 within the team.
-// Warps take pages round-robin; within a page the two half-warps split the head dimension for q.k
-// (lane & 15 = key), then every lane owns D/32 output dims for p.v. The page's value slices are loaded
-// before the score math so their latency overlaps it. Ends with a team barrier (sh may be reused).
-template <int D, int G, typename TeamSync>
-__device__ __forceinline__ void attend_pages(AttnShared<D, G>& sh, const bf16* __restrict__ kv,
+// Warps take pages round-robin; q.k of a page is computed with the key rows spread over lanes and finished by
+// shuffles (lane & 15 then owns a key), then every lane owns D/32 output dims for p.v. Ends with a team barrier (sh may be reused).
+template <int D, int G, int W = kAttnWarps, typename TeamSync>
+__device__ __forceinline__ void attend_pages(AttnShared<D, G, W>& sh, const bf16* __restrict__ kv,
                                              const int32_t* __restrict__ pages, int seq_page, int len, int hk, int kh,
                                              float scale, bf16* __restrict__ out, int tid, const TeamSync& team) {
   constexpr int PV = D / 32;   // output dims per lane
-  constexpr int HALF = D / 2;  // q.k dims per half-warp
   const int lane = tid & 31, warp = tid >> 5;
-  const int key = lane & 15, half = lane >> 4;
+  const int key = lane & 15;
   float m[G], l[G], acc[G][PV];
 #pragma unroll
   for (int g = 0; g < G; ++g) {
@@ -45,11 +49,19 @@ __device__ __forceinline__ void attend_pages(AttnShared<D, G>& sh, const bf16* _
     for (int d = 0; d < PV; ++d) acc[g][d] = 0.f;
   }
   const int npages = (len + 15) >> 4;
-  for (int pi = warp; pi < npages; pi += kAttnWarps) {
+  for (int pi = warp; pi < npages; pi += W) {
     const int64_t page = pages ? pages[pi] : seq_page;
     const int ntok = min(16, len - pi * 16);
     const bf16* kpage = kv + kv_offset<D>(page, hk, kh, 0, 0);
     const bf16* vpage = kpage + 16 * D;
+    // Every load of the page is issued before any of it is used, and every load instruction covers contiguous
+    // memory: a (page, head) K block is 16 rows of D bf16 back to back, so instruction c takes bytes
+    // [512c, 512c + 512) with 16 bytes per lane. A key row is then spread over LPT = D/8 lanes; the dot product
+    // is finished with a shuffle reduction and handed to the lane that owns the key (lane & 15).
+    constexpr int LPT = D / 8, TPI = 32 / LPT, NI = 16 / TPI;
+    Pack8 kraw[NI];
+#pragma unroll
+    for (int c = 0; c < NI; ++c) kraw[c] = *reinterpret_cast<const Pack8*>(kpage + (c * 32 + lane) * 8);
     uint2 vraw[16];
 #pragma unroll
     for (int j = 0; j < 16; ++j) {
@@ -58,24 +70,37 @@ __device__ __forceinline__ void attend_pages(AttnShared<D, G>& sh, const bf16* _
       else
         vraw[j] = make_uint2(*reinterpret_cast<const uint32_t*>(vpage + j * D + lane * 2), 0u);
     }
+    const int sub = lane % LPT;  // which 8 dims of the head this lane multiplies
+    float q8[G][8];
+#pragma unroll
+    for (int g = 0; g < G; ++g)
+#pragma unroll
+      for (int e = 0; e < 8; ++e) q8[g][e] = sh.qs[g][sub * 8 + e];
     float sc[G];
 #pragma unroll
     for (int g = 0; g < G; ++g) sc[g] = 0.f;
-    const bf16* krow = kpage + key * D + half * HALF;
 #pragma unroll
-    for (int c = 0; c < HALF; c += 8) {
+    for (int c = 0; c < NI; ++c) {
       float kf[8];
-      ld8(krow + c, kf);
+      unpack8(kraw[c], kf);
 #pragma unroll
-      for (int g = 0; g < G; ++g)
+      for (int g = 0; g < G; ++g) {
+        float part = 0.f;
 #pragma unroll
-        for (int e = 0; e < 8; ++e) sc[g] = fmaf(sh.qs[g][half * HALF + c + e], kf[e], sc[g]);
+        for (int e = 0; e < 8; ++e) part = fmaf(q8[g][e], kf[e], part);
+#pragma unroll
+        for (int o = LPT / 2; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+#pragma unroll
+        for (int gi = 0; gi < TPI; ++gi) {  // token c*TPI + gi was summed by lane group gi
+          const float v = __shfl_sync(0xffffffffu, part, gi * LPT);
+          if (key == c * TPI + gi) sc[g] = v;
+        }
+      }
     }
     float p[G];
 #pragma unroll
     for (int g = 0; g < G; ++g) {
-      float s = sc[g] + __shfl_xor_sync(0xffffffffu, sc[g], 16);
-      s = key < ntok ? s * scale : -INFINITY;
+      const float s = key < ntok ? sc[g] * scale : -INFINITY;
       const float m2 = fmaxf(m[g], warp_fmax(s));
       const float corr = __expf(m[g] - m2);
       p[g] = __expf(s - m2);
@@ -117,14 +142,14 @@ __device__ __forceinline__ void attend_pages(AttnShared<D, G>& sh, const bf16* _
     for (int d = 0; d < PV; ++d) sh.os[warp][g][lane * PV + d] = acc[g][d];
   }
   team.sync();
-  for (int i = tid; i < G * D; i += kAttnWarps * 32) {
+  for (int i = tid; i < G * D; i += W * 32) {
     const int g = i / D, d = i % D;
     float top = -INFINITY;
 #pragma unroll
-    for (int w = 0; w < kAttnWarps; ++w) top = fmaxf(top, sh.ms[w][g]);
+    for (int w = 0; w < W; ++w) top = fmaxf(top, sh.ms[w][g]);
     float num = 0.f, den = 0.f;
 #pragma unroll
-    for (int w = 0; w < kAttnWarps; ++w) {
+    for (int w = 0; w < W; ++w) {
       const float e = __expf(sh.ms[w][g] - top);
       num += sh.os[w][g][d] * e;
       den += sh.ls[w][g] * e;

@@ -41,7 +41,7 @@ cudaError_t launch_norm_copy(const bf16* x, const bf16* w, bf16* out, bf16* res,
 // res = bf16(x + res); out[n / every] = bf16((x + res) * rsqrt(..) * w) for rows n % every == which.
 cudaError_t launch_add_norm(const bf16* x, bf16* res, const bf16* w, bf16* out, int rows, int dim, float eps,
                             int every, int which, cudaStream_t s);
-// act = bf16(bf16(silu(gate)) * up) over fused [gate | up] rows (interleaved: 16 gate, 16 up, 16 gate, ...).
+// act = bf16(bf16(silu(gate)) * up) over fused [gate | up] rows (interleaved = g > 0: g gate channels, g up, g gate, ...).
 cudaError_t launch_silu_mul(const bf16* gate_up, bf16* act, int rows, int inter, int interleaved, cudaStream_t s);
 // Per-head RMSNorm of q and k, rotary embedding, K and V into the row's slot; q in place.
 cudaError_t launch_rope_kv(bf16* qkv, const bf16* q_norm, const bf16* k_norm, bf16* kv, const RowMap& map, int rows,

@@ -55,16 +55,16 @@ __global__ void add_norm_kernel(const bf16* __restrict__ x, bf16* __restrict__ r
   st8(out + (int64_t)(n / every) * dim + threadIdx.x * 8, v);
 }
 
-// `silu_mul` (common.cuh:66-76). With `interleaved`, the fused row alternates 16 gate channels and the matching
-// 16 up channels (the weight layout the tensor-core SwiGLU epilogue wants) instead of [all gate | all up].
+// `silu_mul` (common.cuh:66-76). With `interleaved` = g > 0, the fused row alternates g gate channels and the matching
+// g up channels (the weight layout the tensor-core SwiGLU epilogue wants) instead of [all gate | all up].
 __global__ void silu_mul_kernel(const bf16* __restrict__ gate_up, bf16* __restrict__ act, int inter, int total,
                                 int interleaved) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= total) return;
   const int64_t n = i / (inter / 8), c = i % (inter / 8) * 8;
   float g[8], u[8];
-  const int64_t g_at = interleaved ? (c / 16) * 32 + c % 16 : c;
-  const int64_t u_at = interleaved ? g_at + 16 : inter + c;
+  const int64_t g_at = interleaved ? (c / interleaved) * 2 * interleaved + c % interleaved : c;
+  const int64_t u_at = interleaved ? g_at + interleaved : inter + c;
   ld8(gate_up + n * 2 * inter + g_at, g);
   ld8(gate_up + n * 2 * inter + u_at, u);
 #pragma unroll
@@ -88,7 +88,7 @@ cudaError_t launch_add_norm(const bf16* x, bf16* res, const bf16* w, bf16* out, 
 
 cudaError_t launch_silu_mul(const bf16* gate_up, bf16* act, int rows, int inter, int interleaved, cudaStream_t s) {
   const int total = rows * (inter / 8);
-  if (interleaved && inter % 16) return cudaErrorInvalidValue;
+  if (interleaved && (inter % interleaved || interleaved % 8)) return cudaErrorInvalidValue;
   silu_mul_kernel<<<(total + 255) / 256, 256, 0, s>>>(gate_up, act, inter, total, interleaved);
   return cudaGetLastError();
 }
@@ -199,7 +199,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attend_kernel(const bf16* __r
   const bf16* q = qkv + ((int64_t)n * (hq + 2 * hk) + kh * G) * D;
   for (int i = threadIdx.x; i < G * D; i += blockDim.x) sh.qs[i / D][i % D] = __bfloat162float(q[i]);
   __syncthreads();
-  attend_pages<D, G>(sh, kv, at.pages, at.seq, at.pos + 1, hk, kh, scale, out + ((int64_t)n * hq + kh * G) * D,
+  attend_pages<D, G, kAttnWarps>(sh, kv, at.pages, at.seq, at.pos + 1, hk, kh, scale, out + ((int64_t)n * hq + kh * G) * D,
                      threadIdx.x, sampler::CtaSync());
 }
 

@@ -40,16 +40,17 @@ __global__ void f32_to_bf16_kernel(const float* __restrict__ src, bf16* __restri
   if (i < n) dst[i] = __float2bfloat16(src[i]);
 }
 
-// dst = the fused [gate; up] rows of src regrouped as 16 gate rows, the matching 16 up rows, 16 gate rows, ...:
-// the layout that puts a gate channel and its up channel 16 TMEM lanes apart in one tensor-core tile.
-__global__ void interleave_gate_up_kernel(const bf16* __restrict__ src, bf16* __restrict__ dst, int inter, int k) {
+// dst = the fused [gate; up] rows of src regrouped as `granule` gate rows, the matching `granule` up rows, ...:
+// one tensor-core tile of 2 * granule weight rows then holds a channel's gate and up columns for the SwiGLU epilogue.
+__global__ void interleave_gate_up_kernel(const bf16* __restrict__ src, bf16* __restrict__ dst, int inter, int k,
+                                          int granule) {
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;  // one 16-byte piece
   const int64_t per_row = k / 8, total = (int64_t)2 * inter * per_row;
   if (i >= total) return;
   const int64_t row = i / per_row, piece = i % per_row;
   const bool up = row >= inter;
   const int64_t c = up ? row - inter : row;
-  const int64_t out_row = (c / 16) * 32 + (up ? 16 : 0) + c % 16;
+  const int64_t out_row = (c / granule) * 2 * granule + (up ? granule : 0) + c % granule;
   *reinterpret_cast<Pack8*>(dst + out_row * k + piece * 8) = *reinterpret_cast<const Pack8*>(src + row * k + piece * 8);
 }
 
@@ -68,6 +69,7 @@ struct StackW {
   };
   std::vector<Layer> layers;
   bf16* norm = nullptr;
+  int granule = 128;  // gate|up interleave (channels per group)
   int qkv_width() const { return (cfg.q_heads + 2 * cfg.kv_heads) * cfg.head_dim; }
   size_t kv_page_elems() const { return (size_t)cfg.kv_heads * 2 * OMNI_PAGE * cfg.head_dim; }
   AttnShape attn() const { return AttnShape{cfg.q_heads, cfg.kv_heads, cfg.head_dim, cfg.rms_eps, cfg.rope_theta}; }
@@ -76,6 +78,36 @@ struct StackW {
 struct Scratch {
   bf16 *x, *res, *qkv, *attn, *gate_up, *act;
 };
+
+// How the persistent kernel tiles one GEMM: weight rows per tile (the MMA N dimension) and K splits.
+// A cost model in microseconds, from measurements on B200: a tcgen05.mma takes ~142 cycles whatever its shape (so a
+// 64-wide K block costs ~0.3 us of issue time), one SM streams ~55 GB/s through a 4-stage TMA ring, a work item
+// pays ~1.5 us of pipeline fill, every consumer pays ~0.15 us per split when it sums partial tiles, and a separate
+// SiLU*up reduce phase costs ~5 us (one more grid barrier).
+struct Tiling {
+  int tile_n = 256, splits = 1;
+  bool swiglu_direct = false;
+  double cost = 1e30;
+};
+
+Tiling choose_tiling(int N, int K, int ctas, bool swiglu) {
+  Tiling best;
+  const int nkb = K / 64;
+  for (int direct = swiglu ? 1 : 0; direct >= 0; --direct) {
+    for (int tn : {256, 128, 64}) {
+      const int tiles = (N + tn - 1) / tn;
+      const int smax = direct ? 1 : std::min(8, nkb);
+      for (int S = 1; S <= smax; ++S) {
+        const int items = tiles * S, waves = (items + ctas - 1) / ctas, kb = (nkb + S - 1) / S;
+        const double per_kb = std::max(0.30, (tn * 128.0 + 8192.0) / 55000.0);
+        double cost = waves * (kb * per_kb + 1.5) + 0.15 * S;
+        if (swiglu && !direct) cost += 5.0;
+        if (cost < best.cost - 1e-9) best = Tiling{tn, S, direct != 0, cost};
+      }
+    }
+  }
+  return best;
+}
 
 }  // namespace
 }  // namespace omni
@@ -241,6 +273,9 @@ int upload(omni_talker* m, const TensorIndex& idx, const std::string& name, std:
 int load_stack(omni_talker* m, const TensorIndex& idx, const std::string& prefix, const omni_stack_config& c,
                StackW* out) {
   out->cfg = c;
+  // gate and up channels are interleaved in groups of half the tile the persistent kernel will use for this GEMM
+  out->granule = choose_tiling(2 * c.inter, c.hidden, std::max(1, m->tick_ctas > 0 ? m->tick_ctas : 148), true).tile_n / 2;
+  if (c.inter % out->granule) out->granule = 64;
   const int64_t h = c.hidden, d = c.head_dim, q = (int64_t)c.q_heads * d, kv = (int64_t)c.kv_heads * d, I = c.inter;
   out->layers.resize(c.layers);
   for (int i = 0; i < c.layers; ++i) {
@@ -263,13 +298,14 @@ int load_stack(omni_talker* m, const TensorIndex& idx, const std::string& prefix
     TRY(upload(m, idx, p + "self_attn.o_proj.weight", {h, q}, L.o));
     TRY(upload(m, idx, p + "post_attention_layernorm.weight", {h}, L.ln2));
     {
-      bf16* fused = nullptr;  // [gate; up] as in the checkpoint, then regrouped 16 by 16 (see interleave_gate_up_kernel)
+      bf16* fused = nullptr;  // [gate; up] as in the checkpoint, then regrouped (see interleave_gate_up_kernel)
       CUDA_TRY(m, cudaMalloc((void**)&fused, (size_t)2 * I * h * sizeof(bf16)));
       int rc = upload(m, idx, p + "mlp.gate_proj.weight", {I, h}, fused);
       if (rc == OMNI_OK) rc = upload(m, idx, p + "mlp.up_proj.weight", {I, h}, fused + I * h);
       if (rc == OMNI_OK) {
         const int64_t pieces = 2 * I * (h / 8);
-        interleave_gate_up_kernel<<<(unsigned)((pieces + 255) / 256), 256, 0, m->stream>>>(fused, L.gate_up, (int)I, (int)h);
+        interleave_gate_up_kernel<<<(unsigned)((pieces + 255) / 256), 256, 0, m->stream>>>(fused, L.gate_up, (int)I, (int)h,
+                                                                                     out->granule);
         if (cudaStreamSynchronize(m->stream) != cudaSuccess) rc = m->fail(OMNI_ERR_CUDA, "gate|up regroup failed");
       }
       cudaFree(fused);
@@ -340,7 +376,7 @@ int stack_forward(omni_talker* m, const StackW& S, const Scratch& s, const bf16*
     TRY(gemm(m, L.o, h, qd, s.attn, rows, s.x, h));
     LAUNCH(m, launch_add_norm(s.x, s.res, L.ln2, s.x, rows, h, c.rms_eps, 1, 0, m->stream));
     TRY(gemm(m, L.gate_up, 2 * I, h, s.x, rows, s.gate_up, 2 * I));
-    LAUNCH(m, launch_silu_mul(s.gate_up, s.act, rows, I, 1, m->stream));
+    LAUNCH(m, launch_silu_mul(s.gate_up, s.act, rows, I, S.granule, m->stream));
     TRY(gemm(m, L.down, h, I, s.act, rows, s.x, h));
     if (i + 1 < c.layers)
       LAUNCH(m, launch_add_norm(s.x, s.res, S.layers[i + 1].ln1, s.x, rows, h, c.rms_eps, 1, 0, m->stream));
@@ -437,7 +473,7 @@ int enqueue_program(omni_talker* m, int program, int b) {
 
 // ---- the persistent tick kernel's phase list ------------------------------------------------------------------
 
-int pick_bn(int rows) { return rows <= 16 ? 16 : rows <= 32 ? 32 : rows <= 64 ? 64 : rows <= 128 ? 128 : 256; }
+int pick_bn(int rows) { return rows <= 16 ? 16 : rows <= 32 ? 32 : rows <= 64 ? 64 : 128; }
 
 struct TickBuilder {
   omni_talker* m;
@@ -466,27 +502,39 @@ struct TickBuilder {
     return ph;
   }
 
-  // y = x . w^T as f32 partial tiles (or SwiGLU activations); returns {tiles, splits, bn} for the consumer.
-  Phase gemm(const bf16* w, int N, int K, const bf16* x, int rows, int mode = kGemmPartials, bf16* act = nullptr,
-             int inter = 0) {
+  // y = x . w^T as f32 partial tiles (or, for gate|up, SwiGLU activations straight from the epilogue when the
+  // cost model prefers no K split); returns the phase so the consumer knows tiles / splits / bn / tile_n.
+  Phase gemm(const bf16* w, int N, int K, const bf16* x, int rows, bool swiglu = false, bf16* act = nullptr,
+             int inter = 0, int granule = 0) {
     Phase ph = blank(kPhGemm, rows);
+    Tiling t = choose_tiling(N, K, ctas, swiglu);
+    if (swiglu && t.tile_n != 2 * granule) {  // the weights were regrouped for another tile width: keep that one
+      t.tile_n = 2 * granule;
+      if (t.swiglu_direct) t.splits = 1;
+    }
     ph.N = N;
     ph.K = K;
     ph.bn = pick_bn(rows);
-    ph.tiles = (N + 127) / 128;
-    const int nkb = K / 64;
-    int splits = mode == kGemmSwiglu ? 1 : std::max(1, std::min(ctas / ph.tiles, nkb / 4));
-    ph.splits = splits;
-    ph.mode = mode;
-    ph.wmap = map_of(w, N, K, 128);
+    ph.tile_n = t.tile_n;
+    ph.tiles = (N + t.tile_n - 1) / t.tile_n;
+    ph.splits = t.splits;
+    ph.mode = swiglu && t.swiglu_direct ? kGemmSwiglu : kGemmPartials;
+    ph.wmap = map_of(w, N, K, t.tile_n);
     ph.xmap = map_of(x, rows, K, ph.bn);
     ph.dst0 = act;
     ph.i0 = inter;
     prog->phases.push_back(ph);
     prog->max_bn = std::max(prog->max_bn, ph.bn);
-    if (mode == kGemmPartials)
-      prog->partial_floats = std::max(prog->partial_floats, (size_t)splits * ph.tiles * ph.bn * 128);
-    offset = (offset + ph.tiles * splits) % ctas;
+    if (ph.mode == kGemmPartials)
+      prog->partial_floats = std::max(prog->partial_floats, (size_t)ph.splits * ph.tiles * ph.bn * ph.tile_n);
+    offset = (offset + ph.tiles * ph.splits) % ctas;
+    if (swiglu && ph.mode == kGemmPartials) {  // SiLU*up over the summed partial tiles
+      Phase rs = blank(kPhReduceSilu, rows);
+      rs.tiles = ph.tiles, rs.splits = ph.splits, rs.bn = ph.bn, rs.tile_n = ph.tile_n;
+      rs.dst0 = act;
+      rs.i0 = inter;
+      prog->phases.push_back(rs);
+    }
     return ph;
   }
 
@@ -497,6 +545,7 @@ struct TickBuilder {
     ph.tiles = src.tiles;
     ph.splits = src.splits;
     ph.bn = src.bn;
+    ph.tile_n = src.tile_n;
     ph.src0 = bias;
     ph.src3 = gain;
     ph.dst0 = res;
@@ -518,7 +567,7 @@ struct TickBuilder {
       const StackW::Layer& L = S.layers[i];
       const Phase qkv = gemm(L.qkv, S.qkv_width(), h, s.x, rows);
       Phase at = blank(kPhRopeAttn, rows);
-      at.tiles = qkv.tiles, at.splits = qkv.splits, at.bn = qkv.bn;
+      at.tiles = qkv.tiles, at.splits = qkv.splits, at.bn = qkv.bn, at.tile_n = qkv.tile_n;
       at.i0 = c.q_heads, at.i1 = c.kv_heads, at.i2 = c.head_dim, at.i3 = per, at.i4 = base, at.i5 = paged, at.i6 = kv_pages;
       at.src0 = L.q_norm, at.src1 = L.k_norm;
       at.dst0 = kv[i], at.dst1 = s.attn;
@@ -526,7 +575,7 @@ struct TickBuilder {
       prog->phases.push_back(at);
       const Phase o = gemm(L.o, h, qd, s.attn, rows);
       row_phase(kPhAddNorm, o, rows, h, nullptr, L.ln2, s.res, s.x, c.rms_eps);
-      gemm(L.gate_up, 2 * I, h, s.x, rows, kGemmSwiglu, s.act, I);
+      gemm(L.gate_up, 2 * I, h, s.x, rows, true, s.act, I, S.granule);
       const Phase down = gemm(L.down, h, I, s.act, rows);
       if (i + 1 < c.layers)
         row_phase(kPhAddNorm, down, rows, h, nullptr, S.layers[i + 1].ln1, s.res, s.x, c.rms_eps);
@@ -539,7 +588,7 @@ struct TickBuilder {
               const bf16* hidden, bf16* p_in, int dim) {
     const omni_talker_config& c = m->cfg;
     Phase ph = blank(kPhSample, rows);
-    ph.tiles = head.tiles, ph.splits = head.splits, ph.bn = head.bn;
+    ph.tiles = head.tiles, ph.splits = head.splits, ph.bn = head.bn, ph.tile_n = head.tile_n;
     ph.dst0 = logits_out;
     ph.i0 = ldl;
     ph.f1 = c.top_p;
@@ -635,7 +684,7 @@ int run_tick_program(omni_talker* m, int program, int b) {
     m->trace_checked = true;
     if (const char* path = getenv("OMNI_TICK_TRACE")) m->trace_path = path;
   }
-  if (!m->trace_path.empty() && !m->trace) TRY(dev_alloc(m, &m->trace, 8192, true));
+  if (!m->trace_path.empty() && !m->trace) TRY(dev_alloc(m, &m->trace, 2 * 8192, true));
   if (m->trace && m->tick_phases <= 8192) m->trace_program = &it->second;
   LAUNCH(m, tick_launch(it->second, io, m->gemm_scratch.partials, m->tick_barrier, m->err, m->tick_ctas, m->stream,
                         m->trace && m->tick_phases <= 8192 ? m->trace : nullptr));
@@ -758,15 +807,15 @@ size_t stage_graph_inputs(omni_talker* m, char* host, const std::vector<FrameRow
 void dump_trace(omni_talker* m) {
   if (!m->trace || !m->trace_program || m->trace_path.empty()) return;
   const TickProgram& prog = *m->trace_program;
-  std::vector<unsigned long long> t(prog.phases.size());
+  std::vector<unsigned long long> t(2 * prog.phases.size());
   if (cudaMemcpy(t.data(), m->trace, t.size() * 8, cudaMemcpyDeviceToHost) != cudaSuccess) return;
   FILE* f = fopen(m->trace_path.c_str(), "w");
   if (!f) return;
-  fprintf(f, "phase type N K tiles splits bn rows ns_since_previous\n");
-  for (size_t i = 0; i < t.size(); ++i) {
+  fprintf(f, "phase type N K tiles splits bn rows ns_since_previous ns_cta0_work\n");
+  for (size_t i = 0; i < prog.phases.size(); ++i) {
     const Phase& ph = prog.phases[i];
-    fprintf(f, "%zu %d %d %d %d %d %d %d %lld\n", i, ph.type, ph.N, ph.K, ph.tiles, ph.splits, ph.bn, ph.rows,
-            i == 0 ? 0ll : (long long)(t[i] - t[i - 1]));
+    fprintf(f, "%zu %d %d %d %d %d %d %d %lld %lld\n", i, ph.type, ph.N, ph.K, ph.tiles, ph.splits, ph.bn, ph.rows,
+            i == 0 ? 0ll : (long long)(t[2 * i + 1] - t[2 * i - 1]), i == 0 ? 0ll : (long long)(t[2 * i] - t[2 * i - 1]));
   }
   fclose(f);
 }
@@ -822,7 +871,7 @@ static int create_impl(omni_talker* m, const omni_tensor* tensors, int32_t n_ten
   if (t.vocab > 4096 || pc.vocab > 4096) return m->fail(OMNI_ERR_UNSUPPORTED, "the sampler takes vocabularies up to 4096");
   for (const omni_stack_config* s : {&t, &pc}) {
     if (s->head_dim != 64 && s->head_dim != 128) return m->fail(OMNI_ERR_UNSUPPORTED, "head_dim %d", s->head_dim);
-    if (s->hidden % 8 || s->hidden > 8192 || s->inter % 16) return m->fail(OMNI_ERR_UNSUPPORTED, "hidden %d", s->hidden);
+    if (s->hidden % 8 || s->hidden > 8192 || s->inter % 64) return m->fail(OMNI_ERR_UNSUPPORTED, "hidden %d / intermediate %d", s->hidden, s->inter);
     const int g = s->kv_heads > 0 ? s->q_heads / s->kv_heads : 0;
     if (g * s->kv_heads != s->q_heads || !(g == 1 || g == 2 || g == 4 || g == 5 || g == 8))
       return m->fail(OMNI_ERR_UNSUPPORTED, "%d query heads over %d key heads", s->q_heads, s->kv_heads);
@@ -841,6 +890,12 @@ static int create_impl(omni_talker* m, const omni_tensor* tensors, int32_t n_ten
   CUDA_TRY(m, cudaEventCreate(&m->ev1));
   if (tc_init() != 0) return m->fail(OMNI_ERR_CUDA, "cuTensorMapEncodeTiled entry point not found");
   tc_configure();
+
+  if (c.tick_kernel) {
+    m->tick_ctas = tick_configure(m->device);
+    m->tick_ok = m->tick_ctas > 0;
+    TRY(dev_alloc(m, &m->tick_barrier, 64, true));
+  }
 
   TensorIndex idx;
   for (int i = 0; i < n_tensors; ++i) idx.by_name[tensors[i].name] = &tensors[i];
@@ -928,12 +983,6 @@ static int create_impl(omni_talker* m, const omni_tensor* tensors, int32_t n_ten
     m->gemm_scratch.counter_slots = 4096;
     TRY(dev_alloc(m, &m->gemm_scratch.partials, m->gemm_scratch.partial_floats));
     TRY(dev_alloc(m, &m->gemm_scratch.counters, (size_t)m->gemm_scratch.counter_slots, true));
-  }
-
-  if (c.tick_kernel) {
-    m->tick_ctas = tick_configure(m->device);
-    m->tick_ok = m->tick_ctas > 0;
-    TRY(dev_alloc(m, &m->tick_barrier, 64, true));
   }
 
   // the pad lease: one page, one slot (model.rs:130)

@@ -22,6 +22,7 @@ enum PhaseType : int32_t {
   kPhAddNorm = 3,     // reduce partials, residual add, RMSNorm (strided keep on the last layer)
   kPhRopeAttn = 4,    // reduce qkv partials, q/k norm + RoPE, KV write, attention
   kPhSample = 5,      // reduce logits partials, draw, next predictor input
+  kPhReduceSilu = 6,  // reduce gate|up partials -> SwiGLU activations (when the gate|up GEMM is split along K)
 };
 
 enum GemmMode : int32_t { kGemmPartials = 0, kGemmSwiglu = 1 };
@@ -35,10 +36,11 @@ enum NextInput : int32_t { kNextNone = 0, kNextHiddenAndCode = 1, kNextCode = 2 
 //  AddNorm:    rows, dim = N, tiles, splits, bn; src3 gain; dst0 res, dst1 out; i0 every, i1 which; f0 eps
 //  RopeAttn:   rows, tiles, splits, bn; i0 hq, i1 hk, i2 head_dim, i3 per, i4 base, i5 paged, i6 kv_pages;
 //              src0 q_norm, src1 k_norm; dst0 kv layer, dst1 attn out; f0 eps, f1 theta
+//  ReduceSilu: rows, tiles, splits, bn; dst0 act; i0 inter
 //  Sample:     rows, tiles, splits, bn, N = vocab; dst0 logits out, i0 ldl (row stride of logits out, elements);
 //              sampling constants in f0..f3 / i1..i7; next-input in i8, src0 table, src1 hidden, dst1 p_in, i9 dim
 struct alignas(16) Phase {
-  int32_t type, rows, bn, N, K, tiles, splits, wmap, xmap, mode, cta_offset, pad0;
+  int32_t type, rows, bn, N, K, tiles, splits, wmap, xmap, mode, cta_offset, tile_n;  // tile_n: weight rows per GEMM tile (64, 128 or 256)
   int32_t i0, i1, i2, i3, i4, i5, i6, i7, i8, i9, i10, i11;
   float f0, f1, f2, f3;
   const void *src0, *src1, *src2, *src3;
@@ -81,7 +83,8 @@ void tick_free(TickProgram* prog);
 // Raises the kernel's shared-memory limit and reports how many CTAs can be co-resident (0 on failure).
 int tick_configure(int device);
 // One cooperative launch of the whole program. `barrier` (one zeroed u32) is reset on the stream first.
-// `trace` (optional, one u64 per phase): CTA 0 records the global timer after each phase's barrier.
+// `trace` (optional, two u64 per phase): CTA 0 records the global timer when its own share of the phase is done
+// and again when the phase's grid barrier has completed.
 cudaError_t tick_launch(const TickProgram& prog, const TickIo& io, float* partials, uint32_t* barrier, uint32_t* err,
                         int ctas, cudaStream_t stream, unsigned long long* trace = nullptr);
 

@@ -1,15 +1,22 @@
-// The persistent tick kernel (see tick.h): 12 warps per CTA, one CTA per SM, cooperative launch.
+// The persistent tick kernel (see tick.h): 11 warps per CTA, one CTA per SM, cooperative launch.
 //   warp 0 / lane 0   weight producer: TMA loads of W tiles, runs ahead of the grid barriers
 //   warp 1 / lane 0   activation producer: TMA loads of X tiles, gated by the barrier before its phase
 //   warp 2 / lane 0   issues tcgen05.mma into one of two TMEM accumulators; whole warp owns the TMEM allocation
-//   warp 3            idle
-//   warps 4..11       workers: GEMM epilogues (TMEM -> partial tiles / SwiGLU) and every non-GEMM phase
+//   warps 3..10       workers: GEMM epilogues (TMEM -> partial tiles / SwiGLU) and every non-GEMM phase
+//
+// GEMM orientation. A tcgen05.mma occupies the tensor pipe for a fixed ~140 cycles whatever its M and N
+// (measured on B200), so each instruction must carry as many weight bytes as possible: the activation
+// rows (sessions, at most 128) sit on the MMA M dimension and 256 weight rows on N, 16 of K per
+// instruction. D[session, weight row] lands with one session per TMEM lane, so a worker thread owns
+// one output row and its 256 columns are contiguous in memory.
+//
 // Every wait (mbarrier, grid barrier, phase release) is bounded; on a timeout the device error word is
 // raised, every CTA sees it within its next wait and the kernel unwinds.
 #include "tick.h"
 
 #include <algorithm>
 #include <cstdio>
+#include <cstdlib>
 
 #include "attend.cuh"
 #include "gemm.h"
@@ -19,13 +26,15 @@
 namespace omni {
 namespace {
 
-constexpr int kThreads = 384;
+constexpr int kThreads = 352;  // 3 control warps + 8 worker warps: 186 registers per thread
 constexpr int kWorkerThreads = 256;
-constexpr int kFirstWorkerWarp = 4;
+constexpr int kFirstWorkerWarp = 3;
 constexpr int kMaxStages = 8;
-constexpr int kTileW = 128, kTileK = 64;
-constexpr int kWBytes = kTileW * kTileK * 2;
-constexpr int kMaxPerThread = 32;  // row-wise phases: hidden <= 32 * 128
+constexpr int kTileN = 256;  // weight rows per tile (the MMA N dimension)
+constexpr int kTileK = 64;   // K elements per stage: one 128-byte swizzle row
+constexpr int kTileM = 128;  // the MMA M dimension: activation rows, zero/garbage padded
+constexpr int kWBytes = kTileN * kTileK * 2;
+constexpr int kGroupThreads = 128;
 
 struct GroupBar {  // named barrier of one 128-thread worker group
   int id;
@@ -43,7 +52,8 @@ struct alignas(16) Control {
 };
 
 union WorkerScratch {
-  AttnShared<128, 4> attn[2];
+  AttnShared<128, 4, 4> attn4[2];  // one per 128-thread group
+  AttnShared<128, 4, 1> attn1[8];  // one per worker warp
   sampler::Shared sample;
 };
 
@@ -54,10 +64,9 @@ struct KernelArgs {
   float* partials;
   uint32_t* barrier;
   uint32_t* err;
-  int n_stages, stage_bytes, acc_stride;  // acc_stride: TMEM columns per accumulator
-  int n_acc;                              // independent accumulators per buffer (K steps rotate over them)
-  int tmem_cols;
-  unsigned long long* trace;  // optional: CTA 0 stamps the global timer after every phase's barrier
+  int n_stages, stage_bytes, x_bytes;  // a stage is [X tile, x_bytes][W tile, kWBytes]
+  int w_ahead;                         // phases the weight producer may run ahead of the grid barriers
+  unsigned long long* trace;           // optional: CTA 0 stamps the global timer after every phase's barrier
   TickIo io;
 };
 
@@ -92,43 +101,110 @@ __device__ bool grid_barrier(uint32_t* counter, uint32_t target, uint32_t* err) 
   }
 }
 
-// Sums of K-split partials are taken in split order, starting from zero, exactly as the per-op GEMM's last CTA does.
-// N columns of one row at once: the split loop is outermost so the N loads of a split are
-// independent and in flight together (one L2 round trip per split instead of one per element).
+// Split-K partial tiles: [split][tile][row (bn)][tile_n columns] f32, tile_n = 64, 128 or 256. Sums are taken in
+// split order starting from zero, so the result does not depend on which CTA computed which split.
+struct Partials {
+  const float* base;
+  int splits, tiles, bn, shift;  // shift = log2(tile_n)
+  size_t split_stride;
+  __device__ __forceinline__ Partials(const float* p, const Phase& ph)
+      : base(p), splits(ph.splits), tiles(ph.tiles), bn(ph.bn), shift(ph.tile_n == 256 ? 8 : ph.tile_n == 128 ? 7 : 6),
+        split_stride((size_t)ph.tiles * ph.bn * ph.tile_n) {}
+  __device__ __forceinline__ uint32_t at(int m, int n) const {  // element offset inside split 0
+    return (uint32_t)((((size_t)(n >> shift) * bn + m) << shift) + (n & ((1 << shift) - 1)));
+  }
+};
+
+// N columns of one row at once: the split loop is outermost and unrolled so the loads of several splits are
+// independent and in flight together (one L2 round trip per batch instead of one per element).
 template <int N>
-__device__ __forceinline__ void reduce_partial_n(const float* __restrict__ partials, int splits, int tiles, int bn,
-                                                 int m, const int (&cols)[N], float (&acc)[N]) {
-  const float* p[N];
+__device__ __forceinline__ void reduce_cols(const Partials& pt, int m, const int (&cols)[N], float (&acc)[N]) {
+  uint32_t off[N];
 #pragma unroll
   for (int j = 0; j < N; ++j) {
-    p[j] = partials + ((size_t)(cols[j] >> 7) * bn + m) * kTileW + (cols[j] & 127);
+    off[j] = pt.at(m, cols[j]);
     acc[j] = 0.f;
   }
-  const size_t stride = (size_t)tiles * bn * kTileW;
-  for (int s = 0; s < splits; ++s) {
-    float f[N];
+  const float* base = pt.base;
+  constexpr int kBatch = N <= 4 ? 8 : N <= 8 ? 4 : 2;  // splits whose loads are issued before any is consumed
+  for (int s0 = 0; s0 < pt.splits; s0 += kBatch, base += kBatch * pt.split_stride) {
+    float f[kBatch][N];
 #pragma unroll
-    for (int j = 0; j < N; ++j) f[j] = __ldcg(p[j] + s * stride);
+    for (int b = 0; b < kBatch; ++b)
 #pragma unroll
-    for (int j = 0; j < N; ++j) acc[j] += f[j];
+      for (int j = 0; j < N; ++j) f[b][j] = s0 + b < pt.splits ? __ldcg(base + b * pt.split_stride + off[j]) : 0.f;
+#pragma unroll
+    for (int b = 0; b < kBatch; ++b)  // adding 0 for a missing split leaves the sum unchanged
+#pragma unroll
+      for (int j = 0; j < N; ++j) acc[j] += f[b][j];
   }
 }
 
-// Row r, columns t*128 + gtid for t < nt (nt <= kMaxPerThread): the row-wise phases' access pattern.
-__device__ __forceinline__ void reduce_row(const float* __restrict__ partials, int splits, int tiles, int bn, int m,
-                                           int gtid, int nt, float (&acc)[kMaxPerThread]) {
-  const float* p = partials + (size_t)m * kTileW + gtid;
-  const size_t tile_stride = (size_t)bn * kTileW, stride = (size_t)tiles * bn * kTileW;
+// The row-wise phases' access pattern: a 128-thread group owns a row; thread j owns, for t < NV, the VEC
+// consecutive columns starting at (t * 128 + j) * VEC. VEC = 4 reads the partial tiles 16 bytes at a time.
+template <int NV, int VEC>
+__device__ __forceinline__ int row_col(int t, int gtid) { return (t * kGroupThreads + gtid) * VEC; }
+
+template <int NV, int VEC>
+__device__ __forceinline__ void reduce_row(const Partials& pt, int m, int gtid, float (&acc)[NV * VEC]) {
+  uint32_t off[NV];
 #pragma unroll
-  for (int t = 0; t < kMaxPerThread; ++t) acc[t] = 0.f;
-  for (int s = 0; s < splits; ++s) {
-    float f[kMaxPerThread];
+  for (int t = 0; t < NV; ++t) off[t] = pt.at(m, row_col<NV, VEC>(t, gtid));
 #pragma unroll
-    for (int t = 0; t < kMaxPerThread; ++t)
-      if (t < nt) f[t] = __ldcg(p + s * stride + t * tile_stride);
+  for (int i = 0; i < NV * VEC; ++i) acc[i] = 0.f;
+  const float* base = pt.base;
+  constexpr int kBatch = NV * VEC <= 8 ? 8 : 4;  // splits whose loads are issued before any is consumed
+  for (int s0 = 0; s0 < pt.splits; s0 += kBatch, base += kBatch * pt.split_stride) {
+    if constexpr (VEC == 4) {
+      float4 f[kBatch][NV];
 #pragma unroll
-    for (int t = 0; t < kMaxPerThread; ++t)
-      if (t < nt) acc[t] += f[t];
+      for (int b = 0; b < kBatch; ++b)
+#pragma unroll
+        for (int t = 0; t < NV; ++t)
+          f[b][t] = s0 + b < pt.splits ? __ldcg(reinterpret_cast<const float4*>(base + b * pt.split_stride + off[t]))
+                                       : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int b = 0; b < kBatch; ++b)
+#pragma unroll
+        for (int t = 0; t < NV; ++t) {
+          acc[4 * t] += f[b][t].x, acc[4 * t + 1] += f[b][t].y, acc[4 * t + 2] += f[b][t].z, acc[4 * t + 3] += f[b][t].w;
+        }
+    } else {
+      float f[kBatch][NV];
+#pragma unroll
+      for (int b = 0; b < kBatch; ++b)
+#pragma unroll
+        for (int t = 0; t < NV; ++t) f[b][t] = s0 + b < pt.splits ? __ldcg(base + b * pt.split_stride + off[t]) : 0.f;
+#pragma unroll
+      for (int b = 0; b < kBatch; ++b)
+#pragma unroll
+        for (int t = 0; t < NV; ++t) acc[t] += f[b][t];
+    }
+  }
+}
+
+// VEC consecutive bf16 at p, widened / narrowed.
+template <int VEC>
+__device__ __forceinline__ void ld_bf16(const bf16* p, float* v) {
+  if constexpr (VEC == 4) {
+    const uint2 u = *reinterpret_cast<const uint2*>(p);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.y));
+    v[0] = a.x, v[1] = a.y, v[2] = b.x, v[3] = b.y;
+  } else {
+    v[0] = __bfloat162float(*p);
+  }
+}
+
+template <int VEC>
+__device__ __forceinline__ void st_bf16(bf16* p, const float* v) {
+  if constexpr (VEC == 4) {
+    uint2 u;
+    *reinterpret_cast<__nv_bfloat162*>(&u.x) = __floats2bfloat162_rn(v[0], v[1]);
+    *reinterpret_cast<__nv_bfloat162*>(&u.y) = __floats2bfloat162_rn(v[2], v[3]);
+    *reinterpret_cast<uint2*>(p) = u;
+  } else {
+    *p = __float2bfloat16(v[0]);
   }
 }
 
@@ -141,125 +217,191 @@ __device__ __forceinline__ float group_sum(float v, int gtid, float* red, const 
   return s;
 }
 
-// ---- row-wise phases: one 128-thread group per row, thread j owns columns t*128 + j -------------------------
+struct Team {  // a 128-thread worker group
+  int group, n_groups, gtid;
+  float* red;
+  GroupBar bar;
+};
 
-__device__ void phase_embed_norm(const Phase& ph, const TickIo& io, int group, int n_groups, int gtid, float* red,
-                                 const GroupBar& bar, uint32_t* err) {
-  const int dim = ph.N, nt = dim / kTileW;
-  const bf16 *pad = (const bf16*)ph.src0, *codec_emb = (const bf16*)ph.src1, *p_emb = (const bf16*)ph.src2,
-             *gain = (const bf16*)ph.src3;
-  bf16 *res = (bf16*)ph.dst0, *x = (bf16*)ph.dst1;
-  for (int row = group; row < ph.rows; row += n_groups) {
-    const int32_t* codes =
-        reinterpret_cast<const int32_t*>(static_cast<const char*>(io.state) + (int64_t)io.lines[row] * io.stride);
-    int c[16];
+// ---- row-wise phases: one 128-thread group per row of hidden size NV * VEC * 128 -----------------------------
+
+// res = v; x = bf16(v * rsqrt(mean(v^2) + eps) * gain)   (v already holds bf16-representable values)
+template <int NV, int VEC>
+__device__ __forceinline__ void norm_store(const float (&v)[NV * VEC], float ss, int dim, float eps, const bf16* gain,
+                                           bf16* res_row, bf16* out_row, const Team& tm) {
+  const float r = rsqrtf(group_sum(ss, tm.gtid, tm.red, tm.bar) / dim + eps);
 #pragma unroll
-    for (int g = 0; g < 16; ++g) {
-      c[g] = g < ph.i2 ? codes[g] : 0;
-      const int limit = g == 0 ? ph.i0 : ph.i1;
-      if (c[g] < 0 || c[g] >= limit) {
-        if (gtid == 0) raise(err, kErrBadIndex);
-        c[g] = 0;
-      }
-    }
-    float v[kMaxPerThread], ss = 0.f;
+  for (int t = 0; t < NV; ++t) {
+    const int col = row_col<NV, VEC>(t, tm.gtid);
+    float g[VEC], o[VEC];
+    ld_bf16<VEC>(gain + col, g);
 #pragma unroll
-    for (int t = 0; t < kMaxPerThread; ++t) {
-      if (t < nt) {
-        const int col = t * kTileW + gtid;
-        float acc = __bfloat162float(pad[col]);
-        acc += __bfloat162float(codec_emb[(int64_t)c[0] * dim + col]);
-#pragma unroll
-        for (int g = 1; g < 16; ++g)
-          if (g < ph.i2) acc += __bfloat162float(p_emb[((int64_t)(g - 1) * ph.i1 + c[g]) * dim + col]);
-        v[t] = bf16_round(acc);
-        ss += v[t] * v[t];
-      }
-    }
-    const float r = rsqrtf(group_sum(ss, gtid, red, bar) / dim + ph.f0);
-#pragma unroll
-    for (int t = 0; t < kMaxPerThread; ++t) {
-      if (t < nt) {
-        const int col = t * kTileW + gtid;
-        res[(int64_t)row * dim + col] = __float2bfloat16(v[t]);
-        x[(int64_t)row * dim + col] = __float2bfloat16(v[t] * r * __bfloat162float(gain[col]));
-      }
-    }
+    for (int e = 0; e < VEC; ++e) o[e] = v[t * VEC + e] * r * g[e];
+    if (res_row) st_bf16<VEC>(res_row + col, &v[t * VEC]);
+    if (out_row) st_bf16<VEC>(out_row + col, o);
   }
 }
 
-__device__ void phase_reduce_norm(const Phase& ph, const float* partials, int group, int n_groups, int gtid, float* red,
-                                  const GroupBar& bar) {
-  const int dim = ph.N, nt = dim / kTileW;
-  const bf16 *bias = (const bf16*)ph.src0, *gain = (const bf16*)ph.src3;
-  bf16 *res = (bf16*)ph.dst0, *x = (bf16*)ph.dst1;
-  for (int row = group; row < ph.rows; row += n_groups) {
-    float v[kMaxPerThread], ss = 0.f;
-    reduce_row(partials, ph.splits, ph.tiles, ph.bn, row, gtid, nt, v);
+template <int NV, int VEC>
+__device__ __noinline__ void embed_norm_rows(const Phase& ph, const TickIo& io, const Team& tm, uint32_t* err) {
+  const int dim = ph.N;
+  const bf16 *pad = (const bf16*)ph.src0, *codec_emb = (const bf16*)ph.src1, *p_emb = (const bf16*)ph.src2;
+  for (int row = tm.group; row < ph.rows; row += tm.n_groups) {
+    const int32_t* codes =
+        reinterpret_cast<const int32_t*>(static_cast<const char*>(io.state) + (int64_t)io.lines[row] * io.stride);
+    float v[NV * VEC];
 #pragma unroll
-    for (int t = 0; t < kMaxPerThread; ++t) {
-      if (t < nt) {
-        const int col = t * kTileW + gtid;
-        float a = bf16_round(v[t]);
-        if (bias) a = bf16_round(a + __bfloat162float(bias[col]));
-        v[t] = a;
+    for (int t = 0; t < NV; ++t) ld_bf16<VEC>(pad + row_col<NV, VEC>(t, tm.gtid), &v[t * VEC]);
+    // f32 sum in the reference's order: pad, codebook 0, codebooks 1.. (talker.cu:76-96)
+    for (int g = 0; g < ph.i2; ++g) {
+      int c = codes[g];
+      if (c < 0 || c >= (g == 0 ? ph.i0 : ph.i1)) {
+        if (tm.gtid == 0) raise(err, kErrBadIndex);
+        c = 0;
+      }
+      const bf16* rowp = g == 0 ? codec_emb + (int64_t)c * dim : p_emb + ((int64_t)(g - 1) * ph.i1 + c) * dim;
+#pragma unroll
+      for (int t = 0; t < NV; ++t) {
+        float e[VEC];
+        ld_bf16<VEC>(rowp + row_col<NV, VEC>(t, tm.gtid), e);
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) v[t * VEC + k] += e[k];
+      }
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV * VEC; ++i) {
+      v[i] = bf16_round(v[i]);
+      ss += v[i] * v[i];
+    }
+    norm_store<NV, VEC>(v, ss, dim, ph.f0, (const bf16*)ph.src3, (bf16*)ph.dst0 + (int64_t)row * dim,
+                        (bf16*)ph.dst1 + (int64_t)row * dim, tm);
+  }
+}
+
+template <int NV, int VEC>
+__device__ __noinline__ void reduce_norm_rows(const Phase& ph, const float* partials, const Team& tm) {
+  const int dim = ph.N;
+  const bf16* bias = (const bf16*)ph.src0;
+  const Partials pt(partials, ph);
+  for (int row = tm.group; row < ph.rows; row += tm.n_groups) {
+    float v[NV * VEC], ss = 0.f;
+    reduce_row<NV, VEC>(pt, row, tm.gtid, v);
+#pragma unroll
+    for (int t = 0; t < NV; ++t) {
+      float b[VEC];
+      if (bias) ld_bf16<VEC>(bias + row_col<NV, VEC>(t, tm.gtid), b);
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) {
+        float a = bf16_round(v[t * VEC + e]);
+        if (bias) a = bf16_round(a + b[e]);
+        v[t * VEC + e] = a;
         ss += a * a;
       }
     }
-    const float r = rsqrtf(group_sum(ss, gtid, red, bar) / dim + ph.f0);
-#pragma unroll
-    for (int t = 0; t < kMaxPerThread; ++t) {
-      if (t < nt) {
-        const int col = t * kTileW + gtid;
-        res[(int64_t)row * dim + col] = __float2bfloat16(v[t]);
-        x[(int64_t)row * dim + col] = __float2bfloat16(v[t] * r * __bfloat162float(gain[col]));
-      }
-    }
+    norm_store<NV, VEC>(v, ss, dim, ph.f0, (const bf16*)ph.src3, (bf16*)ph.dst0 + (int64_t)row * dim,
+                        (bf16*)ph.dst1 + (int64_t)row * dim, tm);
   }
 }
 
-__device__ void phase_add_norm(const Phase& ph, const float* partials, int group, int n_groups, int gtid, float* red,
-                               const GroupBar& bar) {
-  const int dim = ph.N, nt = dim / kTileW, every = ph.i0, which = ph.i1;
-  const bf16* gain = (const bf16*)ph.src3;
+template <int NV, int VEC>
+__device__ __noinline__ void add_norm_rows(const Phase& ph, const float* partials, const Team& tm) {
+  const int dim = ph.N, every = ph.i0, which = ph.i1;
   bf16 *res = (bf16*)ph.dst0, *out = (bf16*)ph.dst1;
-  for (int row = group; row < ph.rows; row += n_groups) {
-    float v[kMaxPerThread], ss = 0.f;
-    reduce_row(partials, ph.splits, ph.tiles, ph.bn, row, gtid, nt, v);
+  const Partials pt(partials, ph);
+  for (int row = tm.group; row < ph.rows; row += tm.n_groups) {
+    float v[NV * VEC], old[NV * VEC], ss = 0.f;
 #pragma unroll
-    for (int t = 0; t < kMaxPerThread; ++t) {
-      if (t < nt) {
-        const int col = t * kTileW + gtid;
-        v[t] = bf16_round(v[t]) + __bfloat162float(res[(int64_t)row * dim + col]);
-        ss += v[t] * v[t];
-      }
+    for (int t = 0; t < NV; ++t) ld_bf16<VEC>(res + (int64_t)row * dim + row_col<NV, VEC>(t, tm.gtid), &old[t * VEC]);
+    reduce_row<NV, VEC>(pt, row, tm.gtid, v);
+#pragma unroll
+    for (int i = 0; i < NV * VEC; ++i) {
+      v[i] = bf16_round(v[i]) + old[i];  // the norm runs over the unrounded sum (qwen3.cu:34)
+      ss += v[i] * v[i];
     }
-    const float r = rsqrtf(group_sum(ss, gtid, red, bar) / dim + ph.f0);
     const bool keep = row % every == which;
+    norm_store<NV, VEC>(v, ss, dim, ph.f0, (const bf16*)ph.src3, res + (int64_t)row * dim,
+                        keep ? out + (int64_t)(row / every) * dim : nullptr, tm);
+  }
+}
+
+// Hidden sizes the decoder stacks use: 128 and 256 column by column, 512 .. 2048 four columns at a time.
+#define OMNI_ROW_DISPATCH(fn, dim, ...)        \
+  switch (dim) {                               \
+    case 128: fn<1, 1>(__VA_ARGS__); break;    \
+    case 256: fn<2, 1>(__VA_ARGS__); break;    \
+    case 512: fn<1, 4>(__VA_ARGS__); break;    \
+    case 1024: fn<2, 4>(__VA_ARGS__); break;   \
+    case 2048: fn<4, 4>(__VA_ARGS__); break;   \
+    default: break;                            \
+  }
+
+// SwiGLU over split-K partials of the gate|up GEMM (each tile holds tile_n/2 gate channels then the matching up
+// channels): act[m, c] = bf16(bf16(silu(bf16(gate))) * bf16(up)). One group per (row, 512-channel chunk).
+__device__ __noinline__ void reduce_silu_rows(const Phase& ph, const float* partials, const Team& tm) {
+  const int inter = ph.i0, chunks = (inter + 4 * kGroupThreads - 1) / (4 * kGroupThreads), half = ph.tile_n >> 1;
+  bf16* act = (bf16*)ph.dst0;
+  const Partials pt(partials, ph);
+  for (int it = tm.group; it < ph.rows * chunks; it += tm.n_groups) {
+    const int row = it % ph.rows, c0 = (it / ph.rows) * 4 * kGroupThreads;
+    int cols[8];
+    float v[8];
 #pragma unroll
-    for (int t = 0; t < kMaxPerThread; ++t) {
-      if (t < nt) {
-        const int col = t * kTileW + gtid;
-        res[(int64_t)row * dim + col] = __float2bfloat16(v[t]);
-        if (keep) out[(int64_t)(row / every) * dim + col] = __float2bfloat16(v[t] * r * __bfloat162float(gain[col]));
+    for (int q = 0; q < 4; ++q) {
+      const int c = min(c0 + q * kGroupThreads + tm.gtid, inter - 1);
+      cols[q] = (c / half) * ph.tile_n + c % half;  // gate
+      cols[4 + q] = cols[q] + half;                 // up
+    }
+    reduce_cols<8>(pt, row, cols, v);
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const int c = c0 + q * kGroupThreads + tm.gtid;
+      if (c < inter) {
+        const float g = bf16_round(v[q]), u = bf16_round(v[4 + q]);
+        act[(int64_t)row * inter + c] = __float2bfloat16(bf16_round(g / (1.f + __expf(-g))) * u);
       }
     }
   }
 }
 
-// ---- rope + KV write + attention: one group per (sequence, kv head) ---------------------------------------------
+// ---- rope + KV write + attention --------------------------------------------------------------------------------
+// A team of W warps per (sequence, kv head): four warps for the talker's paged KV (pages round-robin over the
+// warps), one warp for the code predictor's single-page frames (so all eight worker warps of a CTA hold an item).
 
-template <int D, int G>
-__device__ void rope_attend_item(const Phase& ph, const TickIo& io, const float* partials, int seq, int kh, int gtid,
-                                 AttnShared<128, 4>& shraw, const GroupBar& bar, uint32_t* err) {
-  AttnShared<D, G>& sh = reinterpret_cast<AttnShared<D, G>&>(shraw);
+// q/k of one head: RMSNorm over the head, the normalised value rounded to bf16 before the gain, half-rotation
+// rotary embedding (qwen3.cu:66-107). lo/hi: this lane's E elements of each half.
+template <int D>
+__device__ __forceinline__ void rope_head(float (&lo)[D / 64], float (&hi)[D / 64], const bf16* w, int lane, int pos,
+                                          float eps, float theta) {
   constexpr int E = D / 64;
+  float ss = 0.f;
+#pragma unroll
+  for (int e = 0; e < E; ++e) ss += lo[e] * lo[e] + hi[e] * hi[e];
+  const float rn = rsqrtf(warp_add(ss) / D + eps);
+#pragma unroll
+  for (int e = 0; e < E; ++e) {
+    const int i = lane * E + e;
+    const float a = bf16_round(lo[e] * rn) * __bfloat162float(w[i]);
+    const float b = bf16_round(hi[e] * rn) * __bfloat162float(w[D / 2 + i]);
+    const float inv_freq = 1.f / powf(theta, (float)(2 * i) / D);
+    float sn, cs;
+    sincosf((float)pos * inv_freq, &sn, &cs);
+    lo[e] = bf16_round(a * cs - b * sn);
+    hi[e] = bf16_round(b * cs + a * sn);
+  }
+}
+
+template <int D, int G, int W, typename TeamSync>
+__device__ __noinline__ void rope_attend_item(const Phase& ph, const TickIo& io, const float* partials, int seq, int kh,
+                                              int tid, AttnShared<D, G, W>& sh, const TeamSync& team, uint32_t* err) {
+  constexpr int E = D / 64, VE = D / 32;
   const int hq = ph.i0, hk = ph.i1, per = ph.i3, base = ph.i4;
   const bool paged = ph.i5 != 0;
   const bf16 *q_norm = (const bf16*)ph.src0, *k_norm = (const bf16*)ph.src1;
   bf16 *kv = (bf16*)ph.dst0, *out = (bf16*)ph.dst1;
-  const int lane = gtid & 31, warp = gtid >> 5;
+  const int lane = tid & 31, warp = tid >> 5;
   const float scale = rsqrtf((float)D);
+  const Partials pt(partials, ph);
   for (int r = 0; r < per; ++r) {
     const int n = seq * per + r;
     const int pos = paged ? io.d_pos[n] : base + r;
@@ -267,89 +409,119 @@ __device__ void rope_attend_item(const Phase& ph, const TickIo& io, const float*
     int64_t page = slot >> 4;
     const int tok = (int)(slot & 15);
     if (page < 0 || page >= ph.i6) {
-      if (gtid == 0) raise(err, kErrBadIndex);
+      if (tid == 0) raise(err, kErrBadIndex);
       page = 0;
     }
-    // G query heads, the key head and the value head of this row, a warp per head
-    for (int job = warp; job < G + 2; job += kAttnWarps) {
-      if (job == G + 1) {  // value: plain copy
-        bf16* dst = kv + kv_offset<D>(page, hk, kh, 1, tok);
-        const int col0 = (hq + hk + kh) * D;
-        int cols[D / 32];
-        float val[D / 32];
+    bf16* kdst = kv + kv_offset<D>(page, hk, kh, 0, tok);
+    bf16* vdst = kv + kv_offset<D>(page, hk, kh, 1, tok);
+    if constexpr (W == 1) {
+      // one warp does the G query heads, the key head and the value head; all their partial sums in one batch
+      int cols[(G + 1) * 2 * E + VE];
+      float val[(G + 1) * 2 * E + VE];
 #pragma unroll
-        for (int e = 0; e < D / 32; ++e) cols[e] = col0 + lane + 32 * e;
-        reduce_partial_n(partials, ph.splits, ph.tiles, ph.bn, n, cols, val);
-#pragma unroll
-        for (int e = 0; e < D / 32; ++e) dst[lane + 32 * e] = __float2bfloat16(val[e]);
-        continue;
-      }
-      const bool is_q = job < G;
-      const int col0 = (is_q ? kh * G + job : hq + kh) * D;
-      const bf16* w = is_q ? q_norm : k_norm;
-      float lo[E], hi[E], ss = 0.f;
-      {
-        int cols[2 * E];
-        float val[2 * E];
-#pragma unroll
-        for (int e = 0; e < E; ++e) cols[e] = col0 + lane * E + e, cols[E + e] = col0 + D / 2 + lane * E + e;
-        reduce_partial_n(partials, ph.splits, ph.tiles, ph.bn, n, cols, val);
+      for (int j = 0; j <= G; ++j) {
+        const int col0 = (j < G ? kh * G + j : hq + kh) * D;
 #pragma unroll
         for (int e = 0; e < E; ++e) {
-          lo[e] = bf16_round(val[e]);
-          hi[e] = bf16_round(val[E + e]);
-          ss += lo[e] * lo[e] + hi[e] * hi[e];
+          cols[j * 2 * E + e] = col0 + lane * E + e;
+          cols[j * 2 * E + E + e] = col0 + D / 2 + lane * E + e;
         }
       }
-      const float rn = rsqrtf(warp_add(ss) / D + ph.f0);
-      bf16* kdst = kv + kv_offset<D>(page, hk, kh, 0, tok);
 #pragma unroll
-      for (int e = 0; e < E; ++e) {
-        const int i = lane * E + e;
-        const float a = bf16_round(lo[e] * rn) * __bfloat162float(w[i]);
-        const float b = bf16_round(hi[e] * rn) * __bfloat162float(w[D / 2 + i]);
-        const float inv_freq = 1.f / powf(ph.f1, (float)(2 * i) / D);
-        float sn, cs;
-        sincosf((float)pos * inv_freq, &sn, &cs);
-        const bf16 o_lo = __float2bfloat16(a * cs - b * sn), o_hi = __float2bfloat16(b * cs + a * sn);
-        if (is_q) {
-          sh.qs[job][i] = __bfloat162float(o_lo);
-          sh.qs[job][D / 2 + i] = __bfloat162float(o_hi);
-        } else {
-          kdst[i] = o_lo;
-          kdst[D / 2 + i] = o_hi;
+      for (int e = 0; e < VE; ++e) cols[(G + 1) * 2 * E + e] = (hq + hk + kh) * D + lane + 32 * e;
+      reduce_cols(pt, n, cols, val);
+#pragma unroll
+      for (int j = 0; j <= G; ++j) {
+        float lo[E], hi[E];
+#pragma unroll
+        for (int e = 0; e < E; ++e) lo[e] = bf16_round(val[j * 2 * E + e]), hi[e] = bf16_round(val[j * 2 * E + E + e]);
+        rope_head<D>(lo, hi, j < G ? q_norm : k_norm, lane, pos, ph.f0, ph.f1);
+#pragma unroll
+        for (int e = 0; e < E; ++e) {
+          const int i = lane * E + e;
+          if (j < G) {
+            sh.qs[j][i] = lo[e], sh.qs[j][D / 2 + i] = hi[e];
+          } else {
+            kdst[i] = __float2bfloat16(lo[e]), kdst[D / 2 + i] = __float2bfloat16(hi[e]);
+          }
+        }
+      }
+#pragma unroll
+      for (int e = 0; e < VE; ++e) vdst[lane + 32 * e] = __float2bfloat16(val[(G + 1) * 2 * E + e]);
+    } else {
+      for (int job = warp; job < G + 2; job += W) {
+        if (job == G + 1) {  // value: plain copy
+          int cols[VE];
+          float val[VE];
+#pragma unroll
+          for (int e = 0; e < VE; ++e) cols[e] = (hq + hk + kh) * D + lane + 32 * e;
+          reduce_cols(pt, n, cols, val);
+#pragma unroll
+          for (int e = 0; e < VE; ++e) vdst[lane + 32 * e] = __float2bfloat16(val[e]);
+          continue;
+        }
+        const bool is_q = job < G;
+        const int col0 = (is_q ? kh * G + job : hq + kh) * D;
+        int cols[2 * E];
+        float val[2 * E], lo[E], hi[E];
+#pragma unroll
+        for (int e = 0; e < E; ++e) cols[e] = col0 + lane * E + e, cols[E + e] = col0 + D / 2 + lane * E + e;
+        reduce_cols(pt, n, cols, val);
+#pragma unroll
+        for (int e = 0; e < E; ++e) lo[e] = bf16_round(val[e]), hi[e] = bf16_round(val[E + e]);
+        rope_head<D>(lo, hi, is_q ? q_norm : k_norm, lane, pos, ph.f0, ph.f1);
+#pragma unroll
+        for (int e = 0; e < E; ++e) {
+          const int i = lane * E + e;
+          if (is_q) {
+            sh.qs[job][i] = lo[e], sh.qs[job][D / 2 + i] = hi[e];
+          } else {
+            kdst[i] = __float2bfloat16(lo[e]), kdst[D / 2 + i] = __float2bfloat16(hi[e]);
+          }
         }
       }
     }
     __threadfence_block();
-    bar.sync();
-    attend_pages<D, G>(sh, kv, paged ? io.pages + io.indptr[n] : nullptr, seq, pos + 1, hk, kh, scale,
-                       out + ((int64_t)n * hq + kh * G) * D, gtid, bar);
+    team.sync();
+    attend_pages<D, G, W>(sh, kv, paged ? io.pages + io.indptr[n] : nullptr, seq, pos + 1, hk, kh, scale,
+                          out + ((int64_t)n * hq + kh * G) * D, tid, team);
   }
 }
 
-__device__ void phase_rope_attn(const Phase& ph, const TickIo& io, const float* partials, int group, int n_groups,
-                                int gtid, AttnShared<128, 4>& sh, const GroupBar& bar, uint32_t* err) {
-  const int hq = ph.i0, hk = ph.i1, D = ph.i2, per = ph.i3, G = hq / hk;
-  const int seqs = ph.rows / per, items = seqs * hk;
-  for (int it = group; it < items; it += n_groups) {
-    const int seq = it / hk, kh = it % hk;
-    if (D == 128) {
-      if (G == 1) rope_attend_item<128, 1>(ph, io, partials, seq, kh, gtid, sh, bar, err);
-      else if (G == 2) rope_attend_item<128, 2>(ph, io, partials, seq, kh, gtid, sh, bar, err);
-      else rope_attend_item<128, 4>(ph, io, partials, seq, kh, gtid, sh, bar, err);
-    } else {
-      if (G == 1) rope_attend_item<64, 1>(ph, io, partials, seq, kh, gtid, sh, bar, err);
-      else if (G == 2) rope_attend_item<64, 2>(ph, io, partials, seq, kh, gtid, sh, bar, err);
-      else rope_attend_item<64, 4>(ph, io, partials, seq, kh, gtid, sh, bar, err);
-    }
+template <int D, int G>
+__device__ __forceinline__ void rope_attn_dg(const Phase& ph, const TickIo& io, const float* partials, const Team& tm,
+                                             int wtid, WorkerScratch& scratch, uint32_t* err) {
+  const int hk = ph.i1, per = ph.i3;
+  const int items = (ph.rows / per) * hk;
+  if (ph.i5) {  // paged: a 128-thread group per item
+    auto& sh = reinterpret_cast<AttnShared<D, G, 4>&>(scratch.attn4[wtid >> 7]);
+    for (int it = tm.group; it < items; it += tm.n_groups)
+      rope_attend_item<D, G, 4>(ph, io, partials, it / hk, it % hk, tm.gtid, sh, tm.bar, err);
+  } else {  // one page per sequence: a warp per item
+    auto& sh = reinterpret_cast<AttnShared<D, G, 1>&>(scratch.attn1[wtid >> 5]);
+    const int wid = (int)blockIdx.x * (kWorkerThreads / 32) + (wtid >> 5), n_warps = (int)gridDim.x * (kWorkerThreads / 32);
+    for (int it = wid; it < items; it += n_warps)
+      rope_attend_item<D, G, 1>(ph, io, partials, it / hk, it % hk, wtid & 31, sh, WarpSync(), err);
+  }
+}
+
+__device__ __forceinline__ void phase_rope_attn(const Phase& ph, const TickIo& io, const float* partials, const Team& tm,
+                                                int wtid, WorkerScratch& scratch, uint32_t* err) {
+  const int D = ph.i2, G = ph.i0 / ph.i1;
+  if (D == 128) {
+    if (G == 1) rope_attn_dg<128, 1>(ph, io, partials, tm, wtid, scratch, err);
+    else if (G == 2) rope_attn_dg<128, 2>(ph, io, partials, tm, wtid, scratch, err);
+    else rope_attn_dg<128, 4>(ph, io, partials, tm, wtid, scratch, err);
+  } else {
+    if (G == 1) rope_attn_dg<64, 1>(ph, io, partials, tm, wtid, scratch, err);
+    else if (G == 2) rope_attn_dg<64, 2>(ph, io, partials, tm, wtid, scratch, err);
+    else rope_attn_dg<64, 4>(ph, io, partials, tm, wtid, scratch, err);
   }
 }
 
 // ---- head reduce + draw + next predictor input: one row per CTA (all 256 workers) -----------------------------
 
-__device__ void phase_sample(const Phase& ph, const TickIo& io, const float* partials, int wtid, sampler::Shared& sh,
-                             uint32_t* err) {
+__device__ __noinline__ void phase_sample(const Phase& ph, const TickIo& io, const float* partials, int wtid, sampler::Shared& sh) {
   using Team = sampler::Team<kWorkerThreads, WorkerSync>;
   const int g = gridDim.x;
   bf16* logits_out = (bf16*)ph.dst0;
@@ -375,7 +547,7 @@ __device__ void phase_sample(const Phase& ph, const TickIo& io, const float* par
       int cols[Team::PER];
 #pragma unroll
       for (int j = 0; j < Team::PER; ++j) cols[j] = min(wtid * Team::PER + j, prm.vocab - 1);
-      reduce_partial_n(partials, ph.splits, ph.tiles, ph.bn, row, cols, mine);
+      reduce_cols(Partials(partials, ph), row, cols, mine);
 #pragma unroll
       for (int j = 0; j < Team::PER; ++j) {
         const bf16 b = __float2bfloat16(mine[j]);
@@ -407,51 +579,48 @@ __device__ void phase_sample(const Phase& ph, const TickIo& io, const float* par
     }
     WorkerSync::sync();
   }
-  (void)err;
 }
 
-// ---- GEMM epilogue: this worker warp's TMEM quadrant, every other 16-column chunk ---------------------------------
+// ---- GEMM epilogue: a worker thread owns one activation row (its TMEM lane) and half of the tile's columns -------
 
-// Reads 16 columns of this lane from every accumulator of the buffer and sums them in accumulator order.
-__device__ __forceinline__ void load_acc16(uint32_t addr, int n_acc, int acc_stride, float* v) {
-  sm100::tmem_ld16(addr, v);
-  for (int a = 1; a < n_acc; ++a) {
-    float w[16];
-    sm100::tmem_ld16(addr + (uint32_t)(a * acc_stride), w);
-#pragma unroll
-    for (int j = 0; j < 16; ++j) v[j] += w[j];
-  }
-}
-
-__device__ void gemm_epilogue(const Phase& ph, float* partials, int tile, int split, uint32_t tmem_acc, int n_acc,
-                              int acc_stride, int wwarp, int lane) {
-  const int quad = wwarp & 3, half = wwarp >> 2;
+__device__ __noinline__ void gemm_epilogue(const Phase& ph, float* partials, int tile, int split, uint32_t tmem_acc,
+                                           int wwarp, int lane) {
+  // a warp may only touch the TMEM lanes of its quadrant, (warp index in the CTA) % 4
+  const int quad = (wwarp + kFirstWorkerWarp) & 3, half = wwarp >> 2;
+  const int m = quad * 32 + lane, tn = ph.tile_n;
+  if (quad * 32 >= ph.rows) return;  // no live row in this warp's quadrant (warp-uniform)
   const uint32_t lane_addr = tmem_acc + ((uint32_t)(quad * 32) << 16);
   if (ph.mode == kGemmPartials) {
-    float* tile_base = partials + ((size_t)split * ph.tiles + tile) * ph.bn * kTileW + quad * 32 + lane;
-    for (int c0 = half * 16; c0 < ph.bn; c0 += 32) {
+    float* rowp = partials + (((size_t)split * ph.tiles + tile) * ph.bn + min(m, ph.bn - 1)) * tn;
+#pragma unroll 1
+    for (int c0 = half * (tn / 2); c0 < (half + 1) * (tn / 2); c0 += 16) {
       float v[16];
-      load_acc16(lane_addr + c0, n_acc, acc_stride, v);
+      sm100::tmem_ld16(lane_addr + c0, v);
+      if (m < ph.rows) {
 #pragma unroll
-      for (int j = 0; j < 16; ++j) tile_base[(size_t)(c0 + j) * kTileW] = v[j];
+        for (int j = 0; j < 16; j += 4)
+          *reinterpret_cast<float4*>(rowp + c0 + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+      }
     }
   } else {
-    // SwiGLU: the tile's rows alternate 16 gate channels / 16 up channels, so a lane's partner is lane ^ 16
+    // SwiGLU: columns [0, tn/2) are gate channels tile*tn/2.., columns [tn/2, tn) the matching up channels
     bf16* act = (bf16*)ph.dst0;
-    const int inter = ph.i0;
-    const int ch = tile * 64 + quad * 16 + (lane & 15);
-    for (int c0 = half * 16; c0 < ph.bn; c0 += 32) {
-      float v[16];
-      load_acc16(lane_addr + c0, n_acc, acc_stride, v);
+    const int inter = ph.i0, hc = tn / 2;
+#pragma unroll 1
+    for (int c0 = half * (hc / 2); c0 < (half + 1) * (hc / 2); c0 += 16) {
+      float g[16], u[16];
+      sm100::tmem_ld16(lane_addr + c0, g);
+      sm100::tmem_ld16(lane_addr + hc + c0, u);
+      const int ch = tile * hc + c0;
+      if (m < ph.rows && ch < inter) {
+        float o[16];
 #pragma unroll
-      for (int j = 0; j < 16; ++j) {
-        const float mine = bf16_round(v[j]);
-        const float other = __shfl_xor_sync(0xffffffffu, mine, 16);
-        const int m = c0 + j;
-        if (lane < 16 && m < ph.rows && ch < inter) {
-          const float silu = bf16_round(mine / (1.f + __expf(-mine)));
-          act[(int64_t)m * inter + ch] = __float2bfloat16(silu * other);
+        for (int j = 0; j < 16; ++j) {
+          const float gg = bf16_round(g[j]);
+          o[j] = bf16_round(gg / (1.f + __expf(-gg))) * bf16_round(u[j]);
         }
+        st8(act + (int64_t)m * inter + ch, o);
+        st8(act + (int64_t)m * inter + ch + 8, o + 8);
       }
     }
   }
@@ -468,6 +637,7 @@ __global__ void __launch_bounds__(kThreads, 1) tick_kernel(const __grid_constant
       *reinterpret_cast<WorkerScratch*>(base_ptr + (size_t)a.n_stages * a.stage_bytes + ((sizeof(Control) + 127) & ~127));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int G = gridDim.x;
+  constexpr uint32_t kTmemCols = 512;  // two accumulators of 256 f32 columns
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kMaxStages; ++s) {
@@ -484,12 +654,13 @@ __global__ void __launch_bounds__(kThreads, 1) tick_kernel(const __grid_constant
     ctl.phase[0] = a.phases[0];
     mbar_init_fence();
   }
-  if (warp == 2) tmem_alloc(smem_addr(&ctl.tmem_base), (uint32_t)a.tmem_cols);
+  if (warp == 2) tmem_alloc(smem_addr(&ctl.tmem_base), kTmemCols);
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = ctl.tmem_base;
-  auto stage_addr = [&](int s) { return base + (uint32_t)(s * a.stage_bytes); };
+  auto x_addr = [&](int s) { return base + (uint32_t)(s * a.stage_bytes); };
+  auto w_addr = [&](int s) { return base + (uint32_t)(s * a.stage_bytes + a.x_bytes); };
 
   if (warp == 0) {
     if (lane == 0) {  // ---- weight producer ----
@@ -500,6 +671,17 @@ __global__ void __launch_bounds__(kThreads, 1) tick_kernel(const __grid_constant
         if (ph.type != kPhGemm) continue;
         const int items = ph.tiles * ph.splits, nkb = ph.K / kTileK;
         const CUtensorMap* map = a.maps + ph.wmap;
+        if (first_item(ph) >= items) continue;
+        {  // weights do not depend on activations, but how far ahead of the barriers they are fetched is bounded
+          const uint64_t start = global_timer_ns();
+          while (ctl.released < p - a.w_ahead && !ctl.abort) {
+            __nanosleep(40);
+            if (global_timer_ns() - start > kWaitLimitNs) {
+              raise(a.err, kErrBarrierTimeout);
+              ctl.abort = 1;
+            }
+          }
+        }
         for (int it = first_item(ph); it < items && !ctl.abort; it += G) {
           const int tile = it % ph.tiles, split = it / ph.tiles;
           const int kb0 = (int)((int64_t)nkb * split / ph.splits), kb1 = (int)((int64_t)nkb * (split + 1) / ph.splits);
@@ -509,8 +691,8 @@ __global__ void __launch_bounds__(kThreads, 1) tick_kernel(const __grid_constant
               break;
             }
             const uint32_t bar = smem_addr(&ctl.full_w[stage]);
-            mbar_expect_tx(bar, kWBytes);
-            tma_load_2d(stage_addr(stage), map, bar, kb * kTileK, tile * kTileW, kEvictFirst);
+            mbar_expect_tx(bar, (uint32_t)ph.tile_n * kTileK * 2);
+            tma_load_2d(w_addr(stage), map, bar, kb * kTileK, tile * ph.tile_n, kEvictFirst);
             if (++stage == a.n_stages) stage = 0, par ^= 1u;
           }
         }
@@ -547,7 +729,7 @@ __global__ void __launch_bounds__(kThreads, 1) tick_kernel(const __grid_constant
             }
             const uint32_t bar = smem_addr(&ctl.full_x[stage]);
             mbar_expect_tx(bar, xbytes);
-            tma_load_2d(stage_addr(stage) + kWBytes, map, bar, kb * kTileK, 0, kEvictLast);
+            tma_load_2d(x_addr(stage), map, bar, kb * kTileK, 0, kEvictLast);
             if (++stage == a.n_stages) stage = 0, par ^= 1u;
           }
         }
@@ -557,11 +739,13 @@ __global__ void __launch_bounds__(kThreads, 1) tick_kernel(const __grid_constant
     if (lane == 0) {  // ---- MMA issuer ----
       int stage = 0, buf = 0;
       uint32_t par = 0, empty_par[2] = {0, 0};
+      // A = the activation tile (rows beyond the phase's bn read whatever follows in the stage; those TMEM
+      // lanes are never read back), B = 256 weight rows, both K-major with the 128-byte swizzle
       for (int p = 0; p < a.n_phases && !ctl.abort; ++p) {
         const Phase& ph = a.phases[p];
         if (ph.type != kPhGemm) continue;
         const int items = ph.tiles * ph.splits, nkb = ph.K / kTileK;
-        const uint32_t idesc = idesc_bf16_f32(kTileW, ph.bn);
+        const uint32_t idesc = idesc_bf16_f32(kTileM, ph.tile_n);
         for (int it = first_item(ph); it < items && !ctl.abort; it += G) {
           const int split = it / ph.tiles;
           const int kb0 = (int)((int64_t)nkb * split / ph.splits), kb1 = (int)((int64_t)nkb * (split + 1) / ph.splits);
@@ -571,7 +755,7 @@ __global__ void __launch_bounds__(kThreads, 1) tick_kernel(const __grid_constant
           }
           empty_par[buf] ^= 1u;
           tc_fence_after_sync();
-          const uint32_t tmem_d = tmem_base + (uint32_t)(buf * a.n_acc * a.acc_stride);
+          const uint32_t tmem_d = tmem_base + (uint32_t)(buf * kTileN);
           for (int kb = kb0; kb < kb1; ++kb) {
             if (!mbar_wait(smem_addr(&ctl.full_w[stage]), par, a.err) ||
                 !mbar_wait(smem_addr(&ctl.full_x[stage]), par, a.err)) {
@@ -579,13 +763,10 @@ __global__ void __launch_bounds__(kThreads, 1) tick_kernel(const __grid_constant
               break;
             }
             tc_fence_after_sync();
-            const uint64_t adesc = kmajor_sw128_desc(stage_addr(stage)),
-                           bdesc = kmajor_sw128_desc(stage_addr(stage) + kWBytes);
-            // consecutive MMAs into one accumulator serialise on its latency: rotate the K steps over n_acc of them
+            const uint64_t adesc = kmajor_sw128_desc(x_addr(stage)), bdesc = kmajor_sw128_desc(w_addr(stage));
 #pragma unroll
             for (int k = 0; k < kTileK / 16; ++k)
-              mma_bf16(tmem_d + (uint32_t)((k % a.n_acc) * a.acc_stride), adesc + (uint64_t)(k * 2),
-                       bdesc + (uint64_t)(k * 2), idesc, (kb > kb0 || k >= a.n_acc) ? 1u : 0u);
+              mma_bf16(tmem_d, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2), idesc, (kb > kb0 || k > 0) ? 1u : 0u);
             mma_commit(smem_addr(&ctl.empty[stage]));
             if (++stage == a.n_stages) stage = 0, par ^= 1u;
           }
@@ -598,9 +779,9 @@ __global__ void __launch_bounds__(kThreads, 1) tick_kernel(const __grid_constant
   } else if (warp >= kFirstWorkerWarp) {
     // ---- workers ----
     const int wtid = threadIdx.x - kFirstWorkerWarp * 32, wwarp = warp - kFirstWorkerWarp;
-    const int grp = wtid >> 7, gtid = wtid & 127;
-    const GroupBar gbar{2 + grp};
-    const int group = blockIdx.x * 2 + grp, n_groups = G * 2;
+    const int grp = wtid >> 7;
+    // group ids run over the CTAs first, so a phase with few rows spreads over as many SMs as it has rows
+    const Team tm{grp * G + (int)blockIdx.x, G * 2, wtid & 127, ctl.red[grp], GroupBar{2 + grp}};
     int buf = 0;
     uint32_t full_par[2] = {0, 0};
     for (int p = 0; p < a.n_phases; ++p) {
@@ -618,9 +799,7 @@ __global__ void __launch_bounds__(kThreads, 1) tick_kernel(const __grid_constant
             if (!ok) ctl.abort = 1;
             full_par[buf] ^= 1u;
             tc_fence_after_sync();
-            if (ok)
-              gemm_epilogue(ph, a.partials, it % ph.tiles, it / ph.tiles,
-                            tmem_base + (uint32_t)(buf * a.n_acc * a.acc_stride), a.n_acc, a.acc_stride, wwarp, lane);
+            if (ok) gemm_epilogue(ph, a.partials, it % ph.tiles, it / ph.tiles, tmem_base + (uint32_t)(buf * kTileN), wwarp, lane);
             tc_fence_before_sync();
             WorkerSync::sync();
             if (wtid == 0) mbar_arrive(smem_addr(&ctl.acc_empty[buf]));
@@ -629,22 +808,22 @@ __global__ void __launch_bounds__(kThreads, 1) tick_kernel(const __grid_constant
           }
           break;
         }
-        case kPhEmbedNorm: phase_embed_norm(ph, a.io, group, n_groups, gtid, ctl.red[grp], gbar, a.err); break;
-        case kPhReduceNorm: phase_reduce_norm(ph, a.partials, group, n_groups, gtid, ctl.red[grp], gbar); break;
-        case kPhAddNorm: phase_add_norm(ph, a.partials, group, n_groups, gtid, ctl.red[grp], gbar); break;
-        case kPhRopeAttn:
-          phase_rope_attn(ph, a.io, a.partials, group, n_groups, gtid, scratch.attn[grp], gbar, a.err);
-          break;
-        case kPhSample: phase_sample(ph, a.io, a.partials, wtid, scratch.sample, a.err); break;
+        case kPhEmbedNorm: OMNI_ROW_DISPATCH(embed_norm_rows, ph.N, ph, a.io, tm, a.err); break;
+        case kPhReduceNorm: OMNI_ROW_DISPATCH(reduce_norm_rows, ph.N, ph, a.partials, tm); break;
+        case kPhAddNorm: OMNI_ROW_DISPATCH(add_norm_rows, ph.N, ph, a.partials, tm); break;
+        case kPhReduceSilu: reduce_silu_rows(ph, a.partials, tm); break;
+        case kPhRopeAttn: phase_rope_attn(ph, a.io, a.partials, tm, wtid, scratch, a.err); break;
+        case kPhSample: phase_sample(ph, a.io, a.partials, wtid, scratch.sample); break;
         default: break;
       }
       // end of phase: the team barrier orders every worker's writes before thread 0's gpu-scope fence and arrival
       // (fences are cumulative), then everyone waits for thread 0 to see all CTAs arrive
       WorkerSync::sync();
       if (wtid == 0) {
+        if (a.trace && blockIdx.x == 0) a.trace[2 * p] = global_timer_ns();  // CTA 0's own work is done
         if (!ctl.abort && !grid_barrier(a.barrier, (uint32_t)(p + 1) * (uint32_t)G, a.err)) ctl.abort = 1;
         ctl.released = p + 1;
-        if (a.trace && blockIdx.x == 0) a.trace[p] = global_timer_ns();
+        if (a.trace && blockIdx.x == 0) a.trace[2 * p + 1] = global_timer_ns();  // every CTA has arrived
       }
       WorkerSync::sync();
     }
@@ -653,26 +832,27 @@ __global__ void __launch_bounds__(kThreads, 1) tick_kernel(const __grid_constant
   if (ctl.abort) __nanosleep(20000);  // let copies still in flight land before the shared memory is released
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == 2) tmem_dealloc(tmem_base, (uint32_t)a.tmem_cols);
+  if (warp == 2) tmem_dealloc(tmem_base, kTmemCols);
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
-size_t tick_smem_bytes(int n_stages, int stage_bytes) {
-  return 1024 + (size_t)n_stages * stage_bytes + ((sizeof(Control) + 127) & ~127) + sizeof(WorkerScratch);
+void stage_plan(int max_bn, int* n_stages, int* stage_bytes, int* x_bytes) {
+  *x_bytes = (max_bn * kTileK * 2 + 1023) & ~1023;
+  *stage_bytes = *x_bytes + kWBytes;
+  *n_stages = std::min(kMaxStages, (176 * 1024) / *stage_bytes);
 }
 
-void stage_plan(int max_bn, int* n_stages, int* stage_bytes) {
-  *stage_bytes = kWBytes + max_bn * kTileK * 2;
-  *n_stages = std::min(kMaxStages, (188 * 1024) / *stage_bytes);
+size_t tick_smem_bytes(int n_stages, int stage_bytes) {
+  // the last stage's activation descriptor spans 128 rows whatever bn is: keep the tail inside the allocation
+  return 1024 + (size_t)n_stages * stage_bytes + ((sizeof(Control) + 127) & ~127) + sizeof(WorkerScratch);
 }
 
 }  // namespace
 
 int tick_add_map(TickProgram* prog, const bf16* base, int rows, int K, int box_rows) {
-  if (tc_init() != 0) return -1;
   void* fn = nullptr;
   cudaDriverEntryPointQueryResult q;
   if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess || !fn) return -1;
@@ -692,8 +872,8 @@ int tick_add_map(TickProgram* prog, const bf16* base, int rows, int K, int box_r
 
 bool tick_supports(int hidden, int head_dim, int q_heads, int kv_heads, int rows_max) {
   const int g = kv_heads > 0 ? q_heads / kv_heads : 0;
-  return hidden % kTileW == 0 && hidden <= kMaxPerThread * kTileW && (head_dim == 64 || head_dim == 128) &&
-         (g == 1 || g == 2 || g == 4) && rows_max <= 256;
+  const bool dim_ok = hidden == 128 || hidden == 256 || hidden == 512 || hidden == 1024 || hidden == 2048;
+  return dim_ok && (head_dim == 64 || head_dim == 128) && (g == 1 || g == 2 || g == 4) && rows_max <= kTileM;
 }
 
 int tick_upload(TickProgram* prog) {
@@ -717,11 +897,12 @@ void tick_free(TickProgram* prog) {
 }
 
 int tick_configure(int device) {
-  int n_stages, stage_bytes;
-  stage_plan(256, &n_stages, &stage_bytes);
-  size_t worst = tick_smem_bytes(n_stages, stage_bytes);
-  stage_plan(64, &n_stages, &stage_bytes);
-  worst = std::max(worst, tick_smem_bytes(n_stages, stage_bytes));
+  size_t worst = 0;
+  for (int bn : {16, 32, 64, 128}) {
+    int n_stages, stage_bytes, x_bytes;
+    stage_plan(bn, &n_stages, &stage_bytes, &x_bytes);
+    worst = std::max(worst, tick_smem_bytes(n_stages, stage_bytes));
+  }
   if (cudaFuncSetAttribute(tick_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)worst) != cudaSuccess) return 0;
   int per_sm = 0, sms = 0, coop = 0;
   if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, tick_kernel, kThreads, worst) != cudaSuccess) return 0;
@@ -740,11 +921,9 @@ cudaError_t tick_launch(const TickProgram& prog, const TickIo& io, float* partia
   a.partials = partials;
   a.barrier = barrier;
   a.err = err;
-  stage_plan(prog.max_bn, &a.n_stages, &a.stage_bytes);
-  a.acc_stride = prog.max_bn < 32 ? 32 : prog.max_bn;
-  a.n_acc = std::max(1, std::min(4, 512 / (2 * a.acc_stride)));
-  int cols = 2 * a.n_acc * a.acc_stride;
-  a.tmem_cols = cols <= 32 ? 32 : cols <= 64 ? 64 : cols <= 128 ? 128 : cols <= 256 ? 256 : 512;
+  stage_plan(prog.max_bn, &a.n_stages, &a.stage_bytes, &a.x_bytes);
+  a.w_ahead = 1 << 20;
+  if (const char* e = getenv("OMNI_TICK_WAHEAD")) a.w_ahead = atoi(e);
   a.io = io;
   cudaError_t e = cudaMemsetAsync(barrier, 0, sizeof(uint32_t), stream);
   if (e != cudaSuccess) return e;
