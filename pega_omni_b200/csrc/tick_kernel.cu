@@ -40,6 +40,10 @@ struct GroupBar {  // named barrier of one 128-thread worker group
   int id;
   __device__ __forceinline__ void sync() const { asm volatile("bar.sync %0, 128;" ::"r"(id) : "memory"); }
 };
+struct PairBar {  // named barrier of a two-warp attention team
+  int id;
+  __device__ __forceinline__ void sync() const { asm volatile("bar.sync %0, 64;" ::"r"(id) : "memory"); }
+};
 using WorkerSync = sampler::NamedSync<1, kWorkerThreads>;
 
 struct alignas(16) Control {
@@ -52,7 +56,7 @@ struct alignas(16) Control {
 };
 
 union WorkerScratch {
-  AttnShared<128, 4, 4> attn4[2];  // one per 128-thread group
+  AttnShared<128, 4, 2> attn2[4];  // one per two-warp team
   AttnShared<128, 4, 1> attn1[8];  // one per worker warp
   sampler::Shared sample;
 };
@@ -82,15 +86,14 @@ __device__ __forceinline__ uint32_t ld_acquire(const uint32_t* p) {
 }
 
 // All CTAs arrive, then wait until `target` arrivals have been counted. Returns false on timeout / error.
+// Called by one thread after a team barrier: the release on the counter is cumulative over the team's writes
+// ordered before it by that barrier, and the acquire that sees the last arrival orders every CTA's writes before
+// whatever the team does after its next barrier; no separate fence is needed on either side.
 __device__ bool grid_barrier(uint32_t* counter, uint32_t target, uint32_t* err) {
-  __threadfence();
   asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(counter) : "memory");
   const uint64_t start = sm100::global_timer_ns();
   for (uint32_t spins = 0;; ++spins) {
-    if (ld_acquire(counter) >= target) {
-      __threadfence();
-      return true;
-    }
+    if (ld_acquire(counter) >= target) return true;
     if ((spins & 127u) == 127u) {
       if (*reinterpret_cast<volatile uint32_t*>(err) != 0) return false;
       if (sm100::global_timer_ns() - start > sm100::kWaitLimitNs) {
@@ -365,7 +368,7 @@ __device__ __noinline__ void reduce_silu_rows(const Phase& ph, const float* part
 }
 
 // ---- rope + KV write + attention --------------------------------------------------------------------------------
-// A team of W warps per (sequence, kv head): four warps for the talker's paged KV (pages round-robin over the
+// A team of W warps per (sequence, kv head): two warps for the talker's paged KV (pages alternate between the
 // warps), one warp for the code predictor's single-page frames (so all eight worker warps of a CTA hold an item).
 
 // q/k of one head: RMSNorm over the head, the normalised value rounded to bf16 before the gain, half-rotation
@@ -493,10 +496,12 @@ __device__ __forceinline__ void rope_attn_dg(const Phase& ph, const TickIo& io, 
                                              int wtid, WorkerScratch& scratch, uint32_t* err) {
   const int hk = ph.i1, per = ph.i3;
   const int items = (ph.rows / per) * hk;
-  if (ph.i5) {  // paged: a 128-thread group per item
-    auto& sh = reinterpret_cast<AttnShared<D, G, 4>&>(scratch.attn4[wtid >> 7]);
-    for (int it = tm.group; it < items; it += tm.n_groups)
-      rope_attend_item<D, G, 4>(ph, io, partials, it / hk, it % hk, tm.gtid, sh, tm.bar, err);
+  if (ph.i5) {  // paged: a two-warp team per item, so one round covers 4 x (number of CTAs) items
+    const int team = wtid >> 6;
+    auto& sh = reinterpret_cast<AttnShared<D, G, 2>&>(scratch.attn2[team]);
+    const int first = team * (int)gridDim.x + (int)blockIdx.x, n_teams = 4 * (int)gridDim.x;
+    for (int it = first; it < items; it += n_teams)
+      rope_attend_item<D, G, 2>(ph, io, partials, it / hk, it % hk, wtid & 63, sh, PairBar{4 + team}, err);
   } else {  // one page per sequence: a warp per item
     auto& sh = reinterpret_cast<AttnShared<D, G, 1>&>(scratch.attn1[wtid >> 5]);
     const int wid = (int)blockIdx.x * (kWorkerThreads / 32) + (wtid >> 5), n_warps = (int)gridDim.x * (kWorkerThreads / 32);
