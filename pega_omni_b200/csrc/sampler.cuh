@@ -85,7 +85,14 @@ template <int THREADS, typename Sync>
 struct Team {
   static constexpr int PER = kVocabMax / THREADS;
   static constexpr int VPT = kVirtualThreads / THREADS;  // virtual threads per team thread
-  static_assert(PER % kVirtualPer == 0 && THREADS >= 32 && THREADS <= kVirtualThreads, "team size");
+  static_assert(PER % kVirtualPer == 0 && THREADS >= 128 && THREADS <= kVirtualThreads, "team size");
+  static_assert(32 % PER == 0, "a thread's logits share one word of the seen bitmap");
+
+  // The word of the sequence's seen bitmap that covers this thread's logits (0 when nothing is penalised).
+  static __device__ __forceinline__ uint32_t seen_word(const int32_t* slot, const Params& prm, int tid) {
+    const uint32_t* seen = reinterpret_cast<const uint32_t*>(slot + 16);
+    return prm.penalize && tid * PER < prm.vocab ? seen[tid * PER / 32] : 0u;
+  }
 
   static __device__ float team_max(float v, int tid, Shared& sh) {
     v = warp_fmax(v);
@@ -289,10 +296,11 @@ struct Team {
 
   // `talker_sample` (talker.cu:259-293) for one row. `load(i, j)` returns logit i = tid * PER + j as f32 (already rounded
   // to bf16 by the caller). slot: i32 last_frame[16] | u32 seen[seen_words] | u64 seed (8-byte aligned).
+  // `seen_bits` = seen_word() of this thread, read before the call (so callers can fetch it early).
   // Returns the token (identical in every team thread); thread 0 writes codes, the slot and the bitmap.
   template <typename Load>
   static __device__ int sample_row(Load load, const Params& prm, int frame, float uniform, int forced, int32_t* slot,
-                                   int32_t* code_out, int tid, Shared& sh) {
+                                   uint32_t seen_bits, int32_t* code_out, int tid, Shared& sh) {
     uint32_t* seen = reinterpret_cast<uint32_t*>(slot + 16);
     int token = forced;
     if (forced < 0) {
@@ -304,7 +312,7 @@ struct Team {
         float x = -INFINITY;
         if (i < prm.vocab) {
           x = load(i, j);
-          if (prm.penalize && (seen[i / 32] >> (i % 32) & 1u)) x = x > 0.f ? x / prm.penalty : x * prm.penalty;
+          if (seen_bits >> (i % 32) & 1u) x = x > 0.f ? x / prm.penalty : x * prm.penalty;
           const bool in_range = i >= prm.suppress_lo && i < prm.suppress_hi;
           if ((in_range && i != prm.exempt) || (i == prm.exempt && exempt_blocked)) x = -INFINITY;
         }

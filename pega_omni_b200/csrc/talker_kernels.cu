@@ -135,8 +135,10 @@ __global__ void __launch_bounds__(1024) sample_kernel(const bf16* __restrict__ l
   __shared__ sampler::Shared sh;
   const int s = blockIdx.x;
   const bf16* l = logits + (int64_t)s * prm.vocab;
+  int32_t* slot = slot_of(st, s);
   Team::sample_row([&](int i, int) { return __bfloat162float(l[i]); }, prm, frames[s], uniforms[s * kGroups + prm.group],
-                   force[s * kGroups + prm.group], slot_of(st, s), codes + s * kGroups + prm.group, threadIdx.x, sh);
+                   force[s * kGroups + prm.group], slot, Team::seen_word(slot, prm, threadIdx.x),
+                   codes + s * kGroups + prm.group, threadIdx.x, sh);
 }
 
 cudaError_t launch_sample(const bf16* logits, const SampleParams& p, const int32_t* frames, const float* uniforms,

@@ -122,6 +122,8 @@ struct omni_seq {
   bool live = false;
 };
 
+constexpr int kTraceMaxPhases = 1024;
+
 struct omni_talker {
   omni_talker_config cfg;
   int device = 0, sm_count = 148;
@@ -649,7 +651,8 @@ bool tick_usable(const omni_talker* m, int b) {
     return tick_supports(s.hidden, s.head_dim, s.q_heads, s.kv_heads, 2 * b) && s.inter % 64 == 0 && s.hidden % 64 == 0 &&
            (s.q_heads * s.head_dim) % 64 == 0;
   };
-  return ok(t) && ok(p);
+  // the draw phase reads the head's partial sums four columns at a time
+  return ok(t) && ok(p) && t.vocab % 4 == 0 && p.vocab % 4 == 0;
 }
 
 int run_tick_program(omni_talker* m, int program, int b) {
@@ -684,10 +687,13 @@ int run_tick_program(omni_talker* m, int program, int b) {
     m->trace_checked = true;
     if (const char* path = getenv("OMNI_TICK_TRACE")) m->trace_path = path;
   }
-  if (!m->trace_path.empty() && !m->trace) TRY(dev_alloc(m, &m->trace, 2 * 8192, true));
-  if (m->trace && m->tick_phases <= 8192) m->trace_program = &it->second;
+  if (!m->trace_path.empty() && !m->trace) TRY(dev_alloc(m, &m->trace, (size_t)4 * kTraceMaxPhases * m->tick_ctas, true));
+  if (m->trace && m->tick_phases <= kTraceMaxPhases) {
+    m->trace_program = &it->second;
+    CUDA_TRY(m, cudaMemsetAsync(m->trace, 0, (size_t)4 * kTraceMaxPhases * m->tick_ctas * 8, m->stream));
+  }
   LAUNCH(m, tick_launch(it->second, io, m->gemm_scratch.partials, m->tick_barrier, m->err, m->tick_ctas, m->stream,
-                        m->trace && m->tick_phases <= 8192 ? m->trace : nullptr));
+                        m->trace && m->tick_phases <= kTraceMaxPhases ? m->trace : nullptr));
   return OMNI_OK;
 }
 
@@ -803,19 +809,42 @@ size_t stage_graph_inputs(omni_talker* m, char* host, const std::vector<FrameRow
 }
 
 
-// Writes "index type N K tiles splits bn rows ns" for every phase of the last traced tick.
+// Writes one line per phase of the last traced tick: its shape, then (ns, relative to the median time at which the
+// CTAs saw the previous barrier complete) the median and the latest over CTAs of: first activation tile in shared
+// memory, first accumulator complete, own share done, barrier seen complete.
 void dump_trace(omni_talker* m) {
   if (!m->trace || !m->trace_program || m->trace_path.empty()) return;
   const TickProgram& prog = *m->trace_program;
-  std::vector<unsigned long long> t(2 * prog.phases.size());
+  const size_t G = (size_t)m->tick_ctas, P = prog.phases.size();
+  std::vector<unsigned long long> t(4 * G * P);
   if (cudaMemcpy(t.data(), m->trace, t.size() * 8, cudaMemcpyDeviceToHost) != cudaSuccess) return;
   FILE* f = fopen(m->trace_path.c_str(), "w");
   if (!f) return;
-  fprintf(f, "phase type N K tiles splits bn rows ns_since_previous ns_cta0_work\n");
-  for (size_t i = 0; i < prog.phases.size(); ++i) {
+  fprintf(f, "phase type N K tiles splits bn rows tile_n dur x_med x_max acc_med acc_max work_med work_max bar_med bar_max\n");
+  auto stat = [&](size_t p, int k, long long origin, long long* med, long long* mx) {
+    std::vector<long long> v;
+    for (size_t c = 0; c < G; ++c) {
+      const unsigned long long x = t[(p * G + c) * 4 + k];
+      if (x) v.push_back((long long)x - origin);
+    }
+    if (v.empty()) {
+      *med = *mx = 0;
+      return;
+    }
+    std::sort(v.begin(), v.end());
+    *med = v[v.size() / 2];
+    *mx = v.back();
+  };
+  long long origin = 0, unused;
+  stat(0, 3, 0, &origin, &unused);
+  for (size_t i = 1; i < P; ++i) {
     const Phase& ph = prog.phases[i];
-    fprintf(f, "%zu %d %d %d %d %d %d %d %lld %lld\n", i, ph.type, ph.N, ph.K, ph.tiles, ph.splits, ph.bn, ph.rows,
-            i == 0 ? 0ll : (long long)(t[2 * i + 1] - t[2 * i - 1]), i == 0 ? 0ll : (long long)(t[2 * i] - t[2 * i - 1]));
+    long long s[8];
+    for (int k = 0; k < 4; ++k) stat(i, k, origin, &s[2 * k], &s[2 * k + 1]);
+    fprintf(f, "%zu %d %d %d %d %d %d %d %d %lld", i, ph.type, ph.N, ph.K, ph.tiles, ph.splits, ph.bn, ph.rows, ph.tile_n, s[6]);
+    for (int k = 0; k < 8; ++k) fprintf(f, " %lld", s[k]);
+    fprintf(f, "\n");
+    origin += s[6];
   }
   fclose(f);
 }

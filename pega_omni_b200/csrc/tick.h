@@ -83,8 +83,9 @@ void tick_free(TickProgram* prog);
 // Raises the kernel's shared-memory limit and reports how many CTAs can be co-resident (0 on failure).
 int tick_configure(int device);
 // One cooperative launch of the whole program. `barrier` (one zeroed u32) is reset on the stream first.
-// `trace` (optional, two u64 per phase): CTA 0 records the global timer when its own share of the phase is done
-// and again when the phase's grid barrier has completed.
+// `trace` (optional, four u64 per (phase, CTA), phase-major): the global timer when the CTA's first activation tile
+// of the phase arrived, when its first accumulator was complete (both GEMM phases only), when its own share of
+// the phase was done, and when it saw the phase's grid barrier complete.
 cudaError_t tick_launch(const TickProgram& prog, const TickIo& io, float* partials, uint32_t* barrier, uint32_t* err,
                         int ctas, cudaStream_t stream, unsigned long long* trace = nullptr);
 

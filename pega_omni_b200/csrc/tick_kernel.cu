@@ -70,7 +70,7 @@ struct KernelArgs {
   uint32_t* err;
   int n_stages, stage_bytes, x_bytes;  // a stage is [X tile, x_bytes][W tile, kWBytes]
   int w_ahead;                         // phases the weight producer may run ahead of the grid barriers
-  unsigned long long* trace;           // optional: CTA 0 stamps the global timer after every phase's barrier
+  unsigned long long* trace;           // optional: four global-timer stamps per (phase, CTA), see tick_launch
   TickIo io;
 };
 
@@ -118,29 +118,51 @@ struct Partials {
   }
 };
 
-// N columns of one row at once: the split loop is outermost and unrolled so the loads of several splits are
-// independent and in flight together (one L2 round trip per batch instead of one per element).
-template <int N>
-__device__ __forceinline__ void reduce_cols(const Partials& pt, int m, const int (&cols)[N], float (&acc)[N]) {
-  uint32_t off[N];
+// NV groups of VEC consecutive columns of one row at once (a group never straddles a tile: cols[j] is a multiple
+// of VEC). The split loop is outermost and unrolled so the loads of several splits are independent and in flight
+// together: one L2 round trip per batch instead of one per element.
+template <int VEC>
+struct VecOf;
+template <>
+struct VecOf<1> { using T = float; };
+template <>
+struct VecOf<2> { using T = float2; };
+template <>
+struct VecOf<4> { using T = float4; };
+
+template <int NV, int VEC>
+__device__ __forceinline__ void reduce_vecs(const Partials& pt, int m, const int (&cols)[NV], float (&acc)[NV * VEC]) {
+  using V = typename VecOf<VEC>::T;
+  uint32_t off[NV];
 #pragma unroll
-  for (int j = 0; j < N; ++j) {
-    off[j] = pt.at(m, cols[j]);
-    acc[j] = 0.f;
-  }
+  for (int j = 0; j < NV; ++j) off[j] = pt.at(m, cols[j]);
+#pragma unroll
+  for (int i = 0; i < NV * VEC; ++i) acc[i] = 0.f;
   const float* base = pt.base;
-  constexpr int kBatch = N <= 4 ? 8 : N <= 8 ? 4 : 2;  // splits whose loads are issued before any is consumed
+  constexpr int kBatch = NV * VEC <= 4 ? 8 : NV * VEC <= 16 ? 4 : 2;  // splits whose loads are issued before any is consumed
   for (int s0 = 0; s0 < pt.splits; s0 += kBatch, base += kBatch * pt.split_stride) {
-    float f[kBatch][N];
+    V f[kBatch][NV];
 #pragma unroll
     for (int b = 0; b < kBatch; ++b)
 #pragma unroll
-      for (int j = 0; j < N; ++j) f[b][j] = s0 + b < pt.splits ? __ldcg(base + b * pt.split_stride + off[j]) : 0.f;
+      for (int j = 0; j < NV; ++j) {
+        if (s0 + b < pt.splits)
+          f[b][j] = __ldcg(reinterpret_cast<const V*>(base + b * pt.split_stride + off[j]));
+        else
+          f[b][j] = V{};  // adding 0 for a missing split leaves the sum unchanged
+      }
 #pragma unroll
-    for (int b = 0; b < kBatch; ++b)  // adding 0 for a missing split leaves the sum unchanged
+    for (int b = 0; b < kBatch; ++b)
 #pragma unroll
-      for (int j = 0; j < N; ++j) acc[j] += f[b][j];
+      for (int j = 0; j < NV; ++j)
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) acc[j * VEC + e] += reinterpret_cast<const float*>(&f[b][j])[e];
   }
+}
+
+template <int N>
+__device__ __forceinline__ void reduce_cols(const Partials& pt, int m, const int (&cols)[N], float (&acc)[N]) {
+  reduce_vecs<N, 1>(pt, m, cols, acc);
 }
 
 // The row-wise phases' access pattern: a 128-thread group owns a row; thread j owns, for t < NV, the VEC
@@ -229,15 +251,31 @@ struct Team {  // a 128-thread worker group
 // ---- row-wise phases: one 128-thread group per row of hidden size NV * VEC * 128 -----------------------------
 
 // res = v; x = bf16(v * rsqrt(mean(v^2) + eps) * gain)   (v already holds bf16-representable values)
+// This thread's columns of the norm gain, as raw bf16 (fetched before the row's sums are waited on).
 template <int NV, int VEC>
-__device__ __forceinline__ void norm_store(const float (&v)[NV * VEC], float ss, int dim, float eps, const bf16* gain,
-                                           bf16* res_row, bf16* out_row, const Team& tm) {
+struct Gain {
+  bf16 g[NV * VEC];
+  __device__ __forceinline__ Gain(const bf16* gain, int gtid) {
+#pragma unroll
+    for (int t = 0; t < NV; ++t) {
+      if constexpr (VEC == 4)
+        *reinterpret_cast<uint2*>(&g[t * 4]) = __ldg(reinterpret_cast<const uint2*>(gain + row_col<NV, VEC>(t, gtid)));
+      else
+        g[t] = gain[row_col<NV, VEC>(t, gtid)];
+    }
+  }
+};
+
+template <int NV, int VEC>
+__device__ __forceinline__ void norm_store(const float (&v)[NV * VEC], float ss, int dim, float eps,
+                                           const Gain<NV, VEC>& gain, bf16* res_row, bf16* out_row, const Team& tm) {
   const float r = rsqrtf(group_sum(ss, tm.gtid, tm.red, tm.bar) / dim + eps);
 #pragma unroll
   for (int t = 0; t < NV; ++t) {
     const int col = row_col<NV, VEC>(t, tm.gtid);
     float g[VEC], o[VEC];
-    ld_bf16<VEC>(gain + col, g);
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) g[e] = __bfloat162float(gain.g[t * VEC + e]);
 #pragma unroll
     for (int e = 0; e < VEC; ++e) o[e] = v[t * VEC + e] * r * g[e];
     if (res_row) st_bf16<VEC>(res_row + col, &v[t * VEC]);
@@ -249,6 +287,8 @@ template <int NV, int VEC>
 __device__ __noinline__ void embed_norm_rows(const Phase& ph, const TickIo& io, const Team& tm, uint32_t* err) {
   const int dim = ph.N;
   const bf16 *pad = (const bf16*)ph.src0, *codec_emb = (const bf16*)ph.src1, *p_emb = (const bf16*)ph.src2;
+  if (tm.group >= ph.rows) return;
+  const Gain<NV, VEC> gain((const bf16*)ph.src3, tm.gtid);
   for (int row = tm.group; row < ph.rows; row += tm.n_groups) {
     const int32_t* codes =
         reinterpret_cast<const int32_t*>(static_cast<const char*>(io.state) + (int64_t)io.lines[row] * io.stride);
@@ -277,7 +317,7 @@ __device__ __noinline__ void embed_norm_rows(const Phase& ph, const TickIo& io, 
       v[i] = bf16_round(v[i]);
       ss += v[i] * v[i];
     }
-    norm_store<NV, VEC>(v, ss, dim, ph.f0, (const bf16*)ph.src3, (bf16*)ph.dst0 + (int64_t)row * dim,
+    norm_store<NV, VEC>(v, ss, dim, ph.f0, gain, (bf16*)ph.dst0 + (int64_t)row * dim,
                         (bf16*)ph.dst1 + (int64_t)row * dim, tm);
   }
 }
@@ -287,6 +327,8 @@ __device__ __noinline__ void reduce_norm_rows(const Phase& ph, const float* part
   const int dim = ph.N;
   const bf16* bias = (const bf16*)ph.src0;
   const Partials pt(partials, ph);
+  if (tm.group >= ph.rows) return;
+  const Gain<NV, VEC> gain((const bf16*)ph.src3, tm.gtid);
   for (int row = tm.group; row < ph.rows; row += tm.n_groups) {
     float v[NV * VEC], ss = 0.f;
     reduce_row<NV, VEC>(pt, row, tm.gtid, v);
@@ -302,7 +344,7 @@ __device__ __noinline__ void reduce_norm_rows(const Phase& ph, const float* part
         ss += a * a;
       }
     }
-    norm_store<NV, VEC>(v, ss, dim, ph.f0, (const bf16*)ph.src3, (bf16*)ph.dst0 + (int64_t)row * dim,
+    norm_store<NV, VEC>(v, ss, dim, ph.f0, gain, (bf16*)ph.dst0 + (int64_t)row * dim,
                         (bf16*)ph.dst1 + (int64_t)row * dim, tm);
   }
 }
@@ -312,6 +354,8 @@ __device__ __noinline__ void add_norm_rows(const Phase& ph, const float* partial
   const int dim = ph.N, every = ph.i0, which = ph.i1;
   bf16 *res = (bf16*)ph.dst0, *out = (bf16*)ph.dst1;
   const Partials pt(partials, ph);
+  if (tm.group >= ph.rows) return;
+  const Gain<NV, VEC> gain((const bf16*)ph.src3, tm.gtid);
   for (int row = tm.group; row < ph.rows; row += tm.n_groups) {
     float v[NV * VEC], old[NV * VEC], ss = 0.f;
 #pragma unroll
@@ -323,7 +367,7 @@ __device__ __noinline__ void add_norm_rows(const Phase& ph, const float* partial
       ss += v[i] * v[i];
     }
     const bool keep = row % every == which;
-    norm_store<NV, VEC>(v, ss, dim, ph.f0, (const bf16*)ph.src3, res + (int64_t)row * dim,
+    norm_store<NV, VEC>(v, ss, dim, ph.f0, gain, res + (int64_t)row * dim,
                         keep ? out + (int64_t)(row / every) * dim : nullptr, tm);
   }
 }
@@ -371,11 +415,24 @@ __device__ __noinline__ void reduce_silu_rows(const Phase& ph, const float* part
 // A team of W warps per (sequence, kv head): two warps for the talker's paged KV (pages alternate between the
 // warps), one warp for the code predictor's single-page frames (so all eight worker warps of a CTA hold an item).
 
-// q/k of one head: RMSNorm over the head, the normalised value rounded to bf16 before the gain, half-rotation
-// rotary embedding (qwen3.cu:66-107). lo/hi: this lane's E elements of each half.
+// Rotation angles of this lane's E element pairs at `pos`: inv_freq = theta^(-2i/D) (qwen3.cu:94-98). The same for
+// every head of a row, so computed once per row.
 template <int D>
-__device__ __forceinline__ void rope_head(float (&lo)[D / 64], float (&hi)[D / 64], const bf16* w, int lane, int pos,
-                                          float eps, float theta) {
+__device__ __forceinline__ void rope_angles(int lane, int pos, float theta, float (&cs)[D / 64], float (&sn)[D / 64]) {
+#pragma unroll
+  for (int e = 0; e < D / 64; ++e) {
+    const int i = lane * (D / 64) + e;
+    const float inv_freq = 1.f / powf(theta, (float)(2 * i) / D);
+    sincosf((float)pos * inv_freq, &sn[e], &cs[e]);
+  }
+}
+
+// q/k of one head: RMSNorm over the head, the normalised value rounded to bf16 before the gain, half-rotation
+// rotary embedding (qwen3.cu:66-107). lo/hi: this lane's E elements of each half; wl/wh: the gains of those elements.
+template <int D>
+__device__ __forceinline__ void rope_head(float (&lo)[D / 64], float (&hi)[D / 64], const float (&wl)[D / 64],
+                                          const float (&wh)[D / 64], const float (&cs)[D / 64],
+                                          const float (&sn)[D / 64], float eps) {
   constexpr int E = D / 64;
   float ss = 0.f;
 #pragma unroll
@@ -383,14 +440,10 @@ __device__ __forceinline__ void rope_head(float (&lo)[D / 64], float (&hi)[D / 6
   const float rn = rsqrtf(warp_add(ss) / D + eps);
 #pragma unroll
   for (int e = 0; e < E; ++e) {
-    const int i = lane * E + e;
-    const float a = bf16_round(lo[e] * rn) * __bfloat162float(w[i]);
-    const float b = bf16_round(hi[e] * rn) * __bfloat162float(w[D / 2 + i]);
-    const float inv_freq = 1.f / powf(theta, (float)(2 * i) / D);
-    float sn, cs;
-    sincosf((float)pos * inv_freq, &sn, &cs);
-    lo[e] = bf16_round(a * cs - b * sn);
-    hi[e] = bf16_round(b * cs + a * sn);
+    const float a = bf16_round(lo[e] * rn) * wl[e];
+    const float b = bf16_round(hi[e] * rn) * wh[e];
+    lo[e] = bf16_round(a * cs[e] - b * sn[e]);
+    hi[e] = bf16_round(b * cs[e] + a * sn[e]);
   }
 }
 
@@ -405,9 +458,17 @@ __device__ __noinline__ void rope_attend_item(const Phase& ph, const TickIo& io,
   const int lane = tid & 31, warp = tid >> 5;
   const float scale = rsqrtf((float)D);
   const Partials pt(partials, ph);
+  float qwl[E], qwh[E], kwl[E], kwh[E];  // this lane's q/k norm gains, fetched before any partial sum is waited on
+#pragma unroll
+  for (int e = 0; e < E; ++e) {
+    qwl[e] = __bfloat162float(q_norm[lane * E + e]), qwh[e] = __bfloat162float(q_norm[D / 2 + lane * E + e]);
+    kwl[e] = __bfloat162float(k_norm[lane * E + e]), kwh[e] = __bfloat162float(k_norm[D / 2 + lane * E + e]);
+  }
   for (int r = 0; r < per; ++r) {
     const int n = seq * per + r;
     const int pos = paged ? io.d_pos[n] : base + r;
+    float cs[E], sn[E];
+    rope_angles<D>(lane, pos, ph.f1, cs, sn);
     const int64_t slot = paged ? io.d_slot[n] : (int64_t)seq * 16 + pos;
     int64_t page = slot >> 4;
     const int tok = (int)(slot & 15);
@@ -418,27 +479,27 @@ __device__ __noinline__ void rope_attend_item(const Phase& ph, const TickIo& io,
     bf16* kdst = kv + kv_offset<D>(page, hk, kh, 0, tok);
     bf16* vdst = kv + kv_offset<D>(page, hk, kh, 1, tok);
     if constexpr (W == 1) {
-      // one warp does the G query heads, the key head and the value head; all their partial sums in one batch
-      int cols[(G + 1) * 2 * E + VE];
-      float val[(G + 1) * 2 * E + VE];
+      // one warp does the G query heads, the key head and the value head; all their partial sums in one batch,
+      // E consecutive columns per load (a lane owns value dims lane * VE .. + VE)
+      constexpr int NG = (G + 1) * 2 + VE / E;
+      int cols[NG];
+      float val[NG * E];
 #pragma unroll
       for (int j = 0; j <= G; ++j) {
         const int col0 = (j < G ? kh * G + j : hq + kh) * D;
-#pragma unroll
-        for (int e = 0; e < E; ++e) {
-          cols[j * 2 * E + e] = col0 + lane * E + e;
-          cols[j * 2 * E + E + e] = col0 + D / 2 + lane * E + e;
-        }
+        cols[j * 2] = col0 + lane * E;
+        cols[j * 2 + 1] = col0 + D / 2 + lane * E;
       }
 #pragma unroll
-      for (int e = 0; e < VE; ++e) cols[(G + 1) * 2 * E + e] = (hq + hk + kh) * D + lane + 32 * e;
-      reduce_cols(pt, n, cols, val);
+      for (int g = 0; g < VE / E; ++g) cols[(G + 1) * 2 + g] = (hq + hk + kh) * D + lane * VE + g * E;
+      reduce_vecs<NG, E>(pt, n, cols, val);
 #pragma unroll
       for (int j = 0; j <= G; ++j) {
         float lo[E], hi[E];
 #pragma unroll
         for (int e = 0; e < E; ++e) lo[e] = bf16_round(val[j * 2 * E + e]), hi[e] = bf16_round(val[j * 2 * E + E + e]);
-        rope_head<D>(lo, hi, j < G ? q_norm : k_norm, lane, pos, ph.f0, ph.f1);
+        if (j < G) rope_head<D>(lo, hi, qwl, qwh, cs, sn, ph.f0);
+        else rope_head<D>(lo, hi, kwl, kwh, cs, sn, ph.f0);
 #pragma unroll
         for (int e = 0; e < E; ++e) {
           const int i = lane * E + e;
@@ -450,29 +511,26 @@ __device__ __noinline__ void rope_attend_item(const Phase& ph, const TickIo& io,
         }
       }
 #pragma unroll
-      for (int e = 0; e < VE; ++e) vdst[lane + 32 * e] = __float2bfloat16(val[(G + 1) * 2 * E + e]);
+      for (int e = 0; e < VE; ++e) vdst[lane * VE + e] = __float2bfloat16(val[(G + 1) * 2 * E + e]);
     } else {
       for (int job = warp; job < G + 2; job += W) {
         if (job == G + 1) {  // value: plain copy
-          int cols[VE];
+          int cols[1] = {(hq + hk + kh) * D + lane * VE};
           float val[VE];
+          reduce_vecs<1, VE>(pt, n, cols, val);
 #pragma unroll
-          for (int e = 0; e < VE; ++e) cols[e] = (hq + hk + kh) * D + lane + 32 * e;
-          reduce_cols(pt, n, cols, val);
-#pragma unroll
-          for (int e = 0; e < VE; ++e) vdst[lane + 32 * e] = __float2bfloat16(val[e]);
+          for (int e = 0; e < VE; ++e) vdst[lane * VE + e] = __float2bfloat16(val[e]);
           continue;
         }
         const bool is_q = job < G;
         const int col0 = (is_q ? kh * G + job : hq + kh) * D;
-        int cols[2 * E];
+        int cols[2] = {col0 + lane * E, col0 + D / 2 + lane * E};
         float val[2 * E], lo[E], hi[E];
-#pragma unroll
-        for (int e = 0; e < E; ++e) cols[e] = col0 + lane * E + e, cols[E + e] = col0 + D / 2 + lane * E + e;
-        reduce_cols(pt, n, cols, val);
+        reduce_vecs<2, E>(pt, n, cols, val);
 #pragma unroll
         for (int e = 0; e < E; ++e) lo[e] = bf16_round(val[e]), hi[e] = bf16_round(val[E + e]);
-        rope_head<D>(lo, hi, is_q ? q_norm : k_norm, lane, pos, ph.f0, ph.f1);
+        if (is_q) rope_head<D>(lo, hi, qwl, qwh, cs, sn, ph.f0);
+        else rope_head<D>(lo, hi, kwl, kwh, cs, sn, ph.f0);
 #pragma unroll
         for (int e = 0; e < E; ++e) {
           const int i = lane * E + e;
@@ -546,13 +604,18 @@ __device__ __noinline__ void phase_sample(const Phase& ph, const TickIo& io, con
   prm.seen_words = io.seen_words;
   for (int row = first_item(ph); row < ph.rows; row += g) {
     int32_t* slot = reinterpret_cast<int32_t*>(static_cast<char*>(io.state) + (int64_t)io.lines[row] * io.stride);
+    // everything the draw needs besides the logits is fetched before the partial sums are waited on
+    const int forced = io.force[row * 16 + prm.group], frame = io.frames[row];
+    const float uniform = io.uniforms[row * 16 + prm.group];
+    const uint32_t seen_bits = Team::seen_word(slot, prm, wtid);
     // this thread's PER consecutive logits: reduce the head's split-K partials, round, publish
     float mine[Team::PER];
     {
-      int cols[Team::PER];
+      // four columns per load; the head's vocabulary is a multiple of 4 and tiles are padded to a full tile_n
+      int cols[Team::PER / 4];
 #pragma unroll
-      for (int j = 0; j < Team::PER; ++j) cols[j] = min(wtid * Team::PER + j, prm.vocab - 1);
-      reduce_cols(Partials(partials, ph), row, cols, mine);
+      for (int j = 0; j < Team::PER / 4; ++j) cols[j] = min(wtid * Team::PER + 4 * j, prm.vocab - 4);
+      reduce_vecs<Team::PER / 4, 4>(Partials(partials, ph), row, cols, mine);
 #pragma unroll
       for (int j = 0; j < Team::PER; ++j) {
         const bf16 b = __float2bfloat16(mine[j]);
@@ -560,9 +623,7 @@ __device__ __noinline__ void phase_sample(const Phase& ph, const TickIo& io, con
         if (wtid * Team::PER + j < prm.vocab) logits_out[(int64_t)row * ph.i0 + wtid * Team::PER + j] = b;
       }
     }
-    const int forced = io.force[row * 16 + prm.group];
-    const int token = Team::sample_row([&](int, int j) { return mine[j]; }, prm, io.frames[row],
-                                       io.uniforms[row * 16 + prm.group], forced, slot,
+    const int token = Team::sample_row([&](int, int j) { return mine[j]; }, prm, frame, uniform, forced, slot, seen_bits,
                                        io.codes + row * 16 + prm.group, wtid, sh);
     // the next predictor pass reads the embedding of the code just drawn
     const int dim = ph.i9;
@@ -677,6 +738,8 @@ __global__ void __launch_bounds__(kThreads, 1) tick_kernel(const __grid_constant
         const int items = ph.tiles * ph.splits, nkb = ph.K / kTileK;
         const CUtensorMap* map = a.maps + ph.wmap;
         if (first_item(ph) >= items) continue;
+        prefetch_tensormap(map);  // this producer runs ahead of the phase: both descriptors are warm when needed
+        prefetch_tensormap(a.maps + ph.xmap);
         {  // weights do not depend on activations, but how far ahead of the barriers they are fetched is bounded
           const uint64_t start = global_timer_ns();
           while (ctl.released < p - a.w_ahead && !ctl.abort) {
@@ -722,6 +785,7 @@ __global__ void __launch_bounds__(kThreads, 1) tick_kernel(const __grid_constant
           }
         }
         asm volatile("fence.proxy.async;" ::: "memory");  // generic-proxy writes of other CTAs -> async-proxy reads
+        if (a.trace) a.trace[((size_t)p * G + blockIdx.x) * 4] = global_timer_ns();  // TEMP
         const CUtensorMap* map = a.maps + ph.xmap;
         const uint32_t xbytes = (uint32_t)ph.bn * kTileK * 2;
         for (int it = first_item(ph); it < items && !ctl.abort; it += G) {
@@ -768,6 +832,7 @@ __global__ void __launch_bounds__(kThreads, 1) tick_kernel(const __grid_constant
               break;
             }
             tc_fence_after_sync();
+            if (a.trace && kb == kb0 && it == first_item(ph)) a.trace[((size_t)p * G + blockIdx.x) * 4 + 1] = global_timer_ns();
             const uint64_t adesc = kmajor_sw128_desc(x_addr(stage)), bdesc = kmajor_sw128_desc(w_addr(stage));
 #pragma unroll
             for (int k = 0; k < kTileK / 16; ++k)
@@ -804,6 +869,7 @@ __global__ void __launch_bounds__(kThreads, 1) tick_kernel(const __grid_constant
             if (!ok) ctl.abort = 1;
             full_par[buf] ^= 1u;
             tc_fence_after_sync();
+            
             if (ok) gemm_epilogue(ph, a.partials, it % ph.tiles, it / ph.tiles, tmem_base + (uint32_t)(buf * kTileN), wwarp, lane);
             tc_fence_before_sync();
             WorkerSync::sync();
@@ -825,10 +891,10 @@ __global__ void __launch_bounds__(kThreads, 1) tick_kernel(const __grid_constant
       // (fences are cumulative), then everyone waits for thread 0 to see all CTAs arrive
       WorkerSync::sync();
       if (wtid == 0) {
-        if (a.trace && blockIdx.x == 0) a.trace[2 * p] = global_timer_ns();  // CTA 0's own work is done
+        if (a.trace) a.trace[((size_t)p * G + blockIdx.x) * 4 + 2] = global_timer_ns();  // this CTA's share is done
         if (!ctl.abort && !grid_barrier(a.barrier, (uint32_t)(p + 1) * (uint32_t)G, a.err)) ctl.abort = 1;
         ctl.released = p + 1;
-        if (a.trace && blockIdx.x == 0) a.trace[2 * p + 1] = global_timer_ns();  // every CTA has arrived
+        if (a.trace) a.trace[((size_t)p * G + blockIdx.x) * 4 + 3] = global_timer_ns();  // every CTA has arrived
       }
       WorkerSync::sync();
     }
