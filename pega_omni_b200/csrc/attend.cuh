@@ -23,6 +23,10 @@ struct AttnShared {
   float ms[W][G], ls[W][G];
   float os[W][G][D];
 };
+template <int D, int G>
+struct AttnShared<D, G, 1> {  // a one-warp team has nothing to merge
+  float qs[G][D];
+};
 
 struct WarpSync {  // team barrier of a one-warp team
   __device__ __forceinline__ void sync() const { __syncwarp(); }
@@ -132,6 +136,15 @@ __device__ __forceinline__ void attend_pages(AttnShared<D, G, W>& sh, const bf16
       }
     }
   }
+  if constexpr (W == 1) {
+    // the merge below would multiply by exp(0) = 1: the same quotient, straight from the registers
+#pragma unroll
+    for (int g = 0; g < G; ++g)
+#pragma unroll
+      for (int d = 0; d < PV; ++d) out[(int64_t)g * D + lane * PV + d] = __float2bfloat16(acc[g][d] / l[g]);
+    team.sync();
+    return;
+  } else {
 #pragma unroll
   for (int g = 0; g < G; ++g) {
     if (lane == 0) {
@@ -157,6 +170,7 @@ __device__ __forceinline__ void attend_pages(AttnShared<D, G, W>& sh, const bf16
     out[(int64_t)g * D + d] = __float2bfloat16(num / den);
   }
   team.sync();
+  }
 }
 
 }  // namespace omni

@@ -94,7 +94,9 @@ Tiling choose_tiling(int N, int K, int ctas, bool swiglu) {
   Tiling best;
   const int nkb = K / 64;
   for (int direct = swiglu ? 1 : 0; direct >= 0; --direct) {
-    for (int tn : {256, 128, 64}) {
+    for (int tn : {256, 128, 96, 64}) {
+      // 96 rows (48 gate + 48 up channels) only for the fused SwiGLU epilogue: partial tiles are a power of two wide
+      if (tn == 96 && (!direct || N % 96 != 0)) continue;
       const int tiles = (N + tn - 1) / tn;
       const int smax = direct ? 1 : std::min(8, nkb);
       for (int S = 1; S <= smax; ++S) {
@@ -514,6 +516,7 @@ struct TickBuilder {
       t.tile_n = 2 * granule;
       if (t.swiglu_direct) t.splits = 1;
     }
+    if (swiglu && t.tile_n == 96) t.swiglu_direct = true, t.splits = 1;  // no partial tiles of that width
     ph.N = N;
     ph.K = K;
     ph.bn = pick_bn(rows);

@@ -40,7 +40,7 @@ enum NextInput : int32_t { kNextNone = 0, kNextHiddenAndCode = 1, kNextCode = 2 
 //  Sample:     rows, tiles, splits, bn, N = vocab; dst0 logits out, i0 ldl (row stride of logits out, elements);
 //              sampling constants in f0..f3 / i1..i7; next-input in i8, src0 table, src1 hidden, dst1 p_in, i9 dim
 struct alignas(16) Phase {
-  int32_t type, rows, bn, N, K, tiles, splits, wmap, xmap, mode, cta_offset, tile_n;  // tile_n: weight rows per GEMM tile (64, 128 or 256)
+  int32_t type, rows, bn, N, K, tiles, splits, wmap, xmap, mode, cta_offset, tile_n;  // tile_n: weight rows per GEMM tile (64, 128 or 256; 96 with the SwiGLU epilogue)
   int32_t i0, i1, i2, i3, i4, i5, i6, i7, i8, i9, i10, i11;
   float f0, f1, f2, f3;
   const void *src0, *src1, *src2, *src3;

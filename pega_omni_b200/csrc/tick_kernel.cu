@@ -29,11 +29,11 @@ namespace {
 constexpr int kThreads = 352;  // 3 control warps + 8 worker warps: 186 registers per thread
 constexpr int kWorkerThreads = 256;
 constexpr int kFirstWorkerWarp = 3;
-constexpr int kMaxStages = 8;
+constexpr int kMaxStages = 16;
 constexpr int kTileN = 256;  // weight rows per tile (the MMA N dimension)
 constexpr int kTileK = 64;   // K elements per stage: one 128-byte swizzle row
 constexpr int kTileM = 128;  // the MMA M dimension: activation rows, zero/garbage padded
-constexpr int kWBytes = kTileN * kTileK * 2;
+constexpr int kMaxRingBytes = 192 * 1024;  // most shared memory the tile ring may take
 constexpr int kGroupThreads = 128;
 
 struct GroupBar {  // named barrier of one 128-thread worker group
@@ -68,7 +68,8 @@ struct KernelArgs {
   float* partials;
   uint32_t* barrier;
   uint32_t* err;
-  int n_stages, stage_bytes, x_bytes;  // a stage is [X tile, x_bytes][W tile, kWBytes]
+  int ring_bytes;                      // shared memory of the tile ring (a multiple of 1 KB): the rest of the SM's
+                                       // array stays L1, which the row-wise phases live on
   int w_ahead;                         // phases the weight producer may run ahead of the grid barriers
   unsigned long long* trace;           // optional: four global-timer stamps per (phase, CTA), see tick_launch
   TickIo io;
@@ -78,6 +79,32 @@ __device__ __forceinline__ int first_item(const Phase& ph) {
   const int g = gridDim.x;
   return (int)((blockIdx.x + g - ph.cta_offset % g) % g);
 }
+
+// The tile ring of a GEMM phase: stages of [activation k-block: bn rows][weight k-block: tile_n rows], each row 128
+// bytes, as many as fit (at most kMaxStages). The three pipeline roles of a CTA walk the stages in the same order and
+// restart at stage 0 whenever the geometry changes; a stage's mbarrier parities are tracked per stage (one bit each),
+// so a barrier that one geometry never reaches stays consistent for the next.
+struct Ring {
+  uint32_t x_bytes = 0, stage_bytes = 0;
+  int n = 0, stage = 0;
+  uint32_t par = 0;  // bit s: parity of stage s's next wait
+  // Returns true when the geometry changed (the caller may have to drain the old one first).
+  __device__ __forceinline__ bool enter(const Phase& ph, int ring_bytes) {
+    const uint32_t xb = ((uint32_t)ph.bn * kTileK * 2 + 1023u) & ~1023u, sb = xb + (uint32_t)ph.tile_n * kTileK * 2;
+    if (xb == x_bytes && sb == stage_bytes) return false;
+    x_bytes = xb, stage_bytes = sb;
+    n = min(kMaxStages, (int)((uint32_t)ring_bytes / sb));
+    stage = 0;
+    return true;
+  }
+  __device__ __forceinline__ uint32_t x_off() const { return (uint32_t)stage * stage_bytes; }
+  __device__ __forceinline__ uint32_t w_off() const { return (uint32_t)stage * stage_bytes + x_bytes; }
+  __device__ __forceinline__ uint32_t parity() const { return par >> stage & 1u; }
+  __device__ __forceinline__ void advance() {
+    par ^= 1u << stage;
+    if (++stage == n) stage = 0;
+  }
+};
 
 __device__ __forceinline__ uint32_t ld_acquire(const uint32_t* p) {
   uint32_t v;
@@ -671,9 +698,10 @@ __device__ __noinline__ void gemm_epilogue(const Phase& ph, float* partials, int
   } else {
     // SwiGLU: columns [0, tn/2) are gate channels tile*tn/2.., columns [tn/2, tn) the matching up channels
     bf16* act = (bf16*)ph.dst0;
+    // (16-column chunks alternate between the two warps of a quadrant: hc is 32, 48, 64 or 128)
     const int inter = ph.i0, hc = tn / 2;
 #pragma unroll 1
-    for (int c0 = half * (hc / 2); c0 < (half + 1) * (hc / 2); c0 += 16) {
+    for (int c0 = half * 16; c0 < hc; c0 += 32) {
       float g[16], u[16];
       sm100::tmem_ld16(lane_addr + c0, g);
       sm100::tmem_ld16(lane_addr + hc + c0, u);
@@ -698,9 +726,8 @@ __global__ void __launch_bounds__(kThreads, 1) tick_kernel(const __grid_constant
   const uint32_t raw = smem_addr(tick_smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
   unsigned char* base_ptr = tick_smem_raw + (base - raw);
-  Control& ctl = *reinterpret_cast<Control*>(base_ptr + (size_t)a.n_stages * a.stage_bytes);
-  WorkerScratch& scratch =
-      *reinterpret_cast<WorkerScratch*>(base_ptr + (size_t)a.n_stages * a.stage_bytes + ((sizeof(Control) + 127) & ~127));
+  Control& ctl = *reinterpret_cast<Control*>(base_ptr + a.ring_bytes);
+  WorkerScratch& scratch = *reinterpret_cast<WorkerScratch*>(base_ptr + a.ring_bytes + ((sizeof(Control) + 127) & ~127));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int G = gridDim.x;
   constexpr uint32_t kTmemCols = 512;  // two accumulators of 256 f32 columns
@@ -725,13 +752,10 @@ __global__ void __launch_bounds__(kThreads, 1) tick_kernel(const __grid_constant
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = ctl.tmem_base;
-  auto x_addr = [&](int s) { return base + (uint32_t)(s * a.stage_bytes); };
-  auto w_addr = [&](int s) { return base + (uint32_t)(s * a.stage_bytes + a.x_bytes); };
 
   if (warp == 0) {
     if (lane == 0) {  // ---- weight producer ----
-      int stage = 0;
-      uint32_t par = 0;
+      Ring ring;
       for (int p = 0; p < a.n_phases && !ctl.abort; ++p) {
         const Phase& ph = a.phases[p];
         if (ph.type != kPhGemm) continue;
@@ -750,32 +774,38 @@ __global__ void __launch_bounds__(kThreads, 1) tick_kernel(const __grid_constant
             }
           }
         }
+        const int old_n = ring.n;
+        if (ring.enter(ph, a.ring_bytes)) {
+          // new stage boundaries: every tile of the old geometry must have been consumed before one is overwritten
+          for (int s = 0; s < old_n && !ctl.abort; ++s)
+            if (!mbar_wait(smem_addr(&ctl.empty[s]), (ring.par >> s & 1u) ^ 1u, a.err)) ctl.abort = 1;
+        }
         for (int it = first_item(ph); it < items && !ctl.abort; it += G) {
           const int tile = it % ph.tiles, split = it / ph.tiles;
           const int kb0 = (int)((int64_t)nkb * split / ph.splits), kb1 = (int)((int64_t)nkb * (split + 1) / ph.splits);
           for (int kb = kb0; kb < kb1; ++kb) {
-            if (!mbar_wait(smem_addr(&ctl.empty[stage]), par ^ 1u, a.err)) {
+            if (!mbar_wait(smem_addr(&ctl.empty[ring.stage]), ring.parity() ^ 1u, a.err)) {
               ctl.abort = 1;
               break;
             }
-            const uint32_t bar = smem_addr(&ctl.full_w[stage]);
+            const uint32_t bar = smem_addr(&ctl.full_w[ring.stage]);
             mbar_expect_tx(bar, (uint32_t)ph.tile_n * kTileK * 2);
-            tma_load_2d(w_addr(stage), map, bar, kb * kTileK, tile * ph.tile_n, kEvictFirst);
-            if (++stage == a.n_stages) stage = 0, par ^= 1u;
+            tma_load_2d(base + ring.w_off(), map, bar, kb * kTileK, tile * ph.tile_n, kEvictFirst);
+            ring.advance();
           }
         }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {  // ---- activation producer ----
-      int stage = 0;
-      uint32_t par = 0;
+      Ring ring;
       for (int p = 0; p < a.n_phases && !ctl.abort; ++p) {
         const Phase& ph = a.phases[p];
         if (ph.type != kPhGemm) continue;
         const int items = ph.tiles * ph.splits, nkb = ph.K / kTileK;
         if (first_item(ph) >= items) continue;
         // the rows this phase multiplies were written by earlier phases: wait until those are complete everywhere
+        // (by then this CTA's earlier GEMM phases are over too, so a change of stage geometry needs no further wait)
         const uint64_t start = global_timer_ns();
         while (ctl.released < p && !ctl.abort) {
           __nanosleep(40);
@@ -785,35 +815,38 @@ __global__ void __launch_bounds__(kThreads, 1) tick_kernel(const __grid_constant
           }
         }
         asm volatile("fence.proxy.async;" ::: "memory");  // generic-proxy writes of other CTAs -> async-proxy reads
-        if (a.trace) a.trace[((size_t)p * G + blockIdx.x) * 4] = global_timer_ns();  // TEMP
+        ring.enter(ph, a.ring_bytes);
         const CUtensorMap* map = a.maps + ph.xmap;
         const uint32_t xbytes = (uint32_t)ph.bn * kTileK * 2;
         for (int it = first_item(ph); it < items && !ctl.abort; it += G) {
           const int split = it / ph.tiles;
           const int kb0 = (int)((int64_t)nkb * split / ph.splits), kb1 = (int)((int64_t)nkb * (split + 1) / ph.splits);
           for (int kb = kb0; kb < kb1; ++kb) {
-            if (!mbar_wait(smem_addr(&ctl.empty[stage]), par ^ 1u, a.err)) {
+            if (!mbar_wait(smem_addr(&ctl.empty[ring.stage]), ring.parity() ^ 1u, a.err)) {
               ctl.abort = 1;
               break;
             }
-            const uint32_t bar = smem_addr(&ctl.full_x[stage]);
+            const uint32_t bar = smem_addr(&ctl.full_x[ring.stage]);
             mbar_expect_tx(bar, xbytes);
-            tma_load_2d(x_addr(stage), map, bar, kb * kTileK, 0, kEvictLast);
-            if (++stage == a.n_stages) stage = 0, par ^= 1u;
+            tma_load_2d(base + ring.x_off(), map, bar, kb * kTileK, 0, kEvictLast);
+            ring.advance();
           }
         }
       }
     }
   } else if (warp == 2) {
     if (lane == 0) {  // ---- MMA issuer ----
-      int stage = 0, buf = 0;
-      uint32_t par = 0, empty_par[2] = {0, 0};
-      // A = the activation tile (rows beyond the phase's bn read whatever follows in the stage; those TMEM
-      // lanes are never read back), B = 256 weight rows, both K-major with the 128-byte swizzle
+      Ring ring;
+      int buf = 0;
+      uint32_t empty_par[2] = {0, 0};
+      // A = the activation tile (rows beyond the phase's bn read whatever follows in the ring; those TMEM
+      // lanes are never read back), B = tile_n weight rows, both K-major with the 128-byte swizzle
       for (int p = 0; p < a.n_phases && !ctl.abort; ++p) {
         const Phase& ph = a.phases[p];
         if (ph.type != kPhGemm) continue;
         const int items = ph.tiles * ph.splits, nkb = ph.K / kTileK;
+        if (first_item(ph) >= items) continue;
+        ring.enter(ph, a.ring_bytes);
         const uint32_t idesc = idesc_bf16_f32(kTileM, ph.tile_n);
         for (int it = first_item(ph); it < items && !ctl.abort; it += G) {
           const int split = it / ph.tiles;
@@ -826,19 +859,19 @@ __global__ void __launch_bounds__(kThreads, 1) tick_kernel(const __grid_constant
           tc_fence_after_sync();
           const uint32_t tmem_d = tmem_base + (uint32_t)(buf * kTileN);
           for (int kb = kb0; kb < kb1; ++kb) {
-            if (!mbar_wait(smem_addr(&ctl.full_w[stage]), par, a.err) ||
-                !mbar_wait(smem_addr(&ctl.full_x[stage]), par, a.err)) {
+            if (!mbar_wait(smem_addr(&ctl.full_w[ring.stage]), ring.parity(), a.err) ||
+                !mbar_wait(smem_addr(&ctl.full_x[ring.stage]), ring.parity(), a.err)) {
               ctl.abort = 1;
               break;
             }
             tc_fence_after_sync();
-            if (a.trace && kb == kb0 && it == first_item(ph)) a.trace[((size_t)p * G + blockIdx.x) * 4 + 1] = global_timer_ns();
-            const uint64_t adesc = kmajor_sw128_desc(x_addr(stage)), bdesc = kmajor_sw128_desc(w_addr(stage));
+            if (a.trace && kb == kb0 && it == first_item(ph)) a.trace[((size_t)p * G + blockIdx.x) * 4] = global_timer_ns();
+            const uint64_t adesc = kmajor_sw128_desc(base + ring.x_off()), bdesc = kmajor_sw128_desc(base + ring.w_off());
 #pragma unroll
             for (int k = 0; k < kTileK / 16; ++k)
               mma_bf16(tmem_d, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2), idesc, (kb > kb0 || k > 0) ? 1u : 0u);
-            mma_commit(smem_addr(&ctl.empty[stage]));
-            if (++stage == a.n_stages) stage = 0, par ^= 1u;
+            mma_commit(smem_addr(&ctl.empty[ring.stage]));
+            ring.advance();
           }
           if (ctl.abort) break;
           mma_commit(smem_addr(&ctl.acc_full[buf]));
@@ -869,7 +902,7 @@ __global__ void __launch_bounds__(kThreads, 1) tick_kernel(const __grid_constant
             if (!ok) ctl.abort = 1;
             full_par[buf] ^= 1u;
             tc_fence_after_sync();
-            
+            if (a.trace && wtid == 0 && it == first_item(ph)) a.trace[((size_t)p * G + blockIdx.x) * 4 + 1] = global_timer_ns();
             if (ok) gemm_epilogue(ph, a.partials, it % ph.tiles, it / ph.tiles, tmem_base + (uint32_t)(buf * kTileN), wwarp, lane);
             tc_fence_before_sync();
             WorkerSync::sync();
@@ -910,15 +943,22 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
-void stage_plan(int max_bn, int* n_stages, int* stage_bytes, int* x_bytes) {
-  *x_bytes = (max_bn * kTileK * 2 + 1023) & ~1023;
-  *stage_bytes = *x_bytes + kWBytes;
-  *n_stages = std::min(kMaxStages, (176 * 1024) / *stage_bytes);
+static_assert(1024 + kMaxRingBytes + ((sizeof(Control) + 127) & ~127) + sizeof(WorkerScratch) <= 227 * 1024,
+              "ring + control + scratch exceed the shared memory of an SM");
+
+size_t tick_smem_bytes(int ring_bytes) {
+  // 1 KB of slack to align the ring to the swizzle atom; an activation descriptor spans 128 rows whatever bn is,
+  // so the last stage's reads run into the control block and scratch that follow the ring (and are never used)
+  return 1024 + (size_t)ring_bytes + ((sizeof(Control) + 127) & ~127) + sizeof(WorkerScratch);
 }
 
-size_t tick_smem_bytes(int n_stages, int stage_bytes) {
-  // the last stage's activation descriptor spans 128 rows whatever bn is: keep the tail inside the allocation
-  return 1024 + (size_t)n_stages * stage_bytes + ((sizeof(Control) + 127) & ~127) + sizeof(WorkerScratch);
+// The ring's size. 104 KB by default: with the control block and scratch the CTA then fits the 132 KB shared-memory
+// carve-out and 124 KB of the SM's array stay L1, which measured faster than a deeper ring with less L1.
+// OMNI_TICK_RING_KB overrides it (a tuning aid, 48 .. 192).
+int tick_ring_bytes() {
+  int kb = 104;
+  if (const char* e = getenv("OMNI_TICK_RING_KB")) kb = atoi(e);
+  return std::min(std::max(kb, 48), kMaxRingBytes / 1024) * 1024;
 }
 
 }  // namespace
@@ -968,15 +1008,10 @@ void tick_free(TickProgram* prog) {
 }
 
 int tick_configure(int device) {
-  size_t worst = 0;
-  for (int bn : {16, 32, 64, 128}) {
-    int n_stages, stage_bytes, x_bytes;
-    stage_plan(bn, &n_stages, &stage_bytes, &x_bytes);
-    worst = std::max(worst, tick_smem_bytes(n_stages, stage_bytes));
-  }
-  if (cudaFuncSetAttribute(tick_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)worst) != cudaSuccess) return 0;
+  const size_t smem = tick_smem_bytes(kMaxRingBytes);
+  if (cudaFuncSetAttribute(tick_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return 0;
   int per_sm = 0, sms = 0, coop = 0;
-  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, tick_kernel, kThreads, worst) != cudaSuccess) return 0;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, tick_kernel, kThreads, smem) != cudaSuccess) return 0;
   if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) return 0;
   if (cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, device) != cudaSuccess || !coop) return 0;
   return per_sm >= 1 ? sms : 0;
@@ -992,7 +1027,7 @@ cudaError_t tick_launch(const TickProgram& prog, const TickIo& io, float* partia
   a.partials = partials;
   a.barrier = barrier;
   a.err = err;
-  stage_plan(prog.max_bn, &a.n_stages, &a.stage_bytes, &a.x_bytes);
+  a.ring_bytes = tick_ring_bytes();
   a.w_ahead = 1 << 20;
   if (const char* e = getenv("OMNI_TICK_WAHEAD")) a.w_ahead = atoi(e);
   a.io = io;
@@ -1000,7 +1035,7 @@ cudaError_t tick_launch(const TickProgram& prog, const TickIo& io, float* partia
   if (e != cudaSuccess) return e;
   void* args[] = {&a};
   return cudaLaunchCooperativeKernel((const void*)tick_kernel, dim3(ctas), dim3(kThreads), args,
-                                     tick_smem_bytes(a.n_stages, a.stage_bytes), stream);
+                                     tick_smem_bytes(a.ring_bytes), stream);
 }
 
 }  // namespace omni
