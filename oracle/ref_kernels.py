@@ -1,7 +1,8 @@
 """The reference's own CUDA kernels, compiled for sm_100a and replayed on the GPU (TEST INFRASTRUCTURE).
 
-build(): when the reference checkout is present, compiles `crates/omni-qwen3/kernels/qwen3.cu` and
-`crates/omni-qwen3-tts/kernels/talker.cu` where they lie (include path `crates/omni-kern/kernels`) into
+build(): when the reference checkout is present, compiles `crates/omni-qwen3/kernels/qwen3.cu`,
+`crates/omni-qwen3-tts/kernels/talker.cu` and `crates/omni-personaplex/kernels/lm.cu` where they lie (include path
+`crates/omni-kern/kernels`) into
 `oracle/_ref/*.cubin` with the reference's own flags except the architecture
 (crates/omni-qwen3/build.rs:17-27: `nvcc -cubin -O3 -std=c++17`). Sources are never copied.
 
@@ -25,6 +26,7 @@ REFERENCE = Path(os.environ.get("OMNI_REFERENCE", "/root/reference"))
 SOURCES = {
     "qwen3": "crates/omni-qwen3/kernels/qwen3.cu",
     "talker": "crates/omni-qwen3-tts/kernels/talker.cu",
+    "lm": "crates/omni-personaplex/kernels/lm.cu",
 }
 
 
@@ -42,7 +44,7 @@ def build(force: bool = False) -> bool:
         if not force and dst.exists() and dst.stat().st_mtime >= src.stat().st_mtime:
             continue
         cmd = ["nvcc", "-cubin", "-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a",
-               "-I", str(REFERENCE / "crates/omni-kern/kernels"), "-o", str(dst), str(src)]
+               "-I", str(REFERENCE / "crates/omni-kern/kernels"), "-I", str(src.parent), "-o", str(dst), str(src)]
         res = subprocess.run(cmd, capture_output=True, text=True)
         if res.returncode != 0:
             raise RuntimeError(f"nvcc failed on {rel}:\n{res.stderr}")

@@ -1,4 +1,4 @@
-"""ctypes binding of ``libomni_b200.so`` (declarations of include/omni_b200.h and omni_b200_ops.h).
+"""ctypes binding of ``libomni_b200.so`` (declarations of include/omni_b200.h, omni_b200_ops.h and omni_b200_duplex.h).
 
 Loading fails loudly when the library is missing: there is no fallback path.
 """
@@ -48,6 +48,21 @@ class Stats(C.Structure):
                 ("kv_bytes", C.c_int64)]
 
 
+class DuplexCfg(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in ("dim", "layers", "heads", "hidden", "context", "dep_dim", "dep_layers",
+                                         "dep_heads", "dep_hidden", "text_vocab", "card")] + \
+               [("norm_eps", C.c_float), ("rope_period", C.c_float), ("text_temperature", C.c_float),
+                ("text_top_k", C.c_int32), ("audio_temperature", C.c_float), ("audio_top_k", C.c_int32),
+                ("max_sessions", C.c_int32), ("max_prefill", C.c_int32), ("voice_rows", C.c_int32)]
+
+
+class DuplexStep(C.Structure):
+    _fields_ = [("force", C.c_int32 * 9), ("force_caller", C.c_int32 * 8), ("caller", C.c_int32 * 8),
+                ("seed", C.c_uint64)]
+
+
+DUPLEX_TEXT_LOGITS, DUPLEX_AUDIO_LOGITS, DUPLEX_ROWS, DUPLEX_DRAWN = 0, 1, 2, 3
+
 P = C.POINTER
 VP = C.c_void_p
 I32 = C.c_int32
@@ -84,6 +99,16 @@ SYMBOLS = {
     "omni_op_sample": (I32, [VP, VP, I32, C.c_float, I32, C.c_float, C.c_float, I32, I32, I32, I32, VP, VP, VP, VP,
                              VP, C.c_int64, I32, I32, VP, I32, I32]),
     "omni_op_gemm_noalloc": (I32, [VP, I32, I32, VP, I32, VP, I32, I32, VP, I32, VP, C.c_char_p, C.c_size_t]),
+    "omni_duplex_create": (I32, [P(DuplexCfg), P(Tensor), I32, I32, P(VP)]),
+    "omni_duplex_destroy": (None, [VP]),
+    "omni_duplex_last_error": (C.c_char_p, [VP]),
+    "omni_duplex_open": (I32, [VP, P(VP)]),
+    "omni_duplex_close": (I32, [VP, VP]),
+    "omni_duplex_position": (I32, [VP, P(I32), P(C.c_int64)]),
+    "omni_duplex_start": (I32, [VP, I32, P(VP), P(I32), P(I32), P(I32), P(I32), P(I32)]),
+    "omni_duplex_tick": (I32, [VP, I32, P(VP), P(DuplexStep), P(I32)]),
+    "omni_duplex_read": (I32, [VP, I32, I32, VP, C.c_size_t]),
+    "omni_duplex_stats": (I32, [VP, P(C.c_float), P(I32)]),
 }
 
 _lib = None
