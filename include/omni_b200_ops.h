@@ -66,6 +66,49 @@ int32_t omni_op_sample(omni_ops* ctx, const void* logits, int32_t vocab, float t
                        void* state, const int32_t* lines, int64_t stride, int32_t penalize, int32_t philox,
                        int32_t* codes, int32_t group, int32_t rows);
 
+/* ---- duplex (PersonaPlex) kernels, one call each: crates/omni-personaplex/kernels/lm.cu --------------------------
+ * Helium KV layout of this library (one buffer per layer, FP8 E4M3 + one f32 scale per (token, head)):
+ *   kv[page][head][ K: 16 tokens x 128 B | V: 16 tokens x 128 B | K scales: 16 x f32 | V scales: 16 x f32 ]
+ * a token's slot is page * 16 + ring position % 16. */
+
+/* `lm_norm` (lm.cu:86-92) when y is NULL: out = x * (alpha * rsqrt(eps + mean(x^2))).
+ * `lm_add_norm` (lm.cu:95-106) otherwise: x = bf16(x + y), out = norm(x); out NULL: `lm_add` (lm.cu:109-120). */
+int32_t omni_op_lm_norm(omni_ops* ctx, const void* y, void* x, const void* alpha, void* out, int32_t rows,
+                        int32_t dim, float eps);
+
+/* `lm_embed_prompt` (lm.cu:47-59) without voices: out[r] = sum of the embeddings of ids[r][0..17), every add rounded
+ * to bf16, audio streams first, -1 = no token. text_emb [text_rows, dim], audio_emb [16 * card_rows, dim]. */
+int32_t omni_op_lm_embed(omni_ops* ctx, const int32_t* ids, const void* text_emb, int32_t text_rows,
+                         const void* audio_emb, int32_t card_rows, void* out, int32_t rows, int32_t dim);
+
+/* `lm_rope` + `lm_attend` (lm.cu:129-290): rows of [q | k | v] (heads of 128): interleaved rotary embedding, K and V
+ * quantised to E4M3 into slot[n], attention of row n (session seq[n], or n when seq is NULL) over the first
+ * min(pos[n] + 1, context) ring positions of its pages. q is rotated in place. */
+int32_t omni_op_lm_rope_attend(omni_ops* ctx, void* qkv, void* kv, int32_t kv_pages, const int32_t* pos,
+                               const int32_t* slot, const int32_t* seq, const int32_t* indptr, const int32_t* pages,
+                               int32_t rows, int32_t heads, float coef, float scale, int32_t context, void* out);
+
+/* `lm_dep_embed_norm` (lm.cu:301-313) then `lm_dep_kv_attend` is a separate call below.
+ * x = bf16(projected[s][k] + table[drawn[s][k]]), xn = norm(x). */
+int32_t omni_op_lm_dep_embed_norm(omni_ops* ctx, const void* projected, int32_t k, const void* table,
+                                  int32_t table_rows, const int32_t* drawn, const void* alpha, void* x, void* xn,
+                                  int32_t rows, int32_t dim, float eps);
+
+/* `lm_dep_kv_attend` (lm.cu:319-366): step's K and V into ws ([rows][8][K | V][heads * 64]), causal attention over
+ * steps 0..step. */
+int32_t omni_op_lm_dep_kv_attend(omni_ops* ctx, const void* qkv, void* ws, int32_t step, void* out, int32_t rows,
+                                 int32_t heads, float scale);
+
+/* `lm_sample` (lm.cu:423-537): Gumbel-max over the top-k into drawn[s][col]; force[s][col] >= 0 is taken. */
+int32_t omni_op_lm_sample(omni_ops* ctx, const void* logits, int32_t vocab, int64_t ld, float temperature,
+                          int32_t top_k, const int32_t* force, const int32_t* seeds, int32_t col, int32_t* drawn,
+                          int32_t rows);
+
+/* `lm_init` (lm.cu:576-581) when init is not NULL, then `lm_advance` (lm.cu:546-573) when drawn is not NULL. */
+int32_t omni_op_lm_advance(omni_ops* ctx, void* state, const int32_t* lines, int64_t stride, const int32_t* init,
+                           const int32_t* drawn, const int32_t* caller, const int32_t* force_caller,
+                           int32_t* emitted, int32_t rows);
+
 /* The tensor-core GEMM of omni_op_gemm for callers that cannot allocate device memory. It has no counterpart in the
  * reference. Two kinds of caller are meant: a serving process that handed every free byte of HBM to its KV pool at
  * start-up, where a later cudaMalloc simply fails; and an engine thread in the middle of a live tick, where

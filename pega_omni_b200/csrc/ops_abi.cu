@@ -7,6 +7,7 @@
 #include "../../include/omni_b200.h"
 #include "../../include/omni_b200_ops.h"
 #include "gemm.h"
+#include "duplex.h"
 #include "kernels.h"
 
 using namespace omni;
@@ -184,6 +185,70 @@ int32_t omni_op_sample(omni_ops* c, const void* logits, int32_t vocab, float tem
   p.seen_words = (vocab + 31) / 32;
   OPS_CUDA(c, launch_sample((const bf16*)logits, p, frames, uniforms, force, SlotState{state, lines, stride}, codes,
                             rows, c->stream));
+  return OMNI_OK;
+}
+
+int32_t omni_op_lm_norm(omni_ops* c, const void* y, void* x, const void* alpha, void* out, int32_t rows, int32_t dim,
+                        float eps) {
+  if (!c || !x) return OMNI_ERR_INVALID;
+  if (y)
+    OPS_CUDA(c, launch_lm_add_norm((const bf16*)y, (bf16*)x, (const bf16*)alpha, (bf16*)out, rows, dim, eps, c->stream));
+  else
+    OPS_CUDA(c, launch_lm_norm((const bf16*)x, (const bf16*)alpha, (bf16*)out, rows, dim, eps, c->stream));
+  return OMNI_OK;
+}
+
+int32_t omni_op_lm_embed(omni_ops* c, const int32_t* ids, const void* text_emb, int32_t text_rows,
+                         const void* audio_emb, int32_t card_rows, void* out, int32_t rows, int32_t dim) {
+  if (!c || !ids || !out) return OMNI_ERR_INVALID;
+  const DuplexTables t{(const bf16*)text_emb, (const bf16*)audio_emb, text_rows, card_rows};
+  OPS_CUDA(c, launch_lm_embed_ids(ids, nullptr, nullptr, 0, t, (bf16*)out, rows, dim, c->err, c->stream));
+  return OMNI_OK;
+}
+
+int32_t omni_op_lm_rope_attend(omni_ops* c, void* qkv, void* kv, int32_t kv_pages, const int32_t* pos,
+                               const int32_t* slot, const int32_t* seq, const int32_t* indptr, const int32_t* pages,
+                               int32_t rows, int32_t heads, float coef, float scale, int32_t context, void* out) {
+  if (!c || !qkv || !kv || !pos || !slot || !indptr || !pages || !out) return OMNI_ERR_INVALID;
+  OPS_CUDA(c, launch_lm_rope_kv((bf16*)qkv, pos, slot, kv, rows, heads, coef, kv_pages, c->err, c->stream));
+  OPS_CUDA(c, launch_lm_attend((const bf16*)qkv, kv, pos, seq, indptr, pages, (bf16*)out, rows, heads, scale, context,
+                               kv_pages, c->err, c->stream));
+  return OMNI_OK;
+}
+
+int32_t omni_op_lm_dep_embed_norm(omni_ops* c, const void* projected, int32_t k, const void* table, int32_t table_rows,
+                                  const int32_t* drawn, const void* alpha, void* x, void* xn, int32_t rows, int32_t dim,
+                                  float eps) {
+  if (!c || k < 0 || k >= kDepSteps) return OMNI_ERR_INVALID;
+  OPS_CUDA(c, launch_lm_dep_embed_norm((const bf16*)projected, k, (const bf16*)table, table_rows, drawn,
+                                       (const bf16*)alpha, (bf16*)x, (bf16*)xn, rows, dim, eps, c->err, c->stream));
+  return OMNI_OK;
+}
+
+int32_t omni_op_lm_dep_kv_attend(omni_ops* c, const void* qkv, void* ws, int32_t step, void* out, int32_t rows,
+                                 int32_t heads, float scale) {
+  if (!c) return OMNI_ERR_INVALID;
+  OPS_CUDA(c, launch_lm_dep_kv_attend((const bf16*)qkv, (bf16*)ws, step, (bf16*)out, rows, heads, scale, c->stream));
+  return OMNI_OK;
+}
+
+int32_t omni_op_lm_sample(omni_ops* c, const void* logits, int32_t vocab, int64_t ld, float temperature, int32_t top_k,
+                          const int32_t* force, const int32_t* seeds, int32_t col, int32_t* drawn, int32_t rows) {
+  if (!c || !logits || !force || !seeds || !drawn) return OMNI_ERR_INVALID;
+  OPS_CUDA(c, launch_lm_sample((const bf16*)logits, vocab, ld, temperature, top_k, force, seeds, col, drawn, rows,
+                               c->stream));
+  return OMNI_OK;
+}
+
+int32_t omni_op_lm_advance(omni_ops* c, void* state, const int32_t* lines, int64_t stride, const int32_t* init,
+                           const int32_t* drawn, const int32_t* caller, const int32_t* force_caller, int32_t* emitted,
+                           int32_t rows) {
+  if (!c || !state || !lines) return OMNI_ERR_INVALID;
+  if (init) OPS_CUDA(c, launch_lm_init(state, lines, stride, init, rows, c->stream));
+  if (drawn) {
+    if (!caller || !force_caller || !emitted) return OMNI_ERR_INVALID;
+    OPS_CUDA(c, launch_lm_advance(state, lines, stride, drawn, caller, force_caller, emitted, rows, c->stream));
+  }
   return OMNI_OK;
 }
 

@@ -99,6 +99,13 @@ SYMBOLS = {
     "omni_op_sample": (I32, [VP, VP, I32, C.c_float, I32, C.c_float, C.c_float, I32, I32, I32, I32, VP, VP, VP, VP,
                              VP, C.c_int64, I32, I32, VP, I32, I32]),
     "omni_op_gemm_noalloc": (I32, [VP, I32, I32, VP, I32, VP, I32, I32, VP, I32, VP, C.c_char_p, C.c_size_t]),
+    "omni_op_lm_norm": (I32, [VP, VP, VP, VP, VP, I32, I32, C.c_float]),
+    "omni_op_lm_embed": (I32, [VP, VP, VP, I32, VP, I32, VP, I32, I32]),
+    "omni_op_lm_rope_attend": (I32, [VP, VP, VP, I32, VP, VP, VP, VP, VP, I32, I32, C.c_float, C.c_float, I32, VP]),
+    "omni_op_lm_dep_embed_norm": (I32, [VP, VP, I32, VP, I32, VP, VP, VP, VP, I32, I32, C.c_float]),
+    "omni_op_lm_dep_kv_attend": (I32, [VP, VP, VP, I32, VP, I32, I32, C.c_float]),
+    "omni_op_lm_sample": (I32, [VP, VP, I32, C.c_int64, C.c_float, I32, VP, VP, I32, VP, I32]),
+    "omni_op_lm_advance": (I32, [VP, VP, VP, C.c_int64, VP, VP, VP, VP, VP, I32]),
     "omni_duplex_create": (I32, [P(DuplexCfg), P(Tensor), I32, I32, P(VP)]),
     "omni_duplex_destroy": (None, [VP]),
     "omni_duplex_last_error": (C.c_char_p, [VP]),

@@ -83,6 +83,41 @@ class Ops:
                                              group, rows))
 
 
+    # ---- duplex (PersonaPlex) kernels ----
+    def lm_norm(self, x, alpha, out, eps, y=None):
+        rows, dim = x.shape
+        self._check(self._lib.omni_op_lm_norm(self._h, _p(y), _p(x), _p(alpha), _p(out), rows, dim, eps))
+
+    def lm_embed(self, ids, text_emb, audio_emb, out):
+        rows, dim = out.shape
+        self._check(self._lib.omni_op_lm_embed(self._h, _p(ids), _p(text_emb), text_emb.shape[0], _p(audio_emb),
+                                               audio_emb.shape[0] // 16, _p(out), rows, dim))
+
+    def lm_rope_attend(self, qkv, kv, kv_pages, pos, slot, seq, indptr, pages, heads, coef, scale, context, out):
+        self._check(self._lib.omni_op_lm_rope_attend(self._h, _p(qkv), _p(kv), kv_pages, _p(pos), _p(slot), _p(seq),
+                                                     _p(indptr), _p(pages), qkv.shape[0], heads, coef, scale, context,
+                                                     _p(out)))
+
+    def lm_dep_embed_norm(self, projected, k, table, drawn, alpha, x, xn, eps):
+        rows, dim = x.shape
+        self._check(self._lib.omni_op_lm_dep_embed_norm(self._h, _p(projected), k, _p(table), table.shape[0],
+                                                        _p(drawn), _p(alpha), _p(x), _p(xn), rows, dim, eps))
+
+    def lm_dep_kv_attend(self, qkv, ws, step, out, heads, scale):
+        self._check(self._lib.omni_op_lm_dep_kv_attend(self._h, _p(qkv), _p(ws), step, _p(out), qkv.shape[0], heads,
+                                                       scale))
+
+    def lm_sample(self, logits, temperature, top_k, force, seeds, col, drawn):
+        rows, vocab = logits.shape
+        self._check(self._lib.omni_op_lm_sample(self._h, _p(logits), vocab, logits.stride(0), temperature, top_k,
+                                                _p(force), _p(seeds), col, _p(drawn), rows))
+
+    def lm_advance(self, state, lines, stride, rows, init=None, drawn=None, caller=None, force_caller=None,
+                   emitted=None):
+        self._check(self._lib.omni_op_lm_advance(self._h, _p(state), _p(lines), stride, _p(init), _p(drawn),
+                                                 _p(caller), _p(force_caller), _p(emitted), rows))
+
+
 def gemm_noalloc(w, x, y, splits=0, bias=None, epilogue=0, stream=None):
     """`omni_op_gemm_noalloc`: the tensor-core GEMM with its split-K scratch inside the library image, for callers
     that cannot allocate device memory (no context object, no cudaMalloc). Waits for the result; raises OpsError
