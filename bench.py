@@ -188,6 +188,78 @@ def run_reference(args, rank):
     print(json.dumps(line), flush=True)
 
 
+def run_duplex(args, rank, world, local):
+    """The PersonaPlex-7B tick (Helium 32 x 4096 + depformer 8 x 6 x 1024) at `--sessions` sessions per GPU: W warm-up
+    ticks, K timed ticks through `Model.tick` (host staging and read-back inside), CUDA-event device time per tick from
+    the library. Per-op launches, no CUDA graph yet."""
+    import dataclasses
+    import torch
+    import torch.distributed as dist
+    from pega_omni_b200.duplex import PRESETS, Model, Prompt, Step, random_checkpoint
+    W, K, n = max(3, args.warmup), args.steps, args.sessions
+    c = dataclasses.replace(PRESETS["personaplex-7b"], context=args.context)
+    ck = random_checkpoint(c, seed=0, device=f"cuda:{local}", head_std=0.05)
+    model = Model.load(local, ck, c, max_sessions=n, max_prefill=max(n * 4, 256))
+    del ck
+    torch.cuda.empty_cache()
+    rng = np.random.default_rng(100 + rank)
+    sessions = [model.open() for _ in range(n)]
+    plen = 4  # short prompts: the tick's cost is weights + ring KV, and the ring fills as ticks run
+    for i in range(0, n, 32):
+        part = sessions[i:i + 32]
+        prompts = []
+        for _ in part:
+            rows = rng.integers(0, c.card, (plen, 17)).astype(np.int32)
+            rows[:, 0] = rng.integers(0, c.text_vocab, plen)
+            prompts.append(Prompt(rows, [int(v) for v in rows[-1]], [int(v) for v in rng.integers(0, c.card, 7)]))
+        model.start(list(zip(part, prompts)))
+
+    def steps_for(t):
+        return [Step(caller=[int(v) for v in rng.integers(0, c.card, 8)], seed=(t << 20) | i) for i in range(n)]
+
+    for t in range(W):
+        model.tick(list(zip(sessions, steps_for(t))))
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    dev_ms, launches = [], 0
+    t0 = time.perf_counter()
+    with ClockSampler(local) as clocks:
+        for t in range(K):
+            model.tick(list(zip(sessions, steps_for(W + t))))
+            ms, launches = model.stats()
+            dev_ms.append(ms)
+    torch.cuda.synchronize()
+    wall = time.perf_counter() - t0
+    t_wall = torch.tensor([wall], device="cuda", dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t_wall, op=dist.ReduceOp.MAX)
+    if rank == 0:
+        peak, peak_kind = measured_peaks()
+        mean_len = plen + W + (K - 1) / 2 + 1
+        kv_bytes = n * min(mean_len, c.context) * c.layers * (2 * c.heads * 128 + 2 * c.heads * 4)
+        tick_bytes = c.tick_weight_bytes() + kv_bytes
+        tick_s = float(np.mean(dev_ms)) * 1e-3
+        print(json.dumps({
+            "metric": "PersonaPlex tick ms (device) at %d sessions per GPU" % n, "value": float(np.mean(dev_ms)),
+            "unit": "ms", "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": 1e3 * float(t_wall.item()) / K,
+            "higher_is_better": False, "scaling": "weak", "vs_baseline": None, "dtype": "bf16 (FP8 E4M3 ring KV)",
+            "data": "synthetic",
+            "config": {"workload": "configs[3]: PersonaPlex-7B shapes (Helium 32L d4096 32 heads hidden 11264; depformer "
+                                   "8 steps x 6L d1024), random bf16 weights", "sessions_per_gpu": n,
+                       "context": c.context, "positions": [plen + W, plen + W + K - 1],
+                       "engine": "per-op launches (no CUDA graph, no persistent kernel yet)"},
+            "tick_p50_ms": float(np.percentile(dev_ms, 50)), "tick_p99_ms": float(np.percentile(dev_ms, 99)),
+            "frames_per_s": n * world * K / float(t_wall.item()),
+            "gpu_launches": int(launches * K), "launches_per_tick": int(launches), "clocks": clocks.summary(),
+            "roofline": {"bound": "hbm", "kernel": "whole tick (%d launches)" % launches,
+                         "achieved": tick_bytes / tick_s / 1e9, "peak": peak, "unit": "GB/s",
+                         "frac": tick_bytes / tick_s / 1e9 / peak, "peak_source": f"of {peak_kind}", "traffic": None},
+            "reference_published": "15.0 ms p50 / 15.9 ms p99 at 128 sessions on GB300, Mimi codec included "
+                                   "(docs/personaplex.md:105-111 of the reference)"}))
+    model.close()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -200,6 +272,9 @@ def main():
     ap.add_argument("--no-graphs", action="store_true")
     ap.add_argument("--no-replay", action="store_true", help="skip timing the reference's kernels on this GPU")
     ap.add_argument("--per-op", action="store_true", help="one kernel per op (CUDA graph) instead of the tick kernel")
+    ap.add_argument("--workload", default="talker", choices=["talker", "duplex"],
+                    help="talker: the headline Qwen3-TTS tick (default); duplex: the PersonaPlex-7B tick (configs[3])")
+    ap.add_argument("--context", type=int, default=3000, help="duplex: KV ring length")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -216,6 +291,10 @@ def main():
     torch.cuda.set_device(local)
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+
+    if args.workload == "duplex":
+        run_duplex(args, rank, world, local)
+        return
 
     from pega_omni_b200 import replicas
     from pega_omni_b200.config import presets

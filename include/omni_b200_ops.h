@@ -109,6 +109,36 @@ int32_t omni_op_lm_advance(omni_ops* ctx, void* state, const int32_t* lines, int
                            const int32_t* drawn, const int32_t* caller, const int32_t* force_caller,
                            int32_t* emitted, int32_t rows);
 
+/* ---- Higgs-style speech model glue: crates/omni-higgs-audio/kernels/higgs.cu, src/delay.rs ---------------------- */
+
+/* `higgs_frame_embed` (higgs.cu:24-37): out[s] = bf16(f32 sum over the 8 codebooks of table[b * vocab + code_b]),
+ * codes = the first 8 words of the sequence's state slot (state + lines[s] * stride). */
+int32_t omni_op_higgs_frame_embed(omni_ops* ctx, void* state, const int32_t* lines, int64_t stride, const void* table,
+                                  void* out, int32_t rows, int32_t dim, int32_t vocab);
+
+/* `higgs_sample` (higgs.cu:186-208): eight independent draws per row over logits [rows, 8, vocab] against
+ * uniforms [rows, 8]; force [rows, 8] >= 0 is taken (the delay pattern arrives here); codes [rows, 8] and the slot. */
+int32_t omni_op_higgs_sample(omni_ops* ctx, const void* logits, int32_t vocab, float temperature, int32_t top_k,
+                             const float* uniforms, const int32_t* force, void* state, const int32_t* lines,
+                             int64_t stride, int32_t* codes, int32_t rows);
+
+/* `Delay` (crates/omni-higgs-audio/src/delay.rs:19-46), host only: which codebooks the next step does not draw (they
+ * read OMNI_HIGGS_BOC) and when generation ends. Zero-initialise for a new run. */
+#define OMNI_HIGGS_BOOKS 8
+#define OMNI_HIGGS_BOC 1024
+#define OMNI_HIGGS_EOC 1025
+typedef struct omni_higgs_delay {
+  int32_t steps;
+  int32_t countdown; /* 0: none running; otherwise steps left + 1 */
+  int32_t done;
+} omni_higgs_delay;
+/* `Delay::forced_from` (delay.rs:27-29): the first codebook the next step does not draw. */
+int32_t omni_higgs_delay_forced_from(const omni_higgs_delay* d);
+/* `Delay::advance` (delay.rs:33-46): takes the step's codebook 0 draw; 1 when generation has ended. */
+int32_t omni_higgs_delay_advance(omni_higgs_delay* d, int32_t first);
+/* `undelay` (delay.rs:50-54): frames [max(n_rows - 7, 0), 8] from delayed rows [n_rows, 8]; returns the frame count. */
+int32_t omni_higgs_undelay(const int32_t* rows, int32_t n_rows, int32_t* frames);
+
 /* The tensor-core GEMM of omni_op_gemm for callers that cannot allocate device memory. It has no counterpart in the
  * reference. Two kinds of caller are meant: a serving process that handed every free byte of HBM to its KV pool at
  * start-up, where a later cudaMalloc simply fails; and an engine thread in the middle of a live tick, where

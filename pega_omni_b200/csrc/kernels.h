@@ -87,4 +87,12 @@ struct SampleParams {
 cudaError_t launch_sample(const bf16* logits, const SampleParams& p, const int32_t* frames, const float* uniforms,
                           const int32_t* force, SlotState st, int32_t* codes, int rows, cudaStream_t s);
 
+// out[s] = bf16(sum over the 8 codebooks of table[b * vocab + code_b]) from the slot's last frame (i32 codes[8]).
+cudaError_t launch_higgs_frame_embed(SlotState st, const bf16* table, bf16* out, int rows, int dim, int vocab,
+                                     uint32_t* err, cudaStream_t s);
+// A block per (row, codebook) over logits [rows, 8, vocab]: temperature, top-k with ties, draw against
+// uniforms[row][b]; force[row][b] >= 0 is taken; writes codes[row][b] and word b of the row's slot.
+cudaError_t launch_higgs_sample(const bf16* logits, int vocab, float temperature, int top_k, const float* uniforms,
+                                const int32_t* force, SlotState st, int32_t* codes, int rows, cudaStream_t s);
+
 }  // namespace omni

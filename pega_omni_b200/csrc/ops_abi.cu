@@ -1,5 +1,6 @@
 // Operator-level C ABI (include/omni_b200_ops.h): each kernel as a plain call
 // over caller-owned device buffers.
+#include <algorithm>
 #include <cstdarg>
 #include <cstdio>
 #include <string>
@@ -250,6 +251,50 @@ int32_t omni_op_lm_advance(omni_ops* c, void* state, const int32_t* lines, int64
     OPS_CUDA(c, launch_lm_advance(state, lines, stride, drawn, caller, force_caller, emitted, rows, c->stream));
   }
   return OMNI_OK;
+}
+
+int32_t omni_op_higgs_frame_embed(omni_ops* c, void* state, const int32_t* lines, int64_t stride, const void* table,
+                                  void* out, int32_t rows, int32_t dim, int32_t vocab) {
+  if (!c || !state || !lines || !table || !out) return OMNI_ERR_INVALID;
+  OPS_CUDA(c, launch_higgs_frame_embed(SlotState{state, lines, stride}, (const bf16*)table, (bf16*)out, rows, dim, vocab,
+                                       c->err, c->stream));
+  return OMNI_OK;
+}
+
+int32_t omni_op_higgs_sample(omni_ops* c, const void* logits, int32_t vocab, float temperature, int32_t top_k,
+                             const float* uniforms, const int32_t* force, void* state, const int32_t* lines,
+                             int64_t stride, int32_t* codes, int32_t rows) {
+  if (!c || !logits || !uniforms || !force || !state || !lines || !codes) return OMNI_ERR_INVALID;
+  OPS_CUDA(c, launch_higgs_sample((const bf16*)logits, vocab, temperature, top_k, uniforms, force,
+                                  SlotState{state, lines, stride}, codes, rows, c->stream));
+  return OMNI_OK;
+}
+
+int32_t omni_higgs_delay_forced_from(const omni_higgs_delay* d) {
+  return d ? std::min(d->steps + 1, OMNI_HIGGS_BOOKS) : OMNI_ERR_INVALID;
+}
+
+int32_t omni_higgs_delay_advance(omni_higgs_delay* d, int32_t first) {
+  if (!d) return OMNI_ERR_INVALID;
+  if (d->done) return 1;
+  if (d->steps < OMNI_HIGGS_BOOKS) {  // the ramp: an end drawn here is not one
+    d->steps += 1;
+  } else if (d->countdown > 0) {
+    d->countdown -= 1;
+    d->done = d->countdown <= 1;
+    if (d->done) d->countdown = 0;
+  } else if (first == OMNI_HIGGS_EOC) {
+    d->countdown = OMNI_HIGGS_BOOKS - 2 + 1;  // books - 2 more steps; stored + 1 so that 0 means "not running"
+  }
+  return d->done;
+}
+
+int32_t omni_higgs_undelay(const int32_t* rows, int32_t n_rows, int32_t* frames) {
+  if (n_rows < 0 || (n_rows > 0 && (!rows || !frames))) return OMNI_ERR_INVALID;
+  const int n = std::max(n_rows - (OMNI_HIGGS_BOOKS - 1), 0);
+  for (int t = 0; t < n; ++t)
+    for (int b = 0; b < OMNI_HIGGS_BOOKS; ++b) frames[t * OMNI_HIGGS_BOOKS + b] = rows[(t + b) * OMNI_HIGGS_BOOKS + b];
+  return n;
 }
 
 }  // extern "C"

@@ -96,17 +96,19 @@ def random_checkpoint(c: DuplexConfig, seed: int = 0, std: float = 0.02, device=
     else N(0, std) from a per-tensor seed derived from its name; `head_std` widens the two output heads."""
     import torch
     out = {}
-    for name, shape in tensor_shapes(c, voice_rows):
+    on_device = torch.device(device).type == "cuda"  # full-size models are drawn on the GPU (a different stream of
+    for name, shape in tensor_shapes(c, voice_rows):  # numbers than the CPU generator's: fine for timing)
         if "norm" in name:
-            t = torch.ones(shape, dtype=torch.float32)
+            t = torch.ones(shape, dtype=torch.float32, device=device if on_device else "cpu")
         else:
-            g = torch.Generator().manual_seed((zlib.crc32(name.encode()) + seed) & 0x7fffffff)
+            g = torch.Generator(device=device if on_device else "cpu")
+            g.manual_seed((zlib.crc32(name.encode()) + seed) & 0x7fffffff)
             s = std
             if name.endswith("_emb") or name in ("d.emb", "voices"):
                 s = 1.0
             elif head_std is not None and name in ("h.text_linear", "d.heads"):
                 s = head_std
-            t = torch.randn(shape, generator=g, dtype=torch.float32) * s
+            t = torch.randn(shape, generator=g, dtype=torch.float32, device=device if on_device else "cpu") * s
         out[name] = t.to(torch.bfloat16).to(device)
     return out
 

@@ -61,6 +61,10 @@ class DuplexStep(C.Structure):
                 ("seed", C.c_uint64)]
 
 
+class HiggsDelay(C.Structure):
+    _fields_ = [("steps", C.c_int32), ("countdown", C.c_int32), ("done", C.c_int32)]
+
+
 DUPLEX_TEXT_LOGITS, DUPLEX_AUDIO_LOGITS, DUPLEX_ROWS, DUPLEX_DRAWN = 0, 1, 2, 3
 
 P = C.POINTER
@@ -106,6 +110,11 @@ SYMBOLS = {
     "omni_op_lm_dep_kv_attend": (I32, [VP, VP, VP, I32, VP, I32, I32, C.c_float]),
     "omni_op_lm_sample": (I32, [VP, VP, I32, C.c_int64, C.c_float, I32, VP, VP, I32, VP, I32]),
     "omni_op_lm_advance": (I32, [VP, VP, VP, C.c_int64, VP, VP, VP, VP, VP, I32]),
+    "omni_op_higgs_frame_embed": (I32, [VP, VP, VP, C.c_int64, VP, VP, I32, I32, I32]),
+    "omni_op_higgs_sample": (I32, [VP, VP, I32, C.c_float, I32, VP, VP, VP, VP, C.c_int64, VP, I32]),
+    "omni_higgs_delay_forced_from": (I32, [P(HiggsDelay)]),
+    "omni_higgs_delay_advance": (I32, [P(HiggsDelay), I32]),
+    "omni_higgs_undelay": (I32, [P(I32), I32, P(I32)]),
     "omni_duplex_create": (I32, [P(DuplexCfg), P(Tensor), I32, I32, P(VP)]),
     "omni_duplex_destroy": (None, [VP]),
     "omni_duplex_last_error": (C.c_char_p, [VP]),

@@ -118,6 +118,18 @@ class Ops:
                                                  _p(caller), _p(force_caller), _p(emitted), rows))
 
 
+    # ---- Higgs glue ----
+    def higgs_frame_embed(self, state, lines, stride, table, out, vocab):
+        rows, dim = out.shape
+        self._check(self._lib.omni_op_higgs_frame_embed(self._h, _p(state), _p(lines), stride, _p(table), _p(out), rows,
+                                                        dim, vocab))
+
+    def higgs_sample(self, logits, temperature, top_k, uniforms, force, state, lines, stride, codes):
+        rows, books, vocab = logits.shape
+        assert books == 8
+        self._check(self._lib.omni_op_higgs_sample(self._h, _p(logits), vocab, temperature, top_k, _p(uniforms),
+                                                   _p(force), _p(state), _p(lines), stride, _p(codes), rows))
+
 def gemm_noalloc(w, x, y, splits=0, bias=None, epilogue=0, stream=None):
     """`omni_op_gemm_noalloc`: the tensor-core GEMM with its split-K scratch inside the library image, for callers
     that cannot allocate device memory (no context object, no cudaMalloc). Waits for the result; raises OpsError
