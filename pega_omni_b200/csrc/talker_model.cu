@@ -184,6 +184,7 @@ struct omni_talker {
   bool tick_ok = false;
   int tick_ctas = 0;
   uint32_t* tick_barrier = nullptr;
+  uint32_t tick_barrier_base = 0;  // arrivals left in the counter by earlier launches
   std::map<std::pair<int, int>, TickProgram> tick_programs;
   int launches = 0, tick_phases = 0;
   std::string trace_path;
@@ -695,7 +696,8 @@ int run_tick_program(omni_talker* m, int program, int b) {
     m->trace_program = &it->second;
     CUDA_TRY(m, cudaMemsetAsync(m->trace, 0, (size_t)4 * kTraceMaxPhases * m->tick_ctas * 8, m->stream));
   }
-  LAUNCH(m, tick_launch(it->second, io, m->gemm_scratch.partials, m->tick_barrier, m->err, m->tick_ctas, m->stream,
+  LAUNCH(m, tick_launch(it->second, io, m->gemm_scratch.partials, m->tick_barrier, &m->tick_barrier_base, m->err,
+                        m->tick_ctas, m->stream,
                         m->trace && m->tick_phases <= kTraceMaxPhases ? m->trace : nullptr));
   return OMNI_OK;
 }
@@ -861,6 +863,7 @@ int finish_call(omni_talker* m, int n, int32_t* codes, float* wav) {
   m->stats.last_call_launches = m->launches;
   const uint32_t err = (uint32_t)m->out_host[(size_t)m->max_seqs * OMNI_GROUPS];
   if (err != 0) {
+    m->tick_barrier_base = ~0u;  // CTAs of the failed launch may not all have arrived: restart the counter
     cudaMemsetAsync(m->err, 0, 4, m->stream);
     cudaStreamSynchronize(m->stream);
     return m->fail(OMNI_ERR_DEVICE, "device error word 0x%x (1: barrier wait ran out, 2: index out of range)", err);
@@ -1279,6 +1282,7 @@ int32_t omni_talker_run_ticks(omni_talker* m, int32_t n, omni_seq* const* seqs, 
     uint32_t err = 0;
     CUDA_TRY(m, cudaMemcpy(&err, m->err, 4, cudaMemcpyDeviceToHost));
     if (err != 0) {
+      m->tick_barrier_base = ~0u;
       cudaMemset(m->err, 0, 4);
       return m->fail(OMNI_ERR_DEVICE, "device error word 0x%x", err);
     }

@@ -82,11 +82,14 @@ int tick_upload(TickProgram* prog);
 void tick_free(TickProgram* prog);
 // Raises the kernel's shared-memory limit and reports how many CTAs can be co-resident (0 on failure).
 int tick_configure(int device);
-// One cooperative launch of the whole program. `barrier` (one zeroed u32) is reset on the stream first.
+// One cooperative launch of the whole program. `barrier` is one device u32, zero before the first launch;
+// `*barrier_base` (host, starts at 0) tracks the arrivals earlier launches left in it. Set *barrier_base = ~0u after a
+// launch that raised the error word (its CTAs may not all have arrived): the next launch then restarts the counter.
 // `trace` (optional, four u64 per (phase, CTA), phase-major): the global timer when the CTA's first activation tile
 // of the phase arrived, when its first accumulator was complete (both GEMM phases only), when its own share of
 // the phase was done, and when it saw the phase's grid barrier complete.
-cudaError_t tick_launch(const TickProgram& prog, const TickIo& io, float* partials, uint32_t* barrier, uint32_t* err,
-                        int ctas, cudaStream_t stream, unsigned long long* trace = nullptr);
+cudaError_t tick_launch(const TickProgram& prog, const TickIo& io, float* partials, uint32_t* barrier,
+                        uint32_t* barrier_base, uint32_t* err, int ctas, cudaStream_t stream,
+                        unsigned long long* trace = nullptr);
 
 }  // namespace omni

@@ -67,6 +67,7 @@ struct KernelArgs {
   const CUtensorMap* maps;
   float* partials;
   uint32_t* barrier;
+  uint32_t barrier_base;  // arrivals counted by earlier launches (the counter is not reset between launches)
   uint32_t* err;
   int ring_bytes;                      // shared memory of the tile ring (a multiple of 1 KB): the rest of the SM's
                                        // array stays L1, which the row-wise phases live on
@@ -925,7 +926,7 @@ __global__ void __launch_bounds__(kThreads, 1) tick_kernel(const __grid_constant
       WorkerSync::sync();
       if (wtid == 0) {
         if (a.trace) a.trace[((size_t)p * G + blockIdx.x) * 4 + 2] = global_timer_ns();  // this CTA's share is done
-        if (!ctl.abort && !grid_barrier(a.barrier, (uint32_t)(p + 1) * (uint32_t)G, a.err)) ctl.abort = 1;
+        if (!ctl.abort && !grid_barrier(a.barrier, a.barrier_base + (uint32_t)(p + 1) * (uint32_t)G, a.err)) ctl.abort = 1;
         ctl.released = p + 1;
         if (a.trace) a.trace[((size_t)p * G + blockIdx.x) * 4 + 3] = global_timer_ns();  // every CTA has arrived
       }
@@ -1017,8 +1018,8 @@ int tick_configure(int device) {
   return per_sm >= 1 ? sms : 0;
 }
 
-cudaError_t tick_launch(const TickProgram& prog, const TickIo& io, float* partials, uint32_t* barrier, uint32_t* err,
-                        int ctas, cudaStream_t stream, unsigned long long* trace) {
+cudaError_t tick_launch(const TickProgram& prog, const TickIo& io, float* partials, uint32_t* barrier,
+                        uint32_t* barrier_base, uint32_t* err, int ctas, cudaStream_t stream, unsigned long long* trace) {
   KernelArgs a;
   a.trace = trace;
   a.phases = prog.d_phases;
@@ -1031,8 +1032,16 @@ cudaError_t tick_launch(const TickProgram& prog, const TickIo& io, float* partia
   a.w_ahead = 1 << 20;
   if (const char* e = getenv("OMNI_TICK_WAHEAD")) a.w_ahead = atoi(e);
   a.io = io;
-  cudaError_t e = cudaMemsetAsync(barrier, 0, sizeof(uint32_t), stream);
-  if (e != cudaSuccess) return e;
+  // the arrival counter runs on from launch to launch (one memset less per tick); it restarts from zero when the
+  // next launch could overflow it. After a launch that raised the error word the caller passes *barrier_base = ~0u.
+  const uint32_t arrivals = (uint32_t)a.n_phases * (uint32_t)ctas;
+  if (*barrier_base > 0xffffffffu - 2u * arrivals) {
+    const cudaError_t e = cudaMemsetAsync(barrier, 0, sizeof(uint32_t), stream);
+    if (e != cudaSuccess) return e;
+    *barrier_base = 0;
+  }
+  a.barrier_base = *barrier_base;
+  *barrier_base += arrivals;
   void* args[] = {&a};
   return cudaLaunchCooperativeKernel((const void*)tick_kernel, dim3(ctas), dim3(kThreads), args,
                                      tick_smem_bytes(a.ring_bytes), stream);

@@ -108,7 +108,29 @@ def c_tensors(checkpoint: dict):
     return arr, keep
 
 
-def _draws(draws: Sequence[Draw]):
+DRAW_DTYPE = np.dtype([("uniforms", np.float32, (GROUPS,)), ("force", np.int32, (GROUPS,))])
+
+
+class DrawBatch:
+    """The draws of one call as two arrays, laid out as the C ABI's `omni_draw[n]`: for callers that prepare a step's
+    inputs ahead of time (an engine's staging buffer) instead of building `Draw` objects per row."""
+
+    def __init__(self, uniforms, force=None):
+        uniforms = np.asarray(uniforms, dtype=np.float32).reshape(-1, GROUPS)
+        self.raw = np.zeros(len(uniforms), dtype=DRAW_DTYPE)
+        self.raw["uniforms"] = uniforms
+        self.raw["force"] = -1 if force is None else np.asarray(force, dtype=np.int32).reshape(-1, GROUPS)
+
+    def __len__(self) -> int:
+        return len(self.raw)
+
+    def pointer(self):
+        return self.raw.ctypes.data_as(C.POINTER(L.Draw))
+
+
+def _draws(draws):
+    if isinstance(draws, DrawBatch):
+        return draws.pointer()
     arr = (L.Draw * len(draws))()
     for i, d in enumerate(draws):
         u = list(d.uniforms) + [0.5] * (GROUPS - len(d.uniforms))
@@ -177,7 +199,10 @@ class Model:
         return int(frame[0]) == self.config.codec_eos_token_id
 
     def _seq_array(self, seqs: Sequence[Seq]):
-        return (C.c_void_p * len(seqs))(*[s._h for s in seqs])
+        key = tuple(id(s) for s in seqs)
+        if getattr(self, "_seq_key", None) != key:  # the same batch call after call: keep its handle array
+            self._seq_key, self._seq_arr = key, (C.c_void_p * len(seqs))(*[s._h for s in seqs])
+        return self._seq_arr
 
     # -- Model::start (model.rs:153-177) --
     def start(self, rows: Sequence[tuple]) -> Out:
@@ -197,13 +222,18 @@ class Model:
 
     # -- Model::step (model.rs:180-192) --
     def step(self, rows: Sequence[tuple]) -> Out:
-        n = len(rows)
-        codes = np.zeros((n, GROUPS), dtype=np.int32)
-        wav = np.zeros((n, SAMPLES_PER_FRAME), dtype=np.float32)
+        return self.step_batch([r[0] for r in rows], [r[1] for r in rows])
+
+    def step_batch(self, seqs: Sequence[Seq], draws, out: Optional[Out] = None) -> Out:
+        """`step` with the sequences and their draws as two parallel sequences; `draws` may be a `DrawBatch` and `out`
+        a previous call's `Out` to write into (both spare per-row Python work in a tight serving loop)."""
+        n = len(seqs)
+        if out is None:
+            out = Out(np.zeros((n, GROUPS), dtype=np.int32), np.zeros((n, SAMPLES_PER_FRAME), dtype=np.float32))
         self._check(self._lib.omni_talker_step(
-            self._h, n, self._seq_array([r[0] for r in rows]), _draws([r[1] for r in rows]),
-            codes.ctypes.data_as(C.POINTER(C.c_int32)), wav.ctypes.data_as(C.POINTER(C.c_float))))
-        return Out(codes, wav)
+            self._h, n, self._seq_array(seqs), _draws(draws),
+            out.codes.ctypes.data_as(C.POINTER(C.c_int32)), out.wav.ctypes.data_as(C.POINTER(C.c_float))))
+        return out
 
     def run_ticks(self, seqs: Sequence[Seq], draws: Sequence[Sequence[Draw]]):
         """`len(draws)` decode ticks with all inputs staged on the device first; returns (codes, tick_ms)."""
