@@ -478,7 +478,7 @@ int enqueue_program(omni_talker* m, int program, int b) {
 
 // ---- the persistent tick kernel's phase list ------------------------------------------------------------------
 
-int pick_bn(int rows) { return rows <= 16 ? 16 : rows <= 32 ? 32 : rows <= 64 ? 64 : 128; }
+int pick_bn(int rows) { return rows <= 16 ? 16 : rows <= 32 ? 32 : rows <= 64 ? 64 : rows <= 128 ? 128 : 256; }
 
 struct TickBuilder {
   omni_talker* m;

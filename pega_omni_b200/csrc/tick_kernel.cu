@@ -678,11 +678,11 @@ __device__ __noinline__ void phase_sample(const Phase& ph, const TickIo& io, con
 // ---- GEMM epilogue: a worker thread owns one activation row (its TMEM lane) and half of the tile's columns -------
 
 __device__ __noinline__ void gemm_epilogue(const Phase& ph, float* partials, int tile, int split, uint32_t tmem_acc,
-                                           int wwarp, int lane) {
+                                           int row_base, int wwarp, int lane) {
   // a warp may only touch the TMEM lanes of its quadrant, (warp index in the CTA) % 4
   const int quad = (wwarp + kFirstWorkerWarp) & 3, half = wwarp >> 2;
-  const int m = quad * 32 + lane, tn = ph.tile_n;
-  if (quad * 32 >= ph.rows) return;  // no live row in this warp's quadrant (warp-uniform)
+  const int m = row_base + quad * 32 + lane, tn = ph.tile_n;  // row_base: 128 for the second half of a 256-row tile
+  if (row_base + quad * 32 >= ph.rows) return;  // no live row in this warp's quadrant (warp-uniform)
   const uint32_t lane_addr = tmem_acc + ((uint32_t)(quad * 32) << 16);
   if (ph.mode == kGemmPartials) {
     float* rowp = partials + (((size_t)split * ph.tiles + tile) * ph.bn + min(m, ph.bn - 1)) * tn;
@@ -849,16 +849,23 @@ __global__ void __launch_bounds__(kThreads, 1) tick_kernel(const __grid_constant
         if (first_item(ph) >= items) continue;
         ring.enter(ph, a.ring_bytes);
         const uint32_t idesc = idesc_bf16_f32(kTileM, ph.tile_n);
+        // 129..256 activation rows: two M = 128 halves per k-block into the two accumulators (no double buffering)
+        const bool two = ph.bn > kTileM;
         for (int it = first_item(ph); it < items && !ctl.abort; it += G) {
           const int split = it / ph.tiles;
           const int kb0 = (int)((int64_t)nkb * split / ph.splits), kb1 = (int)((int64_t)nkb * (split + 1) / ph.splits);
-          if (!mbar_wait(smem_addr(&ctl.acc_empty[buf]), empty_par[buf] ^ 1u, a.err)) {
+          bool ok = true;
+          for (int h = 0; h < (two ? 2 : 1) && ok; ++h) {
+            const int b = two ? h : buf;
+            ok = mbar_wait(smem_addr(&ctl.acc_empty[b]), empty_par[b] ^ 1u, a.err);
+            empty_par[b] ^= 1u;
+          }
+          if (!ok) {
             ctl.abort = 1;
             break;
           }
-          empty_par[buf] ^= 1u;
           tc_fence_after_sync();
-          const uint32_t tmem_d = tmem_base + (uint32_t)(buf * kTileN);
+          const uint32_t tmem_d = tmem_base + (uint32_t)((two ? 0 : buf) * kTileN);
           for (int kb = kb0; kb < kb1; ++kb) {
             if (!mbar_wait(smem_addr(&ctl.full_w[ring.stage]), ring.parity(), a.err) ||
                 !mbar_wait(smem_addr(&ctl.full_x[ring.stage]), ring.parity(), a.err)) {
@@ -871,12 +878,24 @@ __global__ void __launch_bounds__(kThreads, 1) tick_kernel(const __grid_constant
 #pragma unroll
             for (int k = 0; k < kTileK / 16; ++k)
               mma_bf16(tmem_d, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2), idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+            if (two) {
+              const uint64_t adesc2 = kmajor_sw128_desc(base + ring.x_off() + kTileM * kTileK * 2);
+#pragma unroll
+              for (int k = 0; k < kTileK / 16; ++k)
+                mma_bf16(tmem_d + kTileN, adesc2 + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2), idesc,
+                         (kb > kb0 || k > 0) ? 1u : 0u);
+            }
             mma_commit(smem_addr(&ctl.empty[ring.stage]));
             ring.advance();
           }
           if (ctl.abort) break;
-          mma_commit(smem_addr(&ctl.acc_full[buf]));
-          buf ^= 1;
+          if (two) {
+            mma_commit(smem_addr(&ctl.acc_full[0]));
+            mma_commit(smem_addr(&ctl.acc_full[1]));
+          } else {
+            mma_commit(smem_addr(&ctl.acc_full[buf]));
+            buf ^= 1;
+          }
         }
       }
     }
@@ -898,17 +917,24 @@ __global__ void __launch_bounds__(kThreads, 1) tick_kernel(const __grid_constant
       switch (ph.type) {
         case kPhGemm: {
           const int items = ph.tiles * ph.splits;
+          const bool two = ph.bn > kTileM;
           for (int it = first_item(ph); it < items; it += G) {
-            const bool ok = mbar_wait(smem_addr(&ctl.acc_full[buf]), full_par[buf], a.err);
-            if (!ok) ctl.abort = 1;
-            full_par[buf] ^= 1u;
-            tc_fence_after_sync();
-            if (a.trace && wtid == 0 && it == first_item(ph)) a.trace[((size_t)p * G + blockIdx.x) * 4 + 1] = global_timer_ns();
-            if (ok) gemm_epilogue(ph, a.partials, it % ph.tiles, it / ph.tiles, tmem_base + (uint32_t)(buf * kTileN), wwarp, lane);
-            tc_fence_before_sync();
-            WorkerSync::sync();
-            if (wtid == 0) mbar_arrive(smem_addr(&ctl.acc_empty[buf]));
-            buf ^= 1;
+            for (int h = 0; h < (two ? 2 : 1); ++h) {
+              const int b = two ? h : buf;
+              const bool ok = mbar_wait(smem_addr(&ctl.acc_full[b]), full_par[b], a.err);
+              if (!ok) ctl.abort = 1;
+              full_par[b] ^= 1u;
+              tc_fence_after_sync();
+              if (a.trace && wtid == 0 && h == 0 && it == first_item(ph))
+                a.trace[((size_t)p * G + blockIdx.x) * 4 + 1] = global_timer_ns();
+              if (ok)
+                gemm_epilogue(ph, a.partials, it % ph.tiles, it / ph.tiles, tmem_base + (uint32_t)(b * kTileN), h * kTileM,
+                              wwarp, lane);
+              tc_fence_before_sync();
+              WorkerSync::sync();
+              if (wtid == 0) mbar_arrive(smem_addr(&ctl.acc_empty[b]));
+            }
+            if (!two) buf ^= 1;
             if (ctl.abort) break;
           }
           break;
@@ -985,7 +1011,7 @@ int tick_add_map(TickProgram* prog, const bf16* base, int rows, int K, int box_r
 bool tick_supports(int hidden, int head_dim, int q_heads, int kv_heads, int rows_max) {
   const int g = kv_heads > 0 ? q_heads / kv_heads : 0;
   const bool dim_ok = hidden == 128 || hidden == 256 || hidden == 512 || hidden == 1024 || hidden == 2048;
-  return dim_ok && (head_dim == 64 || head_dim == 128) && (g == 1 || g == 2 || g == 4) && rows_max <= kTileM;
+  return dim_ok && (head_dim == 64 || head_dim == 128) && (g == 1 || g == 2 || g == 4) && rows_max <= 2 * kTileM;
 }
 
 int tick_upload(TickProgram* prog) {

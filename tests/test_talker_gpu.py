@@ -227,14 +227,18 @@ def test_graph_replay_equals_eager(built_lib):
     assert np.array_equal(outs[0][0], outs[1][0]) and np.array_equal(outs[0][1], outs[1][1])
 
 
-def test_tick_kernel_agrees_with_per_op_kernels(built_lib):
+@pytest.mark.parametrize("sessions", [5, 70, 128])
+def test_tick_kernel_agrees_with_per_op_kernels(built_lib, sessions):
     """The persistent kernel and the per-op kernels are two schedules of the same arithmetic (same rounding points,
-    different K splits): forced frames give logits within tolerance, and each path's own draws are reproducible."""
+    different K splits): forced frames give logits within tolerance, and each path's own draws are reproducible.
+    70 and 128 sessions run the predictor's first pass with 192 and 256 rows: two M = 128 halves per GEMM tile."""
     from pega_omni_b200.model import Draw
     got = {}
     for engine in ("tick", "ops"):
-        cfg, ck, m = make("mid", **ENGINES[engine])
-        ps = prompts_for(cfg, [14, 37, 22, 9, 30], seed=11)
+        from pega_omni_b200.model import Limits
+        cfg, ck, m = make("mid", limits=Limits(max_batch=max(sessions, 8), max_tokens=40 * max(sessions, 8), kv_gib=0.3),
+                          **ENGINES[engine])
+        ps = prompts_for(cfg, [9 + (7 * i) % 29 for i in range(sessions)], seed=11)
         forced = forced_frames(cfg, 5, len(ps), seed=11)
         seqs = [m.open(len(p), 8) for p in ps]
         logits = []
@@ -248,7 +252,10 @@ def test_tick_kernel_agrees_with_per_op_kernels(built_lib):
         got[engine] = np.stack(logits)
         m.close()
     a, b = got["tick"], got["ops"]
-    assert np.abs(a - b).max() <= 2e-2, np.abs(a - b).max()
+    # both store logits as bf16: at most two bf16 steps of the value apart (a step is 1.6e-2 in [2, 4))
+    step = np.exp2(np.floor(np.log2(np.maximum(np.abs(b), 2.0))) - 7)
+    worst = float((np.abs(a - b) / step).max())
+    assert worst <= 2.0, (worst, float(np.abs(a - b).max()))
     for t in range(a.shape[0]):
         for s in range(a.shape[1]):
             assert cosine(a[t, s], b[t, s]) >= 0.9999
