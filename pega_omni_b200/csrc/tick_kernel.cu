@@ -721,6 +721,9 @@ __device__ __noinline__ void gemm_epilogue(const Phase& ph, float* partials, int
   }
 }
 
+// kWide: the program has GEMM phases of more than 128 activation rows (buckets above 64: two accumulators per item).
+// The narrow instantiation carries none of that code: the 64-session tick is sensitive to the kernel's size.
+template <bool kWide>
 __global__ void __launch_bounds__(kThreads, 1) tick_kernel(const __grid_constant__ KernelArgs a) {
   using namespace sm100;
   extern __shared__ unsigned char tick_smem_raw[];
@@ -849,23 +852,52 @@ __global__ void __launch_bounds__(kThreads, 1) tick_kernel(const __grid_constant
         if (first_item(ph) >= items) continue;
         ring.enter(ph, a.ring_bytes);
         const uint32_t idesc = idesc_bf16_f32(kTileM, ph.tile_n);
-        // 129..256 activation rows: two M = 128 halves per k-block into the two accumulators (no double buffering)
-        const bool two = ph.bn > kTileM;
+        if (kWide && ph.bn > kTileM) {
+          // 129..256 activation rows: two M = 128 halves per k-block, one into each accumulator (no double buffering)
+          for (int it = first_item(ph); it < items && !ctl.abort; it += G) {
+            const int split = it / ph.tiles;
+            const int kb0 = (int)((int64_t)nkb * split / ph.splits), kb1 = (int)((int64_t)nkb * (split + 1) / ph.splits);
+            for (int h = 0; h < 2; ++h) {
+              if (!mbar_wait(smem_addr(&ctl.acc_empty[h]), empty_par[h] ^ 1u, a.err)) ctl.abort = 1;
+              empty_par[h] ^= 1u;
+            }
+            if (ctl.abort) break;
+            tc_fence_after_sync();
+            for (int kb = kb0; kb < kb1; ++kb) {
+              if (!mbar_wait(smem_addr(&ctl.full_w[ring.stage]), ring.parity(), a.err) ||
+                  !mbar_wait(smem_addr(&ctl.full_x[ring.stage]), ring.parity(), a.err)) {
+                ctl.abort = 1;
+                break;
+              }
+              tc_fence_after_sync();
+              if (a.trace && kb == kb0 && it == first_item(ph)) a.trace[((size_t)p * G + blockIdx.x) * 4] = global_timer_ns();
+              const uint64_t bdesc = kmajor_sw128_desc(base + ring.w_off());
+              for (int h = 0; h < 2; ++h) {
+                const uint64_t adesc = kmajor_sw128_desc(base + ring.x_off() + (uint32_t)(h * kTileM * kTileK * 2));
+#pragma unroll
+                for (int k = 0; k < kTileK / 16; ++k)
+                  mma_bf16(tmem_base + (uint32_t)(h * kTileN), adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2), idesc,
+                           (kb > kb0 || k > 0) ? 1u : 0u);
+              }
+              mma_commit(smem_addr(&ctl.empty[ring.stage]));
+              ring.advance();
+            }
+            if (ctl.abort) break;
+            mma_commit(smem_addr(&ctl.acc_full[0]));
+            mma_commit(smem_addr(&ctl.acc_full[1]));
+          }
+          continue;
+        }
         for (int it = first_item(ph); it < items && !ctl.abort; it += G) {
           const int split = it / ph.tiles;
           const int kb0 = (int)((int64_t)nkb * split / ph.splits), kb1 = (int)((int64_t)nkb * (split + 1) / ph.splits);
-          bool ok = true;
-          for (int h = 0; h < (two ? 2 : 1) && ok; ++h) {
-            const int b = two ? h : buf;
-            ok = mbar_wait(smem_addr(&ctl.acc_empty[b]), empty_par[b] ^ 1u, a.err);
-            empty_par[b] ^= 1u;
-          }
-          if (!ok) {
+          if (!mbar_wait(smem_addr(&ctl.acc_empty[buf]), empty_par[buf] ^ 1u, a.err)) {
             ctl.abort = 1;
             break;
           }
+          empty_par[buf] ^= 1u;
           tc_fence_after_sync();
-          const uint32_t tmem_d = tmem_base + (uint32_t)((two ? 0 : buf) * kTileN);
+          const uint32_t tmem_d = tmem_base + (uint32_t)(buf * kTileN);
           for (int kb = kb0; kb < kb1; ++kb) {
             if (!mbar_wait(smem_addr(&ctl.full_w[ring.stage]), ring.parity(), a.err) ||
                 !mbar_wait(smem_addr(&ctl.full_x[ring.stage]), ring.parity(), a.err)) {
@@ -878,24 +910,12 @@ __global__ void __launch_bounds__(kThreads, 1) tick_kernel(const __grid_constant
 #pragma unroll
             for (int k = 0; k < kTileK / 16; ++k)
               mma_bf16(tmem_d, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2), idesc, (kb > kb0 || k > 0) ? 1u : 0u);
-            if (two) {
-              const uint64_t adesc2 = kmajor_sw128_desc(base + ring.x_off() + kTileM * kTileK * 2);
-#pragma unroll
-              for (int k = 0; k < kTileK / 16; ++k)
-                mma_bf16(tmem_d + kTileN, adesc2 + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2), idesc,
-                         (kb > kb0 || k > 0) ? 1u : 0u);
-            }
             mma_commit(smem_addr(&ctl.empty[ring.stage]));
             ring.advance();
           }
           if (ctl.abort) break;
-          if (two) {
-            mma_commit(smem_addr(&ctl.acc_full[0]));
-            mma_commit(smem_addr(&ctl.acc_full[1]));
-          } else {
-            mma_commit(smem_addr(&ctl.acc_full[buf]));
-            buf ^= 1;
-          }
+          mma_commit(smem_addr(&ctl.acc_full[buf]));
+          buf ^= 1;
         }
       }
     }
@@ -917,24 +937,34 @@ __global__ void __launch_bounds__(kThreads, 1) tick_kernel(const __grid_constant
       switch (ph.type) {
         case kPhGemm: {
           const int items = ph.tiles * ph.splits;
-          const bool two = ph.bn > kTileM;
-          for (int it = first_item(ph); it < items; it += G) {
-            for (int h = 0; h < (two ? 2 : 1); ++h) {
-              const int b = two ? h : buf;
-              const bool ok = mbar_wait(smem_addr(&ctl.acc_full[b]), full_par[b], a.err);
-              if (!ok) ctl.abort = 1;
-              full_par[b] ^= 1u;
-              tc_fence_after_sync();
-              if (a.trace && wtid == 0 && h == 0 && it == first_item(ph))
-                a.trace[((size_t)p * G + blockIdx.x) * 4 + 1] = global_timer_ns();
-              if (ok)
-                gemm_epilogue(ph, a.partials, it % ph.tiles, it / ph.tiles, tmem_base + (uint32_t)(b * kTileN), h * kTileM,
-                              wwarp, lane);
-              tc_fence_before_sync();
-              WorkerSync::sync();
-              if (wtid == 0) mbar_arrive(smem_addr(&ctl.acc_empty[b]));
+          if (kWide && ph.bn > kTileM) {  // two accumulators per item: rows 0..127 and 128..255
+            for (int it = first_item(ph); it < items && !ctl.abort; it += G) {
+              for (int h = 0; h < 2; ++h) {
+                const bool ok = mbar_wait(smem_addr(&ctl.acc_full[h]), full_par[h], a.err);
+                if (!ok) ctl.abort = 1;
+                full_par[h] ^= 1u;
+                tc_fence_after_sync();
+                if (ok)
+                  gemm_epilogue(ph, a.partials, it % ph.tiles, it / ph.tiles, tmem_base + (uint32_t)(h * kTileN), h * kTileM,
+                                wwarp, lane);
+                tc_fence_before_sync();
+                WorkerSync::sync();
+                if (wtid == 0) mbar_arrive(smem_addr(&ctl.acc_empty[h]));
+              }
             }
-            if (!two) buf ^= 1;
+            break;
+          }
+          for (int it = first_item(ph); it < items; it += G) {
+            const bool ok = mbar_wait(smem_addr(&ctl.acc_full[buf]), full_par[buf], a.err);
+            if (!ok) ctl.abort = 1;
+            full_par[buf] ^= 1u;
+            tc_fence_after_sync();
+            if (a.trace && wtid == 0 && it == first_item(ph)) a.trace[((size_t)p * G + blockIdx.x) * 4 + 1] = global_timer_ns();
+            if (ok) gemm_epilogue(ph, a.partials, it % ph.tiles, it / ph.tiles, tmem_base + (uint32_t)(buf * kTileN), 0, wwarp, lane);
+            tc_fence_before_sync();
+            WorkerSync::sync();
+            if (wtid == 0) mbar_arrive(smem_addr(&ctl.acc_empty[buf]));
+            buf ^= 1;
             if (ctl.abort) break;
           }
           break;
@@ -1036,9 +1066,14 @@ void tick_free(TickProgram* prog) {
 
 int tick_configure(int device) {
   const size_t smem = tick_smem_bytes(kMaxRingBytes);
-  if (cudaFuncSetAttribute(tick_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return 0;
-  int per_sm = 0, sms = 0, coop = 0;
-  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, tick_kernel, kThreads, smem) != cudaSuccess) return 0;
+  if (cudaFuncSetAttribute(tick_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess ||
+      cudaFuncSetAttribute(tick_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+    return 0;
+  int per_sm = 0, per_sm_wide = 0, sms = 0, coop = 0;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, tick_kernel<false>, kThreads, smem) != cudaSuccess ||
+      cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm_wide, tick_kernel<true>, kThreads, smem) != cudaSuccess)
+    return 0;
+  per_sm = std::min(per_sm, per_sm_wide);
   if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) return 0;
   if (cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, device) != cudaSuccess || !coop) return 0;
   return per_sm >= 1 ? sms : 0;
@@ -1069,8 +1104,8 @@ cudaError_t tick_launch(const TickProgram& prog, const TickIo& io, float* partia
   a.barrier_base = *barrier_base;
   *barrier_base += arrivals;
   void* args[] = {&a};
-  return cudaLaunchCooperativeKernel((const void*)tick_kernel, dim3(ctas), dim3(kThreads), args,
-                                     tick_smem_bytes(a.ring_bytes), stream);
+  const void* kernel = prog.max_bn > kTileM ? (const void*)tick_kernel<true> : (const void*)tick_kernel<false>;
+  return cudaLaunchCooperativeKernel(kernel, dim3(ctas), dim3(kThreads), args, tick_smem_bytes(a.ring_bytes), stream);
 }
 
 }  // namespace omni
