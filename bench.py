@@ -199,14 +199,15 @@ def run_duplex(args, rank, world, local):
     W, K, n = max(3, args.warmup), args.steps, args.sessions
     c = dataclasses.replace(PRESETS["personaplex-7b"], context=args.context)
     ck = random_checkpoint(c, seed=0, device=f"cuda:{local}", head_std=0.05)
-    model = Model.load(local, ck, c, max_sessions=n, max_prefill=max(n * 4, 256))
+    plen = args.prompt if args.prompt != 128 else 4  # --prompt: rows prefilled per session (default 4: near-empty ring)
+    model = Model.load(local, ck, c, max_sessions=n, max_prefill=max(2048, plen))
     del ck
     torch.cuda.empty_cache()
     rng = np.random.default_rng(100 + rank)
     sessions = [model.open() for _ in range(n)]
-    plen = 4  # short prompts: the tick's cost is weights + ring KV, and the ring fills as ticks run
-    for i in range(0, n, 32):
-        part = sessions[i:i + 32]
+    per_call = max(1, 2048 // plen)  # prompts per prefill call
+    for i in range(0, n, per_call):
+        part = sessions[i:i + per_call]
         prompts = []
         for _ in part:
             rows = rng.integers(0, c.card, (plen, 17)).astype(np.int32)
@@ -384,7 +385,12 @@ def main():
                 "achieved": tick_bytes / tick_s / 1e9, "peak": peak, "unit": "GB/s",
                 "frac": tick_bytes / tick_s / 1e9 / peak, "peak_source": f"of {peak_kind}",
                 "bytes_per_launch": int(tick_bytes), "us_per_launch": tick_s * 1e6,
-                "traffic": None, "traffic_note": "see profiles/ for the ncu dram bytes of a captured tick"}
+                # ncu cannot run inside the timed region: the DRAM bytes of one captured tick of this kernel
+                # (profiles/tick_kernel_qwen3tts_64sessions.md: 6,467 MB read+written for 6,296 MB algorithmic at
+                # positions 131-132) scaled to this run's algorithmic bytes; traffic grows with the KV length as they do
+                "traffic": int(tick_bytes * 6467.2 / 6296.2) if launches_per_tick == 1 else None,
+                "traffic_note": "ncu dram__bytes_read+write of one captured tick (6.467 GB for 6.296 GB algorithmic), "
+                                "scaled by this run's algorithmic bytes"}
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
             "ms_per_step": 1e3 * elapsed_max / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,

@@ -4,8 +4,8 @@
  * Replaces the model shell of crates/omni-personaplex/src/model.rs (`Model::{load, open, start, tick}` and the debug
  * getters) one level below the engine. The waveform codec (Mimi) is not part of this library yet: the caller's codes
  * of a frame arrive through `omni_duplex_step.caller` (what `force_caller` overrides in the reference), and no PCM is
- * returned. Not built: the prefix cache (`warm_prefix`, `is_cached`, model.rs:325-370) and CUDA-graph capture of the
- * tick; every tick is issued as per-op launches.
+ * returned. Not built: CUDA-graph capture of the tick (every tick is issued as per-op launches, so there are no batch
+ * buckets and no `warmup`).
  *
  * One model per GPU per thread; no internal locking; calls are synchronous. All functions return an omni_status
  * (include/omni_b200.h); after a non-zero status `omni_duplex_last_error` describes it. */
@@ -82,11 +82,20 @@ int32_t omni_duplex_close(omni_duplex* m, omni_duplex_session* session);
 /* Helium position of the session's next step and frames run so far (`Session::pos`, `Session::frame`). */
 int32_t omni_duplex_position(const omni_duplex_session* session, int32_t* pos, int64_t* frame);
 
-/* Replaces `Model::start` (model.rs:325-370) for prompts that are not cached: prefill of each session's prompt rows
- * and its first token state. row_counts[i] rows of session i, concatenated in `ids` ([rows, 17], -1 = no token) and
- * `voice` (per row: index into "voices" taken instead of the ids when >= 0; NULL: none); init[i] = the first input row
- * and the 7 pending caller codes (`Prompt::first`, `Prompt::pending`); first_force[i] (NULL: none) = tokens the first
- * tick takes unless its step forces them (`Prompt::first_force`, model.rs:392-396). */
+/* `Model::is_cached` (model.rs:243-245): 1 when a prompt with exactly these rows (ids [rows, 17] and, when not NULL,
+ * voice rows) sits in the on-device prefix cache. */
+int32_t omni_duplex_is_cached(omni_duplex* m, int32_t rows, const int32_t* ids, const int32_t* voice);
+/* `Model::warm_prefix` (model.rs:248-259): prefills the prompt into the prefix cache when it is not there yet, is at
+ * most 256 rows long and one of the 8 cache slots is free; otherwise does nothing. */
+int32_t omni_duplex_warm_prefix(omni_duplex* m, int32_t rows, const int32_t* ids, const int32_t* voice);
+
+/* Replaces `Model::start` (model.rs:325-370): every eligible prompt is first brought into the prefix cache
+ * (`warm_prefix`), sessions whose prompt is cached get its KV copied into their ring (`lm_copy_kv`), the others are
+ * prefilled; then every session's first token state is written. row_counts[i] rows of session i, concatenated in
+ * `ids` ([rows, 17], -1 = no token) and `voice` (per row: index into "voices" taken instead of the ids when >= 0;
+ * NULL: none); init[i] = the first input row and the 7 pending caller codes (`Prompt::first`, `Prompt::pending`);
+ * first_force[i] (NULL: none) = tokens the first tick takes unless its step forces them (`Prompt::first_force`,
+ * model.rs:392-396). */
 int32_t omni_duplex_start(omni_duplex* m, int32_t n, omni_duplex_session* const* sessions, const int32_t* row_counts,
                           const int32_t* ids, const int32_t* voice, const int32_t* init, const int32_t* first_force);
 

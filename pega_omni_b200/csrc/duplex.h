@@ -68,4 +68,9 @@ cudaError_t launch_lm_advance(void* state, const int32_t* lines, int64_t stride,
 cudaError_t launch_lm_init(void* state, const int32_t* lines, int64_t stride, const int32_t* init, int rows,
                            cudaStream_t s);
 
+// Copies `tokens` KV slots of one layer from src_slot[r] to dst_slot[r] (keys, values and both scales of every head):
+// a cached prefix into a new session's ring (`lm_copy_kv`, lm.cu:584-593).
+cudaError_t launch_lm_copy_kv(void* kv, const int32_t* src_slot, const int32_t* dst_slot, int tokens, int heads,
+                              int kv_pages, uint32_t* err, cudaStream_t s);
+
 }  // namespace omni

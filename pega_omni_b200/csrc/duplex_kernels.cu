@@ -449,6 +449,28 @@ __global__ void lm_init_kernel(void* state, const int32_t* __restrict__ lines, i
   if (threadIdx.x < kDuplexStateWords) own[threadIdx.x] = init[s * kDuplexStateWords + threadIdx.x];
 }
 
+// `lm_copy_kv` (lm.cu:584-593) for this library's layout: a warp per (token, head) moves the 128-byte key row, the
+// 128-byte value row and the two scales.
+__global__ void lm_copy_kv_kernel(void* kv, const int32_t* __restrict__ src_slot, const int32_t* __restrict__ dst_slot,
+                                  int heads, int kv_pages, uint32_t* err) {
+  const int r = blockIdx.x, h = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (h >= heads) return;
+  int64_t src = src_slot[r], dst = dst_slot[r];
+  if (src < 0 || dst < 0 || (src >> 4) >= kv_pages || (dst >> 4) >= kv_pages) {
+    if (lane == 0) raise(err, kErrBadIndex);
+    return;
+  }
+  const uint8_t* from = page_head(kv, src >> 4, heads, h);
+  uint8_t* to = page_head(kv, dst >> 4, heads, h);
+  const int st = (int)(src & 15), dt = (int)(dst & 15);
+  reinterpret_cast<uint32_t*>(to + dt * kHeliumHeadDim)[lane] = reinterpret_cast<const uint32_t*>(from + st * kHeliumHeadDim)[lane];
+  reinterpret_cast<uint32_t*>(to + (16 + dt) * kHeliumHeadDim)[lane] =
+      reinterpret_cast<const uint32_t*>(from + (16 + st) * kHeliumHeadDim)[lane];
+  if (lane < 2)
+    reinterpret_cast<float*>(to + 2 * 16 * kHeliumHeadDim + 64 * lane)[dt] =
+        reinterpret_cast<const float*>(from + 2 * 16 * kHeliumHeadDim + 64 * lane)[st];
+}
+
 bool row_dim_ok(int dim) { return dim % 8 == 0 && dim / 8 <= 1024 && dim / 8 >= 32; }
 
 }  // namespace
@@ -521,6 +543,13 @@ cudaError_t launch_lm_advance(void* state, const int32_t* lines, int64_t stride,
                               const int32_t* caller, const int32_t* force_caller, int32_t* emitted, int rows,
                               cudaStream_t s) {
   lm_advance_kernel<<<(rows + 127) / 128, 128, 0, s>>>(state, lines, stride, drawn, caller, force_caller, emitted, rows);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_lm_copy_kv(void* kv, const int32_t* src_slot, const int32_t* dst_slot, int tokens, int heads,
+                              int kv_pages, uint32_t* err, cudaStream_t s) {
+  if (tokens < 1) return cudaSuccess;
+  lm_copy_kv_kernel<<<dim3(tokens, (heads + 3) / 4), 128, 0, s>>>(kv, src_slot, dst_slot, heads, kv_pages, err);
   return cudaGetLastError();
 }
 

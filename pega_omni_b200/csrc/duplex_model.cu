@@ -31,6 +31,9 @@ struct omni_duplex_session {
 
 namespace {
 
+constexpr int kCacheSlots = 8;     // PREFIX_CACHE_SLOTS (model.rs:68)
+constexpr int kCacheMaxLen = 256;  // PREFIX_CACHE_MAX_LEN (model.rs:70)
+
 struct HeliumLayer {
   bf16 *norm1, *qkv, *o, *norm2, *gate_up, *down;
 };
@@ -71,6 +74,14 @@ struct omni_duplex {
   char* state = nullptr;
   int64_t stride = 256;
   std::vector<int32_t> free_leases;  // lease i owns pages [i * pages_per_session, ..) and state line i
+  // prefix cache (model.rs:67-70, :242-259): up to kCacheSlots prefilled prompts of at most kCacheMaxLen rows, each in
+  // its own pages behind the sessions' rings; a prompt is identified by its rows (ids and voice rows), not by a hash
+  struct CachedPrefix {
+    std::vector<int32_t> ids, voice, pages;
+    int rows = 0;
+  };
+  std::vector<CachedPrefix> cache;
+  int cache_first_page = 0;
   std::vector<std::unique_ptr<omni_duplex_session>> sessions;
 
   // activations (max_rows = max(max_prefill, max_sessions))
@@ -358,7 +369,8 @@ int32_t omni_duplex_create(const omni_duplex_config* config, const omni_tensor* 
   // pools: every lease is a ring of `context` positions (model.rs:67) and one state line
   const int S = c.max_sessions;
   m->pages_per_session = (c.context + 15) / 16;
-  m->kv_pages = S * m->pages_per_session;
+  m->cache_first_page = S * m->pages_per_session;
+  m->kv_pages = m->cache_first_page + kCacheSlots * ((kCacheMaxLen + 15) / 16);
   m->kv.resize(c.layers);
   for (int i = 0; i < c.layers; ++i)
     DTRY(dalloc(m, &m->kv[i], (size_t)m->kv_pages * c.heads * kDuplexPageHeadBytes, true));
@@ -392,7 +404,7 @@ int32_t omni_duplex_create(const omni_duplex_config* config, const omni_tensor* 
   DTRY(dalloc(m, &m->err, 64, true));
 
   // staged inputs: per row pos, slot, seq, voice, 17 ids; per session lines, indptr, pages, init, force, ...
-  m->in_bytes = (R * (4 + kDuplexStreams) + (size_t)S * (8 + m->pages_per_session + OMNI_DUPLEX_STATE + 40)) * 4 + 64 * 256;
+  m->in_bytes = (R * (6 + kDuplexStreams) + (size_t)S * (8 + m->pages_per_session + OMNI_DUPLEX_STATE + 40)) * 4 + 64 * 256;
   DCUDA(m, cudaMallocHost((void**)&m->in_host, m->in_bytes));
   DTRY(dalloc(m, &m->in_dev, m->in_bytes));
   DCUDA(m, cudaMallocHost((void**)&m->out_host, ((size_t)S * kDuplexDrawn + 1) * 4));
@@ -457,57 +469,180 @@ int32_t omni_duplex_position(const omni_duplex_session* session, int32_t* pos, i
   return OMNI_OK;
 }
 
+namespace {
+
+// One prompt as the caller gave it: `rows` rows of 17 ids and (optionally) voice rows.
+struct PromptView {
+  const int32_t* ids;
+  const int32_t* voice;  // may be null
+  int rows;
+};
+
+int find_cached(const omni_duplex* m, const PromptView& p) {
+  for (size_t i = 0; i < m->cache.size(); ++i) {
+    const auto& c = m->cache[i];
+    if (c.rows != p.rows || memcmp(c.ids.data(), p.ids, (size_t)p.rows * kDuplexStreams * 4) != 0) continue;
+    bool same = true;
+    for (int r = 0; r < p.rows && same; ++r) same = c.voice[r] == (p.voice ? p.voice[r] : -1);
+    if (same) return (int)i;
+  }
+  return -1;
+}
+
+// Helium prefill of `n` prompts into the given page lists (`prefill_leases`, model.rs:298-320); lines/init may be null
+// (a cache fill has no token state).
+int prefill(omni_duplex* m, int n, const PromptView* prompts, const std::vector<int32_t>* const* page_lists,
+            const int32_t* lines_in, const int32_t* init) {
+  const omni_duplex_config& c = m->cfg;
+  int total = 0;
+  for (int i = 0; i < n; ++i) total += prompts[i].rows;
+  Staging st{m};
+  int32_t *pos = st.take(total), *slot = st.take(total), *seq = st.take(total), *vrow = st.take(total);
+  int32_t* tok = st.take((size_t)total * kDuplexStreams);
+  size_t page_count = 0;
+  for (int i = 0; i < n; ++i) page_count += page_lists[i]->size();
+  int32_t *lines = st.take(n), *indptr = st.take(n + 1), *pages = st.take(page_count);
+  int32_t* ini = st.take((size_t)n * OMNI_DUPLEX_STATE);
+  if (!ini) return m->fail(OMNI_ERR_INVALID, "staging block too small");
+  int r = 0;
+  indptr[0] = 0;
+  for (int i = 0; i < n; ++i) {
+    const std::vector<int32_t>& pl = *page_lists[i];
+    for (int p = 0; p < prompts[i].rows; ++p, ++r) {
+      pos[r] = p;
+      slot[r] = pl[(p % c.context) >> 4] * 16 + ((p % c.context) & 15);
+      seq[r] = i;
+      vrow[r] = prompts[i].voice ? prompts[i].voice[p] : -1;
+    }
+    memcpy(tok + (size_t)(r - prompts[i].rows) * kDuplexStreams, prompts[i].ids, (size_t)prompts[i].rows * kDuplexStreams * 4);
+    if (lines_in) lines[i] = lines_in[i];
+    memcpy(pages + indptr[i], pl.data(), pl.size() * 4);
+    indptr[i + 1] = indptr[i] + (int)pl.size();
+  }
+  if (init) memcpy(ini, init, (size_t)n * OMNI_DUPLEX_STATE * 4);
+  DCUDA(m, cudaMemcpyAsync(m->in_dev, m->in_host, st.used, cudaMemcpyHostToDevice, m->stream));
+  DLAUNCH(m, launch_lm_embed_ids(st.dev(tok), st.dev(vrow), m->voices, c.voice_rows, tables(m), m->x, total, c.dim,
+                                 m->err, m->stream));
+  DTRY(helium_forward(m, total, st.dev(pos), st.dev(slot), st.dev(seq), st.dev(indptr), st.dev(pages)));
+  if (lines_in && init) DLAUNCH(m, launch_lm_init(m->state, st.dev(lines), m->stride, st.dev(ini), n, m->stream));
+  // the staging block is reused by the next call of this function: wait for this one's copy and kernels
+  DCUDA(m, cudaStreamSynchronize(m->stream));
+  return OMNI_OK;
+}
+
+// `warm_prefix` (model.rs:248-259): prefill into a cache slot if the prompt is short enough and a slot is free.
+int warm(omni_duplex* m, const PromptView& p, bool* cached_now) {
+  *cached_now = find_cached(m, p) >= 0;
+  if (*cached_now || (int)m->cache.size() >= kCacheSlots || p.rows > kCacheMaxLen) return OMNI_OK;
+  omni_duplex::CachedPrefix e;
+  e.rows = p.rows;
+  e.ids.assign(p.ids, p.ids + (size_t)p.rows * kDuplexStreams);
+  e.voice.resize(p.rows);
+  for (int r = 0; r < p.rows; ++r) e.voice[r] = p.voice ? p.voice[r] : -1;
+  const int per = (kCacheMaxLen + 15) / 16, first = m->cache_first_page + (int)m->cache.size() * per;
+  for (int i = 0; i < (p.rows + 15) / 16; ++i) e.pages.push_back(first + i);
+  const std::vector<int32_t>* pl = &e.pages;
+  DTRY(prefill(m, 1, &p, &pl, nullptr, nullptr));
+  m->cache.push_back(std::move(e));
+  *cached_now = true;
+  return OMNI_OK;
+}
+
+int check_prompt_args(omni_duplex* m, const int32_t* ids, const int32_t* voice, int rows) {
+  if (!m || !ids || rows < 1) return OMNI_ERR_INVALID;
+  if (rows >= m->cfg.context) return m->fail(OMNI_ERR_INVALID, "a prompt of %d steps does not fit the %d-step context", rows, m->cfg.context);
+  if (rows > m->cfg.max_prefill) return m->fail(OMNI_ERR_INVALID, "%d prompt rows exceed max_prefill %d", rows, m->cfg.max_prefill);
+  if (voice && m->cfg.voice_rows == 0)
+    for (int r = 0; r < rows; ++r)
+      if (voice[r] >= 0) return m->fail(OMNI_ERR_INVALID, "row %d names a voice but the model has none", r);
+  return OMNI_OK;
+}
+
+}  // namespace
+
+int32_t omni_duplex_is_cached(omni_duplex* m, int32_t rows, const int32_t* ids, const int32_t* voice) {
+  if (!m || !ids || rows < 1) return 0;
+  return find_cached(m, PromptView{ids, voice, rows}) >= 0 ? 1 : 0;
+}
+
+int32_t omni_duplex_warm_prefix(omni_duplex* m, int32_t rows, const int32_t* ids, const int32_t* voice) {
+  DTRY(check_prompt_args(m, ids, voice, rows));
+  DCUDA(m, cudaSetDevice(m->device));
+  m->launches = 0;
+  DCUDA(m, cudaEventRecord(m->ev0, m->stream));
+  bool cached = false;
+  DTRY(warm(m, PromptView{ids, voice, rows}, &cached));
+  return finish(m, 0);
+}
+
 int32_t omni_duplex_start(omni_duplex* m, int32_t n, omni_duplex_session* const* sessions, const int32_t* row_counts,
                           const int32_t* ids, const int32_t* voice, const int32_t* init, const int32_t* first_force) {
   if (!m || !sessions || !row_counts || !ids || !init) return OMNI_ERR_INVALID;
   const omni_duplex_config& c = m->cfg;
   if (n < 1 || n > c.max_sessions) return m->fail(OMNI_ERR_INVALID, "%d sessions in one start", n);
   int total = 0;
+  std::vector<PromptView> prompts(n);
   for (int i = 0; i < n; ++i) {
     if (!sessions[i] || !sessions[i]->live) return m->fail(OMNI_ERR_INVALID, "session %d is not open", i);
     if (sessions[i]->pos != 0) return m->fail(OMNI_ERR_INVALID, "session %d was already started", i);
     for (int j = 0; j < i; ++j)
       if (sessions[j] == sessions[i]) return m->fail(OMNI_ERR_INVALID, "session %d appears twice", i);
-    // a prompt has to leave room in the ring (model.rs:276)
-    if (row_counts[i] < 1 || row_counts[i] >= c.context)
-      return m->fail(OMNI_ERR_INVALID, "a prompt of %d steps does not fit the %d-step context", row_counts[i], c.context);
-    total += row_counts[i];
+    prompts[i] = PromptView{ids + (size_t)total * kDuplexStreams, voice ? voice + total : nullptr, row_counts[i]};
+    DTRY(check_prompt_args(m, prompts[i].ids, prompts[i].voice, row_counts[i]));
+    total += std::max(row_counts[i], 0);
   }
   if (total > c.max_prefill) return m->fail(OMNI_ERR_INVALID, "%d prompt rows exceed max_prefill %d", total, c.max_prefill);
-  if (voice && c.voice_rows == 0) {
-    for (int r = 0; r < total; ++r)
-      if (voice[r] >= 0) return m->fail(OMNI_ERR_INVALID, "row %d names a voice but the model has none", r);
-  }
   DCUDA(m, cudaSetDevice(m->device));
-  Staging st{m};
-  int32_t *pos = st.take(total), *slot = st.take(total), *seq = st.take(total), *vrow = st.take(total);
-  int32_t* tok = st.take((size_t)total * kDuplexStreams);
-  int32_t *lines = st.take(n), *indptr = st.take(n + 1), *pages = st.take((size_t)n * m->pages_per_session);
-  int32_t* ini = st.take((size_t)n * OMNI_DUPLEX_STATE);
-  if (!ini) return m->fail(OMNI_ERR_INVALID, "staging block too small");
-  int r = 0;
-  indptr[0] = 0;
-  for (int i = 0; i < n; ++i) {
-    const omni_duplex_session* s = sessions[i];
-    for (int p = 0; p < row_counts[i]; ++p, ++r) {
-      pos[r] = p;
-      slot[r] = s->pages[(p % c.context) >> 4] * 16 + ((p % c.context) & 15);
-      seq[r] = i;
-      vrow[r] = voice ? voice[r] : -1;
-    }
-    lines[i] = s->line;
-    memcpy(pages + indptr[i], s->pages.data(), s->pages.size() * 4);
-    indptr[i + 1] = indptr[i] + (int)s->pages.size();
-  }
-  memcpy(tok, ids, (size_t)total * kDuplexStreams * 4);
-  memcpy(ini, init, (size_t)n * OMNI_DUPLEX_STATE * 4);
   m->launches = 0;
   DCUDA(m, cudaEventRecord(m->ev0, m->stream));
-  DCUDA(m, cudaMemcpyAsync(m->in_dev, m->in_host, st.used, cudaMemcpyHostToDevice, m->stream));
-  DLAUNCH(m, launch_lm_embed_ids(st.dev(tok), st.dev(vrow), m->voices, c.voice_rows, tables(m), m->x, total, c.dim,
-                                 m->err, m->stream));
-  DTRY(helium_forward(m, total, st.dev(pos), st.dev(slot), st.dev(seq), st.dev(indptr), st.dev(pages)));
-  DLAUNCH(m, launch_lm_init(m->state, st.dev(lines), m->stride, st.dev(ini), n, m->stream));
+  // `Model::start` (model.rs:325-370): fill the cache once per eligible prompt, copy the cached ones, prefill the rest
+  std::vector<int> cached_slot(n, -1);
+  for (int i = 0; i < n; ++i) {
+    bool cached = false;
+    DTRY(warm(m, prompts[i], &cached));
+    if (cached) cached_slot[i] = find_cached(m, prompts[i]);
+  }
+  {
+    Staging st{m};
+    int copies = 0, copied_sessions = 0;
+    for (int i = 0; i < n; ++i)
+      if (cached_slot[i] >= 0) copies += prompts[i].rows, ++copied_sessions;
+    if (copies > 0) {
+      int32_t *src = st.take(copies), *dst = st.take(copies), *lines = st.take(copied_sessions);
+      int32_t* ini = st.take((size_t)copied_sessions * OMNI_DUPLEX_STATE);
+      if (!ini) return m->fail(OMNI_ERR_INVALID, "staging block too small");
+      int r = 0, k = 0;
+      for (int i = 0; i < n; ++i) {
+        if (cached_slot[i] < 0) continue;
+        const auto& e = m->cache[cached_slot[i]];
+        for (int p = 0; p < prompts[i].rows; ++p, ++r) {
+          src[r] = e.pages[p >> 4] * 16 + (p & 15);
+          dst[r] = sessions[i]->pages[(p % c.context) >> 4] * 16 + ((p % c.context) & 15);
+        }
+        lines[k] = sessions[i]->line;
+        memcpy(ini + (size_t)k * OMNI_DUPLEX_STATE, init + (size_t)i * OMNI_DUPLEX_STATE, OMNI_DUPLEX_STATE * 4);
+        ++k;
+      }
+      DCUDA(m, cudaMemcpyAsync(m->in_dev, m->in_host, st.used, cudaMemcpyHostToDevice, m->stream));
+      for (int l = 0; l < c.layers; ++l)
+        DLAUNCH(m, launch_lm_copy_kv(m->kv[l], st.dev(src), st.dev(dst), copies, c.heads, m->kv_pages, m->err, m->stream));
+      DLAUNCH(m, launch_lm_init(m->state, st.dev(lines), m->stride, st.dev(ini), copied_sessions, m->stream));
+      DCUDA(m, cudaStreamSynchronize(m->stream));
+    }
+  }
+  {
+    std::vector<PromptView> rest;
+    std::vector<const std::vector<int32_t>*> lists;
+    std::vector<int32_t> lines, ini;
+    for (int i = 0; i < n; ++i) {
+      if (cached_slot[i] >= 0) continue;
+      rest.push_back(prompts[i]);
+      lists.push_back(&sessions[i]->pages);
+      lines.push_back(sessions[i]->line);
+      ini.insert(ini.end(), init + (size_t)i * OMNI_DUPLEX_STATE, init + (size_t)(i + 1) * OMNI_DUPLEX_STATE);
+    }
+    if (!rest.empty()) DTRY(prefill(m, (int)rest.size(), rest.data(), lists.data(), lines.data(), ini.data()));
+  }
   DTRY(finish(m, 0));
   for (int i = 0; i < n; ++i) {
     sessions[i]->pos = row_counts[i];

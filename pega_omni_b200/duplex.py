@@ -213,7 +213,25 @@ class Model:
         self._check(self._lib.omni_duplex_close(self._h, session._h))
         session._h = None
 
-    # -- Model::start (model.rs:325-370), prompts that are not cached --
+    def _prompt_arrays(self, prompt: "Prompt"):
+        ids = np.ascontiguousarray(np.asarray(prompt.rows, dtype=np.int32).reshape(-1, STREAMS))
+        voice = None if prompt.voice is None else np.ascontiguousarray(np.asarray(prompt.voice, dtype=np.int32))
+        return ids, voice
+
+    # -- Model::is_cached / warm_prefix (model.rs:243-259) --
+    def is_cached(self, prompt: "Prompt") -> bool:
+        ids, voice = self._prompt_arrays(prompt)
+        i32p = C.POINTER(C.c_int32)
+        return bool(self._lib.omni_duplex_is_cached(self._h, len(ids), ids.ctypes.data_as(i32p),
+                                                    voice.ctypes.data_as(i32p) if voice is not None else None))
+
+    def warm_prefix(self, prompt: "Prompt"):
+        ids, voice = self._prompt_arrays(prompt)
+        i32p = C.POINTER(C.c_int32)
+        self._check(self._lib.omni_duplex_warm_prefix(self._h, len(ids), ids.ctypes.data_as(i32p),
+                                                      voice.ctypes.data_as(i32p) if voice is not None else None))
+
+    # -- Model::start (model.rs:325-370) --
     def start(self, rows: Sequence[tuple]):
         """rows: [(session, prompt)]."""
         n = len(rows)

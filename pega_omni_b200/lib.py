@@ -121,6 +121,8 @@ SYMBOLS = {
     "omni_duplex_open": (I32, [VP, P(VP)]),
     "omni_duplex_close": (I32, [VP, VP]),
     "omni_duplex_position": (I32, [VP, P(I32), P(C.c_int64)]),
+    "omni_duplex_is_cached": (I32, [VP, I32, P(I32), P(I32)]),
+    "omni_duplex_warm_prefix": (I32, [VP, I32, P(I32), P(I32)]),
     "omni_duplex_start": (I32, [VP, I32, P(VP), P(I32), P(I32), P(I32), P(I32), P(I32)]),
     "omni_duplex_tick": (I32, [VP, I32, P(VP), P(DuplexStep), P(I32)]),
     "omni_duplex_read": (I32, [VP, I32, I32, VP, C.c_size_t]),

@@ -171,3 +171,80 @@ def test_leases_and_validation(built_lib):
         Model.load(0, missing, c, max_sessions=2)
     assert e3.value.status == -4
     m.close()
+
+
+def test_prefix_cache_copies_instead_of_prefilling(built_lib):
+    """`warm_prefix` / `is_cached` / `start` (model.rs:243-370): a prompt is prefilled once into the cache; every
+    session started with the same rows gets the cached keys and values copied into its ring, so sessions with the same
+    prompt and seeds stay bit-identical, whether they start together or later; a different prompt is not confused
+    with it; prompts longer than 256 rows and a ninth distinct prompt are prefilled directly."""
+    import dataclasses
+    from pega_omni_b200.duplex import PRESETS, Model, Prompt, Step, random_checkpoint
+    c = dataclasses.replace(PRESETS["duplex-tiny"], context=400)
+    ck = random_checkpoint(c, seed=5, voice_rows=3, head_std=0.3)
+    m = Model.load(0, ck, c, max_sessions=12, max_prefill=600)
+    rng = np.random.default_rng(9)
+    p = make_prompt(c, rng, 21, voice_rows=3)
+    q = make_prompt(c, rng, 21, voice_rows=3)
+    assert not m.is_cached(p)
+    m.warm_prefix(p)
+    assert m.is_cached(p) and not m.is_cached(q)
+    a, b, x = m.open(), m.open(), m.open()
+    m.start([(a, p), (x, q), (b, p)])
+    assert m.is_cached(q)
+    callers = [[int(v) for v in rng.integers(0, c.card, 8)] for _ in range(4)]
+    first = []
+    for t in range(4):
+        st = Step(caller=callers[t], seed=t + 3)
+        out = m.tick([(a, st), (x, st), (b, st)])
+        assert np.array_equal(out.emitted[0], out.emitted[2])
+        assert np.array_equal(m.text_logits(0), m.text_logits(2)) and np.array_equal(m.audio_logits(0), m.audio_logits(2))
+        first.append((out.emitted[0].copy(), m.text_logits(0).copy()))
+    late = m.open()  # a later session with the same prompt reads the same cached prefix
+    m.start([(late, p)])
+    for t in range(4):
+        out = m.tick([(late, Step(caller=callers[t], seed=t + 3))])
+        assert np.array_equal(out.emitted[0], first[t][0]) and np.array_equal(m.text_logits(0), first[t][1])
+    # not eligible: longer than 256 rows
+    long_prompt = make_prompt(c, rng, 300)
+    s = m.open()
+    m.start([(s, long_prompt)])
+    assert not m.is_cached(long_prompt) and s.pos == 300
+    # the cache holds eight prompts; the ninth distinct one is prefilled directly and stays uncached
+    others = [make_prompt(c, rng, 5) for _ in range(7)]
+    for o in others:
+        m.warm_prefix(o)
+    assert all(m.is_cached(o) for o in others[:6]) and not m.is_cached(others[6])
+    s2 = m.open()
+    m.start([(s2, others[6])])
+    out = m.tick([(s2, Step(seed=1))])
+    assert out.emitted.shape == (1, 9) and not m.is_cached(others[6])
+    m.close()
+
+
+def test_cached_start_matches_direct_prefill_against_oracle(built_lib):
+    """The copied prefix is the prefilled one: teacher-forced ticks after a cached start still match the oracle."""
+    from oracle.duplex import DuplexOracle
+    from pega_omni_b200.duplex import PRESETS, Model, random_checkpoint
+    c = PRESETS["duplex-tiny"]
+    ck = random_checkpoint(c, seed=6, head_std=0.15)
+    m = Model.load(0, ck, c, max_sessions=4, max_prefill=64)
+    orc = DuplexOracle(c, ck)
+    rng = np.random.default_rng(10)
+    p = make_prompt(c, rng, 9)
+    g1, g2 = m.open(), m.open()
+    o1, o2 = orc.open(), orc.open()
+    m.start([(g1, p), (g2, p)])
+    assert m.is_cached(p)
+    orc.start([(o1, p), (o2, p)])
+    for t in range(4):
+        steps = [forced_step(c, rng, seed=t), forced_step(c, rng, seed=t + 50)]
+        out = m.tick(list(zip([g1, g2], steps)))
+        want = orc.tick(list(zip([o1, o2], steps)))
+        assert np.array_equal(out.emitted, want)
+        for i in range(2):
+            ref = orc.text_logits[i]
+            step = np.exp2(np.floor(np.log2(np.maximum(np.abs(ref), 2.0))) - 7)
+            assert float((np.abs(m.text_logits(i) - ref) / step).max()) <= 2.0
+            assert cosine(m.audio_logits(i), orc.audio_logits[i]) >= 0.9995
+    m.close()
