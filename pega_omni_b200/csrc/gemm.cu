@@ -126,6 +126,48 @@ struct TcShape {
   static constexpr size_t kSmemBytes = (size_t)kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
 };
 
+// The last CTA of a tile sums the splits' partial tiles ([column][128 lanes] f32 each) in split order and stages the
+// finished bf16 tile. This is a chain of L2 round trips on one CTA, so each trip carries as much as the registers
+// hold: PER column chunks of 16 at a time, 8 / PER splits of each (PER = 4, 2, 1 for at most 2, 4, 8+ splits).
+template <int BN, int PER>
+__device__ __forceinline__ void reduce_tile(const float* partial0, size_t split_stride, int splits, int tl, int n, int N,
+                                            const bf16* bias, int kind, bf16* stage) {
+  constexpr int SB = 8 / PER;
+#pragma unroll 1
+  for (int c0 = 0; c0 < BN; c0 += 16 * PER) {
+    float acc[PER][16];
+#pragma unroll
+    for (int q = 0; q < PER; ++q)
+#pragma unroll
+      for (int j = 0; j < 16; ++j) acc[q][j] = 0.f;
+    for (int s0 = 0; s0 < splits; s0 += SB) {
+      float f[PER][SB][16];
+#pragma unroll
+      for (int q = 0; q < PER; ++q)
+#pragma unroll
+        for (int b = 0; b < SB; ++b) {
+          const bool live = s0 + b < splits && c0 + q * 16 < BN;
+          const float* p = partial0 + (size_t)(s0 + b) * split_stride + (size_t)(c0 + q * 16) * kTileW + tl;
+#pragma unroll
+          for (int j = 0; j < 16; ++j) f[q][b][j] = live ? __ldcg(p + j * kTileW) : 0.f;
+        }
+#pragma unroll
+      for (int q = 0; q < PER; ++q)
+#pragma unroll
+        for (int b = 0; b < SB; ++b)  // adding 0 for a missing split leaves the sum unchanged
+#pragma unroll
+          for (int j = 0; j < 16; ++j) acc[q][j] += f[q][b][j];
+    }
+#pragma unroll
+    for (int q = 0; q < PER; ++q)
+      if (c0 + q * 16 < BN) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j)
+          stage[(c0 + q * 16 + j) * kTileW + tl] = n < N ? finish(acc[q][j], n, bias, kind) : __float2bfloat16(0.f);
+      }
+  }
+}
+
 template <int BN>
 __global__ void __launch_bounds__(128, 1)
     gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap xmap,
@@ -268,24 +310,12 @@ __global__ void __launch_bounds__(128, 1)
     if (is_last) {
       __threadfence();
       // sum the splits in index order: the result does not depend on which CTA arrived last
-#pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 16) {
-        float acc[16];
-#pragma unroll
-        for (int j = 0; j < 16; ++j) acc[j] = 0.f;
-#pragma unroll 2
-        for (int s = 0; s < splits; ++s) {
-          const float* p = partial0 + s * split_stride + (size_t)c0 * kTileW + tl;
-          float f[16];
-#pragma unroll
-          for (int j = 0; j < 16; ++j) f[j] = __ldcg(p + j * kTileW);
-#pragma unroll
-          for (int j = 0; j < 16; ++j) acc[j] += f[j];
-        }
-#pragma unroll
-        for (int j = 0; j < 16; ++j)
-          stage[(c0 + j) * kTileW + tl] = n < N ? finish(acc[j], n, bias, kind) : __float2bfloat16(0.f);
-      }
+      if (splits <= 2)
+        reduce_tile<BN, 4>(partial0, split_stride, splits, tl, n, N, bias, kind, stage);
+      else if (splits <= 4)
+        reduce_tile<BN, 2>(partial0, split_stride, splits, tl, n, N, bias, kind, stage);
+      else
+        reduce_tile<BN, 1>(partial0, split_stride, splits, tl, n, N, bias, kind, stage);
       write_out = true;
     }
   }
@@ -367,6 +397,8 @@ int tc_plan(TcGemmPlan* plan, const bf16* w, int N, int K, const bf16* x, int ro
   int splits = force_splits > 0 ? force_splits : std::max(1, sm_count / ctas);
   // at least four K blocks per split (two when forced): below that the reduction costs more than it spreads
   splits = std::max(1, std::min(splits, force_splits > 0 ? nkb / 2 : nkb / 4));
+  // the last CTA's reduction is a serial chain of L2 round trips: at most 8 splits, 4 for wide row tiles
+  if (force_splits <= 0) splits = std::min(splits, p.BN >= 128 ? 4 : 8);
   p.splits = splits;
   if (encode_kmajor(&p.wmap, w, N, K, kTileW) != 0) return -4;
   if (encode_kmajor(&p.xmap, x, rows, K, p.BN) != 0) return -4;
