@@ -188,6 +188,76 @@ def run_reference(args, rank):
     print(json.dumps(line), flush=True)
 
 
+def run_higgs(args, rank, world, local):
+    """The Higgs-style step (36-layer h2560 20q/4kv body, 8 x 1026 tied head) at `--sessions` sequences per GPU with
+    `--prompt`-token prompts: W warm-up steps, K timed steps through `HiggsModel.step`; device time per step from the
+    library's CUDA events. Per-op launches, no CUDA graph."""
+    import torch
+    import torch.distributed as dist
+    from pega_omni_b200.higgs import HIGGS_PRESETS, HiggsDraw, HiggsModel, higgs_random_checkpoint
+    W, K = max(3, args.warmup), args.steps
+    n = args.sessions if args.sessions != 64 else 32  # configs[4]: 32 sessions
+    plen = args.prompt if args.prompt != 128 else 256
+    c = HIGGS_PRESETS["higgs-4b"]
+    ck = higgs_random_checkpoint(c, seed=0, device=f"cuda:{local}", embed_std=0.02)
+    b = c.body
+    kv_token = b.num_hidden_layers * 2 * b.num_key_value_heads * b.head_dim * 2
+    kv_gib = 1.3 * n * (plen + W + K + 32) * kv_token / 2 ** 30
+    model = HiggsModel.load(local, ck, c, max_batch=n, max_tokens=max(2048, plen), kv_gib=max(kv_gib, 0.5))
+    del ck
+    torch.cuda.empty_cache()
+    rng = np.random.default_rng(200 + rank)
+    seqs = [model.open(plen, W + K + 16) for _ in range(n)]
+    per_call = max(1, 2048 // plen)
+    for i in range(0, n, per_call):
+        part = seqs[i:i + per_call]
+        prompts = [rng.integers(0, b.vocab_size, plen).astype(np.int32) for _ in part]
+        model.start([(s, p, HiggsDraw([float(v) for v in rng.random(8)])) for s, p in zip(part, prompts)])
+
+    def draws():
+        return [HiggsDraw([float(v) for v in rng.random(8)]) for _ in range(n)]
+
+    for _ in range(W):
+        model.step(list(zip(seqs, draws())))
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    dev_ms, launches = [], 0
+    t0 = time.perf_counter()
+    with ClockSampler(local) as clocks:
+        for _ in range(K):
+            model.step(list(zip(seqs, draws())))
+            ms, launches = model.stats()
+            dev_ms.append(ms)
+    torch.cuda.synchronize()
+    wall = time.perf_counter() - t0
+    t_wall = torch.tensor([wall], device="cuda", dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t_wall, op=dist.ReduceOp.MAX)
+    if rank == 0:
+        peak, peak_kind = measured_peaks()
+        mean_len = plen + 1 + W + (K - 1) / 2 + 1
+        step_bytes = c.step_weight_bytes() + n * mean_len * kv_token
+        step_s = float(np.mean(dev_ms)) * 1e-3
+        print(json.dumps({
+            "metric": "Higgs-style step ms (device) at %d sequences per GPU" % n, "value": float(np.mean(dev_ms)),
+            "unit": "ms", "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": 1e3 * float(t_wall.item()) / K,
+            "higher_is_better": False, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "configs[4]: Higgs-style body (36L h2560 20q/4kv d128 i9728) + tied 8 x 1026 head, "
+                                   "random bf16 weights", "sessions_per_gpu": n, "prompt_tokens": plen,
+                       "sampling": "T 1.0, top-k 50, delay-pattern ramp",
+                       "engine": "per-op launches (no CUDA graph, no persistent kernel yet)"},
+            "step_p50_ms": float(np.percentile(dev_ms, 50)), "step_p99_ms": float(np.percentile(dev_ms, 99)),
+            "rows_per_s": n * world * K / float(t_wall.item()),
+            "gpu_launches": int(launches * K), "launches_per_step": int(launches), "clocks": clocks.summary(),
+            "roofline": {"bound": "hbm", "kernel": "whole step (%d launches)" % launches,
+                         "achieved": step_bytes / step_s / 1e9, "peak": peak, "unit": "GB/s",
+                         "frac": step_bytes / step_s / 1e9 / peak, "peak_source": f"of {peak_kind}", "traffic": None},
+            "reference_published": "about 9 ms per step at 1 sequence on a 48 GB sm_89 card "
+                                   "(docs/higgs-audio.md:127-137 of the reference)"}))
+    model.close()
+
+
 def run_duplex(args, rank, world, local):
     """The PersonaPlex-7B tick (Helium 32 x 4096 + depformer 8 x 6 x 1024) at `--sessions` sessions per GPU: W warm-up
     ticks, K timed ticks through `Model.tick` (host staging and read-back inside), CUDA-event device time per tick from
@@ -273,8 +343,9 @@ def main():
     ap.add_argument("--no-graphs", action="store_true")
     ap.add_argument("--no-replay", action="store_true", help="skip timing the reference's kernels on this GPU")
     ap.add_argument("--per-op", action="store_true", help="one kernel per op (CUDA graph) instead of the tick kernel")
-    ap.add_argument("--workload", default="talker", choices=["talker", "duplex"],
-                    help="talker: the headline Qwen3-TTS tick (default); duplex: the PersonaPlex-7B tick (configs[3])")
+    ap.add_argument("--workload", default="talker", choices=["talker", "duplex", "higgs"],
+                    help="talker: the headline Qwen3-TTS tick (default); duplex: the PersonaPlex-7B tick (configs[3]); "
+                         "higgs: the Higgs-style 4B step (configs[4])")
     ap.add_argument("--context", type=int, default=3000, help="duplex: KV ring length")
     args = ap.parse_args()
 
@@ -295,6 +366,9 @@ def main():
 
     if args.workload == "duplex":
         run_duplex(args, rank, world, local)
+        return
+    if args.workload == "higgs":
+        run_higgs(args, rank, world, local)
         return
 
     from pega_omni_b200 import replicas

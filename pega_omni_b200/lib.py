@@ -1,4 +1,5 @@
-"""ctypes binding of ``libomni_b200.so`` (declarations of include/omni_b200.h, omni_b200_ops.h and omni_b200_duplex.h).
+"""ctypes binding of ``libomni_b200.so`` (declarations of include/omni_b200.h, omni_b200_ops.h, omni_b200_duplex.h and
+omni_b200_higgs.h).
 
 Loading fails loudly when the library is missing: there is no fallback path.
 """
@@ -61,6 +62,15 @@ class DuplexStep(C.Structure):
                 ("seed", C.c_uint64)]
 
 
+class HiggsCfg(C.Structure):
+    _fields_ = [("body", StackCfg), ("code_vocab", C.c_int32), ("temperature", C.c_float), ("top_k", C.c_int32),
+                ("max_batch", C.c_int32), ("max_tokens", C.c_int32), ("kv_gib", C.c_double)]
+
+
+class HiggsDraw(C.Structure):
+    _fields_ = [("uniforms", C.c_float * 8), ("force", C.c_int32 * 8), ("has_force", C.c_int32)]
+
+
 class HiggsDelay(C.Structure):
     _fields_ = [("steps", C.c_int32), ("countdown", C.c_int32), ("done", C.c_int32)]
 
@@ -115,6 +125,16 @@ SYMBOLS = {
     "omni_higgs_delay_forced_from": (I32, [P(HiggsDelay)]),
     "omni_higgs_delay_advance": (I32, [P(HiggsDelay), I32]),
     "omni_higgs_undelay": (I32, [P(I32), I32, P(I32)]),
+    "omni_higgs_create": (I32, [P(HiggsCfg), P(Tensor), I32, I32, P(VP)]),
+    "omni_higgs_destroy": (None, [VP]),
+    "omni_higgs_last_error": (C.c_char_p, [VP]),
+    "omni_higgs_open": (I32, [VP, I32, I32, P(VP)]),
+    "omni_higgs_close": (I32, [VP, VP]),
+    "omni_higgs_seq_rows": (I32, [VP]),
+    "omni_higgs_start": (I32, [VP, I32, P(VP), P(I32), P(I32), P(HiggsDraw), P(I32), P(I32)]),
+    "omni_higgs_step": (I32, [VP, I32, P(VP), P(HiggsDraw), P(I32), P(I32)]),
+    "omni_higgs_read_logits": (I32, [VP, I32, VP, C.c_size_t]),
+    "omni_higgs_stats": (I32, [VP, P(C.c_float), P(I32)]),
     "omni_duplex_create": (I32, [P(DuplexCfg), P(Tensor), I32, I32, P(VP)]),
     "omni_duplex_destroy": (None, [VP]),
     "omni_duplex_last_error": (C.c_char_p, [VP]),

@@ -99,3 +99,122 @@ def test_code_draws_are_bit_exact(ref, ops, temperature, top_k):
     assert same.float().mean() >= 0.995, (ca[~same], cb[~same])
     assert torch.equal(sa.view(-1, stride // 4)[:, :8][lines.long()], ca)
     assert ((force < 0) | (ca == force)).all()
+
+
+def _cos(a, b):
+    a, b = a.astype(np.float64).ravel(), b.astype(np.float64).ravel()
+    return float(a @ b / (np.linalg.norm(a) * np.linalg.norm(b) + 1e-30))
+
+
+@pytest.mark.parametrize("preset,n", [("higgs-tiny", 3), ("higgs-mid", 10)])
+def test_model_steps_match_oracle(built_lib, oracle_lib, preset, n):
+    """The Higgs model shell (prefill, first draw, decode steps) against the CPU oracle with forced rows: codes exact,
+    logits of every step within two bf16 steps; 3 sequences take the vector GEMM path, 10 the tensor-core path; both
+    presets have 5 query heads per kv head like the full model."""
+    from oracle.higgs import HiggsOracle
+    from pega_omni_b200.higgs import HIGGS_PRESETS, HiggsDraw, HiggsModel, higgs_random_checkpoint
+    c = HIGGS_PRESETS[preset]
+    # the tied table is also the head: N(0, 0.06) keeps logits at |x| < 4, where a bf16 step is at most 1.6e-2
+    ck = higgs_random_checkpoint(c, seed=1, embed_std=0.06)
+    m = HiggsModel.load(0, ck, c, max_batch=16, max_tokens=512, kv_gib=0.05)
+    orc = HiggsOracle(c, ck)
+    rng = np.random.default_rng(3)
+    lens = [int(rng.integers(3, 20)) for _ in range(n)]
+    prompts = [rng.integers(0, c.body.vocab_size, k).astype(np.int32) for k in lens]
+    gs = [m.open(k, 12) for k in lens]
+    os_ = [orc.open(k, 12) for k in lens]
+    worst, over, count = 0.0, 0, 0
+    for t in range(6):
+        draws = [HiggsDraw([0.5] * 8, [int(v) for v in rng.integers(0, c.code_vocab, 8)]) for _ in range(n)]
+        if t == 0:
+            out = m.start(list(zip(gs, prompts, draws)))
+            want, ended = orc.start(list(zip(os_, prompts, draws)))
+        else:
+            out = m.step(list(zip(gs, draws)))
+            want, ended = orc.step(list(zip(os_, draws)))
+        assert np.array_equal(out.rows, want) and np.array_equal(out.ended, ended)
+        for i in range(n):
+            got, ref = m.logits(i), orc.logits[i]
+            step = np.exp2(np.floor(np.log2(np.maximum(np.abs(ref), 2.0))) - 7)
+            steps = np.abs(got - ref) / step
+            worst, over, count = max(worst, float(steps.max())), over + int((steps > 2.0).sum()), count + steps.size
+            assert _cos(got, ref) >= 0.9999
+    # half a million bf16 logits per run: all but one in a thousand within two bf16 steps of the oracle's, none beyond
+    # three (different f32 summation orders through two or three bf16-rounded layers, with logits stored as bf16)
+    assert worst <= 3.0 and over <= count * 1e-3, (worst, over, count)
+    assert gs[0].rows == 6
+    m.close()
+
+
+def test_free_running_draws_follow_the_delay_pattern(built_lib, oracle_lib):
+    """Without forced rows the ramp decides which codebooks draw: row t has BOC from codebook t + 1 on, the draws equal
+    the oracle's on the GPU's own logits, and an EOC in codebook 0 past the ramp ends the run six steps later."""
+    from oracle import cpu
+    from pega_omni_b200.higgs import BOC, EOC, HIGGS_PRESETS, HiggsDraw, HiggsModel, higgs_random_checkpoint, undelay
+    c = HIGGS_PRESETS["higgs-tiny"]
+    ck = higgs_random_checkpoint(c, seed=2)
+    m = HiggsModel.load(0, ck, c, max_batch=4, max_tokens=64, kv_gib=0.02)
+    rng = np.random.default_rng(4)
+    prompt = rng.integers(0, c.body.vocab_size, 7).astype(np.int32)
+    s = m.open(7, 40)
+    rows, total, same = [], 0, 0
+    ended_at = None
+    for t in range(30):
+        u = rng.random(8).astype(np.float32)
+        force = None
+        if t == 12:  # make codebook 0 end the run here: the countdown then takes CODEBOOKS - 2 more steps
+            force = [EOC] + [-1] * 7
+        d = HiggsDraw([float(v) for v in u], force)
+        out = m.start([(s, prompt, d)]) if t == 0 else m.step([(s, d)])
+        row = out.rows[0]
+        rows.append(row.copy())
+        if t < 7:
+            assert (row[t + 1:] == BOC).all()
+        logits = m.logits(0)
+        for b in range(8):
+            if (t < 7 and b > t) or (force is not None and force[b] >= 0):
+                continue
+            last, seen = np.zeros(16, np.int32), np.zeros(64, np.uint32)
+            want = cpu.sample(logits[b], c.temperature, c.top_k, 1.0, 1.0, 0, 0, -1, 0, 0, float(u[b]), -1, last, seen,
+                              False, b)
+            total += 1
+            same += int(want == row[b])
+        if out.ended[0]:
+            ended_at = t
+            break
+    assert ended_at == 12 + 6, ended_at
+    assert same >= total * 0.98, (same, total)
+    frames = undelay(np.array(rows))
+    assert frames.shape == (len(rows) - 7, 8) and frames[0][0] == rows[0][0] and frames[0][7] == rows[7][7]
+    m.close()
+
+
+def test_higgs_leases_and_validation(built_lib):
+    from pega_omni_b200.higgs import HIGGS_PRESETS, HiggsDraw, HiggsModel, higgs_random_checkpoint
+    from pega_omni_b200.model import Denied, OmniError
+    c = HIGGS_PRESETS["higgs-tiny"]
+    ck = higgs_random_checkpoint(c, seed=3)
+    m = HiggsModel.load(0, ck, c, max_batch=2, max_tokens=32, kv_gib=0.0005)
+    with pytest.raises(Denied) as e:
+        m.open(100000, 10)
+    assert e.value.kind == "exceeds_pool"
+    a = m.open(5, 3)
+    with pytest.raises(OmniError):  # not started
+        m.step([(a, HiggsDraw())])
+    with pytest.raises(OmniError):  # prompt length differs from the lease's
+        m.start([(a, np.zeros(4, np.int32), HiggsDraw())])
+    with pytest.raises(OmniError):  # token outside the vocabulary
+        m.start([(a, np.full(5, 10 ** 6, np.int32), HiggsDraw())])
+    out = m.start([(a, np.arange(5, dtype=np.int32), HiggsDraw())])
+    assert out.rows.shape == (1, 8) and not out.ended[0]
+    m.step([(a, HiggsDraw())])
+    m.step([(a, HiggsDraw())])
+    with pytest.raises(OmniError):  # past the rows it leased
+        m.step([(a, HiggsDraw())])
+    m.release(a)
+    missing = dict(ck)
+    del missing["body.norm.weight"]
+    with pytest.raises(OmniError) as e2:
+        HiggsModel.load(0, missing, c)
+    assert e2.value.status == -4
+    m.close()
