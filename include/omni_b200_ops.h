@@ -18,7 +18,12 @@ extern "C" {
 
 typedef struct omni_ops omni_ops;
 
-enum omni_gemm_path { OMNI_GEMM_AUTO = 0, OMNI_GEMM_VECTOR = 1, OMNI_GEMM_TENSOR = 2 };
+enum omni_gemm_path {
+  OMNI_GEMM_AUTO = 0,
+  OMNI_GEMM_VECTOR = 1,
+  OMNI_GEMM_TENSOR = 2,      /* weights on the MMA M dimension, split-K */
+  OMNI_GEMM_TENSOR_ROWS = 3  /* input rows on the MMA M dimension (rows <= 128, K <= 4096), no split */
+};
 enum omni_epilogue { OMNI_EPI_NONE = 0, OMNI_EPI_BIAS = 1, OMNI_EPI_BIAS_SILU = 2 };
 
 int32_t omni_ops_create(int32_t device, omni_ops** out);

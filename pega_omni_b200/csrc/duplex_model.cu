@@ -100,6 +100,7 @@ struct omni_duplex {
 
   GemmScratch scratch;
   std::map<std::tuple<const void*, const void*, const void*, int>, TcGemmPlan> plans;
+  std::map<std::tuple<const void*, const void*, const void*, int>, RmGemmPlan> rm_plans;
 
   int fail(int code, const char* fmt, ...) {
     char buf[512];
@@ -189,6 +190,17 @@ int gemm(omni_duplex* m, const bf16* w, int N, int K, const bf16* x, int rows, b
     return OMNI_OK;
   }
   const auto key = std::make_tuple((const void*)w, (const void*)x, (const void*)y, rows);
+  if (rm_supports(N, K, rows)) {  // decode-sized: input rows on the MMA M dimension, no split and no reduction
+    auto rt = m->rm_plans.find(key);
+    if (rt == m->rm_plans.end()) {
+      RmGemmPlan plan;
+      const int rc = rm_plan(&plan, w, N, K, x, rows, y, ldy, Epilogue{}, m->sm_count);
+      if (rc != 0) return m->fail(OMNI_ERR_CUDA, "tensor-map encode failed (%d) for N=%d K=%d rows=%d", rc, N, K, rows);
+      rt = m->rm_plans.emplace(key, plan).first;
+    }
+    DLAUNCH(m, rm_launch(rt->second, m->err, m->stream));
+    return OMNI_OK;
+  }
   auto it = m->plans.find(key);
   if (it == m->plans.end()) {
     TcGemmPlan plan;

@@ -339,6 +339,127 @@ __global__ void __launch_bounds__(128, 1)
   }
 }
 
+// ---------------------------------------------------------------------------
+// Tensor-core tiles with the input rows on the MMA M dimension (at most 128 of them) and TN weight rows on N: one CTA
+// computes y[:, tile] over the whole K, so there is no split, no partial tile and no reduction. A tcgen05.mma costs
+// the same whatever N is, so this orientation needs K/16 instructions per CTA where the kernel above needs
+// K/16 per 128 weight rows per split: it is the faster one for the decode-sized GEMMs of the secondary model shells
+// (at most 128 sessions, K up to 4096), whose small matrices the split-K kernel cannot spread without paying a serial
+// reduction per tile.
+//   warp 0 / lane 0: TMA producer, a ring of {X tile 128 x 64, W tile TN x 64};  warp 1 / lane 0: MMA issuer;
+//   all four warps: epilogue, a thread owns one output row (its TMEM lane) and writes it 16 columns at a time.
+
+template <int TN>
+struct RmShape {
+  static constexpr int kStageBytes = 128 * kTileK * 2 + TN * kTileK * 2;
+  static constexpr int kStages = (192 * 1024 / kStageBytes) > 8 ? 8 : (192 * 1024 / kStageBytes);
+  static constexpr size_t kSmemBytes = (size_t)kStages * kStageBytes + 1024 + 256;
+};
+
+template <int TN>
+__global__ void __launch_bounds__(128, 1)
+    gemm_rm_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap xmap,
+                   bf16* __restrict__ y, int ldy, int N, int K, int rows, const bf16* bias, int kind, uint32_t* err) {
+  using S = RmShape<TN>;
+  using namespace sm100;
+  if (*reinterpret_cast<volatile uint32_t*>(err) != 0) return;
+  extern __shared__ unsigned char rm_smem_raw[];
+  const uint32_t raw = smem_addr(rm_smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  unsigned char* base_ptr = rm_smem_raw + (base - raw);
+  const uint32_t bars = base + S::kStages * S::kStageBytes;
+  auto full_bar = [&](int s) { return bars + 8u * s; };
+  auto empty_bar = [&](int s) { return bars + 8u * (S::kStages + s); };
+  const uint32_t acc_bar = bars + 8u * (2 * S::kStages);
+  const uint32_t tmem_slot = acc_bar + 8u;
+  volatile uint32_t* tmem_slot_ptr =
+      reinterpret_cast<volatile uint32_t*>(base_ptr + S::kStages * S::kStageBytes + 8 * (2 * S::kStages) + 8);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tile = blockIdx.x, nkb = K / kTileK;
+  constexpr uint32_t kCols = TN < 32 ? 32 : TN;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S::kStages; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    mbar_init(acc_bar, 1);
+    mbar_init_fence();
+    prefetch_tensormap(&wmap);
+    prefetch_tensormap(&xmap);
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, kCols);
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot_ptr;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int kb = 0; kb < nkb; ++kb) {
+        if (!mbar_wait(empty_bar(stage), phase ^ 1u, err)) break;
+        const uint32_t a_dst = base + stage * S::kStageBytes, b_dst = a_dst + 128 * kTileK * 2;
+        mbar_expect_tx(full_bar(stage), S::kStageBytes);
+        tma_load_2d(a_dst, &xmap, full_bar(stage), kb * kTileK, 0, kEvictLast);
+        tma_load_2d(b_dst, &wmap, full_bar(stage), kb * kTileK, tile * TN, kEvictFirst);
+        if (++stage == S::kStages) stage = 0, phase ^= 1u;
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = idesc_bf16_f32(128, TN);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool alive = true;
+      for (int kb = 0; kb < nkb && alive; ++kb) {
+        alive = mbar_wait(full_bar(stage), phase, err);
+        if (!alive) break;
+        tc_fence_after_sync();
+        const uint32_t a_src = base + stage * S::kStageBytes, b_src = a_src + 128 * kTileK * 2;
+        const uint64_t adesc = kmajor_sw128_desc(a_src), bdesc = kmajor_sw128_desc(b_src);
+#pragma unroll
+        for (int k = 0; k < kTileK / 16; ++k)
+          mma_bf16(tmem_base, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+        mma_commit(empty_bar(stage));
+        if (++stage == S::kStages) stage = 0, phase ^= 1u;
+      }
+      if (alive) mma_commit(acc_bar);
+    }
+    __syncwarp();
+  }
+
+  const bool ok = mbar_wait(acc_bar, 0, err);
+  tc_fence_after_sync();
+  const int m = warp * 32 + lane;  // output row = TMEM lane
+  const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
+  if (ok && warp * 32 < rows) {
+    const int n0 = tile * TN;
+    const bool vec = (ldy % 8 == 0) && ((reinterpret_cast<uintptr_t>(y) & 15) == 0);
+#pragma unroll 2
+    for (int c0 = 0; c0 < TN; c0 += 16) {
+      float v[16];
+      tmem_ld16(lane_addr + c0, v);
+      if (m >= rows || n0 + c0 >= N) continue;
+      bf16* dst = y + (int64_t)m * ldy + n0 + c0;
+      if (vec && n0 + c0 + 16 <= N) {
+        float o[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) o[j] = __bfloat162float(finish(v[j], n0 + c0 + j, bias, kind));
+        st8(dst, o);
+        st8(dst + 8, o + 8);
+      } else {
+        for (int j = 0; j < 16 && n0 + c0 + j < N; ++j) dst[j] = finish(v[j], n0 + c0 + j, bias, kind);
+      }
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, kCols);
+}
+
 // --- host side ----------------------------------------------------------------
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -422,6 +543,9 @@ void tc_configure() {
   cudaFuncSetAttribute(gemm_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TcShape<64>::kSmemBytes);
   cudaFuncSetAttribute(gemm_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TcShape<128>::kSmemBytes);
   cudaFuncSetAttribute(gemm_tc_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TcShape<256>::kSmemBytes);
+  cudaFuncSetAttribute(gemm_rm_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)RmShape<64>::kSmemBytes);
+  cudaFuncSetAttribute(gemm_rm_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)RmShape<128>::kSmemBytes);
+  cudaFuncSetAttribute(gemm_rm_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)RmShape<256>::kSmemBytes);
   cudaFuncSetAttribute(gemv_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
   cudaFuncSetAttribute(gemv_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
   cudaFuncSetAttribute(gemv_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
@@ -439,6 +563,42 @@ cudaError_t tc_launch(const TcGemmPlan& p, const GemmScratch& s, uint32_t* err, 
     case 64: return tc_launch_bn<64>(p, s, err, stream);
     case 128: return tc_launch_bn<128>(p, s, err, stream);
     case 256: return tc_launch_bn<256>(p, s, err, stream);
+  }
+  return cudaErrorInvalidValue;
+}
+
+// ---- rows-on-M path ---------------------------------------------------------------
+
+bool rm_supports(int N, int K, int rows) {
+  return K % kTileK == 0 && K >= kTileK && K <= 4096 && rows >= 1 && rows <= 128 && N >= 1;
+}
+
+int rm_plan(RmGemmPlan* plan, const bf16* w, int N, int K, const bf16* x, int rows, bf16* y, int ldy, Epilogue epi,
+            int sm_count) {
+  if (tc_init() != 0) return -1;
+  if (!rm_supports(N, K, rows)) return -2;
+  if ((reinterpret_cast<uintptr_t>(w) & 15) || (reinterpret_cast<uintptr_t>(x) & 15)) return -3;
+  RmGemmPlan& p = *plan;
+  p.N = N, p.K = K, p.rows = rows, p.y = y, p.ldy = ldy, p.epi = epi;
+  // as many CTAs as the GPU has SMs, but not more: the narrowest tile whose count still fits one wave
+  p.TN = (N + 63) / 64 <= sm_count ? 64 : (N + 127) / 128 <= sm_count ? 128 : 256;
+  if (encode_kmajor(&p.wmap, w, N, K, p.TN) != 0) return -4;
+  if (encode_kmajor(&p.xmap, x, rows, K, 128) != 0) return -4;
+  return 0;
+}
+
+template <int TN>
+static cudaError_t rm_launch_tn(const RmGemmPlan& p, uint32_t* err, cudaStream_t stream) {
+  gemm_rm_kernel<TN><<<(p.N + TN - 1) / TN, 128, RmShape<TN>::kSmemBytes, stream>>>(
+      p.wmap, p.xmap, p.y, p.ldy, p.N, p.K, p.rows, p.epi.bias, p.epi.kind, err);
+  return cudaGetLastError();
+}
+
+cudaError_t rm_launch(const RmGemmPlan& p, uint32_t* err, cudaStream_t stream) {
+  switch (p.TN) {
+    case 64: return rm_launch_tn<64>(p, err, stream);
+    case 128: return rm_launch_tn<128>(p, err, stream);
+    case 256: return rm_launch_tn<256>(p, err, stream);
   }
   return cudaErrorInvalidValue;
 }

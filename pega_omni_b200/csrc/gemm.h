@@ -58,6 +58,20 @@ int tc_plan(TcGemmPlan* plan, const bf16* w, int N, int K, const bf16* x, int ro
             int sm_count, int force_splits = 0);
 cudaError_t tc_launch(const TcGemmPlan& plan, const GemmScratch& scratch, uint32_t* err, cudaStream_t stream);
 
+// The tensor-core path with the input rows on the MMA M dimension (rows <= 128, K <= 4096): one CTA per tile of TN
+// weight rows over the whole K, no split and no reduction. For decode-sized GEMMs with small weight matrices.
+struct RmGemmPlan {
+  CUtensorMap wmap, xmap;
+  int N = 0, K = 0, rows = 0, TN = 64;
+  bf16* y = nullptr;
+  int ldy = 0;
+  Epilogue epi;
+};
+bool rm_supports(int N, int K, int rows);
+int rm_plan(RmGemmPlan* plan, const bf16* w, int N, int K, const bf16* x, int rows, bf16* y, int ldy, Epilogue epi,
+            int sm_count);
+cudaError_t rm_launch(const RmGemmPlan& plan, uint32_t* err, cudaStream_t stream);
+
 cudaError_t gemv_launch(const bf16* w, int N, int K, const bf16* x, int rows, bf16* y, int ldy, Epilogue epi,
                         int sm_count, cudaStream_t stream);
 

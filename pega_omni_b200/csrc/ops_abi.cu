@@ -112,6 +112,14 @@ int32_t omni_op_gemm(omni_ops* c, const void* w, int32_t N, int32_t K, const voi
   Epilogue epi;
   epi.bias = static_cast<const bf16*>(bias);
   epi.kind = epilogue;
+  if (path == OMNI_GEMM_TENSOR_ROWS) {
+    if (!rm_supports(N, K, rows)) return c->fail(OMNI_ERR_UNSUPPORTED, "rows-on-M path needs rows <= 128, K %% 64 == 0, K <= 4096");
+    RmGemmPlan plan;
+    const int rc = rm_plan(&plan, (const bf16*)w, N, K, (const bf16*)x, rows, (bf16*)y, ldy, epi, c->sm_count);
+    if (rc != 0) return c->fail(OMNI_ERR_CUDA, "tensor-map encode failed (%d)", rc);
+    OPS_CUDA(c, rm_launch(plan, c->err, c->stream));
+    return OMNI_OK;
+  }
   const bool tensor = path == OMNI_GEMM_TENSOR || (path == OMNI_GEMM_AUTO && rows > 8 && tc_supports(N, K, rows));
   if (!tensor) {
     OPS_CUDA(c, gemv_launch((const bf16*)w, N, K, (const bf16*)x, rows, (bf16*)y, ldy, epi, c->sm_count, c->stream));

@@ -90,6 +90,21 @@ def test_gemm_bias_epilogues(ops, oracle_lib, path, epi):
     close_bf16(to_f32(y), t, ulps=2.0, floor=0.5)
 
 
+@pytest.mark.parametrize("rows,n,k", [(128, 1024, 1024), (128, 3072, 1024), (100, 1000, 2816), (32, 3584, 2560),
+                                      (9, 320, 256), (128, 22528, 4096), (64, 72, 64)])
+def test_gemm_rows_on_m(ops, oracle_lib, rows, n, k):
+    """The no-split tensor-core path (input rows on the MMA M dimension): ragged row counts, N not a multiple of the
+    tile, all three tile widths, a strided output."""
+    w, x = rand_bf16((n, k), 21, 0.05), rand_bf16((rows, k), 22)
+    big = torch.zeros((rows, n + 16), dtype=torch.bfloat16, device="cuda")
+    torch.cuda.synchronize()
+    ops.gemm(w, x, big[:, 8:8 + n], path=3)
+    ops.sync()
+    # outputs near zero are sums of thousands of O(0.05) products: the floor is the accumulator's scale
+    close_bf16(to_f32(big[:, 8:8 + n]), oracle_lib.gemm(to_f32(x), to_bits(w)), floor=0.05)
+    assert not big[:, :8].any() and not big[:, 8 + n:].any()
+
+
 def test_gemm_strided_output(ops, oracle_lib):
     # logits of group g land in a wider buffer (ldy > N), the way p_logits is addressed
     rows, n, k = 16, 256, 128
