@@ -491,7 +491,7 @@ def main():
         if not args.no_replay:
             model.close()
             torch.cuda.empty_cache()
-            rep = replay_baseline(cfg, ck, args.sessions, args.prompt, min(W, 8), min(K, 64))
+            rep = replay_baseline(cfg, ck, args.sessions, args.prompt, W, K)  # same positions as the arm above
             del ck
             if rep is not None:
                 line["reference_replay"] = rep
