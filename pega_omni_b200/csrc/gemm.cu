@@ -349,37 +349,42 @@ __global__ void __launch_bounds__(128, 1)
 //   warp 0 / lane 0: TMA producer, a ring of {X tile 128 x 64, W tile TN x 64};  warp 1 / lane 0: MMA issuer;
 //   all four warps: epilogue, a thread owns one output row (its TMEM lane) and writes it 16 columns at a time.
 
-template <int TN>
+// The tile width TN (weight rows per CTA, a multiple of 16 up to 256) is a launch parameter: the host picks the
+// narrowest one whose tile count still fits one wave, because what bounds a CTA here is the number of 128-byte tile
+// rows its TMA unit moves per k-block (128 activation rows + TN weight rows), so the weight rows should be spread over
+// every SM.
 struct RmShape {
-  static constexpr int kStageBytes = 128 * kTileK * 2 + TN * kTileK * 2;
-  static constexpr int kStages = (192 * 1024 / kStageBytes) > 8 ? 8 : (192 * 1024 / kStageBytes);
-  static constexpr size_t kSmemBytes = (size_t)kStages * kStageBytes + 1024 + 256;
+  static constexpr int kRingBytes = 192 * 1024;
+  static constexpr int kMaxStages = 8;
+  static constexpr size_t kSmemBytes = (size_t)kRingBytes + 1024 + 256;
+  static int stage_bytes(int tn) { return 128 * kTileK * 2 + tn * kTileK * 2; }
+  static int stages(int tn) { return std::min(kMaxStages, kRingBytes / stage_bytes(tn)); }
+  static uint32_t tmem_cols(int tn) { return tn <= 32 ? 32u : tn <= 64 ? 64u : tn <= 128 ? 128u : 256u; }
 };
 
-template <int TN>
 __global__ void __launch_bounds__(128, 1)
     gemm_rm_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap xmap,
-                   bf16* __restrict__ y, int ldy, int N, int K, int rows, const bf16* bias, int kind, uint32_t* err) {
-  using S = RmShape<TN>;
+                   bf16* __restrict__ y, int ldy, int N, int K, int rows, int tn, int n_stages, uint32_t tmem_cols,
+                   const bf16* bias, int kind, uint32_t* err) {
   using namespace sm100;
   if (*reinterpret_cast<volatile uint32_t*>(err) != 0) return;
   extern __shared__ unsigned char rm_smem_raw[];
   const uint32_t raw = smem_addr(rm_smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
   unsigned char* base_ptr = rm_smem_raw + (base - raw);
-  const uint32_t bars = base + S::kStages * S::kStageBytes;
+  const uint32_t stage_bytes = (uint32_t)(128 * kTileK * 2 + tn * kTileK * 2);
+  const uint32_t bars = base + RmShape::kRingBytes;
   auto full_bar = [&](int s) { return bars + 8u * s; };
-  auto empty_bar = [&](int s) { return bars + 8u * (S::kStages + s); };
-  const uint32_t acc_bar = bars + 8u * (2 * S::kStages);
+  auto empty_bar = [&](int s) { return bars + 8u * (RmShape::kMaxStages + s); };
+  const uint32_t acc_bar = bars + 8u * (2 * RmShape::kMaxStages);
   const uint32_t tmem_slot = acc_bar + 8u;
   volatile uint32_t* tmem_slot_ptr =
-      reinterpret_cast<volatile uint32_t*>(base_ptr + S::kStages * S::kStageBytes + 8 * (2 * S::kStages) + 8);
+      reinterpret_cast<volatile uint32_t*>(base_ptr + RmShape::kRingBytes + 8 * (2 * RmShape::kMaxStages) + 8);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tile = blockIdx.x, nkb = K / kTileK;
-  constexpr uint32_t kCols = TN < 32 ? 32 : TN;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < S::kStages; ++s) {
+    for (int s = 0; s < n_stages; ++s) {
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
     }
@@ -388,7 +393,7 @@ __global__ void __launch_bounds__(128, 1)
     prefetch_tensormap(&wmap);
     prefetch_tensormap(&xmap);
   }
-  if (warp == 1) tmem_alloc(tmem_slot, kCols);
+  if (warp == 1) tmem_alloc(tmem_slot, tmem_cols);
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
@@ -400,17 +405,17 @@ __global__ void __launch_bounds__(128, 1)
       uint32_t phase = 0;
       for (int kb = 0; kb < nkb; ++kb) {
         if (!mbar_wait(empty_bar(stage), phase ^ 1u, err)) break;
-        const uint32_t a_dst = base + stage * S::kStageBytes, b_dst = a_dst + 128 * kTileK * 2;
-        mbar_expect_tx(full_bar(stage), S::kStageBytes);
+        const uint32_t a_dst = base + stage * stage_bytes, b_dst = a_dst + 128 * kTileK * 2;
+        mbar_expect_tx(full_bar(stage), stage_bytes);
         tma_load_2d(a_dst, &xmap, full_bar(stage), kb * kTileK, 0, kEvictLast);
-        tma_load_2d(b_dst, &wmap, full_bar(stage), kb * kTileK, tile * TN, kEvictFirst);
-        if (++stage == S::kStages) stage = 0, phase ^= 1u;
+        tma_load_2d(b_dst, &wmap, full_bar(stage), kb * kTileK, tile * tn, kEvictFirst);
+        if (++stage == n_stages) stage = 0, phase ^= 1u;
       }
     }
     __syncwarp();
   } else if (warp == 1) {
     if (lane == 0) {
-      constexpr uint32_t idesc = idesc_bf16_f32(128, TN);
+      const uint32_t idesc = idesc_bf16_f32(128, tn);
       int stage = 0;
       uint32_t phase = 0;
       bool alive = true;
@@ -418,13 +423,13 @@ __global__ void __launch_bounds__(128, 1)
         alive = mbar_wait(full_bar(stage), phase, err);
         if (!alive) break;
         tc_fence_after_sync();
-        const uint32_t a_src = base + stage * S::kStageBytes, b_src = a_src + 128 * kTileK * 2;
+        const uint32_t a_src = base + stage * stage_bytes, b_src = a_src + 128 * kTileK * 2;
         const uint64_t adesc = kmajor_sw128_desc(a_src), bdesc = kmajor_sw128_desc(b_src);
 #pragma unroll
         for (int k = 0; k < kTileK / 16; ++k)
           mma_bf16(tmem_base, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2), idesc, (kb > 0 || k > 0) ? 1u : 0u);
         mma_commit(empty_bar(stage));
-        if (++stage == S::kStages) stage = 0, phase ^= 1u;
+        if (++stage == n_stages) stage = 0, phase ^= 1u;
       }
       if (alive) mma_commit(acc_bar);
     }
@@ -436,10 +441,10 @@ __global__ void __launch_bounds__(128, 1)
   const int m = warp * 32 + lane;  // output row = TMEM lane
   const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
   if (ok && warp * 32 < rows) {
-    const int n0 = tile * TN;
+    const int n0 = tile * tn;
     const bool vec = (ldy % 8 == 0) && ((reinterpret_cast<uintptr_t>(y) & 15) == 0);
 #pragma unroll 2
-    for (int c0 = 0; c0 < TN; c0 += 16) {
+    for (int c0 = 0; c0 < tn; c0 += 16) {
       float v[16];
       tmem_ld16(lane_addr + c0, v);
       if (m >= rows || n0 + c0 >= N) continue;
@@ -457,7 +462,7 @@ __global__ void __launch_bounds__(128, 1)
   }
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == 1) tmem_dealloc(tmem_base, kCols);
+  if (warp == 1) tmem_dealloc(tmem_base, tmem_cols);
 }
 
 // --- host side ----------------------------------------------------------------
@@ -543,9 +548,7 @@ void tc_configure() {
   cudaFuncSetAttribute(gemm_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TcShape<64>::kSmemBytes);
   cudaFuncSetAttribute(gemm_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TcShape<128>::kSmemBytes);
   cudaFuncSetAttribute(gemm_tc_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TcShape<256>::kSmemBytes);
-  cudaFuncSetAttribute(gemm_rm_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)RmShape<64>::kSmemBytes);
-  cudaFuncSetAttribute(gemm_rm_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)RmShape<128>::kSmemBytes);
-  cudaFuncSetAttribute(gemm_rm_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)RmShape<256>::kSmemBytes);
+  cudaFuncSetAttribute(gemm_rm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)RmShape::kSmemBytes);
   cudaFuncSetAttribute(gemv_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
   cudaFuncSetAttribute(gemv_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
   cudaFuncSetAttribute(gemv_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
@@ -580,27 +583,20 @@ int rm_plan(RmGemmPlan* plan, const bf16* w, int N, int K, const bf16* x, int ro
   if ((reinterpret_cast<uintptr_t>(w) & 15) || (reinterpret_cast<uintptr_t>(x) & 15)) return -3;
   RmGemmPlan& p = *plan;
   p.N = N, p.K = K, p.rows = rows, p.y = y, p.ldy = ldy, p.epi = epi;
-  // as many CTAs as the GPU has SMs, but not more: the narrowest tile whose count still fits one wave
-  p.TN = (N + 63) / 64 <= sm_count ? 64 : (N + 127) / 128 <= sm_count ? 128 : 256;
+  // the narrowest tile (a multiple of 16 weight rows) whose count still fits one wave of CTAs
+  const int per_sm = (N + sm_count - 1) / std::max(1, sm_count);
+  p.TN = std::min(256, std::max(16, (per_sm + 15) / 16 * 16));
   if (encode_kmajor(&p.wmap, w, N, K, p.TN) != 0) return -4;
   if (encode_kmajor(&p.xmap, x, rows, K, 128) != 0) return -4;
   return 0;
 }
 
-template <int TN>
-static cudaError_t rm_launch_tn(const RmGemmPlan& p, uint32_t* err, cudaStream_t stream) {
-  gemm_rm_kernel<TN><<<(p.N + TN - 1) / TN, 128, RmShape<TN>::kSmemBytes, stream>>>(
-      p.wmap, p.xmap, p.y, p.ldy, p.N, p.K, p.rows, p.epi.bias, p.epi.kind, err);
-  return cudaGetLastError();
-}
-
 cudaError_t rm_launch(const RmGemmPlan& p, uint32_t* err, cudaStream_t stream) {
-  switch (p.TN) {
-    case 64: return rm_launch_tn<64>(p, err, stream);
-    case 128: return rm_launch_tn<128>(p, err, stream);
-    case 256: return rm_launch_tn<256>(p, err, stream);
-  }
-  return cudaErrorInvalidValue;
+  if (p.TN < 16 || p.TN > 256 || p.TN % 16) return cudaErrorInvalidValue;
+  gemm_rm_kernel<<<(p.N + p.TN - 1) / p.TN, 128, RmShape::kSmemBytes, stream>>>(
+      p.wmap, p.xmap, p.y, p.ldy, p.N, p.K, p.rows, p.TN, RmShape::stages(p.TN), RmShape::tmem_cols(p.TN), p.epi.bias,
+      p.epi.kind, err);
+  return cudaGetLastError();
 }
 
 // ---------------------------------------------------------------------------

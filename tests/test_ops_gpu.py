@@ -91,7 +91,7 @@ def test_gemm_bias_epilogues(ops, oracle_lib, path, epi):
 
 
 @pytest.mark.parametrize("rows,n,k", [(128, 1024, 1024), (128, 3072, 1024), (100, 1000, 2816), (32, 3584, 2560),
-                                      (9, 320, 256), (128, 22528, 4096), (64, 72, 64)])
+                                      (9, 320, 256), (128, 22528, 4096), (64, 72, 64), (128, 12288, 4096), (77, 4096, 4096)])
 def test_gemm_rows_on_m(ops, oracle_lib, rows, n, k):
     """The no-split tensor-core path (input rows on the MMA M dimension): ragged row counts, N not a multiple of the
     tile, all three tile widths, a strided output."""
