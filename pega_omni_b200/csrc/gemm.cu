@@ -357,14 +357,14 @@ struct RmShape {
   static constexpr int kRingBytes = 192 * 1024;
   static constexpr int kMaxStages = 8;
   static constexpr size_t kSmemBytes = (size_t)kRingBytes + 1024 + 256;
-  static int stage_bytes(int tn) { return 128 * kTileK * 2 + tn * kTileK * 2; }
-  static int stages(int tn) { return std::min(kMaxStages, kRingBytes / stage_bytes(tn)); }
+  static int stage_bytes(int tn, int kbs) { return kbs * (128 * kTileK * 2 + tn * kTileK * 2); }
+  static int stages(int tn, int kbs) { return std::min(kMaxStages, kRingBytes / stage_bytes(tn, kbs)); }
   static uint32_t tmem_cols(int tn) { return tn <= 32 ? 32u : tn <= 64 ? 64u : tn <= 128 ? 128u : 256u; }
 };
 
 __global__ void __launch_bounds__(128, 1)
     gemm_rm_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap xmap,
-                   bf16* __restrict__ y, int ldy, int N, int K, int rows, int tn, int n_stages, uint32_t tmem_cols,
+                   bf16* __restrict__ y, int ldy, int N, int K, int rows, int tn, int kbs, int n_stages, uint32_t tmem_cols,
                    const bf16* bias, int kind, uint32_t* err) {
   using namespace sm100;
   if (*reinterpret_cast<volatile uint32_t*>(err) != 0) return;
@@ -372,7 +372,8 @@ __global__ void __launch_bounds__(128, 1)
   const uint32_t raw = smem_addr(rm_smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
   unsigned char* base_ptr = rm_smem_raw + (base - raw);
-  const uint32_t stage_bytes = (uint32_t)(128 * kTileK * 2 + tn * kTileK * 2);
+  const uint32_t x_bytes = (uint32_t)kbs * 128 * kTileK * 2, w_slice = (uint32_t)tn * kTileK * 2;
+  const uint32_t stage_bytes = x_bytes + (uint32_t)kbs * w_slice;
   const uint32_t bars = base + RmShape::kRingBytes;
   auto full_bar = [&](int s) { return bars + 8u * s; };
   auto empty_bar = [&](int s) { return bars + 8u * (RmShape::kMaxStages + s); };
@@ -403,12 +404,12 @@ __global__ void __launch_bounds__(128, 1)
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
-      for (int kb = 0; kb < nkb; ++kb) {
+      for (int kb = 0; kb < nkb; kb += kbs) {
         if (!mbar_wait(empty_bar(stage), phase ^ 1u, err)) break;
-        const uint32_t a_dst = base + stage * stage_bytes, b_dst = a_dst + 128 * kTileK * 2;
+        const uint32_t a_dst = base + stage * stage_bytes, b_dst = a_dst + x_bytes;
         mbar_expect_tx(full_bar(stage), stage_bytes);
-        tma_load_2d(a_dst, &xmap, full_bar(stage), kb * kTileK, 0, kEvictLast);
-        tma_load_2d(b_dst, &wmap, full_bar(stage), kb * kTileK, tile * tn, kEvictFirst);
+        tma_load_3d(a_dst, &xmap, full_bar(stage), 0, 0, kb, kEvictLast);
+        tma_load_3d(b_dst, &wmap, full_bar(stage), 0, tile * tn, kb, kEvictFirst);
         if (++stage == n_stages) stage = 0, phase ^= 1u;
       }
     }
@@ -419,15 +420,19 @@ __global__ void __launch_bounds__(128, 1)
       int stage = 0;
       uint32_t phase = 0;
       bool alive = true;
-      for (int kb = 0; kb < nkb && alive; ++kb) {
+      for (int kb = 0; kb < nkb && alive; kb += kbs) {
         alive = mbar_wait(full_bar(stage), phase, err);
         if (!alive) break;
         tc_fence_after_sync();
-        const uint32_t a_src = base + stage * stage_bytes, b_src = a_src + 128 * kTileK * 2;
-        const uint64_t adesc = kmajor_sw128_desc(a_src), bdesc = kmajor_sw128_desc(b_src);
+        const uint32_t a_src = base + stage * stage_bytes, b_src = a_src + x_bytes;
+        for (int j = 0; j < kbs; ++j) {
+          const uint64_t adesc = kmajor_sw128_desc(a_src + (uint32_t)j * (128 * kTileK * 2));
+          const uint64_t bdesc = kmajor_sw128_desc(b_src + (uint32_t)j * w_slice);
 #pragma unroll
-        for (int k = 0; k < kTileK / 16; ++k)
-          mma_bf16(tmem_base, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          for (int k = 0; k < kTileK / 16; ++k)
+            mma_bf16(tmem_base, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2), idesc,
+                     (kb > 0 || j > 0 || k > 0) ? 1u : 0u);
+        }
         mma_commit(empty_bar(stage));
         if (++stage == n_stages) stage = 0, phase ^= 1u;
       }
@@ -488,6 +493,18 @@ static int encode_kmajor(CUtensorMap* map, const bf16* base, int rows, int K, in
   const cuuint32_t box[2] = {(cuuint32_t)kTileK, (cuuint32_t)box_rows};
   const cuuint32_t elem[2] = {1, 1};
   const CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<bf16*>(base), dims, strides, box,
+                              elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -1;
+}
+
+// The same matrix as a rank-3 map {element in a k-block, row, k-block} whose box holds `kbs` k-blocks of `box_rows` rows.
+static int encode_kmajor3(CUtensorMap* map, const bf16* base, int rows, int K, int box_rows, int kbs) {
+  const cuuint64_t dims[3] = {(cuuint64_t)kTileK, (cuuint64_t)rows, (cuuint64_t)(K / kTileK)};
+  const cuuint64_t strides[2] = {(cuuint64_t)K * sizeof(bf16), (cuuint64_t)kTileK * sizeof(bf16)};
+  const cuuint32_t box[3] = {(cuuint32_t)kTileK, (cuuint32_t)box_rows, (cuuint32_t)kbs};
+  const cuuint32_t elem[3] = {1, 1, 1};
+  const CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<bf16*>(base), dims, strides, box,
                               elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? 0 : -1;
@@ -586,15 +603,29 @@ int rm_plan(RmGemmPlan* plan, const bf16* w, int N, int K, const bf16* x, int ro
   // the narrowest tile (a multiple of 16 weight rows) whose count still fits one wave of CTAs
   const int per_sm = (N + sm_count - 1) / std::max(1, sm_count);
   p.TN = std::min(256, std::max(16, (per_sm + 15) / 16 * 16));
-  if (encode_kmajor(&p.wmap, w, N, K, p.TN) != 0) return -4;
-  if (encode_kmajor(&p.xmap, x, rows, K, 128) != 0) return -4;
+  // k-blocks per stage: a tiled copy occupies the TMA unit for about 0.19 us whatever its size, a stage is two copies
+  // (about 110 GB/s per SM at best), and the ring must cover about 2 us of latency
+  const int nkb = K / kTileK;
+  double best = 1e30;
+  p.kbs = 1;
+  for (int kbs : {1, 2, 4}) {
+    if (nkb % kbs) continue;
+    const int stages = RmShape::stages(p.TN, kbs);
+    if (stages < 2) continue;
+    const double per_stage = std::max({0.38, RmShape::stage_bytes(p.TN, kbs) / 110e3, 2.0 / stages});
+    const double cost = per_stage * (nkb / kbs);
+    if (cost < best - 1e-9) best = cost, p.kbs = kbs;
+  }
+  if (encode_kmajor3(&p.wmap, w, N, K, p.TN, p.kbs) != 0) return -4;
+  if (encode_kmajor3(&p.xmap, x, rows, K, 128, p.kbs) != 0) return -4;
   return 0;
 }
 
 cudaError_t rm_launch(const RmGemmPlan& p, uint32_t* err, cudaStream_t stream) {
   if (p.TN < 16 || p.TN > 256 || p.TN % 16) return cudaErrorInvalidValue;
   gemm_rm_kernel<<<(p.N + p.TN - 1) / p.TN, 128, RmShape::kSmemBytes, stream>>>(
-      p.wmap, p.xmap, p.y, p.ldy, p.N, p.K, p.rows, p.TN, RmShape::stages(p.TN), RmShape::tmem_cols(p.TN), p.epi.bias,
+      p.wmap, p.xmap, p.y, p.ldy, p.N, p.K, p.rows, p.TN, p.kbs, RmShape::stages(p.TN, p.kbs), RmShape::tmem_cols(p.TN),
+      p.epi.bias,
       p.epi.kind, err);
   return cudaGetLastError();
 }

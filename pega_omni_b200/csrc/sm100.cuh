@@ -88,6 +88,18 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
       : "memory");
 }
 
+// The same for a rank-3 map (x: element in a 64-wide k-block, y: row, z: k-block): one instruction moves several
+// k-blocks of a row tile, each landing as its own [rows x 128 B] swizzled block. A tiled copy costs about 0.19 us of
+// the SM's TMA unit whatever its size, so small tiles are moved several k-blocks at a time.
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y, int z,
+                                            uint64_t hint) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
+      " [%0], [%1, {%3, %4, %5}], [%2], %6;"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y), "r"(z), "l"(hint)
+      : "memory");
+}
+
 // Untiled bulk load global -> shared; both addresses 16-byte aligned, bytes a multiple of 16.
 __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),

@@ -485,14 +485,14 @@ struct TickBuilder {
   TickProgram* prog;
   int ctas;
   int offset = 0;  // CTA the next phase's first item lands on, so consecutive phases load different SMs first
-  std::map<std::tuple<const void*, int, int, int>, int> map_cache;
+  std::map<std::tuple<const void*, int, int, int, int>, int> map_cache;
   bool failed = false;
 
-  int map_of(const bf16* base, int rows, int K, int box) {
-    const auto key = std::make_tuple((const void*)base, rows, K, box);
+  int map_of(const bf16* base, int rows, int K, int box, int kbs) {
+    const auto key = std::make_tuple((const void*)base, rows, K, box, kbs);
     auto it = map_cache.find(key);
     if (it != map_cache.end()) return it->second;
-    const int idx = tick_add_map(prog, base, rows, K, box);
+    const int idx = tick_add_map(prog, base, rows, K, box, kbs);
     if (idx < 0) failed = true;
     map_cache[key] = idx;
     return idx;
@@ -505,6 +505,20 @@ struct TickBuilder {
     ph.rows = rows;
     ph.cta_offset = offset;
     return ph;
+  }
+
+  // k-blocks per ring stage. A tiled TMA copy occupies the SM's TMA unit for about 0.19 us whatever its size and a
+  // stage is two copies, so one k-block per stage (16-24 KB) caps a CTA near 45 GB/s; several k-blocks per copy lift
+  // that. The most (up to 4) that divide a work item's k-blocks and still leave two stages in the ring measured best.
+  int stage_kblocks(int nkb, int splits, int bn, int tile_n) const {
+    int cap = 4;
+    if (const char* e = getenv("OMNI_TICK_KBS")) cap = std::max(1, atoi(e));  // tuning aid
+    if (nkb % splits) return 1;
+    const int per = nkb / splits, ring = tick_ring_size();
+    int best = 1;
+    for (int kbs = 2; kbs <= std::min(cap, per); ++kbs)
+      if (per % kbs == 0 && ring / (kbs * (bn + tile_n) * 128) >= 2) best = kbs;
+    return best;
   }
 
   // y = x . w^T as f32 partial tiles (or, for gate|up, SwiGLU activations straight from the epilogue when the
@@ -525,8 +539,9 @@ struct TickBuilder {
     ph.tiles = (N + t.tile_n - 1) / t.tile_n;
     ph.splits = t.splits;
     ph.mode = swiglu && t.swiglu_direct ? kGemmSwiglu : kGemmPartials;
-    ph.wmap = map_of(w, N, K, t.tile_n);
-    ph.xmap = map_of(x, rows, K, ph.bn);
+    ph.i1 = stage_kblocks(K / 64, ph.splits, ph.bn, ph.tile_n);
+    ph.wmap = map_of(w, N, K, t.tile_n, ph.i1);
+    ph.xmap = map_of(x, rows, K, ph.bn, ph.i1);
     ph.dst0 = act;
     ph.i0 = inter;
     prog->phases.push_back(ph);

@@ -29,7 +29,8 @@ enum GemmMode : int32_t { kGemmPartials = 0, kGemmSwiglu = 1 };
 enum NextInput : int32_t { kNextNone = 0, kNextHiddenAndCode = 1, kNextCode = 2 };
 
 // One phase. Field use by type:
-//  Gemm:       N, K, bn, rows, tiles, splits, wmap, xmap, mode; dst0 = act (SwiGLU), i0 = inter
+//  Gemm:       N, K, bn, rows, tiles, splits, wmap, xmap, mode; dst0 = act (SwiGLU), i0 = inter, i1 = k-blocks per
+//              ring stage (one TMA copy each for the activations and the weights)
 //  EmbedNorm:  rows, dim = N; src0 pad, src1 codec_emb, src2 p_emb, src3 gain; dst0 res, dst1 x; i0 vocab, i1 p_vocab,
 //              i2 groups; f0 eps
 //  ReduceNorm: rows, dim = N, tiles, splits, bn; src0 bias (or null), src3 gain; dst0 res, dst1 x; f0 eps
@@ -73,8 +74,10 @@ struct TickProgram {
   CUtensorMap* d_maps = nullptr;
 };
 
-// Appends a K-major bf16 tensor map ([rows, K] with a box of box_rows x 64) and returns its index.
-int tick_add_map(TickProgram* prog, const bf16* base, int rows, int K, int box_rows);
+// Appends a K-major bf16 tensor map ([rows, K] with a box of box_rows rows x kbs k-blocks of 64) and returns its index.
+int tick_add_map(TickProgram* prog, const bf16* base, int rows, int K, int box_rows, int kbs);
+// Bytes of shared memory the kernel's tile ring takes (what a GEMM phase's stages must fit).
+int tick_ring_size();
 // Largest SwiGLU/partials GEMM the kernel can run; false when a shape needs the per-op path.
 bool tick_supports(int hidden, int head_dim, int q_heads, int kv_heads, int rows_max);
 // Copies the phase list and the maps to the device. 0 on success.

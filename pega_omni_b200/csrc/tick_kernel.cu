@@ -86,20 +86,25 @@ __device__ __forceinline__ int first_item(const Phase& ph) {
 // restart at stage 0 whenever the geometry changes; a stage's mbarrier parities are tracked per stage (one bit each),
 // so a barrier that one geometry never reaches stays consistent for the next.
 struct Ring {
-  uint32_t x_bytes = 0, stage_bytes = 0;
-  int n = 0, stage = 0;
+  uint32_t x_slice = 0, w_slice = 0, x_bytes = 0, stage_bytes = 0;
+  int kbs = 1, n = 0, stage = 0;
   uint32_t par = 0;  // bit s: parity of stage s's next wait
   // Returns true when the geometry changed (the caller may have to drain the old one first).
   __device__ __forceinline__ bool enter(const Phase& ph, int ring_bytes) {
-    const uint32_t xb = ((uint32_t)ph.bn * kTileK * 2 + 1023u) & ~1023u, sb = xb + (uint32_t)ph.tile_n * kTileK * 2;
-    if (xb == x_bytes && sb == stage_bytes) return false;
-    x_bytes = xb, stage_bytes = sb;
-    n = min(kMaxStages, (int)((uint32_t)ring_bytes / sb));
+    const uint32_t xs = ((uint32_t)ph.bn * kTileK * 2 + 1023u) & ~1023u, ws = (uint32_t)ph.tile_n * kTileK * 2;
+    const int k = ph.i1 > 0 ? ph.i1 : 1;
+    if (xs == x_slice && ws == w_slice && k == kbs) return false;
+    x_slice = xs, w_slice = ws, kbs = k;
+    x_bytes = xs * (uint32_t)k, stage_bytes = (xs + ws) * (uint32_t)k;
+    n = min(kMaxStages, (int)((uint32_t)ring_bytes / stage_bytes));
     stage = 0;
     return true;
   }
-  __device__ __forceinline__ uint32_t x_off() const { return (uint32_t)stage * stage_bytes; }
-  __device__ __forceinline__ uint32_t w_off() const { return (uint32_t)stage * stage_bytes + x_bytes; }
+  // k-block j of the stage's activation / weight tile
+  __device__ __forceinline__ uint32_t x_off(int j = 0) const { return (uint32_t)stage * stage_bytes + (uint32_t)j * x_slice; }
+  __device__ __forceinline__ uint32_t w_off(int j = 0) const {
+    return (uint32_t)stage * stage_bytes + x_bytes + (uint32_t)j * w_slice;
+  }
   __device__ __forceinline__ uint32_t parity() const { return par >> stage & 1u; }
   __device__ __forceinline__ void advance() {
     par ^= 1u << stage;
@@ -787,14 +792,17 @@ __global__ void __launch_bounds__(kThreads, 1) tick_kernel(const __grid_constant
         for (int it = first_item(ph); it < items && !ctl.abort; it += G) {
           const int tile = it % ph.tiles, split = it / ph.tiles;
           const int kb0 = (int)((int64_t)nkb * split / ph.splits), kb1 = (int)((int64_t)nkb * (split + 1) / ph.splits);
-          for (int kb = kb0; kb < kb1; ++kb) {
+          for (int kb = kb0; kb < kb1; kb += ring.kbs) {
             if (!mbar_wait(smem_addr(&ctl.empty[ring.stage]), ring.parity() ^ 1u, a.err)) {
               ctl.abort = 1;
               break;
             }
             const uint32_t bar = smem_addr(&ctl.full_w[ring.stage]);
-            mbar_expect_tx(bar, (uint32_t)ph.tile_n * kTileK * 2);
-            tma_load_2d(base + ring.w_off(), map, bar, kb * kTileK, tile * ph.tile_n, kEvictFirst);
+            mbar_expect_tx(bar, ring.w_slice * (uint32_t)ring.kbs);
+            if (ring.kbs == 1)  // rank-2 map: the plain tile copy is about 10 % cheaper than a rank-3 one
+              tma_load_2d(base + ring.w_off(), map, bar, kb * kTileK, tile * ph.tile_n, kEvictFirst);
+            else
+              tma_load_3d(base + ring.w_off(), map, bar, 0, tile * ph.tile_n, kb, kEvictFirst);
             ring.advance();
           }
         }
@@ -821,18 +829,21 @@ __global__ void __launch_bounds__(kThreads, 1) tick_kernel(const __grid_constant
         asm volatile("fence.proxy.async;" ::: "memory");  // generic-proxy writes of other CTAs -> async-proxy reads
         ring.enter(ph, a.ring_bytes);
         const CUtensorMap* map = a.maps + ph.xmap;
-        const uint32_t xbytes = (uint32_t)ph.bn * kTileK * 2;
+        const uint32_t xbytes = (uint32_t)ph.bn * kTileK * 2 * (uint32_t)ring.kbs;
         for (int it = first_item(ph); it < items && !ctl.abort; it += G) {
           const int split = it / ph.tiles;
           const int kb0 = (int)((int64_t)nkb * split / ph.splits), kb1 = (int)((int64_t)nkb * (split + 1) / ph.splits);
-          for (int kb = kb0; kb < kb1; ++kb) {
+          for (int kb = kb0; kb < kb1; kb += ring.kbs) {
             if (!mbar_wait(smem_addr(&ctl.empty[ring.stage]), ring.parity() ^ 1u, a.err)) {
               ctl.abort = 1;
               break;
             }
             const uint32_t bar = smem_addr(&ctl.full_x[ring.stage]);
             mbar_expect_tx(bar, xbytes);
-            tma_load_2d(base + ring.x_off(), map, bar, kb * kTileK, 0, kEvictLast);
+            if (ring.kbs == 1)
+              tma_load_2d(base + ring.x_off(), map, bar, kb * kTileK, 0, kEvictLast);
+            else
+              tma_load_3d(base + ring.x_off(), map, bar, 0, 0, kb, kEvictLast);
             ring.advance();
           }
         }
@@ -863,7 +874,7 @@ __global__ void __launch_bounds__(kThreads, 1) tick_kernel(const __grid_constant
             }
             if (ctl.abort) break;
             tc_fence_after_sync();
-            for (int kb = kb0; kb < kb1; ++kb) {
+            for (int kb = kb0; kb < kb1; kb += ring.kbs) {
               if (!mbar_wait(smem_addr(&ctl.full_w[ring.stage]), ring.parity(), a.err) ||
                   !mbar_wait(smem_addr(&ctl.full_x[ring.stage]), ring.parity(), a.err)) {
                 ctl.abort = 1;
@@ -871,13 +882,15 @@ __global__ void __launch_bounds__(kThreads, 1) tick_kernel(const __grid_constant
               }
               tc_fence_after_sync();
               if (a.trace && kb == kb0 && it == first_item(ph)) a.trace[((size_t)p * G + blockIdx.x) * 4] = global_timer_ns();
-              const uint64_t bdesc = kmajor_sw128_desc(base + ring.w_off());
-              for (int h = 0; h < 2; ++h) {
-                const uint64_t adesc = kmajor_sw128_desc(base + ring.x_off() + (uint32_t)(h * kTileM * kTileK * 2));
+              for (int j = 0; j < ring.kbs; ++j) {
+                const uint64_t bdesc = kmajor_sw128_desc(base + ring.w_off(j));
+                for (int h = 0; h < 2; ++h) {
+                  const uint64_t adesc = kmajor_sw128_desc(base + ring.x_off(j) + (uint32_t)(h * kTileM * kTileK * 2));
 #pragma unroll
-                for (int k = 0; k < kTileK / 16; ++k)
-                  mma_bf16(tmem_base + (uint32_t)(h * kTileN), adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2), idesc,
-                           (kb > kb0 || k > 0) ? 1u : 0u);
+                  for (int k = 0; k < kTileK / 16; ++k)
+                    mma_bf16(tmem_base + (uint32_t)(h * kTileN), adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2), idesc,
+                             (kb > kb0 || j > 0 || k > 0) ? 1u : 0u);
+                }
               }
               mma_commit(smem_addr(&ctl.empty[ring.stage]));
               ring.advance();
@@ -898,7 +911,7 @@ __global__ void __launch_bounds__(kThreads, 1) tick_kernel(const __grid_constant
           empty_par[buf] ^= 1u;
           tc_fence_after_sync();
           const uint32_t tmem_d = tmem_base + (uint32_t)(buf * kTileN);
-          for (int kb = kb0; kb < kb1; ++kb) {
+          for (int kb = kb0; kb < kb1; kb += ring.kbs) {
             if (!mbar_wait(smem_addr(&ctl.full_w[ring.stage]), ring.parity(), a.err) ||
                 !mbar_wait(smem_addr(&ctl.full_x[ring.stage]), ring.parity(), a.err)) {
               ctl.abort = 1;
@@ -906,10 +919,17 @@ __global__ void __launch_bounds__(kThreads, 1) tick_kernel(const __grid_constant
             }
             tc_fence_after_sync();
             if (a.trace && kb == kb0 && it == first_item(ph)) a.trace[((size_t)p * G + blockIdx.x) * 4] = global_timer_ns();
-            const uint64_t adesc = kmajor_sw128_desc(base + ring.x_off()), bdesc = kmajor_sw128_desc(base + ring.w_off());
+            {
+              const uint64_t adesc = kmajor_sw128_desc(base + ring.x_off()), bdesc = kmajor_sw128_desc(base + ring.w_off());
 #pragma unroll
-            for (int k = 0; k < kTileK / 16; ++k)
-              mma_bf16(tmem_d, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2), idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+              for (int k = 0; k < kTileK / 16; ++k)
+                mma_bf16(tmem_d, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2), idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+            }
+            for (int j = 1; j < ring.kbs; ++j) {
+              const uint64_t adesc = kmajor_sw128_desc(base + ring.x_off(j)), bdesc = kmajor_sw128_desc(base + ring.w_off(j));
+#pragma unroll
+              for (int k = 0; k < kTileK / 16; ++k) mma_bf16(tmem_d, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2), idesc, 1u);
+            }
             mma_commit(smem_addr(&ctl.empty[ring.stage]));
             ring.advance();
           }
@@ -1009,28 +1029,35 @@ size_t tick_smem_bytes(int ring_bytes) {
   return 1024 + (size_t)ring_bytes + ((sizeof(Control) + 127) & ~127) + sizeof(WorkerScratch);
 }
 
-// The ring's size. 104 KB by default: with the control block and scratch the CTA then fits the 132 KB shared-memory
-// carve-out and 124 KB of the SM's array stay L1, which measured faster than a deeper ring with less L1.
+// The ring's size. 128 KB by default: with the control block and scratch the CTA then takes the 164 KB shared-memory
+// carve-out and 92 KB of the SM's array stay L1. With one k-block per stage 104 KB (132 KB carve-out, 124 KB L1) was
+// the faster trade; stages of several k-blocks need the room (two stages of 48 KB for the 128-row weight tiles).
 // OMNI_TICK_RING_KB overrides it (a tuning aid, 48 .. 192).
 int tick_ring_bytes() {
-  int kb = 104;
+  int kb = 128;
   if (const char* e = getenv("OMNI_TICK_RING_KB")) kb = atoi(e);
   return std::min(std::max(kb, 48), kMaxRingBytes / 1024) * 1024;
 }
 
 }  // namespace
 
-int tick_add_map(TickProgram* prog, const bf16* base, int rows, int K, int box_rows) {
+int tick_ring_size() { return tick_ring_bytes(); }
+
+int tick_add_map(TickProgram* prog, const bf16* base, int rows, int K, int box_rows, int kbs) {
   void* fn = nullptr;
   cudaDriverEntryPointQueryResult q;
   if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess || !fn) return -1;
-  const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
-  const cuuint64_t strides[1] = {(cuuint64_t)K * sizeof(bf16)};
-  const cuuint32_t box[2] = {(cuuint32_t)kTileK, (cuuint32_t)box_rows};
-  const cuuint32_t elem[2] = {1, 1};
+  // kbs == 1: rank 2, {column, row}, a box of 64 columns x box_rows rows. Otherwise rank 3, {element in a 64-wide
+  // k-block, row, k-block}: one copy moves kbs k-blocks of box_rows rows, each landing as its own [box_rows x 128 B]
+  // swizzled block.
+  const bool flat = kbs == 1;
+  const cuuint64_t dims[3] = {(cuuint64_t)(flat ? K : kTileK), (cuuint64_t)rows, (cuuint64_t)(K / kTileK)};
+  const cuuint64_t strides[2] = {(cuuint64_t)K * sizeof(bf16), (cuuint64_t)kTileK * sizeof(bf16)};
+  const cuuint32_t box[3] = {(cuuint32_t)kTileK, (cuuint32_t)box_rows, (cuuint32_t)kbs};
+  const cuuint32_t elem[3] = {1, 1, 1};
   CUtensorMap map;
   const CUresult r = reinterpret_cast<EncodeTiledFn>(fn)(
-      &map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<bf16*>(base), dims, strides, box, elem,
+      &map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, flat ? 2 : 3, const_cast<bf16*>(base), dims, strides, box, elem,
       CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return -1;
