@@ -101,8 +101,13 @@ Tiling choose_tiling(int N, int K, int ctas, bool swiglu) {
       const int smax = direct ? 1 : std::min(8, nkb);
       for (int S = 1; S <= smax; ++S) {
         const int items = tiles * S, waves = (items + ctas - 1) / ctas, kb = (nkb + S - 1) / S;
-        const double per_kb = std::max(0.30, (tn * 128.0 + 8192.0) / 55000.0);
-        double cost = waves * (kb * per_kb + 1.5) + 0.15 * S;
+        static const double* tune = [] {
+          static double v[4] = {0.20, 80000.0, 1.5, 0.30};  // us floor per k-block, bytes per us, us per wave, us per split
+          if (const char* e = getenv("OMNI_TICK_COST")) sscanf(e, "%lf,%lf,%lf,%lf", &v[0], &v[1], &v[2], &v[3]);
+          return v;
+        }();
+        const double per_kb = std::max(tune[0], (tn * 128.0 + 8192.0) / tune[1]);
+        double cost = waves * (kb * per_kb + tune[2]) + tune[3] * S;
         if (swiglu && !direct) cost += 5.0;
         if (cost < best.cost - 1e-9) best = Tiling{tn, S, direct != 0, cost};
       }
