@@ -460,10 +460,10 @@ def main():
                 "frac": tick_bytes / tick_s / 1e9 / peak, "peak_source": f"of {peak_kind}",
                 "bytes_per_launch": int(tick_bytes), "us_per_launch": tick_s * 1e6,
                 # ncu cannot run inside the timed region: the DRAM bytes of one captured tick of this kernel
-                # (profiles/tick_kernel_qwen3tts_64sessions.md: 6,467 MB read+written for 6,296 MB algorithmic at
+                # (profiles/tick_kernel_qwen3tts_64sessions.md: 6,399 MB read+written for 6,296 MB algorithmic at
                 # positions 131-132) scaled to this run's algorithmic bytes; traffic grows with the KV length as they do
-                "traffic": int(tick_bytes * 6467.2 / 6296.2) if launches_per_tick == 1 else None,
-                "traffic_note": "ncu dram__bytes_read+write of one captured tick (6.467 GB for 6.296 GB algorithmic), "
+                "traffic": int(tick_bytes * 6399.1 / 6296.2) if launches_per_tick == 1 else None,
+                "traffic_note": "ncu dram__bytes_read+write of one captured tick (6.399 GB for 6.296 GB algorithmic), "
                                 "scaled by this run's algorithmic bytes"}
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,

@@ -341,12 +341,11 @@ __global__ void __launch_bounds__(128, 1)
 
 // ---------------------------------------------------------------------------
 // Tensor-core tiles with the input rows on the MMA M dimension (at most 128 of them) and TN weight rows on N: one CTA
-// computes y[:, tile] over the whole K, so there is no split, no partial tile and no reduction. A tcgen05.mma costs
-// the same whatever N is, so this orientation needs K/16 instructions per CTA where the kernel above needs
-// K/16 per 128 weight rows per split: it is the faster one for the decode-sized GEMMs of the secondary model shells
-// (at most 128 sessions, K up to 4096), whose small matrices the split-K kernel cannot spread without paying a serial
-// reduction per tile.
-//   warp 0 / lane 0: TMA producer, a ring of {X tile 128 x 64, W tile TN x 64};  warp 1 / lane 0: MMA issuer;
+// computes y[:, tile] over the whole K, so there is no split, no partial tile and no reduction. It is the faster
+// one for the decode-sized GEMMs of the secondary model shells (at most 128 sessions, K up to 4096), whose small
+// matrices the split-K kernel cannot spread without paying a serial reduction per tile.
+//   warp 0 / lane 0: TMA producer, a ring of {X tile 128 x 64 x kbs, W tile TN x 64 x kbs} (kbs k-blocks per copy);
+//   warp 1 / lane 0: MMA issuer;
 //   all four warps: epilogue, a thread owns one output row (its TMEM lane) and writes it 16 columns at a time.
 
 // The tile width TN (weight rows per CTA, a multiple of 16 up to 256) is a launch parameter: the host picks the

@@ -80,10 +80,12 @@ struct Scratch {
 };
 
 // How the persistent kernel tiles one GEMM: weight rows per tile (the MMA N dimension) and K splits.
-// A cost model in microseconds, from measurements on B200: a tcgen05.mma takes ~142 cycles whatever its shape (so a
-// 64-wide K block costs ~0.3 us of issue time), one SM streams ~55 GB/s through a 4-stage TMA ring, a work item
-// pays ~1.5 us of pipeline fill, every consumer pays ~0.15 us per split when it sums partial tiles, and a separate
-// SiLU*up reduce phase costs ~5 us (one more grid barrier).
+// A cost model in microseconds, fitted to the kernel's own per-phase timestamps on B200. What bounds a streaming CTA
+// is its TMA unit (about 0.19 us per tiled copy whatever its size, two copies per ring stage) and the bytes the ring
+// keeps under way, not the tensor pipe (a tcgen05.mma with M = 128 takes (128 + N) / 4 cycles of operand fetch,
+// 48-64 cycles here): a 64-wide K block costs max(0.2 us, its bytes at 80 GB/s), a wave of work items pays ~1.5 us
+// of pipeline fill, every K split costs ~0.3 us in the phase that sums the partial tiles, and a separate SiLU*up
+// reduce phase costs ~5 us (one more grid barrier).
 struct Tiling {
   int tile_n = 256, splits = 1;
   bool swiglu_direct = false;

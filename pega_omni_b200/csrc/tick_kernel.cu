@@ -81,8 +81,8 @@ __device__ __forceinline__ int first_item(const Phase& ph) {
   return (int)((blockIdx.x + g - ph.cta_offset % g) % g);
 }
 
-// The tile ring of a GEMM phase: stages of [activation k-block: bn rows][weight k-block: tile_n rows], each row 128
-// bytes, as many as fit (at most kMaxStages). The three pipeline roles of a CTA walk the stages in the same order and
+// The tile ring of a GEMM phase: stages of [kbs activation k-blocks: bn rows each][kbs weight k-blocks: tile_n rows
+// each], each row 128 bytes, as many stages as fit (at most kMaxStages); one TMA copy fills each half of a stage. The three pipeline roles of a CTA walk the stages in the same order and
 // restart at stage 0 whenever the geometry changes; a stage's mbarrier parities are tracked per stage (one bit each),
 // so a barrier that one geometry never reaches stays consistent for the next.
 struct Ring {
