@@ -119,8 +119,8 @@ template <int BN>
 struct TcShape {
   static constexpr int kStageBytes = kTileW * kTileK * 2 + BN * kTileK * 2;
   static constexpr int kStages = (200 * 1024 / kStageBytes) > 8 ? 8 : (200 * 1024 / kStageBytes);
-  // One accumulator: a tcgen05.mma occupies the tensor pipe for a fixed ~140 cycles whatever its shape
-  // (measured), so rotating accumulators buys nothing.
+  // One accumulator: the pipeline is bound by its TMA copies, not by the tensor pipe, so rotating accumulators
+  // buys nothing.
   static constexpr int kAccs = 1;
   static constexpr int kTmemCols = BN * kAccs < 32 ? 32 : BN * kAccs;
   static constexpr size_t kSmemBytes = (size_t)kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
@@ -171,9 +171,13 @@ __device__ __forceinline__ void reduce_tile(const float* partial0, size_t split_
 template <int BN>
 __global__ void __launch_bounds__(128, 1)
     gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap xmap,
-                   bf16* __restrict__ y, int ldy, int N, int K, int rows, int splits, float* __restrict__ partials,
-                   uint32_t* __restrict__ counters, const bf16* bias, int kind, uint32_t* err) {
+                   bf16* __restrict__ y, int ldy, int N, int K, int rows, int splits, int kbs,
+                   float* __restrict__ partials, uint32_t* __restrict__ counters, const bf16* bias, int kind,
+                   uint32_t* err) {
   using S = TcShape<BN>;
+  // kbs k-blocks per ring stage and per TMA copy (rank-3 maps when kbs > 1): a stage is kbs W slices, then kbs X slices
+  const int n_stages = S::kStages / kbs;
+  const uint32_t stage_bytes = (uint32_t)kbs * S::kStageBytes, x_base = (uint32_t)kbs * kTileW * kTileK * 2;
   using namespace sm100;
   if (*reinterpret_cast<volatile uint32_t*>(err) != 0) return;  // an earlier kernel failed: do not wait on hardware
 
@@ -217,13 +221,18 @@ __global__ void __launch_bounds__(128, 1)
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
-      for (int kb = kb_begin; kb < kb_end; ++kb) {
+      for (int kb = kb_begin; kb < kb_end; kb += kbs) {
         if (!mbar_wait(empty_bar(stage), phase ^ 1u, err)) break;
-        const uint32_t a_dst = base + stage * S::kStageBytes, b_dst = a_dst + kTileW * kTileK * 2;
-        mbar_expect_tx(full_bar(stage), S::kStageBytes);
-        tma_load_2d(a_dst, &wmap, full_bar(stage), kb * kTileK, tile * kTileW, kEvictFirst);
-        tma_load_2d(b_dst, &xmap, full_bar(stage), kb * kTileK, row_tile * BN, kEvictLast);
-        if (++stage == S::kStages) {
+        const uint32_t a_dst = base + stage * stage_bytes, b_dst = a_dst + x_base;
+        mbar_expect_tx(full_bar(stage), stage_bytes);
+        if (kbs == 1) {
+          tma_load_2d(a_dst, &wmap, full_bar(stage), kb * kTileK, tile * kTileW, kEvictFirst);
+          tma_load_2d(b_dst, &xmap, full_bar(stage), kb * kTileK, row_tile * BN, kEvictLast);
+        } else {
+          tma_load_3d(a_dst, &wmap, full_bar(stage), 0, tile * kTileW, kb, kEvictFirst);
+          tma_load_3d(b_dst, &xmap, full_bar(stage), 0, row_tile * BN, kb, kEvictLast);
+        }
+        if (++stage == n_stages) {
           stage = 0;
           phase ^= 1u;
         }
@@ -236,18 +245,21 @@ __global__ void __launch_bounds__(128, 1)
       int stage = 0;
       uint32_t phase = 0;
       bool alive = true;
-      for (int kb = kb_begin; kb < kb_end && alive; ++kb) {
+      for (int kb = kb_begin; kb < kb_end && alive; kb += kbs) {
         alive = mbar_wait(full_bar(stage), phase, err);
         if (!alive) break;
         tc_fence_after_sync();
-        const uint32_t a_src = base + stage * S::kStageBytes, b_src = a_src + kTileW * kTileK * 2;
-        const uint64_t adesc = kmajor_sw128_desc(a_src), bdesc = kmajor_sw128_desc(b_src);
+        const uint32_t a_src = base + stage * stage_bytes, b_src = a_src + x_base;
+        for (int j = 0; j < kbs; ++j) {
+          const uint64_t adesc = kmajor_sw128_desc(a_src + (uint32_t)j * (kTileW * kTileK * 2));
+          const uint64_t bdesc = kmajor_sw128_desc(b_src + (uint32_t)j * (BN * kTileK * 2));
 #pragma unroll
-        for (int k = 0; k < kTileK / 16; ++k)
-          mma_bf16(tmem_base + (uint32_t)((k % S::kAccs) * BN), adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2),
-                   idesc, (kb > kb_begin || k >= S::kAccs) ? 1u : 0u);
+          for (int k = 0; k < kTileK / 16; ++k)
+            mma_bf16(tmem_base, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2), idesc,
+                     (kb > kb_begin || j > 0 || k > 0) ? 1u : 0u);
+        }
         mma_commit(empty_bar(stage));  // frees the stage once these MMAs have read it
-        if (++stage == S::kStages) {
+        if (++stage == n_stages) {
           stage = 0;
           phase ^= 1u;
         }
@@ -542,8 +554,26 @@ int tc_plan(TcGemmPlan* plan, const bf16* w, int N, int K, const bf16* x, int ro
   // the last CTA's reduction is a serial chain of L2 round trips: at most 8 splits, 4 for wide row tiles
   if (force_splits <= 0) splits = std::min(splits, p.BN >= 128 ? 4 : 8);
   p.splits = splits;
-  if (encode_kmajor(&p.wmap, w, N, K, kTileW) != 0) return -4;
-  if (encode_kmajor(&p.xmap, x, rows, K, p.BN) != 0) return -4;
+  // k-blocks per TMA copy: a tiled copy occupies the TMA unit for about 0.19 us whatever its size; the ring must still
+  // hold two stages, and every split must be a whole number of copies
+  p.kbs = 1;
+  if (nkb % splits == 0) {
+    const int per = nkb / splits, stage = kTileW * kTileK * 2 + p.BN * kTileK * 2;
+    const int stages1 = std::min(8, 200 * 1024 / stage);
+    double best = 1e30;
+    for (int kbs : {1, 2, 4}) {
+      if (per % kbs || stages1 / kbs < 2) continue;
+      const double cost = (per / kbs) * std::max({0.38, kbs * stage / 110e3, 2.0 / (stages1 / kbs)});
+      if (cost < best - 1e-9) best = cost, p.kbs = kbs;
+    }
+  }
+  if (p.kbs == 1) {
+    if (encode_kmajor(&p.wmap, w, N, K, kTileW) != 0) return -4;
+    if (encode_kmajor(&p.xmap, x, rows, K, p.BN) != 0) return -4;
+  } else {
+    if (encode_kmajor3(&p.wmap, w, N, K, kTileW, p.kbs) != 0) return -4;
+    if (encode_kmajor3(&p.xmap, x, rows, K, p.BN, p.kbs) != 0) return -4;
+  }
   return 0;
 }
 
@@ -552,7 +582,7 @@ static cudaError_t tc_launch_bn(const TcGemmPlan& p, const GemmScratch& s, uint3
   using S = TcShape<BN>;
   const dim3 grid(p.tiles_n(), p.splits, p.row_tiles);
   gemm_tc_kernel<BN><<<grid, 128, S::kSmemBytes, stream>>>(p.wmap, p.xmap, p.y, p.ldy, p.N, p.K, p.rows, p.splits,
-                                                           s.partials, s.counters, p.epi.bias, p.epi.kind, err);
+                                                           p.kbs, s.partials, s.counters, p.epi.bias, p.epi.kind, err);
   return cudaGetLastError();
 }
 

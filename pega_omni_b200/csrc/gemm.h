@@ -40,6 +40,7 @@ struct TcGemmPlan {
   int BN = 0;        // rows (sessions) per tile: 16..256, multiple of 16
   int row_tiles = 1; // ceil(rows / BN)
   int splits = 1;
+  int kbs = 1;       // k-blocks per ring stage and per TMA copy
   bf16* y = nullptr;
   int ldy = 0;
   Epilogue epi;
