@@ -4,8 +4,8 @@
  * Replaces the model shell of crates/omni-personaplex/src/model.rs (`Model::{load, open, start, tick}` and the debug
  * getters) one level below the engine. The waveform codec (Mimi) is not part of this library yet: the caller's codes
  * of a frame arrive through `omni_duplex_step.caller` (what `force_caller` overrides in the reference), and no PCM is
- * returned. Not built: CUDA-graph capture of the tick (every tick is issued as per-op launches, so there are no batch
- * buckets and no `warmup`).
+ * returned. A tick's kernels are captured into one CUDA graph per session count the second time that count is seen and
+ * replayed from then on (no batch buckets, no padding rows and no `warmup` call).
  *
  * One model per GPU per thread; no internal locking; calls are synchronous. All functions return an omni_status
  * (include/omni_b200.h); after a non-zero status `omni_duplex_last_error` describes it. */

@@ -4,7 +4,8 @@
  *
  * Replaces the model shell of crates/omni-higgs-audio/src/model.rs (`Model::{load, open, start, step, logits}`) one
  * level below its engine. Not part of this library: the waveform codec (`Model::decode`, the reference's `codec`
- * program) and CUDA-graph capture (every call is issued as per-op launches, so there are no batch buckets).
+ * program). A decode step's kernels are captured into one CUDA graph per sequence count the second time that count
+ * is seen and replayed from then on (no batch buckets, no padding rows); `start` is issued as per-op launches.
  *
  * One model per GPU per thread; no internal locking; calls are synchronous. All functions return an omni_status
  * (include/omni_b200.h); after a non-zero status `omni_higgs_last_error` describes it. */

@@ -98,6 +98,14 @@ struct omni_duplex {
   int32_t* out_host = nullptr;  // emitted + error word
   uint32_t* err = nullptr;
 
+  // one CUDA graph of the tick's kernels per session count
+  struct TickGraph {
+    cudaGraphExec_t exec = nullptr;
+    int seen = 0, nodes = 0;
+  };
+  std::map<int, TickGraph> tick_graphs;
+  bool use_graphs = true;
+
   GemmScratch scratch;
   std::map<std::tuple<const void*, const void*, const void*, int>, TcGemmPlan> plans;
   std::map<std::tuple<const void*, const void*, const void*, int>, RmGemmPlan> rm_plans;
@@ -336,6 +344,7 @@ int32_t omni_duplex_create(const omni_duplex_config* config, const omni_tensor* 
   if (prop.major != 10)
     return m->fail(OMNI_ERR_UNSUPPORTED, "device is sm_%d%d; this library is sm_100a only", prop.major, prop.minor);
   m->sm_count = prop.multiProcessorCount;
+  m->use_graphs = getenv("OMNI_DUPLEX_NO_GRAPH") == nullptr;  // tuning aid: per-op launches every tick
   DCUDA(m, cudaStreamCreateWithFlags(&m->stream, cudaStreamNonBlocking));
   DCUDA(m, cudaEventCreate(&m->ev0));
   DCUDA(m, cudaEventCreate(&m->ev1));
@@ -433,6 +442,8 @@ void omni_duplex_destroy(omni_duplex* m) {
   if (!m) return;
   cudaSetDevice(m->device);
   if (m->stream) cudaStreamSynchronize(m->stream);
+  for (auto& g : m->tick_graphs)
+    if (g.second.exec) cudaGraphExecDestroy(g.second.exec);
   for (void* p : m->allocations) cudaFree(p);
   if (m->in_host) cudaFreeHost(m->in_host);
   if (m->out_host) cudaFreeHost(m->out_host);
@@ -704,16 +715,48 @@ int32_t omni_duplex_tick(omni_duplex* m, int32_t n, omni_duplex_session* const* 
   m->launches = 0;
   DCUDA(m, cudaEventRecord(m->ev0, m->stream));
   DCUDA(m, cudaMemcpyAsync(m->in_dev, m->in_host, st.used, cudaMemcpyHostToDevice, m->stream));
-  // `Helium::step` (helium.rs:189-222)
-  DLAUNCH(m, launch_lm_embed_state(m->state, st.dev(lines), m->stride, tables(m), m->x, m->rows_buf, n, c.dim, m->err,
-                                   m->stream));
-  DTRY(helium_forward(m, n, st.dev(pos), st.dev(slot), nullptr, st.dev(indptr), st.dev(pages)));
-  DTRY(gemm(m, m->text_linear, c.text_vocab, c.dim, m->xn, n, m->text_logits, c.text_vocab));
-  DLAUNCH(m, launch_lm_sample(m->text_logits, c.text_vocab, c.text_vocab, c.text_temperature, c.text_top_k,
-                              st.dev(force), st.dev(seeds), 0, m->drawn, n, m->stream));
-  DTRY(depformer_step(m, n, st.dev(force), st.dev(seeds)));
-  DLAUNCH(m, launch_lm_advance(m->state, st.dev(lines), m->stride, m->drawn, st.dev(caller), st.dev(force_caller),
-                               m->emitted, n, m->stream));
+  // The kernels of a tick and their arguments depend on n alone (positions, pages, forces and seeds are read from the
+  // staged block, whose layout n fixes), so the sequence is captured once per n and replayed as a CUDA graph. The first
+  // tick of a size runs eagerly (it creates the GEMM plans), the second is captured.
+  auto body = [&]() -> int {
+    // `Helium::step` (helium.rs:189-222)
+    DLAUNCH(m, launch_lm_embed_state(m->state, st.dev(lines), m->stride, tables(m), m->x, m->rows_buf, n, c.dim, m->err,
+                                     m->stream));
+    DTRY(helium_forward(m, n, st.dev(pos), st.dev(slot), nullptr, st.dev(indptr), st.dev(pages)));
+    DTRY(gemm(m, m->text_linear, c.text_vocab, c.dim, m->xn, n, m->text_logits, c.text_vocab));
+    DLAUNCH(m, launch_lm_sample(m->text_logits, c.text_vocab, c.text_vocab, c.text_temperature, c.text_top_k,
+                                st.dev(force), st.dev(seeds), 0, m->drawn, n, m->stream));
+    DTRY(depformer_step(m, n, st.dev(force), st.dev(seeds)));
+    DLAUNCH(m, launch_lm_advance(m->state, st.dev(lines), m->stride, m->drawn, st.dev(caller), st.dev(force_caller),
+                                 m->emitted, n, m->stream));
+    return OMNI_OK;
+  };
+  omni_duplex::TickGraph& tg = m->tick_graphs[n];
+  if (!m->use_graphs || tg.seen == 0) {
+    DTRY(body());
+    tg.seen = 1;
+  } else {
+    if (!tg.exec) {
+      DCUDA(m, cudaStreamBeginCapture(m->stream, cudaStreamCaptureModeThreadLocal));
+      const int rc = body();
+      cudaGraph_t graph = nullptr;
+      const cudaError_t end = cudaStreamEndCapture(m->stream, &graph);  // always ends the capture, also after a failure
+      if (rc != OMNI_OK || end != cudaSuccess) {
+        if (graph) cudaGraphDestroy(graph);
+        cudaGetLastError();
+        return rc != OMNI_OK ? rc : m->fail(OMNI_ERR_CUDA, "tick capture: %s", cudaGetErrorString(end));
+      }
+      const cudaError_t inst = cudaGraphInstantiate(&tg.exec, graph, 0);
+      cudaGraphDestroy(graph);
+      if (inst != cudaSuccess) {
+        tg.exec = nullptr;
+        return m->fail(OMNI_ERR_CUDA, "tick graph: %s", cudaGetErrorString(inst));
+      }
+      tg.nodes = m->launches;
+    }
+    DCUDA(m, cudaGraphLaunch(tg.exec, m->stream));
+    m->launches = tg.nodes;
+  }
   DCUDA(m, cudaMemcpyAsync(m->out_host, m->emitted, (size_t)n * kDuplexDrawn * 4, cudaMemcpyDeviceToHost, m->stream));
   DTRY(finish(m, (size_t)n * kDuplexDrawn));
   memcpy(emitted, m->out_host, (size_t)n * kDuplexDrawn * 4);

@@ -77,6 +77,13 @@ struct omni_higgs {
   GemmScratch scratch;
   std::map<std::tuple<const void*, const void*, const void*, int>, TcGemmPlan> plans;
   std::map<std::tuple<const void*, const void*, const void*, int>, RmGemmPlan> rm_plans;
+  // one CUDA graph of the decode step's kernels per sequence count
+  struct StepGraph {
+    cudaGraphExec_t exec = nullptr;
+    int seen = 0, nodes = 0;
+  };
+  std::map<int, StepGraph> step_graphs;
+  bool use_graphs = true;
 
   int fail(int code, const char* fmt, ...) {
     char buf[512];
@@ -232,14 +239,20 @@ void force_row(const omni_higgs_seq* s, const omni_higgs_draw& d, int32_t* out) 
   for (int b = 0; b < OMNI_HIGGS_CODEBOOKS; ++b) out[b] = d.has_force ? d.force[b] : (b >= from ? OMNI_HIGGS_BOC : -1);
 }
 
-// head GEMM + the eight draws + read-back (`first` / the tail of `decode`, model.rs:381-404; `run`, :226-240; `finish`, :267-272)
-int tail(omni_higgs* m, int n, omni_higgs_seq* const* seqs, const float* uniforms_dev, const int32_t* force_dev,
-         const int32_t* lines_dev, int32_t* rows_out, int32_t* ended_out) {
+// head GEMM + the eight draws (`first` / the tail of `decode`, model.rs:381-404)
+int tail_kernels(omni_higgs* m, int n, const float* uniforms_dev, const int32_t* force_dev, const int32_t* lines_dev) {
   const omni_higgs_config& c = m->cfg;
   const int head = OMNI_HIGGS_CODEBOOKS * c.code_vocab;
   HTRY(gemm(m, m->fused, head, c.body.hidden, m->hidden, n, m->logits, head));
   HLAUNCH(m, launch_higgs_sample(m->logits, c.code_vocab, c.temperature, c.top_k, uniforms_dev, force_dev,
                                  SlotState{m->state, lines_dev, m->stride}, m->codes, n, m->stream));
+  return OMNI_OK;
+}
+
+// The tail's kernels (unless a replayed graph already ran them) + read-back (`run`, model.rs:226-240; `finish`, :267-272)
+int tail(omni_higgs* m, int n, omni_higgs_seq* const* seqs, const float* uniforms_dev, const int32_t* force_dev,
+         const int32_t* lines_dev, int32_t* rows_out, int32_t* ended_out, bool kernels_done = false) {
+  if (!kernels_done) HTRY(tail_kernels(m, n, uniforms_dev, force_dev, lines_dev));
   const size_t ints = (size_t)n * OMNI_HIGGS_CODEBOOKS;
   HCUDA(m, cudaMemcpyAsync(m->out_host, m->codes, ints * 4, cudaMemcpyDeviceToHost, m->stream));
   HCUDA(m, cudaMemcpyAsync(m->out_host + ints, m->err, 4, cudaMemcpyDeviceToHost, m->stream));
@@ -301,6 +314,7 @@ int32_t omni_higgs_create(const omni_higgs_config* config, const omni_tensor* te
   if (prop.major != 10)
     return m->fail(OMNI_ERR_UNSUPPORTED, "device is sm_%d%d; this library is sm_100a only", prop.major, prop.minor);
   m->sm_count = prop.multiProcessorCount;
+  m->use_graphs = getenv("OMNI_HIGGS_NO_GRAPH") == nullptr;  // tuning aid: per-op launches every step
   HCUDA(m, cudaStreamCreateWithFlags(&m->stream, cudaStreamNonBlocking));
   HCUDA(m, cudaEventCreate(&m->ev0));
   HCUDA(m, cudaEventCreate(&m->ev1));
@@ -381,6 +395,8 @@ void omni_higgs_destroy(omni_higgs* m) {
   if (!m) return;
   cudaSetDevice(m->device);
   if (m->stream) cudaStreamSynchronize(m->stream);
+  for (auto& g : m->step_graphs)
+    if (g.second.exec) cudaGraphExecDestroy(g.second.exec);
   for (void* p : m->allocations) cudaFree(p);
   if (m->in_host) cudaFreeHost(m->in_host);
   if (m->out_host) cudaFreeHost(m->out_host);
@@ -497,13 +513,16 @@ int32_t omni_higgs_step(omni_higgs* m, int32_t n, omni_higgs_seq* const* seqs, c
   }
   HCUDA(m, cudaSetDevice(m->device));
   Staging st{m};
+  // every array but the page list has a size n fixes, and the page list comes last: the device addresses the step's
+  // kernels get depend on n alone, which is what lets the step be replayed as a CUDA graph
   int32_t *pos = st.take<int32_t>(n), *slot = st.take<int32_t>(n), *indptr = st.take<int32_t>(n + 1);
-  size_t page_count = 0;
-  for (int i = 0; i < n; ++i) page_count += seqs[i]->pages.size();
-  int32_t *pages = st.take<int32_t>(page_count), *lines = st.take<int32_t>(n);
+  int32_t* lines = st.take<int32_t>(n);
   float* uniforms = st.take<float>((size_t)n * OMNI_HIGGS_CODEBOOKS);
   int32_t* force = st.take<int32_t>((size_t)n * OMNI_HIGGS_CODEBOOKS);
-  if (!force) return m->fail(OMNI_ERR_INVALID, "staging block too small");
+  size_t page_count = 0;
+  for (int i = 0; i < n; ++i) page_count += seqs[i]->pages.size();
+  int32_t* pages = st.take<int32_t>(page_count);
+  if (!pages || !force) return m->fail(OMNI_ERR_INVALID, "staging block too small");
   indptr[0] = 0;
   for (int i = 0; i < n; ++i) {
     const omni_higgs_seq* s = seqs[i];
@@ -519,17 +538,47 @@ int32_t omni_higgs_step(omni_higgs* m, int32_t n, omni_higgs_seq* const* seqs, c
   m->launches = 0;
   HCUDA(m, cudaEventRecord(m->ev0, m->stream));
   HCUDA(m, cudaMemcpyAsync(m->in_dev, m->in_host, st.used, cudaMemcpyHostToDevice, m->stream));
-  // `decode` (model.rs:369-380): the last row's eight codes embedded, the body over one row per sequence
-  HLAUNCH(m, launch_higgs_frame_embed(SlotState{m->state, st.dev(lines), m->stride}, m->fused, m->embeds, n, c.body.hidden,
-                                      c.code_vocab, m->err, m->stream));
-  RowMap map;
-  map.pos = st.dev(pos);
-  map.slot = st.dev(slot);
-  map.seq = nullptr;
-  map.indptr = st.dev(indptr);
-  map.pages = st.dev(pages);
-  HTRY(body_forward(m, m->embeds, n, map, m->hidden));
-  return tail(m, n, seqs, st.dev(uniforms), st.dev(force), st.dev(lines), rows_out, ended_out);
+  // `decode` (model.rs:369-380): the last row's eight codes embedded, the body over one row per sequence, the head and
+  // the draws. Captured once per n (the first step of a size runs eagerly and creates the GEMM plans).
+  auto body = [&]() -> int {
+    HLAUNCH(m, launch_higgs_frame_embed(SlotState{m->state, st.dev(lines), m->stride}, m->fused, m->embeds, n,
+                                        c.body.hidden, c.code_vocab, m->err, m->stream));
+    RowMap map;
+    map.pos = st.dev(pos);
+    map.slot = st.dev(slot);
+    map.seq = nullptr;
+    map.indptr = st.dev(indptr);
+    map.pages = st.dev(pages);
+    HTRY(body_forward(m, m->embeds, n, map, m->hidden));
+    return tail_kernels(m, n, st.dev(uniforms), st.dev(force), st.dev(lines));
+  };
+  omni_higgs::StepGraph& sg = m->step_graphs[n];
+  if (!m->use_graphs || sg.seen == 0) {
+    HTRY(body());
+    sg.seen = 1;
+  } else {
+    if (!sg.exec) {
+      HCUDA(m, cudaStreamBeginCapture(m->stream, cudaStreamCaptureModeThreadLocal));
+      const int rc = body();
+      cudaGraph_t graph = nullptr;
+      const cudaError_t end = cudaStreamEndCapture(m->stream, &graph);  // always ends the capture, also after a failure
+      if (rc != OMNI_OK || end != cudaSuccess) {
+        if (graph) cudaGraphDestroy(graph);
+        cudaGetLastError();
+        return rc != OMNI_OK ? rc : m->fail(OMNI_ERR_CUDA, "step capture: %s", cudaGetErrorString(end));
+      }
+      const cudaError_t inst = cudaGraphInstantiate(&sg.exec, graph, 0);
+      cudaGraphDestroy(graph);
+      if (inst != cudaSuccess) {
+        sg.exec = nullptr;
+        return m->fail(OMNI_ERR_CUDA, "step graph: %s", cudaGetErrorString(inst));
+      }
+      sg.nodes = m->launches;
+    }
+    HCUDA(m, cudaGraphLaunch(sg.exec, m->stream));
+    m->launches = sg.nodes;
+  }
+  return tail(m, n, seqs, st.dev(uniforms), st.dev(force), st.dev(lines), rows_out, ended_out, true);
 }
 
 int32_t omni_higgs_read_logits(omni_higgs* m, int32_t s, void* dst, size_t bytes) {
