@@ -248,3 +248,34 @@ def test_cached_start_matches_direct_prefill_against_oracle(built_lib):
             assert float((np.abs(m.text_logits(i) - ref) / step).max()) <= 2.0
             assert cosine(m.audio_logits(i), orc.audio_logits[i]) >= 0.9995
     m.close()
+
+
+def test_graph_replay_equals_per_op_launches(built_lib, monkeypatch):
+    """A tick replayed as a CUDA graph (the default from the third tick of a session count on) gives bit-identical
+    draws and logits to the same tick issued kernel by kernel; a change of the session count in between takes the
+    eager path again and a second graph."""
+    from pega_omni_b200.duplex import PRESETS, Model, Step, random_checkpoint
+    c = PRESETS["duplex-mid"]
+    ck = random_checkpoint(c, seed=4, head_std=0.3)
+    rng = np.random.default_rng(9)
+    prompts = [make_prompt(c, rng, int(rng.integers(3, 9))) for _ in range(10)]
+    callers = [[[int(v) for v in rng.integers(0, c.card, 8)] for _ in range(10)] for _ in range(8)]
+
+    def run():
+        m = Model.load(0, ck, c, max_sessions=16, max_prefill=256)
+        ss = [m.open() for _ in prompts]
+        m.start(list(zip(ss, prompts)))
+        trace = []
+        for t in range(8):
+            live = ss if t not in (4, 5, 6) else ss[:9]  # three ticks with one session fewer
+            out = m.tick([(s, Step(caller=callers[t][i], seed=17 * t + i)) for i, s in enumerate(live)])
+            trace.append((out.emitted.copy(), m.text_logits(0).copy(), m.audio_logits(len(live) - 1).copy()))
+        m.close()
+        return trace
+
+    replayed = run()
+    monkeypatch.setenv("OMNI_DUPLEX_NO_GRAPH", "1")
+    launched = run()
+    for t, (g, e) in enumerate(zip(replayed, launched)):
+        for a, b in zip(g, e):
+            assert np.array_equal(a, b), t

@@ -218,3 +218,34 @@ def test_higgs_leases_and_validation(built_lib):
         HiggsModel.load(0, missing, c)
     assert e2.value.status == -4
     m.close()
+
+
+def test_graph_replay_equals_per_op_launches(built_lib, monkeypatch):
+    """A decode step replayed as a CUDA graph (the default from the third step of a sequence count on) gives
+    bit-identical rows and logits to the same step issued kernel by kernel; sequences of different lengths, so the
+    page list's length differs from step to step while the graph stays the same."""
+    from pega_omni_b200.higgs import HIGGS_PRESETS, HiggsDraw, HiggsModel, higgs_random_checkpoint
+    c = HIGGS_PRESETS["higgs-mid"]
+    ck = higgs_random_checkpoint(c, seed=2, embed_std=0.06)
+    rng = np.random.default_rng(4)
+    lens = [int(rng.integers(3, 40)) for _ in range(10)]
+    prompts = [rng.integers(0, c.body.vocab_size, k).astype(np.int32) for k in lens]
+    uniforms = [[[float(v) for v in rng.random(8)] for _ in lens] for _ in range(24)]
+
+    def run():
+        m = HiggsModel.load(0, ck, c, max_batch=16, max_tokens=512, kv_gib=0.05)
+        ss = [m.open(k, 30) for k in lens]
+        trace = []
+        for t in range(24):
+            draws = [HiggsDraw(u) for u in uniforms[t]]
+            out = m.start(list(zip(ss, prompts, draws))) if t == 0 else m.step(list(zip(ss, draws)))
+            trace.append((out.rows.copy(), m.logits(0).copy(), m.logits(9).copy()))
+        m.close()
+        return trace
+
+    replayed = run()
+    monkeypatch.setenv("OMNI_HIGGS_NO_GRAPH", "1")
+    launched = run()
+    for t, (g, e) in enumerate(zip(replayed, launched)):
+        for a, b in zip(g, e):
+            assert np.array_equal(a, b), t
