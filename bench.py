@@ -229,8 +229,8 @@ def run_higgs(args, rank, world, local):
             model.step(list(zip(seqs, draws())))
             ms, launches = model.stats()
             dev_ms.append(ms)
-    torch.cuda.synchronize()
-    wall = time.perf_counter() - t0
+        torch.cuda.synchronize()
+        wall = time.perf_counter() - t0  # before the sampler's shutdown
     t_wall = torch.tensor([wall], device="cuda", dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t_wall, op=dist.ReduceOp.MAX)
@@ -300,8 +300,8 @@ def run_duplex(args, rank, world, local):
             model.tick(list(zip(sessions, steps_for(W + t))))
             ms, launches = model.stats()
             dev_ms.append(ms)
-    torch.cuda.synchronize()
-    wall = time.perf_counter() - t0
+        torch.cuda.synchronize()
+        wall = time.perf_counter() - t0  # before the sampler's shutdown
     t_wall = torch.tensor([wall], device="cuda", dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t_wall, op=dist.ReduceOp.MAX)

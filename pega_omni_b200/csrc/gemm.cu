@@ -368,14 +368,21 @@ struct RmShape {
   static constexpr int kRingBytes = 192 * 1024;
   static constexpr int kMaxStages = 8;
   static constexpr size_t kSmemBytes = (size_t)kRingBytes + 1024 + 256;
-  static int stage_bytes(int tn, int kbs) { return kbs * (128 * kTileK * 2 + tn * kTileK * 2); }
-  static int stages(int tn, int kbs) { return std::min(kMaxStages, kRingBytes / stage_bytes(tn, kbs)); }
+  // bn: rows of the activation box (16, 32, 64 or 128). The MMA reads 128 rows from where the box starts, so with a
+  // smaller box it reads on into whatever follows (those TMEM lanes are never read back); 16 KB of the ring stay
+  // unused so that the last stage's reads end inside the CTA's shared memory.
+  static int box_rows(int rows) { return rows <= 16 ? 16 : rows <= 32 ? 32 : rows <= 64 ? 64 : 128; }
+  static int stage_bytes(int tn, int kbs, int bn) { return kbs * (bn * kTileK * 2 + tn * kTileK * 2); }
+  static int stages(int tn, int kbs, int bn) {
+    return std::min(kMaxStages, (kRingBytes - (bn < 128 ? 16 * 1024 : 0)) / stage_bytes(tn, kbs, bn));
+  }
   static uint32_t tmem_cols(int tn) { return tn <= 32 ? 32u : tn <= 64 ? 64u : tn <= 128 ? 128u : 256u; }
 };
 
 __global__ void __launch_bounds__(128, 1)
     gemm_rm_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap xmap,
-                   bf16* __restrict__ y, int ldy, int N, int K, int rows, int tn, int kbs, int n_stages, uint32_t tmem_cols,
+                   bf16* __restrict__ y, int ldy, int N, int K, int rows, int tn, int kbs, int bn, int n_stages,
+                   uint32_t tmem_cols,
                    const bf16* bias, int kind, uint32_t* err) {
   using namespace sm100;
   if (*reinterpret_cast<volatile uint32_t*>(err) != 0) return;
@@ -383,7 +390,7 @@ __global__ void __launch_bounds__(128, 1)
   const uint32_t raw = smem_addr(rm_smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
   unsigned char* base_ptr = rm_smem_raw + (base - raw);
-  const uint32_t x_bytes = (uint32_t)kbs * 128 * kTileK * 2, w_slice = (uint32_t)tn * kTileK * 2;
+  const uint32_t x_slice = (uint32_t)bn * kTileK * 2, x_bytes = (uint32_t)kbs * x_slice, w_slice = (uint32_t)tn * kTileK * 2;
   const uint32_t stage_bytes = x_bytes + (uint32_t)kbs * w_slice;
   const uint32_t bars = base + RmShape::kRingBytes;
   auto full_bar = [&](int s) { return bars + 8u * s; };
@@ -437,7 +444,7 @@ __global__ void __launch_bounds__(128, 1)
         tc_fence_after_sync();
         const uint32_t a_src = base + stage * stage_bytes, b_src = a_src + x_bytes;
         for (int j = 0; j < kbs; ++j) {
-          const uint64_t adesc = kmajor_sw128_desc(a_src + (uint32_t)j * (128 * kTileK * 2));
+          const uint64_t adesc = kmajor_sw128_desc(a_src + (uint32_t)j * x_slice);
           const uint64_t bdesc = kmajor_sw128_desc(b_src + (uint32_t)j * w_slice);
 #pragma unroll
           for (int k = 0; k < kTileK / 16; ++k)
@@ -637,23 +644,25 @@ int rm_plan(RmGemmPlan* plan, const bf16* w, int N, int K, const bf16* x, int ro
   const int nkb = K / kTileK;
   double best = 1e30;
   p.kbs = 1;
+  p.bn = RmShape::box_rows(rows);
   for (int kbs : {1, 2, 4}) {
     if (nkb % kbs) continue;
-    const int stages = RmShape::stages(p.TN, kbs);
+    const int stages = RmShape::stages(p.TN, kbs, p.bn);
     if (stages < 2) continue;
-    const double per_stage = std::max({0.38, RmShape::stage_bytes(p.TN, kbs) / 110e3, 2.0 / stages});
+    const double per_stage = std::max({0.38, RmShape::stage_bytes(p.TN, kbs, p.bn) / 110e3, 2.0 / stages});
     const double cost = per_stage * (nkb / kbs);
     if (cost < best - 1e-9) best = cost, p.kbs = kbs;
   }
   if (encode_kmajor3(&p.wmap, w, N, K, p.TN, p.kbs) != 0) return -4;
-  if (encode_kmajor3(&p.xmap, x, rows, K, 128, p.kbs) != 0) return -4;
+  if (encode_kmajor3(&p.xmap, x, rows, K, p.bn, p.kbs) != 0) return -4;
   return 0;
 }
 
 cudaError_t rm_launch(const RmGemmPlan& p, uint32_t* err, cudaStream_t stream) {
   if (p.TN < 16 || p.TN > 256 || p.TN % 16) return cudaErrorInvalidValue;
   gemm_rm_kernel<<<(p.N + p.TN - 1) / p.TN, 128, RmShape::kSmemBytes, stream>>>(
-      p.wmap, p.xmap, p.y, p.ldy, p.N, p.K, p.rows, p.TN, p.kbs, RmShape::stages(p.TN, p.kbs), RmShape::tmem_cols(p.TN),
+      p.wmap, p.xmap, p.y, p.ldy, p.N, p.K, p.rows, p.TN, p.kbs, p.bn, RmShape::stages(p.TN, p.kbs, p.bn),
+      RmShape::tmem_cols(p.TN),
       p.epi.bias,
       p.epi.kind, err);
   return cudaGetLastError();

@@ -63,7 +63,7 @@ cudaError_t tc_launch(const TcGemmPlan& plan, const GemmScratch& scratch, uint32
 // weight rows over the whole K, no split and no reduction. For decode-sized GEMMs with small weight matrices.
 struct RmGemmPlan {
   CUtensorMap wmap, xmap;
-  int N = 0, K = 0, rows = 0, TN = 64, kbs = 1;  // TN weight rows per CTA, kbs k-blocks per TMA copy
+  int N = 0, K = 0, rows = 0, TN = 64, kbs = 1, bn = 128;  // TN weight rows per CTA, kbs k-blocks per TMA copy, bn rows per activation box
   bf16* y = nullptr;
   int ldy = 0;
   Epilogue epi;
