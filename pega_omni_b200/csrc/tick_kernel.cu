@@ -595,7 +595,8 @@ __device__ __forceinline__ void rope_attn_dg(const Phase& ph, const TickIo& io, 
       rope_attend_item<D, G, 2>(ph, io, partials, it / hk, it % hk, wtid & 63, sh, PairBar{4 + team}, err);
   } else {  // one page per sequence: a warp per item
     auto& sh = reinterpret_cast<AttnShared<D, G, 1>&>(scratch.attn1[wtid >> 5]);
-    const int wid = (int)blockIdx.x * (kWorkerThreads / 32) + (wtid >> 5), n_warps = (int)gridDim.x * (kWorkerThreads / 32);
+    // warp ids run over the CTAs first, so a phase with few items spreads over as many SMs as it has items
+    const int wid = (wtid >> 5) * (int)gridDim.x + (int)blockIdx.x, n_warps = (int)gridDim.x * (kWorkerThreads / 32);
     for (int it = wid; it < items; it += n_warps)
       rope_attend_item<D, G, 1>(ph, io, partials, it / hk, it % hk, wtid & 31, sh, WarpSync(), err);
   }
