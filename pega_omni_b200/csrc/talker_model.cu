@@ -92,7 +92,7 @@ struct Tiling {
   double cost = 1e30;
 };
 
-Tiling choose_tiling(int N, int K, int ctas, bool swiglu) {
+Tiling choose_tiling(int N, int K, int ctas, bool swiglu, int bn = 64) {
   Tiling best;
   const int nkb = K / 64;
   for (int direct = swiglu ? 1 : 0; direct >= 0; --direct) {
@@ -108,7 +108,7 @@ Tiling choose_tiling(int N, int K, int ctas, bool swiglu) {
           if (const char* e = getenv("OMNI_TICK_COST")) sscanf(e, "%lf,%lf,%lf,%lf", &v[0], &v[1], &v[2], &v[3]);
           return v;
         }();
-        const double per_kb = std::max(tune[0], (tn * 128.0 + 8192.0) / tune[1]);
+        const double per_kb = std::max(tune[0], (tn * 128.0 + bn * 128.0) / tune[1]);  // weight + activation bytes
         double cost = waves * (kb * per_kb + tune[2]) + tune[3] * S;
         if (swiglu && !direct) cost += 5.0;
         if (cost < best.cost - 1e-9) best = Tiling{tn, S, direct != 0, cost};
@@ -533,7 +533,9 @@ struct TickBuilder {
   Phase gemm(const bf16* w, int N, int K, const bf16* x, int rows, bool swiglu = false, bf16* act = nullptr,
              int inter = 0, int granule = 0) {
     Phase ph = blank(kPhGemm, rows);
-    Tiling t = choose_tiling(N, K, ctas, swiglu);
+    // (the model's constants were fitted at 64 rows; taller activation tiles count their bytes, shorter ones measured
+    // better with the 64-row figure)
+    Tiling t = choose_tiling(N, K, ctas, swiglu, std::max(64, pick_bn(rows)));
     if (swiglu && t.tile_n != 2 * granule) {  // the weights were regrouped for another tile width: keep that one
       t.tile_n = 2 * granule;
       if (t.swiglu_direct) t.splits = 1;
