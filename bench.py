@@ -457,14 +457,14 @@ def main():
         tick_bytes = cfg.tick_weight_bytes() + cfg.talker.kv_bytes_per_token() * n * (mean_len + 1)
         tick_s = elapsed / K
         # the dominant kernel IS the tick: one persistent cooperative launch per step (or, with --per-op, the graph)
-        roof = {"bound": "hbm", "kernel": "tick_kernel (whole decode tick)" if launches_per_tick == 1 else "per-op graph",
+        roof = {"bound": "hbm", "kernel": "tick_kernel + pred_kernel (whole decode tick)" if launches_per_tick <= 2 else "per-op graph",
                 "achieved": tick_bytes / tick_s / 1e9, "peak": peak, "unit": "GB/s",
                 "frac": tick_bytes / tick_s / 1e9 / peak, "peak_source": f"of {peak_kind}",
                 "bytes_per_launch": int(tick_bytes), "us_per_launch": tick_s * 1e6,
                 # ncu cannot run inside the timed region: the DRAM bytes of one captured tick of this kernel
                 # (profiles/tick_kernel_qwen3tts_64sessions.md: 6,399 MB read+written for 6,296 MB algorithmic at
                 # positions 131-132) scaled to this run's algorithmic bytes; traffic grows with the KV length as they do
-                "traffic": int(tick_bytes * 6399.1 / 6296.2) if launches_per_tick == 1 else None,
+                "traffic": int(tick_bytes * 6399.1 / 6296.2) if launches_per_tick <= 2 else None,
                 "traffic_note": "ncu dram__bytes_read+write of one captured tick (6.399 GB for 6.296 GB algorithmic), "
                                 "scaled by this run's algorithmic bytes"}
         line = {
@@ -478,7 +478,7 @@ def main():
                        "step": "one decode tick = 64 frames per GPU", "positions": [lens[0], lens[-1]],
                        "parallelism": f"{world} replica(s), sessions round-robin, no collective",
                        "l2": "each tick streams 5.3 GB of weights, far larger than the 126 MB L2",
-                       "engine": "persistent tick kernel" if launches_per_tick == 1 else "per-op CUDA graph"},
+                       "engine": "persistent tick kernel" if launches_per_tick == 1 else "persistent talker kernel + cluster predictor kernel" if launches_per_tick == 2 else "per-op CUDA graph"},
             "tick_p99_ms": float(t_p99.item()), "tick_p50_ms": float(np.percentile(tick_ms, 50)),
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
                     "timing": "wall clock around K Model.step_batch calls (each stages its inputs, runs the tick and waits for its frame), max over ranks",

@@ -21,6 +21,7 @@
 #include "../../include/omni_b200.h"
 #include "gemm.h"
 #include "kernels.h"
+#include "predictor.h"
 #include "tick.h"
 
 namespace omni {
@@ -192,6 +193,15 @@ struct omni_talker {
   int tick_ctas = 0;
   uint32_t* tick_barrier = nullptr;
   uint32_t tick_barrier_base = 0;  // arrivals left in the counter by earlier launches
+  // split-K partial tiles of the tick kernel: its own buffer (the kernel hands elements over through an "unset" bit
+  // pattern that must be in place between launches, so nothing else may write here); grown when a program needs more
+  float* tick_partials = nullptr;
+  size_t tick_partial_floats = 0;
+  // the code predictor's sub-steps as one launch of thread-block clusters (predictor.h): clusters that can be
+  // resident at once (0: this device or shape cannot run it), one compiled entry list per bucket, exchange buffer
+  int pred_clusters = 0;
+  std::map<int, PredProgram> pred_programs;
+  float* pred_vbuf = nullptr;
   std::map<std::pair<int, int>, TickProgram> tick_programs;
   int launches = 0, tick_phases = 0;
   std::string trace_path;
@@ -643,8 +653,9 @@ struct TickBuilder {
     offset = (offset + rows) % ctas;
   }
 
-  // `Talker::advance` + `Talker::tail` (talker.rs:224-251, 293-356) at bucket b.
-  void build(int program, int b) {
+  // `Talker::advance` + `Talker::tail` (talker.rs:224-251, 293-356) at bucket b. with_predictor = false: the list ends
+  // with the first codebook's draw (which also writes the predictor's two input rows); the cluster kernel does the rest.
+  void build(int program, int b, bool with_predictor = true) {
     const omni_talker_config& c = m->cfg;
     const int h = c.talker.hidden, p = c.predictor.hidden, V = c.talker.vocab, PV = c.predictor.vocab;
     if (program == kDecode) {
@@ -659,7 +670,7 @@ struct TickBuilder {
     }
     const Phase head = gemm(m->codec_head, V, h, m->hidden, b);
     sample(head, 0, b, m->logits, V, kNextHiddenAndCode, m->codec_emb, m->hidden, m->p_in, h);
-    for (int g = 1; g < c.groups; ++g) {
+    for (int g = 1; g < c.groups && with_predictor; ++g) {
       const int per = g == 1 ? 2 : 1, rows = b * per;
       const Phase mtp = gemm(m->mtp_w, p, h, m->p_in, rows);
       row_phase(kPhReduceNorm, mtp, rows, p, m->mtp_b, m->pred.layers[0].ln1, m->P.res, m->P.x, c.predictor.rms_eps);
@@ -668,6 +679,142 @@ struct TickBuilder {
       const bool more = g + 1 < c.groups;
       sample(ph, g, b, m->p_logits + (size_t)(g - 1) * m->max_seqs * PV, PV, more ? kNextCode : kNextNone,
              more ? m->p_emb + (size_t)(g - 1) * PV * h : nullptr, nullptr, m->p_in, h);
+    }
+  }
+};
+
+// ---- the cluster predictor kernel's entry list ----------------------------------------------------------------
+
+// Sessions per cluster and clusters for bucket b (0 clusters: the bucket does not fit the resident clusters).
+void pred_partition(const omni_talker* m, int b, int* per_cluster, int* clusters) {
+  const int use = std::min(m->pred_clusters, b);
+  *per_cluster = use > 0 ? (b + use - 1) / use : 0;
+  *clusters = *per_cluster > 0 && *per_cluster <= kPredRows ? (b + *per_cluster - 1) / *per_cluster : 0;
+}
+
+bool pred_shape_ok(const omni_talker_config& c, int granule) {
+  const omni_stack_config &t = c.talker, &p = c.predictor;
+  const int C = p.q_heads;
+  if (!(C == 2 || C == 4 || C == 8 || C == 16) || p.head_dim != 128 || 2 * p.kv_heads != C || p.hidden != 64 * C) return false;
+  if ((2 * p.inter) % (C * 128) != 0 || !(granule == 32 || granule == 64)) return false;
+  const int per = p.vocab / C;
+  if (p.vocab % C || !(per == 64 || per % 128 == 0) || p.vocab % 16 || p.vocab > 4096) return false;
+  if (t.hidden % 64 || p.hidden % 128 || p.inter % 64) return false;
+  return c.groups >= 2;
+}
+
+bool pred_usable(const omni_talker* m, int b) {
+  if (m->pred_clusters <= 0) return false;
+  int per = 0, clusters = 0;
+  pred_partition(m, b, &per, &clusters);
+  return clusters > 0;
+}
+
+struct PredBuilder {
+  omni_talker* m;
+  PredProgram* prog;
+  std::map<std::tuple<const void*, int64_t, int, int64_t, int, int>, int> map_cache;
+  bool failed = false;
+  int bars = 0;  // cluster barriers the kernel passes before the next entry
+
+  int map_of(const bf16* base, int64_t rows, int K, int64_t row_stride, int box_rows, int kbs) {
+    const auto key = std::make_tuple((const void*)base, rows, K, row_stride, box_rows, kbs);
+    auto it = map_cache.find(key);
+    if (it != map_cache.end()) return it->second;
+    const int idx = pred_add_map(prog, base, rows, K, row_stride, box_rows, kbs);
+    if (idx < 0) failed = true;
+    map_cache[key] = idx;
+    return idx;
+  }
+  static int stage_kblocks(int nkb, int cap) {
+    for (int k = cap; k > 1; --k)
+      if (nkb % k == 0) return k;
+    return 1;
+  }
+
+  // One box of `rows` weight rows of w [n, K]; x: the activation rows read through TMA (nullptr: the resident tile).
+  PredEntry& box(int epi, const bf16* w, int64_t n, int K, int rows, int wrow, int cta_stride, const bf16* x, int x_cols,
+                 int64_t x_stride, int xz0) {
+    PredEntry e;
+    memset(&e, 0, sizeof(e));
+    e.epi = epi;
+    e.rows = rows;
+    e.nkb = K / 64;
+    e.kbs = stage_kblocks(e.nkb, rows == 64 ? 4 : 2);
+    e.wmap = map_of(w, n, K, K, rows, e.kbs);
+    e.wrow = wrow;
+    e.cta_stride = cta_stride;
+    e.xmap = x ? map_of(x, m->max_seqs, x_cols, x_stride, kPredRows, e.kbs) : -1;
+    e.xz0 = xz0;
+    e.need_bars = bars;
+    prog->entries.push_back(e);
+    return prog->entries.back();
+  }
+
+  // The sub-steps at positions 0 .. groups-1 of the frame (`Talker::tail`, talker.rs:300-356): position 0 is the
+  // talker's hidden row (no head), position j >= 1 the embedding of code j-1 followed by head j-1 and the draw of
+  // code j. The reference runs positions 0 and 1 as one two-row pass; row by row the arithmetic is the same.
+  void build(int b) {
+    const omni_talker_config& c = m->cfg;
+    const omni_stack_config& pc = c.predictor;
+    const int h = c.talker.hidden, p = pc.hidden, PV = pc.vocab, C = pc.q_heads, I = pc.inter, qd = pc.q_heads * pc.head_dim;
+    const StackW& S = m->pred;
+    PredConfig& cfg = prog->cfg;
+    cfg.C = C, cfg.hidden = p, cfg.q_heads = pc.q_heads, cfg.kv_heads = pc.kv_heads, cfg.inter = I, cfg.granule = S.granule;
+    cfg.vocab = PV, cfg.next_stride = 2 * h;
+    cfg.temperature = c.sub_temperature, cfg.top_p = c.top_p, cfg.top_k = c.sub_top_k;
+    cfg.philox = c.sampler == OMNI_SAMPLER_PHILOX;
+    prog->rows = b;
+    pred_partition(m, b, &prog->per_cluster, &prog->clusters);
+    for (int j = 0; j < c.groups; ++j) {
+      {  // the input row through small_to_mtp_projection (talker.rs:306-312): p_in holds [hidden | code embedding] per session
+        PredEntry& e = box(kPeBiasNorm, m->mtp_w, p, h, 64, 0, 64, m->p_in, 2 * h, 2 * h, j == 0 ? 0 : h / 64);
+        e.p0 = m->mtp_b, e.p1 = S.layers[0].ln1, e.eps = pc.rms_eps, e.pos = j;
+        bars += 1;
+      }
+      for (int i = 0; i < pc.layers; ++i) {
+        const StackW::Layer& L = S.layers[i];
+        {
+          PredEntry& e = box(kPeQ, L.qkv, S.qkv_width(), p, 128, 0, 128, nullptr, 0, 0, 0);
+          e.p0 = L.q_norm, e.eps = pc.rms_eps, e.theta = pc.rope_theta, e.pos = j;
+        }
+        {
+          PredEntry& e = box(kPeKv, L.qkv, S.qkv_width(), p, 128, pc.q_heads * 128, 128, nullptr, 0, 0, 0);
+          e.wrow2 = (pc.q_heads + pc.kv_heads) * 128;
+          e.p0 = L.k_norm, e.q0 = m->pkv[i], e.q1 = m->P.attn, e.eps = pc.rms_eps, e.theta = pc.rope_theta, e.pos = j;
+          bars += 2;
+        }
+        {
+          PredEntry& e = box(kPeAddNorm, L.o, p, qd, 64, 0, 64, m->P.attn, qd, qd, 0);
+          e.p1 = L.ln2, e.eps = pc.rms_eps, e.pos = j;
+          bars += 1;
+        }
+        const int gu_rows = 2 * I / C, gu_boxes = gu_rows / 128;
+        for (int bb = 0; bb < gu_boxes; ++bb) {
+          PredEntry& e = box(kPeSwiglu, L.gate_up, 2 * I, p, 128, bb * 128, gu_rows, nullptr, 0, 0, 0);
+          e.q0 = m->P.act, e.last = bb + 1 == gu_boxes, e.pos = j;
+          if (e.last) bars += 1;
+        }
+        {
+          PredEntry& e = box(kPeAddNorm, L.down, p, I, 64, 0, 64, m->P.act, I, I, 0);
+          e.p1 = i + 1 < pc.layers ? S.layers[i + 1].ln1 : S.norm, e.eps = pc.rms_eps, e.pos = j;
+          bars += 1;
+        }
+      }
+      if (j == 0) continue;
+      const int per = PV / C, hb = per == 64 ? 64 : 128, head_boxes = per / hb;
+      for (int bb = 0; bb < head_boxes; ++bb) {
+        PredEntry& e = box(kPeHead, m->lm_heads, (int64_t)(c.groups - 1) * PV, p, hb, (j - 1) * PV + bb * hb, per, nullptr, 0, 0, 0);
+        e.col0 = bb * hb, e.group = j, e.pos = j, e.last = bb + 1 == head_boxes;
+        e.q0 = m->p_logits + (size_t)(j - 1) * m->max_seqs * PV;
+        if (e.last) {
+          const bool more = j + 1 < c.groups;
+          e.next_dim = more ? h : 0;
+          e.p0 = more ? m->p_emb + (size_t)(j - 1) * PV * h : nullptr;
+          e.q1 = m->p_in + h;  // the code-embedding half of a session's input row
+          bars += 2;
+        }
+      }
     }
   }
 };
@@ -684,15 +831,24 @@ bool tick_usable(const omni_talker* m, int b) {
 }
 
 int run_tick_program(omni_talker* m, int program, int b) {
+  const bool clusters = pred_usable(m, b);  // the predictor's sub-steps run as a second launch of thread-block clusters
   auto key = std::make_pair(program, b);
   auto it = m->tick_programs.find(key);
   if (it == m->tick_programs.end()) {
     TickProgram prog;
     TickBuilder builder{m, &prog, m->tick_ctas};
-    builder.build(program, b);
+    builder.build(program, b, !clusters);
     if (builder.failed) return m->fail(OMNI_ERR_CUDA, "tensor-map encode failed while compiling the tick program");
-    if (prog.partial_floats > m->gemm_scratch.partial_floats)
-      return m->fail(OMNI_ERR_UNSUPPORTED, "split-K scratch too small for the tick program");
+    if (!tick_finish(&prog)) return m->fail(OMNI_ERR_UNSUPPORTED, "tick program: a split-K GEMM without its consumer");
+    if (prog.partial_floats > m->tick_partial_floats) {
+      // first program of this size (a first call at a larger bucket): no launch is in flight once the stream is idle
+      CUDA_TRY(m, cudaStreamSynchronize(m->stream));
+      if (m->tick_partials) cudaFree(m->tick_partials);
+      m->tick_partials = nullptr, m->tick_partial_floats = 0;
+      CUDA_TRY(m, cudaMalloc((void**)&m->tick_partials, prog.partial_floats * sizeof(float)));
+      m->tick_partial_floats = prog.partial_floats;
+      CUDA_TRY(m, tick_reset_partials(m->tick_partials, m->tick_partial_floats, m->stream));
+    }
     if (tick_upload(&prog) != 0) return m->fail(OMNI_ERR_CUDA, "uploading the tick program failed");
     it = m->tick_programs.emplace(key, prog).first;
   }
@@ -720,9 +876,21 @@ int run_tick_program(omni_talker* m, int program, int b) {
     m->trace_program = &it->second;
     CUDA_TRY(m, cudaMemsetAsync(m->trace, 0, (size_t)4 * kTraceMaxPhases * m->tick_ctas * 8, m->stream));
   }
-  LAUNCH(m, tick_launch(it->second, io, m->gemm_scratch.partials, m->tick_barrier, &m->tick_barrier_base, m->err,
+  LAUNCH(m, tick_launch(it->second, io, m->tick_partials, m->tick_barrier, &m->tick_barrier_base, m->err,
                         m->tick_ctas, m->stream,
                         m->trace && m->tick_phases <= kTraceMaxPhases ? m->trace : nullptr));
+  if (clusters) {
+    auto pit = m->pred_programs.find(b);
+    if (pit == m->pred_programs.end()) {
+      PredProgram prog;
+      PredBuilder builder{m, &prog};
+      builder.build(b);
+      if (builder.failed) return m->fail(OMNI_ERR_CUDA, "tensor-map encode failed while compiling the predictor program");
+      if (pred_upload(&prog) != 0) return m->fail(OMNI_ERR_CUDA, "uploading the predictor program failed");
+      pit = m->pred_programs.emplace(b, prog).first;
+    }
+    LAUNCH(m, pred_launch(pit->second, io, m->pred_vbuf, m->err, m->stream));
+  }
   return OMNI_OK;
 }
 
@@ -888,6 +1056,7 @@ int finish_call(omni_talker* m, int n, int32_t* codes, float* wav) {
   const uint32_t err = (uint32_t)m->out_host[(size_t)m->max_seqs * OMNI_GROUPS];
   if (err != 0) {
     m->tick_barrier_base = ~0u;  // CTAs of the failed launch may not all have arrived: restart the counter
+    if (m->tick_partials) tick_reset_partials(m->tick_partials, m->tick_partial_floats, m->stream);
     cudaMemsetAsync(m->err, 0, 4, m->stream);
     cudaStreamSynchronize(m->stream);
     return m->fail(OMNI_ERR_DEVICE, "device error word 0x%x (1: barrier wait ran out, 2: index out of range)", err);
@@ -914,7 +1083,9 @@ void omni_talker_destroy(omni_talker* m) {
   if (m->stream) cudaStreamSynchronize(m->stream);
   for (auto& g : m->graphs) cudaGraphExecDestroy(g.second);
   for (auto& t : m->tick_programs) tick_free(&t.second);
+  for (auto& t : m->pred_programs) pred_free(&t.second);
   for (void* p : m->allocations) cudaFree(p);
+  if (m->tick_partials) cudaFree(m->tick_partials);
   if (m->in_host) cudaFreeHost(m->in_host);
   if (m->out_host) cudaFreeHost(m->out_host);
   if (m->ev0) cudaEventDestroy(m->ev0);
@@ -993,6 +1164,7 @@ static int create_impl(omni_talker* m, const omni_tensor* tensors, int32_t n_ten
   }
   TRY(load_stack(m, idx, "talker.model", t, &m->talker));
   TRY(load_stack(m, idx, "talker.code_predictor.model", pc, &m->pred));
+  if (c.tick_kernel == 1 && m->tick_ok && pred_shape_ok(c, m->pred.granule)) m->pred_clusters = pred_configure(pc.q_heads);
 
   // pools (model.rs:111-131,306-309)
   m->max_seqs = bucket_of(c.max_batch);
@@ -1030,6 +1202,7 @@ static int create_impl(omni_talker* m, const omni_tensor* tensors, int32_t n_ten
   TRY(dev_alloc(m, &m->p_in, (size_t)2 * m->max_seqs * h));
   TRY(dev_alloc(m, &m->p_h, (size_t)2 * m->max_seqs * p));
   TRY(dev_alloc(m, &m->p_last, (size_t)m->max_seqs * p));
+  if (m->pred_clusters > 0) TRY(dev_alloc(m, &m->pred_vbuf, (size_t)m->max_seqs * p, true));
   TRY(dev_alloc(m, &m->logits, (size_t)m->max_seqs * V, true));
   TRY(dev_alloc(m, &m->p_logits, (size_t)(G - 1) * m->max_seqs * PV, true));
   TRY(dev_alloc(m, &m->codes, (size_t)m->max_seqs * OMNI_GROUPS + 1, true));
@@ -1307,6 +1480,8 @@ int32_t omni_talker_run_ticks(omni_talker* m, int32_t n, omni_seq* const* seqs, 
     CUDA_TRY(m, cudaMemcpy(&err, m->err, 4, cudaMemcpyDeviceToHost));
     if (err != 0) {
       m->tick_barrier_base = ~0u;
+      if (m->tick_partials) tick_reset_partials(m->tick_partials, m->tick_partial_floats, m->stream);
+      cudaStreamSynchronize(m->stream);
       cudaMemset(m->err, 0, 4);
       return m->fail(OMNI_ERR_DEVICE, "device error word 0x%x", err);
     }
