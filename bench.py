@@ -6,8 +6,10 @@
 Prints ONE JSON line (rank 0). `value`: codec frames/s over all GPUs with every tick's inputs already in HBM
 (`omni_talker_run_ticks`), timed per tick with CUDA events on the model's stream, max over ranks. `e2e`: the same
 metric through the public `Model.step` call with host draws (H2D staging and D2H frame read-back inside each step).
-`--impl reference` times the CPU restatement of the reference's path (the reference's implementation of this path is
-CUDA-only and needs an un-vendored Rust runtime, so the CPU arm is the oracle port) on a bounded sample.
+`--impl reference` times the reference's own implementation of this path: it is CUDA-only (no CPU decode exists in
+the reference), so the arm runs the reference's kernels — compiled from its sources into oracle/_ref — sequenced as
+its manifest emits them with cuBLAS GEMMs, one CUDA graph per tick, on every rank's GPU with the same sessions and
+positions. `cpu_baseline` (rank 0, N = 1) is the CPU restatement on all host cores, on a bounded sample.
 """
 from __future__ import annotations
 
@@ -47,11 +49,19 @@ class ClockSampler:
 
     def __init__(self, index: int):
         self.index, self.rows, self.proc = index, [], None
+        self.t0 = self.t1 = None
+
+    def mark_start(self):
+        """The timed region begins now: only samples read between the two marks are summarised."""
+        self.t0 = time.monotonic()
+
+    def mark_end(self):
+        self.t1 = time.monotonic()
 
     def __enter__(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "50",
                  "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -61,7 +71,7 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.rows.append([c.strip() for c in line.split(",")])
+            self.rows.append((time.monotonic(), [c.strip() for c in line.split(",")]))
 
     def __exit__(self, *exc):
         if self.proc:
@@ -74,7 +84,13 @@ class ClockSampler:
     def summary(self):
         sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for r in self.rows:
+        # a sample is printed up to one period after it was taken: keep those read inside the timed window, widened by
+        # one period at the end; when the window is shorter than the sampling period, the nearest sample after its start
+        rows = [r for t, r in self.rows if self.t0 is None or (self.t0 <= t <= (self.t1 or t) + 0.06)]
+        if not rows and self.rows and self.t0 is not None:
+            later = [r for t, r in self.rows if t >= self.t0]
+            rows = later[:1] or [self.rows[-1][1]]
+        for r in rows:
             try:
                 sm.append(float(r[1]))
                 mx.append(float(r[2]))
@@ -103,7 +119,7 @@ def draws_for(ticks, sessions, seed):
     return [[Draw(list(u[t, s])) for s in range(sessions)] for t in range(ticks)]
 
 
-def replay_baseline(cfg, ck, sessions, prompt_len, warmup, steps, seed=0):
+def replay_baseline(cfg, ck, sessions, prompt_len, warmup, steps, seed=0, clocks=None):
     """The reference's own kernels (compiled for sm_100a into oracle/_ref) sequenced as its manifest does, GEMMs on
     cuBLAS, one CUDA graph per tick like its `decode` program: the 'reference build on the same box'. Returns None
     when the cubins are not there. Timing: CUDA events around `steps` graph replays on torch's current stream."""
@@ -121,6 +137,8 @@ def replay_baseline(cfg, ck, sessions, prompt_len, warmup, steps, seed=0):
     ev = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
     us = [rng.random((sessions, 16)).astype(np.float32) for _ in range(steps)]
     torch.cuda.synchronize()
+    if clocks is not None:
+        clocks.mark_start()
     ev[0].record()
     for t in range(steps):
         r._stage(us[t], free)
@@ -128,8 +146,11 @@ def replay_baseline(cfg, ck, sessions, prompt_len, warmup, steps, seed=0):
         r.n_frames += 1
         ev[t + 1].record()
     torch.cuda.synchronize()
+    if clocks is not None:
+        clocks.mark_end()
     ms = np.array([ev[t].elapsed_time(ev[t + 1]) for t in range(steps)])
     return {"value": sessions * steps / (ms.sum() * 1e-3), "unit": UNIT, "ms_per_step": float(ms.mean()),
+            "elapsed_s": float(ms.sum()) * 1e-3, "h2d_bytes_per_step": int(2 * sessions * 16 * 4),
             "tick_p99_ms": float(np.percentile(ms, 99)), "graph_nodes": int(r.graph_nodes),
             "what": "reference qwen3.cu + talker.cu kernels (sm_100a cubins) + cuBLAS bf16 GEMMs, one CUDA graph per "
                     "tick, no codec tail; input staging copies inside the timed region"}
@@ -140,8 +161,8 @@ def cpu_baseline(cfg, ck_host, threads=None, sessions=4, prompt_len=16, warmup=1
     `sessions` sessions, short prompts, `ticks` decode ticks. Returns frames/s, cores used, per-tick seconds."""
     from oracle import cpu as orc
     lib = orc.load()
-    if threads:
-        lib.orc_set_threads(threads)
+    # every host core, asked for by name: a launcher may have set OMP_NUM_THREADS=1 in this process's environment
+    lib.orc_set_threads(threads or os.cpu_count() or 1)
     cores = lib.orc_max_threads()
     o = orc.CpuOracle(cfg, ck_host)
     prompts = workload(cfg, sessions, prompt_len, seed)
@@ -162,29 +183,70 @@ def cpu_baseline(cfg, ck_host, threads=None, sessions=4, prompt_len=16, warmup=1
                       f"prompts (the GPU workload runs 64 sessions x 128-token prompts)"}, per_tick
 
 
-def run_reference(args, rank):
-    """CPU arm: the oracle port on all host cores. Rank 0 only."""
-    if rank != 0:
-        return
+CONFIG_WORKLOAD = ("configs[1]: Qwen3-TTS-12Hz-1.7B talker (28L h2048 16q/8kv d128 i6144, head 3072) + "
+                   "code predictor (5L h1024, 15 codebooks x 2048), random bf16 weights N(0,0.02)")
+
+
+def run_reference(args, rank, world, local):
+    """The reference arm: the reference's own kernels on this rank's GPU (see replay_baseline), the same sessions,
+    prompts and positions as the library's arm; every rank runs its replica, the time is the max over ranks. Rank 0
+    prints the line. With N = 1 the line also carries the CPU restatement's number (`cpu_baseline`)."""
     import torch
+    import torch.distributed as dist
+    if not torch.cuda.is_available():
+        if rank == 0:
+            print(json.dumps({"impl": "reference", "unavailable": "no CUDA device: the reference's path is CUDA-only"}))
+        return
+    from oracle import ref_kernels
+    if not ref_kernels.available():
+        if rank == 0:
+            print(json.dumps({"impl": "reference", "unavailable": "oracle/_ref holds no reference cubins (built from "
+                              "the reference checkout by __graft_entry__.build())"}))
+        return
     from pega_omni_b200.config import presets
     from pega_omni_b200.synthetic import random_checkpoint
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    W, K = max(3, args.warmup), args.steps
     cfg = presets["qwen3-tts-1.7b"]()
-    ck = random_checkpoint(cfg, seed=0, device="cuda" if torch.cuda.is_available() else "cpu")
-    ck = {k: v.cpu() for k, v in ck.items()}
-    sessions = 4
-    base, per_tick = cpu_baseline(cfg, ck, sessions=sessions, warmup=max(0, min(args.warmup, 3)),
-                                  ticks=max(1, min(args.steps, 24)))
-    ms = 1e3 * float(np.mean(per_tick))
-    line = {"impl": "reference", "metric": METRIC, "value": base["value"], "unit": UNIT, "n_gpus": args.gpus,
-            "steps": len(per_tick), "warmup": max(0, min(args.warmup, 3)), "ms_per_step": ms,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": "Qwen3-TTS-12Hz-1.7B talker architecture, decode tick = talker step + 15 "
-                                   "code-predictor sub-steps; CPU arm on a bounded sample", "sessions": sessions,
-                       "note": "requested steps/warmup are clamped (24/3) so the CPU run ends in minutes"},
-            "cpu_baseline": base,
-            "e2e": {"value": base["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-            "gpu_launches": 0}
+    ck = random_checkpoint(cfg, seed=0, device="cuda")
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    with ClockSampler(local) as clocks:
+        rep = replay_baseline(cfg, ck, args.sessions, args.prompt, W, K, seed=rank, clocks=clocks)
+    t_el = torch.tensor([rep["elapsed_s"]], device="cuda", dtype=torch.float64)
+    t_p99 = torch.tensor([rep["tick_p99_ms"]], device="cuda", dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t_el, op=dist.ReduceOp.MAX)
+        dist.all_reduce(t_p99, op=dist.ReduceOp.MAX)
+        dist.barrier()
+        dist.destroy_process_group()  # the other ranks leave here; rank 0 alone may go on to the CPU leg
+    if rank != 0:
+        return
+    value = args.sessions * world * K / float(t_el.item())
+    line = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
+            "ms_per_step": 1e3 * float(t_el.item()) / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": CONFIG_WORKLOAD, "sessions_per_gpu": args.sessions, "prompt_tokens": args.prompt,
+                       "kv_page": 16, "sampling": "top-k 50, T 0.9, repetition penalty 1.05, host uniforms",
+                       "step": "one decode tick = %d frames per GPU" % args.sessions,
+                       "parallelism": f"{world} replica(s), no collective",
+                       "engine": rep["what"]},
+            "tick_p99_ms": float(t_p99.item()), "graph_nodes": rep["graph_nodes"], "clocks": clocks.summary(),
+            "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": rep["h2d_bytes_per_step"], "d2h_bytes_per_step": 0,
+                    "timing": "the arm's timed region already holds its per-tick input staging copies"},
+            "gpu_launches": int(rep["graph_nodes"] * K),
+            "reference_kind": "reference (its CUDA sources compiled unmodified for sm_100a into oracle/_ref; the Rust "
+                              "runtime that sequences them is not in the reference tree, so the sequencing and the "
+                              "cuBLAS calls are this repository's)"}
+    if world == 1 and not args.no_cpu_baseline:
+        del ck
+        torch.cuda.empty_cache()
+        ck_host = {k: v.cpu() for k, v in random_checkpoint(cfg, seed=0, device="cuda").items()}
+        base, _ = cpu_baseline(cfg, ck_host)
+        line["cpu_baseline"] = base
     print(json.dumps(line), flush=True)
 
 
@@ -353,7 +415,7 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
-        run_reference(args, rank)
+        run_reference(args, rank, world, local)
         return
 
     import torch
@@ -384,9 +446,9 @@ def main():
     model = Model.load(local, ck, cfg, Limits(args.sessions, args.sessions * args.prompt, kv_gib),
                        use_graphs=not args.no_graphs, tick_kernel=not args.per_op)
     ck_host = None
-    if rank == 0 and not args.no_cpu_baseline:
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
         ck_host = {k: v.cpu() for k, v in ck.items()}
-    if not (rank == 0 and not args.no_replay):
+    if not (rank == 0 and world == 1 and not args.no_replay):
         del ck
         torch.cuda.empty_cache()
 
@@ -408,13 +470,17 @@ def main():
             torch.cuda.synchronize()
 
     # ---- device-resident arm: W warm-up ticks, then exactly K timed ticks ----
-    model.run_ticks(seqs, draws_for(W, n, seed=10 + rank))
-    draws = draws_for(K, n, seed=20 + rank)
-    first_frame = seqs[0].frames
-    barrier()
+    # (the clock sampler starts before the warm-up: the timed region can be shorter than nvidia-smi's start-up)
     with ClockSampler(local) as clocks:
+        model.run_ticks(seqs, draws_for(W, n, seed=10 + rank))
+        draws = draws_for(K, n, seed=20 + rank)
+        first_frame = seqs[0].frames
+        barrier()
+        clocks.mark_start()
         _, tick_ms = model.run_ticks(seqs, draws)
         barrier()
+        clocks.mark_end()
+        time.sleep(0.12)  # two more sampling periods, so that a sample taken inside the window has been printed
     launches_per_tick = model.stats().last_call_launches // K
     elapsed = float(tick_ms.sum()) * 1e-3
     lens = [args.prompt + first_frame - 1 + t for t in range(K)]  # the position every session's row sits at
@@ -446,6 +512,9 @@ def main():
     if world > 1:
         dist.all_reduce(t_e2e, op=dist.ReduceOp.MAX)
     e2e_value = args.sessions * world * K / float(t_e2e.item())
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()  # the other ranks are done; rank 0 alone runs the comparison legs below
     bucket = model.stats().bucket
     pages_per_seq = (lens[-1] + K) // 16 + 1
     h2d = 4 * (bucket * (1 + 1 + 16 + 16 + 1 + 1) + bucket + 1) + 4 * n * pages_per_seq  # staged front block (approx.)
@@ -456,14 +525,21 @@ def main():
         mean_len = float(np.mean(lens)) + 1
         tick_bytes = cfg.tick_weight_bytes() + cfg.talker.kv_bytes_per_token() * n * (mean_len + 1)
         tick_s = elapsed / K
+        # two more readings of the same time: against the nominal 8 TB/s, and counting the predictor's weights once per tick
+        # (they are one L2's worth: 14 of the 15 passes can be served on chip)
+        p_cfg, t_cfg = cfg.predictor, cfg.talker
+        per_pass = p_cfg.num_hidden_layers * p_cfg.layer_weight_bytes() + 2 * p_cfg.hidden_size * t_cfg.hidden_size
+        once_bytes = tick_bytes - (cfg.num_code_groups - 2) * per_pass
         # the dominant kernel IS the tick: one persistent cooperative launch per step (or, with --per-op, the graph)
         roof = {"bound": "hbm", "kernel": "tick_kernel + pred_kernel (whole decode tick)" if launches_per_tick <= 2 else "per-op graph",
                 "achieved": tick_bytes / tick_s / 1e9, "peak": peak, "unit": "GB/s",
                 "frac": tick_bytes / tick_s / 1e9 / peak, "peak_source": f"of {peak_kind}",
+                "frac_nominal": tick_bytes / tick_s / 1e9 / 8000.0, "peak_nominal": 8000.0,
+                "frac_predictor_weights_once": once_bytes / tick_s / 1e9 / peak,
                 "bytes_per_launch": int(tick_bytes), "us_per_launch": tick_s * 1e6,
-                # ncu cannot run inside the timed region: the DRAM bytes of one captured tick of this kernel
-                # (profiles/tick_kernel_qwen3tts_64sessions.md: 6,399 MB read+written for 6,296 MB algorithmic at
-                # positions 131-132) scaled to this run's algorithmic bytes; traffic grows with the KV length as they do
+                # ncu cannot run inside the timed region: the DRAM bytes of one captured tick (6,399 MB read + written
+                # for 6,296 MB algorithmic at positions 131-132) scaled to this run's algorithmic bytes; the traffic
+                # grows with the KV length as they do
                 "traffic": int(tick_bytes * 6399.1 / 6296.2) if launches_per_tick <= 2 else None,
                 "traffic_note": "ncu dram__bytes_read+write of one captured tick (6.399 GB for 6.296 GB algorithmic), "
                                 "scaled by this run's algorithmic bytes"}
@@ -471,8 +547,7 @@ def main():
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
             "ms_per_step": 1e3 * elapsed_max / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": "configs[1]: Qwen3-TTS-12Hz-1.7B talker (28L h2048 16q/8kv d128 i6144, head 3072) + "
-                                   "code predictor (5L h1024, 15 codebooks x 2048), random bf16 weights N(0,0.02)",
+            "config": {"workload": CONFIG_WORKLOAD,
                        "sessions_per_gpu": args.sessions, "prompt_tokens": args.prompt, "kv_page": 16,
                        "sampling": "top-k 50, T 0.9, repetition penalty 1.05, host uniforms (reference sampler)",
                        "step": "one decode tick = 64 frames per GPU", "positions": [lens[0], lens[-1]],
@@ -494,21 +569,19 @@ def main():
             "tick_bytes": {"weights": int(cfg.tick_weight_bytes()), "kv": int(tick_bytes - cfg.tick_weight_bytes()),
                            "mean_kv_len": mean_len},
         }
-        if not args.no_replay:
+        if not args.no_replay and world == 1:
             model.close()
             torch.cuda.empty_cache()
             rep = replay_baseline(cfg, ck, args.sessions, args.prompt, W, K)  # same positions as the arm above
             del ck
             if rep is not None:
                 line["reference_replay"] = rep
-        if ck_host is not None:
+                line["vs_replay"] = value / rep["value"]
+        if ck_host is not None and world == 1:
             base, _ = cpu_baseline(cfg, ck_host)
             line["cpu_baseline"] = base
         print(json.dumps(line), flush=True)
     model.close()
-    if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
 
 
 if __name__ == "__main__":

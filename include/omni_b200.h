@@ -91,9 +91,10 @@ typedef struct omni_talker_config {
   int32_t use_graphs;     /* 1: one CUDA graph per batch bucket per program; 0: eager launches */
   int32_t gemm_path;      /* 0: auto (vector GEMV for few rows, tcgen05 tiles otherwise); 1: GEMV only */
   int32_t tick_kernel;    /* 1: run each graph program as ONE persistent cooperative kernel (phase list with grid
-                             barriers, weights streamed across phase boundaries) when the shapes allow it, followed by
-                             ONE launch of thread-block clusters for the code predictor's sub-steps when its shape
-                             allows that (else they stay in the persistent kernel); 2: the persistent kernel alone;
+                             barriers, weights streamed across phase boundaries) when the shapes allow it;
+                             3: the same for the talker step, then ONE launch of thread-block clusters for the code
+                             predictor's sub-steps (sessions dealt to clusters of 16 CTAs that never talk to one
+                             another; measured slower than 1 on B200 at every session count, kept as an option);
                              0: one kernel per op */
 } omni_talker_config;
 

@@ -192,6 +192,8 @@ int32_t omni_op_sample(omni_ops* c, const void* logits, int32_t vocab, float tem
   p.group = group;
   p.philox = philox;
   p.seen_words = (vocab + 31) / 32;
+  if (top_p < 1.f && (top_k <= 0 || top_k > 1024))
+    return c->fail(OMNI_ERR_UNSUPPORTED, "top_p < 1 needs 0 < top_k <= 1024 (the nucleus filter ranks the survivors of the top-k cut)");
   OPS_CUDA(c, launch_sample((const bf16*)logits, p, frames, uniforms, force, SlotState{state, lines, stride}, codes,
                             rows, c->stream));
   return OMNI_OK;

@@ -4,19 +4,26 @@
 //
 // Why clusters. A predictor pass is ~40 dependent steps over a few megabytes of weights each; split over all 148 SMs
 // every step pays a grid-wide hand-over (store -> barrier -> load through L2, 2-3 us), which is most of its time.
-// Sessions are independent, so they are dealt to clusters of C CTAs (C = the predictor's query heads, 16 at the
+// Sessions are independent, so here they are dealt to clusters of C CTAs (C = the predictor's query heads, 16 at the
 // headline shape) that never talk to one another: a cluster runs all sub-steps for its (at most 16) sessions, every
 // matrix split C ways by output rows with the whole K per CTA, so a step's hand-over is a cluster barrier (an
 // mbarrier in each CTA's shared memory, arrived on by one thread of every peer) around a few KB in L2. Every cluster
-// streams every weight byte (from L2 after the first cluster pulled it from HBM): the bound is the 64 B/clk at which
-// an SM ingests from L2, the 161 MB of a pass over C SMs.
+// streams every weight byte (from L2 after the first cluster pulled it from HBM).
 //
-// Per CTA: one weight producer thread (TMA into a ring of 40 KB stages, free-running over the whole launch), one
-// activation producer thread (TMA of activation k-blocks that another CTA wrote, gated by the cluster barrier),
-// eight MMA warps. With at most 16 rows per cluster the tensor-core tile that fits is mma.sync m16n8k16 (weights on
-// M from the swizzled stage via ldmatrix, sessions on N = 2 x 8), accumulators in registers; tcgen05's M = 128 tile
-// would bring nothing here, the kernel is ingest-bound. Work is a flat list of entries (one weight box of 64 or 128
-// rows each) compiled once per (bucket) by the host, as the tick kernel's phase list is.
+// What was measured on B200 (64 sessions, 7 resident clusters of 16): the launch takes 6.1 ms against 3.9 ms for the
+// same sub-steps inside the persistent tick kernel, so the tick kernel stays the default and this one is an option.
+// A CTA consumes its weight stream at 48 GB/s (a 128 x 1024 box in 5.3 us), not the 114 GB/s its TMA unit can
+// deliver: 64 tcgen05.mma (M = 128, N = 16) take 5.3 us whether they accumulate into one TMEM accumulator or
+// alternate between two, and with the MMAs left out the same loop streams the box in 2.0 us. (mma.sync m16n8k16
+// from the same stages: 7.6 us.) Eight-fold re-reading of the weights needs the full ingest rate; a hand-over
+// through a cluster barrier (1.5-2 us with the L2 round trip of the exchanged rows) is not cheap enough to pay for it.
+//
+// Per CTA: one weight producer thread (TMA into a ring of 40 KB stages, free-running over the whole launch, with an
+// L2 prefetch of its boxes about 1 MB ahead), one activation producer thread (TMA of activation k-blocks that another
+// CTA wrote, gated by the cluster barrier), eight consumer warps: thread 0 issues tcgen05.mma with the weight rows
+// on M (128 or 64) and the cluster's 16 session rows on N, accumulator in TMEM; all eight read it back and run the
+// epilogues, norms, attention and draws. Work is a flat list of entries (one weight box of 64 or 128 rows each)
+// compiled once per bucket by the host, as the tick kernel's phase list is.
 #pragma once
 #include <cuda.h>
 #include <cuda_runtime.h>
@@ -59,6 +66,7 @@ struct alignas(16) PredEntry {
   int32_t next_dim;    // kPeHead: elements of the next input row (0: no next sub-step)
   float eps, theta;
   int32_t pad_[2];
+  const void* w;        // the weight matrix (row-major, K contiguous: a box of whole rows is one contiguous range)
   const void *p0, *p1;  // BiasNorm: bias, gain; Q/Kv: norm gain, -; AddNorm: -, gain; Head: next-input table, -
   void *q0, *q1;        // Kv: KV layer, attention out; Swiglu: act; Head: logits out (row stride = vocab), next-input rows
 };
@@ -90,7 +98,9 @@ int pred_add_map(PredProgram* prog, const bf16* base, int64_t rows, int K, int64
 int pred_configure(int C);
 int pred_upload(PredProgram* prog);
 void pred_free(PredProgram* prog);
-// One launch: prog.clusters clusters of C CTAs. `vbuf`: rows x hidden floats of exchange space.
-cudaError_t pred_launch(const PredProgram& prog, const TickIo& io, float* vbuf, uint32_t* err, cudaStream_t stream);
+// One launch: prog.clusters clusters of C CTAs. `vbuf`: rows x hidden floats of exchange space. `trace` (optional,
+// three u64 per entry): the global timer when rank 0 of cluster 0 started the entry, left its main loop, finished it.
+cudaError_t pred_launch(const PredProgram& prog, const TickIo& io, float* vbuf, uint32_t* err, cudaStream_t stream,
+                        unsigned long long* trace = nullptr);
 
 }  // namespace omni

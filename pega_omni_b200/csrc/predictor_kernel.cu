@@ -2,7 +2,10 @@
 // most 16 sessions, no communication between clusters.
 //   warp 0 / lane 0   weight producer: TMA loads of weight boxes into the stage ring, never waits for activations
 //   warp 1 / lane 0   activation producer: TMA loads of activation k-blocks written by the cluster's other CTAs
-//   warps 2..9        MMA (mma.sync m16n8k16 from the swizzled stages) + every epilogue, norm, attention and draw
+//   warps 2..9        consumers: thread 0 issues tcgen05.mma (weight rows on M = 128 or 64, the cluster's 16 session rows
+//                     on N, accumulator in TMEM; the legacy mma.sync path was measured at a quarter of the rate the
+//                     weight stream needs); all eight warps read the accumulator back and run every epilogue, norm,
+//                     attention and draw
 // Every wait is bounded; a wait that runs out raises the device error word and the CTA unwinds.
 #include "predictor.h"
 
@@ -21,20 +24,26 @@ constexpr int kStageW = 32 * 1024;           // weight part of a stage: 128 rows
 constexpr int kStageX = 8 * 1024;            // activation part: 16 rows x up to 4 k-blocks
 constexpr int kStageBytes = kStageW + kStageX;
 constexpr int kStages = 4;
+constexpr uint32_t kTmemCols = 32;           // one accumulator of 16 f32 columns (the smallest allocation is 32)
 constexpr int kOutPitch = 132;               // floats per row of the epilogue tile (128 columns + 4 of padding)
+
+constexpr int64_t kPrefetchAhead = 1 << 20;   // bytes of a CTA's future weight boxes asked into L2
+constexpr int kPrefetchChunk = 64 * 1024;
 
 using ConsumerSync = sampler::NamedSync<1, kConsumers>;
 using DrawTeam = sampler::Team<kConsumers, ConsumerSync>;
 
 struct alignas(16) Control {
   uint64_t full_w[kStages], full_x[kStages], empty[kStages];
+  uint64_t acc_full;       // the entry's accumulator is complete in TMEM
   uint64_t cbar[2];        // the cluster barrier: every CTA's elected thread arrives on every peer's
+  uint32_t tmem_base;
   volatile int bars_done;  // cluster barriers this CTA has passed
   volatile int abort;
 };
 
 struct EpilogueTiles {
-  float out[2][kPredRows][kOutPitch];  // accumulators as [K half][session row][weight row of the box]
+  float out[1][kPredRows][kOutPitch];  // the accumulator as [session row][weight row of the box]
   float q[kPredRows][128];             // the CTA's query head after norm + RoPE
 };
 union Scratch {
@@ -51,6 +60,7 @@ struct KernelArgs {
   TickIo io;
   float* vbuf;  // [rows][hidden] f32: the residual sums the norm runs over, exchanged through L2
   uint32_t* err;
+  unsigned long long* trace;  // optional: per entry, the global timer at its start, after its main loop and at its end (cluster 0, rank 0)
 };
 
 __device__ __forceinline__ uint32_t cluster_rank() {
@@ -122,14 +132,17 @@ __device__ __forceinline__ int weight_row(const PredEntry& e, int rank) {
   return e.wrow + rank * e.cta_stride;
 }
 
-__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t (&r)[4]) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
-}
-__device__ __forceinline__ void mma_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
-               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+// This thread's TMEM lane, 8 consecutive f32 columns starting at the column encoded in `taddr`.
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, float* v) {
+  uint32_t r[8];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];\n\t"
+      "tcgen05.wait::ld.sync.aligned;"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+      : "r"(taddr)
+      : "memory");
+#pragma unroll
+  for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[i]);
 }
 
 // Byte offset of element k (a multiple of 8) of row n inside a [rows][64] bf16 block stored with the 128-byte swizzle.
@@ -141,11 +154,16 @@ __device__ __forceinline__ uint32_t swz(int n, int k) { return (uint32_t)(n * 12
 __device__ __forceinline__ bool cluster_barrier(Control& ctl, int& n_bars, int C, int ctid, uint32_t* err) {
   ConsumerSync::sync();
   const uint32_t bar = sm100::smem_addr(&ctl.cbar[n_bars & 1]);
-  if (ctid < C) remote_arrive(bar, (uint32_t)ctid);  // thread p arrives on peer p's barrier (C <= 16 threads)
-  const bool ok = wait_bar<true>(bar, (uint32_t)(n_bars >> 1) & 1u, ctl, err, kAtClusterBarrier);
+  if (ctid < 32) {
+    if (ctid < C) remote_arrive(bar, (uint32_t)ctid);  // lane p arrives on peer p's barrier (C <= 16)
+    if (ctid == 0) {  // one thread watches the barrier; the team barrier below passes its acquire on to the others
+      wait_bar<true>(bar, (uint32_t)(n_bars >> 1) & 1u, ctl, err, kAtClusterBarrier);
+      ctl.bars_done = n_bars + 1;
+    }
+  }
   ++n_bars;
-  if (ctid == 0) ctl.bars_done = n_bars;  // (this barrier's mbarrier is used again two barriers on, after the team barrier above)
-  return ok && !ctl.abort;
+  ConsumerSync::sync();
+  return !ctl.abort;
 }
 
 __device__ __forceinline__ void ld_bf16x4(const bf16* p, float* v) {
@@ -156,27 +174,51 @@ __device__ __forceinline__ void ld_bf16x4(const bf16* p, float* v) {
 }
 
 // x = bf16(v * rsqrt(mean(v^2) + eps) * gain) for the cluster's rows, v from the exchange buffer, into the resident
-// activation tile (k-blocks of [16 rows][64] bf16, swizzled like a TMA box). A warp per row, rows w and w + 8.
-__device__ __forceinline__ void norm_to_tile(const float* vbuf, const bf16* gain, int hidden, float eps, int s0, int live,
-                                             unsigned char* xs, int cwarp, int lane) {
-  for (int n = cwarp; n < live; n += 8) {
-    const float* row = vbuf + (int64_t)(s0 + n) * hidden;
-    float ss = 0.f;
-    for (int k = lane * 4; k < hidden; k += 128) {
-      const float4 v = __ldcg(reinterpret_cast<const float4*>(row + k));
-      ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+// activation tile (k-blocks of [16 rows][64] bf16, swizzled like a TMA box). A warp per row, rows w and w + 8; both
+// rows' loads are issued before either is summed (one L2 round trip), and a row is read once. NV = hidden / 128.
+template <int NV>
+__device__ __forceinline__ void norm_rows(const float* vbuf, const bf16* gain, float eps, int s0, int live, unsigned char* xs,
+                                          int cwarp, int lane) {
+  constexpr int hidden = NV * 128;
+  float4 v[2][NV];
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int n = cwarp + 8 * r;
+    if (n < live) {
+      const float* row = vbuf + (int64_t)(s0 + n) * hidden;
+#pragma unroll
+      for (int t = 0; t < NV; ++t) v[r][t] = __ldcg(reinterpret_cast<const float4*>(row + t * 128 + lane * 4));
     }
-    const float r = rsqrtf(warp_add(ss) / hidden + eps);
-    for (int k = lane * 4; k < hidden; k += 128) {
-      const float4 v = __ldcg(reinterpret_cast<const float4*>(row + k));
-      float g[4], o[4];
-      ld_bf16x4(gain + k, g);
-      o[0] = v.x * r * g[0], o[1] = v.y * r * g[1], o[2] = v.z * r * g[2], o[3] = v.w * r * g[3];
+  }
+  float g[NV][4];
+#pragma unroll
+  for (int t = 0; t < NV; ++t) ld_bf16x4(gain + t * 128 + lane * 4, g[t]);
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int n = cwarp + 8 * r;
+    if (n >= live) continue;  // warp-uniform
+    float ss = 0.f;
+#pragma unroll
+    for (int t = 0; t < NV; ++t) ss += v[r][t].x * v[r][t].x + v[r][t].y * v[r][t].y + v[r][t].z * v[r][t].z + v[r][t].w * v[r][t].w;
+    const float rn = rsqrtf(warp_add(ss) / hidden + eps);
+#pragma unroll
+    for (int t = 0; t < NV; ++t) {
+      const int k = t * 128 + lane * 4;
       uint2 u;
-      *reinterpret_cast<__nv_bfloat162*>(&u.x) = __floats2bfloat162_rn(o[0], o[1]);
-      *reinterpret_cast<__nv_bfloat162*>(&u.y) = __floats2bfloat162_rn(o[2], o[3]);
+      *reinterpret_cast<__nv_bfloat162*>(&u.x) = __floats2bfloat162_rn(v[r][t].x * rn * g[t][0], v[r][t].y * rn * g[t][1]);
+      *reinterpret_cast<__nv_bfloat162*>(&u.y) = __floats2bfloat162_rn(v[r][t].z * rn * g[t][2], v[r][t].w * rn * g[t][3]);
       *reinterpret_cast<uint2*>(xs + (k >> 6) * (kPredRows * 128) + swz(n, k & 63) + (k & 7) * 2) = u;
     }
+  }
+}
+
+__device__ __forceinline__ void norm_to_tile(const float* vbuf, const bf16* gain, int hidden, float eps, int s0, int live,
+                                             unsigned char* xs, int cwarp, int lane) {
+  switch (hidden) {  // 64 * C
+    case 128: norm_rows<1>(vbuf, gain, eps, s0, live, xs, cwarp, lane); break;
+    case 256: norm_rows<2>(vbuf, gain, eps, s0, live, xs, cwarp, lane); break;
+    case 512: norm_rows<4>(vbuf, gain, eps, s0, live, xs, cwarp, lane); break;
+    default: norm_rows<8>(vbuf, gain, eps, s0, live, xs, cwarp, lane); break;
   }
 }
 
@@ -201,8 +243,9 @@ __global__ void __launch_bounds__(kThreads, 1) pred_kernel(const __grid_constant
     for (int s = 0; s < kStages; ++s) {
       mbar_init(smem_addr(&ctl.full_w[s]), 1);
       mbar_init(smem_addr(&ctl.full_x[s]), 1);
-      mbar_init(smem_addr(&ctl.empty[s]), 8);
+      mbar_init(smem_addr(&ctl.empty[s]), 1);
     }
+    mbar_init(smem_addr(&ctl.acc_full), 1);
     mbar_init(smem_addr(&ctl.cbar[0]), (uint32_t)C);
     mbar_init(smem_addr(&ctl.cbar[1]), (uint32_t)C);
     ctl.bars_done = 0;
@@ -211,14 +254,34 @@ __global__ void __launch_bounds__(kThreads, 1) pred_kernel(const __grid_constant
   }
   // rows past the cluster's sessions stay zero in the resident tile for the whole launch
   for (int i = threadIdx.x * 16; i < xs_bytes; i += kThreads * 16) *reinterpret_cast<uint4*>(xs + i) = make_uint4(0, 0, 0, 0);
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  if (warp == kFirstConsumerWarp) tmem_alloc(smem_addr(&ctl.tmem_base), kTmemCols);
+  tc_fence_before_sync();
   __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_acc = ctl.tmem_base;
   hw_cluster_sync();  // every peer's barriers exist before anyone arrives on them
 
   if (live > 0 && warp == 0) {
     if (lane == 0) {  // ---- weight producer ----
       StageWalk w;
+      // Every cluster reads the same weights at about the same time, so the distinct bytes under way from HBM are one
+      // cluster's rings (2 MB). Each CTA therefore asks for its own boxes (contiguous: whole rows) into L2 about
+      // 1 MB before it loads them (measured: 7 % on the main loops).
+      int pf = 0;
+      int64_t ahead = 0;
       for (int i = 0; i < a.n_entries && !ctl.abort; ++i) {
         const PredEntry& e = a.entries[i];
+        while (pf < a.n_entries && (ahead < kPrefetchAhead || pf <= i)) {
+          const PredEntry& f = a.entries[pf];
+          const int64_t box_bytes = (int64_t)f.rows * f.nkb * 128;
+          const char* src = static_cast<const char*>(f.w) + (int64_t)weight_row(f, rank) * f.nkb * 128;
+          for (int64_t off = 0; off < box_bytes; off += kPrefetchChunk)
+            sm100::prefetch_l2(src + off, (uint32_t)min((int64_t)kPrefetchChunk, box_bytes - off));
+          ahead += box_bytes;
+          ++pf;
+        }
+        ahead -= (int64_t)e.rows * e.nkb * 128;
         const CUtensorMap* map = a.maps + e.wmap;
         const int row = weight_row(e, rank);
         const uint32_t bytes = (uint32_t)e.rows * 128u * (uint32_t)e.kbs;
@@ -269,64 +332,59 @@ __global__ void __launch_bounds__(kThreads, 1) pred_kernel(const __grid_constant
   } else if (live > 0 && warp >= kFirstConsumerWarp) {
     // ---- consumers ----
     const int ctid = threadIdx.x - kFirstConsumerWarp * 32, cw = warp - kFirstConsumerWarp;
-    const int gq = lane >> 2, tig = lane & 3;
     StageWalk w;
     uint32_t xpar = 0;  // bit s: parity of stage s's next activation wait (only some uses of a stage carry activations)
     int n_bars = 0;
     const int hidden = a.cfg.hidden;
     for (int i = 0; i < a.n_entries && !ctl.abort; ++i) {
       const PredEntry& e = a.entries[i];
-      // ---- main loop: acc[n tile][4] of this warp's 16 weight rows ----
-      float acc[2][4];
-#pragma unroll
-      for (int t = 0; t < 2; ++t)
-#pragma unroll
-        for (int j = 0; j < 4; ++j) acc[t][j] = 0.f;
-      const bool narrow = e.rows == 64;  // 64-row box: warps 0-3 take the first two k16 steps of a k-block, 4-7 the last two
-      const int tile = narrow ? (cw & 3) : cw, kk0 = narrow ? (cw >> 2) * 2 : 0, kk1 = narrow ? kk0 + 2 : 4;
-      const int a_row = tile * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, a_sel = lane >> 4;
-      const int b_row = (lane & 7) + (lane >> 4) * 8, b_sel = (lane >> 3) & 1;
-      const uint32_t a_off = (uint32_t)a_row * 128u, b_off = (uint32_t)b_row * 128u;
-      bool ok = true;
-      for (int kb = 0; kb < e.nkb; kb += e.kbs) {
-        const uint32_t stage_base = ring + (uint32_t)w.stage * kStageBytes;
-        ok = wait_bar<false>(smem_addr(&ctl.full_w[w.stage]), w.parity(), ctl, a.err, kAtWeightFull);
-        if (ok && e.xmap >= 0) {
-          ok = wait_bar<false>(smem_addr(&ctl.full_x[w.stage]), xpar >> w.stage & 1u, ctl, a.err, kAtRowsFull);
-          xpar ^= 1u << w.stage;
-        }
-        if (!ok) break;
-        for (int j = 0; j < e.kbs; ++j) {
-          const uint32_t wb = stage_base + (uint32_t)j * (uint32_t)e.rows * 128u + a_off;
-          const uint32_t xb = (e.xmap >= 0 ? stage_base + kStageW + (uint32_t)j * (kPredRows * 128)
-                                           : smem_addr(xs) + (uint32_t)(kb + j) * (kPredRows * 128)) + b_off;
-#pragma unroll
-          for (int kk = 0; kk < 4; ++kk) {
-            if (kk < kk0 || kk >= kk1) continue;
-            uint32_t af[4], bf[4];
-            ldmatrix_x4(wb + (uint32_t)(((kk * 2 + a_sel) ^ (a_row & 7)) << 4), af);
-            ldmatrix_x4(xb + (uint32_t)(((kk * 2 + b_sel) ^ (b_row & 7)) << 4), bf);
-            mma_16816(acc[0], af, bf[0], bf[1]);
-            mma_16816(acc[1], af, bf[2], bf[3]);
+      const bool tracing = a.trace && ctid == 0 && rank == 0 && s0 == 0;
+      if (tracing) a.trace[3 * i] = global_timer_ns();
+      // ---- main loop: thread 0 issues the entry's MMAs, D[weight row, session] accumulates in TMEM ----
+      const bool narrow = e.rows == 64;
+      if (ctid == 0) {
+        const uint32_t idesc = idesc_bf16_f32(e.rows, kPredRows);
+        bool ok = true;
+        for (int kb = 0; kb < e.nkb; kb += e.kbs) {
+          const uint32_t stage_base = ring + (uint32_t)w.stage * kStageBytes;
+          ok = wait_bar<false>(smem_addr(&ctl.full_w[w.stage]), w.parity(), ctl, a.err, kAtWeightFull);
+          if (ok && e.xmap >= 0) {
+            ok = wait_bar<false>(smem_addr(&ctl.full_x[w.stage]), xpar >> w.stage & 1u, ctl, a.err, kAtRowsFull);
+            xpar ^= 1u << w.stage;
           }
-        }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(smem_addr(&ctl.empty[w.stage]));
-        w.advance();
-      }
-      if (!ok) break;
-      // ---- accumulators -> out[half][session][weight row] ----
-      {
-        float(*o)[kOutPitch] = scratch.t.out[narrow ? (cw >> 2) : 0];
+          if (!ok) break;
+          tc_fence_after_sync();
+          for (int j = 0; j < e.kbs; ++j) {
+            const uint64_t adesc = kmajor_sw128_desc(stage_base + (uint32_t)j * (uint32_t)e.rows * 128u);
+            const uint64_t bdesc = kmajor_sw128_desc(e.xmap >= 0 ? stage_base + kStageW + (uint32_t)j * (kPredRows * 128)
+                                                                 : smem_addr(xs) + (uint32_t)(kb + j) * (kPredRows * 128));
 #pragma unroll
-        for (int t = 0; t < 2; ++t) {
-          const int n = t * 8 + 2 * tig, c = tile * 16 + gq;
-          o[n][c] = acc[t][0], o[n + 1][c] = acc[t][1], o[n][c + 8] = acc[t][2], o[n + 1][c + 8] = acc[t][3];
+            for (int k = 0; k < 4; ++k)
+              mma_bf16(tmem_acc, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2), idesc, (kb > 0 || j > 0 || k > 0) ? 1u : 0u);
+          }
+          mma_commit(smem_addr(&ctl.empty[w.stage]));  // the stage is free once these MMAs have read it
+          w.advance();
         }
+        if (ok) mma_commit(smem_addr(&ctl.acc_full));
+      }
+      if (!wait_bar<false>(smem_addr(&ctl.acc_full), (uint32_t)i & 1u, ctl, a.err, kAtWeightFull)) break;
+      tc_fence_after_sync();
+      if (tracing) a.trace[3 * i + 1] = global_timer_ns();
+      // ---- accumulator -> out[session][weight row]: a warp reads the TMEM lanes of its quadrant (warp index % 4), the two
+      // warps of a quadrant eight sessions each. M = 64 keeps rows 16q .. 16q + 15 in the first 16 lanes of quadrant q.
+      {
+        const int quad = warp & 3, half = cw >> 2;
+        float v[8];
+        tmem_ld8(tmem_acc + ((uint32_t)(quad * 32) << 16) + (uint32_t)(half * 8), v);
+        const int c = narrow ? quad * 16 + lane : quad * 32 + lane;
+        if (!narrow || lane < 16) {
+#pragma unroll
+          for (int x = 0; x < 8; ++x) scratch.t.out[0][half * 8 + x][c] = v[x];
+        }
+        tc_fence_before_sync();
       }
       ConsumerSync::sync();
       const float(*o0)[kOutPitch] = scratch.t.out[0];
-      const float(*o1)[kOutPitch] = scratch.t.out[1];
 
       switch (e.epi) {
         case kPeBiasNorm:
@@ -336,7 +394,7 @@ __global__ void __launch_bounds__(kThreads, 1) pred_kernel(const __grid_constant
           const int col0 = rank * 64;
           for (int idx = ctid; idx < kPredRows * 64; idx += kConsumers) {
             const int n = idx >> 6, c = idx & 63;
-            const float y = bf16_round(o0[n][c] + o1[n][c]);
+            const float y = bf16_round(o0[n][c]);
             float v;
             if (e.epi == kPeBiasNorm) v = bias ? bf16_round(y + __bfloat162float(bias[col0 + c])) : y;
             else v = y + res[n][c];  // the norm runs over the unrounded sum (qwen3.cu:34)
@@ -345,6 +403,7 @@ __global__ void __launch_bounds__(kThreads, 1) pred_kernel(const __grid_constant
           }
           if (!cluster_barrier(ctl, n_bars, C, ctid, a.err)) break;
           norm_to_tile(a.vbuf, (const bf16*)e.p1, hidden, e.eps, s0, live, xs, cw, lane);
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // these stores are read by tcgen05.mma
           ConsumerSync::sync();
           break;
         }
@@ -397,28 +456,34 @@ __global__ void __launch_bounds__(kThreads, 1) pred_kernel(const __grid_constant
             for (int n = cw; n < live; n += 8) {
               const bf16* kpage = kv + kv_offset<128>(s0 + n, hk, kh, 0, 0);
               const bf16* vpage = kpage + 16 * 128;
-              float s = -INFINITY;
-              if (lane < len) {
-                float dot = 0.f;
+              // every load of the page is issued before any is used: lane j holds key row j, and every lane its four
+              // output dims of all 16 value rows (rows past the frame's length are never read)
+              uint4 kraw[16];
+              uint2 vraw[16];
 #pragma unroll
-                for (int c = 0; c < 16; ++c) {
-                  const uint4 raw = __ldcg(reinterpret_cast<const uint4*>(kpage + lane * 128 + c * 8));
-                  float kf[8];
-                  unpack8(*reinterpret_cast<const Pack8*>(&raw), kf);
+              for (int c = 0; c < 16; ++c)
+                kraw[c] = lane < len ? __ldcg(reinterpret_cast<const uint4*>(kpage + lane * 128 + c * 8)) : make_uint4(0, 0, 0, 0);
 #pragma unroll
-                  for (int x = 0; x < 8; ++x) dot = fmaf(scratch.t.q[n][c * 8 + x], kf[x], dot);
-                }
-                s = dot * scale;
+              for (int j = 0; j < 16; ++j)
+                vraw[j] = j < len ? __ldcg(reinterpret_cast<const uint2*>(vpage + j * 128 + lane * 4)) : make_uint2(0, 0);
+              float dot = 0.f;
+#pragma unroll
+              for (int c = 0; c < 16; ++c) {
+                float kf[8];
+                unpack8(*reinterpret_cast<const Pack8*>(&kraw[c]), kf);
+#pragma unroll
+                for (int x = 0; x < 8; ++x) dot = fmaf(scratch.t.q[n][c * 8 + x], kf[x], dot);
               }
+              const float s = lane < len ? dot * scale : -INFINITY;
               const float mx = warp_fmax(s);
               const float p = lane < len ? __expf(s - mx) : 0.f;
               const float l = warp_add(p);
               float acc4[4] = {0.f, 0.f, 0.f, 0.f};
-              for (int j = 0; j < len; ++j) {
-                const float pj = __shfl_sync(0xffffffffu, p, j);
-                const uint2 raw = __ldcg(reinterpret_cast<const uint2*>(vpage + j * 128 + lane * 4));
-                const float2 v0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
-                const float2 v1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                const float pj = __shfl_sync(0xffffffffu, p, j);  // 0 past the frame's length
+                const float2 v0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&vraw[j].x));
+                const float2 v1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&vraw[j].y));
                 acc4[0] = fmaf(pj, v0.x, acc4[0]), acc4[1] = fmaf(pj, v0.y, acc4[1]);
                 acc4[2] = fmaf(pj, v1.x, acc4[2]), acc4[3] = fmaf(pj, v1.y, acc4[3]);
               }
@@ -454,7 +519,7 @@ __global__ void __launch_bounds__(kThreads, 1) pred_kernel(const __grid_constant
           for (int idx = ctid; idx < kPredRows * e.rows; idx += kConsumers) {
             const int n = idx / e.rows, c = idx % e.rows;
             if (n < live && col + c < vocab) {
-              const float y = narrow ? o0[n][c] + o1[n][c] : o0[n][c];
+              const float y = o0[n][c];
               logits[(int64_t)(s0 + n) * vocab + col + c] = __float2bfloat16(y);
             }
           }
@@ -506,10 +571,13 @@ __global__ void __launch_bounds__(kThreads, 1) pred_kernel(const __grid_constant
         }
         default: break;
       }
+      if (tracing) a.trace[3 * i + 2] = global_timer_ns();
     }
   }
   __syncwarp();
+  tc_fence_before_sync();
   __syncthreads();
+  if (warp == kFirstConsumerWarp) tmem_dealloc(tmem_acc, kTmemCols);
   hw_cluster_sync();  // no CTA leaves while a peer may still arrive on its barriers
 }
 
@@ -584,7 +652,8 @@ void pred_free(PredProgram* prog) {
   prog->d_maps = nullptr;
 }
 
-cudaError_t pred_launch(const PredProgram& prog, const TickIo& io, float* vbuf, uint32_t* err, cudaStream_t stream) {
+cudaError_t pred_launch(const PredProgram& prog, const TickIo& io, float* vbuf, uint32_t* err, cudaStream_t stream,
+                        unsigned long long* trace) {
   KernelArgs a;
   a.entries = prog.d_entries;
   a.n_entries = (int)prog.entries.size();
@@ -595,6 +664,7 @@ cudaError_t pred_launch(const PredProgram& prog, const TickIo& io, float* vbuf, 
   a.io = io;
   a.vbuf = vbuf;
   a.err = err;
+  a.trace = trace;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(prog.clusters * prog.cfg.C);
   cfg.blockDim = dim3(kThreads);

@@ -57,6 +57,7 @@ struct Shared {
   float wtot[32];
   float vscan[kVirtualThreads];
   uint32_t sel_prefix, sel_left;
+  uint32_t warp_count[8];
   int token, last;
   unsigned long long best;
   int n_cand;
@@ -105,38 +106,54 @@ struct Team {
     return m;
   }
 
-  // The k-th largest key of the row (ties share it): four 8-bit digits from the top, each pass
-  // histogramming the keys that match the digits fixed so far.
+  // The k-th largest key of the row (ties share it), most significant digit first, eight bits at a time. Logits are
+  // a few units wide, so the keys' leading digits take a handful of values: counted one atomic per key, a pass would
+  // serialise thousands of additions on two or three shared-memory words. In the first pass each warp therefore
+  // groups its lanes by digit (__match_any_sync) and the lowest lane of a group adds the group's size, so a counter
+  // sees at most one addition per warp and step. The digit is then picked by a suffix count
+  // over the 256 counters: warp w owns counters 32w .. 32w + 31 (one per lane, a shuffle scan inside the warp), the
+  // eight warp totals are combined by every thread that needs them.
   static __device__ uint32_t kth_largest_key(const uint32_t* key, int vocab, uint32_t k, int tid, Shared& sh) {
+    static_assert(THREADS >= 256, "one counter per thread of the first eight warps");
     uint32_t prefix = 0, left = k;
+    const int lane = tid & 31, warp = tid >> 5;
     for (int shift = 24; shift >= 0; shift -= 8) {
-      for (int i = tid; i < 256; i += THREADS) sh.hist[i] = 0;
+      if (tid < 256) sh.hist[tid] = 0;
       Sync::sync();
       const uint32_t fixed = shift == 24 ? 0u : 0xffffffffu << (shift + 8);
+      if (shift == 24) {
 #pragma unroll
-      for (int j = 0; j < PER; ++j)
-        if (tid * PER + j < vocab && ((key[j] ^ prefix) & fixed) == 0)
-          atomicAdd(&sh.hist[(key[j] >> shift) & 255], 1u);
+        for (int j = 0; j < PER; ++j) {
+          const bool in = tid * PER + j < vocab;
+          const uint32_t digit = in ? key[j] >> 24 : 256u;  // lanes past the vocabulary form their own group
+          const uint32_t same = __match_any_sync(0xffffffffu, digit);
+          if (in && lane == __ffs(same) - 1) atomicAdd(&sh.hist[digit], (uint32_t)__popc(same));
+        }
+      } else {  // only the keys that carry the digits fixed so far count: few, and spread over the counters
+#pragma unroll
+        for (int j = 0; j < PER; ++j)
+          if (tid * PER + j < vocab && ((key[j] ^ prefix) & fixed) == 0) atomicAdd(&sh.hist[(key[j] >> shift) & 255u], 1u);
+      }
       Sync::sync();
-      if (tid < 32) {
-        // lane t holds digits 8t..8t+7; keys in strictly higher lanes via a suffix scan
-        uint32_t c[8], mine = 0;
-#pragma unroll
-        for (int b = 0; b < 8; ++b) mine += c[b] = sh.hist[tid * 8 + b];
-        uint32_t suffix = mine;
+      // suffix[d] = keys whose digit is >= d; the digit wanted is the largest d with suffix[d] >= left
+      uint32_t mine = 0, incl = 0;  // this counter, and the inclusive suffix sum inside the warp (towards higher lanes)
+      if (tid < 256) {
+        mine = incl = sh.hist[tid];
 #pragma unroll
         for (int o = 1; o < 32; o <<= 1) {
-          const uint32_t other = __shfl_down_sync(0xffffffffu, suffix, o);
-          if (tid + o < 32) suffix += other;
+          const uint32_t other = __shfl_down_sync(0xffffffffu, incl, o);
+          if (lane + o < 32) incl += other;
         }
-        uint32_t above = suffix - mine;
-#pragma unroll
-        for (int b = 7; b >= 0; --b) {
-          if (above < left && above + c[b] >= left) {
-            sh.sel_prefix = prefix | (uint32_t)(tid * 8 + b) << shift;
-            sh.sel_left = left - above;
-          }
-          above += c[b];
+        if (lane == 0) sh.warp_count[warp] = incl;
+      }
+      Sync::sync();
+      if (tid < 256) {
+        uint32_t above_warps = 0;  // keys in the counters of higher warps
+        for (int w = warp + 1; w < 8; ++w) above_warps += sh.warp_count[w];
+        const uint32_t at_least = incl + above_warps, above = at_least - mine;
+        if (above < left && at_least >= left) {  // exactly one counter satisfies this
+          sh.sel_prefix = prefix | (uint32_t)tid << shift;
+          sh.sel_left = left - above;
         }
       }
       Sync::sync();

@@ -144,6 +144,9 @@ __global__ void __launch_bounds__(1024) sample_kernel(const bf16* __restrict__ l
 cudaError_t launch_sample(const bf16* logits, const SampleParams& p, const int32_t* frames, const float* uniforms,
                           const int32_t* force, SlotState st, int32_t* codes, int rows, cudaStream_t s) {
   if (p.vocab > sampler::kVocabMax || p.vocab < 1) return cudaErrorInvalidValue;
+  // the nucleus filter ranks at most kMaxNucleus survivors of the top-k cut: without a cut that small it would
+  // silently drop candidates in arrival order
+  if (p.top_p < 1.f && (p.top_k <= 0 || p.top_k > sampler::kMaxNucleus)) return cudaErrorInvalidValue;
   sampler::Params prm{p.vocab,  p.temperature, p.top_k,    p.top_p, p.penalty, p.suppress_lo, p.suppress_hi,
                       p.exempt, p.min_frames,  p.penalize, p.group, p.philox,  p.seen_words};
   sample_kernel<<<rows, 1024, 0, s>>>(logits, prm, frames, uniforms, force, st, codes);

@@ -193,15 +193,13 @@ struct omni_talker {
   int tick_ctas = 0;
   uint32_t* tick_barrier = nullptr;
   uint32_t tick_barrier_base = 0;  // arrivals left in the counter by earlier launches
-  // split-K partial tiles of the tick kernel: its own buffer (the kernel hands elements over through an "unset" bit
-  // pattern that must be in place between launches, so nothing else may write here); grown when a program needs more
-  float* tick_partials = nullptr;
-  size_t tick_partial_floats = 0;
   // the code predictor's sub-steps as one launch of thread-block clusters (predictor.h): clusters that can be
   // resident at once (0: this device or shape cannot run it), one compiled entry list per bucket, exchange buffer
   int pred_clusters = 0;
   std::map<int, PredProgram> pred_programs;
   float* pred_vbuf = nullptr;
+  unsigned long long* pred_trace = nullptr;
+  const PredProgram* pred_trace_program = nullptr;
   std::map<std::pair<int, int>, TickProgram> tick_programs;
   int launches = 0, tick_phases = 0;
   std::string trace_path;
@@ -742,6 +740,7 @@ struct PredBuilder {
     e.nkb = K / 64;
     e.kbs = stage_kblocks(e.nkb, rows == 64 ? 4 : 2);
     e.wmap = map_of(w, n, K, K, rows, e.kbs);
+    e.w = w;
     e.wrow = wrow;
     e.cta_stride = cta_stride;
     e.xmap = x ? map_of(x, m->max_seqs, x_cols, x_stride, kPredRows, e.kbs) : -1;
@@ -839,16 +838,8 @@ int run_tick_program(omni_talker* m, int program, int b) {
     TickBuilder builder{m, &prog, m->tick_ctas};
     builder.build(program, b, !clusters);
     if (builder.failed) return m->fail(OMNI_ERR_CUDA, "tensor-map encode failed while compiling the tick program");
-    if (!tick_finish(&prog)) return m->fail(OMNI_ERR_UNSUPPORTED, "tick program: a split-K GEMM without its consumer");
-    if (prog.partial_floats > m->tick_partial_floats) {
-      // first program of this size (a first call at a larger bucket): no launch is in flight once the stream is idle
-      CUDA_TRY(m, cudaStreamSynchronize(m->stream));
-      if (m->tick_partials) cudaFree(m->tick_partials);
-      m->tick_partials = nullptr, m->tick_partial_floats = 0;
-      CUDA_TRY(m, cudaMalloc((void**)&m->tick_partials, prog.partial_floats * sizeof(float)));
-      m->tick_partial_floats = prog.partial_floats;
-      CUDA_TRY(m, tick_reset_partials(m->tick_partials, m->tick_partial_floats, m->stream));
-    }
+    if (prog.partial_floats > m->gemm_scratch.partial_floats)
+      return m->fail(OMNI_ERR_UNSUPPORTED, "split-K scratch too small for the tick program");
     if (tick_upload(&prog) != 0) return m->fail(OMNI_ERR_CUDA, "uploading the tick program failed");
     it = m->tick_programs.emplace(key, prog).first;
   }
@@ -876,7 +867,7 @@ int run_tick_program(omni_talker* m, int program, int b) {
     m->trace_program = &it->second;
     CUDA_TRY(m, cudaMemsetAsync(m->trace, 0, (size_t)4 * kTraceMaxPhases * m->tick_ctas * 8, m->stream));
   }
-  LAUNCH(m, tick_launch(it->second, io, m->tick_partials, m->tick_barrier, &m->tick_barrier_base, m->err,
+  LAUNCH(m, tick_launch(it->second, io, m->gemm_scratch.partials, m->tick_barrier, &m->tick_barrier_base, m->err,
                         m->tick_ctas, m->stream,
                         m->trace && m->tick_phases <= kTraceMaxPhases ? m->trace : nullptr));
   if (clusters) {
@@ -889,7 +880,10 @@ int run_tick_program(omni_talker* m, int program, int b) {
       if (pred_upload(&prog) != 0) return m->fail(OMNI_ERR_CUDA, "uploading the predictor program failed");
       pit = m->pred_programs.emplace(b, prog).first;
     }
-    LAUNCH(m, pred_launch(pit->second, io, m->pred_vbuf, m->err, m->stream));
+    if (!m->trace_path.empty() && !m->pred_trace) TRY(dev_alloc(m, &m->pred_trace, (size_t)3 * 4096, true));
+    m->pred_trace_program = m->pred_trace ? &pit->second : nullptr;
+    LAUNCH(m, pred_launch(pit->second, io, m->pred_vbuf, m->err, m->stream,
+                          m->pred_trace && pit->second.entries.size() <= 4096 ? m->pred_trace : nullptr));
   }
   return OMNI_OK;
 }
@@ -1010,6 +1004,21 @@ size_t stage_graph_inputs(omni_talker* m, char* host, const std::vector<FrameRow
 // CTAs saw the previous barrier complete) the median and the latest over CTAs of: first activation tile in shared
 // memory, first accumulator complete, own share done, barrier seen complete.
 void dump_trace(omni_talker* m) {
+  if (m->pred_trace && m->pred_trace_program && !m->trace_path.empty()) {
+    // the cluster kernel's entries: "entry epilogue rows k-blocks position start loop end" (ns after the first entry's start)
+    const PredProgram& prog = *m->pred_trace_program;
+    std::vector<unsigned long long> t(3 * prog.entries.size());
+    if (cudaMemcpy(t.data(), m->pred_trace, t.size() * 8, cudaMemcpyDeviceToHost) == cudaSuccess) {
+      if (FILE* f = fopen((m->trace_path + ".pred").c_str(), "w")) {
+        for (size_t i = 0; i < prog.entries.size(); ++i) {
+          const PredEntry& e = prog.entries[i];
+          fprintf(f, "%zu %d %d %d %d %lld %lld %lld\n", i, e.epi, e.rows, e.nkb, e.pos, (long long)(t[3 * i] - t[0]),
+                  (long long)(t[3 * i + 1] - t[0]), (long long)(t[3 * i + 2] - t[0]));
+        }
+        fclose(f);
+      }
+    }
+  }
   if (!m->trace || !m->trace_program || m->trace_path.empty()) return;
   const TickProgram& prog = *m->trace_program;
   const size_t G = (size_t)m->tick_ctas, P = prog.phases.size();
@@ -1056,7 +1065,6 @@ int finish_call(omni_talker* m, int n, int32_t* codes, float* wav) {
   const uint32_t err = (uint32_t)m->out_host[(size_t)m->max_seqs * OMNI_GROUPS];
   if (err != 0) {
     m->tick_barrier_base = ~0u;  // CTAs of the failed launch may not all have arrived: restart the counter
-    if (m->tick_partials) tick_reset_partials(m->tick_partials, m->tick_partial_floats, m->stream);
     cudaMemsetAsync(m->err, 0, 4, m->stream);
     cudaStreamSynchronize(m->stream);
     return m->fail(OMNI_ERR_DEVICE, "device error word 0x%x (1: barrier wait ran out, 2: index out of range)", err);
@@ -1085,7 +1093,6 @@ void omni_talker_destroy(omni_talker* m) {
   for (auto& t : m->tick_programs) tick_free(&t.second);
   for (auto& t : m->pred_programs) pred_free(&t.second);
   for (void* p : m->allocations) cudaFree(p);
-  if (m->tick_partials) cudaFree(m->tick_partials);
   if (m->in_host) cudaFreeHost(m->in_host);
   if (m->out_host) cudaFreeHost(m->out_host);
   if (m->ev0) cudaEventDestroy(m->ev0);
@@ -1164,7 +1171,7 @@ static int create_impl(omni_talker* m, const omni_tensor* tensors, int32_t n_ten
   }
   TRY(load_stack(m, idx, "talker.model", t, &m->talker));
   TRY(load_stack(m, idx, "talker.code_predictor.model", pc, &m->pred));
-  if (c.tick_kernel == 1 && m->tick_ok && pred_shape_ok(c, m->pred.granule)) m->pred_clusters = pred_configure(pc.q_heads);
+  if (c.tick_kernel == 3 && m->tick_ok && pred_shape_ok(c, m->pred.granule)) m->pred_clusters = pred_configure(pc.q_heads);
 
   // pools (model.rs:111-131,306-309)
   m->max_seqs = bucket_of(c.max_batch);
@@ -1480,8 +1487,6 @@ int32_t omni_talker_run_ticks(omni_talker* m, int32_t n, omni_seq* const* seqs, 
     CUDA_TRY(m, cudaMemcpy(&err, m->err, 4, cudaMemcpyDeviceToHost));
     if (err != 0) {
       m->tick_barrier_base = ~0u;
-      if (m->tick_partials) tick_reset_partials(m->tick_partials, m->tick_partial_floats, m->stream);
-      cudaStreamSynchronize(m->stream);
       cudaMemset(m->err, 0, 4);
       return m->fail(OMNI_ERR_DEVICE, "device error word 0x%x", err);
     }

@@ -30,9 +30,7 @@ enum NextInput : int32_t { kNextNone = 0, kNextHiddenAndCode = 1, kNextCode = 2 
 
 // One phase. Field use by type:
 //  Gemm:       N, K, bn, rows, tiles, splits, wmap, xmap, mode; dst0 = act (SwiGLU), i0 = inter, i1 = k-blocks per
-//              ring stage (one TMA copy each for the activations and the weights); i11 = 1: the next phase sums this
-//              GEMM's partial tiles and waits for them element by element, so no grid barrier follows this phase
-//              (tick_finish sets it)
+//              ring stage (one TMA copy each for the activations and the weights)
 //  EmbedNorm:  rows, dim = N; src0 pad, src1 codec_emb, src2 p_emb, src3 gain; dst0 res, dst1 x; i0 vocab, i1 p_vocab,
 //              i2 groups; f0 eps
 //  ReduceNorm: rows, dim = N, tiles, splits, bn; src0 bias (or null), src3 gain; dst0 res, dst1 x; f0 eps
@@ -82,20 +80,12 @@ int tick_add_map(TickProgram* prog, const bf16* base, int rows, int K, int box_r
 int tick_ring_size();
 // Largest SwiGLU/partials GEMM the kernel can run; false when a shape needs the per-op path.
 bool tick_supports(int hidden, int head_dim, int q_heads, int kv_heads, int rows_max);
-// Marks the GEMM phases that hand their partial tiles to the next phase without a grid barrier. Every GEMM with
-// partial tiles must be followed at once by the phase that sums them (each partial element is read, and put back
-// to its unset state, by exactly one thread of that phase); false when the list breaks that rule.
-bool tick_finish(TickProgram* prog);
 // Copies the phase list and the maps to the device. 0 on success.
 int tick_upload(TickProgram* prog);
-// Puts `floats` elements of a partial-tile buffer into the unset state the kernel expects between launches: once
-// after allocation, and again after a launch that raised the error word.
-cudaError_t tick_reset_partials(float* partials, size_t floats, cudaStream_t stream);
 void tick_free(TickProgram* prog);
 // Raises the kernel's shared-memory limit and reports how many CTAs can be co-resident (0 on failure).
 int tick_configure(int device);
-// One cooperative launch of the whole program. `partials`: a buffer of prog.partial_floats floats that only this
-// kernel writes, unset (tick_reset_partials) before the first launch. `barrier` is one device u32, zero before the first launch;
+// One cooperative launch of the whole program. `barrier` is one device u32, zero before the first launch;
 // `*barrier_base` (host, starts at 0) tracks the arrivals earlier launches left in it. Set *barrier_base = ~0u after a
 // launch that raised the error word (its CTAs may not all have arrived): the next launch then restarts the counter.
 // `trace` (optional, four u64 per (phase, CTA), phase-major): the global timer when the CTA's first activation tile

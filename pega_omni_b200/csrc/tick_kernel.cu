@@ -140,17 +140,21 @@ __device__ bool grid_barrier(uint32_t* counter, uint32_t target, uint32_t* err) 
 
 // Split-K partial tiles: [split][tile][row (bn)][tile_n columns] f32, tile_n = 64, 128 or 256. Sums are taken in
 // split order starting from zero, so the result does not depend on which CTA computed which split.
-//
-// Hand-off without a grid barrier. Between launches and between uses every element of the partial buffer holds
-// kUnsetBits, a NaN pattern that no tcgen05 accumulator produces (the tensor core's NaN is 0x7fffffff). A GEMM
-// epilogue overwrites its elements; the consumer loads the elements it sums and loads them again until none reads
-// kUnsetBits (every 4-byte element is written whole, so a 16-byte store that lands in pieces is still read
-// correctly), then puts kUnsetBits back. A phase that consumes partial tiles therefore starts as soon as the CTA's
-// own GEMM items are stored, and its loads are already under way when the last producer's stores land. The phase
-// ends with a grid barrier, which orders the restored kUnsetBits before the next GEMM that writes the buffer. Every
-// partial element is summed by exactly one thread.
-constexpr uint32_t kUnsetBits = 0xffffffffu;
+struct Partials {
+  const float* base;
+  int splits, tiles, bn, shift;  // shift = log2(tile_n)
+  size_t split_stride;
+  __device__ __forceinline__ Partials(const float* p, const Phase& ph)
+      : base(p), splits(ph.splits), tiles(ph.tiles), bn(ph.bn), shift(ph.tile_n == 256 ? 8 : ph.tile_n == 128 ? 7 : 6),
+        split_stride((size_t)ph.tiles * ph.bn * ph.tile_n) {}
+  __device__ __forceinline__ uint32_t at(int m, int n) const {  // element offset inside split 0
+    return (uint32_t)((((size_t)(n >> shift) * bn + m) << shift) + (n & ((1 << shift) - 1)));
+  }
+};
 
+// NV groups of VEC consecutive columns of one row at once (a group never straddles a tile: cols[j] is a multiple
+// of VEC). The split loop is outermost and unrolled so the loads of several splits are independent and in flight
+// together: one L2 round trip per batch instead of one per element.
 template <int VEC>
 struct VecOf;
 template <>
@@ -160,110 +164,39 @@ struct VecOf<2> { using T = float2; };
 template <>
 struct VecOf<4> { using T = float4; };
 
-template <int VEC>
-__device__ __forceinline__ void ld_partial(const float* p, float* v) {
-  if constexpr (VEC == 4)
-    asm volatile("ld.relaxed.gpu.global.v4.f32 {%0, %1, %2, %3}, [%4];"
-                 : "=f"(v[0]), "=f"(v[1]), "=f"(v[2]), "=f"(v[3]) : "l"(p));
-  else if constexpr (VEC == 2)
-    asm volatile("ld.relaxed.gpu.global.v2.f32 {%0, %1}, [%2];" : "=f"(v[0]), "=f"(v[1]) : "l"(p));
-  else
-    asm volatile("ld.relaxed.gpu.global.f32 %0, [%1];" : "=f"(v[0]) : "l"(p));
-}
-
-template <int VEC>
-__device__ __forceinline__ void unset_partial(float* p) {
-  const float u = __uint_as_float(kUnsetBits);
-  if constexpr (VEC == 4) *reinterpret_cast<float4*>(p) = make_float4(u, u, u, u);
-  else if constexpr (VEC == 2) *reinterpret_cast<float2*>(p) = make_float2(u, u);
-  else *p = u;
-}
-
-struct Partials {
-  float* base;
-  uint32_t* err;
-  int splits, tiles, bn, shift;  // shift = log2(tile_n)
-  size_t split_stride;
-  __device__ __forceinline__ Partials(float* p, const Phase& ph, uint32_t* e)
-      : base(p), err(e), splits(ph.splits), tiles(ph.tiles), bn(ph.bn),
-        shift(ph.tile_n == 256 ? 8 : ph.tile_n == 128 ? 7 : 6), split_stride((size_t)ph.tiles * ph.bn * ph.tile_n) {}
-  __device__ __forceinline__ uint32_t at(int m, int n) const {  // element offset inside split 0
-    return (uint32_t)((((size_t)(n >> shift) * bn + m) << shift) + (n & ((1 << shift) - 1)));
-  }
-};
-
-// Sums, over the splits in index order, NV groups of VEC consecutive floats at element offsets off[] of split 0
-// (bit j of `valid` clear: group j is skipped and reads as zero, so threads whose columns were clamped onto a
-// neighbour's never touch them). The loads of kBatch splits are issued together (one L2 round trip per batch instead of
-// one per element) and repeated until every element has been produced; the elements are then handed back unset.
-template <int NV, int VEC, int kBatch>
-__device__ __forceinline__ void reduce_at(const Partials& pt, const uint32_t (&off)[NV], uint32_t valid,
-                                          float (&acc)[NV * VEC]) {
-#pragma unroll
-  for (int i = 0; i < NV * VEC; ++i) acc[i] = 0.f;
-  float* base = pt.base;
-  for (int s0 = 0; s0 < pt.splits; s0 += kBatch, base += kBatch * pt.split_stride) {
-    float f[kBatch][NV][VEC];
-    uint64_t start = 0;
-    for (uint32_t spins = 0;; ++spins) {
-#pragma unroll
-      for (int b = 0; b < kBatch; ++b)
-#pragma unroll
-        for (int j = 0; j < NV; ++j) {
-          if (s0 + b < pt.splits && (valid >> j & 1u)) {
-            ld_partial<VEC>(base + b * pt.split_stride + off[j], f[b][j]);
-          } else {
-#pragma unroll
-            for (int e = 0; e < VEC; ++e) f[b][j][e] = 0.f;  // adding 0 for a missing split leaves the sum unchanged
-          }
-        }
-      bool unset = false;
-#pragma unroll
-      for (int b = 0; b < kBatch; ++b)
-#pragma unroll
-        for (int j = 0; j < NV; ++j)
-#pragma unroll
-          for (int e = 0; e < VEC; ++e) unset |= __float_as_uint(f[b][j][e]) == kUnsetBits;
-      if (!unset) break;
-      if ((spins & 63u) == 63u) {  // bounded: a producer that never stores raises the error word instead of a hang
-        if (*reinterpret_cast<volatile uint32_t*>(pt.err) != 0) break;
-        const uint64_t now = sm100::global_timer_ns();
-        if (start == 0) start = now;
-        if (now - start > sm100::kWaitLimitNs) {
-          raise(pt.err, kErrBarrierTimeout);
-          break;
-        }
-      }
-    }
-#pragma unroll
-    for (int b = 0; b < kBatch; ++b)
-#pragma unroll
-      for (int j = 0; j < NV; ++j)
-        if (s0 + b < pt.splits && (valid >> j & 1u)) unset_partial<VEC>(base + b * pt.split_stride + off[j]);
-#pragma unroll
-    for (int b = 0; b < kBatch; ++b)
-#pragma unroll
-      for (int j = 0; j < NV; ++j)
-#pragma unroll
-        for (int e = 0; e < VEC; ++e) acc[j * VEC + e] += f[b][j][e];
-  }
-}
-
-// NV groups of VEC consecutive columns of row m (a group never straddles a tile: cols[j] is a multiple of VEC).
 template <int NV, int VEC>
-__device__ __forceinline__ void reduce_vecs(const Partials& pt, int m, const int (&cols)[NV], float (&acc)[NV * VEC],
-                                            uint32_t valid = 0xffffffffu) {
+__device__ __forceinline__ void reduce_vecs(const Partials& pt, int m, const int (&cols)[NV], float (&acc)[NV * VEC]) {
+  using V = typename VecOf<VEC>::T;
   uint32_t off[NV];
 #pragma unroll
   for (int j = 0; j < NV; ++j) off[j] = pt.at(m, cols[j]);
+#pragma unroll
+  for (int i = 0; i < NV * VEC; ++i) acc[i] = 0.f;
+  const float* base = pt.base;
   constexpr int kBatch = NV * VEC <= 4 ? 8 : NV * VEC <= 16 ? 4 : 2;  // splits whose loads are issued before any is consumed
-  reduce_at<NV, VEC, kBatch>(pt, off, valid, acc);
+  for (int s0 = 0; s0 < pt.splits; s0 += kBatch, base += kBatch * pt.split_stride) {
+    V f[kBatch][NV];
+#pragma unroll
+    for (int b = 0; b < kBatch; ++b)
+#pragma unroll
+      for (int j = 0; j < NV; ++j) {
+        if (s0 + b < pt.splits)
+          f[b][j] = __ldcg(reinterpret_cast<const V*>(base + b * pt.split_stride + off[j]));
+        else
+          f[b][j] = V{};  // adding 0 for a missing split leaves the sum unchanged
+      }
+#pragma unroll
+    for (int b = 0; b < kBatch; ++b)
+#pragma unroll
+      for (int j = 0; j < NV; ++j)
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) acc[j * VEC + e] += reinterpret_cast<const float*>(&f[b][j])[e];
+  }
 }
 
 template <int N>
-__device__ __forceinline__ void reduce_cols(const Partials& pt, int m, const int (&cols)[N], float (&acc)[N],
-                                            uint32_t valid = 0xffffffffu) {
-  reduce_vecs<N, 1>(pt, m, cols, acc, valid);
+__device__ __forceinline__ void reduce_cols(const Partials& pt, int m, const int (&cols)[N], float (&acc)[N]) {
+  reduce_vecs<N, 1>(pt, m, cols, acc);
 }
 
 // The row-wise phases' access pattern: a 128-thread group owns a row; thread j owns, for t < NV, the VEC
@@ -276,8 +209,37 @@ __device__ __forceinline__ void reduce_row(const Partials& pt, int m, int gtid, 
   uint32_t off[NV];
 #pragma unroll
   for (int t = 0; t < NV; ++t) off[t] = pt.at(m, row_col<NV, VEC>(t, gtid));
+#pragma unroll
+  for (int i = 0; i < NV * VEC; ++i) acc[i] = 0.f;
+  const float* base = pt.base;
   constexpr int kBatch = NV * VEC <= 8 ? 8 : 4;  // splits whose loads are issued before any is consumed
-  reduce_at<NV, VEC, kBatch>(pt, off, 0xffffffffu, acc);
+  for (int s0 = 0; s0 < pt.splits; s0 += kBatch, base += kBatch * pt.split_stride) {
+    if constexpr (VEC == 4) {
+      float4 f[kBatch][NV];
+#pragma unroll
+      for (int b = 0; b < kBatch; ++b)
+#pragma unroll
+        for (int t = 0; t < NV; ++t)
+          f[b][t] = s0 + b < pt.splits ? __ldcg(reinterpret_cast<const float4*>(base + b * pt.split_stride + off[t]))
+                                       : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int b = 0; b < kBatch; ++b)
+#pragma unroll
+        for (int t = 0; t < NV; ++t) {
+          acc[4 * t] += f[b][t].x, acc[4 * t + 1] += f[b][t].y, acc[4 * t + 2] += f[b][t].z, acc[4 * t + 3] += f[b][t].w;
+        }
+    } else {
+      float f[kBatch][NV];
+#pragma unroll
+      for (int b = 0; b < kBatch; ++b)
+#pragma unroll
+        for (int t = 0; t < NV; ++t) f[b][t] = s0 + b < pt.splits ? __ldcg(base + b * pt.split_stride + off[t]) : 0.f;
+#pragma unroll
+      for (int b = 0; b < kBatch; ++b)
+#pragma unroll
+        for (int t = 0; t < NV; ++t) acc[t] += f[b][t];
+    }
+  }
 }
 
 // VEC consecutive bf16 at p, widened / narrowed.
@@ -395,10 +357,10 @@ __device__ __noinline__ void embed_norm_rows(const Phase& ph, const TickIo& io, 
 }
 
 template <int NV, int VEC>
-__device__ __noinline__ void reduce_norm_rows(const Phase& ph, float* partials, const Team& tm, uint32_t* err) {
+__device__ __noinline__ void reduce_norm_rows(const Phase& ph, const float* partials, const Team& tm) {
   const int dim = ph.N;
   const bf16* bias = (const bf16*)ph.src0;
-  const Partials pt(partials, ph, err);
+  const Partials pt(partials, ph);
   if (tm.group >= ph.rows) return;
   const Gain<NV, VEC> gain((const bf16*)ph.src3, tm.gtid);
   for (int row = tm.group; row < ph.rows; row += tm.n_groups) {
@@ -422,10 +384,10 @@ __device__ __noinline__ void reduce_norm_rows(const Phase& ph, float* partials, 
 }
 
 template <int NV, int VEC>
-__device__ __noinline__ void add_norm_rows(const Phase& ph, float* partials, const Team& tm, uint32_t* err) {
+__device__ __noinline__ void add_norm_rows(const Phase& ph, const float* partials, const Team& tm) {
   const int dim = ph.N, every = ph.i0, which = ph.i1;
   bf16 *res = (bf16*)ph.dst0, *out = (bf16*)ph.dst1;
-  const Partials pt(partials, ph, err);
+  const Partials pt(partials, ph);
   if (tm.group >= ph.rows) return;
   const Gain<NV, VEC> gain((const bf16*)ph.src3, tm.gtid);
   for (int row = tm.group; row < ph.rows; row += tm.n_groups) {
@@ -457,23 +419,21 @@ __device__ __noinline__ void add_norm_rows(const Phase& ph, float* partials, con
 
 // SwiGLU over split-K partials of the gate|up GEMM (each tile holds tile_n/2 gate channels then the matching up
 // channels): act[m, c] = bf16(bf16(silu(bf16(gate))) * bf16(up)). One group per (row, 512-channel chunk).
-__device__ __noinline__ void reduce_silu_rows(const Phase& ph, float* partials, const Team& tm, uint32_t* err) {
+__device__ __noinline__ void reduce_silu_rows(const Phase& ph, const float* partials, const Team& tm) {
   const int inter = ph.i0, chunks = (inter + 4 * kGroupThreads - 1) / (4 * kGroupThreads), half = ph.tile_n >> 1;
   bf16* act = (bf16*)ph.dst0;
-  const Partials pt(partials, ph, err);
+  const Partials pt(partials, ph);
   for (int it = tm.group; it < ph.rows * chunks; it += tm.n_groups) {
     const int row = it % ph.rows, c0 = (it / ph.rows) * 4 * kGroupThreads;
     int cols[8];
     float v[8];
-    uint32_t valid = 0u;
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
       const int c = min(c0 + q * kGroupThreads + tm.gtid, inter - 1);
       cols[q] = (c / half) * ph.tile_n + c % half;  // gate
       cols[4 + q] = cols[q] + half;                 // up
-      if (c0 + q * kGroupThreads + tm.gtid < inter) valid |= 0x11u << q;
     }
-    reduce_cols<8>(pt, row, cols, v, valid);
+    reduce_cols<8>(pt, row, cols, v);
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
       const int c = c0 + q * kGroupThreads + tm.gtid;
@@ -490,8 +450,9 @@ __device__ __noinline__ void reduce_silu_rows(const Phase& ph, float* partials, 
 // warps), one warp for the code predictor's single-page frames (so all eight worker warps of a CTA hold an item).
 
 template <int D, int G, int W, typename TeamSync>
-__device__ __noinline__ void rope_attend_item(const Phase& ph, const TickIo& io, float* partials, int seq, int kh,
-                                              int tid, AttnShared<D, G, W>& sh, const TeamSync& team, uint32_t* err) {
+__device__ __noinline__ void rope_attend_item(const Phase& ph, const TickIo& io, const float* partials, int seq, int kh,
+                                              int tid, AttnShared<D, G, W>& sh, const TeamSync& team, uint32_t* err,
+                                              unsigned long long* stamp = nullptr) {
   constexpr int E = D / 64, VE = D / 32;
   const int hq = ph.i0, hk = ph.i1, per = ph.i3, base = ph.i4;
   const bool paged = ph.i5 != 0;
@@ -499,7 +460,7 @@ __device__ __noinline__ void rope_attend_item(const Phase& ph, const TickIo& io,
   bf16 *kv = (bf16*)ph.dst0, *out = (bf16*)ph.dst1;
   const int lane = tid & 31, warp = tid >> 5;
   const float scale = rsqrtf((float)D);
-  const Partials pt(partials, ph, err);
+  const Partials pt(partials, ph);
   float qwl[E], qwh[E], kwl[E], kwh[E];  // this lane's q/k norm gains, fetched before any partial sum is waited on
 #pragma unroll
   for (int e = 0; e < E; ++e) {
@@ -586,14 +547,16 @@ __device__ __noinline__ void rope_attend_item(const Phase& ph, const TickIo& io,
     }
     __threadfence_block();
     team.sync();
+    if (stamp && tid == 0) stamp[0] = sm100::global_timer_ns();  // q/k/v summed, normed, rotated, K/V written
     attend_pages<D, G, W>(sh, kv, paged ? io.pages + io.indptr[n] : nullptr, seq, pos + 1, hk, kh, scale,
                           out + ((int64_t)n * hq + kh * G) * D, tid, team);
+    if (stamp && tid == 0) stamp[1] = sm100::global_timer_ns();  // attention of the item's row done
   }
 }
 
 template <int D, int G>
-__device__ __forceinline__ void rope_attn_dg(const Phase& ph, const TickIo& io, float* partials, const Team& tm,
-                                             int wtid, WorkerScratch& scratch, uint32_t* err) {
+__device__ __forceinline__ void rope_attn_dg(const Phase& ph, const TickIo& io, const float* partials, const Team& tm,
+                                             int wtid, WorkerScratch& scratch, uint32_t* err, unsigned long long* stamp) {
   const int hk = ph.i1, per = ph.i3;
   const int items = (ph.rows / per) * hk;
   if (ph.i5) {  // paged: a two-warp team per item, so one round covers 4 x (number of CTAs) items
@@ -601,34 +564,35 @@ __device__ __forceinline__ void rope_attn_dg(const Phase& ph, const TickIo& io, 
     auto& sh = reinterpret_cast<AttnShared<D, G, 2>&>(scratch.attn2[team]);
     const int first = team * (int)gridDim.x + (int)blockIdx.x, n_teams = 4 * (int)gridDim.x;
     for (int it = first; it < items; it += n_teams)
-      rope_attend_item<D, G, 2>(ph, io, partials, it / hk, it % hk, wtid & 63, sh, PairBar{4 + team}, err);
+      rope_attend_item<D, G, 2>(ph, io, partials, it / hk, it % hk, wtid & 63, sh, PairBar{4 + team}, err,
+                                wtid == 0 ? stamp : nullptr);
   } else {  // one page per sequence: a warp per item
     auto& sh = reinterpret_cast<AttnShared<D, G, 1>&>(scratch.attn1[wtid >> 5]);
     // warp ids run over the CTAs first, so a phase with few items spreads over as many SMs as it has items
     const int wid = (wtid >> 5) * (int)gridDim.x + (int)blockIdx.x, n_warps = (int)gridDim.x * (kWorkerThreads / 32);
     for (int it = wid; it < items; it += n_warps)
-      rope_attend_item<D, G, 1>(ph, io, partials, it / hk, it % hk, wtid & 31, sh, WarpSync(), err);
+      rope_attend_item<D, G, 1>(ph, io, partials, it / hk, it % hk, wtid & 31, sh, WarpSync(), err, wtid == 0 ? stamp : nullptr);
   }
 }
 
-__device__ __forceinline__ void phase_rope_attn(const Phase& ph, const TickIo& io, float* partials, const Team& tm,
-                                                int wtid, WorkerScratch& scratch, uint32_t* err) {
+__device__ __forceinline__ void phase_rope_attn(const Phase& ph, const TickIo& io, const float* partials, const Team& tm,
+                                                int wtid, WorkerScratch& scratch, uint32_t* err, unsigned long long* stamp) {
   const int D = ph.i2, G = ph.i0 / ph.i1;
   if (D == 128) {
-    if (G == 1) rope_attn_dg<128, 1>(ph, io, partials, tm, wtid, scratch, err);
-    else if (G == 2) rope_attn_dg<128, 2>(ph, io, partials, tm, wtid, scratch, err);
-    else rope_attn_dg<128, 4>(ph, io, partials, tm, wtid, scratch, err);
+    if (G == 1) rope_attn_dg<128, 1>(ph, io, partials, tm, wtid, scratch, err, stamp);
+    else if (G == 2) rope_attn_dg<128, 2>(ph, io, partials, tm, wtid, scratch, err, stamp);
+    else rope_attn_dg<128, 4>(ph, io, partials, tm, wtid, scratch, err, stamp);
   } else {
-    if (G == 1) rope_attn_dg<64, 1>(ph, io, partials, tm, wtid, scratch, err);
-    else if (G == 2) rope_attn_dg<64, 2>(ph, io, partials, tm, wtid, scratch, err);
-    else rope_attn_dg<64, 4>(ph, io, partials, tm, wtid, scratch, err);
+    if (G == 1) rope_attn_dg<64, 1>(ph, io, partials, tm, wtid, scratch, err, stamp);
+    else if (G == 2) rope_attn_dg<64, 2>(ph, io, partials, tm, wtid, scratch, err, stamp);
+    else rope_attn_dg<64, 4>(ph, io, partials, tm, wtid, scratch, err, stamp);
   }
 }
 
 // ---- head reduce + draw + next predictor input: one row per CTA (all 256 workers) -----------------------------
 
-__device__ __noinline__ void phase_sample(const Phase& ph, const TickIo& io, float* partials, int wtid, sampler::Shared& sh,
-                                          uint32_t* err) {
+__device__ __noinline__ void phase_sample(const Phase& ph, const TickIo& io, const float* partials, int wtid, sampler::Shared& sh,
+                                          unsigned long long* stamp) {
   using Team = sampler::Team<kWorkerThreads, WorkerSync>;
   const int g = gridDim.x;
   bf16* logits_out = (bf16*)ph.dst0;
@@ -656,15 +620,10 @@ __device__ __noinline__ void phase_sample(const Phase& ph, const TickIo& io, flo
     float mine[Team::PER];
     {
       // four columns per load; the head's vocabulary is a multiple of 4 and tiles are padded to a full tile_n
-      // (threads past the vocabulary sum nothing: every partial element has exactly one reader)
       int cols[Team::PER / 4];
-      uint32_t valid = 0u;
 #pragma unroll
-      for (int j = 0; j < Team::PER / 4; ++j) {
-        cols[j] = min(wtid * Team::PER + 4 * j, prm.vocab - 4);
-        if (wtid * Team::PER + 4 * j < prm.vocab) valid |= 1u << j;
-      }
-      reduce_vecs<Team::PER / 4, 4>(Partials(partials, ph, err), row, cols, mine, valid);
+      for (int j = 0; j < Team::PER / 4; ++j) cols[j] = min(wtid * Team::PER + 4 * j, prm.vocab - 4);
+      reduce_vecs<Team::PER / 4, 4>(Partials(partials, ph), row, cols, mine);
 #pragma unroll
       for (int j = 0; j < Team::PER; ++j) {
         const bf16 b = __float2bfloat16(mine[j]);
@@ -672,8 +631,10 @@ __device__ __noinline__ void phase_sample(const Phase& ph, const TickIo& io, flo
         if (wtid * Team::PER + j < prm.vocab) logits_out[(int64_t)row * ph.i0 + wtid * Team::PER + j] = b;
       }
     }
+    if (stamp && wtid == 0) stamp[0] = sm100::global_timer_ns();  // the row's logits are summed
     const int token = Team::sample_row([&](int, int j) { return mine[j]; }, prm, frame, uniform, forced, slot, seen_bits,
                                        io.codes + row * 16 + prm.group, wtid, sh);
+    if (stamp && wtid == 0) stamp[1] = sm100::global_timer_ns();  // the token is drawn
     // the next predictor pass reads the embedding of the code just drawn
     const int dim = ph.i9;
     if (ph.i8 == kNextHiddenAndCode) {
@@ -834,19 +795,12 @@ __global__ void __launch_bounds__(kThreads, 1) tick_kernel(const __grid_constant
         if (first_item(ph) >= items) continue;
         // the rows this phase multiplies were written by earlier phases: wait until those are complete everywhere
         // (by then this CTA's earlier GEMM phases are over too, so a change of stage geometry needs no further wait)
-        // (a tight poll of the shared-memory word: a __nanosleep here, however short, was measured to add 0.4-0.5 us
-        // to every GEMM phase)
-        {
-          uint64_t start = 0;
-          for (uint32_t spins = 0; ctl.released < p && !ctl.abort; ++spins) {
-            if ((spins & 255u) == 255u) {
-              const uint64_t now = global_timer_ns();
-              if (start == 0) start = now;
-              if (now - start > kWaitLimitNs) {
-                raise(a.err, kErrBarrierTimeout);
-                ctl.abort = 1;
-              }
-            }
+        const uint64_t start = global_timer_ns();
+        while (ctl.released < p && !ctl.abort) {
+          __nanosleep(40);
+          if (global_timer_ns() - start > kWaitLimitNs) {
+            raise(a.err, kErrBarrierTimeout);
+            ctl.abort = 1;
           }
         }
         asm volatile("fence.proxy.async;" ::: "memory");  // generic-proxy writes of other CTAs -> async-proxy reads
@@ -970,7 +924,6 @@ __global__ void __launch_bounds__(kThreads, 1) tick_kernel(const __grid_constant
     const Team tm{grp * G + (int)blockIdx.x, G * 2, wtid & 127, ctl.red[grp], GroupBar{2 + grp}};
     int buf = 0;
     uint32_t full_par[2] = {0, 0};
-    uint32_t barriers = 0;  // grid barriers this launch has passed
     for (int p = 0; p < a.n_phases; ++p) {
       if (ctl.abort) break;
       // the phase record was copied to shared memory during the previous phase; fetch the next one now
@@ -1014,28 +967,23 @@ __global__ void __launch_bounds__(kThreads, 1) tick_kernel(const __grid_constant
           break;
         }
         case kPhEmbedNorm: OMNI_ROW_DISPATCH(embed_norm_rows, ph.N, ph, a.io, tm, a.err); break;
-        case kPhReduceNorm: OMNI_ROW_DISPATCH(reduce_norm_rows, ph.N, ph, a.partials, tm, a.err); break;
-        case kPhAddNorm: OMNI_ROW_DISPATCH(add_norm_rows, ph.N, ph, a.partials, tm, a.err); break;
-        case kPhReduceSilu: reduce_silu_rows(ph, a.partials, tm, a.err); break;
-        case kPhRopeAttn: phase_rope_attn(ph, a.io, a.partials, tm, wtid, scratch, a.err); break;
-        case kPhSample: phase_sample(ph, a.io, a.partials, wtid, scratch.sample, a.err); break;
+        case kPhReduceNorm: OMNI_ROW_DISPATCH(reduce_norm_rows, ph.N, ph, a.partials, tm); break;
+        case kPhAddNorm: OMNI_ROW_DISPATCH(add_norm_rows, ph.N, ph, a.partials, tm); break;
+        case kPhReduceSilu: reduce_silu_rows(ph, a.partials, tm); break;
+        case kPhRopeAttn:
+          phase_rope_attn(ph, a.io, a.partials, tm, wtid, scratch, a.err, a.trace ? a.trace + ((size_t)p * G + blockIdx.x) * 4 : nullptr);
+          break;
+        case kPhSample:
+          phase_sample(ph, a.io, a.partials, wtid, scratch.sample, a.trace ? a.trace + ((size_t)p * G + blockIdx.x) * 4 : nullptr);
+          break;
         default: break;
       }
-      // A GEMM whose partial tiles the next phase sums hands them over element by element (see Partials): no grid
-      // barrier, only the team barrier that keeps the two phase records in shared memory apart.
-      const bool handoff = ph.type == kPhGemm && ph.i11 != 0;
       // end of phase: the team barrier orders every worker's writes before thread 0's gpu-scope fence and arrival
       // (fences are cumulative), then everyone waits for thread 0 to see all CTAs arrive
       WorkerSync::sync();
-      if (handoff) {
-        if (a.trace && wtid == 0)
-          a.trace[((size_t)p * G + blockIdx.x) * 4 + 2] = a.trace[((size_t)p * G + blockIdx.x) * 4 + 3] = global_timer_ns();
-        continue;
-      }
-      ++barriers;
       if (wtid == 0) {
         if (a.trace) a.trace[((size_t)p * G + blockIdx.x) * 4 + 2] = global_timer_ns();  // this CTA's share is done
-        if (!ctl.abort && !grid_barrier(a.barrier, a.barrier_base + barriers * (uint32_t)G, a.err)) ctl.abort = 1;
+        if (!ctl.abort && !grid_barrier(a.barrier, a.barrier_base + (uint32_t)(p + 1) * (uint32_t)G, a.err)) ctl.abort = 1;
         ctl.released = p + 1;
         if (a.trace) a.trace[((size_t)p * G + blockIdx.x) * 4 + 3] = global_timer_ns();  // every CTA has arrived
       }
@@ -1104,31 +1052,6 @@ bool tick_supports(int hidden, int head_dim, int q_heads, int kv_heads, int rows
   return dim_ok && (head_dim == 64 || head_dim == 128) && (g == 1 || g == 2 || g == 4) && rows_max <= 2 * kTileM;
 }
 
-bool tick_finish(TickProgram* prog) {
-  auto sums_partials = [](int type) {
-    return type == kPhReduceNorm || type == kPhAddNorm || type == kPhRopeAttn || type == kPhSample || type == kPhReduceSilu;
-  };
-  for (size_t i = 0; i < prog->phases.size(); ++i) {
-    Phase& ph = prog->phases[i];
-    const bool next_sums = i + 1 < prog->phases.size() && sums_partials(prog->phases[i + 1].type);
-    if (ph.type == kPhGemm && ph.mode == kGemmPartials) {
-      if (!next_sums) return false;
-      // Measured on B200 (64 sessions): behind the large projections (hidden 2048) the hand-off saves 2-3 us per
-      // GEMM -> consumer pair; behind small ones (a few MB of weights, every CTA done within a microsecond) and
-      // in front of the draw phase the repeated loads cost more than the barrier they replace.
-      const int next = prog->phases[i + 1].type;
-      ph.i11 = (next == kPhRopeAttn || next == kPhAddNorm) && (int64_t)ph.N * ph.K >= (int64_t)4 << 20;
-    } else if (next_sums) {
-      return false;  // a phase that sums partial tiles nobody stored would wait for them until its time limit
-    }
-  }
-  return true;
-}
-
-cudaError_t tick_reset_partials(float* partials, size_t floats, cudaStream_t stream) {
-  return cudaMemsetAsync(partials, 0xff, floats * sizeof(float), stream);  // four 0xff bytes = kUnsetBits
-}
-
 int tick_upload(TickProgram* prog) {
   tick_free(prog);
   if (cudaMalloc((void**)&prog->d_phases, prog->phases.size() * sizeof(Phase)) != cudaSuccess) return -1;
@@ -1180,9 +1103,7 @@ cudaError_t tick_launch(const TickProgram& prog, const TickIo& io, float* partia
   a.io = io;
   // the arrival counter runs on from launch to launch (one memset less per tick); it restarts from zero when the
   // next launch could overflow it. After a launch that raised the error word the caller passes *barrier_base = ~0u.
-  uint32_t n_barriers = 0;
-  for (const Phase& ph : prog.phases) n_barriers += !(ph.type == kPhGemm && ph.i11 != 0);
-  const uint32_t arrivals = n_barriers * (uint32_t)ctas;
+  const uint32_t arrivals = (uint32_t)a.n_phases * (uint32_t)ctas;
   if (*barrier_base > 0xffffffffu - 2u * arrivals) {
     const cudaError_t e = cudaMemsetAsync(barrier, 0, sizeof(uint32_t), stream);
     if (e != cudaSuccess) return e;
