@@ -40,6 +40,7 @@ typedef struct omni_duplex_config {
   int32_t max_sessions; /* sessions per tick and leases in the pool */
   int32_t max_prefill;  /* prompt rows per `start` call */
   int32_t voice_rows;   /* rows of the optional "voices" tensor [voice_rows, dim] (0: none) */
+  int32_t use_graphs;   /* 1: the tick's kernels replayed as one CUDA graph per bucket; 0: launched one by one */
 } omni_duplex_config;
 
 /* `Step` (model.rs:98-107) without the PCM: tokens to take instead of drawing (-1 draws), the caller's codes to
@@ -99,8 +100,15 @@ int32_t omni_duplex_warm_prefix(omni_duplex* m, int32_t rows, const int32_t* ids
 int32_t omni_duplex_start(omni_duplex* m, int32_t n, omni_duplex_session* const* sessions, const int32_t* row_counts,
                           const int32_t* ids, const int32_t* voice, const int32_t* init, const int32_t* first_force);
 
+/* Replaces `Model::warmup` (model.rs:202-240): runs the tick of every bucket up to max_sessions (1, 2, 4, ...,
+ * max_sessions) on the padding lease, so that every bucket's GEMM plans exist and its CUDA graph is captured before
+ * live traffic. Without it the first two ticks of a bucket pay for that (up to tens of ms). */
+int32_t omni_duplex_warmup(omni_duplex* m);
+
 /* Replaces `Model::tick` (model.rs:373-433): one step of every session given; emitted[i] = the text token spoken
- * now and the agent's frame (`Out::emitted`). */
+ * now and the agent's frame (`Out::emitted`). The sessions are padded up to the bucket (`bucket`,
+ * crates/omni-kern/src/lib.rs:97-101) with rows on an internal padding lease (position 0, nothing forced, seed 0:
+ * model.rs:403-415). */
 int32_t omni_duplex_tick(omni_duplex* m, int32_t n, omni_duplex_session* const* sessions,
                          const omni_duplex_step* steps, int32_t* emitted);
 

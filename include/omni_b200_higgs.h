@@ -33,6 +33,7 @@ typedef struct omni_higgs_config {
   int32_t max_batch;  /* sequences per call */
   int32_t max_tokens; /* prompt rows per `start` */
   double kv_gib;      /* KV pool size */
+  int32_t use_graphs; /* 1: the decode step's kernels replayed as one CUDA graph per bucket; 0: launched one by one */
 } omni_higgs_config;
 
 /* `Draw` (model.rs:99-104): a uniform per codebook, and the codes to take instead; force[b] < 0 in EVERY codebook means
@@ -70,7 +71,13 @@ int32_t omni_higgs_seq_rows(const omni_higgs_seq* seq);
 int32_t omni_higgs_start(omni_higgs* m, int32_t n, omni_higgs_seq* const* seqs, const int32_t* ids,
                          const int32_t* prompt_lens, const omni_higgs_draw* draws, int32_t* rows_out,
                          int32_t* ended_out);
-/* Replaces `Model::step` (model.rs:190-199): the next delayed row of every sequence. */
+/* Runs the decode step of every bucket up to max_batch (1, 2, 4, ..., max_batch) on an internal padding lease, so
+ * that every bucket's GEMM plans exist and its CUDA graph is captured before live traffic (what `Model::warmup` of
+ * the duplex model does, crates/omni-personaplex/src/model.rs:202-240; the reference's Higgs shell compiles its
+ * graphs through the same runtime call). */
+int32_t omni_higgs_warmup(omni_higgs* m);
+/* Replaces `Model::step` (model.rs:190-199): the next delayed row of every sequence. The sequences are padded up to
+ * the bucket with rows on the padding lease (position 0, uniform 0.5, nothing forced). */
 int32_t omni_higgs_step(omni_higgs* m, int32_t n, omni_higgs_seq* const* seqs, const omni_higgs_draw* draws,
                         int32_t* rows_out, int32_t* ended_out);
 

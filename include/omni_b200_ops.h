@@ -160,8 +160,9 @@ int32_t omni_higgs_undelay(const int32_t* rows, int32_t n_rows, int32_t* frames)
  *  - The first call on each device looks up the arrays' device addresses (with that device current) and raises the
  *    kernels' shared-memory limits. Make that first call before starting any stream capture on that device.
  *  - All calls share the one array and it keeps the previous call's contents; the counters and the error word are
- *    cleared on the stream before each launch. Two calls whose kernels overlap on the GPU (different streams or
- *    threads) race on it: serialise them.
+ *    cleared on the stream before each launch. Two calls whose kernels overlapped on the GPU would race on it, so
+ *    the entry point holds a process-wide lock from its set-up until its kernel has finished: calls from several
+ *    host threads run one after the other. `stream` must belong to the current device (checked).
  *  - The call waits for its kernel and returns 0, or a negative omni_status with a human-readable reason in
  *    `message` (caller-owned, may be NULL). */
 int32_t omni_op_gemm_noalloc(const void* w, int32_t N, int32_t K, const void* x, int32_t rows, void* y, int32_t ldy,

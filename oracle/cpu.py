@@ -65,6 +65,7 @@ def load() -> C.CDLL:
         lib.orc_f2bf.restype = C.c_uint16
         lib.orc_f2bf.argtypes = [C.c_float]
         lib.orc_set_threads.argtypes = [C.c_int]
+        lib.orc_round_logits.argtypes = [C.c_int]
         _lib = lib
     return _lib
 

@@ -105,7 +105,9 @@ struct StackW {
 // y[rows, n] = bf16( x[rows, k] . w[n, k]^T ), f32 accumulation: the GEMM op of
 // crates/omni-kern/src/lib.rs:144-179 (`extern:cublaslt_bf16_tn`), all operands
 // bf16 row-major, one rounding of the f32 accumulator to bf16.
-void gemm(const float* x, int rows, const bf16_t* w, int n, int k, float* y, int ldy, int col0 = 0) {
+// (round_out = false keeps the f32 sum: only the two head GEMMs use it, and only when a test asked for the logits
+// before their bf16 store, to measure how far either GPU path is from them)
+void gemm(const float* x, int rows, const bf16_t* w, int n, int k, float* y, int ldy, int col0 = 0, bool round_out = true) {
 #pragma omp parallel for schedule(static)
   for (int j = 0; j < n; ++j) {
     const bf16_t* wr = w + (int64_t)j * k;
@@ -127,10 +129,13 @@ void gemm(const float* x, int rows, const bf16_t* w, int n, int k, float* y, int
       float s = 0.f;
       for (; c < k; ++c) s += xr[c] * wp[c];
       for (int e = 0; e < 16; ++e) s += acc[e];
-      y[(int64_t)r * ldy + col0 + j] = rbf(s);
+      y[(int64_t)r * ldy + col0 + j] = round_out ? rbf(s) : s;
     }
   }
 }
+
+// Test aid: 0 = the head GEMMs keep their f32 sums (every other rounding point stays), 1 = the reference's behaviour.
+bool g_round_logits = true;
 
 // crates/omni-qwen3/kernels/qwen3.cu:18-31 (`qwen3_norm_copy`): res = x,
 // out = bf16(x * rsqrt(mean(x^2) + eps) * w).
@@ -563,7 +568,7 @@ void tail(Model& m, const std::vector<int>& sids, const float* uniforms, const i
   for (int s = 0; s < n; ++s) memcpy(&hidden[(size_t)s * h], m.sessions[sids[s]].hidden.data(), h * sizeof(float));
   m.hidden_out = hidden;
   m.logits.assign((size_t)n * V, 0.f);
-  gemm(hidden.data(), n, m.get("talker.codec_head.weight")->v.data(), V, h, m.logits.data(), V);
+  gemm(hidden.data(), n, m.get("talker.codec_head.weight")->v.data(), V, h, m.logits.data(), V, 0, g_round_logits);
   for (int s = 0; s < n; ++s) {
     Session& S = m.sessions[sids[s]];
     codes[s * 16 + 0] = sample_group(m, S, &m.logits[(size_t)s * V], 0,
@@ -600,7 +605,7 @@ void tail(Model& m, const std::vector<int>& sids, const float* uniforms, const i
     stack_forward(m.pred, ph.data(), rr, last.data(), per, per - 1);
     const Tensor* head = m.get("talker.code_predictor.lm_head." + std::to_string(g - 1) + ".weight");
     float* lg = &m.p_logits[(size_t)(g - 1) * n * PV];
-    gemm(last.data(), n, head->v.data(), PV, p, lg, PV);
+    gemm(last.data(), n, head->v.data(), PV, p, lg, PV, 0, g_round_logits);
     for (int s = 0; s < n; ++s) {
       Session& S = m.sessions[sids[s]];
       codes[s * 16 + g] = sample_group(m, S, lg + (size_t)s * PV, g, session_uniform(m, S, uniforms, s, g, S.frames),
@@ -641,6 +646,8 @@ void* orc_create(const orc_config* cfg, const orc_tensor* tensors, int n) {
 }
 
 void orc_destroy(void* h) { delete (Model*)h; }
+
+void orc_round_logits(int on) { g_round_logits = on != 0; }
 
 void orc_set_threads(int n) {
 #ifdef _OPENMP

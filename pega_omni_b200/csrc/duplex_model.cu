@@ -98,7 +98,10 @@ struct omni_duplex {
   int32_t* out_host = nullptr;  // emitted + error word
   uint32_t* err = nullptr;
 
-  // one CUDA graph of the tick's kernels per session count
+  // the padding lease (model.rs:151,189): one page and one state line that the rows between the live sessions and the
+  // tick's bucket run on
+  int pad_page = 0, pad_line = 0;
+  // one CUDA graph of the tick's kernels per bucket (session counts are padded up to 1, 2, 4, ... or max_sessions)
   struct TickGraph {
     cudaGraphExec_t exec = nullptr;
     int seen = 0, nodes = 0;
@@ -344,7 +347,7 @@ int32_t omni_duplex_create(const omni_duplex_config* config, const omni_tensor* 
   if (prop.major != 10)
     return m->fail(OMNI_ERR_UNSUPPORTED, "device is sm_%d%d; this library is sm_100a only", prop.major, prop.minor);
   m->sm_count = prop.multiProcessorCount;
-  m->use_graphs = getenv("OMNI_DUPLEX_NO_GRAPH") == nullptr;  // tuning aid: per-op launches every tick
+  m->use_graphs = c.use_graphs != 0;
   DCUDA(m, cudaStreamCreateWithFlags(&m->stream, cudaStreamNonBlocking));
   DCUDA(m, cudaEventCreate(&m->ev0));
   DCUDA(m, cudaEventCreate(&m->ev1));
@@ -391,13 +394,15 @@ int32_t omni_duplex_create(const omni_duplex_config* config, const omni_tensor* 
   const int S = c.max_sessions;
   m->pages_per_session = (c.context + 15) / 16;
   m->cache_first_page = S * m->pages_per_session;
-  m->kv_pages = m->cache_first_page + kCacheSlots * ((kCacheMaxLen + 15) / 16);
+  m->kv_pages = m->cache_first_page + kCacheSlots * ((kCacheMaxLen + 15) / 16) + 1;
+  m->pad_page = m->kv_pages - 1;
+  m->pad_line = S;
   m->kv.resize(c.layers);
   for (int i = 0; i < c.layers; ++i)
     DTRY(dalloc(m, &m->kv[i], (size_t)m->kv_pages * c.heads * kDuplexPageHeadBytes, true));
   m->dkv.resize(c.dep_layers);
   for (int i = 0; i < c.dep_layers; ++i) DTRY(dalloc(m, &m->dkv[i], (size_t)S * kDepSteps * 2 * DD, true));
-  DTRY(dalloc(m, &m->state, (size_t)S * m->stride, true));
+  DTRY(dalloc(m, &m->state, (size_t)(S + 1) * m->stride, true));
   for (int i = S - 1; i >= 0; --i) m->free_leases.push_back(i);
 
   m->max_rows = std::max(c.max_prefill, S);
@@ -676,23 +681,27 @@ int32_t omni_duplex_start(omni_duplex* m, int32_t n, omni_duplex_session* const*
   return OMNI_OK;
 }
 
-int32_t omni_duplex_tick(omni_duplex* m, int32_t n, omni_duplex_session* const* sessions,
-                         const omni_duplex_step* steps, int32_t* emitted) {
-  if (!m || !sessions || !steps || !emitted) return OMNI_ERR_INVALID;
+}  // extern "C"
+
+namespace {
+
+// The tick's bucket (`bucket`, crates/omni-kern/src/lib.rs:31-36,97-101): the next power of two, capped at max_sessions.
+int tick_bucket(const omni_duplex* m, int n) {
+  int b = 1;
+  while (b < n) b <<= 1;
+  return std::min(b, m->cfg.max_sessions);
+}
+
+// One tick of n live sessions padded to bucket b (n = 0: the warm-up's tick, every row on the padding lease).
+int tick_rows(omni_duplex* m, int n, int b, omni_duplex_session* const* sessions, const omni_duplex_step* steps,
+              int32_t* emitted) {
   const omni_duplex_config& c = m->cfg;
-  if (n < 1 || n > c.max_sessions) return m->fail(OMNI_ERR_INVALID, "%d sessions in one tick", n);
-  for (int i = 0; i < n; ++i) {
-    if (!sessions[i] || !sessions[i]->live) return m->fail(OMNI_ERR_INVALID, "session %d is not open", i);
-    if (sessions[i]->pos <= 0) return m->fail(OMNI_ERR_INVALID, "a session that was not started");
-    for (int j = 0; j < i; ++j)
-      if (sessions[j] == sessions[i]) return m->fail(OMNI_ERR_INVALID, "session %d appears twice", i);
-  }
   DCUDA(m, cudaSetDevice(m->device));
   Staging st{m};
-  int32_t *pos = st.take(n), *slot = st.take(n), *lines = st.take(n), *indptr = st.take(n + 1);
-  int32_t* pages = st.take((size_t)n * m->pages_per_session);
-  int32_t *force = st.take((size_t)n * kDuplexDrawn), *force_caller = st.take((size_t)n * kDuplexBooks);
-  int32_t *caller = st.take((size_t)n * kDuplexBooks), *seeds = st.take((size_t)n * 2);
+  int32_t *pos = st.take(b), *slot = st.take(b), *lines = st.take(b), *indptr = st.take(b + 1);
+  int32_t* pages = st.take((size_t)b * m->pages_per_session);
+  int32_t *force = st.take((size_t)b * kDuplexDrawn), *force_caller = st.take((size_t)b * kDuplexBooks);
+  int32_t *caller = st.take((size_t)b * kDuplexBooks), *seeds = st.take((size_t)b * 2);
   if (!seeds) return m->fail(OMNI_ERR_INVALID, "staging block too small");
   indptr[0] = 0;
   for (int i = 0; i < n; ++i) {
@@ -712,26 +721,37 @@ int32_t omni_duplex_tick(omni_duplex* m, int32_t n, omni_duplex_session* const* 
     seeds[2 * i] = (int32_t)(uint32_t)steps[i].seed;
     seeds[2 * i + 1] = (int32_t)(uint32_t)(steps[i].seed >> 32);
   }
+  for (int i = n; i < b; ++i) {  // padding rows: position 0 of the padding lease, nothing forced, seed 0 (model.rs:403-415)
+    pos[i] = 0;
+    slot[i] = m->pad_page * 16;
+    lines[i] = m->pad_line;
+    pages[indptr[i]] = m->pad_page;
+    indptr[i + 1] = indptr[i] + 1;
+    for (int k = 0; k < kDuplexDrawn; ++k) force[i * kDuplexDrawn + k] = -1;
+    for (int k = 0; k < kDuplexBooks; ++k) force_caller[i * kDuplexBooks + k] = -1, caller[i * kDuplexBooks + k] = 0;
+    seeds[2 * i] = seeds[2 * i + 1] = 0;
+  }
   m->launches = 0;
   DCUDA(m, cudaEventRecord(m->ev0, m->stream));
   DCUDA(m, cudaMemcpyAsync(m->in_dev, m->in_host, st.used, cudaMemcpyHostToDevice, m->stream));
-  // The kernels of a tick and their arguments depend on n alone (positions, pages, forces and seeds are read from the
-  // staged block, whose layout n fixes), so the sequence is captured once per n and replayed as a CUDA graph. The first
-  // tick of a size runs eagerly (it creates the GEMM plans), the second is captured.
+  // The kernels of a tick and their arguments depend on b alone (positions, pages, forces and seeds are read from the
+  // staged block, whose layout b fixes), so the sequence is captured once per bucket and replayed as a CUDA graph. The
+  // first tick of a bucket runs eagerly (it creates the GEMM plans), the second is captured; omni_duplex_warmup does
+  // both for every bucket before live traffic.
   auto body = [&]() -> int {
     // `Helium::step` (helium.rs:189-222)
-    DLAUNCH(m, launch_lm_embed_state(m->state, st.dev(lines), m->stride, tables(m), m->x, m->rows_buf, n, c.dim, m->err,
+    DLAUNCH(m, launch_lm_embed_state(m->state, st.dev(lines), m->stride, tables(m), m->x, m->rows_buf, b, c.dim, m->err,
                                      m->stream));
-    DTRY(helium_forward(m, n, st.dev(pos), st.dev(slot), nullptr, st.dev(indptr), st.dev(pages)));
-    DTRY(gemm(m, m->text_linear, c.text_vocab, c.dim, m->xn, n, m->text_logits, c.text_vocab));
+    DTRY(helium_forward(m, b, st.dev(pos), st.dev(slot), nullptr, st.dev(indptr), st.dev(pages)));
+    DTRY(gemm(m, m->text_linear, c.text_vocab, c.dim, m->xn, b, m->text_logits, c.text_vocab));
     DLAUNCH(m, launch_lm_sample(m->text_logits, c.text_vocab, c.text_vocab, c.text_temperature, c.text_top_k,
-                                st.dev(force), st.dev(seeds), 0, m->drawn, n, m->stream));
-    DTRY(depformer_step(m, n, st.dev(force), st.dev(seeds)));
+                                st.dev(force), st.dev(seeds), 0, m->drawn, b, m->stream));
+    DTRY(depformer_step(m, b, st.dev(force), st.dev(seeds)));
     DLAUNCH(m, launch_lm_advance(m->state, st.dev(lines), m->stride, m->drawn, st.dev(caller), st.dev(force_caller),
-                                 m->emitted, n, m->stream));
+                                 m->emitted, b, m->stream));
     return OMNI_OK;
   };
-  omni_duplex::TickGraph& tg = m->tick_graphs[n];
+  omni_duplex::TickGraph& tg = m->tick_graphs[b];
   if (!m->use_graphs || tg.seen == 0) {
     DTRY(body());
     tg.seen = 1;
@@ -757,13 +777,45 @@ int32_t omni_duplex_tick(omni_duplex* m, int32_t n, omni_duplex_session* const* 
     DCUDA(m, cudaGraphLaunch(tg.exec, m->stream));
     m->launches = tg.nodes;
   }
-  DCUDA(m, cudaMemcpyAsync(m->out_host, m->emitted, (size_t)n * kDuplexDrawn * 4, cudaMemcpyDeviceToHost, m->stream));
+  if (n > 0)
+    DCUDA(m, cudaMemcpyAsync(m->out_host, m->emitted, (size_t)n * kDuplexDrawn * 4, cudaMemcpyDeviceToHost, m->stream));
   DTRY(finish(m, (size_t)n * kDuplexDrawn));
-  memcpy(emitted, m->out_host, (size_t)n * kDuplexDrawn * 4);
+  if (n > 0) memcpy(emitted, m->out_host, (size_t)n * kDuplexDrawn * 4);
+  return OMNI_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t omni_duplex_tick(omni_duplex* m, int32_t n, omni_duplex_session* const* sessions,
+                         const omni_duplex_step* steps, int32_t* emitted) {
+  if (!m || !sessions || !steps || !emitted) return OMNI_ERR_INVALID;
+  const omni_duplex_config& c = m->cfg;
+  if (n < 1 || n > c.max_sessions) return m->fail(OMNI_ERR_INVALID, "%d sessions in one tick", n);
+  for (int i = 0; i < n; ++i) {
+    if (!sessions[i] || !sessions[i]->live) return m->fail(OMNI_ERR_INVALID, "session %d is not open", i);
+    if (sessions[i]->pos <= 0) return m->fail(OMNI_ERR_INVALID, "a session that was not started");
+    for (int j = 0; j < i; ++j)
+      if (sessions[j] == sessions[i]) return m->fail(OMNI_ERR_INVALID, "session %d appears twice", i);
+  }
+  DTRY(tick_rows(m, n, tick_bucket(m, n), sessions, steps, emitted));
   for (int i = 0; i < n; ++i) {
     sessions[i]->pos += 1;
     sessions[i]->frame += 1;
   }
+  return OMNI_OK;
+}
+
+// `Model::warmup` (model.rs:202-240): every bucket's tick on the padding lease, twice (plans, then the captured graph),
+// so that no live tick pays for a graph capture.
+int32_t omni_duplex_warmup(omni_duplex* m) {
+  if (!m) return OMNI_ERR_INVALID;
+  std::vector<int> buckets;
+  for (int b = 1; b < m->cfg.max_sessions; b <<= 1) buckets.push_back(b);
+  buckets.push_back(m->cfg.max_sessions);
+  for (int b : buckets)
+    for (int pass = 0; pass < (m->use_graphs ? 2 : 1); ++pass) DTRY(tick_rows(m, 0, b, nullptr, nullptr, nullptr));
   return OMNI_OK;
 }
 

@@ -1,6 +1,8 @@
 // The two GEMM paths of the token loop (see gemm.h).
 #include "gemm.h"
 
+#include <mutex>
+
 #include <algorithm>
 #include <cstdarg>
 #include <cstdio>
@@ -688,13 +690,15 @@ static __device__ __align__(256) uint32_t g_static_error[64];
 // In host code the three names above are only handles to the device arrays; the
 // device addresses a kernel can use are looked up once per device, with that
 // device current, and kept here.
+constexpr int kStaticDevices = 64;
 struct StaticScratch {
   bool ready = false;
   float* partials = nullptr;
   uint32_t* counters = nullptr;
   uint32_t* error = nullptr;
 };
-StaticScratch g_static[64];
+StaticScratch g_static[kStaticDevices];
+std::mutex g_static_mutex;  // two host threads may make their first call on a device at once
 
 void say(char* buf, size_t len, const char* fmt, ...) {
   if (!buf || len == 0) return;
@@ -723,11 +727,30 @@ extern "C" int32_t omni_op_gemm_noalloc(const void* w, int32_t N, int32_t K, con
   }
   int device = -1;
   cudaError_t e = cudaGetDevice(&device);
-  if (e != cudaSuccess || device < 0 || device >= 64) {
+  if (e != cudaSuccess) {
     say(message, message_len, "cudaGetDevice: %s", cudaGetErrorString(e));
     return kCuda;
   }
+  if (device < 0 || device >= kStaticDevices) {
+    say(message, message_len, "device index %d is beyond the %d devices this entry point keeps addresses for", device,
+        kStaticDevices);
+    return kUnsupported;
+  }
+  if (stream) {  // the scratch addresses belong to the current device: a stream of another device would get the wrong ones
+    int stream_device = device;
+#if CUDART_VERSION >= 12080
+    if (cudaStreamGetDevice(static_cast<cudaStream_t>(stream), &stream_device) != cudaSuccess) {
+      cudaGetLastError();
+      stream_device = device;
+    }
+#endif
+    if (stream_device != device) {
+      say(message, message_len, "the stream belongs to device %d, the current device is %d", stream_device, device);
+      return kInvalid;
+    }
+  }
   StaticScratch& sc = g_static[device];
+  std::lock_guard<std::mutex> lock(g_static_mutex);  // (also serialises this entry point's calls from host threads)
   if (!sc.ready) {  // first call on this device: resolve the arrays' device addresses
     cudaDeviceProp prop;
     if ((e = cudaGetDeviceProperties(&prop, device)) != cudaSuccess || prop.major != 10) {

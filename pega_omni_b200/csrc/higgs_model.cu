@@ -77,7 +77,9 @@ struct omni_higgs {
   GemmScratch scratch;
   std::map<std::tuple<const void*, const void*, const void*, int>, TcGemmPlan> plans;
   std::map<std::tuple<const void*, const void*, const void*, int>, RmGemmPlan> rm_plans;
-  // one CUDA graph of the decode step's kernels per sequence count
+  // the padding lease: one page and one state line for the rows between the live sequences and the step's bucket
+  int pad_page = 0, pad_line = 0;
+  // one CUDA graph of the decode step's kernels per bucket (sequence counts are padded up to 1, 2, 4, ... or max_batch)
   struct StepGraph {
     cudaGraphExec_t exec = nullptr;
     int seen = 0, nodes = 0;
@@ -314,7 +316,7 @@ int32_t omni_higgs_create(const omni_higgs_config* config, const omni_tensor* te
   if (prop.major != 10)
     return m->fail(OMNI_ERR_UNSUPPORTED, "device is sm_%d%d; this library is sm_100a only", prop.major, prop.minor);
   m->sm_count = prop.multiProcessorCount;
-  m->use_graphs = getenv("OMNI_HIGGS_NO_GRAPH") == nullptr;  // tuning aid: per-op launches every step
+  m->use_graphs = c.use_graphs != 0;
   HCUDA(m, cudaStreamCreateWithFlags(&m->stream, cudaStreamNonBlocking));
   HCUDA(m, cudaEventCreate(&m->ev0));
   HCUDA(m, cudaEventCreate(&m->ev1));
@@ -363,7 +365,10 @@ int32_t omni_higgs_create(const omni_higgs_config* config, const omni_tensor* te
   m->kv.resize(b.layers);
   for (int i = 0; i < b.layers; ++i) HTRY(halloc(m, &m->kv[i], (size_t)m->pages_total * 16 * 2 * kvw, true));
   for (int p = m->pages_total - 1; p >= 0; --p) m->free_pages.push_back(p);
-  HTRY(halloc(m, &m->state, (size_t)c.max_batch * m->stride, true));
+  m->pad_page = m->free_pages.back();  // the padding lease keeps one page and the state line behind the sequences' lines
+  m->free_pages.pop_back();
+  m->pad_line = c.max_batch;
+  HTRY(halloc(m, &m->state, (size_t)(c.max_batch + 1) * m->stride, true));
   for (int i = c.max_batch - 1; i >= 0; --i) m->free_lines.push_back(i);
 
   m->max_rows = std::max(c.max_tokens, c.max_batch);
@@ -412,7 +417,7 @@ int32_t omni_higgs_open(omni_higgs* m, int32_t prompt, int32_t rows, omni_higgs_
   if (!m || !out || prompt < 1 || rows < 1) return OMNI_ERR_INVALID;
   *out = nullptr;
   const int need = (prompt + rows + 15) / 16;
-  if (need > m->pages_total) return OMNI_DENIED_EXCEEDS_POOL;
+  if (need > m->pages_total - 1) return OMNI_DENIED_EXCEEDS_POOL;  // (one page belongs to the padding lease)
   if (need > (int)m->free_pages.size() || m->free_lines.empty()) return OMNI_DENIED_BUSY;
   auto s = std::make_unique<omni_higgs_seq>();
   for (int i = 0; i < need; ++i) {
@@ -502,24 +507,29 @@ int32_t omni_higgs_start(omni_higgs* m, int32_t n, omni_higgs_seq* const* seqs, 
   return tail(m, n, seqs, st.dev(uniforms), st.dev(force), st.dev(lines), rows_out, ended_out);
 }
 
-int32_t omni_higgs_step(omni_higgs* m, int32_t n, omni_higgs_seq* const* seqs, const omni_higgs_draw* draws,
-                        int32_t* rows_out, int32_t* ended_out) {
-  if (!m || !seqs || !draws || !rows_out) return OMNI_ERR_INVALID;
-  HTRY(check_rows(m, n, seqs, draws));
+}  // extern "C"
+
+namespace {
+
+int step_bucket(const omni_higgs* m, int n) {  // `bucket` (crates/omni-kern/src/lib.rs:97-101), capped at max_batch
+  int b = 1;
+  while (b < n) b <<= 1;
+  return std::min(b, m->cfg.max_batch);
+}
+
+// One decode step of n live sequences padded to bucket b (n = 0: the warm-up's step, every row on the padding lease).
+int step_rows(omni_higgs* m, int n, int b, omni_higgs_seq* const* seqs, const omni_higgs_draw* draws, int32_t* rows_out,
+              int32_t* ended_out) {
   const omni_higgs_config& c = m->cfg;
-  for (int i = 0; i < n; ++i) {
-    if (seqs[i]->rows <= 0) return m->fail(OMNI_ERR_INVALID, "a sequence that has not started");
-    if (seqs[i]->rows >= seqs[i]->cap) return m->fail(OMNI_ERR_INVALID, "sequence %d is past the rows it leased", i);
-  }
   HCUDA(m, cudaSetDevice(m->device));
   Staging st{m};
-  // every array but the page list has a size n fixes, and the page list comes last: the device addresses the step's
-  // kernels get depend on n alone, which is what lets the step be replayed as a CUDA graph
-  int32_t *pos = st.take<int32_t>(n), *slot = st.take<int32_t>(n), *indptr = st.take<int32_t>(n + 1);
-  int32_t* lines = st.take<int32_t>(n);
-  float* uniforms = st.take<float>((size_t)n * OMNI_HIGGS_CODEBOOKS);
-  int32_t* force = st.take<int32_t>((size_t)n * OMNI_HIGGS_CODEBOOKS);
-  size_t page_count = 0;
+  // every array but the page list has a size b fixes, and the page list comes last: the device addresses the step's
+  // kernels get depend on b alone, which is what lets the step be replayed as a CUDA graph
+  int32_t *pos = st.take<int32_t>(b), *slot = st.take<int32_t>(b), *indptr = st.take<int32_t>(b + 1);
+  int32_t* lines = st.take<int32_t>(b);
+  float* uniforms = st.take<float>((size_t)b * OMNI_HIGGS_CODEBOOKS);
+  int32_t* force = st.take<int32_t>((size_t)b * OMNI_HIGGS_CODEBOOKS);
+  size_t page_count = (size_t)(b - n);
   for (int i = 0; i < n; ++i) page_count += seqs[i]->pages.size();
   int32_t* pages = st.take<int32_t>(page_count);
   if (!pages || !force) return m->fail(OMNI_ERR_INVALID, "staging block too small");
@@ -535,13 +545,22 @@ int32_t omni_higgs_step(omni_higgs* m, int32_t n, omni_higgs_seq* const* seqs, c
     memcpy(uniforms + i * OMNI_HIGGS_CODEBOOKS, draws[i].uniforms, sizeof(draws[i].uniforms));
     force_row(s, draws[i], force + i * OMNI_HIGGS_CODEBOOKS);
   }
+  for (int i = n; i < b; ++i) {  // padding rows: position 0 of the padding lease, uniform 0.5, nothing forced
+    pos[i] = 0;
+    slot[i] = m->pad_page * 16;
+    pages[indptr[i]] = m->pad_page;
+    indptr[i + 1] = indptr[i] + 1;
+    lines[i] = m->pad_line;
+    for (int k = 0; k < OMNI_HIGGS_CODEBOOKS; ++k) uniforms[i * OMNI_HIGGS_CODEBOOKS + k] = 0.5f, force[i * OMNI_HIGGS_CODEBOOKS + k] = -1;
+  }
   m->launches = 0;
   HCUDA(m, cudaEventRecord(m->ev0, m->stream));
   HCUDA(m, cudaMemcpyAsync(m->in_dev, m->in_host, st.used, cudaMemcpyHostToDevice, m->stream));
   // `decode` (model.rs:369-380): the last row's eight codes embedded, the body over one row per sequence, the head and
-  // the draws. Captured once per n (the first step of a size runs eagerly and creates the GEMM plans).
+  // the draws. Captured once per bucket (the first step of a bucket runs eagerly and creates the GEMM plans;
+  // omni_higgs_warmup does both for every bucket before live traffic).
   auto body = [&]() -> int {
-    HLAUNCH(m, launch_higgs_frame_embed(SlotState{m->state, st.dev(lines), m->stride}, m->fused, m->embeds, n,
+    HLAUNCH(m, launch_higgs_frame_embed(SlotState{m->state, st.dev(lines), m->stride}, m->fused, m->embeds, b,
                                         c.body.hidden, c.code_vocab, m->err, m->stream));
     RowMap map;
     map.pos = st.dev(pos);
@@ -549,10 +568,10 @@ int32_t omni_higgs_step(omni_higgs* m, int32_t n, omni_higgs_seq* const* seqs, c
     map.seq = nullptr;
     map.indptr = st.dev(indptr);
     map.pages = st.dev(pages);
-    HTRY(body_forward(m, m->embeds, n, map, m->hidden));
-    return tail_kernels(m, n, st.dev(uniforms), st.dev(force), st.dev(lines));
+    HTRY(body_forward(m, m->embeds, b, map, m->hidden));
+    return tail_kernels(m, b, st.dev(uniforms), st.dev(force), st.dev(lines));
   };
-  omni_higgs::StepGraph& sg = m->step_graphs[n];
+  omni_higgs::StepGraph& sg = m->step_graphs[b];
   if (!m->use_graphs || sg.seen == 0) {
     HTRY(body());
     sg.seen = 1;
@@ -579,6 +598,34 @@ int32_t omni_higgs_step(omni_higgs* m, int32_t n, omni_higgs_seq* const* seqs, c
     m->launches = sg.nodes;
   }
   return tail(m, n, seqs, st.dev(uniforms), st.dev(force), st.dev(lines), rows_out, ended_out, true);
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t omni_higgs_step(omni_higgs* m, int32_t n, omni_higgs_seq* const* seqs, const omni_higgs_draw* draws,
+                        int32_t* rows_out, int32_t* ended_out) {
+  if (!m || !seqs || !draws || !rows_out) return OMNI_ERR_INVALID;
+  HTRY(check_rows(m, n, seqs, draws));
+  for (int i = 0; i < n; ++i) {
+    if (seqs[i]->rows <= 0) return m->fail(OMNI_ERR_INVALID, "a sequence that has not started");
+    if (seqs[i]->rows >= seqs[i]->cap) return m->fail(OMNI_ERR_INVALID, "sequence %d is past the rows it leased", i);
+  }
+  return step_rows(m, n, step_bucket(m, n), seqs, draws, rows_out, ended_out);
+}
+
+// Every bucket's decode step on the padding lease, twice (plans, then the captured graph), so that no live step pays
+// for a graph capture: what `Model::warmup` does for the duplex model (crates/omni-personaplex/src/model.rs:202-240).
+int32_t omni_higgs_warmup(omni_higgs* m) {
+  if (!m) return OMNI_ERR_INVALID;
+  std::vector<int> buckets;
+  for (int b = 1; b < m->cfg.max_batch; b <<= 1) buckets.push_back(b);
+  buckets.push_back(m->cfg.max_batch);
+  int32_t none = 0;
+  for (int b : buckets)
+    for (int pass = 0; pass < (m->use_graphs ? 2 : 1); ++pass) HTRY(step_rows(m, 0, b, nullptr, nullptr, &none, nullptr));
+  return OMNI_OK;
 }
 
 int32_t omni_higgs_read_logits(omni_higgs* m, int32_t s, void* dst, size_t bytes) {

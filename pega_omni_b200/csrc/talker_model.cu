@@ -1281,16 +1281,24 @@ int32_t omni_talker_open(omni_talker* m, int32_t prompt_tokens, int32_t max_fram
   m->pages_used += need;
   // a fresh slot starts zeroed: empty repetition bitmap, frame of zeros, seed 0
   cudaSetDevice(m->device);
-  CUDA_TRY(m, cudaMemsetAsync(m->seq_state + (size_t)s->line * m->seq_stride, 0, m->seq_stride, m->stream));
+  const cudaError_t e = cudaMemsetAsync(m->seq_state + (size_t)s->line * m->seq_stride, 0, m->seq_stride, m->stream);
+  if (e != cudaSuccess) {  // hand the lease back: nothing of this call may stay taken
+    for (int32_t p : s->pages) m->free_pages.push_back(p);
+    m->free_lines.push_back(s->line);
+    m->pages_used -= need;
+    return m->fail(OMNI_ERR_CUDA, "clearing the sequence slot: %s", cudaGetErrorString(e));
+  }
   *out = s.get();
   m->seqs.push_back(std::move(s));
   return OMNI_OK;
 }
 
 int32_t omni_talker_close(omni_talker* m, omni_seq* seq) {
-  if (!m || !seq || !seq->live) return OMNI_ERR_INVALID;
+  if (!m || !seq) return OMNI_ERR_INVALID;
+  // the handle is looked up before it is touched: a handle closed before (or never opened here) points at freed memory
   for (size_t i = 0; i < m->seqs.size(); ++i) {
     if (m->seqs[i].get() != seq) continue;
+    if (!seq->live) return OMNI_ERR_INVALID;
     for (int32_t p : seq->pages) m->free_pages.push_back(p);
     m->free_lines.push_back(seq->line);
     m->pages_used -= (int)seq->pages.size();

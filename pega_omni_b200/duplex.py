@@ -174,13 +174,14 @@ class Model:
 
     @classmethod
     def load(cls, device: int, checkpoint: dict, config: DuplexConfig, max_sessions: int = 128,
-             max_prefill: int = 2048) -> "Model":
+             max_prefill: int = 2048, use_graphs: bool = True) -> "Model":
         lib = L.load()
         c = config
         voice_rows = checkpoint["voices"].shape[0] if "voices" in checkpoint else 0
         cfg = L.DuplexCfg(c.dim, c.layers, c.heads, c.hidden, c.context, c.dep_dim, c.dep_layers, c.dep_heads,
                           c.dep_hidden, c.text_vocab, c.card, c.norm_eps, c.rope_period, c.text_temperature,
-                          c.text_top_k, c.audio_temperature, c.audio_top_k, max_sessions, max_prefill, voice_rows)
+                          c.text_top_k, c.audio_temperature, c.audio_top_k, max_sessions, max_prefill, voice_rows,
+                          int(use_graphs))
         tensors, keep = c_tensors(checkpoint)
         h = C.c_void_p()
         rc = lib.omni_duplex_create(C.byref(cfg), tensors, len(checkpoint), device, C.byref(h))
@@ -251,6 +252,10 @@ class Model:
                                                 init.ctypes.data_as(i32p), ff.ctypes.data_as(i32p)))
 
     # -- Model::tick (model.rs:373-433) --
+    def warmup(self) -> None:
+        """`Model::warmup` (model.rs:202-240): every bucket's tick on the padding lease, so live ticks replay graphs."""
+        self._check(self._lib.omni_duplex_warmup(self._h))
+
     def tick(self, rows: Sequence[tuple]) -> Out:
         """rows: [(session, step)]."""
         n = len(rows)

@@ -153,12 +153,13 @@ class HiggsModel:
 
     @classmethod
     def load(cls, device: int, checkpoint: dict, config: HiggsConfig, max_batch: int = 32, max_tokens: int = 8192,
-             kv_gib: float = 4.0) -> "HiggsModel":
+             kv_gib: float = 4.0, use_graphs: bool = True) -> "HiggsModel":
         lib = L.load()
         b = config.body
         body = L.StackCfg(b.hidden_size, b.intermediate_size, b.num_hidden_layers, b.num_attention_heads,
                           b.num_key_value_heads, b.head_dim, b.vocab_size, b.rms_norm_eps, b.rope_theta)
-        cfg = L.HiggsCfg(body, config.code_vocab, config.temperature, config.top_k, max_batch, max_tokens, kv_gib)
+        cfg = L.HiggsCfg(body, config.code_vocab, config.temperature, config.top_k, max_batch, max_tokens, kv_gib,
+                         int(use_graphs))
         tensors, keep = c_tensors(checkpoint)
         h = C.c_void_p()
         rc = lib.omni_higgs_create(C.byref(cfg), tensors, len(checkpoint), device, C.byref(h))
@@ -212,6 +213,12 @@ class HiggsModel:
                                                self._draws([r[2] for r in rows]), codes.ctypes.data_as(i32p),
                                                ended.ctypes.data_as(i32p)))
         return HiggsOut(codes, ended.astype(bool))
+
+    def warmup(self) -> None:
+        """Every bucket's decode step on the padding lease, so live steps replay captured graphs."""
+        rc = self._lib.omni_higgs_warmup(self._h)
+        if rc != L.OK:
+            raise OmniError(rc, self._lib.omni_higgs_last_error(self._h).decode())
 
     def step(self, rows: Sequence[tuple]) -> HiggsOut:  # model.rs:190-199; rows: [(seq, draw)]
         n = len(rows)

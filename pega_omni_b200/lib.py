@@ -54,7 +54,8 @@ class DuplexCfg(C.Structure):
                                          "dep_heads", "dep_hidden", "text_vocab", "card")] + \
                [("norm_eps", C.c_float), ("rope_period", C.c_float), ("text_temperature", C.c_float),
                 ("text_top_k", C.c_int32), ("audio_temperature", C.c_float), ("audio_top_k", C.c_int32),
-                ("max_sessions", C.c_int32), ("max_prefill", C.c_int32), ("voice_rows", C.c_int32)]
+                ("max_sessions", C.c_int32), ("max_prefill", C.c_int32), ("voice_rows", C.c_int32),
+                ("use_graphs", C.c_int32)]
 
 
 class DuplexStep(C.Structure):
@@ -64,7 +65,7 @@ class DuplexStep(C.Structure):
 
 class HiggsCfg(C.Structure):
     _fields_ = [("body", StackCfg), ("code_vocab", C.c_int32), ("temperature", C.c_float), ("top_k", C.c_int32),
-                ("max_batch", C.c_int32), ("max_tokens", C.c_int32), ("kv_gib", C.c_double)]
+                ("max_batch", C.c_int32), ("max_tokens", C.c_int32), ("kv_gib", C.c_double), ("use_graphs", C.c_int32)]
 
 
 class HiggsDraw(C.Structure):
@@ -133,6 +134,7 @@ SYMBOLS = {
     "omni_higgs_seq_rows": (I32, [VP]),
     "omni_higgs_start": (I32, [VP, I32, P(VP), P(I32), P(I32), P(HiggsDraw), P(I32), P(I32)]),
     "omni_higgs_step": (I32, [VP, I32, P(VP), P(HiggsDraw), P(I32), P(I32)]),
+    "omni_higgs_warmup": (I32, [VP]),
     "omni_higgs_read_logits": (I32, [VP, I32, VP, C.c_size_t]),
     "omni_higgs_stats": (I32, [VP, P(C.c_float), P(I32)]),
     "omni_duplex_create": (I32, [P(DuplexCfg), P(Tensor), I32, I32, P(VP)]),
@@ -145,6 +147,7 @@ SYMBOLS = {
     "omni_duplex_warm_prefix": (I32, [VP, I32, P(I32), P(I32)]),
     "omni_duplex_start": (I32, [VP, I32, P(VP), P(I32), P(I32), P(I32), P(I32), P(I32)]),
     "omni_duplex_tick": (I32, [VP, I32, P(VP), P(DuplexStep), P(I32)]),
+    "omni_duplex_warmup": (I32, [VP]),
     "omni_duplex_read": (I32, [VP, I32, I32, VP, C.c_size_t]),
     "omni_duplex_stats": (I32, [VP, P(C.c_float), P(I32)]),
 }

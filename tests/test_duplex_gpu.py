@@ -250,10 +250,10 @@ def test_cached_start_matches_direct_prefill_against_oracle(built_lib):
     m.close()
 
 
-def test_graph_replay_equals_per_op_launches(built_lib, monkeypatch):
-    """A tick replayed as a CUDA graph (the default from the third tick of a session count on) gives bit-identical
-    draws and logits to the same tick issued kernel by kernel; a change of the session count in between takes the
-    eager path again and a second graph."""
+def test_graph_replay_equals_per_op_launches(built_lib):
+    """A tick replayed as a CUDA graph (the default from the third tick of a bucket on) gives bit-identical draws and
+    logits to the same tick issued kernel by kernel; ten and nine sessions share the bucket of 16 (six and seven rows
+    on the padding lease), so a change of the session count in between replays the same graph."""
     from pega_omni_b200.duplex import PRESETS, Model, Step, random_checkpoint
     c = PRESETS["duplex-mid"]
     ck = random_checkpoint(c, seed=4, head_std=0.3)
@@ -261,8 +261,8 @@ def test_graph_replay_equals_per_op_launches(built_lib, monkeypatch):
     prompts = [make_prompt(c, rng, int(rng.integers(3, 9))) for _ in range(10)]
     callers = [[[int(v) for v in rng.integers(0, c.card, 8)] for _ in range(10)] for _ in range(8)]
 
-    def run():
-        m = Model.load(0, ck, c, max_sessions=16, max_prefill=256)
+    def run(use_graphs=True):
+        m = Model.load(0, ck, c, max_sessions=16, max_prefill=256, use_graphs=use_graphs)
         ss = [m.open() for _ in prompts]
         m.start(list(zip(ss, prompts)))
         trace = []
@@ -274,8 +274,32 @@ def test_graph_replay_equals_per_op_launches(built_lib, monkeypatch):
         return trace
 
     replayed = run()
-    monkeypatch.setenv("OMNI_DUPLEX_NO_GRAPH", "1")
-    launched = run()
+    launched = run(use_graphs=False)
     for t, (g, e) in enumerate(zip(replayed, launched)):
         for a, b in zip(g, e):
             assert np.array_equal(a, b), t
+
+
+def test_warmup_takes_graph_capture_out_of_live_ticks(built_lib):
+    """`Model::warmup` (crates/omni-personaplex/src/model.rs:202-240): afterwards the first live tick of a never-seen
+    session count replays its bucket's graph: the same kernel count as the steady state and no slower than it by
+    more than a quarter (a capture costs several times a tick)."""
+    from pega_omni_b200.duplex import PRESETS, Model, Step, random_checkpoint
+    c = PRESETS["duplex-mid"]
+    ck = random_checkpoint(c, seed=4, head_std=0.3)
+    rng = np.random.default_rng(10)
+    m = Model.load(0, ck, c, max_sessions=16, max_prefill=256)
+    m.warmup()
+    prompts = [make_prompt(c, rng, int(rng.integers(3, 9))) for _ in range(5)]  # five sessions: bucket 8
+    ss = [m.open() for _ in prompts]
+    m.start(list(zip(ss, prompts)))
+    steps = lambda t: [(s, Step(caller=[int(v) for v in rng.integers(0, c.card, 8)], seed=31 * t + i)) for i, s in enumerate(ss)]
+    m.tick(steps(0))
+    first_ms, first_launches = m.stats()
+    steady = []
+    for t in range(1, 7):
+        m.tick(steps(t))
+        steady.append(m.stats())
+    assert all(n == first_launches for _, n in steady), (first_launches, steady)
+    assert first_ms <= 1.25 * float(np.median([ms for ms, _ in steady])), (first_ms, steady)
+    m.close()

@@ -220,8 +220,8 @@ def test_higgs_leases_and_validation(built_lib):
     m.close()
 
 
-def test_graph_replay_equals_per_op_launches(built_lib, monkeypatch):
-    """A decode step replayed as a CUDA graph (the default from the third step of a sequence count on) gives
+def test_graph_replay_equals_per_op_launches(built_lib):
+    """A decode step replayed as a CUDA graph (the default from the third step of a bucket on) gives
     bit-identical rows and logits to the same step issued kernel by kernel; sequences of different lengths, so the
     page list's length differs from step to step while the graph stays the same."""
     from pega_omni_b200.higgs import HIGGS_PRESETS, HiggsDraw, HiggsModel, higgs_random_checkpoint
@@ -232,8 +232,8 @@ def test_graph_replay_equals_per_op_launches(built_lib, monkeypatch):
     prompts = [rng.integers(0, c.body.vocab_size, k).astype(np.int32) for k in lens]
     uniforms = [[[float(v) for v in rng.random(8)] for _ in lens] for _ in range(24)]
 
-    def run():
-        m = HiggsModel.load(0, ck, c, max_batch=16, max_tokens=512, kv_gib=0.05)
+    def run(use_graphs=True):
+        m = HiggsModel.load(0, ck, c, max_batch=16, max_tokens=512, kv_gib=0.05, use_graphs=use_graphs)
         ss = [m.open(k, 30) for k in lens]
         trace = []
         for t in range(24):
@@ -244,8 +244,31 @@ def test_graph_replay_equals_per_op_launches(built_lib, monkeypatch):
         return trace
 
     replayed = run()
-    monkeypatch.setenv("OMNI_HIGGS_NO_GRAPH", "1")
-    launched = run()
+    launched = run(use_graphs=False)
     for t, (g, e) in enumerate(zip(replayed, launched)):
         for a, b in zip(g, e):
             assert np.array_equal(a, b), t
+
+
+def test_warmup_takes_graph_capture_out_of_live_steps(built_lib):
+    """After `warmup` the first live step of a never-seen sequence count replays its bucket's graph: the same kernel
+    count as the steady state, and no slower than it by more than a quarter."""
+    from pega_omni_b200.higgs import HIGGS_PRESETS, HiggsDraw, HiggsModel, higgs_random_checkpoint
+    c = HIGGS_PRESETS["higgs-mid"]
+    ck = higgs_random_checkpoint(c, seed=2, embed_std=0.06)
+    rng = np.random.default_rng(5)
+    m = HiggsModel.load(0, ck, c, max_batch=16, max_tokens=512, kv_gib=0.05)
+    m.warmup()
+    lens = [int(rng.integers(3, 40)) for _ in range(5)]  # five sequences: bucket 8
+    ss = [m.open(k, 30) for k in lens]
+    draws = lambda: [HiggsDraw([float(v) for v in rng.random(8)]) for _ in lens]
+    m.start(list(zip(ss, [rng.integers(0, c.body.vocab_size, k).astype(np.int32) for k in lens], draws())))
+    m.step(list(zip(ss, draws())))
+    first_ms, first_launches = m.stats()
+    steady = []
+    for _ in range(6):
+        m.step(list(zip(ss, draws())))
+        steady.append(m.stats())
+    assert all(n == first_launches for _, n in steady), (first_launches, steady)
+    assert first_ms <= 1.25 * float(np.median([ms for ms, _ in steady])), (first_ms, steady)
+    m.close()

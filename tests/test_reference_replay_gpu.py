@@ -1,9 +1,12 @@
 """Parity against the reference's own CUDA kernels replayed on the same GPU (oracle/ref_kernels.py).
 
 The cubins are compiled from the reference checkout where it is present and travel with the repository; where they
-are missing these tests skip. Two claims: (1) the fused sampler picks bit-identical token ids (and leaves a
+are missing these tests skip. Claims: (1) the fused sampler picks bit-identical token ids (and leaves a
 bit-identical slot) for identical logits, uniforms and state; (2) teacher-forced logits of the whole tick agree
-with the reference's kernels + cuBLAS: cosine >= 0.9999 and max-abs within two bf16 steps (see the comment at the gate)."""
+with the reference's kernels + cuBLAS: cosine >= 0.9999 and max-abs within two bf16 steps (see the comment at the
+gate), on a mid-size shape and on the headline configuration (1.7B shapes, 64 sessions, 128-token prompts);
+(3) measured against the CPU oracle's logits before their bf16 store, this library is no further off than the
+reference's kernels are."""
 import ctypes
 
 import numpy as np
@@ -108,4 +111,136 @@ def test_teacher_forced_logits_match_reference_kernels(built_lib, ref, preset, e
     # magnitude 2..4, where one bf16 step is 0.0156; the gate is two such steps, plus the north-star's cosine.
     assert worst_abs <= 3.2e-2, worst_abs
     assert worst_cos >= 0.9999, worst_cos
+    m.close()
+
+
+def bf16_steps(got, ref):
+    """Largest difference in bf16 steps of the reference value (a step is 2^-7 of its binade; logits below 2 count as 2)."""
+    step = np.exp2(np.floor(np.log2(np.maximum(np.abs(ref), 2.0))) - 7)
+    return float((np.abs(got - ref) / step).max())
+
+
+def test_headline_configuration_matches_reference_kernels(built_lib, ref):
+    """configs[1] as benchmarked: Qwen3-TTS-1.7B shapes, 64 sessions, 128-token prompts, 8 teacher-forced frames
+    through Model.start / Model.step (the persistent tick kernel) and through the reference's kernels: 448 decode
+    frame-rows of talker logits and 448 x 15 rows of predictor logits, forced codes equal.
+
+    What two bf16 pipelines with different f32 summation orders agree to at this depth (28 + 5 layers, every
+    activation rounded to bf16, random weights, logits of magnitude ~1): measured here cosine 0.99984-0.99986 on every
+    talker row (mean and minimum alike: it is the noise floor, not an outlier), 0.9996 at worst on a predictor row,
+    at most 5 bf16 steps on one logit, greedy argmax equal in 96.5 % of the rows with 98 % of the flips near-ties.
+    The mid-size shapes above meet the north-star's 0.9999 / 2e-2; at this size neither this library nor the
+    reference's kernels do against the other, and the test below shows that, against f32 sums, this library's error is
+    the smaller of the two. The gates are set just outside those measurements so that a regression shows."""
+    from pega_omni_b200.config import presets
+    from pega_omni_b200.model import Draw, Limits, Model, Prompt
+    from pega_omni_b200.synthetic import random_checkpoint
+    cfg = presets["qwen3-tts-1.7b"]()
+    ck = random_checkpoint(cfg, seed=0, device="cuda")
+    n, plen, frames = 64, 128, 8
+    m = Model.load(0, ck, cfg, Limits(max_batch=n, max_tokens=32 * plen, kv_gib=1.5))
+    rng = np.random.default_rng(21)
+    prompts = [Prompt(list(rng.integers(0, cfg.text_vocab_size, plen)), [-1] * plen) for _ in range(n)]
+    forced = rng.integers(0, 2048, size=(frames, n, 16)).astype(np.int32)
+    r = ref.RefTalker(cfg, ck, n, plen + frames + 2)
+    del ck
+    seqs = [m.open(plen, frames + 2) for _ in range(n)]
+    uniforms = np.full((n, 16), 0.5, dtype=np.float32)
+    worst_abs, worst_steps, worst_cos, agree, rows, ties = 0.0, 0.0, 1.0, 0, 0, 0
+    cos_by_kind = {"talker": [], "predictor": []}
+    for t in range(frames):
+        draws = [Draw([0.5] * 16, list(forced[t, s])) for s in range(n)]
+        if t == 0:
+            for i in range(0, n, 32):  # prefill in calls of 32 prompts
+                ours_part = m.start(list(zip(seqs[i:i + 32], prompts[i:i + 32], draws[i:i + 32]))).codes
+                assert np.array_equal(ours_part, forced[t, i:i + 32])
+            theirs = r.start(prompts, uniforms, forced[t])
+            assert np.array_equal(theirs, forced[t])
+            # the first frame's logits come from the prefill pass on both sides; compare the decode ticks below
+            continue
+        ours = m.step(list(zip(seqs, draws))).codes
+        theirs = r.step(uniforms, forced[t])
+        assert np.array_equal(ours, theirs) and np.array_equal(ours, forced[t])
+        for s in range(n):
+            pairs = [(m.talker_logits(s), r.talker_logits(s))] + list(zip(m.predictor_logits(s), r.predictor_logits(s)))
+            for k, (a, b) in enumerate(pairs):
+                worst_abs = max(worst_abs, float(np.abs(a - b).max()))
+                worst_steps = max(worst_steps, bf16_steps(a, b))
+                worst_cos = min(worst_cos, cosine(a, b))
+                cos_by_kind["talker" if k == 0 else "predictor"].append(cosine(a, b))
+                rows += 1
+                if int(np.argmax(a)) == int(np.argmax(b)):
+                    agree += 1
+                else:  # a flip must be a near-tie: the reference's own top two within two bf16 steps
+                    top2 = np.sort(b)[-2:]
+                    ties += int((top2[1] - top2[0]) <= 2 * np.exp2(np.floor(np.log2(max(abs(top2[1]), 2.0))) - 7))
+    summary = (f"headline parity vs reference kernels: {rows} rows, worst |d| {worst_abs:.4f} = {worst_steps:.2f} bf16 steps, "
+               f"cosine talker min {min(cos_by_kind['talker']):.6f} mean {np.mean(cos_by_kind['talker']):.6f}, predictor min "
+               f"{min(cos_by_kind['predictor']):.6f} mean {np.mean(cos_by_kind['predictor']):.6f}, argmax equal {agree}/{rows}, "
+               f"flips that are near-ties {ties}/{rows - agree}")
+    print(summary)
+    import os
+    if os.path.isdir("gpurun_out"):
+        open("gpurun_out/headline_parity.txt", "w").write(summary + "\n")
+    assert min(cos_by_kind["talker"]) >= 0.9997 and min(cos_by_kind["predictor"]) >= 0.9994, worst_cos
+    assert np.mean(cos_by_kind["talker"]) >= 0.9998 and np.mean(cos_by_kind["predictor"]) >= 0.9998
+    assert worst_steps <= 6.0, (worst_steps, worst_abs)
+    assert agree / rows >= 0.95, (agree, rows)
+    assert ties >= 0.95 * (rows - agree), (ties, rows - agree)
+    m.close()
+
+
+@pytest.mark.parametrize("preset,lens,frames,limit", [("mid", [9, 33, 17, 26], 6, 2.4e-2),
+                                                      ("qwen3-tts-1.7b", [16, 11, 16, 7], 3, 8e-2)])
+def test_error_against_unrounded_logits_is_not_larger_than_the_reference_kernels(built_lib, oracle_lib, ref, preset, lens,
+                                                                                 frames, limit):
+    """Why the max-abs gates above are in bf16 steps and not the north-star's 2e-2: both GPU paths store logits as
+    bf16 and sum in different orders. Against the CPU oracle's logits *before* that store (same rounding points
+    everywhere else, f32 sums): this library's worst error is no larger than the error of the reference's kernels
+    (+ a quarter of a bf16 step of slack for the comparison of two maxima), on the mid shapes (measured 0.0204 against
+    0.0268) and on the full-size shapes with four short sessions (what the CPU oracle finishes in seconds)."""
+    from pega_omni_b200.config import presets
+    from pega_omni_b200.model import Draw, Limits, Model, Prompt
+    from pega_omni_b200.synthetic import random_checkpoint
+    cfg = presets[preset]()
+    ck = random_checkpoint(cfg, seed=3, device="cuda")
+    m = Model.load(0, ck, cfg, Limits(max_batch=8, max_tokens=256, kv_gib=0.05))
+    oracle_lib.load().orc_round_logits(0)
+    try:
+        o = oracle_lib.CpuOracle(cfg, ck)
+        rng = np.random.default_rng(12)
+        prompts = [Prompt(list(rng.integers(0, cfg.text_vocab_size, k)), [-1] * k) for k in lens]
+        forced = rng.integers(0, 2048, size=(frames, len(lens), 16)).astype(np.int32)
+        r = ref.RefTalker(cfg, ck, len(lens), max(lens) + frames + 2)
+        seqs = [m.open(k, frames + 2) for k in lens]
+        sids = [o.open(k, frames + 2) for k in lens]
+        uniforms = np.full((len(lens), 16), 0.5, dtype=np.float32)
+        err_ours, err_ref = 0.0, 0.0
+        for t in range(frames):
+            draws = [Draw([0.5] * 16, list(forced[t, s])) for s in range(len(lens))]
+            if t == 0:
+                m.start(list(zip(seqs, prompts, draws)))
+                r.start(prompts, uniforms, forced[t])
+                o.start(sids, prompts, draws)
+            else:
+                m.step(list(zip(seqs, draws)))
+                r.step(uniforms, forced[t])
+                o.step(sids, draws)
+            for s in range(len(lens)):
+                truth = [o.talker_logits(s)] + list(o.predictor_logits(s))
+                mine = [m.talker_logits(s)] + list(m.predictor_logits(s))
+                theirs = [r.talker_logits(s)] + list(r.predictor_logits(s))
+                for tr, a, b in zip(truth, mine, theirs):
+                    err_ours = max(err_ours, float(np.abs(a - tr).max()))
+                    err_ref = max(err_ref, float(np.abs(b - tr).max()))
+        line = f"{preset}: worst |logit - unrounded oracle logit|: this library {err_ours:.4f}, reference kernels {err_ref:.4f}"
+        print(line)
+        import os
+        if os.path.isdir("gpurun_out"):
+            open("gpurun_out/unrounded_parity.txt", "a").write(line + "\n")
+        assert err_ours <= limit, err_ours
+        assert err_ours <= err_ref + 0.004, (err_ours, err_ref)
+        o.close()
+    finally:
+        oracle_lib.load().orc_round_logits(1)
     m.close()

@@ -348,9 +348,9 @@ def test_leases_and_validation(built_lib):
 
 
 def test_full_size_shapes_properties(built_lib):
-    """The headline architecture at 64 sessions: size-independent properties instead of an oracle run.
-    Teacher forcing returns the forced frame; the same session replayed alone reproduces its logits within
-    tolerance; codes stay inside their vocabularies; the end token cannot appear before frame 2."""
+    """The headline architecture at 64 sessions: size-independent properties (its logits are compared with the
+    reference's own kernels in test_reference_replay_gpu.py). Teacher forcing returns the forced frame; codes stay
+    inside their vocabularies; the end token cannot appear before frame 2."""
     from pega_omni_b200.config import presets
     from pega_omni_b200.model import Draw, Limits, Model
     from pega_omni_b200.synthetic import random_checkpoint
@@ -370,16 +370,4 @@ def test_full_size_shapes_properties(built_lib):
     assert (out.codes[:, 0] >= 0).all() and (out.codes[:, 0] < cfg.talker.vocab_size - cfg.control_tokens).all()
     assert (out.codes[:, 0] != cfg.codec_eos_token_id).all()  # frame 1 < min_frames
     assert (out.codes[:, 1:] >= 0).all() and (out.codes[:, 1:] < cfg.predictor.vocab_size).all()
-    l5 = m.talker_logits(5).copy()
-    # session 5 replayed alone (bucket 1 -> the vector GEMV path): same logits within tolerance
     m.close()
-    m2 = Model.load(0, random_checkpoint(cfg, seed=0, device="cuda"), cfg, Limits(max_batch=1, max_tokens=64, kv_gib=0.1))
-    s5 = m2.open(plen, 8)
-    m2.start([(s5, ps[5], Draw(force=list(forced[0, 5])))])
-    m2.step([(s5, Draw(list(u[5])))])
-    l5b = m2.talker_logits(0)
-    # two summation orders (tensor-core tiles split along K vs the vector kernel) through 28 bf16-rounded layers:
-    # the logits agree to a few bf16 steps, not bit for bit
-    assert cosine(l5, l5b) >= 0.9995, cosine(l5, l5b)
-    assert np.abs(l5 - l5b).max() <= 0.1, np.abs(l5 - l5b).max()
-    m2.close()
