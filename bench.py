@@ -409,6 +409,7 @@ def main():
                     help="talker: the headline Qwen3-TTS tick (default); duplex: the PersonaPlex-7B tick (configs[3]); "
                          "higgs: the Higgs-style 4B step (configs[4])")
     ap.add_argument("--context", type=int, default=3000, help="duplex: KV ring length")
+    ap.add_argument("--trace", default=None, help="talker: write the tick kernel's per-phase device timestamps here")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -445,6 +446,8 @@ def main():
     kv_gib = max(1.0, 1.25 * args.sessions * (args.prompt + frames_cap + 16) * cfg.talker.kv_bytes_per_token() / 2 ** 30)
     model = Model.load(local, ck, cfg, Limits(args.sessions, args.sessions * args.prompt, kv_gib),
                        use_graphs=not args.no_graphs, tick_kernel=not args.per_op)
+    if args.trace:
+        model.trace(args.trace)
     ck_host = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         ck_host = {k: v.cpu() for k, v in ck.items()}

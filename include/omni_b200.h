@@ -168,6 +168,12 @@ int32_t omni_talker_read(omni_talker* m, int32_t buffer, int32_t s, void* dst, s
 /* `Model::is_end` (model.rs:148-150). */
 int32_t omni_talker_is_end(const omni_talker* m, const int32_t* frame);
 int32_t omni_talker_stats(omni_talker* m, omni_stats* out);
+/* A measurement aid with no counterpart in the reference (which is profiled with nsys from outside): names a text
+ * file that receives, after every omni_talker_run_ticks call, the per-phase device timestamps of the call's last tick
+ * (one line per phase of the persistent kernel: its shape, its barrier-to-barrier time, and when the first operand
+ * tile, the first accumulator, the CTA's share and the barrier were reached, median and latest over the CTAs, in
+ * ns). NULL or "" switches it off. The stamps cost about 1 % of a tick. */
+int32_t omni_talker_trace(omni_talker* m, const char* path);
 const char* omni_talker_last_error(const omni_talker* m);
 /* `omni_kern::bucket` (crates/omni-kern/src/lib.rs:31-36). */
 int32_t omni_bucket(int32_t n);

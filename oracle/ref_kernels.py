@@ -23,7 +23,8 @@ from pathlib import Path
 
 HERE = Path(__file__).resolve().parent
 OUT = HERE / "_ref"
-REFERENCE = Path(os.environ.get("OMNI_REFERENCE", "/root/reference"))
+# the reference checkout: named by OMNI_REFERENCE, else looked for beside this repository's checkout
+REFERENCE = Path(os.environ.get("OMNI_REFERENCE") or HERE.parent.parent / "reference")
 SOURCES = {
     "qwen3": "crates/omni-qwen3/kernels/qwen3.cu",
     "talker": "crates/omni-qwen3-tts/kernels/talker.cu",

@@ -5,10 +5,11 @@
 
 #include "duplex.h"
 
+#include "sm100.cuh"
+
 namespace omni {
 namespace {
 
-constexpr int kAttendWarps = 4;
 
 __device__ __forceinline__ const int32_t* state_row(const void* state, const int32_t* lines, int s, int64_t stride) {
   return reinterpret_cast<const int32_t*>(static_cast<const char*>(state) + (int64_t)lines[s] * stride);
@@ -106,66 +107,61 @@ __device__ __forceinline__ uint8_t* page_head(void* kv, int64_t page, int heads,
 
 __device__ __forceinline__ float e4m3_scale(float amax) { return fmaxf(amax * (1.f / 448.f), 1e-12f); }
 
-// `lm_rope` (lm.cu:129-184): a warp per head of the row.
-__global__ void lm_rope_kv_kernel(bf16* __restrict__ qkv, const int32_t* __restrict__ pos,
-                                  const int32_t* __restrict__ slots, void* kv, int heads, float coef, int kv_pages,
-                                  uint32_t* err) {
-  const int n = blockIdx.x;
-  const int head = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (head >= 3 * heads) return;
-  const int lane = threadIdx.x & 31;
-  bf16* src = qkv + ((int64_t)n * 3 * heads + head) * kHeliumHeadDim;
-  const float p = (float)pos[n];
+// Interleaved rotary embedding + FP8 KV write of one row (value semantics of `lm_rope`, lm.cu:129-184). kRopeParts
+// CTAs per row: the 64 rotation angles depend on the row's position alone, so a CTA computes them once into shared
+// memory (freq_i = expf(i * coef), sincosf(freq_i * pos)) for all the heads it rotates; its eight warps then walk
+// its share of the 3 * heads heads, a lane owning four consecutive elements of the head (two rotation pairs): one
+// 8-byte load, and for k / v one 4-byte FP8 store. k and v are quantised per head to E4M3 with the scale
+// max(amax / 448, 1e-12), kept as f32 beside the page's values.
+constexpr int kRopeWarps = 8, kRopeParts = 4;
+
+__global__ void __launch_bounds__(kRopeWarps * 32)
+    lm_rope_kv_kernel(bf16* __restrict__ qkv, const int32_t* __restrict__ pos, const int32_t* __restrict__ slots, void* kv,
+                      int heads, float coef, int kv_pages, uint32_t* err) {
+  __shared__ float cs[kHeliumHeadDim / 2], sn[kHeliumHeadDim / 2];
+  const int n = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (threadIdx.x < kHeliumHeadDim / 2) {
+    const float freq = expf((float)threadIdx.x * coef);
+    sincosf(freq * (float)pos[n], &sn[threadIdx.x], &cs[threadIdx.x]);
+  }
   int64_t slot = slots[n];
   if (slot < 0 || (slot >> 4) >= kv_pages) {
-    if (lane == 0) raise(err, kErrBadIndex);
+    if (threadIdx.x == 0) raise(err, kErrBadIndex);
     slot = 0;
   }
   const int tok = (int)(slot & 15);
-  if (head < 2 * heads) {
-    float out_r[2], out_i[2];
+  __syncthreads();
+  for (int head = blockIdx.y * kRopeWarps + warp; head < 3 * heads; head += kRopeWarps * kRopeParts) {
+    bf16* src = qkv + ((int64_t)n * 3 * heads + head) * kHeliumHeadDim + lane * 4;
+    const uint2 raw = *reinterpret_cast<const uint2*>(src);
+    const float2 p0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+    const float2 p1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+    float v[4] = {p0.x, p0.y, p1.x, p1.y};
+    if (head < 2 * heads) {  // q and k: pairs (2i, 2i + 1) rotated by angle i
 #pragma unroll
-    for (int k = 0; k < 2; ++k) {
-      const int i = lane + k * 32;
-      const float freq = expf((float)i * coef);
-      float s, c;
-      sincosf(freq * p, &s, &c);
-      const __nv_bfloat162 pair = *reinterpret_cast<const __nv_bfloat162*>(src + 2 * i);
-      const float r = __bfloat162float(pair.x), im = __bfloat162float(pair.y);
-      out_r[k] = r * c - im * s;
-      out_i[k] = r * s + im * c;
+      for (int k = 0; k < 2; ++k) {
+        const float c = cs[2 * lane + k], sv = sn[2 * lane + k];
+        const float r = v[2 * k], im = v[2 * k + 1];
+        v[2 * k] = r * c - im * sv;
+        v[2 * k + 1] = r * sv + im * c;
+      }
     }
     if (head < heads) {  // q: rounded to bf16 in place
-#pragma unroll
-      for (int k = 0; k < 2; ++k)
-        *reinterpret_cast<__nv_bfloat162*>(src + 2 * (lane + k * 32)) = __floats2bfloat162_rn(out_r[k], out_i[k]);
-      return;
+      uint2 o;
+      *reinterpret_cast<__nv_bfloat162*>(&o.x) = __floats2bfloat162_rn(v[0], v[1]);
+      *reinterpret_cast<__nv_bfloat162*>(&o.y) = __floats2bfloat162_rn(v[2], v[3]);
+      *reinterpret_cast<uint2*>(src) = o;
+      continue;
     }
-    const int h = head - heads;
-    const float amax = warp_fmax(fmaxf(fmaxf(fabsf(out_r[0]), fabsf(out_i[0])), fmaxf(fabsf(out_r[1]), fabsf(out_i[1]))));
-    const float sc = e4m3_scale(amax), inv = 1.f / sc;
-    uint8_t* block = page_head(kv, slot >> 4, heads, h);
-    uint8_t* dst = block + tok * kHeliumHeadDim;
-#pragma unroll
-    for (int k = 0; k < 2; ++k)
-      *reinterpret_cast<__nv_fp8x2_storage_t*>(dst + 2 * (lane + k * 32)) =
-          __nv_cvt_float2_to_fp8x2(make_float2(out_r[k] * inv, out_i[k] * inv), __NV_SATFINITE, __NV_E4M3);
-    if (lane == 0) reinterpret_cast<float*>(block + 2 * 16 * kHeliumHeadDim)[tok] = sc;
-  } else {
-    const int h = head - 2 * heads;
-    float v[4];
-    const uint2 raw = *reinterpret_cast<const uint2*>(src + lane * 4);
-    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
-    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
-    v[0] = a.x, v[1] = a.y, v[2] = b.x, v[3] = b.y;
+    const bool is_v = head >= 2 * heads;
+    const int h = head - (is_v ? 2 : 1) * heads;
     const float amax = warp_fmax(fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3]))));
     const float sc = e4m3_scale(amax), inv = 1.f / sc;
     uint8_t* block = page_head(kv, slot >> 4, heads, h);
-    uint8_t* dst = block + (16 + tok) * kHeliumHeadDim + lane * 4;
     const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(v[0] * inv, v[1] * inv), __NV_SATFINITE, __NV_E4M3);
     const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(v[2] * inv, v[3] * inv), __NV_SATFINITE, __NV_E4M3);
-    *reinterpret_cast<uint32_t*>(dst) = lo | hi << 16;
-    if (lane == 0) reinterpret_cast<float*>(block + 2 * 16 * kHeliumHeadDim + 64)[tok] = sc;
+    *reinterpret_cast<uint32_t*>(block + ((is_v ? 16 : 0) + tok) * kHeliumHeadDim + lane * 4) = lo | hi << 16;
+    if (lane == 0) reinterpret_cast<float*>(block + 2 * 16 * kHeliumHeadDim + (is_v ? 64 : 0))[tok] = sc;
   }
 }
 
@@ -173,84 +169,127 @@ __device__ __forceinline__ float4 e4m3x4(uint32_t raw) {
   return static_cast<float4>(*reinterpret_cast<const __nv_fp8x4_e4m3*>(&raw));
 }
 
-// `lm_attend` / `attend_row_fp8` (lm.cu:197-290): a CTA per (row, head), four warps over tiles of 32 ring positions
-// (a lane owns a key for the scores, then four output dims for the values), online softmax per warp, merged at the end.
+// Decode attention over the FP8 ring (value semantics of `lm_attend` / `attend_row_fp8`, lm.cu:197-290: f32 scores,
+// score * (k_scale * scale), __expf, p * v_scale, bf16 out). One CTA per (row, head), four warps. A (page, head) block
+// is 4,224 contiguous bytes (16 keys, 16 values, their scales), so a warp stages whole pages into its own two
+// shared-memory slots with one bulk copy each (cp.async.bulk, completion on an mbarrier) and has the next page under
+// way while it works on the current one. Inside a page a lane scores half a key (64 of the 128 FP8 dims; lanes t and
+// t + 16 share key t), the online softmax advances one page (16 keys) at a time, then every lane adds its four output
+// dims of the 16 values. The warps' states are merged at the end. Waits are bounded (the error word, then out).
+constexpr int kAttendWarps = 4;
+constexpr int kAttendSlotBytes = ((kDuplexPageHeadBytes + 127) / 128) * 128;
+
+struct AttendShared {
+  float q[kHeliumHeadDim];
+  float ms[kAttendWarps], ls[kAttendWarps];
+  float os[kAttendWarps][kHeliumHeadDim];
+  uint64_t bar[kAttendWarps][2];
+};
+
 __global__ void __launch_bounds__(kAttendWarps * 32)
     lm_attend_kernel(const bf16* __restrict__ qkv, const void* kv, const int32_t* __restrict__ pos,
                      const int32_t* __restrict__ seq, const int32_t* __restrict__ indptr,
                      const int32_t* __restrict__ pages, bf16* __restrict__ out, int heads, float scale, int context,
                      int kv_pages, uint32_t* err) {
+  extern __shared__ __align__(128) unsigned char attend_smem[];
+  AttendShared& sh = *reinterpret_cast<AttendShared*>(attend_smem);
+  unsigned char* slots = attend_smem + ((sizeof(AttendShared) + 127) & ~(size_t)127);
   const int n = blockIdx.x, h = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int s = seq ? seq[n] : n;
-  const int len = min(pos[n] + 1, context);
+  const int len = min(pos[n] + 1, context), npages = (len + 15) >> 4;
   const int32_t* my_pages = pages + indptr[s];
-  __shared__ float qs[kHeliumHeadDim];
-  __shared__ float ms[kAttendWarps], ls[kAttendWarps];
-  __shared__ float os[kAttendWarps][kHeliumHeadDim];
-  qs[threadIdx.x] = __bfloat162float(qkv[((int64_t)n * 3 * heads + h) * kHeliumHeadDim + threadIdx.x]);
+  if (threadIdx.x < kHeliumHeadDim)
+    sh.q[threadIdx.x] = __bfloat162float(qkv[((int64_t)n * 3 * heads + h) * kHeliumHeadDim + threadIdx.x]);
+  if (lane == 0) {
+    sm100::mbar_init(sm100::smem_addr(&sh.bar[warp][0]), 1);
+    sm100::mbar_init(sm100::smem_addr(&sh.bar[warp][1]), 1);
+  }
+  sm100::mbar_init_fence();
   __syncthreads();
-  float m = -INFINITY, l = 0.f, acc[4] = {0.f, 0.f, 0.f, 0.f};
-  for (int base = warp * 32; base < len; base += kAttendWarps * 32) {
-    const int t = base + lane;
-    const bool valid = t < len;
-    const int tt = valid ? t : base;
-    int64_t page = my_pages[tt >> 4];
+
+  unsigned char* mine = slots + (size_t)warp * 2 * kAttendSlotBytes;
+  auto fetch = [&](int pi, int slot) {  // lane 0: one bulk copy of page pi's block for this head
+    int64_t page = my_pages[pi];
     if (page < 0 || page >= kv_pages) {
       raise(err, kErrBadIndex);
       page = 0;
     }
-    const uint8_t* block = page_head(const_cast<void*>(kv), page, heads, h);
-    const int tok = tt & 15;
-    const uint8_t* k = block + tok * kHeliumHeadDim;
-    const float ks = reinterpret_cast<const float*>(block + 2 * 16 * kHeliumHeadDim)[tok];
-    const float vs = reinterpret_cast<const float*>(block + 2 * 16 * kHeliumHeadDim + 64)[tok];
-    float sc = 0.f;
-#pragma unroll 2
-    for (int c = 0; c < kHeliumHeadDim; c += 16) {
-      const uint4 raw = *reinterpret_cast<const uint4*>(k + c);
-      const float4 k0 = e4m3x4(raw.x), k1 = e4m3x4(raw.y), k2 = e4m3x4(raw.z), k3 = e4m3x4(raw.w);
-      sc += qs[c + 0] * k0.x + qs[c + 1] * k0.y + qs[c + 2] * k0.z + qs[c + 3] * k0.w + qs[c + 4] * k1.x +
-            qs[c + 5] * k1.y + qs[c + 6] * k1.z + qs[c + 7] * k1.w;
-      sc += qs[c + 8] * k2.x + qs[c + 9] * k2.y + qs[c + 10] * k2.z + qs[c + 11] * k2.w + qs[c + 12] * k3.x +
-            qs[c + 13] * k3.y + qs[c + 14] * k3.z + qs[c + 15] * k3.w;
+    const uint32_t bar = sm100::smem_addr(&sh.bar[warp][slot]);
+    sm100::mbar_expect_tx(bar, kDuplexPageHeadBytes);
+    sm100::bulk_load(sm100::smem_addr(mine + (size_t)slot * kAttendSlotBytes),
+                     page_head(const_cast<void*>(kv), page, heads, h), kDuplexPageHeadBytes, bar);
+  };
+  float m = -INFINITY, l = 0.f, acc[4] = {0.f, 0.f, 0.f, 0.f};
+  const int tok = lane & 15, half = lane >> 4;
+  if (warp < npages && lane == 0) fetch(warp, 0);
+  uint32_t parity[2] = {0, 0};
+  int slot = 0;
+  for (int pi = warp; pi < npages; pi += kAttendWarps, slot ^= 1) {
+    if (pi + kAttendWarps < npages && lane == 0) fetch(pi + kAttendWarps, slot ^ 1);  // (that slot was read a round ago)
+    if (!sm100::mbar_wait(sm100::smem_addr(&sh.bar[warp][slot]), parity[slot], err)) break;
+    parity[slot] ^= 1u;
+    const unsigned char* blk = mine + (size_t)slot * kAttendSlotBytes;
+    const int ntok = min(16, len - pi * 16);
+    float dot = 0.f;
+    {
+      const uint4* krow = reinterpret_cast<const uint4*>(blk + tok * kHeliumHeadDim + half * 64);
+      const float* qh = sh.q + half * 64;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const uint4 raw = krow[c];
+        const float4 k0 = e4m3x4(raw.x), k1 = e4m3x4(raw.y), k2 = e4m3x4(raw.z), k3 = e4m3x4(raw.w);
+        const float* qc = qh + c * 16;
+        dot += qc[0] * k0.x + qc[1] * k0.y + qc[2] * k0.z + qc[3] * k0.w + qc[4] * k1.x + qc[5] * k1.y + qc[6] * k1.z +
+               qc[7] * k1.w;
+        dot += qc[8] * k2.x + qc[9] * k2.y + qc[10] * k2.z + qc[11] * k2.w + qc[12] * k3.x + qc[13] * k3.y +
+               qc[14] * k3.z + qc[15] * k3.w;
+      }
     }
-    const float sv = valid ? sc * (ks * scale) : -INFINITY;
+    dot += __shfl_xor_sync(0xffffffffu, dot, 16);  // both halves of key `tok`
+    const float ks = reinterpret_cast<const float*>(blk + 2 * 16 * kHeliumHeadDim)[tok];
+    const float vs = reinterpret_cast<const float*>(blk + 2 * 16 * kHeliumHeadDim + 64)[tok];
+    const float sv = tok < ntok ? dot * (ks * scale) : -INFINITY;
     const float m2 = fmaxf(m, warp_fmax(sv));
     const float corr = __expf(m - m2);
     const float p = __expf(sv - m2);
-    l = l * corr + warp_add(p);
+    float psum = p;  // over the 16 keys (both half-warps hold the same values)
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) psum += __shfl_xor_sync(0xffffffffu, psum, o);
+    l = l * corr + psum;
 #pragma unroll
     for (int d = 0; d < 4; ++d) acc[d] *= corr;
     m = m2;
-    const float pv = p * vs;
-    const int64_t vrow = (block - static_cast<const uint8_t*>(kv)) + (16 + tok) * kHeliumHeadDim;
-    const int count = min(32, len - base);
-    for (int j = 0; j < count; ++j) {
-      const int64_t vj = __shfl_sync(0xffffffffu, vrow, j);
-      const float pvj = __shfl_sync(0xffffffffu, pv, j);
-      const float4 vf = e4m3x4(*reinterpret_cast<const uint32_t*>(static_cast<const uint8_t*>(kv) + vj + lane * 4));
-      acc[0] += pvj * vf.x, acc[1] += pvj * vf.y, acc[2] += pvj * vf.z, acc[3] += pvj * vf.w;
+    const float pv = p * vs;  // 0 for keys past the row's length
+    const uint32_t* vrows = reinterpret_cast<const uint32_t*>(blk + 16 * kHeliumHeadDim) + lane;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      const float pj = __shfl_sync(0xffffffffu, pv, j);
+      const float4 vf = e4m3x4(vrows[j * (kHeliumHeadDim / 4)]);
+      acc[0] += pj * vf.x, acc[1] += pj * vf.y, acc[2] += pj * vf.z, acc[3] += pj * vf.w;
     }
+    __syncwarp();  // every lane is done with this slot before lane 0 refills it in the next round
   }
   if (lane == 0) {
-    ms[warp] = m;
-    ls[warp] = l;
+    sh.ms[warp] = m;
+    sh.ls[warp] = l;
   }
 #pragma unroll
-  for (int d = 0; d < 4; ++d) os[warp][lane * 4 + d] = acc[d];
+  for (int d = 0; d < 4; ++d) sh.os[warp][lane * 4 + d] = acc[d];
   __syncthreads();
-  const int d = threadIdx.x;
-  float top = -INFINITY;
+  if (threadIdx.x < kHeliumHeadDim) {
+    const int d = threadIdx.x;
+    float top = -INFINITY;
 #pragma unroll
-  for (int w = 0; w < kAttendWarps; ++w) top = fmaxf(top, ms[w]);
-  float num = 0.f, den = 0.f;
+    for (int w = 0; w < kAttendWarps; ++w) top = fmaxf(top, sh.ms[w]);
+    float num = 0.f, den = 0.f;
 #pragma unroll
-  for (int w = 0; w < kAttendWarps; ++w) {
-    const float e = ms[w] == -INFINITY ? 0.f : __expf(ms[w] - top);
-    num += os[w][d] * e;
-    den += ls[w] * e;
+    for (int w = 0; w < kAttendWarps; ++w) {
+      const float e = sh.ms[w] == -INFINITY ? 0.f : __expf(sh.ms[w] - top);
+      num += sh.os[w][d] * e;
+      den += sh.ls[w] * e;
+    }
+    out[((int64_t)n * heads + h) * kHeliumHeadDim + d] = __float2bfloat16(num / den);
   }
-  out[((int64_t)n * heads + h) * kHeliumHeadDim + d] = __float2bfloat16(num / den);
 }
 
 // `lm_dep_embed_norm` (lm.cu:301-313)
@@ -310,20 +349,31 @@ __global__ void lm_dep_kv_attend_kernel(const bf16* __restrict__ qkv, bf16* __re
   *reinterpret_cast<__nv_bfloat162*>(out + (int64_t)s * width + at) = __floats2bfloat162_rn(a0 * inv_l, a1 * inv_l);
 }
 
-// ---- Gumbel-max draw over the top-k (lm.cu:368-537) ----------------------------------------------------------
-// Every element's score depends only on (logit, seed, index): key = 16-bit order key of the bf16 logit, the k-th
-// largest key found by a two-pass radix select (ties kept), score = logit / T - log(-log u) with
-// u = ((mix(seed ^ mix(index)) >> 8) + 0.5) / 2^24, winner = largest (order_key(score), lowest index).
+// ---- Gumbel-max draw over the top-k (value semantics of `lm_sample`, lm.cu:368-537) ----------------------------
+// Every element's score depends only on (logit, seed, index): key = 16-bit order key of the bf16 logit, the cut is
+// the k-th largest key (ties kept), score = logit / T - log(-log u) with u = ((mix(seed ^ mix(index)) >> 8) + 0.5) /
+// 2^24, winner = largest (order_key(score), lowest index).
+//
+// One CTA of 1024 threads per row. The row is read from memory ONCE: every thread keeps its share of the keys in
+// registers (two per register, up to 64 per thread = a vocabulary of 65,536). The cut is then found by bisection on
+// the key's 16 bits, most significant first: a bit stays set when at least k keys are >= the candidate, which takes
+// one count per round over registers, a shuffle sum per warp and one block barrier (the per-warp counts are
+// double-buffered in shared memory, so a round needs no second barrier). The survivors' scores are computed from the
+// same registers and the winner is reduced by shuffles and one pass over the 32 warp results.
 
 constexpr int kSampleThreads = 1024;
+constexpr int kSampleRegs = 32;  // packed key pairs per thread
 
 __device__ __forceinline__ uint32_t order_key32(float v) {
   const uint32_t u = __float_as_uint(v);
   return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
 }
-__device__ __forceinline__ uint32_t order_key16(bf16 v) {
-  const uint16_t u = *reinterpret_cast<const uint16_t*>(&v);
-  return (u & 0x8000u) ? (uint16_t)~u : (uint16_t)(u | 0x8000u);
+__device__ __forceinline__ uint32_t order_key16(uint32_t bits) {  // bits: a bf16 in the low half
+  return (bits & 0x8000u) ? (~bits & 0xffffu) : (bits | 0x8000u);
+}
+__device__ __forceinline__ float logit_of(uint32_t key) {  // the inverse of order_key16
+  const uint32_t bits = (key & 0x8000u) ? (key & 0x7fffu) : (~key & 0xffffu);
+  return __uint_as_float(bits << 16);
 }
 __device__ __forceinline__ uint32_t mix32(uint32_t x) {
   x ^= x >> 16;
@@ -338,78 +388,77 @@ __global__ void __launch_bounds__(kSampleThreads)
     lm_sample_kernel(const bf16* __restrict__ logits, int vocab, int64_t ld, float temperature, int top_k,
                      const int32_t* __restrict__ force, const int32_t* __restrict__ seeds, int col,
                      int32_t* __restrict__ drawn) {
-  const int s = blockIdx.x, tid = threadIdx.x;
-  __shared__ uint32_t hist[256];
-  __shared__ uint32_t sel_prefix, sel_left;
-  __shared__ unsigned long long best;
+  const int s = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  __shared__ uint32_t counts[2][kSampleThreads / 32];
+  __shared__ unsigned long long best[kSampleThreads / 32];
   const int forced = force[s * kDuplexDrawn + col];
   if (forced >= 0) {
     if (tid == 0) drawn[s * kDuplexDrawn + col] = forced;
     return;
   }
-  const bf16* l = logits + (int64_t)s * ld;
+  // element 2 * (r * 1024 + tid) + {0, 1} lives in the low / high half of reg[r]; 0 past the vocabulary (the smallest
+  // key there is: -NaN with every mantissa bit set orders lowest, and no count ever includes index >= vocab)
+  const uint16_t* row = reinterpret_cast<const uint16_t*>(logits + (int64_t)s * ld);
+  uint32_t reg[kSampleRegs];
+#pragma unroll
+  for (int r = 0; r < kSampleRegs; ++r) {
+    const int i = 2 * (r * kSampleThreads + tid);
+    const uint32_t k0 = i < vocab ? order_key16(row[i]) : 0u, k1 = i + 1 < vocab ? order_key16(row[i + 1]) : 0u;
+    reg[r] = k0 | k1 << 16;
+  }
   const float inv_t = temperature > 0.f ? 1.f / temperature : 1.f;
   const int keep = top_k > 0 && top_k < vocab ? top_k : vocab;
-  const uint32_t seed = mix32((uint32_t)seeds[2 * s] ^ mix32((uint32_t)seeds[2 * s + 1] + 0x9e3779b9u * (col + 1)));
-  uint32_t prefix = 0;
+  uint32_t cut = 0;
   if (temperature > 0.f && keep < vocab) {
-    uint32_t left = keep;
-    for (int shift = 8; shift >= 0; shift -= 8) {
-      if (tid < 256) hist[tid] = 0;
-      __syncthreads();
-      const uint32_t high = shift == 8 ? 0u : 0xff00u;
-      for (int i = tid; i < vocab; i += kSampleThreads) {
-        const uint32_t key = order_key16(l[i]);
-        if (((key ^ prefix) & high) == 0) atomicAdd(&hist[(key >> shift) & 255], 1u);
-      }
-      __syncthreads();
-      if (tid < 32) {  // lane t holds digits 8t..8t+7; keys in strictly higher digits via a suffix scan
-        uint32_t c[8], mine = 0;
+    for (int bit = 15; bit >= 0; --bit) {
+      const uint32_t cand = cut | 1u << bit;  // cand >= 1: the padding keys (0) never count
+      uint32_t c = 0;
 #pragma unroll
-        for (int b = 0; b < 8; ++b) mine += c[b] = hist[tid * 8 + b];
-        uint32_t suffix = mine;
+      for (int r = 0; r < kSampleRegs; ++r) c += ((reg[r] & 0xffffu) >= cand) + ((reg[r] >> 16) >= cand);
 #pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-          const uint32_t other = __shfl_down_sync(0xffffffffu, suffix, o);
-          if (tid + o < 32) suffix += other;
-        }
-        uint32_t above = suffix - mine;
-#pragma unroll
-        for (int b = 7; b >= 0; --b) {
-          if (above < left && above + c[b] >= left) {
-            sel_prefix = prefix | (uint32_t)(tid * 8 + b) << shift;
-            sel_left = left - above;
-          }
-          above += c[b];
-        }
-      }
+      for (int o = 16; o > 0; o >>= 1) c += __shfl_xor_sync(0xffffffffu, c, o);
+      if (lane == 0) counts[bit & 1][warp] = c;
       __syncthreads();
-      prefix = sel_prefix;
-      left = sel_left;
+      uint32_t total = 0;
+#pragma unroll
+      for (int w = 0; w < kSampleThreads / 32; ++w) total += counts[bit & 1][w];
+      if (total >= (uint32_t)keep) cut = cand;
     }
   }
-  if (tid == 0) best = 0ull;
-  __syncthreads();
+  const uint32_t seed = mix32((uint32_t)seeds[2 * s] ^ mix32((uint32_t)seeds[2 * s + 1] + 0x9e3779b9u * (col + 1)));
   unsigned long long mine = 0ull;
-  for (int i = tid; i < vocab; i += kSampleThreads) {
-    const bf16 val = l[i];
-    if (order_key16(val) < prefix) continue;
-    float score = __bfloat162float(val) * inv_t;
-    if (temperature > 0.f) {
-      const float u = ((mix32(seed ^ mix32((uint32_t)i)) >> 8) + 0.5f) * (1.f / 16777216.f);
-      score -= __logf(-__logf(u));
+#pragma unroll
+  for (int r = 0; r < kSampleRegs; ++r) {
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const int i = 2 * (r * kSampleThreads + tid) + e;
+      const uint32_t key = e ? reg[r] >> 16 : reg[r] & 0xffffu;
+      if (i >= vocab || key < cut) continue;
+      float score = logit_of(key) * inv_t;
+      if (temperature > 0.f) {
+        const float u = ((mix32(seed ^ mix32((uint32_t)i)) >> 8) + 0.5f) * (1.f / 16777216.f);
+        score -= __logf(-__logf(u));
+      }
+      const unsigned long long packed = (unsigned long long)order_key32(score) << 32 | (uint32_t)(0xffffffffu - i);
+      mine = packed > mine ? packed : mine;
     }
-    const unsigned long long packed = (unsigned long long)order_key32(score) << 32 | (uint32_t)(0xffffffffu - i);
-    mine = packed > mine ? packed : mine;
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
     const unsigned long long other = __shfl_xor_sync(0xffffffffu, mine, o);
     mine = other > mine ? other : mine;
   }
-  if ((tid & 31) == 0) atomicMax(&best, mine);
+  if (lane == 0) best[warp] = mine;
   __syncthreads();
-  if (tid == 0) drawn[s * kDuplexDrawn + col] = (int32_t)(0xffffffffu - (uint32_t)(best & 0xffffffffull));
+  if (warp == 0) {
+    mine = best[lane];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const unsigned long long other = __shfl_xor_sync(0xffffffffu, mine, o);
+      mine = other > mine ? other : mine;
+    }
+    if (lane == 0) drawn[s * kDuplexDrawn + col] = (int32_t)(0xffffffffu - (uint32_t)(mine & 0xffffffffull));
+  }
 }
 
 // `lm_advance` (lm.cu:546-573): one thread per session.
@@ -504,15 +553,24 @@ cudaError_t launch_lm_add_norm(const bf16* y, bf16* x, const bf16* alpha, bf16* 
 
 cudaError_t launch_lm_rope_kv(bf16* qkv, const int32_t* pos, const int32_t* slots, void* kv, int rows, int heads,
                               float coef, int kv_pages, uint32_t* err, cudaStream_t s) {
-  lm_rope_kv_kernel<<<dim3(rows, (3 * heads + 7) / 8), 256, 0, s>>>(qkv, pos, slots, kv, heads, coef, kv_pages, err);
+  lm_rope_kv_kernel<<<dim3(rows, kRopeParts), kRopeWarps * 32, 0, s>>>(qkv, pos, slots, kv, heads, coef, kv_pages, err);
   return cudaGetLastError();
 }
 
 cudaError_t launch_lm_attend(const bf16* qkv, const void* kv, const int32_t* pos, const int32_t* seq,
                              const int32_t* indptr, const int32_t* pages, bf16* out, int rows, int heads, float scale,
                              int context, int kv_pages, uint32_t* err, cudaStream_t s) {
-  lm_attend_kernel<<<dim3(rows, heads), kAttendWarps * 32, 0, s>>>(qkv, kv, pos, seq, indptr, pages, out, heads, scale,
-                                                                  context, kv_pages, err);
+  const size_t smem = ((sizeof(AttendShared) + 127) & ~(size_t)127) + (size_t)kAttendWarps * 2 * kAttendSlotBytes;
+  static bool raised[64] = {};  // per device: 70 KB of staging slots is above the default 48 KB of dynamic shared memory
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return cudaErrorInvalidDevice;
+  if (!raised[device]) {
+    const cudaError_t e = cudaFuncSetAttribute(lm_attend_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    raised[device] = true;
+  }
+  lm_attend_kernel<<<dim3(rows, heads), kAttendWarps * 32, smem, s>>>(qkv, kv, pos, seq, indptr, pages, out, heads, scale,
+                                                                     context, kv_pages, err);
   return cudaGetLastError();
 }
 
@@ -535,6 +593,7 @@ cudaError_t launch_lm_sample(const bf16* logits, int vocab, int64_t ld, float te
                              const int32_t* force, const int32_t* seeds, int col, int32_t* drawn, int rows,
                              cudaStream_t s) {
   if (vocab < 1 || col < 0 || col >= kDuplexDrawn) return cudaErrorInvalidValue;
+  if (vocab > 2 * kSampleRegs * kSampleThreads) return cudaErrorInvalidValue;  // a thread keeps 64 keys in registers
   lm_sample_kernel<<<rows, kSampleThreads, 0, s>>>(logits, vocab, ld, temperature, top_k, force, seeds, col, drawn);
   return cudaGetLastError();
 }

@@ -104,11 +104,7 @@ Tiling choose_tiling(int N, int K, int ctas, bool swiglu, int bn = 64) {
       const int smax = direct ? 1 : std::min(8, nkb);
       for (int S = 1; S <= smax; ++S) {
         const int items = tiles * S, waves = (items + ctas - 1) / ctas, kb = (nkb + S - 1) / S;
-        static const double* tune = [] {
-          static double v[4] = {0.20, 80000.0, 1.5, 0.30};  // us floor per k-block, bytes per us, us per wave, us per split
-          if (const char* e = getenv("OMNI_TICK_COST")) sscanf(e, "%lf,%lf,%lf,%lf", &v[0], &v[1], &v[2], &v[3]);
-          return v;
-        }();
+        static const double tune[4] = {0.20, 80000.0, 1.5, 0.30};  // us floor per k-block, bytes per us, us per wave, us per split
         const double per_kb = std::max(tune[0], (tn * 128.0 + bn * 128.0) / tune[1]);  // weight + activation bytes
         double cost = waves * (kb * per_kb + tune[2]) + tune[3] * S;
         if (swiglu && !direct) cost += 5.0;
@@ -202,8 +198,7 @@ struct omni_talker {
   const PredProgram* pred_trace_program = nullptr;
   std::map<std::pair<int, int>, TickProgram> tick_programs;
   int launches = 0, tick_phases = 0;
-  std::string trace_path;
-  bool trace_checked = false;
+  std::string trace_path;  // omni_talker_trace: where the per-phase device timestamps of a tick are written
   unsigned long long* trace = nullptr;
   const TickProgram* trace_program = nullptr;
   omni_stats stats{};
@@ -526,8 +521,7 @@ struct TickBuilder {
   // stage is two copies, so one k-block per stage (16-24 KB) caps a CTA near 45 GB/s; several k-blocks per copy lift
   // that. The most (up to 4) that divide a work item's k-blocks and still leave two stages in the ring measured best.
   int stage_kblocks(int nkb, int splits, int bn, int tile_n) const {
-    int cap = 4;
-    if (const char* e = getenv("OMNI_TICK_KBS")) cap = std::max(1, atoi(e));  // tuning aid
+    const int cap = 4;
     if (nkb % splits) return 1;
     const int per = nkb / splits, ring = tick_ring_size();
     int best = 1;
@@ -857,11 +851,7 @@ int run_tick_program(omni_talker* m, int program, int b) {
   io.codes = m->codes;
   io.seen_words = m->seen_words;
   m->tick_phases = (int)it->second.phases.size();
-  // OMNI_TICK_TRACE=<file>: per-phase device timestamps of the last tick are written there (a profiling aid)
-  if (m->trace_path.empty() && !m->trace_checked) {
-    m->trace_checked = true;
-    if (const char* path = getenv("OMNI_TICK_TRACE")) m->trace_path = path;
-  }
+  // (omni_talker_trace named a file: the per-phase device timestamps of the last tick of a call are written there)
   if (!m->trace_path.empty() && !m->trace) TRY(dev_alloc(m, &m->trace, (size_t)4 * kTraceMaxPhases * m->tick_ctas, true));
   if (m->trace && m->tick_phases <= kTraceMaxPhases) {
     m->trace_program = &it->second;
@@ -1082,6 +1072,12 @@ extern "C" {
 const char* omni_version(void) { return "omni_b200 0.1 (sm_100a)"; }
 
 int32_t omni_bucket(int32_t n) { return bucket_of(n); }
+
+int32_t omni_talker_trace(omni_talker* m, const char* path) {
+  if (!m) return OMNI_ERR_INVALID;
+  m->trace_path = path ? path : "";
+  return OMNI_OK;
+}
 
 const char* omni_talker_last_error(const omni_talker* m) { return m ? m->error.c_str() : "null model"; }
 

@@ -703,6 +703,14 @@ __device__ __noinline__ void gemm_epilogue(const Phase& ph, float* partials, int
   }
 }
 
+// After an abort: waits (bounded) until the last copy this producer issued into each stage it ever used has landed, so
+// that no TMA write is in flight when the CTA gives its shared memory back. bit s of `par` is the parity of stage
+// s's NEXT use, i.e. the last issued use has the opposite parity; a phase that completed earlier reads as complete.
+__device__ __noinline__ void drain_copies(uint64_t* full, uint32_t touched, uint32_t par, uint32_t* err) {
+  for (int s = 0; s < kMaxStages; ++s)
+    if (touched >> s & 1u) sm100::mbar_wait(sm100::smem_addr(&full[s]), (par >> s & 1u) ^ 1u, err);
+}
+
 // kWide: the program has GEMM phases of more than 128 activation rows (buckets above 64: two accumulators per item).
 // The narrow instantiation carries none of that code: the 64-session tick is sensitive to the kernel's size.
 template <bool kWide>
@@ -742,6 +750,7 @@ __global__ void __launch_bounds__(kThreads, 1) tick_kernel(const __grid_constant
   if (warp == 0) {
     if (lane == 0) {  // ---- weight producer ----
       Ring ring;
+      uint32_t touched = 0;  // stages this thread has issued a copy into
       for (int p = 0; p < a.n_phases && !ctl.abort; ++p) {
         const Phase& ph = a.phases[p];
         if (ph.type != kPhGemm) continue;
@@ -780,14 +789,17 @@ __global__ void __launch_bounds__(kThreads, 1) tick_kernel(const __grid_constant
               tma_load_2d(base + ring.w_off(), map, bar, kb * kTileK, tile * ph.tile_n, kEvictFirst);
             else
               tma_load_3d(base + ring.w_off(), map, bar, 0, tile * ph.tile_n, kb, kEvictFirst);
+            touched |= 1u << ring.stage;
             ring.advance();
           }
         }
       }
+      if (ctl.abort) drain_copies(ctl.full_w, touched, ring.par, a.err);
     }
   } else if (warp == 1) {
     if (lane == 0) {  // ---- activation producer ----
       Ring ring;
+      uint32_t touched = 0;
       for (int p = 0; p < a.n_phases && !ctl.abort; ++p) {
         const Phase& ph = a.phases[p];
         if (ph.type != kPhGemm) continue;
@@ -821,10 +833,12 @@ __global__ void __launch_bounds__(kThreads, 1) tick_kernel(const __grid_constant
               tma_load_2d(base + ring.x_off(), map, bar, kb * kTileK, 0, kEvictLast);
             else
               tma_load_3d(base + ring.x_off(), map, bar, 0, 0, kb, kEvictLast);
+            touched |= 1u << ring.stage;
             ring.advance();
           }
         }
       }
+      if (ctl.abort) drain_copies(ctl.full_x, touched, ring.par, a.err);
     }
   } else if (warp == 2) {
     if (lane == 0) {  // ---- MMA issuer ----
@@ -991,7 +1005,6 @@ __global__ void __launch_bounds__(kThreads, 1) tick_kernel(const __grid_constant
     }
   }
   __syncwarp();
-  if (ctl.abort) __nanosleep(20000);  // let copies still in flight land before the shared memory is released
   tc_fence_before_sync();
   __syncthreads();
   if (warp == 2) tmem_dealloc(tmem_base, kTmemCols);
@@ -1013,12 +1026,8 @@ size_t tick_smem_bytes(int ring_bytes) {
 // The ring's size. 128 KB by default: with the control block and scratch the CTA then takes the 164 KB shared-memory
 // carve-out and 92 KB of the SM's array stay L1. With one k-block per stage 104 KB (132 KB carve-out, 124 KB L1) was
 // the faster trade; stages of several k-blocks need the room (two stages of 48 KB for the 128-row weight tiles).
-// OMNI_TICK_RING_KB overrides it (a tuning aid, 48 .. 192).
-int tick_ring_bytes() {
-  int kb = 128;
-  if (const char* e = getenv("OMNI_TICK_RING_KB")) kb = atoi(e);
-  return std::min(std::max(kb, 48), kMaxRingBytes / 1024) * 1024;
-}
+// Measured with multi-k-block stages: 104 / 112 / 120 / 128 / 136 KB -> 6.25 / 6.32 / 6.26 / 6.17 / 6.17 ms per tick.
+int tick_ring_bytes() { return 128 * 1024; }
 
 }  // namespace
 
@@ -1098,8 +1107,7 @@ cudaError_t tick_launch(const TickProgram& prog, const TickIo& io, float* partia
   a.barrier = barrier;
   a.err = err;
   a.ring_bytes = tick_ring_bytes();
-  a.w_ahead = 1 << 20;
-  if (const char* e = getenv("OMNI_TICK_WAHEAD")) a.w_ahead = atoi(e);
+  a.w_ahead = 1 << 20;  // unbounded: limiting the run-ahead to 0 / 1 / 2 phases measured 6.23 / 6.08 / 6.06 ms against 6.06
   a.io = io;
   // the arrival counter runs on from launch to launch (one memset less per tick); it restarts from zero when the
   // next launch could overflow it. After a launch that raised the error word the caller passes *barrier_base = ~0u.

@@ -96,6 +96,7 @@ SYMBOLS = {
     "omni_talker_read": (I32, [VP, I32, I32, VP, C.c_size_t]),
     "omni_talker_is_end": (I32, [VP, P(I32)]),
     "omni_talker_stats": (I32, [VP, P(Stats)]),
+    "omni_talker_trace": (I32, [VP, C.c_char_p]),
     "omni_talker_last_error": (C.c_char_p, [VP]),
     "omni_bucket": (I32, [I32]),
     "omni_version": (C.c_char_p, []),

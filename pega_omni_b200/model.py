@@ -269,6 +269,10 @@ class Model:
     def pad_embed(self) -> np.ndarray:
         return self._read(L.BUF_PAD_EMBED, 0, self.config.talker.hidden_size)
 
+    def trace(self, path) -> None:
+        """Per-phase device timestamps of the last tick of every later `run_ticks` call go to `path` (None: off)."""
+        self._check(self._lib.omni_talker_trace(self._h, str(path).encode() if path else None))
+
     def stats(self) -> L.Stats:
         st = L.Stats()
         self._check(self._lib.omni_talker_stats(self._h, C.byref(st)))
