@@ -409,6 +409,8 @@ def main():
                     help="talker: the headline Qwen3-TTS tick (default); duplex: the PersonaPlex-7B tick (configs[3]); "
                          "higgs: the Higgs-style 4B step (configs[4])")
     ap.add_argument("--context", type=int, default=3000, help="duplex: KV ring length")
+    ap.add_argument("--e2e-waited", action="store_true", help="talker: the end-to-end arm waits on every step (Model.step) "
+                    "instead of keeping two steps under way (step_begin / step_end)")
     ap.add_argument("--trace", default=None, help="talker: write the tick kernel's per-phase device timestamps here")
     args = ap.parse_args()
 
@@ -506,8 +508,17 @@ def main():
     barrier()
     t0 = time.perf_counter()
     dev_ms = 0.0
-    for t in range(K):
-        out = model.step_batch(seqs, e2e_draws[W + t], out)
+    if args.e2e_waited:  # one waited call per step, as the reference's engine drives its model
+        for t in range(K):
+            out = model.step_batch(seqs, e2e_draws[W + t], out)
+            dev_ms += model.stats().last_call_gpu_ms
+    else:  # step_begin / step_end, two steps under way: every step still stages its draws and reads its frames back
+        model.step_begin(seqs, e2e_draws[W])
+        for t in range(1, K):
+            model.step_begin(seqs, e2e_draws[W + t])
+            out = model.step_end(n, out)
+            dev_ms += model.stats().last_call_gpu_ms
+        out = model.step_end(n, out)
         dev_ms += model.stats().last_call_gpu_ms
     torch.cuda.synchronize()
     e2e_s = time.perf_counter() - t0
@@ -559,7 +570,8 @@ def main():
                        "engine": "persistent tick kernel" if launches_per_tick == 1 else "persistent talker kernel + cluster predictor kernel" if launches_per_tick == 2 else "per-op CUDA graph"},
             "tick_p99_ms": float(t_p99.item()), "tick_p50_ms": float(np.percentile(tick_ms, 50)),
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
-                    "timing": "wall clock around K Model.step_batch calls (each stages its inputs, runs the tick and waits for its frame), max over ranks",
+                    "timing": "wall clock around K steps through the C ABI, each staging its draws from host memory and reading its frame back; "
+                              + ("one waited call per step" if args.e2e_waited else "step_begin / step_end with two steps under way") + ", max over ranks",
                     "device_ms_per_step": dev_ms / K},
             "gpu_launches": int(launches_per_tick * K),
             "launches_per_tick": int(launches_per_tick),

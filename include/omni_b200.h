@@ -154,6 +154,17 @@ int32_t omni_talker_start(omni_talker* m, int32_t n, omni_seq* const* seqs, cons
 int32_t omni_talker_step(omni_talker* m, int32_t n, omni_seq* const* seqs, const omni_draw* draws, int32_t* codes,
                          float* wav);
 
+/* `Model::step` in two halves, so that the engine thread can work while the GPU does (the reference's engine waits
+ * on `prefill+first` and on `decode` with nothing else to do, docs/qwen3-tts.md:218-221): `step_begin` stages the
+ * draws in its own pinned block, enqueues the tick and the read-back and returns; `step_end` waits for the OLDEST
+ * step begun and hands out its frames. Up to two steps may be under way: a step's inputs are its draws alone (the
+ * codes it needs sit in the sequences' slots on the device), so step t + 1 can be begun before step t is ended and
+ * the host's staging, the copies and the engine's own work between the calls overlap the previous tick. Sequences
+ * count a frame at `step_begin`. While a step is under way `start`, `step`, `run_ticks` and `close` are refused.
+ * The first `step_begin` after create allocates the two pinned blocks. */
+int32_t omni_talker_step_begin(omni_talker* m, int32_t n, omni_seq* const* seqs, const omni_draw* draws);
+int32_t omni_talker_step_end(omni_talker* m, int32_t* codes, float* wav);
+
 /* `ticks` back-to-back steps of the same `n` sequences with every tick's draws
  * staged in device memory before the first tick starts, so no host transfer
  * falls inside a tick. draws: [ticks][n]. codes: [ticks][n][16] or NULL.

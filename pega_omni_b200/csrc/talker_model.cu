@@ -203,6 +203,15 @@ struct omni_talker {
   const TickProgram* trace_program = nullptr;
   omni_stats stats{};
   int last_n = 0;
+  // omni_talker_step_begin / _end: up to two decode steps under way, each with its own pinned staging and read-back
+  // blocks and events (the host prepares step t + 1 while the device runs step t)
+  struct Flight {
+    char* in_host = nullptr;
+    int32_t* out_host = nullptr;
+    cudaEvent_t start = nullptr, done = nullptr;
+    int n = 0, launches = 0;
+  } flight[2];
+  int flight_first = 0, in_flight = 0;
 
   int fail(int code, const char* fmt, ...) {
     char buf[512];
@@ -1091,6 +1100,12 @@ void omni_talker_destroy(omni_talker* m) {
   for (void* p : m->allocations) cudaFree(p);
   if (m->in_host) cudaFreeHost(m->in_host);
   if (m->out_host) cudaFreeHost(m->out_host);
+  for (auto& f : m->flight) {
+    if (f.in_host) cudaFreeHost(f.in_host);
+    if (f.out_host) cudaFreeHost(f.out_host);
+    if (f.start) cudaEventDestroy(f.start);
+    if (f.done) cudaEventDestroy(f.done);
+  }
   if (m->ev0) cudaEventDestroy(m->ev0);
   if (m->ev1) cudaEventDestroy(m->ev1);
   if (m->stream) cudaStreamDestroy(m->stream);
@@ -1291,6 +1306,7 @@ int32_t omni_talker_open(omni_talker* m, int32_t prompt_tokens, int32_t max_fram
 
 int32_t omni_talker_close(omni_talker* m, omni_seq* seq) {
   if (!m || !seq) return OMNI_ERR_INVALID;
+  if (m->in_flight > 0) return m->fail(OMNI_ERR_INVALID, "a step is under way: end it before closing a sequence");
   // the handle is looked up before it is touched: a handle closed before (or never opened here) points at freed memory
   for (size_t i = 0; i < m->seqs.size(); ++i) {
     if (m->seqs[i].get() != seq) continue;
@@ -1323,6 +1339,7 @@ int32_t omni_talker_start(omni_talker* m, int32_t n, omni_seq* const* seqs, cons
                           const int32_t* codec_ids, const int32_t* prompt_lens, const omni_draw* draws,
                           int32_t* codes, float* wav) {
   if (!m || !seqs || !text_ids || !codec_ids || !prompt_lens || !draws || !codes) return OMNI_ERR_INVALID;
+  if (m->in_flight > 0) return m->fail(OMNI_ERR_INVALID, "a step is under way: end it before a start");
   const omni_talker_config& c = m->cfg;
   if (n < 1 || n > c.max_batch) return m->fail(OMNI_ERR_INVALID, "%d sequences in one call", n);
   int64_t tokens = 0;
@@ -1403,6 +1420,9 @@ int32_t omni_talker_start(omni_talker* m, int32_t n, omni_seq* const* seqs, cons
 }
 
 static int check_step(omni_talker* m, int n, omni_seq* const* seqs, const omni_draw* draws, int ticks) {
+  if (m->in_flight > 0 && ticks != 0)
+    return m->fail(OMNI_ERR_INVALID, "%d step(s) begun with omni_talker_step_begin are still to be ended", m->in_flight);
+  if (ticks == 0) ticks = 1;
   const omni_talker_config& c = m->cfg;
   if (n < 1 || n > c.max_batch) return m->fail(OMNI_ERR_INVALID, "%d sequences in one call", n);
   for (int s = 0; s < n; ++s) {
@@ -1434,6 +1454,62 @@ int32_t omni_talker_step(omni_talker* m, int32_t n, omni_seq* const* seqs, const
   m->stats.bucket = b;
   TRY(finish_call(m, n, codes, wav));
   for (int s = 0; s < n; ++s) seqs[s]->frames += 1;
+  return OMNI_OK;
+}
+
+int32_t omni_talker_step_begin(omni_talker* m, int32_t n, omni_seq* const* seqs, const omni_draw* draws) {
+  if (!m || !seqs || !draws) return OMNI_ERR_INVALID;
+  if (m->in_flight >= 2) return m->fail(OMNI_ERR_INVALID, "two steps are under way: end the older one first");
+  TRY(check_step(m, n, seqs, draws, 0));
+  CUDA_TRY(m, cudaSetDevice(m->device));
+  omni_talker::Flight& f = m->flight[(m->flight_first + m->in_flight) % 2];
+  if (!f.in_host) {  // first use of this slot (before any stream capture: these are allocations)
+    CUDA_TRY(m, cudaHostAlloc((void**)&f.in_host, m->in.total_bytes, cudaHostAllocDefault));
+    CUDA_TRY(m, cudaHostAlloc((void**)&f.out_host, ((size_t)m->max_seqs * OMNI_GROUPS + 1) * 4, cudaHostAllocDefault));
+    CUDA_TRY(m, cudaEventCreate(&f.start));
+    CUDA_TRY(m, cudaEventCreate(&f.done));
+  }
+  std::vector<FrameRow> rows(n);
+  for (int s = 0; s < n; ++s) rows[s] = FrameRow{seqs[s], seqs[s]->prompt + seqs[s]->frames - 1, seqs[s]->frames, &draws[s]};
+  const int b = bucket_of(n);
+  const size_t bytes = stage_graph_inputs(m, f.in_host, rows, b, true);
+  CUDA_TRY(m, cudaEventRecord(f.start, m->stream));
+  CUDA_TRY(m, cudaMemcpyAsync(m->in_dev, f.in_host, bytes, cudaMemcpyHostToDevice, m->stream));
+  TRY(run_program(m, kDecode, b));
+  m->stats.bucket = b;
+  CUDA_TRY(m, cudaMemcpyAsync(f.out_host, m->codes, ((size_t)m->max_seqs * OMNI_GROUPS + 1) * 4, cudaMemcpyDeviceToHost,
+                              m->stream));
+  CUDA_TRY(m, cudaEventRecord(f.done, m->stream));
+  f.n = n;
+  f.launches = m->launches;
+  m->in_flight += 1;
+  for (int s = 0; s < n; ++s) seqs[s]->frames += 1;  // the next step_begin computes its positions from these
+  return OMNI_OK;
+}
+
+int32_t omni_talker_step_end(omni_talker* m, int32_t* codes, float* wav) {
+  if (!m || !codes) return OMNI_ERR_INVALID;
+  if (m->in_flight < 1) return m->fail(OMNI_ERR_INVALID, "no step under way");
+  CUDA_TRY(m, cudaSetDevice(m->device));
+  omni_talker::Flight& f = m->flight[m->flight_first];
+  CUDA_TRY(m, cudaEventSynchronize(f.done));
+  m->flight_first ^= 1;
+  m->in_flight -= 1;
+  cudaEventElapsedTime(&m->stats.last_call_gpu_ms, f.start, f.done);
+  m->stats.last_call_launches = f.launches;
+  const uint32_t err = (uint32_t)f.out_host[(size_t)m->max_seqs * OMNI_GROUPS];
+  if (err != 0) {
+    // a step begun after this one ran on the same error word: wait for it, drop it, then clear the word
+    CUDA_TRY(m, cudaStreamSynchronize(m->stream));
+    m->in_flight = 0;
+    m->tick_barrier_base = ~0u;
+    cudaMemsetAsync(m->err, 0, 4, m->stream);
+    cudaStreamSynchronize(m->stream);
+    return m->fail(OMNI_ERR_DEVICE, "device error word 0x%x (1: barrier wait ran out, 2: index out of range)", err);
+  }
+  memcpy(codes, f.out_host, (size_t)f.n * OMNI_GROUPS * 4);
+  if (wav) memset(wav, 0, (size_t)f.n * 1920 * sizeof(float));
+  m->last_n = f.n;
   return OMNI_OK;
 }
 

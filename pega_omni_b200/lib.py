@@ -92,6 +92,8 @@ SYMBOLS = {
     "omni_talker_seq_frames": (I32, [VP]),
     "omni_talker_start": (I32, [VP, I32, P(VP), P(I32), P(I32), P(I32), P(Draw), P(I32), P(C.c_float)]),
     "omni_talker_step": (I32, [VP, I32, P(VP), P(Draw), P(I32), P(C.c_float)]),
+    "omni_talker_step_begin": (I32, [VP, I32, P(VP), P(Draw)]),
+    "omni_talker_step_end": (I32, [VP, P(I32), P(C.c_float)]),
     "omni_talker_run_ticks": (I32, [VP, I32, P(VP), I32, P(Draw), P(I32), P(C.c_float)]),
     "omni_talker_read": (I32, [VP, I32, I32, VP, C.c_size_t]),
     "omni_talker_is_end": (I32, [VP, P(I32)]),

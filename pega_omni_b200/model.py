@@ -235,6 +235,18 @@ class Model:
             out.codes.ctypes.data_as(C.POINTER(C.c_int32)), out.wav.ctypes.data_as(C.POINTER(C.c_float))))
         return out
 
+    def step_begin(self, seqs: Sequence[Seq], draws) -> None:
+        """Enqueues one decode step and returns at once (`omni_talker_step_begin`); up to two may be under way."""
+        self._check(self._lib.omni_talker_step_begin(self._h, len(seqs), self._seq_array(seqs), _draws(draws)))
+
+    def step_end(self, n: int, out: Optional[Out] = None) -> Out:
+        """Waits for the oldest step begun (of `n` sequences) and returns its frames."""
+        if out is None:
+            out = Out(np.zeros((n, GROUPS), dtype=np.int32), np.zeros((n, SAMPLES_PER_FRAME), dtype=np.float32))
+        self._check(self._lib.omni_talker_step_end(
+            self._h, out.codes.ctypes.data_as(C.POINTER(C.c_int32)), out.wav.ctypes.data_as(C.POINTER(C.c_float))))
+        return out
+
     def run_ticks(self, seqs: Sequence[Seq], draws: Sequence[Sequence[Draw]]):
         """`len(draws)` decode ticks with all inputs staged on the device first; returns (codes, tick_ms)."""
         ticks, n = len(draws), len(seqs)

@@ -267,7 +267,7 @@ def test_tick_kernel_agrees_with_per_op_kernels(built_lib, sessions):
 def test_run_ticks_equals_steps(built_lib):
     from pega_omni_b200.model import Draw
     results = []
-    for mode in ("steps", "ticks"):
+    for mode in ("steps", "ticks", "overlapped"):
         cfg, ck, m = make("tiny128")
         ps = prompts_for(cfg, [11, 19, 40], seed=7)
         rng = np.random.default_rng(7)
@@ -276,13 +276,28 @@ def test_run_ticks_equals_steps(built_lib):
         draws = [[Draw(list(rng.random(16))) for _ in ps] for _ in range(8)]
         if mode == "steps":
             codes = np.stack([m.step(list(zip(seqs, d))).codes for d in draws])
-        else:
+        elif mode == "ticks":
             codes, ms = m.run_ticks(seqs, draws)
             assert (ms > 0).all()
+        else:  # step_begin / step_end with two steps under way: step t + 1 is begun before step t is ended
+            from pega_omni_b200.model import OmniError
+            got = []
+            m.step_begin(seqs, draws[0])
+            for t in range(1, len(draws)):
+                m.step_begin(seqs, draws[t])
+                with pytest.raises(OmniError):  # a third step, or a waited call, is refused while two are under way
+                    m.step_begin(seqs, draws[t])
+                with pytest.raises(OmniError):
+                    m.step(list(zip(seqs, draws[t])))
+                got.append(m.step_end(len(seqs)).codes.copy())
+            got.append(m.step_end(len(seqs)).codes.copy())
+            with pytest.raises(OmniError):
+                m.step_end(len(seqs))
+            codes = np.stack(got)
         assert all(s.frames == 9 for s in seqs)
         results.append(codes)
         m.close()
-    assert np.array_equal(results[0], results[1])
+    assert np.array_equal(results[0], results[1]) and np.array_equal(results[0], results[2])
 
 
 def test_philox_mode_matches_oracle_stream(built_lib, oracle_lib):
