@@ -393,6 +393,81 @@ def run_duplex(args, rank, world, local):
     model.close()
 
 
+def run_sweep(args, rank, world, local):
+    """configs[2]: the headline model at `--sessions` sessions per GPU with prompt lengths uniform in [--prompt,
+    --prompt-max] and `--steps` decode frames per session. Buckets go up to 128 sessions, so larger counts run as
+    consecutive groups of at most 128 (a tick of 256 sessions = two launches); the line reports the whole-tick time.
+    Device-resident timing as in the headline arm; the reference's kernels are replayed at the mean prompt length for
+    counts their shapes allow (<= 128)."""
+    import torch
+    import torch.distributed as dist
+    from pega_omni_b200.config import presets
+    from pega_omni_b200.model import Limits, Model
+    from pega_omni_b200.synthetic import random_checkpoint
+    W, K, n = max(3, args.warmup), args.steps, args.sessions
+    lo, hi = args.prompt, max(args.prompt, args.prompt_max or args.prompt)
+    cfg = presets["qwen3-tts-1.7b"]()
+    ck = random_checkpoint(cfg, seed=0, device="cuda")
+    rng = np.random.default_rng(2000 + rank)
+    lens = [int(v) for v in rng.integers(lo, hi + 1, n)]
+    frames_cap = W + K + 8
+    group = min(n, 128)
+    kv_gib = max(1.0, 1.15 * sum(l + frames_cap + 16 for l in lens) * cfg.talker.kv_bytes_per_token() / 2 ** 30)
+    model = Model.load(local, ck, cfg, Limits(n, 16 * hi, kv_gib))
+    from pega_omni_b200.model import Prompt
+    prompts = [Prompt(list(rng.integers(0, cfg.text_vocab_size, l)), [-1] * l) for l in lens]
+    seqs = [model.open(l, frames_cap) for l in lens]
+    d0 = draws_for(1, n, seed=rank)[0]
+    i = 0
+    while i < n:  # prefill in calls that fit the token limit
+        j, tokens = i, 0
+        while j < n and j - i < group and tokens + lens[j] <= 16 * hi:
+            tokens += lens[j]
+            j += 1
+        model.start(list(zip(seqs[i:j], prompts[i:j], d0[i:j])))
+        i = j
+    groups = [list(range(g, min(g + 128, n))) for g in range(0, n, 128)]
+    for g in groups:
+        model.run_ticks([seqs[k] for k in g], draws_for(W, len(g), seed=10 + rank))
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    tick_ms = np.zeros(K)
+    for g in groups:
+        _, ms = model.run_ticks([seqs[k] for k in g], draws_for(K, len(g), seed=20 + rank))
+        tick_ms += ms
+    torch.cuda.synchronize()
+    t_el = torch.tensor([float(tick_ms.sum()) * 1e-3], device="cuda", dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t_el, op=dist.ReduceOp.MAX)
+        dist.barrier()
+        dist.destroy_process_group()
+    if rank == 0:
+        peak, peak_kind = measured_peaks()
+        mean_len = float(np.mean(lens)) + 1 + W + (K - 1) / 2 + 1
+        tick_bytes = len(groups) * cfg.tick_weight_bytes() + cfg.talker.kv_bytes_per_token() * n * (mean_len + 1)
+        tick_s = float(t_el.item()) / K
+        line = {"metric": "codec frames/sec at %d sessions per GPU (Qwen3-TTS talker), ragged prompts" % n,
+                "value": n * world * K / float(t_el.item()), "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
+                "ms_per_step": 1e3 * tick_s, "tick_p99_ms": float(np.percentile(tick_ms, 99)), "higher_is_better": True,
+                "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+                "config": {"workload": "configs[2]: " + CONFIG_WORKLOAD, "sessions_per_gpu": n,
+                           "prompt_tokens": [lo, hi], "frames": K, "launches_per_tick": len(groups),
+                           "parallelism": f"{world} replica(s), no collective"},
+                "roofline": {"bound": "hbm", "achieved": tick_bytes / tick_s / 1e9, "peak": peak, "unit": "GB/s",
+                             "frac": tick_bytes / tick_s / 1e9 / peak, "peak_source": f"of {peak_kind}",
+                             "note": "weights counted once per launch of a tick (%d)" % len(groups)}}
+        if not args.no_replay and world == 1 and n <= 128:
+            model.close()
+            torch.cuda.empty_cache()
+            rep = replay_baseline(cfg, ck, n, int(np.mean(lens)), W, K)
+            if rep is not None:
+                line["reference_replay"] = rep
+                line["vs_replay"] = line["value"] / rep["value"]
+        print(json.dumps(line), flush=True)
+    model.close()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -405,7 +480,8 @@ def main():
     ap.add_argument("--no-graphs", action="store_true")
     ap.add_argument("--no-replay", action="store_true", help="skip timing the reference's kernels on this GPU")
     ap.add_argument("--per-op", action="store_true", help="one kernel per op (CUDA graph) instead of the tick kernel")
-    ap.add_argument("--workload", default="talker", choices=["talker", "duplex", "higgs"],
+    ap.add_argument("--prompt-max", type=int, default=0, help="sweep: prompt lengths uniform in [--prompt, --prompt-max]")
+    ap.add_argument("--workload", default="talker", choices=["talker", "duplex", "higgs", "sweep"],
                     help="talker: the headline Qwen3-TTS tick (default); duplex: the PersonaPlex-7B tick (configs[3]); "
                          "higgs: the Higgs-style 4B step (configs[4])")
     ap.add_argument("--context", type=int, default=3000, help="duplex: KV ring length")
@@ -434,6 +510,9 @@ def main():
         return
     if args.workload == "higgs":
         run_higgs(args, rank, world, local)
+        return
+    if args.workload == "sweep":
+        run_sweep(args, rank, world, local)
         return
 
     from pega_omni_b200 import replicas
