@@ -468,6 +468,56 @@ def run_sweep(args, rank, world, local):
     model.close()
 
 
+def run_attend(args):
+    """The stand-alone decode-attention op (`omni_op_rope_attend`: per-head norm + RoPE + K/V write, then paged GQA
+    attention) at the headline head shape (16 query / 8 kv heads of 128) with `--sessions` rows, one line per context
+    length: device time between two events on the op context's stream (L2 flushed before every call), the KV bytes it
+    must read, and the marginal rate between consecutive context lengths, which leaves the two launches' fixed cost out."""
+    import torch
+    from pega_omni_b200.ops import Ops
+    ops = Ops(0)
+    hq, hk, d, rows = 16, 8, 128, args.sessions
+    peak, peak_kind = measured_peaks()
+    g = torch.Generator(device="cuda")
+    g.manual_seed(1)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    dev = lambda a: torch.tensor(np.asarray(a), dtype=torch.int32, device="cuda")
+    prev = None
+    for ctx in (16, 144, 384, 1024, 2048):
+        per = (ctx + 15) // 16
+        n_pages = rows * per
+        kv = torch.randn((n_pages, hk, 2, 16, d), generator=g, device="cuda").to(torch.bfloat16)
+        qkv0 = torch.randn((rows, (hq + 2 * hk) * d), generator=g, device="cuda").to(torch.bfloat16)
+        gain = torch.ones(d, dtype=torch.bfloat16, device="cuda")
+        pages = np.random.default_rng(0).permutation(n_pages).astype(np.int32)
+        slot = [int(pages[s * per + (ctx - 1) // 16]) * 16 + (ctx - 1) % 16 for s in range(rows)]
+        dpos, dslot, dseq = dev(np.full(rows, ctx - 1)), dev(slot), dev(np.arange(rows))
+        dind, dpages = dev(np.arange(rows + 1) * per), dev(pages)
+        out = torch.zeros((rows, hq * d), dtype=torch.bfloat16, device="cuda")
+        times = []
+        for it in range(max(3, args.warmup) + args.steps):
+            qkv = qkv0.clone()
+            flush.fill_(it & 255)
+            torch.cuda.synchronize()
+            ops.mark(0)
+            ops.rope_attend(qkv, gain, gain, kv, n_pages, dpos, dslot, dseq, dind, dpages, hq, hk, d, 1e-6, 1e6, out)
+            ops.mark(1)
+            ops.sync()
+            times.append(ops.elapsed_ms())
+        t = float(np.median(times[max(3, args.warmup):])) * 1e-3
+        kv_bytes = rows * ctx * hk * 2 * d * 2
+        line = {"workload": "omni_op_rope_attend, %d rows, 16q/8kv heads of 128, paged bf16 KV" % rows, "context": ctx,
+                "us": t * 1e6, "kv_mb": kv_bytes / 1e6, "gbs": kv_bytes / t / 1e9, "frac": kv_bytes / t / 1e9 / peak,
+                "peak_source": f"of {peak_kind}", "l2": "flushed before every call"}
+        if prev is not None:
+            line["marginal_gbs"] = (kv_bytes - prev[0]) / (t - prev[1]) / 1e9
+            line["marginal_frac"] = line["marginal_gbs"] / peak
+        prev = (kv_bytes, t)
+        print(json.dumps(line), flush=True)
+        del kv
+    ops.close()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -481,7 +531,7 @@ def main():
     ap.add_argument("--no-replay", action="store_true", help="skip timing the reference's kernels on this GPU")
     ap.add_argument("--per-op", action="store_true", help="one kernel per op (CUDA graph) instead of the tick kernel")
     ap.add_argument("--prompt-max", type=int, default=0, help="sweep: prompt lengths uniform in [--prompt, --prompt-max]")
-    ap.add_argument("--workload", default="talker", choices=["talker", "duplex", "higgs", "sweep"],
+    ap.add_argument("--workload", default="talker", choices=["talker", "duplex", "higgs", "sweep", "attend"],
                     help="talker: the headline Qwen3-TTS tick (default); duplex: the PersonaPlex-7B tick (configs[3]); "
                          "higgs: the Higgs-style 4B step (configs[4])")
     ap.add_argument("--context", type=int, default=3000, help="duplex: KV ring length")
@@ -510,6 +560,9 @@ def main():
         return
     if args.workload == "higgs":
         run_higgs(args, rank, world, local)
+        return
+    if args.workload == "attend":
+        run_attend(args)
         return
     if args.workload == "sweep":
         run_sweep(args, rank, world, local)

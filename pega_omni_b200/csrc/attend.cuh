@@ -5,11 +5,32 @@
 // Value semantics of `attend` (crates/omni-qwen3/kernels/qwen3.cu:123-207): f32 scores and
 // accumulation, __expf, per-warp online softmax states merged at the end, bf16 output.
 #pragma once
+#include "sm100.cuh"
 #include "util.cuh"
 
 namespace omni {
 
 constexpr int kAttnWarps = 4;
+
+// A warp's staging slots for K|V blocks: a (page, kv head) block is 2 * 16 * D contiguous bf16 of this GPU's own
+// memory, so one untiled bulk copy brings it into shared memory while the warp works on the block before it. With
+// S slots a warp has S blocks in flight or in use. `slots`: S * kv_block_bytes<D>() bytes, 128-byte aligned; `bars`:
+// S mbarriers initialised with count 1 by the owner (one lane arms and issues). `par` holds the slots' wait parities
+// and lives as long as the barriers do.
+template <int D>
+__host__ __device__ constexpr uint32_t kv_block_bytes() { return 2u * 16u * D * 2u; }
+
+template <int S>
+struct PageStage {
+  static constexpr int kSlots = S;
+  unsigned char* slots;  // this warp's S slots
+  uint64_t* bars;        // this warp's S barriers
+  uint32_t par;
+  uint32_t* err;
+};
+struct NoStage {
+  static constexpr int kSlots = 0;
+};
 
 // Element offset of (page, head, K or V, token-in-page) in a layer's KV buffer.
 template <int D>
@@ -37,11 +58,15 @@ struct WarpSync {  // team barrier of a one-warp team
 // predictor's per-frame KV). `len` keys. `out`: G heads of D, contiguous. tid: 0..127 within the team.
 // Warps take pages round-robin; q.k of a page is computed with the key rows spread over lanes and finished by
 // shuffles (lane & 15 then owns a key), then every lane owns D/32 output dims for p.v. Ends with a team barrier (sh may be reused).
-template <int D, int G, int W = kAttnWarps, typename TeamSync>
+// `stage` (optional): the warp's staging slots; the blocks then come through bulk copies, S of them ahead, and the
+// arithmetic below reads the same bytes from shared memory in the same order (results are bit-identical).
+template <int D, int G, int W = kAttnWarps, typename TeamSync, typename Stage = NoStage>
 __device__ __forceinline__ void attend_pages(AttnShared<D, G, W>& sh, const bf16* __restrict__ kv,
                                              const int32_t* __restrict__ pages, int seq_page, int len, int hk, int kh,
-                                             float scale, bf16* __restrict__ out, int tid, const TeamSync& team) {
+                                             float scale, bf16* __restrict__ out, int tid, const TeamSync& team,
+                                             Stage* stage = nullptr) {
   constexpr int PV = D / 32;   // output dims per lane
+  constexpr int S = Stage::kSlots;
   const int lane = tid & 31, warp = tid >> 5;
   const int key = lane & 15;
   float m[G], l[G], acc[G][PV];
@@ -53,11 +78,35 @@ __device__ __forceinline__ void attend_pages(AttnShared<D, G, W>& sh, const bf16
     for (int d = 0; d < PV; ++d) acc[g][d] = 0.f;
   }
   const int npages = (len + 15) >> 4;
-  for (int pi = warp; pi < npages; pi += W) {
-    const int64_t page = pages ? pages[pi] : seq_page;
+  if constexpr (S > 0) {
+    if (lane == 0) {
+#pragma unroll
+      for (int s = 0; s < S; ++s) {
+        const int pi = warp + s * W;
+        if (pi < npages) {
+          const int64_t page = pages ? pages[pi] : seq_page;
+          const uint32_t bar = sm100::smem_addr(stage->bars + s);
+          sm100::mbar_expect_tx(bar, kv_block_bytes<D>());
+          sm100::bulk_load(sm100::smem_addr(stage->slots + s * kv_block_bytes<D>()), kv + kv_offset<D>(page, hk, kh, 0, 0),
+                           kv_block_bytes<D>(), bar);
+        }
+      }
+    }
+  }
+  int turn = 0;
+  for (int pi = warp; pi < npages; pi += W, ++turn) {
     const int ntok = min(16, len - pi * 16);
-    const bf16* kpage = kv + kv_offset<D>(page, hk, kh, 0, 0);
-    const bf16* vpage = kpage + 16 * D;
+    const bf16 *kpage, *vpage;
+    if constexpr (S > 0) {
+      const int s = turn % S;
+      sm100::mbar_wait(sm100::smem_addr(stage->bars + s), stage->par >> s & 1u, stage->err);
+      stage->par ^= 1u << s;
+      kpage = reinterpret_cast<const bf16*>(stage->slots + s * kv_block_bytes<D>());
+    } else {
+      const int64_t page = pages ? pages[pi] : seq_page;
+      kpage = kv + kv_offset<D>(page, hk, kh, 0, 0);
+    }
+    vpage = kpage + 16 * D;
     // Every load of the page is issued before any of it is used, and every load instruction covers contiguous
     // memory: a (page, head) K block is 16 rows of D bf16 back to back, so instruction c takes bytes
     // [512c, 512c + 512) with 16 bytes per lane. A key row is then spread over LPT = D/8 lanes; the dot product
@@ -73,6 +122,18 @@ __device__ __forceinline__ void attend_pages(AttnShared<D, G, W>& sh, const bf16
         vraw[j] = *reinterpret_cast<const uint2*>(vpage + j * D + lane * 4);
       else
         vraw[j] = make_uint2(*reinterpret_cast<const uint32_t*>(vpage + j * D + lane * 2), 0u);
+    }
+    if constexpr (S > 0) {  // the block is in registers: its slot takes the block S turns ahead
+      __syncwarp();
+      const int next = pi + S * W;
+      if (lane == 0 && next < npages) {
+        const int s = turn % S;
+        const int64_t page = pages ? pages[next] : seq_page;
+        const uint32_t bar = sm100::smem_addr(stage->bars + s);
+        sm100::mbar_expect_tx(bar, kv_block_bytes<D>());
+        sm100::bulk_load(sm100::smem_addr(stage->slots + s * kv_block_bytes<D>()), kv + kv_offset<D>(page, hk, kh, 0, 0),
+                         kv_block_bytes<D>(), bar);
+      }
     }
     const int sub = lane % LPT;  // which 8 dims of the head this lane multiplies
     float q8[G][8];

@@ -187,45 +187,69 @@ cudaError_t launch_rope_kv(bf16* qkv, const bf16* q_norm, const bf16* k_norm, bf
 }
 
 // ---- decode attention -------------------------------------------------------------
-// The page loop lives in attend.cuh; here one CTA of four warps handles one (row, kv head).
+// The page loop lives in attend.cuh; here one CTA of four warps handles one (row, kv head). Every warp owns
+// kAttnSlots staging slots in dynamic shared memory: its K|V blocks arrive through bulk copies, kAttnSlots of them
+// ahead of the block it is working on.
+
+constexpr int kAttnSlots = 1;
 
 template <int D, int G>
 __global__ void __launch_bounds__(kAttnWarps * 32) attend_kernel(const bf16* __restrict__ qkv,
                                                                  const bf16* __restrict__ kv, bf16* __restrict__ out,
-                                                                 RowMap map, int hq, int hk, float scale) {
+                                                                 RowMap map, int hq, int hk, float scale, uint32_t* err) {
+  extern __shared__ __align__(128) unsigned char attend_slots[];
   __shared__ AttnShared<D, G> sh;
+  __shared__ __align__(8) uint64_t bars[kAttnWarps * kAttnSlots];
   const int n = blockIdx.x, kh = blockIdx.y;
   const RowAt at = locate(map, n);
   const bf16* q = qkv + ((int64_t)n * (hq + 2 * hk) + kh * G) * D;
+  if (threadIdx.x < kAttnWarps * kAttnSlots) sm100::mbar_init(sm100::smem_addr(&bars[threadIdx.x]), 1);
+  if (threadIdx.x == 0) sm100::mbar_init_fence();
   for (int i = threadIdx.x; i < G * D; i += blockDim.x) sh.qs[i / D][i % D] = __bfloat162float(q[i]);
   __syncthreads();
+  const int warp = threadIdx.x >> 5;
+  PageStage<kAttnSlots> stage{attend_slots + (size_t)warp * kAttnSlots * kv_block_bytes<D>(), bars + warp * kAttnSlots, 0u, err};
   attend_pages<D, G, kAttnWarps>(sh, kv, at.pages, at.seq, at.pos + 1, hk, kh, scale, out + ((int64_t)n * hq + kh * G) * D,
-                     threadIdx.x, sampler::CtaSync());
+                                 threadIdx.x, sampler::CtaSync(), &stage);
+}
+
+template <int D, int G>
+static cudaError_t launch_attend_dg(const bf16* qkv, const bf16* kv, bf16* out, const RowMap& map, int rows, int hq, int hk,
+                                    uint32_t* err, cudaStream_t s) {
+  constexpr size_t smem = (size_t)kAttnWarps * kAttnSlots * kv_block_bytes<D>();
+  if (smem > 48 * 1024) {  // per device and instantiation: above the default limit of dynamic shared memory
+    static bool raised[64] = {};
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return cudaErrorInvalidDevice;
+    if (!raised[device]) {
+      const cudaError_t e = cudaFuncSetAttribute(attend_kernel<D, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) return e;
+      raised[device] = true;
+    }
+  }
+  attend_kernel<D, G><<<dim3(rows, hk), kAttnWarps * 32, smem, s>>>(qkv, kv, out, map, hq, hk, 1.f / sqrtf((float)D), err);
+  return cudaGetLastError();
 }
 
 template <int D>
 static cudaError_t launch_attend_d(const bf16* qkv, const bf16* kv, bf16* out, const RowMap& map, int rows,
-                                   const AttnShape& a, cudaStream_t s) {
-  const dim3 grid(rows, a.kv_heads);
-  const float scale = 1.f / sqrtf((float)D);
+                                   const AttnShape& a, uint32_t* err, cudaStream_t s) {
   const int hq = a.q_heads, hk = a.kv_heads;
   switch (hq / hk) {
-    case 1: attend_kernel<D, 1><<<grid, kAttnWarps * 32, 0, s>>>(qkv, kv, out, map, hq, hk, scale); break;
-    case 2: attend_kernel<D, 2><<<grid, kAttnWarps * 32, 0, s>>>(qkv, kv, out, map, hq, hk, scale); break;
-    case 4: attend_kernel<D, 4><<<grid, kAttnWarps * 32, 0, s>>>(qkv, kv, out, map, hq, hk, scale); break;
-    case 5: attend_kernel<D, 5><<<grid, kAttnWarps * 32, 0, s>>>(qkv, kv, out, map, hq, hk, scale); break;
-    case 8: attend_kernel<D, 8><<<grid, kAttnWarps * 32, 0, s>>>(qkv, kv, out, map, hq, hk, scale); break;
+    case 1: return launch_attend_dg<D, 1>(qkv, kv, out, map, rows, hq, hk, err, s);
+    case 2: return launch_attend_dg<D, 2>(qkv, kv, out, map, rows, hq, hk, err, s);
+    case 4: return launch_attend_dg<D, 4>(qkv, kv, out, map, rows, hq, hk, err, s);
+    case 5: return launch_attend_dg<D, 5>(qkv, kv, out, map, rows, hq, hk, err, s);
+    case 8: return launch_attend_dg<D, 8>(qkv, kv, out, map, rows, hq, hk, err, s);
     default: return cudaErrorInvalidValue;
   }
-  return cudaGetLastError();
 }
 
 cudaError_t launch_attend(const bf16* qkv, const bf16* kv, bf16* out, const RowMap& map, int rows, const AttnShape& a,
                           uint32_t* err, cudaStream_t s) {
-  (void)err;
   if (a.q_heads % a.kv_heads) return cudaErrorInvalidValue;
-  if (a.head_dim == 128) return launch_attend_d<128>(qkv, kv, out, map, rows, a, s);
-  if (a.head_dim == 64) return launch_attend_d<64>(qkv, kv, out, map, rows, a, s);
+  if (a.head_dim == 128) return launch_attend_d<128>(qkv, kv, out, map, rows, a, err, s);
+  if (a.head_dim == 64) return launch_attend_d<64>(qkv, kv, out, map, rows, a, err, s);
   return cudaErrorInvalidValue;
 }
 

@@ -203,6 +203,49 @@ def test_rope_attend_ragged_paged(ops, oracle_lib, hq, hk, d):
     close_bf16(to_f32(out), want, ulps=3.0, floor=0.25)  # averages of O(1) values: absolute scale
 
 
+def test_rope_attend_decode_rows_over_long_paged_contexts(ops, oracle_lib):
+    """Decode rows (one per sequence) at positions from 0 to several hundred over shuffled pages: a warp of the
+    attention team then goes through its staging slots many times, and the last block holds the token written by the
+    same call. Every row equals the oracle's attention over the pool's rows 0..pos."""
+    hq, hk, d = 16, 8, 128
+    rng = np.random.default_rng(77)
+    lens = [1, 17, 129, 200, 333, 512, 64, 33]  # keys per sequence, the new token included
+    rows = len(lens)
+    n_pages = sum((n + 15) // 16 for n in lens) + 3
+    width = (hq + 2 * hk) * d
+    qkv = rand_bf16((rows, width), 21)
+    qn, kn = rand_bf16((d,), 22, 0.2) + 1, rand_bf16((d,), 23, 0.2) + 1
+    kv = rand_bf16((n_pages, hk, 2, 16, d), 24)
+    perm = rng.permutation(n_pages)
+    pos, slot, seq, indptr, pages = [], [], [], [0], []
+    at = 0
+    for s, n in enumerate(lens):
+        mine = [int(p) for p in perm[at:at + (n + 15) // 16]]
+        at += len(mine)
+        pages += mine
+        indptr.append(len(pages))
+        pos.append(n - 1)
+        slot.append(mine[(n - 1) // 16] * 16 + (n - 1) % 16)
+        seq.append(s)
+    dev = lambda a: torch.tensor(a, dtype=torch.int32, device="cuda")
+    out = torch.zeros((rows, hq * d), dtype=torch.bfloat16, device="cuda")
+    torch.cuda.synchronize()
+    ops.rope_attend(qkv, qn, kn, kv, n_pages, dev(pos), dev(slot), dev(seq), dev(indptr), dev(pages), hq, hk, d, 1e-6,
+                    1e6, out)
+    ops.sync()
+    pool = to_f32(kv)      # after the call: the new tokens' rotated keys and values are in their slots
+    q_rot = to_f32(qkv)    # and the query heads were rotated in place
+    for s, n in enumerate(lens):
+        mine = pages[indptr[s]:indptr[s + 1]]
+        rows_kv = np.zeros((n, 2 * hk * d), dtype=np.float32)
+        for t in range(n):
+            blk = pool[mine[t // 16]]  # [hk, 2, 16, d]
+            rows_kv[t, :hk * d] = blk[:, 0, t % 16, :].reshape(-1)
+            rows_kv[t, hk * d:] = blk[:, 1, t % 16, :].reshape(-1)
+        want = oracle_lib.attend(q_rot[s, :hq * d], oracle_lib.bf16_bits(rows_kv), hq, hk, d)
+        close_bf16(to_f32(out)[s:s + 1], want[None, :], ulps=3.0, floor=0.25)
+
+
 def _slots(rows, vocab):
     words = (vocab + 31) // 32
     stride = ((4 * (16 + words + (words & 1)) + 8 + 255) // 256) * 256
