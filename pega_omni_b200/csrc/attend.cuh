@@ -53,13 +53,109 @@ struct WarpSync {  // team barrier of a one-warp team
   __device__ __forceinline__ void sync() const { __syncwarp(); }
 };
 
+// One (page, kv head) K|V block in a warp's registers. Every load instruction covers contiguous memory: a K block is
+// 16 rows of D bf16 back to back, so instruction c takes bytes [512c, 512c + 512) with 16 bytes per lane (a key row
+// is spread over LPT = D/8 lanes); of a value row every lane takes its D/32 output dims.
+template <int D>
+struct KvBlock {
+  static constexpr int PV = D / 32;           // output dims per lane
+  static constexpr int LPT = D / 8;           // lanes per key row
+  static constexpr int TPI = 32 / LPT;        // key rows per load instruction
+  static constexpr int NI = 16 / TPI;         // load instructions per K block
+  Pack8 k[NI];
+  uint2 v[16];
+  // `block`: the K rows, then the V rows (global or shared memory)
+  __device__ __forceinline__ void load(const bf16* block, int lane) {
+    const bf16* vrows = block + 16 * D;
+#pragma unroll
+    for (int c = 0; c < NI; ++c) k[c] = *reinterpret_cast<const Pack8*>(block + (c * 32 + lane) * 8);
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      if constexpr (PV == 4)
+        v[j] = *reinterpret_cast<const uint2*>(vrows + j * D + lane * 4);
+      else
+        v[j] = make_uint2(*reinterpret_cast<const uint32_t*>(vrows + j * D + lane * 2), 0u);
+    }
+  }
+};
+
+// One online-softmax step of G query heads (`qs`, f32 in shared memory) over the first `ntok` keys of a block:
+// q.k with the key rows spread over lanes and finished by shuffles (lane & 15 then owns a key), the running maximum
+// and sum, then p.v with every lane on its own output dims. Whole warp.
+template <int D, int G>
+__device__ __forceinline__ void page_update(const KvBlock<D>& blk, const float (*qs)[D], int ntok, float scale, int lane,
+                                            float (&m)[G], float (&l)[G], float (&acc)[G][D / 32]) {
+  constexpr int PV = KvBlock<D>::PV, LPT = KvBlock<D>::LPT, TPI = KvBlock<D>::TPI, NI = KvBlock<D>::NI;
+  const int key = lane & 15;
+  const int sub = lane % LPT;  // which 8 dims of the head this lane multiplies
+  float q8[G][8];
+#pragma unroll
+  for (int g = 0; g < G; ++g)
+#pragma unroll
+    for (int e = 0; e < 8; ++e) q8[g][e] = qs[g][sub * 8 + e];
+  float sc[G];
+#pragma unroll
+  for (int g = 0; g < G; ++g) sc[g] = 0.f;
+#pragma unroll
+  for (int c = 0; c < NI; ++c) {
+    float kf[8];
+    unpack8(blk.k[c], kf);
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      float part = 0.f;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) part = fmaf(q8[g][e], kf[e], part);
+#pragma unroll
+      for (int o = LPT / 2; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+#pragma unroll
+      for (int gi = 0; gi < TPI; ++gi) {  // token c*TPI + gi was summed by lane group gi
+        const float v = __shfl_sync(0xffffffffu, part, gi * LPT);
+        if (key == c * TPI + gi) sc[g] = v;
+      }
+    }
+  }
+  float p[G];
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    const float s = key < ntok ? sc[g] * scale : -INFINITY;
+    const float m2 = fmaxf(m[g], warp_fmax(s));
+    const float corr = __expf(m[g] - m2);
+    p[g] = __expf(s - m2);
+    float ps = p[g];  // sum over the 16 keys (both half-warps hold the same values)
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) ps += __shfl_xor_sync(0xffffffffu, ps, o);
+    l[g] = l[g] * corr + ps;
+#pragma unroll
+    for (int d = 0; d < PV; ++d) acc[g][d] *= corr;
+    m[g] = m2;
+  }
+#pragma unroll
+  for (int j = 0; j < 16; ++j) {
+    float vf[PV];
+    if constexpr (PV == 4) {
+      const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&blk.v[j].x));
+      const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&blk.v[j].y));
+      vf[0] = a.x, vf[1] = a.y, vf[2] = b.x, vf[3] = b.y;
+    } else {
+      const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&blk.v[j].x));
+      vf[0] = a.x, vf[1] = a.y;
+    }
+    const bool live = j < ntok;  // tokens past the sequence end contribute nothing
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      const float pj = __shfl_sync(0xffffffffu, p[g], j);
+#pragma unroll
+      for (int d = 0; d < PV; ++d) acc[g][d] = live ? fmaf(pj, vf[d], acc[g][d]) : acc[g][d];
+    }
+  }
+}
+
 // tid: 0 .. 32*W-1 within the team.
 // `pages`: the sequence's page list, or nullptr when the sequence owns page `seq_page` alone (the code
-// predictor's per-frame KV). `len` keys. `out`: G heads of D, contiguous. tid: 0..127 within the team.
-// Warps take pages round-robin; q.k of a page is computed with the key rows spread over lanes and finished by
-// shuffles (lane & 15 then owns a key), then every lane owns D/32 output dims for p.v. Ends with a team barrier (sh may be reused).
+// predictor's per-frame KV). `len` keys. `out`: G heads of D, contiguous.
+// Warps take pages round-robin (block load and page step above). Ends with a team barrier (sh may be reused).
 // `stage` (optional): the warp's staging slots; the blocks then come through bulk copies, S of them ahead, and the
-// arithmetic below reads the same bytes from shared memory in the same order (results are bit-identical).
+// arithmetic reads the same bytes from shared memory in the same order (results are bit-identical).
 template <int D, int G, int W = kAttnWarps, typename TeamSync, typename Stage = NoStage>
 __device__ __forceinline__ void attend_pages(AttnShared<D, G, W>& sh, const bf16* __restrict__ kv,
                                              const int32_t* __restrict__ pages, int seq_page, int len, int hk, int kh,
@@ -68,7 +164,6 @@ __device__ __forceinline__ void attend_pages(AttnShared<D, G, W>& sh, const bf16
   constexpr int PV = D / 32;   // output dims per lane
   constexpr int S = Stage::kSlots;
   const int lane = tid & 31, warp = tid >> 5;
-  const int key = lane & 15;
   float m[G], l[G], acc[G][PV];
 #pragma unroll
   for (int g = 0; g < G; ++g) {
@@ -78,124 +173,38 @@ __device__ __forceinline__ void attend_pages(AttnShared<D, G, W>& sh, const bf16
     for (int d = 0; d < PV; ++d) acc[g][d] = 0.f;
   }
   const int npages = (len + 15) >> 4;
+  auto issue = [&](int s, int pi) {  // one lane: block `pi` of the sequence into slot s
+    if constexpr (S > 0) {
+      const int64_t page = pages ? pages[pi] : seq_page;
+      const uint32_t bar = sm100::smem_addr(stage->bars + s);
+      sm100::mbar_expect_tx(bar, kv_block_bytes<D>());
+      sm100::bulk_load(sm100::smem_addr(stage->slots + s * kv_block_bytes<D>()), kv + kv_offset<D>(page, hk, kh, 0, 0),
+                       kv_block_bytes<D>(), bar);
+    }
+  };
   if constexpr (S > 0) {
     if (lane == 0) {
 #pragma unroll
-      for (int s = 0; s < S; ++s) {
-        const int pi = warp + s * W;
-        if (pi < npages) {
-          const int64_t page = pages ? pages[pi] : seq_page;
-          const uint32_t bar = sm100::smem_addr(stage->bars + s);
-          sm100::mbar_expect_tx(bar, kv_block_bytes<D>());
-          sm100::bulk_load(sm100::smem_addr(stage->slots + s * kv_block_bytes<D>()), kv + kv_offset<D>(page, hk, kh, 0, 0),
-                           kv_block_bytes<D>(), bar);
-        }
-      }
+      for (int s = 0; s < S; ++s)
+        if (warp + s * W < npages) issue(s, warp + s * W);
     }
   }
   int turn = 0;
   for (int pi = warp; pi < npages; pi += W, ++turn) {
     const int ntok = min(16, len - pi * 16);
-    const bf16 *kpage, *vpage;
+    KvBlock<D> blk;
     if constexpr (S > 0) {
       const int s = turn % S;
       sm100::mbar_wait(sm100::smem_addr(stage->bars + s), stage->par >> s & 1u, stage->err);
       stage->par ^= 1u << s;
-      kpage = reinterpret_cast<const bf16*>(stage->slots + s * kv_block_bytes<D>());
+      blk.load(reinterpret_cast<const bf16*>(stage->slots + s * kv_block_bytes<D>()), lane);
+      __syncwarp();  // the block is in registers: its slot takes the block S turns ahead
+      if (lane == 0 && pi + S * W < npages) issue(s, pi + S * W);
     } else {
       const int64_t page = pages ? pages[pi] : seq_page;
-      kpage = kv + kv_offset<D>(page, hk, kh, 0, 0);
+      blk.load(kv + kv_offset<D>(page, hk, kh, 0, 0), lane);
     }
-    vpage = kpage + 16 * D;
-    // Every load of the page is issued before any of it is used, and every load instruction covers contiguous
-    // memory: a (page, head) K block is 16 rows of D bf16 back to back, so instruction c takes bytes
-    // [512c, 512c + 512) with 16 bytes per lane. A key row is then spread over LPT = D/8 lanes; the dot product
-    // is finished with a shuffle reduction and handed to the lane that owns the key (lane & 15).
-    constexpr int LPT = D / 8, TPI = 32 / LPT, NI = 16 / TPI;
-    Pack8 kraw[NI];
-#pragma unroll
-    for (int c = 0; c < NI; ++c) kraw[c] = *reinterpret_cast<const Pack8*>(kpage + (c * 32 + lane) * 8);
-    uint2 vraw[16];
-#pragma unroll
-    for (int j = 0; j < 16; ++j) {
-      if constexpr (PV == 4)
-        vraw[j] = *reinterpret_cast<const uint2*>(vpage + j * D + lane * 4);
-      else
-        vraw[j] = make_uint2(*reinterpret_cast<const uint32_t*>(vpage + j * D + lane * 2), 0u);
-    }
-    if constexpr (S > 0) {  // the block is in registers: its slot takes the block S turns ahead
-      __syncwarp();
-      const int next = pi + S * W;
-      if (lane == 0 && next < npages) {
-        const int s = turn % S;
-        const int64_t page = pages ? pages[next] : seq_page;
-        const uint32_t bar = sm100::smem_addr(stage->bars + s);
-        sm100::mbar_expect_tx(bar, kv_block_bytes<D>());
-        sm100::bulk_load(sm100::smem_addr(stage->slots + s * kv_block_bytes<D>()), kv + kv_offset<D>(page, hk, kh, 0, 0),
-                         kv_block_bytes<D>(), bar);
-      }
-    }
-    const int sub = lane % LPT;  // which 8 dims of the head this lane multiplies
-    float q8[G][8];
-#pragma unroll
-    for (int g = 0; g < G; ++g)
-#pragma unroll
-      for (int e = 0; e < 8; ++e) q8[g][e] = sh.qs[g][sub * 8 + e];
-    float sc[G];
-#pragma unroll
-    for (int g = 0; g < G; ++g) sc[g] = 0.f;
-#pragma unroll
-    for (int c = 0; c < NI; ++c) {
-      float kf[8];
-      unpack8(kraw[c], kf);
-#pragma unroll
-      for (int g = 0; g < G; ++g) {
-        float part = 0.f;
-#pragma unroll
-        for (int e = 0; e < 8; ++e) part = fmaf(q8[g][e], kf[e], part);
-#pragma unroll
-        for (int o = LPT / 2; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
-#pragma unroll
-        for (int gi = 0; gi < TPI; ++gi) {  // token c*TPI + gi was summed by lane group gi
-          const float v = __shfl_sync(0xffffffffu, part, gi * LPT);
-          if (key == c * TPI + gi) sc[g] = v;
-        }
-      }
-    }
-    float p[G];
-#pragma unroll
-    for (int g = 0; g < G; ++g) {
-      const float s = key < ntok ? sc[g] * scale : -INFINITY;
-      const float m2 = fmaxf(m[g], warp_fmax(s));
-      const float corr = __expf(m[g] - m2);
-      p[g] = __expf(s - m2);
-      float ps = p[g];  // sum over the 16 keys (both half-warps hold the same values)
-#pragma unroll
-      for (int o = 8; o > 0; o >>= 1) ps += __shfl_xor_sync(0xffffffffu, ps, o);
-      l[g] = l[g] * corr + ps;
-#pragma unroll
-      for (int d = 0; d < PV; ++d) acc[g][d] *= corr;
-      m[g] = m2;
-    }
-#pragma unroll
-    for (int j = 0; j < 16; ++j) {
-      float vf[PV];
-      if constexpr (PV == 4) {
-        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&vraw[j].x));
-        const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&vraw[j].y));
-        vf[0] = a.x, vf[1] = a.y, vf[2] = b.x, vf[3] = b.y;
-      } else {
-        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&vraw[j].x));
-        vf[0] = a.x, vf[1] = a.y;
-      }
-      const bool live = j < ntok;  // tokens past the sequence end contribute nothing
-#pragma unroll
-      for (int g = 0; g < G; ++g) {
-        const float pj = __shfl_sync(0xffffffffu, p[g], j);
-#pragma unroll
-        for (int d = 0; d < PV; ++d) acc[g][d] = live ? fmaf(pj, vf[d], acc[g][d]) : acc[g][d];
-      }
-    }
+    page_update<D, G>(blk, sh.qs, ntok, scale, lane, m, l, acc);
   }
   if constexpr (W == 1) {
     // the merge below would multiply by exp(0) = 1: the same quotient, straight from the registers

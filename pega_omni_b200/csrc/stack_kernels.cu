@@ -217,7 +217,7 @@ template <int D, int G>
 static cudaError_t launch_attend_dg(const bf16* qkv, const bf16* kv, bf16* out, const RowMap& map, int rows, int hq, int hk,
                                     uint32_t* err, cudaStream_t s) {
   constexpr size_t smem = (size_t)kAttnWarps * kAttnSlots * kv_block_bytes<D>();
-  if (smem > 48 * 1024) {  // per device and instantiation: above the default limit of dynamic shared memory
+  if (smem + sizeof(AttnShared<D, G>) > 40 * 1024) {  // per device and instantiation: above the default limit of dynamic shared memory
     static bool raised[64] = {};
     int device = 0;
     if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return cudaErrorInvalidDevice;
