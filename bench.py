@@ -266,6 +266,7 @@ def run_higgs(args, rank, world, local):
     kv_token = b.num_hidden_layers * 2 * b.num_key_value_heads * b.head_dim * 2
     kv_gib = 1.3 * n * (plen + W + K + 32) * kv_token / 2 ** 30
     model = HiggsModel.load(local, ck, c, max_batch=n, max_tokens=max(2048, plen), kv_gib=max(kv_gib, 0.5))
+    model.warmup()  # every bucket's graph before the first live step, as the reference's Model::warmup does
     del ck
     torch.cuda.empty_cache()
     rng = np.random.default_rng(200 + rank)
@@ -308,7 +309,7 @@ def run_higgs(args, rank, world, local):
             "config": {"workload": "configs[4]: Higgs-style body (36L h2560 20q/4kv d128 i9728) + tied 8 x 1026 head, "
                                    "random bf16 weights", "sessions_per_gpu": n, "prompt_tokens": plen,
                        "sampling": "T 1.0, top-k 50, delay-pattern ramp",
-                       "engine": "per-op launches (no CUDA graph, no persistent kernel yet)"},
+                       "engine": "one kernel per op, one CUDA graph per session bucket"},
             "step_p50_ms": float(np.percentile(dev_ms, 50)), "step_p99_ms": float(np.percentile(dev_ms, 99)),
             "rows_per_s": n * world * K / float(t_wall.item()),
             "gpu_launches": int(launches * K), "launches_per_step": int(launches), "clocks": clocks.summary(),
@@ -323,7 +324,8 @@ def run_higgs(args, rank, world, local):
 def run_duplex(args, rank, world, local):
     """The PersonaPlex-7B tick (Helium 32 x 4096 + depformer 8 x 6 x 1024) at `--sessions` sessions per GPU: W warm-up
     ticks, K timed ticks through `Model.tick` (host staging and read-back inside), CUDA-event device time per tick from
-    the library. Per-op launches, no CUDA graph yet."""
+    the library. One kernel per op, the tick replayed as one CUDA graph per session bucket (captured by `warmup`).
+    `--prompt` rows are prefilled per session, so `--prompt 2990` measures the full 3,000-slot ring."""
     import dataclasses
     import torch
     import torch.distributed as dist
@@ -333,6 +335,7 @@ def run_duplex(args, rank, world, local):
     ck = random_checkpoint(c, seed=0, device=f"cuda:{local}", head_std=0.05)
     plen = args.prompt if args.prompt != 128 else 4  # --prompt: rows prefilled per session (default 4: near-empty ring)
     model = Model.load(local, ck, c, max_sessions=n, max_prefill=max(2048, plen))
+    model.warmup()  # every bucket's graph before the first live tick (model.rs:202-240 of the reference)
     del ck
     torch.cuda.empty_cache()
     rng = np.random.default_rng(100 + rank)
@@ -381,7 +384,7 @@ def run_duplex(args, rank, world, local):
             "config": {"workload": "configs[3]: PersonaPlex-7B shapes (Helium 32L d4096 32 heads hidden 11264; depformer "
                                    "8 steps x 6L d1024), random bf16 weights", "sessions_per_gpu": n,
                        "context": c.context, "positions": [plen + W, plen + W + K - 1],
-                       "engine": "per-op launches (no CUDA graph, no persistent kernel yet)"},
+                       "engine": "one kernel per op, one CUDA graph per session bucket"},
             "tick_p50_ms": float(np.percentile(dev_ms, 50)), "tick_p99_ms": float(np.percentile(dev_ms, 99)),
             "frames_per_s": n * world * K / float(t_wall.item()),
             "gpu_launches": int(launches * K), "launches_per_tick": int(launches), "clocks": clocks.summary(),
@@ -530,6 +533,8 @@ def main():
     ap.add_argument("--no-graphs", action="store_true")
     ap.add_argument("--no-replay", action="store_true", help="skip timing the reference's kernels on this GPU")
     ap.add_argument("--per-op", action="store_true", help="one kernel per op (CUDA graph) instead of the tick kernel")
+    ap.add_argument("--cluster-predictor", action="store_true",
+                    help="tick_kernel = 3: the predictor's sub-steps as one launch of thread-block clusters (measured slower)")
     ap.add_argument("--prompt-max", type=int, default=0, help="sweep: prompt lengths uniform in [--prompt, --prompt-max]")
     ap.add_argument("--workload", default="talker", choices=["talker", "duplex", "higgs", "sweep", "attend"],
                     help="talker: the headline Qwen3-TTS tick (default); duplex: the PersonaPlex-7B tick (configs[3]); "
@@ -579,7 +584,7 @@ def main():
     frames_cap = 2 * (W + K) + 8
     kv_gib = max(1.0, 1.25 * args.sessions * (args.prompt + frames_cap + 16) * cfg.talker.kv_bytes_per_token() / 2 ** 30)
     model = Model.load(local, ck, cfg, Limits(args.sessions, args.sessions * args.prompt, kv_gib),
-                       use_graphs=not args.no_graphs, tick_kernel=not args.per_op)
+                       use_graphs=not args.no_graphs, tick_kernel=0 if args.per_op else (3 if args.cluster_predictor else 1))
     if args.trace:
         model.trace(args.trace)
     ck_host = None
@@ -677,7 +682,8 @@ def main():
         per_pass = p_cfg.num_hidden_layers * p_cfg.layer_weight_bytes() + 2 * p_cfg.hidden_size * t_cfg.hidden_size
         once_bytes = tick_bytes - (cfg.num_code_groups - 2) * per_pass
         # the dominant kernel IS the tick: one persistent cooperative launch per step (or, with --per-op, the graph)
-        roof = {"bound": "hbm", "kernel": "tick_kernel + pred_kernel (whole decode tick)" if launches_per_tick <= 2 else "per-op graph",
+        roof = {"bound": "hbm", "kernel": ("tick_kernel (one launch = one decode tick)" if launches_per_tick == 1 else
+                           "tick_kernel + pred_kernel" if launches_per_tick == 2 else "per-op graph"),
                 "achieved": tick_bytes / tick_s / 1e9, "peak": peak, "unit": "GB/s",
                 "frac": tick_bytes / tick_s / 1e9 / peak, "peak_source": f"of {peak_kind}",
                 "frac_nominal": tick_bytes / tick_s / 1e9 / 8000.0, "peak_nominal": 8000.0,
