@@ -260,7 +260,8 @@ def run_higgs(args, rank, world, local):
     W, K = max(3, args.warmup), args.steps
     n = args.sessions if args.sessions != 64 else 32  # configs[4]: 32 sessions
     plen = args.prompt if args.prompt != 128 else 256
-    c = HIGGS_PRESETS["higgs-4b"]
+    import dataclasses
+    c = dataclasses.replace(HIGGS_PRESETS["higgs-4b"], audio_adapter=args.audio_adapter)
     ck = higgs_random_checkpoint(c, seed=0, device=f"cuda:{local}", embed_std=0.02)
     b = c.body
     kv_token = b.num_hidden_layers * 2 * b.num_key_value_heads * b.head_dim * 2
@@ -308,6 +309,7 @@ def run_higgs(args, rank, world, local):
             "higher_is_better": False, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": "configs[4]: Higgs-style body (36L h2560 20q/4kv d128 i9728) + tied 8 x 1026 head, "
                                    "random bf16 weights", "sessions_per_gpu": n, "prompt_tokens": plen,
+                       "audio_adapter": bool(c.audio_adapter),
                        "sampling": "T 1.0, top-k 50, delay-pattern ramp",
                        "engine": "one kernel per op, one CUDA graph per session bucket"},
             "step_p50_ms": float(np.percentile(dev_ms, 50)), "step_p99_ms": float(np.percentile(dev_ms, 99)),
@@ -533,6 +535,8 @@ def main():
     ap.add_argument("--no-graphs", action="store_true")
     ap.add_argument("--no-replay", action="store_true", help="skip timing the reference's kernels on this GPU")
     ap.add_argument("--per-op", action="store_true", help="one kernel per op (CUDA graph) instead of the tick kernel")
+    ap.add_argument("--audio-adapter", action="store_true",
+                    help="higgs: every layer carries the audio-only MLP of configs[4] beside its MLP (run on every decode row)")
     ap.add_argument("--cluster-predictor", action="store_true",
                     help="tick_kernel = 3: the predictor's sub-steps as one launch of thread-block clusters (measured slower)")
     ap.add_argument("--prompt-max", type=int, default=0, help="sweep: prompt lengths uniform in [--prompt, --prompt-max]")

@@ -34,6 +34,12 @@ typedef struct omni_higgs_config {
   int32_t max_tokens; /* prompt rows per `start` */
   double kv_gib;      /* KV pool size */
   int32_t use_graphs; /* 1: the decode step's kernels replayed as one CUDA graph per bucket; 0: launched one by one */
+  int32_t audio_adapter; /* 1: every layer carries a second, audio-only MLP of the same width beside its MLP (tensors
+                            body.layers.{i}.audio_mlp.{gate,up,down}_proj.weight); on audio positions (the frame rows of
+                            `start`'s first draw onwards, i.e. every decode step) both run on the same normed input and
+                            their down projections are summed in f32 before the one bf16 rounding; text positions (the
+                            prompt) use the plain MLP alone. No counterpart in the reference, whose Higgs body is the
+                            plain Qwen3 stack (model.rs:339-405). 0: off */
 } omni_higgs_config;
 
 /* `Draw` (model.rs:99-104): a uniform per codebook, and the codes to take instead; force[b] < 0 in EVERY codebook means

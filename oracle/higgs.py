@@ -71,6 +71,15 @@ class HiggsOracle:
                 o=w[p + "self_attn.o_proj.weight"],
                 gate_up=np.concatenate([w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"]]),
                 down=w[p + "mlp.down_proj.weight"]))
+            if getattr(cfg, "audio_adapter", False):
+                # an audio position's MLP: the text and the audio branch side by side along the channel axis, so the
+                # down projection sums both branches in f32 before its one bf16 rounding (this library's definition:
+                # the reference's Higgs body has no such adapter)
+                self.layers[-1]["gate_up_audio"] = np.concatenate(
+                    [w[p + "mlp.gate_proj.weight"], w[p + "audio_mlp.gate_proj.weight"],
+                     w[p + "mlp.up_proj.weight"], w[p + "audio_mlp.up_proj.weight"]])
+                self.layers[-1]["down_audio"] = np.concatenate(
+                    [w[p + "mlp.down_proj.weight"], w[p + "audio_mlp.down_proj.weight"]], axis=1)
         self.norm = w["body.norm.weight"]
         self.text = cpu.bits_to_f32(w["tied.embedding.text_embedding.weight"])
         self.fused_bits = w["tied.embedding.modality_embeddings.0.embedding.weight"]
@@ -86,8 +95,9 @@ class HiggsOracle:
                               kv=[[] for _ in self.layers])
         return sid
 
-    def _body_row(self, s, x_in, pos):
-        """One row through every layer (stack.rs:152-203); returns the final norm's row."""
+    def _body_row(self, s, x_in, pos, audio=False):
+        """One row through every layer (stack.rs:152-203); returns the final norm's row. `audio`: the row is an audio
+        position (a frame row), whose MLP includes the audio branch when the model has the adapter."""
         b = self.c.body
         hq, hk, d = b.num_attention_heads, b.num_key_value_heads, b.head_dim
         x, res = cpu.norm_copy(x_in[None, :], self.layers[0]["ln1"], b.rms_norm_eps)
@@ -104,8 +114,9 @@ class HiggsOracle:
             attn = cpu.attend(q.ravel(), np.stack(s["kv"][i]), hq, hk, d)
             o = cpu.gemm(attn[None, :], L["o"])
             x, res = cpu.add_norm(o, res, L["ln2"], b.rms_norm_eps)
-            act = cpu.silu_mul(cpu.gemm(x, L["gate_up"]))
-            down = cpu.gemm(act, L["down"])
+            both = audio and "gate_up_audio" in L
+            act = cpu.silu_mul(cpu.gemm(x, L["gate_up_audio" if both else "gate_up"]))
+            down = cpu.gemm(act, np.ascontiguousarray(L["down_audio"]) if both else L["down"])
             nxt = self.layers[i + 1]["ln1"] if i + 1 < len(self.layers) else self.norm
             x, res = cpu.add_norm(down, res, nxt, b.rms_norm_eps)
         return x[0]
@@ -153,5 +164,5 @@ class HiggsOracle:
             acc = np.zeros(c.body.hidden_size, np.float32)
             for b in range(BOOKS):  # f32 sum in codebook order, one rounding (higgs.cu:24-37)
                 acc = acc + self.fused[b * c.code_vocab + s["codes"][b]]
-            hidden.append(self._body_row(s, cpu.bf16_round(acc), s["prompt"] + s["rows"] - 1))
+            hidden.append(self._body_row(s, cpu.bf16_round(acc), s["prompt"] + s["rows"] - 1, audio=True))
         return self._tail(rows, hidden)

@@ -33,6 +33,9 @@ namespace {
 
 struct Layer {
   bf16 *ln1, *qkv, *q_norm, *k_norm, *o, *ln2, *gate_up, *down;
+  // with the audio-FFN adapter: the MLP of an audio position, text and audio branch fused along the channel axis:
+  // [gate_text; gate_audio; up_text; up_audio] (4I x h) and [down_text | down_audio] (h x 2I)
+  bf16 *gate_up_audio = nullptr, *down_audio = nullptr;
 };
 
 uint16_t f2bf(float f) {
@@ -199,9 +202,13 @@ int gemm(omni_higgs* m, const bf16* w, int N, int K, const bf16* x, int rows, bf
 }
 
 // One pass of the body over `rows` rows of `input`: `Stack::forward` (stack.rs:152-203); the final norm's rows go to out.
-int body_forward(omni_higgs* m, const bf16* input, int rows, const RowMap& map, bf16* out) {
+// `audio`: every row is an audio position. With the audio-FFN adapter such a row's MLP is the text branch and the audio
+// branch side by side — one gate|up GEMM over both branches' channels, SwiGLU, one down GEMM whose K runs over both
+// branches' activations, so the two branches' outputs are summed in f32 before the one bf16 rounding.
+int body_forward(omni_higgs* m, const bf16* input, int rows, const RowMap& map, bf16* out, bool audio) {
   const omni_stack_config& c = m->cfg.body;
-  const int h = c.hidden, I = c.inter, qd = c.q_heads * c.head_dim, qw = m->qkv_width();
+  const bool both = audio && m->cfg.audio_adapter != 0;
+  const int h = c.hidden, I = both ? 2 * c.inter : c.inter, qd = c.q_heads * c.head_dim, qw = m->qkv_width();
   const AttnShape a{c.q_heads, c.kv_heads, c.head_dim, c.rms_eps, c.rope_theta};
   HLAUNCH(m, launch_norm_copy(input, m->layers[0].ln1, m->x, m->res, rows, h, c.rms_eps, m->stream));
   for (int i = 0; i < c.layers; ++i) {
@@ -211,9 +218,9 @@ int body_forward(omni_higgs* m, const bf16* input, int rows, const RowMap& map, 
     HLAUNCH(m, launch_attend(m->qkv, m->kv[i], m->attn, map, rows, a, m->err, m->stream));
     HTRY(gemm(m, L.o, h, qd, m->attn, rows, m->x, h));
     HLAUNCH(m, launch_add_norm(m->x, m->res, L.ln2, m->x, rows, h, c.rms_eps, 1, 0, m->stream));
-    HTRY(gemm(m, L.gate_up, 2 * I, h, m->x, rows, m->gate_up, 2 * I));
+    HTRY(gemm(m, both ? L.gate_up_audio : L.gate_up, 2 * I, h, m->x, rows, m->gate_up, 2 * I));
     HLAUNCH(m, launch_silu_mul(m->gate_up, m->act, rows, I, 0, m->stream));
-    HTRY(gemm(m, L.down, h, I, m->act, rows, m->x, h));
+    HTRY(gemm(m, both ? L.down_audio : L.down, h, I, m->act, rows, m->x, h));
     const bf16* next = i + 1 < c.layers ? m->layers[i + 1].ln1 : m->norm;
     HLAUNCH(m, launch_add_norm(m->x, m->res, next, i + 1 < c.layers ? m->x : out, rows, h, c.rms_eps, 1, 0, m->stream));
   }
@@ -328,6 +335,7 @@ int32_t omni_higgs_create(const omni_higgs_config* config, const omni_tensor* te
     if (tensors[i].name) idx[tensors[i].name] = &tensors[i];
   const int64_t h = b.hidden, d = b.head_dim, q = (int64_t)b.q_heads * d, kvw = (int64_t)b.kv_heads * d, I = b.inter;
   m->layers.resize(b.layers);
+  bf16* adapter_tmp = nullptr;  // staging for the audio branch's down projection (stays allocated with the model)
   for (int i = 0; i < b.layers; ++i) {  // `Stack::load` (stack.rs:93-141): Q|K|V rows and gate|up rows fused
     const std::string p = "body.layers." + std::to_string(i) + ".";
     Layer& L = m->layers[i];
@@ -350,6 +358,18 @@ int32_t omni_higgs_create(const omni_higgs_config* config, const omni_tensor* te
     HTRY(upload(m, idx, p + "mlp.gate_proj.weight", {I, h}, L.gate_up));
     HTRY(upload(m, idx, p + "mlp.up_proj.weight", {I, h}, L.gate_up + I * h));
     HTRY(upload(m, idx, p + "mlp.down_proj.weight", {h, I}, L.down));
+    if (c.audio_adapter) {
+      HTRY(halloc(m, &L.gate_up_audio, 4 * I * h));
+      HTRY(halloc(m, &L.down_audio, h * 2 * I));
+      HCUDA(m, cudaMemcpy(L.gate_up_audio, L.gate_up, I * h * 2, cudaMemcpyDeviceToDevice));
+      HTRY(upload(m, idx, p + "audio_mlp.gate_proj.weight", {I, h}, L.gate_up_audio + I * h));
+      HCUDA(m, cudaMemcpy(L.gate_up_audio + 2 * I * h, L.gate_up + I * h, I * h * 2, cudaMemcpyDeviceToDevice));
+      HTRY(upload(m, idx, p + "audio_mlp.up_proj.weight", {I, h}, L.gate_up_audio + 3 * I * h));
+      if (!adapter_tmp) HTRY(halloc(m, &adapter_tmp, h * I));
+      HTRY(upload(m, idx, p + "audio_mlp.down_proj.weight", {h, I}, adapter_tmp));
+      HCUDA(m, cudaMemcpy2D(L.down_audio, 2 * I * 2, L.down, I * 2, I * 2, h, cudaMemcpyDeviceToDevice));
+      HCUDA(m, cudaMemcpy2D(L.down_audio + I, 2 * I * 2, adapter_tmp, I * 2, I * 2, h, cudaMemcpyDeviceToDevice));
+    }
   }
   HTRY(halloc(m, &m->norm, h));
   HTRY(upload(m, idx, "body.norm.weight", {h}, m->norm));
@@ -378,8 +398,9 @@ int32_t omni_higgs_create(const omni_higgs_config* config, const omni_tensor* te
   HTRY(halloc(m, &m->res, R * h));
   HTRY(halloc(m, &m->qkv, R * (q + 2 * kvw)));
   HTRY(halloc(m, &m->attn, R * q));
-  HTRY(halloc(m, &m->gate_up, R * 2 * I));
-  HTRY(halloc(m, &m->act, R * I));
+  const size_t Iw = c.audio_adapter ? 2 * I : I;  // widest MLP a row goes through
+  HTRY(halloc(m, &m->gate_up, R * 2 * Iw));
+  HTRY(halloc(m, &m->act, R * Iw));
   HTRY(halloc(m, &m->hidden, (size_t)c.max_batch * h, true));
   HTRY(halloc(m, &m->logits, (size_t)c.max_batch * head, true));
   HTRY(halloc(m, &m->codes, (size_t)c.max_batch * OMNI_HIGGS_CODEBOOKS, true));
@@ -502,7 +523,7 @@ int32_t omni_higgs_start(omni_higgs* m, int32_t n, omni_higgs_seq* const* seqs, 
   map.seq = st.dev(seq);
   map.indptr = st.dev(indptr);
   map.pages = st.dev(pages);
-  HTRY(body_forward(m, m->embeds, total, map, m->x));
+  HTRY(body_forward(m, m->embeds, total, map, m->x, false));  // prompt rows are text positions
   HLAUNCH(m, launch_gather(st.dev(last), 1, m->x, total, m->hidden, n, c.body.hidden, m->err, m->stream));
   return tail(m, n, seqs, st.dev(uniforms), st.dev(force), st.dev(lines), rows_out, ended_out);
 }
@@ -568,7 +589,7 @@ int step_rows(omni_higgs* m, int n, int b, omni_higgs_seq* const* seqs, const om
     map.seq = nullptr;
     map.indptr = st.dev(indptr);
     map.pages = st.dev(pages);
-    HTRY(body_forward(m, m->embeds, b, map, m->hidden));
+    HTRY(body_forward(m, m->embeds, b, map, m->hidden, true));  // frame rows are audio positions
     return tail_kernels(m, b, st.dev(uniforms), st.dev(force), st.dev(lines));
   };
   omni_higgs::StepGraph& sg = m->step_graphs[b];

@@ -63,11 +63,15 @@ class HiggsConfig:
     code_vocab: int = VOCAB
     temperature: float = 1.0
     top_k: int = 50
+    # a second, audio-only MLP of the same width beside every layer's MLP, run on audio positions (every decode row);
+    # the reference's Higgs body has none
+    audio_adapter: bool = False
 
     def step_weight_bytes(self) -> int:
         b = self.body
         q, kv = b.num_attention_heads * b.head_dim, b.num_key_value_heads * b.head_dim
-        layer = (q + 2 * kv) * b.hidden_size + b.hidden_size * q + 3 * b.intermediate_size * b.hidden_size
+        mlps = 2 if self.audio_adapter else 1
+        layer = (q + 2 * kv) * b.hidden_size + b.hidden_size * q + mlps * 3 * b.intermediate_size * b.hidden_size
         return 2 * (b.num_hidden_layers * layer + CODEBOOKS * self.code_vocab * b.hidden_size)
 
 
@@ -100,6 +104,10 @@ def higgs_tensor_shapes(c: HiggsConfig):
         yield p + "mlp.gate_proj.weight", (i, h)
         yield p + "mlp.up_proj.weight", (i, h)
         yield p + "mlp.down_proj.weight", (h, i)
+        if c.audio_adapter:
+            yield p + "audio_mlp.gate_proj.weight", (i, h)
+            yield p + "audio_mlp.up_proj.weight", (i, h)
+            yield p + "audio_mlp.down_proj.weight", (h, i)
     yield "body.norm.weight", (h,)
     yield "tied.embedding.text_embedding.weight", (b.vocab_size, h)
     yield "tied.embedding.modality_embeddings.0.embedding.weight", (CODEBOOKS * c.code_vocab, h)
@@ -159,7 +167,7 @@ class HiggsModel:
         body = L.StackCfg(b.hidden_size, b.intermediate_size, b.num_hidden_layers, b.num_attention_heads,
                           b.num_key_value_heads, b.head_dim, b.vocab_size, b.rms_norm_eps, b.rope_theta)
         cfg = L.HiggsCfg(body, config.code_vocab, config.temperature, config.top_k, max_batch, max_tokens, kv_gib,
-                         int(use_graphs))
+                         int(use_graphs), int(config.audio_adapter))
         tensors, keep = c_tensors(checkpoint)
         h = C.c_void_p()
         rc = lib.omni_higgs_create(C.byref(cfg), tensors, len(checkpoint), device, C.byref(h))

@@ -65,7 +65,8 @@ class DuplexStep(C.Structure):
 
 class HiggsCfg(C.Structure):
     _fields_ = [("body", StackCfg), ("code_vocab", C.c_int32), ("temperature", C.c_float), ("top_k", C.c_int32),
-                ("max_batch", C.c_int32), ("max_tokens", C.c_int32), ("kv_gib", C.c_double), ("use_graphs", C.c_int32)]
+                ("max_batch", C.c_int32), ("max_tokens", C.c_int32), ("kv_gib", C.c_double), ("use_graphs", C.c_int32),
+                ("audio_adapter", C.c_int32)]
 
 
 class HiggsDraw(C.Structure):

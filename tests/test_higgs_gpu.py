@@ -106,14 +106,18 @@ def _cos(a, b):
     return float(a @ b / (np.linalg.norm(a) * np.linalg.norm(b) + 1e-30))
 
 
-@pytest.mark.parametrize("preset,n", [("higgs-tiny", 3), ("higgs-mid", 10)])
-def test_model_steps_match_oracle(built_lib, oracle_lib, preset, n):
+@pytest.mark.parametrize("preset,n,adapter", [("higgs-tiny", 3, False), ("higgs-mid", 10, False),
+                                              ("higgs-tiny", 3, True), ("higgs-mid", 10, True)])
+def test_model_steps_match_oracle(built_lib, oracle_lib, preset, n, adapter):
     """The Higgs model shell (prefill, first draw, decode steps) against the CPU oracle with forced rows: codes exact,
     logits of every step within two bf16 steps; 3 sequences take the vector GEMM path, 10 the tensor-core path; both
-    presets have 5 query heads per kv head like the full model."""
+    presets have 5 query heads per kv head like the full model. With `adapter` every layer carries the audio-only MLP
+    beside its MLP: prompt rows go through the plain MLP, frame rows through both (oracle-only parity: the reference
+    has no such adapter)."""
+    import dataclasses
     from oracle.higgs import HiggsOracle
     from pega_omni_b200.higgs import HIGGS_PRESETS, HiggsDraw, HiggsModel, higgs_random_checkpoint
-    c = HIGGS_PRESETS[preset]
+    c = dataclasses.replace(HIGGS_PRESETS[preset], audio_adapter=adapter)
     # the tied table is also the head: N(0, 0.06) keeps logits at |x| < 4, where a bf16 step is at most 1.6e-2
     ck = higgs_random_checkpoint(c, seed=1, embed_std=0.06)
     m = HiggsModel.load(0, ck, c, max_batch=16, max_tokens=512, kv_gib=0.05)
