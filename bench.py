@@ -333,14 +333,21 @@ def run_duplex(args, rank, world, local):
     import torch.distributed as dist
     from pega_omni_b200.duplex import PRESETS, Model, Prompt, Step, random_checkpoint
     W, K, n = max(3, args.warmup), args.steps, args.sessions
+    tp = args.tp if args.tp > 1 else 1
+    if tp > 1 and (world % tp or tp != 2):
+        raise SystemExit("--tp 2 needs an even number of ranks (torchrun --nproc-per-node 2)")
     c = dataclasses.replace(PRESETS["personaplex-7b"], context=args.context)
     ck = random_checkpoint(c, seed=0, device=f"cuda:{local}", head_std=0.05)
     plen = args.prompt if args.prompt != 128 else 4  # --prompt: rows prefilled per session (default 4: near-empty ring)
-    model = Model.load(local, ck, c, max_sessions=n, max_prefill=max(2048, plen))
+    model = Model.load(local, ck, c, max_sessions=n, max_prefill=max(2048, plen), tp_rank=rank % tp, tp_size=tp)
+    if tp > 1:  # ranks 2g and 2g + 1 form a pair: each maps the other's exchange region
+        handles = [None] * world
+        dist.all_gather_object(handles, model.tp_export())
+        model.tp_connect(handles[rank ^ 1])
     model.warmup()  # every bucket's graph before the first live tick (model.rs:202-240 of the reference)
     del ck
     torch.cuda.empty_cache()
-    rng = np.random.default_rng(100 + rank)
+    rng = np.random.default_rng(100 + rank // tp)  # the two ranks of a pair play the same sessions
     sessions = [model.open() for _ in range(n)]
     per_call = max(1, 2048 // plen)  # prompts per prefill call
     for i in range(0, n, per_call):
@@ -377,6 +384,9 @@ def run_duplex(args, rank, world, local):
         mean_len = plen + W + (K - 1) / 2 + 1
         kv_bytes = n * min(mean_len, c.context) * c.layers * (2 * c.heads * 128 + 2 * c.heads * 4)
         tick_bytes = c.tick_weight_bytes() + kv_bytes
+        if tp > 1:  # per GPU: half of Helium's layer weights and of the ring, everything else whole
+            layers_bytes = 2 * c.layers * (4 * c.dim * c.dim + 3 * c.hidden * c.dim)
+            tick_bytes = c.tick_weight_bytes() - layers_bytes // 2 + kv_bytes / 2
         tick_s = float(np.mean(dev_ms)) * 1e-3
         print(json.dumps({
             "metric": "PersonaPlex tick ms (device) at %d sessions per GPU" % n, "value": float(np.mean(dev_ms)),
@@ -388,13 +398,20 @@ def run_duplex(args, rank, world, local):
                        "context": c.context, "positions": [plen + W, plen + W + K - 1],
                        "engine": "one kernel per op, one CUDA graph per session bucket"},
             "tick_p50_ms": float(np.percentile(dev_ms, 50)), "tick_p99_ms": float(np.percentile(dev_ms, 99)),
-            "frames_per_s": n * world * K / float(t_wall.item()),
+            "frames_per_s": n * (world // tp) * K / float(t_wall.item()),
+            "tensor_parallel": None if tp == 1 else {
+                "ranks_per_model": tp, "exchanges_per_tick": 2 * c.layers,
+                "nvlink_bytes_per_tick_per_direction": 2 * c.layers * n * c.dim * 2,
+                "how": "partial rows of the o and down projections read from the peer's buffer inside the add + norm "
+                       "kernel (plain peer loads, flag words, bounded waits); no collective library on the data path"},
             "gpu_launches": int(launches * K), "launches_per_tick": int(launches), "clocks": clocks.summary(),
             "roofline": {"bound": "hbm", "kernel": "whole tick (%d launches)" % launches,
                          "achieved": tick_bytes / tick_s / 1e9, "peak": peak, "unit": "GB/s",
                          "frac": tick_bytes / tick_s / 1e9 / peak, "peak_source": f"of {peak_kind}", "traffic": None},
             "reference_published": "15.0 ms p50 / 15.9 ms p99 at 128 sessions on GB300, Mimi codec included "
                                    "(docs/personaplex.md:105-111 of the reference)"}))
+    if tp > 1:
+        dist.barrier()  # neither rank unmaps its exchange region while the other may still be reading it
     model.close()
 
 
@@ -535,6 +552,7 @@ def main():
     ap.add_argument("--no-graphs", action="store_true")
     ap.add_argument("--no-replay", action="store_true", help="skip timing the reference's kernels on this GPU")
     ap.add_argument("--per-op", action="store_true", help="one kernel per op (CUDA graph) instead of the tick kernel")
+    ap.add_argument("--tp", type=int, default=1, help="duplex: 2 = Helium split over a pair of GPUs (run under torchrun with 2 ranks)")
     ap.add_argument("--audio-adapter", action="store_true",
                     help="higgs: every layer carries the audio-only MLP of configs[4] beside its MLP (run on every decode row)")
     ap.add_argument("--cluster-predictor", action="store_true",

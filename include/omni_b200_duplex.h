@@ -41,6 +41,8 @@ typedef struct omni_duplex_config {
   int32_t max_prefill;  /* prompt rows per `start` call */
   int32_t voice_rows;   /* rows of the optional "voices" tensor [voice_rows, dim] (0: none) */
   int32_t use_graphs;   /* 1: the tick's kernels replayed as one CUDA graph per bucket; 0: launched one by one */
+  int32_t tp_rank, tp_size; /* tp_size = 2: this model is rank tp_rank (0 or 1) of a tensor-parallel pair, one process
+                               and one GPU per rank (below); 0 or 1: the whole model on one GPU */
 } omni_duplex_config;
 
 /* `Step` (model.rs:98-107) without the PCM: tokens to take instead of drawing (-1 draws), the caller's codes to
@@ -99,6 +101,23 @@ int32_t omni_duplex_warm_prefix(omni_duplex* m, int32_t rows, const int32_t* ids
  * model.rs:392-396). */
 int32_t omni_duplex_start(omni_duplex* m, int32_t n, omni_duplex_session* const* sessions, const int32_t* row_counts,
                           const int32_t* ids, const int32_t* voice, const int32_t* init, const int32_t* first_force);
+
+/* Tensor-parallel pair for Helium (no counterpart in the reference, which has no multi-GPU path). Rank r holds heads
+ * [r * heads/2, (r+1) * heads/2) and MLP channels [r * hidden/2, (r+1) * hidden/2): its `create` is given
+ *   h.l{i}.qkv     [3 * dim/2, dim]  = the q rows, the k rows and the v rows of its heads, in that order,
+ *   h.l{i}.o       [dim, dim/2]      = the columns of its heads,
+ *   h.l{i}.gate_up [2 * hidden/2, dim] = its gate rows, then its up rows,
+ *   h.l{i}.down    [dim, hidden/2]   = its columns,
+ * every other tensor whole (embeddings, norms, heads and the depformer are replicated; each rank's ring KV holds its
+ * own heads only). After the o and the down projection the two ranks' partial rows are summed inside the add + norm
+ * kernel that follows: plain loads from the peer's exchange buffer over NVLink, a flag word per rank, bounded waits
+ * (a wait that runs out gives status OMNI_ERR_DEVICE on both ranks), no collective library on the data path.
+ * Both ranks make the same calls with the same arguments; their logits and draws are bit-identical.
+ * `tp_export` writes the handle (64 bytes) under which the other process maps this rank's exchange region;
+ * `tp_connect` takes the other rank's. start / tick / warmup are refused until the pair is connected. */
+#define OMNI_TP_HANDLE_BYTES 64
+int32_t omni_duplex_tp_export(omni_duplex* m, void* handle, size_t bytes);
+int32_t omni_duplex_tp_connect(omni_duplex* m, const void* peer_handle, size_t bytes);
 
 /* Replaces `Model::warmup` (model.rs:202-240): runs the tick of every bucket up to max_sessions (1, 2, 4, ...,
  * max_sessions) on the padding lease, so that every bucket's GEMM plans exist and its CUDA graph is captured before

@@ -81,6 +81,17 @@ int32_t omni_op_sample(omni_ops* ctx, const void* logits, int32_t vocab, float t
 int32_t omni_op_lm_norm(omni_ops* ctx, const void* y, void* x, const void* alpha, void* out, int32_t rows,
                         int32_t dim, float eps);
 
+/* One rank's side of the tensor-parallel pair's exchange (include/omni_b200_duplex.h; no counterpart in the
+ * reference): waits (at most 2 s) until the flag word words[0] has reached this exchange's number words[32] + 1, which
+ * it also stores to words[16] (in the model: the peer's flag), then y = bf16(mine + peer), x = bf16(x + y),
+ * out = norm(x), and the last CTA advances words[32]. words: 64 zero-initialised u32 in device memory
+ * (0: this rank's flag, 16: where the peer's flag is written, 32: exchange counter, 48: CTA counter). With a flag that
+ * nothing raises the wait runs out: the device error word is set (status OMNI_ERR_DEVICE at the next
+ * omni_ops_sync) and peer counts as zero. This entry exists so that the kernel's arithmetic and its bounded wait can
+ * be tested on one GPU. */
+int32_t omni_op_lm_tp_add_norm(omni_ops* ctx, const void* mine, const void* peer, void* x, const void* alpha, void* out,
+                               int32_t rows, int32_t dim, float eps, void* words);
+
 /* `lm_embed_prompt` (lm.cu:47-59) without voices: out[r] = sum of the embeddings of ids[r][0..17), every add rounded
  * to bf16, audio streams first, -1 = no token. text_emb [text_rows, dim], audio_emb [16 * card_rows, dim]. */
 int32_t omni_op_lm_embed(omni_ops* ctx, const int32_t* ids, const void* text_emb, int32_t text_rows,

@@ -40,6 +40,14 @@ cudaError_t launch_lm_norm(const bf16* x, const bf16* alpha, bf16* out, int rows
 // x = bf16(x + y); out = norm(x) (out == nullptr: the add alone)
 cudaError_t launch_lm_add_norm(const bf16* y, bf16* x, const bf16* alpha, bf16* out, int rows, int dim, float eps,
                                cudaStream_t s);
+// The words of a tensor-parallel pair's exchange: `my_flag` lives in this rank's memory and is written by the peer,
+// `peer_flag` is the peer's, mapped here; `counter` numbers the exchanges, `finished` counts a launch's CTAs.
+struct TpLink {
+  uint32_t *my_flag = nullptr, *peer_flag = nullptr, *counter = nullptr, *finished = nullptr;
+};
+// y = bf16(mine + peer) over both ranks' partial rows, then x = bf16(x + y); out = norm(x) (out == nullptr: the add alone)
+cudaError_t launch_lm_tp_add_norm(const bf16* mine, const bf16* peer, bf16* x, const bf16* alpha, bf16* out, int rows,
+                                  int dim, float eps, const TpLink& link, uint32_t* err, cudaStream_t s);
 // Rows [q | k | v] of `heads` heads of 128: interleaved rotary embedding of q in place; k rotated, then k and v
 // quantised per head to E4M3 with scale max(amax / 448, 1e-12) into the row's slot.
 cudaError_t launch_lm_rope_kv(bf16* qkv, const int32_t* pos, const int32_t* slots, void* kv, int rows, int heads,

@@ -101,6 +101,85 @@ __global__ void lm_add_norm_kernel(const bf16* __restrict__ y, bf16* __restrict_
   if (out) norm_row(v, alpha, out + (int64_t)blockIdx.x * dim, dim, eps, scratch);
 }
 
+// ---- tensor-parallel pair: all-reduce of a projection's partial rows, fused with the add + norm that follows -----
+// Two ranks (two GPUs, one process each) hold half of the attention heads and half of the MLP channels; after the o
+// and down projections each has a partial row block y_r [rows, dim]. This kernel makes y = bf16(y_0 + y_1) on both
+// ranks and goes on as lm_add_norm does (x = bf16(x + y), out = norm(x)). The exchange is plain peer-memory traffic:
+//   - `mine` sits in this rank's exchange buffer (written by the GEMM launched before this kernel), `peer` is the same
+//     buffer of the other rank, mapped into this process;
+//   - one thread stores this exchange's number into the PEER's flag word (release, system scope), so each rank polls
+//     a word in its own memory; thread 0 of every CTA waits (acquire, system scope, at most kTpWaitNs) until its own
+//     flag has reached the number, then the CTA reads the peer's rows with system-scope loads that bypass L1;
+//   - exchanges are numbered by a device-resident counter that the last CTA to finish advances, so a captured graph
+//     replays the same launch with new numbers; two buffers alternate (o, down), and a rank can only overwrite a
+//     buffer two exchanges later, after it has seen the peer's next flag, which the peer raises only when its
+//     previous exchange kernel (the reader of that buffer) has completed.
+// f32 addition commutes, so both ranks round the same sum: their rows stay bit-identical.
+// A wait that runs out raises the error word, takes the peer's rows as zero and lets the kernel finish.
+constexpr uint64_t kTpWaitNs = 2000ull * 1000 * 1000;
+
+__global__ void lm_tp_add_norm_kernel(const bf16* __restrict__ mine, const bf16* peer, bf16* __restrict__ x,
+                                      const bf16* __restrict__ alpha, bf16* __restrict__ out, int dim, float eps,
+                                      uint32_t* my_flag, uint32_t* peer_flag, uint32_t* counter, uint32_t* finished,
+                                      uint32_t* err) {
+  __shared__ float scratch[32];
+  __shared__ int peer_ready;
+  const uint32_t number = *reinterpret_cast<volatile uint32_t*>(counter) + 1u;
+  if (threadIdx.x == 0) {
+    if (blockIdx.x == 0) {
+      __threadfence_system();
+      asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(peer_flag), "r"(number) : "memory");
+    }
+    int ok = 1;
+    if (*reinterpret_cast<volatile uint32_t*>(err) != 0) {
+      ok = 0;  // an earlier kernel gave up: do not wait for a peer that may have given up as well
+    } else {
+      const uint64_t start = sm100::global_timer_ns();
+      for (uint32_t spins = 0;; ++spins) {
+        uint32_t seen;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(my_flag) : "memory");
+        if ((int32_t)(seen - number) >= 0) break;
+        if ((spins & 63u) == 63u && sm100::global_timer_ns() - start > kTpWaitNs) {
+          raise(err, kErrBarrierTimeout);
+          ok = 0;
+          break;
+        }
+      }
+    }
+    peer_ready = ok;
+  }
+  __syncthreads();
+  const int64_t at = (int64_t)blockIdx.x * dim + threadIdx.x * 8;
+  float v[8], a[8], b[8];
+  ld8(x + at, v);
+  ld8(mine + at, a);
+  if (peer_ready) {
+    Pack8 raw;
+    uint32_t* w = reinterpret_cast<uint32_t*>(&raw);
+    asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3])
+                 : "l"(peer + at)
+                 : "memory");
+    unpack8(raw, b);
+  } else {
+#pragma unroll
+    for (int k = 0; k < 8; ++k) b[k] = 0.f;
+  }
+#pragma unroll
+  for (int k = 0; k < 8; ++k) v[k] = bf16_round(v[k] + bf16_round(a[k] + b[k]));
+  st8(x + at, v);
+  if (out) norm_row(v, alpha, out + (int64_t)blockIdx.x * dim, dim, eps, scratch);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    if (atomicAdd(finished, 1u) == gridDim.x - 1) {  // every CTA has read the counter: advance it for the next launch
+      *finished = 0;
+      *reinterpret_cast<volatile uint32_t*>(counter) = number;
+      __threadfence();
+    }
+  }
+}
+
 __device__ __forceinline__ uint8_t* page_head(void* kv, int64_t page, int heads, int h) {
   return static_cast<uint8_t*>(kv) + (page * heads + h) * (int64_t)kDuplexPageHeadBytes;
 }
@@ -548,6 +627,14 @@ cudaError_t launch_lm_add_norm(const bf16* y, bf16* x, const bf16* alpha, bf16* 
                                cudaStream_t s) {
   if (!row_dim_ok(dim)) return cudaErrorInvalidValue;
   lm_add_norm_kernel<<<rows, dim / 8, 0, s>>>(y, x, alpha, out, dim, eps);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_lm_tp_add_norm(const bf16* mine, const bf16* peer, bf16* x, const bf16* alpha, bf16* out, int rows,
+                                  int dim, float eps, const TpLink& link, uint32_t* err, cudaStream_t s) {
+  if (!row_dim_ok(dim) || !peer || !link.my_flag || !link.peer_flag) return cudaErrorInvalidValue;
+  lm_tp_add_norm_kernel<<<rows, dim / 8, 0, s>>>(mine, peer, x, alpha, out, dim, eps, link.my_flag, link.peer_flag,
+                                                 link.counter, link.finished, err);
   return cudaGetLastError();
 }
 

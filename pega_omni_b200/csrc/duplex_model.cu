@@ -67,6 +67,27 @@ struct omni_duplex {
   bf16 *d_input = nullptr, *d_text_emb = nullptr, *d_emb = nullptr, *d_heads = nullptr;
   std::vector<DepLayer> d;
 
+  // tensor-parallel pair (tp > 1): this rank holds heads / tp attention heads and hidden / tp MLP channels of Helium;
+  // the depformer, the embeddings, the norms and the heads are replicated
+  int tp = 1, tp_rank = 0;
+  char* tp_region = nullptr;       // [256 B of words | exchange buffer 0 | exchange buffer 1]
+  char* tp_peer_region = nullptr;  // the other rank's region, mapped by omni_duplex_tp_connect
+  size_t tp_buf_bytes = 0;
+  int local_heads() const { return cfg.heads / tp; }
+  int local_hidden() const { return cfg.hidden / tp; }
+  bf16* tp_buf(int which) const { return reinterpret_cast<bf16*>(tp_region + 256 + (size_t)which * tp_buf_bytes); }
+  const bf16* tp_peer_buf(int which) const {
+    return reinterpret_cast<const bf16*>(tp_peer_region + 256 + (size_t)which * tp_buf_bytes);
+  }
+  TpLink tp_link() const {
+    TpLink l;
+    l.my_flag = reinterpret_cast<uint32_t*>(tp_region);
+    l.counter = reinterpret_cast<uint32_t*>(tp_region + 64);
+    l.finished = reinterpret_cast<uint32_t*>(tp_region + 128);
+    l.peer_flag = reinterpret_cast<uint32_t*>(tp_peer_region);
+    return l;
+  }
+
   // pools
   int pages_per_session = 0, kv_pages = 0;
   std::vector<uint8_t*> kv;  // per layer
@@ -248,26 +269,38 @@ float rope_coef(const omni_duplex_config& c) {  // helium.rs:79-81
   return (float)(-std::log((double)c.rope_period) * 2.0 / (double)kHeliumHeadDim);
 }
 
-// Every Helium layer over `rows` rows of m->x; the output norm's rows end in m->xn (helium.rs:225-284).
+// Every Helium layer over `rows` rows of m->x; the output norm's rows end in m->xn (helium.rs:225-284). In a
+// tensor-parallel pair the projections run on this rank's heads and channels, and the o and down projections' partial
+// rows are summed over the pair inside the add + norm kernel that follows them.
 int helium_forward(omni_duplex* m, int rows, const int32_t* pos, const int32_t* slot, const int32_t* seq,
                    const int32_t* indptr, const int32_t* pages) {
   const omni_duplex_config& c = m->cfg;
-  const int D = c.dim, H = c.hidden;
+  const int D = c.dim, Dl = m->local_heads() * kHeliumHeadDim, Hl = m->local_hidden();
+  const bool pair = m->tp > 1;
+  if (pair && !m->tp_peer_region) return m->fail(OMNI_ERR_INVALID, "tensor-parallel pair not connected (omni_duplex_tp_connect)");
   const float scale = 1.f / std::sqrt((float)kHeliumHeadDim);
   DLAUNCH(m, launch_lm_norm(m->x, m->h[0].norm1, m->xn, rows, D, c.norm_eps, m->stream));
   for (int i = 0; i < c.layers; ++i) {
     const HeliumLayer& L = m->h[i];
-    DTRY(gemm(m, L.qkv, 3 * D, D, m->xn, rows, m->qkv, 3 * D));
-    DLAUNCH(m, launch_lm_rope_kv(m->qkv, pos, slot, m->kv[i], rows, c.heads, rope_coef(c), m->kv_pages, m->err, m->stream));
-    DLAUNCH(m, launch_lm_attend(m->qkv, m->kv[i], pos, seq, indptr, pages, m->attn, rows, c.heads, scale, c.context,
+    DTRY(gemm(m, L.qkv, 3 * Dl, D, m->xn, rows, m->qkv, 3 * Dl));
+    DLAUNCH(m, launch_lm_rope_kv(m->qkv, pos, slot, m->kv[i], rows, m->local_heads(), rope_coef(c), m->kv_pages, m->err, m->stream));
+    DLAUNCH(m, launch_lm_attend(m->qkv, m->kv[i], pos, seq, indptr, pages, m->attn, rows, m->local_heads(), scale, c.context,
                                 m->kv_pages, m->err, m->stream));
-    DTRY(gemm(m, L.o, D, D, m->attn, rows, m->y, D));
-    DLAUNCH(m, launch_lm_add_norm(m->y, m->x, L.norm2, m->xn, rows, D, c.norm_eps, m->stream));
-    DTRY(gemm(m, L.gate_up, 2 * H, D, m->xn, rows, m->gu, 2 * H));
-    DLAUNCH(m, launch_silu_mul(m->gu, m->act, rows, H, 0, m->stream));
-    DTRY(gemm(m, L.down, D, H, m->act, rows, m->y, D));
+    bf16* y_o = pair ? m->tp_buf(0) : m->y;
+    DTRY(gemm(m, L.o, D, Dl, m->attn, rows, y_o, D));
+    if (pair)
+      DLAUNCH(m, launch_lm_tp_add_norm(y_o, m->tp_peer_buf(0), m->x, L.norm2, m->xn, rows, D, c.norm_eps, m->tp_link(), m->err, m->stream));
+    else
+      DLAUNCH(m, launch_lm_add_norm(m->y, m->x, L.norm2, m->xn, rows, D, c.norm_eps, m->stream));
+    DTRY(gemm(m, L.gate_up, 2 * Hl, D, m->xn, rows, m->gu, 2 * Hl));
+    DLAUNCH(m, launch_silu_mul(m->gu, m->act, rows, Hl, 0, m->stream));
+    bf16* y_d = pair ? m->tp_buf(1) : m->y;
+    DTRY(gemm(m, L.down, D, Hl, m->act, rows, y_d, D));
     const bf16* next = i + 1 < c.layers ? m->h[i + 1].norm1 : m->out_norm;
-    DLAUNCH(m, launch_lm_add_norm(m->y, m->x, next, m->xn, rows, D, c.norm_eps, m->stream));
+    if (pair)
+      DLAUNCH(m, launch_lm_tp_add_norm(y_d, m->tp_peer_buf(1), m->x, next, m->xn, rows, D, c.norm_eps, m->tp_link(), m->err, m->stream));
+    else
+      DLAUNCH(m, launch_lm_add_norm(m->y, m->x, next, m->xn, rows, D, c.norm_eps, m->stream));
   }
   return OMNI_OK;
 }
@@ -325,7 +358,8 @@ bool valid_config(const omni_duplex_config& c) {
   return row(c.dim) && row(c.dep_dim) && c.dim == c.heads * kHeliumHeadDim && c.dep_dim == c.dep_heads * kDepHeadDim &&
          c.layers >= 1 && c.dep_layers >= 1 && c.hidden % 64 == 0 && c.dep_hidden % 64 == 0 && c.hidden > 0 &&
          c.dep_hidden > 0 && c.context >= 1 && c.text_vocab >= 1 && c.card >= 1 && c.max_sessions >= 1 &&
-         c.max_prefill >= 1 && c.voice_rows >= 0;
+         c.max_prefill >= 1 && c.voice_rows >= 0 && c.tp_size >= 0 && c.tp_size <= 2 && c.tp_rank >= 0 &&
+         c.tp_rank < std::max(c.tp_size, 1) && (c.tp_size < 2 || (c.heads % 2 == 0 && c.hidden % 128 == 0));
 }
 
 }  // namespace
@@ -348,6 +382,8 @@ int32_t omni_duplex_create(const omni_duplex_config* config, const omni_tensor* 
     return m->fail(OMNI_ERR_UNSUPPORTED, "device is sm_%d%d; this library is sm_100a only", prop.major, prop.minor);
   m->sm_count = prop.multiProcessorCount;
   m->use_graphs = c.use_graphs != 0;
+  m->tp = c.tp_size >= 2 ? c.tp_size : 1;
+  m->tp_rank = c.tp_rank;
   DCUDA(m, cudaStreamCreateWithFlags(&m->stream, cudaStreamNonBlocking));
   DCUDA(m, cudaEventCreate(&m->ev0));
   DCUDA(m, cudaEventCreate(&m->ev1));
@@ -358,6 +394,7 @@ int32_t omni_duplex_create(const omni_duplex_config* config, const omni_tensor* 
   for (int i = 0; i < n_tensors; ++i)
     if (tensors[i].name) idx[tensors[i].name] = &tensors[i];
   const int64_t D = c.dim, H = c.hidden, DD = c.dep_dim, DH = c.dep_hidden, card1 = c.card + 1;
+  const int64_t Dl = (int64_t)m->local_heads() * kHeliumHeadDim, Hl = m->local_hidden();
   DTRY(weight(m, idx, "h.text_emb", {c.text_vocab + 1, D}, &m->text_emb));
   DTRY(weight(m, idx, "h.audio_emb", {16 * card1, D}, &m->audio_emb));
   DTRY(weight(m, idx, "h.out_norm", {D}, &m->out_norm));
@@ -368,11 +405,12 @@ int32_t omni_duplex_create(const omni_duplex_config* config, const omni_tensor* 
     const std::string p = "h.l" + std::to_string(i) + ".";
     HeliumLayer& L = m->h[i];
     DTRY(weight(m, idx, p + "norm1", {D}, &L.norm1));
-    DTRY(weight(m, idx, p + "qkv", {3 * D, D}, &L.qkv));
-    DTRY(weight(m, idx, p + "o", {D, D}, &L.o));
+    // a rank of a tensor-parallel pair is given its own rows / columns of the four projections (header)
+    DTRY(weight(m, idx, p + "qkv", {3 * Dl, D}, &L.qkv));
+    DTRY(weight(m, idx, p + "o", {D, Dl}, &L.o));
     DTRY(weight(m, idx, p + "norm2", {D}, &L.norm2));
-    DTRY(weight(m, idx, p + "gate_up", {2 * H, D}, &L.gate_up));
-    DTRY(weight(m, idx, p + "down", {D, H}, &L.down));
+    DTRY(weight(m, idx, p + "gate_up", {2 * Hl, D}, &L.gate_up));
+    DTRY(weight(m, idx, p + "down", {D, Hl}, &L.down));
   }
   DTRY(weight(m, idx, "d.input", {kDepSteps * DD, D}, &m->d_input));
   DTRY(weight(m, idx, "d.text_emb", {c.text_vocab + 1, DD}, &m->d_text_emb));
@@ -399,7 +437,7 @@ int32_t omni_duplex_create(const omni_duplex_config* config, const omni_tensor* 
   m->pad_line = S;
   m->kv.resize(c.layers);
   for (int i = 0; i < c.layers; ++i)
-    DTRY(dalloc(m, &m->kv[i], (size_t)m->kv_pages * c.heads * kDuplexPageHeadBytes, true));
+    DTRY(dalloc(m, &m->kv[i], (size_t)m->kv_pages * m->local_heads() * kDuplexPageHeadBytes, true));
   m->dkv.resize(c.dep_layers);
   for (int i = 0; i < c.dep_layers; ++i) DTRY(dalloc(m, &m->dkv[i], (size_t)S * kDepSteps * 2 * DD, true));
   DTRY(dalloc(m, &m->state, (size_t)(S + 1) * m->stride, true));
@@ -412,6 +450,10 @@ int32_t omni_duplex_create(const omni_duplex_config* config, const omni_tensor* 
   DTRY(dalloc(m, &m->qkv, R * 3 * D));
   DTRY(dalloc(m, &m->attn, R * D));
   DTRY(dalloc(m, &m->y, R * D));
+  if (m->tp > 1) {  // the pair's exchange region: words, then two buffers of max_rows x dim partial rows
+    m->tp_buf_bytes = (R * D * sizeof(bf16) + 255) & ~(size_t)255;
+    DTRY(dalloc(m, &m->tp_region, 256 + 2 * m->tp_buf_bytes, true));
+  }
   DTRY(dalloc(m, &m->gu, R * 2 * H));
   DTRY(dalloc(m, &m->act, R * H));
   DTRY(dalloc(m, &m->text_logits, (size_t)S * c.text_vocab, true));
@@ -449,6 +491,7 @@ void omni_duplex_destroy(omni_duplex* m) {
   if (m->stream) cudaStreamSynchronize(m->stream);
   for (auto& g : m->tick_graphs)
     if (g.second.exec) cudaGraphExecDestroy(g.second.exec);
+  if (m->tp_peer_region) cudaIpcCloseMemHandle(m->tp_peer_region);
   for (void* p : m->allocations) cudaFree(p);
   if (m->in_host) cudaFreeHost(m->in_host);
   if (m->out_host) cudaFreeHost(m->out_host);
@@ -459,6 +502,31 @@ void omni_duplex_destroy(omni_duplex* m) {
 }
 
 const char* omni_duplex_last_error(const omni_duplex* m) { return m ? m->error.c_str() : "null model"; }
+
+int32_t omni_duplex_tp_export(omni_duplex* m, void* handle, size_t bytes) {
+  if (!m || !handle) return OMNI_ERR_INVALID;
+  if (m->tp < 2) return m->fail(OMNI_ERR_INVALID, "the model is not a rank of a tensor-parallel pair");
+  if (bytes < sizeof(cudaIpcMemHandle_t)) return m->fail(OMNI_ERR_INVALID, "handle buffer below %zu bytes", sizeof(cudaIpcMemHandle_t));
+  DCUDA(m, cudaSetDevice(m->device));
+  cudaIpcMemHandle_t h;
+  DCUDA(m, cudaIpcGetMemHandle(&h, m->tp_region));
+  memcpy(handle, &h, sizeof(h));
+  return OMNI_OK;
+}
+
+int32_t omni_duplex_tp_connect(omni_duplex* m, const void* peer_handle, size_t bytes) {
+  if (!m || !peer_handle) return OMNI_ERR_INVALID;
+  if (m->tp < 2) return m->fail(OMNI_ERR_INVALID, "the model is not a rank of a tensor-parallel pair");
+  if (bytes < sizeof(cudaIpcMemHandle_t)) return m->fail(OMNI_ERR_INVALID, "handle below %zu bytes", sizeof(cudaIpcMemHandle_t));
+  if (m->tp_peer_region) return m->fail(OMNI_ERR_INVALID, "the pair is connected already");
+  DCUDA(m, cudaSetDevice(m->device));
+  cudaIpcMemHandle_t h;
+  memcpy(&h, peer_handle, sizeof(h));
+  void* p = nullptr;
+  DCUDA(m, cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess));
+  m->tp_peer_region = static_cast<char*>(p);
+  return OMNI_OK;
+}
 
 int32_t omni_duplex_open(omni_duplex* m, omni_duplex_session** out) {
   if (!m || !out) return OMNI_ERR_INVALID;
@@ -653,7 +721,7 @@ int32_t omni_duplex_start(omni_duplex* m, int32_t n, omni_duplex_session* const*
       }
       DCUDA(m, cudaMemcpyAsync(m->in_dev, m->in_host, st.used, cudaMemcpyHostToDevice, m->stream));
       for (int l = 0; l < c.layers; ++l)
-        DLAUNCH(m, launch_lm_copy_kv(m->kv[l], st.dev(src), st.dev(dst), copies, c.heads, m->kv_pages, m->err, m->stream));
+        DLAUNCH(m, launch_lm_copy_kv(m->kv[l], st.dev(src), st.dev(dst), copies, m->local_heads(), m->kv_pages, m->err, m->stream));
       DLAUNCH(m, launch_lm_init(m->state, st.dev(lines), m->stride, st.dev(ini), copied_sessions, m->stream));
       DCUDA(m, cudaStreamSynchronize(m->stream));
     }

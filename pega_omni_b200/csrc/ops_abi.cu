@@ -209,6 +209,17 @@ int32_t omni_op_lm_norm(omni_ops* c, const void* y, void* x, const void* alpha, 
   return OMNI_OK;
 }
 
+int32_t omni_op_lm_tp_add_norm(omni_ops* c, const void* mine, const void* peer, void* x, const void* alpha, void* out,
+                               int32_t rows, int32_t dim, float eps, void* words) {
+  if (!c || !mine || !peer || !x || !words) return OMNI_ERR_INVALID;
+  TpLink link;
+  uint32_t* w = static_cast<uint32_t*>(words);
+  link.my_flag = w, link.peer_flag = w + 16, link.counter = w + 32, link.finished = w + 48;
+  OPS_CUDA(c, launch_lm_tp_add_norm((const bf16*)mine, (const bf16*)peer, (bf16*)x, (const bf16*)alpha, (bf16*)out, rows,
+                                    dim, eps, link, c->err, c->stream));
+  return OMNI_OK;
+}
+
 int32_t omni_op_lm_embed(omni_ops* c, const int32_t* ids, const void* text_emb, int32_t text_rows,
                          const void* audio_emb, int32_t card_rows, void* out, int32_t rows, int32_t dim) {
   if (!c || !ids || !out) return OMNI_ERR_INVALID;

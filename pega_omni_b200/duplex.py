@@ -167,6 +167,38 @@ class Session:
         return self._where()[1]
 
 
+def shard_checkpoint(checkpoint: dict, c: "DuplexConfig", rank: int, size: int) -> dict:
+    """Rank `rank`'s tensors of a tensor-parallel group of `size`: of every Helium layer the q, k and v rows of its
+    heads, the matching columns of o, its gate and up rows and the matching columns of down; everything else whole."""
+    d, h = c.dim, c.hidden
+    dl, hl = d // size, h // size
+    out = {}
+    for name, t in checkpoint.items():
+        if name.startswith("h.l") and name.endswith(".qkv"):
+            parts = [t[k * d + rank * dl: k * d + (rank + 1) * dl] for k in range(3)]
+            out[name] = _cat(parts)
+        elif name.startswith("h.l") and name.endswith(".o"):
+            out[name] = _contig(t[:, rank * dl:(rank + 1) * dl])
+        elif name.startswith("h.l") and name.endswith(".gate_up"):
+            out[name] = _cat([t[k * h + rank * hl: k * h + (rank + 1) * hl] for k in range(2)])
+        elif name.startswith("h.l") and name.endswith(".down"):
+            out[name] = _contig(t[:, rank * hl:(rank + 1) * hl])
+        else:
+            out[name] = t
+    return out
+
+
+def _cat(parts):
+    if isinstance(parts[0], np.ndarray):
+        return np.ascontiguousarray(np.concatenate(parts))
+    import torch
+    return torch.cat(parts).contiguous()
+
+
+def _contig(t):
+    return np.ascontiguousarray(t) if isinstance(t, np.ndarray) else t.contiguous()
+
+
 class Model:
     def __init__(self, handle, config: DuplexConfig, max_sessions: int):
         self._h, self.config, self.max_sessions = handle, config, max_sessions
@@ -174,14 +206,19 @@ class Model:
 
     @classmethod
     def load(cls, device: int, checkpoint: dict, config: DuplexConfig, max_sessions: int = 128,
-             max_prefill: int = 2048, use_graphs: bool = True) -> "Model":
+             max_prefill: int = 2048, use_graphs: bool = True, tp_rank: int = 0, tp_size: int = 1) -> "Model":
+        """`tp_size = 2`: this process is rank `tp_rank` of a tensor-parallel pair; `checkpoint` is the whole model and
+        the rank's rows / columns of Helium's projections are cut out here (`shard_checkpoint`). The pair must then be
+        connected: each rank's `tp_export()` bytes go to the other rank's `tp_connect()`."""
         lib = L.load()
         c = config
+        if tp_size > 1:
+            checkpoint = shard_checkpoint(checkpoint, c, tp_rank, tp_size)
         voice_rows = checkpoint["voices"].shape[0] if "voices" in checkpoint else 0
         cfg = L.DuplexCfg(c.dim, c.layers, c.heads, c.hidden, c.context, c.dep_dim, c.dep_layers, c.dep_heads,
                           c.dep_hidden, c.text_vocab, c.card, c.norm_eps, c.rope_period, c.text_temperature,
                           c.text_top_k, c.audio_temperature, c.audio_top_k, max_sessions, max_prefill, voice_rows,
-                          int(use_graphs))
+                          int(use_graphs), tp_rank, tp_size)
         tensors, keep = c_tensors(checkpoint)
         h = C.c_void_p()
         rc = lib.omni_duplex_create(C.byref(cfg), tensors, len(checkpoint), device, C.byref(h))
@@ -197,6 +234,16 @@ class Model:
         if self._h:
             self._lib.omni_duplex_destroy(self._h)
             self._h = None
+
+    def tp_export(self) -> bytes:
+        """The handle under which the other rank's process maps this rank's exchange region."""
+        buf = C.create_string_buffer(64)
+        self._check(self._lib.omni_duplex_tp_export(self._h, buf, 64))
+        return buf.raw
+
+    def tp_connect(self, peer_handle: bytes) -> None:
+        buf = C.create_string_buffer(bytes(peer_handle), 64)
+        self._check(self._lib.omni_duplex_tp_connect(self._h, buf, 64))
 
     def _check(self, rc: int):
         if rc in (L.DENIED_BUSY, L.DENIED_EXCEEDS_POOL):

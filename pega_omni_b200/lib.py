@@ -55,7 +55,7 @@ class DuplexCfg(C.Structure):
                [("norm_eps", C.c_float), ("rope_period", C.c_float), ("text_temperature", C.c_float),
                 ("text_top_k", C.c_int32), ("audio_temperature", C.c_float), ("audio_top_k", C.c_int32),
                 ("max_sessions", C.c_int32), ("max_prefill", C.c_int32), ("voice_rows", C.c_int32),
-                ("use_graphs", C.c_int32)]
+                ("use_graphs", C.c_int32), ("tp_rank", C.c_int32), ("tp_size", C.c_int32)]
 
 
 class DuplexStep(C.Structure):
@@ -119,6 +119,7 @@ SYMBOLS = {
                              VP, C.c_int64, I32, I32, VP, I32, I32]),
     "omni_op_gemm_noalloc": (I32, [VP, I32, I32, VP, I32, VP, I32, I32, VP, I32, VP, C.c_char_p, C.c_size_t]),
     "omni_op_lm_norm": (I32, [VP, VP, VP, VP, VP, I32, I32, C.c_float]),
+    "omni_op_lm_tp_add_norm": (I32, [VP, VP, VP, VP, VP, VP, I32, I32, C.c_float, VP]),
     "omni_op_lm_embed": (I32, [VP, VP, VP, I32, VP, I32, VP, I32, I32]),
     "omni_op_lm_rope_attend": (I32, [VP, VP, VP, I32, VP, VP, VP, VP, VP, I32, I32, C.c_float, C.c_float, I32, VP]),
     "omni_op_lm_dep_embed_norm": (I32, [VP, VP, I32, VP, I32, VP, VP, VP, VP, I32, I32, C.c_float]),
@@ -152,6 +153,8 @@ SYMBOLS = {
     "omni_duplex_start": (I32, [VP, I32, P(VP), P(I32), P(I32), P(I32), P(I32), P(I32)]),
     "omni_duplex_tick": (I32, [VP, I32, P(VP), P(DuplexStep), P(I32)]),
     "omni_duplex_warmup": (I32, [VP]),
+    "omni_duplex_tp_export": (I32, [VP, VP, C.c_size_t]),
+    "omni_duplex_tp_connect": (I32, [VP, VP, C.c_size_t]),
     "omni_duplex_read": (I32, [VP, I32, I32, VP, C.c_size_t]),
     "omni_duplex_stats": (I32, [VP, P(C.c_float), P(I32)]),
 }

@@ -88,6 +88,11 @@ class Ops:
         rows, dim = x.shape
         self._check(self._lib.omni_op_lm_norm(self._h, _p(y), _p(x), _p(alpha), _p(out), rows, dim, eps))
 
+    def lm_tp_add_norm(self, mine, peer, x, alpha, out, eps, words):
+        rows, dim = x.shape
+        self._check(self._lib.omni_op_lm_tp_add_norm(self._h, _p(mine), _p(peer), _p(x), _p(alpha), _p(out), rows, dim,
+                                                     eps, _p(words)))
+
     def lm_embed(self, ids, text_emb, audio_emb, out):
         rows, dim = out.shape
         self._check(self._lib.omni_op_lm_embed(self._h, _p(ids), _p(text_emb), text_emb.shape[0], _p(audio_emb),

@@ -51,4 +51,4 @@ def test_struct_layouts_match_header(built_lib):
     from pega_omni_b200 import lib
     assert C.sizeof(lib.Draw) == 128 and C.sizeof(lib.StackCfg) == 36
     assert C.sizeof(lib.Tensor) == 64
-    assert C.sizeof(lib.DuplexCfg) == 84 and C.sizeof(lib.DuplexStep) == 112 and C.sizeof(lib.HiggsDelay) == 12
+    assert C.sizeof(lib.DuplexCfg) == 92 and C.sizeof(lib.DuplexStep) == 112 and C.sizeof(lib.HiggsDelay) == 12
