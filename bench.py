@@ -603,7 +603,7 @@ def main():
     W, K = max(3, args.warmup), args.steps
     cfg = presets["qwen3-tts-1.7b"]()
     ck = random_checkpoint(cfg, seed=0, device="cuda")
-    frames_cap = 2 * (W + K) + 8
+    frames_cap = W + K + 8
     kv_gib = max(1.0, 1.25 * args.sessions * (args.prompt + frames_cap + 16) * cfg.talker.kv_bytes_per_token() / 2 ** 30)
     model = Model.load(local, ck, cfg, Limits(args.sessions, args.sessions * args.prompt, kv_gib),
                        use_graphs=not args.no_graphs, tick_kernel=0 if args.per_op else (3 if args.cluster_predictor else 1))
@@ -658,12 +658,20 @@ def main():
 
     # ---- end-to-end arm: Model.step with host draws, staging and read-back inside every step ----
     # (each step's draws sit ready in host memory, laid out as the C ABI takes them, as an engine's staging buffer would)
+    # On fresh sessions with the same prompts and the same W warm-up ticks, so that the timed steps sit at the same
+    # positions (the same KV lengths) as the device-resident arm's and the reference arm's.
     from pega_omni_b200.model import DrawBatch
+    for s in seqs:
+        model.release(s)
+    seqs = [model.open(args.prompt, frames_cap) for _ in range(n)]
+    for i in range(0, n, 32):
+        model.start(list(zip(seqs[i:i + 32], prompts[i:i + 32], d0[i:i + 32])))
     e2e_rng = np.random.default_rng(30 + rank)
     e2e_draws = [DrawBatch(e2e_rng.random((n, 16)).astype(np.float32)) for _ in range(W + K)]
     out = None
-    for t in range(min(W, 8)):
+    for t in range(W):
         out = model.step_batch(seqs, e2e_draws[t], out)
+    assert seqs[0].frames == first_frame
     barrier()
     t0 = time.perf_counter()
     dev_ms = 0.0
@@ -689,7 +697,7 @@ def main():
         dist.barrier()
         dist.destroy_process_group()  # the other ranks are done; rank 0 alone runs the comparison legs below
     bucket = model.stats().bucket
-    pages_per_seq = (lens[-1] + K) // 16 + 1
+    pages_per_seq = lens[-1] // 16 + 1
     h2d = 4 * (bucket * (1 + 1 + 16 + 16 + 1 + 1) + bucket + 1) + 4 * n * pages_per_seq  # staged front block (approx.)
     d2h = 4 * (bucket * 16 + 1)
 
