@@ -317,7 +317,7 @@ __global__ void __launch_bounds__(kThreads, 1) pred_kernel(const __grid_constant
             }
           }
         }
-        asm volatile("fence.proxy.async;" ::: "memory");  // generic-proxy writes of other CTAs -> async-proxy reads
+        asm volatile("fence.proxy.async.global;" ::: "memory");  // generic-proxy writes of other CTAs -> async-proxy reads
         const CUtensorMap* map = a.maps + e.xmap;
         const uint32_t bytes = (uint32_t)kPredRows * 128u * (uint32_t)e.kbs;
         for (int kb = 0; kb < e.nkb && !ctl.abort; kb += e.kbs) {

@@ -815,7 +815,7 @@ __global__ void __launch_bounds__(kThreads, 1) tick_kernel(const __grid_constant
             ctl.abort = 1;
           }
         }
-        asm volatile("fence.proxy.async;" ::: "memory");  // generic-proxy writes of other CTAs -> async-proxy reads
+        asm volatile("fence.proxy.async.global;" ::: "memory");  // generic-proxy writes of other CTAs -> async-proxy reads
         ring.enter(ph, a.ring_bytes);
         const CUtensorMap* map = a.maps + ph.xmap;
         const uint32_t xbytes = (uint32_t)ph.bn * kTileK * 2 * (uint32_t)ring.kbs;
