@@ -623,7 +623,12 @@ __device__ __noinline__ void phase_sample(const Phase& ph, const TickIo& io, con
       int cols[Team::PER / 4];
 #pragma unroll
       for (int j = 0; j < Team::PER / 4; ++j) cols[j] = min(wtid * Team::PER + 4 * j, prm.vocab - 4);
-      reduce_vecs<Team::PER / 4, 4>(Partials(partials, ph), row, cols, mine);
+      if (wtid * Team::PER < prm.vocab) {  // threads past the vocabulary own no logit: no loads for them
+        reduce_vecs<Team::PER / 4, 4>(Partials(partials, ph), row, cols, mine);
+      } else {
+#pragma unroll
+        for (int j = 0; j < Team::PER; ++j) mine[j] = 0.f;
+      }
 #pragma unroll
       for (int j = 0; j < Team::PER; ++j) {
         const bf16 b = __float2bfloat16(mine[j]);
