@@ -144,6 +144,7 @@ struct omni_talker {
   bf16 *text_emb = nullptr, *codec_emb = nullptr, *codec_head = nullptr;
   bf16 *fc1_w = nullptr, *fc1_b = nullptr, *fc2_w = nullptr, *fc2_b = nullptr, *mtp_w = nullptr, *mtp_b = nullptr;
   bf16 *p_emb = nullptr, *lm_heads = nullptr;
+  bf16* p_emb_proj = nullptr;  // p_emb's rows sent through small_to_mtp_projection at load: [(groups - 1) * PV, p]
   int text_vocab = 0;
 
   // pools
@@ -626,7 +627,7 @@ struct TickBuilder {
   }
 
   void sample(const Phase& head, int group, int rows, bf16* logits_out, int ldl, int next, const bf16* table,
-              const bf16* hidden, bf16* p_in, int dim) {
+              const bf16* hidden, bf16* p_in, int dim, const bf16* gain = nullptr, float eps = 0.f, bf16* normed = nullptr) {
     const omni_talker_config& c = m->cfg;
     Phase ph = blank(kPhSample, rows);
     ph.tiles = head.tiles, ph.splits = head.splits, ph.bn = head.bn, ph.tile_n = head.tile_n;
@@ -650,6 +651,7 @@ struct TickBuilder {
     ph.src1 = hidden;
     ph.dst1 = p_in;
     ph.i9 = dim;
+    ph.src3 = gain, ph.f3 = eps, ph.dst2 = normed;  // kNextProjected only
     prog->phases.push_back(ph);
     offset = (offset + rows) % ctas;
   }
@@ -671,15 +673,28 @@ struct TickBuilder {
     }
     const Phase head = gemm(m->codec_head, V, h, m->hidden, b);
     sample(head, 0, b, m->logits, V, kNextHiddenAndCode, m->codec_emb, m->hidden, m->p_in, h);
+    // From the second predictor pass on, a pass's one input row per session is the embedding of the code just drawn,
+    // sent through the input projection (talker.rs:306-312). The projection of every table row was taken at load
+    // (p_emb_proj), so the draw writes the pass's residual start and first normed row itself and the pass has no
+    // projection GEMM and no ReduceNorm phase. The first pass (two rows per session, one of them the talker's
+    // hidden state) keeps both.
+    const bool folded = m->p_emb_proj != nullptr && (p == 128 || p == 256 || p == 512 || p == 1024 || p == 2048);
     for (int g = 1; g < c.groups && with_predictor; ++g) {
       const int per = g == 1 ? 2 : 1, rows = b * per;
-      const Phase mtp = gemm(m->mtp_w, p, h, m->p_in, rows);
-      row_phase(kPhReduceNorm, mtp, rows, p, m->mtp_b, m->pred.layers[0].ln1, m->P.res, m->P.x, c.predictor.rms_eps);
+      if (g == 1 || !folded) {
+        const Phase mtp = gemm(m->mtp_w, p, h, m->p_in, rows);
+        row_phase(kPhReduceNorm, mtp, rows, p, m->mtp_b, m->pred.layers[0].ln1, m->P.res, m->P.x, c.predictor.rms_eps);
+      }
       stack_pass(m->pred, m->P, rows, false, per, g == 1 ? 0 : g, m->pkv, m->max_seqs, m->p_last, per, per - 1);
       const Phase ph = gemm(m->lm_heads + (size_t)(g - 1) * PV * p, PV, p, m->p_last, b);
       const bool more = g + 1 < c.groups;
-      sample(ph, g, b, m->p_logits + (size_t)(g - 1) * m->max_seqs * PV, PV, more ? kNextCode : kNextNone,
-             more ? m->p_emb + (size_t)(g - 1) * PV * h : nullptr, nullptr, m->p_in, h);
+      bf16* lg = m->p_logits + (size_t)(g - 1) * m->max_seqs * PV;
+      if (more && folded)
+        sample(ph, g, b, lg, PV, kNextProjected, m->p_emb_proj + (size_t)(g - 1) * PV * p, nullptr, m->P.res, p,
+               m->pred.layers[0].ln1, c.predictor.rms_eps, m->P.x);
+      else
+        sample(ph, g, b, lg, PV, more ? kNextCode : kNextNone, more ? m->p_emb + (size_t)(g - 1) * PV * h : nullptr,
+               nullptr, m->p_in, h);
     }
   }
 };
@@ -1257,6 +1272,22 @@ static int create_impl(omni_talker* m, const omni_tensor* tensors, int32_t n_ten
     TRY(gemm(m, m->fc1_w, (int)h, (int)h, m->t_e, 1, m->t_p, (int)h, e1));
     TRY(gemm(m, m->fc2_w, (int)h, (int)h, m->t_p, 1, m->pad_embed, (int)h, e2));
     CUDA_TRY(m, cudaStreamSynchronize(m->stream));
+  }
+  // The residual codebooks' embedding tables through small_to_mtp_projection, once: from its second pass on the
+  // predictor's input row is projection(embedding of the code just drawn) (talker.rs:306-312), a linear map of a
+  // table row, so the persistent kernel looks the projected row up instead of running the projection every pass.
+  // Same arithmetic as the per-pass GEMM: bf16(bf16(W . e) + bias).
+  if (c.tick_kernel != 0 && m->tick_ok && G > 2) {
+    const int64_t total = (G - 1) * PV;
+    TRY(dev_alloc(m, &m->p_emb_proj, (size_t)total * p));
+    Epilogue bias;
+    bias.bias = m->mtp_b, bias.kind = kEpiBias;
+    const int64_t chunk = 256;
+    for (int64_t r0 = 0; r0 < total; r0 += chunk)
+      TRY(gemm(m, m->mtp_w, (int)p, (int)h, m->p_emb + r0 * h, (int)std::min(chunk, total - r0), m->p_emb_proj + r0 * p,
+               (int)p, bias));
+    CUDA_TRY(m, cudaStreamSynchronize(m->stream));
+    m->plans.clear();  // the plans of these one-off products are not needed again
   }
   return OMNI_OK;
 }

@@ -26,7 +26,7 @@ enum PhaseType : int32_t {
 };
 
 enum GemmMode : int32_t { kGemmPartials = 0, kGemmSwiglu = 1 };
-enum NextInput : int32_t { kNextNone = 0, kNextHiddenAndCode = 1, kNextCode = 2 };
+enum NextInput : int32_t { kNextNone = 0, kNextHiddenAndCode = 1, kNextCode = 2, kNextProjected = 3 };
 
 // One phase. Field use by type:
 //  Gemm:       N, K, bn, rows, tiles, splits, wmap, xmap, mode; dst0 = act (SwiGLU), i0 = inter, i1 = k-blocks per
@@ -39,13 +39,16 @@ enum NextInput : int32_t { kNextNone = 0, kNextHiddenAndCode = 1, kNextCode = 2 
 //              src0 q_norm, src1 k_norm; dst0 kv layer, dst1 attn out; f0 eps, f1 theta
 //  ReduceSilu: rows, tiles, splits, bn; dst0 act; i0 inter
 //  Sample:     rows, tiles, splits, bn, N = vocab; dst0 logits out, i0 ldl (row stride of logits out, elements);
-//              sampling constants in f0..f3 / i1..i7; next-input in i8, src0 table, src1 hidden, dst1 p_in, i9 dim
+//              sampling constants in f0..f3 / i1..i7; next-input in i8, src0 table, src1 hidden, dst1 p_in, i9 dim;
+//              i8 = kNextProjected: src0 is the table of code embeddings ALREADY sent through the predictor's input
+//              projection (one row of i9 elements per code), so the drawn code's row is the next pass's residual
+//              start: dst1 residual rows, dst2 normed rows, src3 the first layer's norm gain, f3 its eps
 struct alignas(16) Phase {
   int32_t type, rows, bn, N, K, tiles, splits, wmap, xmap, mode, cta_offset, tile_n;  // tile_n: weight rows per GEMM tile (64, 128 or 256; 96 with the SwiGLU epilogue)
   int32_t i0, i1, i2, i3, i4, i5, i6, i7, i8, i9, i10, i11;
   float f0, f1, f2, f3;
   const void *src0, *src1, *src2, *src3;
-  void *dst0, *dst1;
+  void *dst0, *dst1, *dst2;
 };
 
 // Pointers every phase may need (the staged inputs of the call and the per-sequence state).

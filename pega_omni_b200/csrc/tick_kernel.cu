@@ -589,10 +589,25 @@ __device__ __forceinline__ void phase_rope_attn(const Phase& ph, const TickIo& i
   }
 }
 
+// The next predictor pass's input when the code embeddings were sent through the input projection at load: the drawn
+// code's projected row IS the pass's residual start, and its RMSNorm the first layer's input (what the projection GEMM
+// and the ReduceNorm phase after it would produce, without either phase). One 128-thread group.
+template <int NV, int VEC>
+__device__ __forceinline__ void projected_input_row(const bf16* table_row, const bf16* gain_ptr, float eps, int dim,
+                                                    bf16* res_row, bf16* out_row, const Team& tm) {
+  const Gain<NV, VEC> gain(gain_ptr, tm.gtid);
+  float v[NV * VEC], ss = 0.f;
+#pragma unroll
+  for (int t = 0; t < NV; ++t) ld_bf16<VEC>(table_row + row_col<NV, VEC>(t, tm.gtid), &v[t * VEC]);
+#pragma unroll
+  for (int i = 0; i < NV * VEC; ++i) ss += v[i] * v[i];
+  norm_store<NV, VEC>(v, ss, dim, eps, gain, res_row, out_row, tm);
+}
+
 // ---- head reduce + draw + next predictor input: one row per CTA (all 256 workers) -----------------------------
 
 __device__ __noinline__ void phase_sample(const Phase& ph, const TickIo& io, const float* partials, int wtid, sampler::Shared& sh,
-                                          unsigned long long* stamp) {
+                                          unsigned long long* stamp, const Team& tm) {
   using Team = sampler::Team<kWorkerThreads, WorkerSync>;
   const int g = gridDim.x;
   bf16* logits_out = (bf16*)ph.dst0;
@@ -657,6 +672,16 @@ __device__ __noinline__ void phase_sample(const Phase& ph, const TickIo& io, con
       for (int i = wtid * 8; i < dim; i += kWorkerThreads * 8)
         *reinterpret_cast<Pack8*>(dst + (int64_t)row * dim + i) =
             *reinterpret_cast<const Pack8*>(table + (int64_t)token * dim + i);
+    } else if (ph.i8 == kNextProjected && wtid < kGroupThreads) {
+      const bf16* src = (const bf16*)ph.src0 + (int64_t)token * dim;
+      bf16 *res = (bf16*)ph.dst1 + (int64_t)row * dim, *out = (bf16*)ph.dst2 + (int64_t)row * dim;
+      switch (dim) {
+        case 256: projected_input_row<2, 1>(src, (const bf16*)ph.src3, ph.f3, dim, res, out, tm); break;
+        case 512: projected_input_row<1, 4>(src, (const bf16*)ph.src3, ph.f3, dim, res, out, tm); break;
+        case 1024: projected_input_row<2, 4>(src, (const bf16*)ph.src3, ph.f3, dim, res, out, tm); break;
+        case 2048: projected_input_row<4, 4>(src, (const bf16*)ph.src3, ph.f3, dim, res, out, tm); break;
+        default: projected_input_row<1, 1>(src, (const bf16*)ph.src3, ph.f3, dim, res, out, tm); break;  // 128
+      }
     }
     WorkerSync::sync();
   }
@@ -993,7 +1018,7 @@ __global__ void __launch_bounds__(kThreads, 1) tick_kernel(const __grid_constant
           phase_rope_attn(ph, a.io, a.partials, tm, wtid, scratch, a.err, a.trace ? a.trace + ((size_t)p * G + blockIdx.x) * 4 : nullptr);
           break;
         case kPhSample:
-          phase_sample(ph, a.io, a.partials, wtid, scratch.sample, a.trace ? a.trace + ((size_t)p * G + blockIdx.x) * 4 : nullptr);
+          phase_sample(ph, a.io, a.partials, wtid, scratch.sample, a.trace ? a.trace + ((size_t)p * G + blockIdx.x) * 4 : nullptr, tm);
           break;
         default: break;
       }
