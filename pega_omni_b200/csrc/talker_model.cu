@@ -145,6 +145,7 @@ struct omni_talker {
   bf16 *fc1_w = nullptr, *fc1_b = nullptr, *fc2_w = nullptr, *fc2_b = nullptr, *mtp_w = nullptr, *mtp_b = nullptr;
   bf16 *p_emb = nullptr, *lm_heads = nullptr;
   bf16* p_emb_proj = nullptr;  // p_emb's rows sent through small_to_mtp_projection at load: [(groups - 1) * PV, p]
+  bf16* p_qkv0 = nullptr;      // ... then through the predictor's first norm and q|k|v projection: [(groups - 1) * PV, qkv width]
   int text_vocab = 0;
 
   // pools
@@ -601,15 +602,23 @@ struct TickBuilder {
   // One pass of a decoder stack over rows whose normalised input is already in s.x and residual in s.res:
   // `Stack::forward` (crates/omni-qwen3/src/stack.rs:152-203) with the reduce of every split-K GEMM folded into its
   // consumer and SiLU*up folded into the gate|up GEMM.
+  // qkv0_table (optional): the first layer's q | k | v of every row, looked up by the code of group `code_group` (see
+  // p_qkv0); that layer then has no q|k|v GEMM phase.
   void stack_pass(const StackW& S, const Scratch& s, int rows, bool paged, int per, int base,
-                  const std::vector<bf16*>& kv, int kv_pages, bf16* keep_out, int every, int which) {
+                  const std::vector<bf16*>& kv, int kv_pages, bf16* keep_out, int every, int which,
+                  const bf16* qkv0_table = nullptr, int code_group = 0) {
     const omni_stack_config& c = S.cfg;
     const int h = c.hidden, I = c.inter, qd = c.q_heads * c.head_dim;
     for (int i = 0; i < c.layers; ++i) {
       const StackW::Layer& L = S.layers[i];
-      const Phase qkv = gemm(L.qkv, S.qkv_width(), h, s.x, rows);
+      const bool looked_up = i == 0 && qkv0_table != nullptr;
+      const Phase qkv = looked_up ? blank(kPhGemm, rows) : gemm(L.qkv, S.qkv_width(), h, s.x, rows);
       Phase at = blank(kPhRopeAttn, rows);
       at.tiles = qkv.tiles, at.splits = qkv.splits, at.bn = qkv.bn, at.tile_n = qkv.tile_n;
+      if (looked_up) {
+        at.tiles = 1, at.splits = 1, at.bn = 64, at.tile_n = 64;  // unused: nothing is read from the partial tiles
+        at.src2 = qkv0_table, at.i7 = code_group, at.i8 = S.qkv_width();
+      }
       at.i0 = c.q_heads, at.i1 = c.kv_heads, at.i2 = c.head_dim, at.i3 = per, at.i4 = base, at.i5 = paged, at.i6 = kv_pages;
       at.src0 = L.q_norm, at.src1 = L.k_norm;
       at.dst0 = kv[i], at.dst1 = s.attn;
@@ -685,7 +694,9 @@ struct TickBuilder {
         const Phase mtp = gemm(m->mtp_w, p, h, m->p_in, rows);
         row_phase(kPhReduceNorm, mtp, rows, p, m->mtp_b, m->pred.layers[0].ln1, m->P.res, m->P.x, c.predictor.rms_eps);
       }
-      stack_pass(m->pred, m->P, rows, false, per, g == 1 ? 0 : g, m->pkv, m->max_seqs, m->p_last, per, per - 1);
+      const bool qkv_folded = folded && g >= 2 && m->p_qkv0 != nullptr;
+      stack_pass(m->pred, m->P, rows, false, per, g == 1 ? 0 : g, m->pkv, m->max_seqs, m->p_last, per, per - 1,
+                 qkv_folded ? m->p_qkv0 + (size_t)(g - 2) * PV * m->pred.qkv_width() : nullptr, g - 1);
       const Phase ph = gemm(m->lm_heads + (size_t)(g - 1) * PV * p, PV, p, m->p_last, b);
       const bool more = g + 1 < c.groups;
       bf16* lg = m->p_logits + (size_t)(g - 1) * m->max_seqs * PV;
@@ -1286,6 +1297,18 @@ static int create_impl(omni_talker* m, const omni_tensor* tensors, int32_t n_ten
     for (int64_t r0 = 0; r0 < total; r0 += chunk)
       TRY(gemm(m, m->mtp_w, (int)p, (int)h, m->p_emb + r0 * h, (int)std::min(chunk, total - r0), m->p_emb_proj + r0 * p,
                (int)p, bias));
+    // ... and on through the first layer's input norm and q|k|v projection: that layer's q | k | v of a pass's row
+    // depend on the code alone too (attention is where the pass first meets its earlier rows)
+    const int64_t qw = m->pred.qkv_width();
+    bf16 *xn = nullptr, *res = nullptr;
+    TRY(dev_alloc(m, &m->p_qkv0, (size_t)total * qw));
+    TRY(dev_alloc(m, &xn, (size_t)chunk * p));
+    TRY(dev_alloc(m, &res, (size_t)chunk * p));
+    for (int64_t r0 = 0; r0 < total; r0 += chunk) {
+      const int rows = (int)std::min(chunk, total - r0);
+      LAUNCH(m, launch_norm_copy(m->p_emb_proj + r0 * p, m->pred.layers[0].ln1, xn, res, rows, (int)p, pc.rms_eps, m->stream));
+      TRY(gemm(m, m->pred.layers[0].qkv, (int)qw, (int)p, xn, rows, m->p_qkv0 + r0 * qw, (int)qw));
+    }
     CUDA_TRY(m, cudaStreamSynchronize(m->stream));
     m->plans.clear();  // the plans of these one-off products are not needed again
   }

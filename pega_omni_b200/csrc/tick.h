@@ -37,6 +37,8 @@ enum NextInput : int32_t { kNextNone = 0, kNextHiddenAndCode = 1, kNextCode = 2,
 //  AddNorm:    rows, dim = N, tiles, splits, bn; src3 gain; dst0 res, dst1 out; i0 every, i1 which; f0 eps
 //  RopeAttn:   rows, tiles, splits, bn; i0 hq, i1 hk, i2 head_dim, i3 per, i4 base, i5 paged, i6 kv_pages;
 //              src0 q_norm, src1 k_norm; dst0 kv layer, dst1 attn out; f0 eps, f1 theta
+//  RopeAttn (one-page sequences only): src2 != nullptr: the rows' q | k | v are rows of the table at src2 (bf16, i8
+//              elements per row), row = the code of group i7 drawn for the sequence; no partial tiles are read
 //  ReduceSilu: rows, tiles, splits, bn; dst0 act; i0 inter
 //  Sample:     rows, tiles, splits, bn, N = vocab; dst0 logits out, i0 ldl (row stride of logits out, elements);
 //              sampling constants in f0..f3 / i1..i7; next-input in i8, src0 table, src1 hidden, dst1 p_in, i9 dim;

@@ -495,7 +495,23 @@ __device__ __noinline__ void rope_attend_item(const Phase& ph, const TickIo& io,
       }
 #pragma unroll
       for (int g = 0; g < VE / E; ++g) cols[(G + 1) * 2 + g] = (hq + hk + kh) * D + lane * VE + g * E;
-      reduce_vecs<NG, E>(pt, n, cols, val);
+      if (ph.src2) {
+        // the row's q | k | v were computed at load for every code (a pass's first-layer input is a function of the
+        // code drawn before it alone): read the code's row instead of summing partial tiles of a GEMM
+        const int code = io.codes[n * 16 + ph.i7];
+        const bf16* qkv_row = (const bf16*)ph.src2 + (int64_t)code * ph.i8;
+#pragma unroll
+        for (int j = 0; j < NG; ++j) {
+          if constexpr (E == 2) {
+            const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(qkv_row + cols[j]));
+            val[j * E] = f.x, val[j * E + 1] = f.y;
+          } else {
+            val[j] = __bfloat162float(qkv_row[cols[j]]);
+          }
+        }
+      } else {
+        reduce_vecs<NG, E>(pt, n, cols, val);
+      }
 #pragma unroll
       for (int j = 0; j <= G; ++j) {
         float lo[E], hi[E];
