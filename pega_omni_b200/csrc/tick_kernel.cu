@@ -740,7 +740,8 @@ __device__ __noinline__ void gemm_epilogue(const Phase& ph, float* partials, int
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
           const float gg = bf16_round(g[j]);
-          o[j] = bf16_round(gg / (1.f + __expf(-gg))) * bf16_round(u[j]);
+          // the fast division differs from the IEEE one by at most 2 ulp of an f32 that is rounded to bf16 next
+          o[j] = bf16_round(__fdividef(gg, 1.f + __expf(-gg))) * bf16_round(u[j]);
         }
         st8(act + (int64_t)m * inter + ch, o);
         st8(act + (int64_t)m * inter + ch + 8, o + 8);
