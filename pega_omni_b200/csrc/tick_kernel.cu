@@ -714,14 +714,20 @@ __device__ __noinline__ void gemm_epilogue(const Phase& ph, float* partials, int
   const uint32_t lane_addr = tmem_acc + ((uint32_t)(quad * 32) << 16);
   if (ph.mode == kGemmPartials) {
     float* rowp = partials + (((size_t)split * ph.tiles + tile) * ph.bn + min(m, ph.bn - 1)) * tn;
+    // 32 columns per round: both loads are under way before the one wait (tn / 2 is 32, 64 or 128 here)
 #pragma unroll 1
-    for (int c0 = half * (tn / 2); c0 < (half + 1) * (tn / 2); c0 += 16) {
-      float v[16];
-      sm100::tmem_ld16(lane_addr + c0, v);
+    for (int c0 = half * (tn / 2); c0 < (half + 1) * (tn / 2); c0 += 32) {
+      uint32_t a[16], b[16];
+      sm100::tmem_ld16_issue(lane_addr + c0, a);
+      sm100::tmem_ld16_issue(lane_addr + c0 + 16, b);
+      sm100::tmem_ld_fence(a, b);
       if (m < ph.rows) {
 #pragma unroll
         for (int j = 0; j < 16; j += 4)
-          *reinterpret_cast<float4*>(rowp + c0 + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+          *reinterpret_cast<uint4*>(rowp + c0 + j) = make_uint4(a[j], a[j + 1], a[j + 2], a[j + 3]);
+#pragma unroll
+        for (int j = 0; j < 16; j += 4)
+          *reinterpret_cast<uint4*>(rowp + c0 + 16 + j) = make_uint4(b[j], b[j + 1], b[j + 2], b[j + 3]);
       }
     }
   } else {
@@ -732,8 +738,14 @@ __device__ __noinline__ void gemm_epilogue(const Phase& ph, float* partials, int
 #pragma unroll 1
     for (int c0 = half * 16; c0 < hc; c0 += 32) {
       float g[16], u[16];
-      sm100::tmem_ld16(lane_addr + c0, g);
-      sm100::tmem_ld16(lane_addr + hc + c0, u);
+      {
+        uint32_t gr[16], ur[16];
+        sm100::tmem_ld16_issue(lane_addr + c0, gr);
+        sm100::tmem_ld16_issue(lane_addr + hc + c0, ur);
+        sm100::tmem_ld_fence(gr, ur);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) g[j] = __uint_as_float(gr[j]), u[j] = __uint_as_float(ur[j]);
+      }
       const int ch = tile * hc + c0;
       if (m < ph.rows && ch < inter) {
         float o[16];
