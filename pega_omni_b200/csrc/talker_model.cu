@@ -700,12 +700,19 @@ struct TickBuilder {
       const Phase ph = gemm(m->lm_heads + (size_t)(g - 1) * PV * p, PV, p, m->p_last, b);
       const bool more = g + 1 < c.groups;
       bf16* lg = m->p_logits + (size_t)(g - 1) * m->max_seqs * PV;
-      if (more && folded)
+      if (more && folded) {
         sample(ph, g, b, lg, PV, kNextProjected, m->p_emb_proj + (size_t)(g - 1) * PV * p, nullptr, m->P.res, p,
                m->pred.layers[0].ln1, c.predictor.rms_eps, m->P.x);
-      else
+        if (m->p_qkv0) {  // the row the next pass's first attention phase will read
+          Phase& sp = prog->phases.back();
+          sp.src1 = m->p_qkv0 + (size_t)(g - 1) * PV * m->pred.qkv_width();
+          sp.i11 = m->pred.qkv_width() * (int)sizeof(bf16);
+        }
+      }
+      else {
         sample(ph, g, b, lg, PV, more ? kNextCode : kNextNone, more ? m->p_emb + (size_t)(g - 1) * PV * h : nullptr,
                nullptr, m->p_in, h);
+      }
     }
   }
 };

@@ -471,7 +471,8 @@ __device__ __noinline__ void rope_attend_item(const Phase& ph, const TickIo& io,
     const int n = seq * per + r;
     const int pos = paged ? io.d_pos[n] : base + r;
     float cs[E], sn[E];
-    rope_angles<D>(lane, pos, ph.f1, cs, sn);
+    // (the two-warp path takes its angles after it has asked for its partial sums: the row's position is a load there)
+    if constexpr (!(G == 2 && W == 2 && D == 128)) rope_angles<D>(lane, pos, ph.f1, cs, sn);
     const int64_t slot = paged ? io.d_slot[n] : (int64_t)seq * 16 + pos;
     int64_t page = slot >> 4;
     const int tok = (int)(slot & 15);
@@ -531,6 +532,35 @@ __device__ __noinline__ void rope_attend_item(const Phase& ph, const TickIo& io,
       }
 #pragma unroll
       for (int e = 0; e < VE; ++e) vdst[lane * VE + e] = __float2bfloat16(val[(G + 1) * 2 * E + e]);
+    } else if constexpr (G == 2 && W == 2 && D == 128) {
+      // two query heads, the key head and the value head over two warps: each warp takes one query head and one of
+      // key / value, and asks for all its partial sums in one batch (one L2 round trip instead of two)
+      const int qcol = (kh * G + warp) * D, kcol = (hq + kh) * D, vcol = (hq + hk + kh) * D;
+      int cols[4];
+      cols[0] = qcol + lane * E, cols[1] = qcol + D / 2 + lane * E;
+      if (warp == 0) cols[2] = kcol + lane * E, cols[3] = kcol + D / 2 + lane * E;
+      else cols[2] = vcol + lane * VE, cols[3] = vcol + lane * VE + E;
+      float val[4 * E], lo[E], hi[E];
+      reduce_vecs<4, E>(pt, n, cols, val);
+      rope_angles<D>(lane, pos, ph.f1, cs, sn);
+#pragma unroll
+      for (int e = 0; e < E; ++e) lo[e] = bf16_round(val[e]), hi[e] = bf16_round(val[E + e]);
+      rope_head<D>(lo, hi, qwl, qwh, cs, sn, ph.f0);
+#pragma unroll
+      for (int e = 0; e < E; ++e) sh.qs[warp][lane * E + e] = lo[e], sh.qs[warp][D / 2 + lane * E + e] = hi[e];
+      if (warp == 0) {
+#pragma unroll
+        for (int e = 0; e < E; ++e) lo[e] = bf16_round(val[2 * E + e]), hi[e] = bf16_round(val[3 * E + e]);
+        rope_head<D>(lo, hi, kwl, kwh, cs, sn, ph.f0);
+#pragma unroll
+        for (int e = 0; e < E; ++e) {
+          kdst[lane * E + e] = __float2bfloat16(lo[e]);
+          kdst[D / 2 + lane * E + e] = __float2bfloat16(hi[e]);
+        }
+      } else {
+#pragma unroll
+        for (int e = 0; e < VE; ++e) vdst[lane * VE + e] = __float2bfloat16(val[2 * E + e]);
+      }
     } else {
       for (int job = warp; job < G + 2; job += W) {
         if (job == G + 1) {  // value: plain copy
@@ -689,6 +719,8 @@ __device__ __noinline__ void phase_sample(const Phase& ph, const TickIo& io, con
         *reinterpret_cast<Pack8*>(dst + (int64_t)row * dim + i) =
             *reinterpret_cast<const Pack8*>(table + (int64_t)token * dim + i);
     } else if (ph.i8 == kNextProjected && wtid < kGroupThreads) {
+      // the next pass's first attention phase reads the code's q | k | v row (src1, i11 bytes): ask it into L2 now
+      if (wtid == 0 && ph.src1) sm100::prefetch_l2((const char*)ph.src1 + (int64_t)token * ph.i11, (uint32_t)ph.i11);
       const bf16* src = (const bf16*)ph.src0 + (int64_t)token * dim;
       bf16 *res = (bf16*)ph.dst1 + (int64_t)row * dim, *out = (bf16*)ph.dst2 + (int64_t)row * dim;
       switch (dim) {
