@@ -246,6 +246,10 @@ struct Team {
     }
 
     // --- the reference's block scan over 1024 virtual threads (talker.cu:136-169) ---
+    // A virtual warp is 32 / VPT neighbouring lanes of a real warp, each holding VPT consecutive virtual lanes, so the
+    // reference's shuffle scan (x[i] += x[i - o] for o = 1, 2, 4, 8, 16, every lane reading the values of the step
+    // before) runs on real shuffles: a source o < VPT lanes back sits in this thread or in the lane before it, a
+    // source o >= VPT lanes back o / VPT lanes before, in the same slot. Same additions in the same order.
     float own[VPT], incl[VPT];
 #pragma unroll
     for (int q = 0; q < VPT; ++q) {
@@ -253,7 +257,6 @@ struct Team {
 #pragma unroll
       for (int e = 0; e < kVirtualPer; ++e) o += p[q * kVirtualPer + e];
       own[q] = incl[q] = o;
-      sh.vscan[tid * VPT + q] = o;
     }
     if (tid == 0) {
       sh.token = -1;
@@ -261,21 +264,21 @@ struct Team {
     }
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
-      Sync::sync();
       float up[VPT];
 #pragma unroll
       for (int q = 0; q < VPT; ++q) {
-        const int vt = tid * VPT + q;
-        up[q] = (vt & 31) >= o ? sh.vscan[vt - o] : 0.f;
+        if (o >= VPT) {
+          up[q] = __shfl_up_sync(0xffffffffu, incl[q], o / VPT);
+        } else {
+          const float before = __shfl_up_sync(0xffffffffu, incl[(q + VPT - o) % VPT], 1);
+          up[q] = q >= o ? incl[q - o] : before;
+        }
       }
-      Sync::sync();
 #pragma unroll
-      for (int q = 0; q < VPT; ++q) {
-        const int vt = tid * VPT + q;
-        if ((vt & 31) >= o) incl[q] += up[q];
-        sh.vscan[vt] = incl[q];
-      }
+      for (int q = 0; q < VPT; ++q)
+        if (((tid * VPT + q) & 31) >= o) incl[q] += up[q];
     }
+    if (((tid * VPT + VPT - 1) & 31) == 31) sh.vscan[tid * VPT + VPT - 1] = incl[VPT - 1];  // a virtual warp's total
     Sync::sync();
     if (tid < 32) {  // the same scan over the 32 group totals
       float wsum = sh.vscan[tid * 32 + 31];
