@@ -61,7 +61,7 @@ struct Shared {
   int token, last;
   unsigned long long best;
   int n_cand;
-  int cand_idx[kMaxNucleus];
+  alignas(16) int cand_idx[kMaxNucleus];  // 16-byte aligned: the four arrays from here on also stage a row of logits
   float cand_p[kMaxNucleus];
   int sorted_idx[kMaxNucleus];
   float sorted_p[kMaxNucleus];

@@ -677,25 +677,44 @@ __device__ __noinline__ void phase_sample(const Phase& ph, const TickIo& io, con
     const int forced = io.force[row * 16 + prm.group], frame = io.frames[row];
     const float uniform = io.uniforms[row * 16 + prm.group];
     const uint32_t seen_bits = Team::seen_word(slot, prm, wtid);
-    // this thread's PER consecutive logits: reduce the head's split-K partials, round, publish
+    // The head's split-K partials are summed with every warp reading whole 512-byte runs of a tile row (thread t takes
+    // columns 4 (256 j + t) .. + 3), rounded and published from there; a thread's own PER consecutive logits then
+    // come back through shared memory (the nucleus arrays, idle until the draw needs them).
     float mine[Team::PER];
     {
-      // four columns per load; the head's vocabulary is a multiple of 4 and tiles are padded to a full tile_n
-      int cols[Team::PER / 4];
+      float* stage = reinterpret_cast<float*>(sh.cand_idx);  // cand_idx | cand_p | sorted_idx | sorted_p: kVocabMax floats
+      static_assert(offsetof(sampler::Shared, sorted_p) - offsetof(sampler::Shared, cand_idx) == 3 * sampler::kMaxNucleus * 4 &&
+                        4 * sampler::kMaxNucleus >= sampler::kVocabMax,
+                    "the four nucleus arrays are contiguous and hold a row of logits");
+      const Partials pt(partials, ph);
 #pragma unroll
-      for (int j = 0; j < Team::PER / 4; ++j) cols[j] = min(wtid * Team::PER + 4 * j, prm.vocab - 4);
-      if (wtid * Team::PER < prm.vocab) {  // threads past the vocabulary own no logit: no loads for them
-        reduce_vecs<Team::PER / 4, 4>(Partials(partials, ph), row, cols, mine);
-      } else {
+      for (int j0 = 0; j0 < Team::PER / 4; j0 += 2) {
+        if ((j0 * kWorkerThreads) * 4 >= prm.vocab) break;  // CTA-uniform: no column of this round is inside the vocabulary
+        int cols[2];
+        float sum[8];
 #pragma unroll
-        for (int j = 0; j < Team::PER; ++j) mine[j] = 0.f;
+        for (int j = 0; j < 2; ++j) cols[j] = min(((j0 + j) * kWorkerThreads + wtid) * 4, prm.vocab - 4);
+        reduce_vecs<2, 4>(pt, row, cols, sum);
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          const int col = ((j0 + j) * kWorkerThreads + wtid) * 4;
+          if (col < prm.vocab) {
+            float r[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) r[e] = bf16_round(sum[j * 4 + e]);
+            *reinterpret_cast<float4*>(stage + col) = make_float4(r[0], r[1], r[2], r[3]);
+            st_bf16<4>(logits_out + (int64_t)row * ph.i0 + col, r);
+          }
+        }
       }
+      WorkerSync::sync();
 #pragma unroll
-      for (int j = 0; j < Team::PER; ++j) {
-        const bf16 b = __float2bfloat16(mine[j]);
-        mine[j] = __bfloat162float(b);
-        if (wtid * Team::PER + j < prm.vocab) logits_out[(int64_t)row * ph.i0 + wtid * Team::PER + j] = b;
+      for (int j = 0; j < Team::PER; j += 4) {
+        const int col = wtid * Team::PER + j;
+        const float4 v = col < prm.vocab ? *reinterpret_cast<const float4*>(stage + col) : make_float4(0.f, 0.f, 0.f, 0.f);
+        mine[j] = v.x, mine[j + 1] = v.y, mine[j + 2] = v.z, mine[j + 3] = v.w;
       }
+      WorkerSync::sync();  // the staging rows are the draw's nucleus arrays again
     }
     if (stamp && wtid == 0) stamp[0] = sm100::global_timer_ns();  // the row's logits are summed
     const int token = Team::sample_row([&](int, int j) { return mine[j]; }, prm, frame, uniform, forced, slot, seen_bits,
