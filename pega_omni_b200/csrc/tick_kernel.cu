@@ -406,49 +406,50 @@ __device__ __noinline__ void add_norm_rows(const Phase& ph, const float* partial
   }
 }
 
-// AddNorm of a 2048-wide row by all 256 workers of a CTA (one row per CTA, when the phase has no more rows than the
-// grid has CTAs): a thread owns columns 4 (256 j + t) .. + 3 for j = 0, 1, so the partial tiles of up to eight K
-// splits are one batch of sixteen 16-byte loads per thread (a 128-thread group needs two batches, two L2 round
-// trips). The splits are summed in split order per element, as everywhere.
+// AddNorm of a 1024- or 2048-wide row by all 256 workers of a CTA (one row per CTA, when the phase has no more rows
+// than the grid has CTAs): a thread owns columns 4 (256 j + t) .. + 3 for j < kDim / 1024, so the partial tiles of up
+// to eight K splits are one batch of at most sixteen 16-byte loads per thread (a 128-thread group needs two batches,
+// two L2 round trips, for a 2048-wide row). The splits are summed in split order per element, as everywhere.
+template <int kDim>
 __device__ __noinline__ void add_norm_rows_wide(const Phase& ph, const float* partials, int wtid, float* red) {
-  constexpr int kDim = 2048;
+  constexpr int NJ = kDim / (kWorkerThreads * 4);
   const int row = blockIdx.x, every = ph.i0, which = ph.i1;
   if (row >= ph.rows) return;
   bf16 *res = (bf16*)ph.dst0 + (int64_t)row * kDim, *out = (bf16*)ph.dst1;
   const bf16* gain = (const bf16*)ph.src3;
   const Partials pt(partials, ph);
-  int col[2];
-  uint32_t off[2];
-  uint2 graw[2];
-  float v[8], old[8];
+  int col[NJ];
+  uint32_t off[NJ];
+  uint2 graw[NJ];
+  float v[4 * NJ], old[4 * NJ];
 #pragma unroll
-  for (int j = 0; j < 2; ++j) {
+  for (int j = 0; j < NJ; ++j) {
     col[j] = (j * kWorkerThreads + wtid) * 4;
     off[j] = pt.at(row, col[j]);
     graw[j] = __ldg(reinterpret_cast<const uint2*>(gain + col[j]));
     ld_bf16<4>(res + col[j], &old[j * 4]);
   }
 #pragma unroll
-  for (int i = 0; i < 8; ++i) v[i] = 0.f;
+  for (int i = 0; i < 4 * NJ; ++i) v[i] = 0.f;
   const float* base = pt.base;
   for (int s0 = 0; s0 < pt.splits; s0 += 8, base += 8 * pt.split_stride) {
-    float4 f[8][2];
+    float4 f[8][NJ];
 #pragma unroll
     for (int b = 0; b < 8; ++b)
 #pragma unroll
-      for (int j = 0; j < 2; ++j)
+      for (int j = 0; j < NJ; ++j)
         f[b][j] = s0 + b < pt.splits ? __ldcg(reinterpret_cast<const float4*>(base + b * pt.split_stride + off[j]))
                                      : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
     for (int b = 0; b < 8; ++b)
 #pragma unroll
-      for (int j = 0; j < 2; ++j) {
+      for (int j = 0; j < NJ; ++j) {
         v[4 * j] += f[b][j].x, v[4 * j + 1] += f[b][j].y, v[4 * j + 2] += f[b][j].z, v[4 * j + 3] += f[b][j].w;
       }
   }
   float ss = 0.f;
 #pragma unroll
-  for (int i = 0; i < 8; ++i) {
+  for (int i = 0; i < 4 * NJ; ++i) {
     v[i] = bf16_round(v[i]) + old[i];  // the norm runs over the unrounded sum (qwen3.cu:34)
     ss += v[i] * v[i];
   }
@@ -462,7 +463,7 @@ __device__ __noinline__ void add_norm_rows_wide(const Phase& ph, const float* pa
   const float r = rsqrtf(total / kDim + ph.f0);
   const bool keep = row % every == which;
 #pragma unroll
-  for (int j = 0; j < 2; ++j) {
+  for (int j = 0; j < NJ; ++j) {
     const float2 g0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&graw[j].x));
     const float2 g1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&graw[j].y));
     const float g[4] = {g0.x, g0.y, g1.x, g1.y};
@@ -1161,7 +1162,8 @@ __global__ void __launch_bounds__(kThreads, 1) tick_kernel(const __grid_constant
         case kPhEmbedNorm: OMNI_ROW_DISPATCH(embed_norm_rows, ph.N, ph, a.io, tm, a.err); break;
         case kPhReduceNorm: OMNI_ROW_DISPATCH(reduce_norm_rows, ph.N, ph, a.partials, tm); break;
         case kPhAddNorm:
-          if (ph.N == 2048 && ph.rows <= G) add_norm_rows_wide(ph, a.partials, wtid, &ctl.red[0][0]);
+          if (ph.N == 2048 && ph.rows <= G) add_norm_rows_wide<2048>(ph, a.partials, wtid, &ctl.red[0][0]);
+          else if (ph.N == 1024 && ph.rows <= G) add_norm_rows_wide<1024>(ph, a.partials, wtid, &ctl.red[0][0]);
           else OMNI_ROW_DISPATCH(add_norm_rows, ph.N, ph, a.partials, tm);
           break;
         case kPhReduceSilu: reduce_silu_rows(ph, a.partials, tm); break;
