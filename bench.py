@@ -467,7 +467,8 @@ def run_sweep(args, rank, world, local):
     if rank == 0:
         peak, peak_kind = measured_peaks()
         mean_len = float(np.mean(lens)) + 1 + W + (K - 1) / 2 + 1
-        tick_bytes = len(groups) * cfg.tick_weight_bytes() + cfg.talker.kv_bytes_per_token() * n * (mean_len + 1)
+        tick_bytes = (len(groups) * (cfg.tick_weight_bytes() - cfg.tick_folded_bytes(min(n, 128))) +
+                      cfg.talker.kv_bytes_per_token() * n * (mean_len + 1))
         tick_s = float(t_el.item()) / K
         line = {"metric": "codec frames/sec at %d sessions per GPU (Qwen3-TTS talker), ragged prompts" % n,
                 "value": n * world * K / float(t_el.item()), "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
@@ -704,7 +705,8 @@ def main():
     if rank == 0:
         peak, peak_kind = measured_peaks()
         mean_len = float(np.mean(lens)) + 1
-        tick_bytes = cfg.tick_weight_bytes() + cfg.talker.kv_bytes_per_token() * n * (mean_len + 1)
+        weight_bytes = cfg.tick_weight_bytes() - (cfg.tick_folded_bytes(n) if launches_per_tick <= 2 else 0)
+        tick_bytes = weight_bytes + cfg.talker.kv_bytes_per_token() * n * (mean_len + 1)
         tick_s = elapsed / K
         # two more readings of the same time: against the nominal 8 TB/s, and counting the predictor's weights once per tick
         # (they are one L2's worth: 14 of the 15 passes can be served on chip)
@@ -719,11 +721,11 @@ def main():
                 "frac_nominal": tick_bytes / tick_s / 1e9 / 8000.0, "peak_nominal": 8000.0,
                 "frac_predictor_weights_once": once_bytes / tick_s / 1e9 / peak,
                 "bytes_per_launch": int(tick_bytes), "us_per_launch": tick_s * 1e6,
-                # ncu cannot run inside the timed region: the DRAM bytes of one captured tick (6,399 MB read + written
-                # for 6,296 MB algorithmic at positions 131-132) scaled to this run's algorithmic bytes; the traffic
+                # ncu cannot run inside the timed region: the DRAM bytes of one captured tick (6,231 MB read + written
+                # for 6,129 MB algorithmic at positions 131-132) scaled to this run's algorithmic bytes; the traffic
                 # grows with the KV length as they do
-                "traffic": int(tick_bytes * 6399.1 / 6296.2) if launches_per_tick <= 2 else None,
-                "traffic_note": "ncu dram__bytes_read+write of one captured tick (6.399 GB for 6.296 GB algorithmic), "
+                "traffic": int(tick_bytes * 6230.8 / 6129.2) if launches_per_tick <= 2 else None,
+                "traffic_note": "ncu dram__bytes_read+write of one captured tick (6.231 GB for 6.129 GB algorithmic), "
                                 "scaled by this run's algorithmic bytes"}
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
@@ -749,8 +751,8 @@ def main():
                         "tokens_per_s": n * args.prompt / (prefill_ms * 1e-3) if prefill_ms > 0 else None,
                         "what": "omni_talker_start in calls of at most 32 prompts: ragged prefill + first frame, untimed "
                                 "by the headline metric (includes first-call plan building)"},
-            "tick_bytes": {"weights": int(cfg.tick_weight_bytes()), "kv": int(tick_bytes - cfg.tick_weight_bytes()),
-                           "mean_kv_len": mean_len},
+            "tick_bytes": {"weights": int(weight_bytes), "kv": int(tick_bytes - weight_bytes), "mean_kv_len": mean_len,
+                           "folded_at_load": int(cfg.tick_weight_bytes() - weight_bytes)},
         }
         if not args.no_replay and world == 1:
             model.close()

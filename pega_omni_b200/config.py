@@ -68,6 +68,18 @@ class TalkerConfig:
         heads = (g - 1) * 2 * p.vocab_size * p.hidden_size
         return talker + (g - 1) * per_pass + heads
 
+    def tick_folded_bytes(self, sessions: int) -> int:
+        """What the persistent kernel does NOT stream of tick_weight_bytes(): from the second predictor pass on the input
+        projection and the first layer's q|k|v projection are table rows computed at load (one projected row and one
+        q|k|v row per session and pass are read instead)."""
+        t, p, g = self.talker, self.predictor, self.num_code_groups
+        if g <= 2:
+            return 0
+        qkv = (p.num_attention_heads + 2 * p.num_key_value_heads) * p.head_dim
+        per_pass = 2 * (p.hidden_size * t.hidden_size + qkv * p.hidden_size)
+        rows = 2 * sessions * (p.hidden_size + qkv)
+        return (g - 2) * (per_pass - rows)
+
     def tick_kv_bytes(self, lens) -> int:
         """KV bytes a tick reads (positions 0..len-1 of every session) plus the row it writes."""
         per = self.talker.kv_bytes_per_token()
