@@ -52,12 +52,10 @@ __device__ __forceinline__ float philox_uniform(uint64_t seed, uint32_t frame, u
 }
 
 struct Shared {
-  uint32_t hist[256];
+  alignas(16) uint32_t hist[4][256];  // one set of digit counters per pass of the k-th key selection
   float red[32];
   float wtot[32];
   float vscan[kVirtualThreads];
-  uint32_t sel_prefix, sel_left;
-  uint32_t warp_count[8];
   int token, last;
   unsigned long long best;
   int n_cand;
@@ -110,16 +108,17 @@ struct Team {
   // a few units wide, so the keys' leading digits take a handful of values: counted one atomic per key, a pass would
   // serialise thousands of additions on two or three shared-memory words. In the first pass each warp therefore
   // groups its lanes by digit (__match_any_sync) and the lowest lane of a group adds the group's size, so a counter
-  // sees at most one addition per warp and step. The digit is then picked by a suffix count
-  // over the 256 counters: warp w owns counters 32w .. 32w + 31 (one per lane, a shuffle scan inside the warp), the
-  // eight warp totals are combined by every thread that needs them.
+  // sees at most one addition per warp and step. Every pass has its own 256 counters (zeroed once, up front), and
+  // after the pass's one team barrier EVERY warp picks the digit by itself from the counters (lane l sums counters
+  // 8l .. 8l + 7, a shuffle scan gives the keys above each lane's range), so a pass costs one barrier, not four.
   static __device__ uint32_t kth_largest_key(const uint32_t* key, int vocab, uint32_t k, int tid, Shared& sh) {
-    static_assert(THREADS >= 256, "one counter per thread of the first eight warps");
     uint32_t prefix = 0, left = k;
-    const int lane = tid & 31, warp = tid >> 5;
-    for (int shift = 24; shift >= 0; shift -= 8) {
-      if (tid < 256) sh.hist[tid] = 0;
-      Sync::sync();
+    const int lane = tid & 31;
+    for (int i = tid; i < 4 * 256; i += THREADS) (&sh.hist[0][0])[i] = 0;
+    Sync::sync();
+    for (int pass = 0; pass < 4; ++pass) {
+      const int shift = 24 - 8 * pass;
+      uint32_t* hist = sh.hist[pass];
       const uint32_t fixed = shift == 24 ? 0u : 0xffffffffu << (shift + 8);
       if (shift == 24) {
 #pragma unroll
@@ -127,38 +126,43 @@ struct Team {
           const bool in = tid * PER + j < vocab;
           const uint32_t digit = in ? key[j] >> 24 : 256u;  // lanes past the vocabulary form their own group
           const uint32_t same = __match_any_sync(0xffffffffu, digit);
-          if (in && lane == __ffs(same) - 1) atomicAdd(&sh.hist[digit], (uint32_t)__popc(same));
+          if (in && lane == __ffs(same) - 1) atomicAdd(&hist[digit], (uint32_t)__popc(same));
         }
       } else {  // only the keys that carry the digits fixed so far count: few, and spread over the counters
 #pragma unroll
         for (int j = 0; j < PER; ++j)
-          if (tid * PER + j < vocab && ((key[j] ^ prefix) & fixed) == 0) atomicAdd(&sh.hist[(key[j] >> shift) & 255u], 1u);
+          if (tid * PER + j < vocab && ((key[j] ^ prefix) & fixed) == 0) atomicAdd(&hist[(key[j] >> shift) & 255u], 1u);
       }
       Sync::sync();
-      // suffix[d] = keys whose digit is >= d; the digit wanted is the largest d with suffix[d] >= left
-      uint32_t mine = 0, incl = 0;  // this counter, and the inclusive suffix sum inside the warp (towards higher lanes)
-      if (tid < 256) {
-        mine = incl = sh.hist[tid];
+      // at_least[d] = keys whose digit is >= d; the digit wanted is the one with at_least - count < left <= at_least
+      uint32_t c[8];
+      *reinterpret_cast<uint4*>(&c[0]) = *reinterpret_cast<const uint4*>(&hist[8 * lane]);
+      *reinterpret_cast<uint4*>(&c[4]) = *reinterpret_cast<const uint4*>(&hist[8 * lane + 4]);
+      uint32_t mine = 0;
 #pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-          const uint32_t other = __shfl_down_sync(0xffffffffu, incl, o);
-          if (lane + o < 32) incl += other;
-        }
-        if (lane == 0) sh.warp_count[warp] = incl;
+      for (int j = 0; j < 8; ++j) mine += c[j];
+      uint32_t incl = mine;  // keys in this lane's counters and in those of the lanes above it
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const uint32_t other = __shfl_down_sync(0xffffffffu, incl, o);
+        if (lane + o < 32) incl += other;
       }
-      Sync::sync();
-      if (tid < 256) {
-        uint32_t above_warps = 0;  // keys in the counters of higher warps
-        for (int w = warp + 1; w < 8; ++w) above_warps += sh.warp_count[w];
-        const uint32_t at_least = incl + above_warps, above = at_least - mine;
-        if (above < left && at_least >= left) {  // exactly one counter satisfies this
-          sh.sel_prefix = prefix | (uint32_t)tid << shift;
-          sh.sel_left = left - above;
+      uint32_t at_least = incl - mine, digit = 0, new_left = 0;
+      bool found = false;
+#pragma unroll
+      for (int j = 7; j >= 0; --j) {
+        const uint32_t above = at_least;
+        at_least += c[j];
+        if (!found && above < left && at_least >= left) {
+          found = true;
+          digit = 8u * lane + j;
+          new_left = left - above;
         }
       }
-      Sync::sync();
-      prefix = sh.sel_prefix;
-      left = sh.sel_left;
+      const uint32_t who = __ballot_sync(0xffffffffu, found);  // exactly one lane
+      const int src = __ffs(who) - 1;
+      prefix |= __shfl_sync(0xffffffffu, digit, src) << shift;
+      left = __shfl_sync(0xffffffffu, new_left, src);
     }
     return prefix;
   }
