@@ -53,6 +53,7 @@ __device__ __forceinline__ float philox_uniform(uint64_t seed, uint32_t frame, u
 
 struct Shared {
   alignas(16) uint32_t hist[4][256];  // one set of digit counters per pass of the k-th key selection
+  uint32_t warp_cnt[32];
   float red[32];
   float wtot[32];
   float vscan[kVirtualThreads];
@@ -105,34 +106,44 @@ struct Team {
   }
 
   // The k-th largest key of the row (ties share it), most significant digit first, eight bits at a time. Logits are
-  // a few units wide, so the keys' leading digits take a handful of values: counted one atomic per key, a pass would
-  // serialise thousands of additions on two or three shared-memory words. In the first pass each warp therefore
-  // groups its lanes by digit (__match_any_sync) and the lowest lane of a group adds the group's size, so a counter
-  // sees at most one addition per warp and step. Every pass has its own 256 counters (zeroed once, up front), and
-  // after the pass's one team barrier EVERY warp picks the digit by itself from the counters (lane l sums counters
-  // 8l .. 8l + 7, a shuffle scan gives the keys above each lane's range), so a pass costs one barrier, not four.
-  static __device__ uint32_t kth_largest_key(const uint32_t* key, int vocab, uint32_t k, int tid, Shared& sh) {
+  // a few units wide, so the keys' leading digits take a handful of values: counted one atomic per key, that pass would
+  // serialise thousands of additions on two or three shared-memory words, so the first digit is found by counting
+  // (below). The other passes count through shared-memory atomics; every pass has its own 256 counters (zeroed once,
+  // up front), and after the pass's one team barrier EVERY warp picks the digit by itself from the counters (lane l
+  // sums counters 8l .. 8l + 7, a shuffle scan gives the keys above each lane's range).
+  static __device__ uint32_t kth_largest_key(const uint32_t* key, int vocab, uint32_t k, uint32_t top_digit, int tid,
+                                             Shared& sh) {
     uint32_t prefix = 0, left = k;
     const int lane = tid & 31;
     for (int i = tid; i < 4 * 256; i += THREADS) (&sh.hist[0][0])[i] = 0;
-    Sync::sync();
-    for (int pass = 0; pass < 4; ++pass) {
+    // First digit: the keys' leading bytes take two or three values just below the largest key's (`top_digit`), so
+    // they are not counted through shared-memory atomics at all: from the top byte downwards, every thread counts
+    // its own keys with that byte and the team adds the counts, until the k-th key's byte is reached.
+    for (uint32_t d = top_digit;; --d) {
+      uint32_t mine = 0;
+#pragma unroll
+      for (int j = 0; j < PER; ++j) mine += tid * PER + j < vocab && key[j] >> 24 == d ? 1u : 0u;
+      mine = __reduce_add_sync(0xffffffffu, mine);
+      Sync::sync();  // (also orders the zeroing above, and the previous round's reads, before the writes below)
+      if (lane == 0) sh.warp_cnt[tid >> 5] = mine;
+      Sync::sync();
+      uint32_t total = 0;
+#pragma unroll
+      for (int w = 0; w < THREADS / 32; ++w) total += sh.warp_cnt[w];
+      if (total >= left || d == 0) {
+        prefix = d << 24;
+        break;
+      }
+      left -= total;
+    }
+    for (int pass = 1; pass < 4; ++pass) {
       const int shift = 24 - 8 * pass;
       uint32_t* hist = sh.hist[pass];
-      const uint32_t fixed = shift == 24 ? 0u : 0xffffffffu << (shift + 8);
-      if (shift == 24) {
+      const uint32_t fixed = 0xffffffffu << (shift + 8);
+      // only the keys that carry the digits fixed so far count, spread over the counters
 #pragma unroll
-        for (int j = 0; j < PER; ++j) {
-          const bool in = tid * PER + j < vocab;
-          const uint32_t digit = in ? key[j] >> 24 : 256u;  // lanes past the vocabulary form their own group
-          const uint32_t same = __match_any_sync(0xffffffffu, digit);
-          if (in && lane == __ffs(same) - 1) atomicAdd(&hist[digit], (uint32_t)__popc(same));
-        }
-      } else {  // only the keys that carry the digits fixed so far count: few, and spread over the counters
-#pragma unroll
-        for (int j = 0; j < PER; ++j)
-          if (tid * PER + j < vocab && ((key[j] ^ prefix) & fixed) == 0) atomicAdd(&hist[(key[j] >> shift) & 255u], 1u);
-      }
+      for (int j = 0; j < PER; ++j)
+        if (tid * PER + j < vocab && ((key[j] ^ prefix) & fixed) == 0) atomicAdd(&hist[(key[j] >> shift) & 255u], 1u);
       Sync::sync();
       // at_least[d] = keys whose digit is >= d; the digit wanted is the one with at_least - count < left <= at_least
       uint32_t c[8];
@@ -193,8 +204,8 @@ struct Team {
       mx = fmaxf(mx, x[j]);
     }
     const int keep = top_k > 0 && top_k < vocab ? top_k : vocab;
-    const uint32_t threshold = keep < vocab ? kth_largest_key(key, vocab, (uint32_t)keep, tid, sh) : 0u;
     const float m = team_max(mx, tid, sh);
+    const uint32_t threshold = keep < vocab ? kth_largest_key(key, vocab, (uint32_t)keep, order_key(m) >> 24, tid, sh) : 0u;
     float p[PER];
 #pragma unroll
     for (int j = 0; j < PER; ++j) p[j] = tid * PER + j < vocab && key[j] >= threshold ? __expf(x[j] - m) : 0.f;
