@@ -13,7 +13,8 @@ HERE = Path(__file__).resolve().parent
 CSRC = HERE / "csrc"
 LIB = HERE / "libomni_b200.so"
 SOURCES = ["gemm.cu", "stack_kernels.cu", "talker_kernels.cu", "tick_kernel.cu", "predictor_kernel.cu", "talker_model.cu", "ops_abi.cu",
-           "duplex_kernels.cu", "duplex_model.cu", "higgs_kernels.cu", "higgs_model.cu"]
+           "duplex_kernels.cu", "duplex_model.cu", "higgs_kernels.cu", "higgs_model.cu", "codec_gemm.cu", "codec_kernels.cu",
+           "codec_model.cu"]
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 
 

@@ -1,0 +1,242 @@
+// The codec decoder's causal conv as an implicit GEMM on tcgen05 (declared in codec.h).
+//
+// The reference materialises every conv's dilated im2col matrix [rows, taps * C] and hands it to a library GEMM
+// (crates/omni-qwen3-tts/src/codec.rs:60-93, kernels/codec.cu:291-318). Here the im2col matrix never exists: the
+// activation is kept once, padded with its history, as [stream][H + T][C], and the K loop walks (tap, channel block);
+// for tap j the activation tile of 128 output rows is the same rank-3/4 TMA box shifted down by j * dil rows. The rows
+// of a tile are SB streams x TB consecutive frame rows (TB * SB = 128), so a tile never reads across a stream's padding.
+//
+//   warp 0 / lane 0: TMA producer, a ring of {activation tile 128 x 64 x kbs, weight tile tn x 64 x kbs};
+//   warp 1 / lane 0: MMA issuer (M = 128 rows, N = tn output channels, accumulator in TMEM);
+//   all four warps:  epilogue, a thread owns one output row (its TMEM lane), 16 channels at a time.
+//
+// Channel counts that are not multiples of 64 (96 in the last decoder block) take the "ragged" loads: the activation
+// box past channel C is zero-filled by TMA, so whatever weight columns of the next tap the weight box then covers
+// multiply zeros.
+#include <algorithm>
+
+#include "codec.h"
+#include "gemm.h"
+#include "sm100.cuh"
+
+namespace omni {
+
+namespace {
+
+constexpr int kConvK = 64;                    // channels per k-block: one 128-byte swizzle row
+constexpr int kConvRows = 128;                // output rows per CTA
+constexpr int kConvRing = 192 * 1024;
+constexpr int kConvMaxStages = 8;
+constexpr size_t kConvSmem = (size_t)kConvRing + 1024 + 256;
+
+struct ConvArgs {
+  bf16* y;
+  const bf16* bias;
+  const float* alpha;
+  const float* inv_b;
+  uint32_t* err;
+  int N, C, taps, dil, T, seqs, TB, SB, tn, kbs, cpb, ragged, stages, kind, t_tiles;
+  uint32_t tmem_cols;
+};
+
+__global__ void __launch_bounds__(128, 1)
+    conv_gemm_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap wmap,
+                     const ConvArgs a) {
+  using namespace sm100;
+  if (*reinterpret_cast<volatile uint32_t*>(a.err) != 0) return;
+  extern __shared__ unsigned char conv_smem_raw[];
+  const uint32_t raw = smem_addr(conv_smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  unsigned char* base_ptr = conv_smem_raw + (base - raw);
+  const uint32_t x_slice = kConvRows * kConvK * 2, x_bytes = (uint32_t)a.kbs * x_slice;
+  const uint32_t w_slice = (uint32_t)a.tn * kConvK * 2, stage_bytes = x_bytes + (uint32_t)a.kbs * w_slice;
+  const uint32_t bars = base + kConvRing;
+  auto full_bar = [&](int s) { return bars + 8u * s; };
+  auto empty_bar = [&](int s) { return bars + 8u * (kConvMaxStages + s); };
+  const uint32_t acc_bar = bars + 8u * (2 * kConvMaxStages);
+  const uint32_t tmem_slot = acc_bar + 8u;
+  volatile uint32_t* tmem_slot_ptr =
+      reinterpret_cast<volatile uint32_t*>(base_ptr + kConvRing + 8 * (2 * kConvMaxStages) + 8);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = blockIdx.x * a.tn;
+  const int t0 = ((int)blockIdx.y % a.t_tiles) * a.TB, s0 = ((int)blockIdx.y / a.t_tiles) * a.SB;
+  const int steps = a.taps * a.cpb / a.kbs;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < a.stages; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    mbar_init(acc_bar, 1);
+    mbar_init_fence();
+    prefetch_tensormap(&xmap);
+    prefetch_tensormap(&wmap);
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, a.tmem_cols);
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot_ptr;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int i = 0; i < steps; ++i) {
+        if (!mbar_wait(empty_bar(stage), phase ^ 1u, a.err)) break;
+        const int kb = i * a.kbs, tap = kb / a.cpb, cb = kb % a.cpb;
+        const uint32_t a_dst = base + stage * stage_bytes, b_dst = a_dst + x_bytes;
+        mbar_expect_tx(full_bar(stage), stage_bytes);
+        if (a.ragged) {
+          tma_load_3d(a_dst, &xmap, full_bar(stage), cb * kConvK, t0 + tap * a.dil, s0, kEvictLast);
+          tma_load_2d(b_dst, &wmap, full_bar(stage), tap * a.C + cb * kConvK, n0, kEvictLast);
+        } else {
+          tma_load_4d(a_dst, &xmap, full_bar(stage), 0, t0 + tap * a.dil, s0, cb, kEvictLast);
+          tma_load_3d(b_dst, &wmap, full_bar(stage), 0, n0, tap * a.cpb + cb, kEvictLast);
+        }
+        if (++stage == a.stages) stage = 0, phase ^= 1u;
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc = idesc_bf16_f32(kConvRows, a.tn);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool alive = true;
+      for (int i = 0; i < steps && alive; ++i) {
+        alive = mbar_wait(full_bar(stage), phase, a.err);
+        if (!alive) break;
+        tc_fence_after_sync();
+        const uint32_t a_src = base + stage * stage_bytes, b_src = a_src + x_bytes;
+        for (int j = 0; j < a.kbs; ++j) {
+          const uint64_t adesc = kmajor_sw128_desc(a_src + (uint32_t)j * x_slice);
+          const uint64_t bdesc = kmajor_sw128_desc(b_src + (uint32_t)j * w_slice);
+#pragma unroll
+          for (int k = 0; k < kConvK / 16; ++k)
+            mma_bf16(tmem_base, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2), idesc,
+                     (i > 0 || j > 0 || k > 0) ? 1u : 0u);
+        }
+        mma_commit(empty_bar(stage));
+        if (++stage == a.stages) stage = 0, phase ^= 1u;
+      }
+      if (alive) mma_commit(acc_bar);
+    }
+    __syncwarp();
+  }
+
+  const bool ok = mbar_wait(acc_bar, 0, a.err);
+  tc_fence_after_sync();
+  const int m = warp * 32 + lane;  // output row of the tile = TMEM lane
+  const int s = s0 + m / a.TB, t = t0 + m % a.TB;
+  const bool live = ok && s < a.seqs;
+  bf16* row = a.y + ((int64_t)s * a.T + t) * a.N;
+  const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
+  if (ok) {
+#pragma unroll 1
+    for (int c0 = 0; c0 < a.tn; c0 += 16) {
+      float v[16];
+      tmem_ld16(lane_addr + c0, v);  // warp-wide: every lane takes part whether or not its row is live
+      const int n = n0 + c0;
+      if (!live || n >= a.N) continue;
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int nn = n + 8 * h;
+        if (nn + 8 > a.N) break;
+        float* o = v + 8 * h;
+        if (a.kind == kConvAccumulate) {
+          float old[8];
+          ld8(row + nn, old);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o[j] += old[j];
+        } else if (a.kind == kConvBiasSnake) {
+          float b[8];
+          ld8(a.bias + nn, b);
+          const float4 a0 = *reinterpret_cast<const float4*>(a.alpha + nn), a1 = *reinterpret_cast<const float4*>(a.alpha + nn + 4);
+          const float4 i0 = *reinterpret_cast<const float4*>(a.inv_b + nn), i1 = *reinterpret_cast<const float4*>(a.inv_b + nn + 4);
+          const float al[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+          const float ib[8] = {i0.x, i0.y, i0.z, i0.w, i1.x, i1.y, i1.z, i1.w};
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o[j] = snake_beta(bf16_round(o[j]) + b[j], al[j], ib[j]);
+        }
+        st8(row + nn, o);
+      }
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, a.tmem_cols);
+}
+
+}  // namespace
+
+void conv_configure() {
+  cudaFuncSetAttribute(conv_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kConvSmem);
+}
+
+int conv_plan(ConvGemmPlan* plan, const bf16* w, int N, int C, int taps, int dil, const bf16* x, int T, int seqs, bf16* y,
+              int kind, const bf16* bias, const float* alpha, const float* inv_b, int sm_count) {
+  if (N < 8 || N % 8 || C < 8 || C % 8 || taps < 1 || T < 1 || seqs < 1) return -2;
+  if ((reinterpret_cast<uintptr_t>(w) & 15) || (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(y) & 15))
+    return -3;
+  ConvGemmPlan& p = *plan;
+  p.N = N, p.C = C, p.taps = taps, p.dil = dil, p.T = T, p.seqs = seqs, p.y = y;
+  p.kind = kind, p.bias = bias, p.alpha = alpha, p.inv_b = inv_b;
+  p.TB = 1;
+  while (p.TB < kConvRows && T % (p.TB * 2) == 0) p.TB *= 2;
+  p.SB = kConvRows / p.TB;
+  p.row_tiles = (T / p.TB) * ((seqs + p.SB - 1) / p.SB);
+  p.cpb = (C + kConvK - 1) / kConvK;
+  p.ragged = C % kConvK != 0;
+  // output channels per CTA: as wide as the accumulator allows when the rows alone fill the machine, else narrow
+  // enough that every SM gets a tile
+  const int min_tiles = (N + 255) / 256;
+  const int want = std::max(min_tiles, std::min((N + 15) / 16, sm_count / std::max(1, p.row_tiles)));
+  p.tn = std::min(256, ((N + want - 1) / want + 15) / 16 * 16);
+  p.n_tiles = (N + p.tn - 1) / p.tn;
+  // k-blocks per TMA copy: a tiled copy occupies the SM's TMA unit for about 0.19 us whatever its size, so narrow
+  // tiles move several channel blocks of a tap at once; the ring keeps at least three stages
+  p.kbs = 1;
+  if (!p.ragged)
+    for (int kbs : {4, 2})
+      if (p.cpb % kbs == 0 && kConvRing / (kbs * (kConvRows * kConvK * 2 + p.tn * kConvK * 2)) >= 3) {
+        p.kbs = kbs;
+        break;
+      }
+  p.stages = std::min(kConvMaxStages, kConvRing / (p.kbs * (kConvRows * kConvK * 2 + p.tn * kConvK * 2)));
+  if (p.stages < 2) return -2;
+  const int P = (taps - 1) * dil + T, Ktot = taps * C;
+  if (p.ragged) {
+    const uint64_t xd[3] = {(uint64_t)C, (uint64_t)P, (uint64_t)seqs};
+    const uint64_t xs[2] = {(uint64_t)C * 2, (uint64_t)P * C * 2};
+    const uint32_t xb[3] = {kConvK, (uint32_t)p.TB, (uint32_t)p.SB};
+    if (tc_encode_bf16(&p.xmap, x, 3, xd, xs, xb) != 0) return -4;
+    const uint64_t wd[2] = {(uint64_t)Ktot, (uint64_t)N};
+    const uint64_t ws[1] = {(uint64_t)Ktot * 2};
+    const uint32_t wb[2] = {kConvK, (uint32_t)p.tn};
+    if (tc_encode_bf16(&p.wmap, w, 2, wd, ws, wb) != 0) return -4;
+  } else {
+    const uint64_t xd[4] = {kConvK, (uint64_t)P, (uint64_t)seqs, (uint64_t)p.cpb};
+    const uint64_t xs[3] = {(uint64_t)C * 2, (uint64_t)P * C * 2, kConvK * 2};
+    const uint32_t xb[4] = {kConvK, (uint32_t)p.TB, (uint32_t)p.SB, (uint32_t)p.kbs};
+    if (tc_encode_bf16(&p.xmap, x, 4, xd, xs, xb) != 0) return -4;
+    const uint64_t wd[3] = {kConvK, (uint64_t)N, (uint64_t)(Ktot / kConvK)};
+    const uint64_t ws[2] = {(uint64_t)Ktot * 2, kConvK * 2};
+    const uint32_t wb[3] = {kConvK, (uint32_t)p.tn, (uint32_t)p.kbs};
+    if (tc_encode_bf16(&p.wmap, w, 3, wd, ws, wb) != 0) return -4;
+  }
+  return 0;
+}
+
+cudaError_t conv_launch(const ConvGemmPlan& p, uint32_t* err, cudaStream_t stream) {
+  ConvArgs a;
+  a.y = p.y, a.bias = p.bias, a.alpha = p.alpha, a.inv_b = p.inv_b, a.err = err;
+  a.N = p.N, a.C = p.C, a.taps = p.taps, a.dil = p.dil, a.T = p.T, a.seqs = p.seqs, a.TB = p.TB, a.SB = p.SB;
+  a.tn = p.tn, a.kbs = p.kbs, a.cpb = p.cpb, a.ragged = p.ragged, a.stages = p.stages, a.kind = p.kind;
+  a.t_tiles = p.T / p.TB;
+  a.tmem_cols = p.tn <= 32 ? 32u : p.tn <= 64 ? 64u : p.tn <= 128 ? 128u : 256u;
+  conv_gemm_kernel<<<dim3(p.n_tiles, p.row_tiles), 128, kConvSmem, stream>>>(p.xmap, p.wmap, a);
+  return cudaGetLastError();
+}
+
+}  // namespace omni

@@ -518,6 +518,21 @@ static int encode_kmajor(CUtensorMap* map, const bf16* base, int rows, int K, in
   return r == CUDA_SUCCESS ? 0 : -1;
 }
 
+// A bf16 tensor of any rank up to 5 with the 128-byte swizzle (box[0] must be 64 elements); strides in bytes for the
+// dimensions above the innermost. For callers that tile something other than a dense [rows, K] matrix.
+int tc_encode_bf16(CUtensorMap* map, const bf16* base, int rank, const uint64_t* dims, const uint64_t* strides,
+                   const uint32_t* box) {
+  if (tc_init() != 0) return -1;
+  cuuint64_t d[5], s[4];
+  cuuint32_t b[5], elem[5] = {1, 1, 1, 1, 1};
+  for (int i = 0; i < rank; ++i) d[i] = dims[i], b[i] = box[i];
+  for (int i = 0; i + 1 < rank; ++i) s[i] = strides[i];
+  const CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, (cuuint32_t)rank, const_cast<bf16*>(base), d, s, b,
+                              elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -1;
+}
+
 // The same matrix as a rank-3 map {element in a k-block, row, k-block} whose box holds `kbs` k-blocks of `box_rows` rows.
 static int encode_kmajor3(CUtensorMap* map, const bf16* base, int rows, int K, int box_rows, int kbs) {
   const cuuint64_t dims[3] = {(cuuint64_t)kTileK, (cuuint64_t)rows, (cuuint64_t)(K / kTileK)};

@@ -52,6 +52,9 @@ struct TcGemmPlan {
 void tc_configure();
 // Resolves the driver entry point used to encode tensor maps. 0 on success.
 int tc_init();
+// Encodes a bf16 tensor map of rank <= 5 with the 128-byte swizzle; strides (bytes) for dimensions 1..rank-1. 0 on success.
+int tc_encode_bf16(CUtensorMap* map, const bf16* base, int rank, const uint64_t* dims, const uint64_t* strides,
+                   const uint32_t* box);
 // Whether a GEMM of this shape can run on the tensor-core path.
 bool tc_supports(int N, int K, int rows);
 // Encodes the tensor maps and picks the tiling. x is [rows, K] dense, w is [N, K] dense.

@@ -1,5 +1,5 @@
-"""ctypes binding of ``libomni_b200.so`` (declarations of include/omni_b200.h, omni_b200_ops.h, omni_b200_duplex.h and
-omni_b200_higgs.h).
+"""ctypes binding of ``libomni_b200.so`` (declarations of include/omni_b200.h, omni_b200_ops.h, omni_b200_duplex.h,
+omni_b200_higgs.h and omni_b200_codec.h).
 
 Loading fails loudly when the library is missing: there is no fallback path.
 """
@@ -56,6 +56,15 @@ class DuplexCfg(C.Structure):
                 ("text_top_k", C.c_int32), ("audio_temperature", C.c_float), ("audio_top_k", C.c_int32),
                 ("max_sessions", C.c_int32), ("max_prefill", C.c_int32), ("voice_rows", C.c_int32),
                 ("use_graphs", C.c_int32), ("tp_rank", C.c_int32), ("tp_size", C.c_int32)]
+
+
+class CodecCfg(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in ("codebook_size", "codebook_dim", "latent_dim", "decoder_dim", "hidden_size",
+                                         "intermediate_size", "num_hidden_layers", "num_attention_heads", "head_dim")] + \
+               [("rms_norm_eps", C.c_float), ("rope_theta", C.c_float), ("sliding_window", C.c_int32),
+                ("num_quantizers", C.c_int32), ("n_upsampling_ratios", C.c_int32), ("upsampling_ratios", C.c_int32 * 4),
+                ("n_upsample_rates", C.c_int32), ("upsample_rates", C.c_int32 * 8), ("max_batch", C.c_int32),
+                ("max_streams", C.c_int32), ("use_graphs", C.c_int32)]
 
 
 class DuplexStep(C.Structure):
@@ -142,6 +151,16 @@ SYMBOLS = {
     "omni_higgs_warmup": (I32, [VP]),
     "omni_higgs_read_logits": (I32, [VP, I32, VP, C.c_size_t]),
     "omni_higgs_stats": (I32, [VP, P(C.c_float), P(I32)]),
+    "omni_codec_create": (I32, [P(CodecCfg), P(Tensor), I32, I32, P(VP)]),
+    "omni_codec_destroy": (None, [VP]),
+    "omni_codec_last_error": (C.c_char_p, [VP]),
+    "omni_codec_open": (I32, [VP, P(VP)]),
+    "omni_codec_close": (I32, [VP, VP]),
+    "omni_codec_stream_frames": (I32, [VP]),
+    "omni_codec_samples_per_frame": (I32, [VP]),
+    "omni_codec_warmup": (I32, [VP]),
+    "omni_codec_decode": (I32, [VP, I32, P(VP), P(I32), P(C.c_float)]),
+    "omni_codec_stats": (I32, [VP, P(C.c_float), P(I32)]),
     "omni_duplex_create": (I32, [P(DuplexCfg), P(Tensor), I32, I32, P(VP)]),
     "omni_duplex_destroy": (None, [VP]),
     "omni_duplex_last_error": (C.c_char_p, [VP]),
