@@ -25,7 +25,7 @@ struct ConvGemmPlan {
   CUtensorMap xmap, wmap;
   int N = 0, C = 0, taps = 1, dil = 1, T = 1, seqs = 1;
   int TB = 1, SB = 128, tn = 16, kbs = 1, cpb = 1, ragged = 0, stages = 2;
-  int n_tiles = 1, row_tiles = 1;
+  int n_tiles = 1, row_tiles = 1, ctas = 1;
   bf16* y = nullptr;
   int kind = kConvStore;
   const bf16* bias = nullptr;

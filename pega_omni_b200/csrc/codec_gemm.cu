@@ -23,10 +23,11 @@ namespace omni {
 
 namespace {
 
-constexpr int kConvK = 64;                    // channels per k-block: one 128-byte swizzle row
-constexpr int kConvRows = 128;                // output rows per CTA
-constexpr int kConvRing = 192 * 1024;
+constexpr int kConvK = 64;        // channels per k-block: one 128-byte swizzle row
+constexpr int kConvRows = 128;    // output rows per tile
+constexpr int kConvRing = 200 * 1024;
 constexpr int kConvMaxStages = 8;
+constexpr int kConvThreads = 192; // warp 0 producer, warp 1 MMA issuer, warps 2..5 epilogue
 constexpr size_t kConvSmem = (size_t)kConvRing + 1024 + 256;
 
 struct ConvArgs {
@@ -35,11 +36,14 @@ struct ConvArgs {
   const float* alpha;
   const float* inv_b;
   uint32_t* err;
-  int N, C, taps, dil, T, seqs, TB, SB, tn, kbs, cpb, ragged, stages, kind, t_tiles;
-  uint32_t tmem_cols;
+  int N, C, taps, dil, T, seqs, TB, SB, tn, kbs, cpb, ragged, stages, kind, t_tiles, n_tiles, tiles;
+  uint32_t acc_cols;  // TMEM columns per accumulator (a power of two >= tn); two accumulators are allocated
 };
 
-__global__ void __launch_bounds__(128, 1)
+// Persistent: a CTA walks tiles blockIdx.x, blockIdx.x + gridDim.x, ... (output-channel tile fastest, so CTAs that run
+// together share activation rows in L2). The ring never drains between tiles: the producer runs ahead into the next
+// tile's loads while the epilogue warps drain the accumulator of the one before, which is why there are two.
+__global__ void __launch_bounds__(kConvThreads, 1)
     conv_gemm_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap wmap,
                      const ConvArgs a) {
   using namespace sm100;
@@ -53,13 +57,12 @@ __global__ void __launch_bounds__(128, 1)
   const uint32_t bars = base + kConvRing;
   auto full_bar = [&](int s) { return bars + 8u * s; };
   auto empty_bar = [&](int s) { return bars + 8u * (kConvMaxStages + s); };
-  const uint32_t acc_bar = bars + 8u * (2 * kConvMaxStages);
-  const uint32_t tmem_slot = acc_bar + 8u;
+  auto acc_full = [&](int b) { return bars + 8u * (2 * kConvMaxStages + b); };
+  auto acc_empty = [&](int b) { return bars + 8u * (2 * kConvMaxStages + 2 + b); };
+  const uint32_t tmem_slot = bars + 8u * (2 * kConvMaxStages + 4);
   volatile uint32_t* tmem_slot_ptr =
-      reinterpret_cast<volatile uint32_t*>(base_ptr + kConvRing + 8 * (2 * kConvMaxStages) + 8);
+      reinterpret_cast<volatile uint32_t*>(base_ptr + kConvRing + 8 * (2 * kConvMaxStages + 4));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n0 = blockIdx.x * a.tn;
-  const int t0 = ((int)blockIdx.y % a.t_tiles) * a.TB, s0 = ((int)blockIdx.y / a.t_tiles) * a.SB;
   const int steps = a.taps * a.cpb / a.kbs;
 
   if (threadIdx.x == 0) {
@@ -67,12 +70,15 @@ __global__ void __launch_bounds__(128, 1)
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
     }
-    mbar_init(acc_bar, 1);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(acc_full(b), 1);
+      mbar_init(acc_empty(b), 4);  // one arrival per epilogue warp
+    }
     mbar_init_fence();
     prefetch_tensormap(&xmap);
     prefetch_tensormap(&wmap);
   }
-  if (warp == 1) tmem_alloc(tmem_slot, a.tmem_cols);
+  if (warp == 1) tmem_alloc(tmem_slot, 2 * a.acc_cols);
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
@@ -82,90 +88,140 @@ __global__ void __launch_bounds__(128, 1)
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
-      for (int i = 0; i < steps; ++i) {
-        if (!mbar_wait(empty_bar(stage), phase ^ 1u, a.err)) break;
-        const int kb = i * a.kbs, tap = kb / a.cpb, cb = kb % a.cpb;
-        const uint32_t a_dst = base + stage * stage_bytes, b_dst = a_dst + x_bytes;
-        mbar_expect_tx(full_bar(stage), stage_bytes);
-        if (a.ragged) {
-          tma_load_3d(a_dst, &xmap, full_bar(stage), cb * kConvK, t0 + tap * a.dil, s0, kEvictLast);
-          tma_load_2d(b_dst, &wmap, full_bar(stage), tap * a.C + cb * kConvK, n0, kEvictLast);
-        } else {
-          tma_load_4d(a_dst, &xmap, full_bar(stage), 0, t0 + tap * a.dil, s0, cb, kEvictLast);
-          tma_load_3d(b_dst, &wmap, full_bar(stage), 0, n0, tap * a.cpb + cb, kEvictLast);
+      bool alive = true;
+      for (int tile = blockIdx.x; tile < a.tiles && alive; tile += gridDim.x) {
+        const int n0 = (tile % a.n_tiles) * a.tn, rt = tile / a.n_tiles;
+        const int t0 = (rt % a.t_tiles) * a.TB, s0 = (rt / a.t_tiles) * a.SB;
+        for (int i = 0; i < steps; ++i) {
+          alive = mbar_wait(empty_bar(stage), phase ^ 1u, a.err);
+          if (!alive) break;
+          const int kb = i * a.kbs, tap = kb / a.cpb, cb = kb % a.cpb;
+          const uint32_t a_dst = base + stage * stage_bytes, b_dst = a_dst + x_bytes;
+          mbar_expect_tx(full_bar(stage), stage_bytes);
+          if (a.ragged) {
+            tma_load_3d(a_dst, &xmap, full_bar(stage), cb * kConvK, t0 + tap * a.dil, s0, kEvictNormal);
+            tma_load_2d(b_dst, &wmap, full_bar(stage), tap * a.C + cb * kConvK, n0, kEvictLast);
+          } else {
+            tma_load_4d(a_dst, &xmap, full_bar(stage), 0, t0 + tap * a.dil, s0, cb, kEvictNormal);
+            tma_load_3d(b_dst, &wmap, full_bar(stage), 0, n0, tap * a.cpb + cb, kEvictLast);
+          }
+          if (++stage == a.stages) stage = 0, phase ^= 1u;
         }
-        if (++stage == a.stages) stage = 0, phase ^= 1u;
       }
     }
     __syncwarp();
   } else if (warp == 1) {
     if (lane == 0) {
       const uint32_t idesc = idesc_bf16_f32(kConvRows, a.tn);
-      int stage = 0;
+      int stage = 0, use = 0;
       uint32_t phase = 0;
       bool alive = true;
-      for (int i = 0; i < steps && alive; ++i) {
-        alive = mbar_wait(full_bar(stage), phase, a.err);
+      for (int tile = blockIdx.x; tile < a.tiles && alive; tile += gridDim.x, ++use) {
+        const int buf = use & 1;
+        // the epilogue of this accumulator's previous tile must have read it out (a fresh barrier passes at once)
+        alive = mbar_wait(acc_empty(buf), ((uint32_t)(use >> 1) & 1u) ^ 1u, a.err);
         if (!alive) break;
         tc_fence_after_sync();
-        const uint32_t a_src = base + stage * stage_bytes, b_src = a_src + x_bytes;
-        for (int j = 0; j < a.kbs; ++j) {
-          const uint64_t adesc = kmajor_sw128_desc(a_src + (uint32_t)j * x_slice);
-          const uint64_t bdesc = kmajor_sw128_desc(b_src + (uint32_t)j * w_slice);
+        const uint32_t acc = tmem_base + (uint32_t)buf * a.acc_cols;
+        for (int i = 0; i < steps; ++i) {
+          alive = mbar_wait(full_bar(stage), phase, a.err);
+          if (!alive) break;
+          tc_fence_after_sync();
+          const uint32_t a_src = base + stage * stage_bytes, b_src = a_src + x_bytes;
+          for (int j = 0; j < a.kbs; ++j) {
+            const uint64_t adesc = kmajor_sw128_desc(a_src + (uint32_t)j * x_slice);
+            const uint64_t bdesc = kmajor_sw128_desc(b_src + (uint32_t)j * w_slice);
 #pragma unroll
-          for (int k = 0; k < kConvK / 16; ++k)
-            mma_bf16(tmem_base, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2), idesc,
-                     (i > 0 || j > 0 || k > 0) ? 1u : 0u);
+            for (int k = 0; k < kConvK / 16; ++k)
+              mma_bf16(acc, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2), idesc,
+                       (i > 0 || j > 0 || k > 0) ? 1u : 0u);
+          }
+          mma_commit(empty_bar(stage));
+          if (++stage == a.stages) stage = 0, phase ^= 1u;
         }
-        mma_commit(empty_bar(stage));
-        if (++stage == a.stages) stage = 0, phase ^= 1u;
+        if (alive) mma_commit(acc_full(buf));
       }
-      if (alive) mma_commit(acc_bar);
     }
     __syncwarp();
-  }
-
-  const bool ok = mbar_wait(acc_bar, 0, a.err);
-  tc_fence_after_sync();
-  const int m = warp * 32 + lane;  // output row of the tile = TMEM lane
-  const int s = s0 + m / a.TB, t = t0 + m % a.TB;
-  const bool live = ok && s < a.seqs;
-  bf16* row = a.y + ((int64_t)s * a.T + t) * a.N;
-  const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
-  if (ok) {
-#pragma unroll 1
-    for (int c0 = 0; c0 < a.tn; c0 += 16) {
-      float v[16];
-      tmem_ld16(lane_addr + c0, v);  // warp-wide: every lane takes part whether or not its row is live
-      const int n = n0 + c0;
-      if (!live || n >= a.N) continue;
+  } else {
+    // Epilogue: a thread owns one output row (its TMEM lane; a warp reaches the 32 lanes of quadrant warp % 4) and
+    // walks it 32 channels at a time. What an accumulating GEMM adds to does not depend on the accumulator, so the
+    // row's old values are requested one step ahead: the first step's before the wait for the accumulator.
+    const int quad = warp & 3, m = quad * 32 + lane;
+    int use = 0;
+    bool alive = true;
+    for (int tile = blockIdx.x; tile < a.tiles && alive; tile += gridDim.x, ++use) {
+      const int buf = use & 1;
+      const int n0 = (tile % a.n_tiles) * a.tn, rt = tile / a.n_tiles;
+      const int t0 = (rt % a.t_tiles) * a.TB, s0 = (rt / a.t_tiles) * a.SB;
+      const int s = s0 + m / a.TB, t = t0 + m % a.TB;
+      const bool in_range = s < a.seqs;
+      bf16* row = a.y + ((int64_t)s * a.T + t) * a.N;
+      const uint32_t lane_addr = tmem_base + (uint32_t)buf * a.acc_cols + ((uint32_t)(quad * 32) << 16);
+      uint4 ahead[4] = {};
+      auto fetch_old = [&](int c0) {
 #pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        const int nn = n + 8 * h;
-        if (nn + 8 > a.N) break;
-        float* o = v + 8 * h;
-        if (a.kind == kConvAccumulate) {
-          float old[8];
-          ld8(row + nn, old);
-#pragma unroll
-          for (int j = 0; j < 8; ++j) o[j] += old[j];
-        } else if (a.kind == kConvBiasSnake) {
-          float b[8];
-          ld8(a.bias + nn, b);
-          const float4 a0 = *reinterpret_cast<const float4*>(a.alpha + nn), a1 = *reinterpret_cast<const float4*>(a.alpha + nn + 4);
-          const float4 i0 = *reinterpret_cast<const float4*>(a.inv_b + nn), i1 = *reinterpret_cast<const float4*>(a.inv_b + nn + 4);
-          const float al[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
-          const float ib[8] = {i0.x, i0.y, i0.z, i0.w, i1.x, i1.y, i1.z, i1.w};
-#pragma unroll
-          for (int j = 0; j < 8; ++j) o[j] = snake_beta(bf16_round(o[j]) + b[j], al[j], ib[j]);
+        for (int h = 0; h < 4; ++h) {
+          const int nn = n0 + c0 + 8 * h;
+          if (in_range && c0 + 8 * h < a.tn && nn + 8 <= a.N) ahead[h] = *reinterpret_cast<const uint4*>(row + nn);
         }
-        st8(row + nn, o);
+      };
+      if (a.kind == kConvAccumulate) fetch_old(0);
+      alive = mbar_wait(acc_full(buf), (uint32_t)(use >> 1) & 1u, a.err);
+      if (!alive) break;
+      tc_fence_after_sync();
+#pragma unroll 1
+      for (int c0 = 0; c0 < a.tn; c0 += 32) {
+        uint32_t r0[16], r1[16];
+        const bool second = c0 + 16 < a.tn;  // tn is a multiple of 16: the last step may hold one half only
+        tmem_ld16_issue(lane_addr + c0, r0);  // warp-wide: every lane takes part whether or not its row is live
+        if (second) {
+          tmem_ld16_issue(lane_addr + c0 + 16, r1);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) r1[j] = 0u;
+        }
+        uint4 old[4];
+#pragma unroll
+        for (int h = 0; h < 4; ++h) old[h] = ahead[h];
+        if (a.kind == kConvAccumulate && c0 + 32 < a.tn) fetch_old(c0 + 32);
+        tmem_ld_fence(r0, r1);
+        if (c0 + 32 >= a.tn) {  // the accumulator is in registers: the MMA issuer may start the tile after next
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(acc_empty(buf));
+        }
+        if (!in_range) continue;
+#pragma unroll
+        for (int h = 0; h < 4; ++h) {
+          const int nn = n0 + c0 + 8 * h;
+          if (c0 + 8 * h >= a.tn || nn + 8 > a.N) break;
+          float o[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o[j] = __uint_as_float(h < 2 ? r0[8 * h + j] : r1[8 * (h - 2) + j]);
+          if (a.kind == kConvAccumulate) {
+            float prev[8];
+            unpack8v(old[h], prev);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) o[j] += prev[j];
+          } else if (a.kind == kConvBiasSnake) {
+            float b[8];
+            ld8v(a.bias + nn, b);
+            const float4 a0 = *reinterpret_cast<const float4*>(a.alpha + nn), a1 = *reinterpret_cast<const float4*>(a.alpha + nn + 4);
+            const float4 i0 = *reinterpret_cast<const float4*>(a.inv_b + nn), i1 = *reinterpret_cast<const float4*>(a.inv_b + nn + 4);
+            const float al[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+            const float ib[8] = {i0.x, i0.y, i0.z, i0.w, i1.x, i1.y, i1.z, i1.w};
+#pragma unroll
+            for (int j = 0; j < 8; ++j) o[j] = snake_beta(bf16_round(o[j]) + b[j], al[j], ib[j]);
+          }
+          st8v(row + nn, o);
+        }
       }
     }
   }
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == 1) tmem_dealloc(tmem_base, a.tmem_cols);
+  if (warp == 1) tmem_dealloc(tmem_base, 2 * a.acc_cols);
 }
 
 }  // namespace
@@ -198,12 +254,13 @@ int conv_plan(ConvGemmPlan* plan, const bf16* w, int N, int C, int taps, int dil
   // tiles move several channel blocks of a tap at once; the ring keeps at least three stages
   p.kbs = 1;
   if (!p.ragged)
-    for (int kbs : {4, 2})
+    for (int kbs : {4, 3, 2})
       if (p.cpb % kbs == 0 && kConvRing / (kbs * (kConvRows * kConvK * 2 + p.tn * kConvK * 2)) >= 3) {
         p.kbs = kbs;
         break;
       }
   p.stages = std::min(kConvMaxStages, kConvRing / (p.kbs * (kConvRows * kConvK * 2 + p.tn * kConvK * 2)));
+  p.ctas = std::min(p.n_tiles * p.row_tiles, sm_count);
   if (p.stages < 2) return -2;
   const int P = (taps - 1) * dil + T, Ktot = taps * C;
   if (p.ragged) {
@@ -233,9 +290,9 @@ cudaError_t conv_launch(const ConvGemmPlan& p, uint32_t* err, cudaStream_t strea
   a.y = p.y, a.bias = p.bias, a.alpha = p.alpha, a.inv_b = p.inv_b, a.err = err;
   a.N = p.N, a.C = p.C, a.taps = p.taps, a.dil = p.dil, a.T = p.T, a.seqs = p.seqs, a.TB = p.TB, a.SB = p.SB;
   a.tn = p.tn, a.kbs = p.kbs, a.cpb = p.cpb, a.ragged = p.ragged, a.stages = p.stages, a.kind = p.kind;
-  a.t_tiles = p.T / p.TB;
-  a.tmem_cols = p.tn <= 32 ? 32u : p.tn <= 64 ? 64u : p.tn <= 128 ? 128u : 256u;
-  conv_gemm_kernel<<<dim3(p.n_tiles, p.row_tiles), 128, kConvSmem, stream>>>(p.xmap, p.wmap, a);
+  a.t_tiles = p.T / p.TB, a.n_tiles = p.n_tiles, a.tiles = p.n_tiles * p.row_tiles;
+  a.acc_cols = p.tn <= 32 ? 32u : p.tn <= 64 ? 64u : p.tn <= 128 ? 128u : 256u;
+  conv_gemm_kernel<<<p.ctas, kConvThreads, kConvSmem, stream>>>(p.xmap, p.wmap, a);
   return cudaGetLastError();
 }
 

@@ -35,16 +35,16 @@ __global__ void codec_rvq_kernel(const int32_t* __restrict__ codes, const bf16* 
   for (int c = threadIdx.x * 8; c < half; c += blockDim.x * 8) {
     const int32_t* code = codes + s * 16;
     const int64_t first = code[0] < book_rows ? code[0] : 0;  // a code past the book (end of speech) reads as 0
-    *reinterpret_cast<Pack8*>(out + (int64_t)s * 2 * half + c) = *reinterpret_cast<const Pack8*>(books + first * half + c);
+    *reinterpret_cast<uint4*>(out + (int64_t)s * 2 * half + c) = *reinterpret_cast<const uint4*>(books + first * half + c);
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
 #pragma unroll
     for (int g = 1; g < 16; ++g) {
       float v[8];
-      ld8(books + ((int64_t)g * book_rows + code[g]) * half + c, v);
+      ld8v(books + ((int64_t)g * book_rows + code[g]) * half + c, v);
 #pragma unroll
       for (int k = 0; k < 8; ++k) acc[k] += v[k];
     }
-    st8(out + (int64_t)s * 2 * half + half + c, acc);
+    st8v(out + (int64_t)s * 2 * half + half + c, acc);
   }
 }
 
@@ -62,14 +62,14 @@ __global__ void codec_add_norm_kernel(const bf16* add, int64_t add_stride, bf16*
     const int c = (k * 32 + lane) * 8;
     if (c < dim) {
       float x[8];
-      ld8(a + c, x);
-      ld8(rr + c, v[k]);
+      ld8v(a + c, x);
+      ld8v(rr + c, v[k]);
 #pragma unroll
       for (int e = 0; e < 8; ++e) {
         v[k][e] += x[e];
         ss += v[k][e] * v[k][e];
       }
-      st8(rr + c, v[k]);
+      st8v(rr + c, v[k]);
     }
   }
   const float rs = rsqrtf(warp_add(ss) / dim + eps);
@@ -78,10 +78,10 @@ __global__ void codec_add_norm_kernel(const bf16* add, int64_t add_stride, bf16*
     const int c = (k * 32 + lane) * 8;
     if (c < dim) {
       float g[8];
-      ld8(w + c, g);
+      ld8v(w + c, g);
 #pragma unroll
       for (int e = 0; e < 8; ++e) v[k][e] *= rs * g[e];
-      st8(out + (int64_t)r * dim + c, v[k]);
+      st8v(out + (int64_t)r * dim + c, v[k]);
     }
   }
 }
@@ -118,12 +118,12 @@ __global__ void __launch_bounds__(128)
   __syncwarp();  // the ring rows of this (stream, head) are written and read by this warp alone
   float mx = -INFINITY;
   for (int j = lane; j < n; j += 32) {
-    const Pack8* kr = reinterpret_cast<const Pack8*>(ring + (int64_t)((first + j) % kWindow) * width + head * kHeadDim);
+    const uint4* kr = reinterpret_cast<const uint4*>(ring + (int64_t)((first + j) % kWindow) * width + head * kHeadDim);
     float dot = 0.f;
 #pragma unroll
     for (int q8 = 0; q8 < 8; ++q8) {
       float kv[8];
-      unpack8(kr[q8], kv);
+      unpack8v(kr[q8], kv);
 #pragma unroll
       for (int e = 0; e < 8; ++e) dot += sq[warp][q8 * 8 + e] * kv[e];
     }
@@ -158,30 +158,30 @@ __global__ void codec_silu_mul_kernel(const bf16* __restrict__ gate_up, bf16* __
   const int per = inter / 8;
   const int64_t r = i / per, c = i % per * 8;
   float g[8], u[8];
-  ld8(gate_up + r * 2 * inter + c, g);
-  ld8(gate_up + r * 2 * inter + inter + c, u);
+  ld8v(gate_up + r * 2 * inter + c, g);
+  ld8v(gate_up + r * 2 * inter + inter + c, u);
 #pragma unroll
   for (int k = 0; k < 8; ++k) g[k] = bf16_round(g[k] / (1.f + __expf(-g[k]))) * u[k];
-  st8(out + i * 8, g);
+  st8v(out + i * 8, g);
 }
 
 __global__ void codec_bias_gelu_kernel(bf16* __restrict__ x, const bf16* __restrict__ bias, int cols, int64_t total) {
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= total) return;
   float v[8], b[8];
-  ld8(x + i * 8, v);
-  ld8(bias + i % (cols / 8) * 8, b);
+  ld8v(x + i * 8, v);
+  ld8v(bias + i % (cols / 8) * 8, b);
 #pragma unroll
   for (int k = 0; k < 8; ++k) {
     const float y = bf16_round(v[k] + b[k]);
     v[k] = 0.5f * y * (1.f + erff(y * 0.70710678118654752f));
   }
-  st8(x + i * 8, v);
+  st8v(x + i * 8, v);
 }
 
 __device__ __forceinline__ void bias_snake8(float* v, const bf16* bias, const float* alpha, const float* inv_b, int c) {
   float b[8], al[8], ib[8];
-  ld8(bias + c, b);
+  ld8v(bias + c, b);
   ldf8(alpha + c, al);
   ldf8(inv_b + c, ib);
 #pragma unroll
@@ -194,9 +194,9 @@ __global__ void codec_bias_snake_kernel(const bf16* __restrict__ x, const bf16* 
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= total) return;
   float v[8];
-  ld8(x + i * 8, v);
+  ld8v(x + i * 8, v);
   bias_snake8(v, bias, alpha, inv_b, (int)(i % (cols / 8)) * 8);
-  st8(out + i * 8, v);
+  st8v(out + i * 8, v);
 }
 
 // One thread per eight channels of a padded row: rows below H come from the history, the rest are the transformed
@@ -213,24 +213,24 @@ __global__ void codec_stage_kernel(const bf16* __restrict__ x, const bf16* __res
   const int p = st.pos[s];
   bf16* hist = slot_ptr(st, s, hist_offset);
   const int64_t half = (int64_t)H * C;
-  Pack8 u;
+  uint4 u;
   if (r < H) {
-    u = *reinterpret_cast<const Pack8*>(hist + (p & 1) * half + (int64_t)r * C + c);
+    u = *reinterpret_cast<const uint4*>(hist + (p & 1) * half + (int64_t)r * C + c);
   } else {
     float v[8];
-    ld8(x + ((int64_t)s * T + r - H) * C + c, v);
+    ld8v(x + ((int64_t)s * T + r - H) * C + c, v);
     if (alpha != nullptr) {
       bias_snake8(v, bias, alpha, inv_b, c);
     } else {
       float b[8];
-      ld8(bias + c, b);
+      ld8v(bias + c, b);
 #pragma unroll
       for (int k = 0; k < 8; ++k) v[k] += b[k];
     }
-    u = pack8(v);
+    u = pack8v(v);
   }
-  *reinterpret_cast<Pack8*>(padded + ((int64_t)s * P + r) * C + c) = u;
-  if (r >= T) *reinterpret_cast<Pack8*>(hist + ((p + 1) & 1) * half + (int64_t)(r - T) * C + c) = u;
+  *reinterpret_cast<uint4*>(padded + ((int64_t)s * P + r) * C + c) = u;
+  if (r >= T) *reinterpret_cast<uint4*>(hist + ((p + 1) & 1) * half + (int64_t)(r - T) * C + c) = u;
 }
 
 __global__ void codec_gather_taps_kernel(const bf16* __restrict__ padded, bf16* __restrict__ col, int T, int C, int taps,
@@ -243,8 +243,8 @@ __global__ void codec_gather_taps_kernel(const bf16* __restrict__ padded, bf16* 
   const int j = (int)(g % taps);
   g /= taps;
   const int t = (int)(g % T), s = (int)(g / T);
-  *reinterpret_cast<Pack8*>(col + (((int64_t)s * T + t) * taps + j) * C + c) =
-      *reinterpret_cast<const Pack8*>(padded + ((int64_t)s * P + t + j * dil) * C + c);
+  *reinterpret_cast<uint4*>(col + (((int64_t)s * T + t) * taps + j) * C + c) =
+      *reinterpret_cast<const uint4*>(padded + ((int64_t)s * P + t + j * dil) * C + c);
 }
 
 __global__ void codec_overlap_add_kernel(const bf16* __restrict__ z, const bf16* __restrict__ bias, CodecStateRef st,
@@ -259,20 +259,20 @@ __global__ void codec_overlap_add_kernel(const bf16* __restrict__ z, const bf16*
   const int64_t w = (int64_t)2 * r * C;
   const bf16* zs = z + (int64_t)s * L * w;
   float v[8], y[8];
-  ld8(bias + c, v);
-  ld8(zs + l * w + (int64_t)j * C + c, y);
+  ld8v(bias + c, v);
+  ld8v(zs + l * w + (int64_t)j * C + c, y);
 #pragma unroll
   for (int k = 0; k < 8; ++k) v[k] += y[k];
   if (l > 0) {
-    ld8(zs + (l - 1) * w + (int64_t)(j + r) * C + c, y);
+    ld8v(zs + (l - 1) * w + (int64_t)(j + r) * C + c, y);
   } else {  // the row before the frame's first: kept from the last call; this thread alone touches the entry
     bf16* prev = slot_ptr(st, s, prev_offset) + (int64_t)j * C + c;
-    ld8(prev, y);
-    *reinterpret_cast<Pack8*>(prev) = *reinterpret_cast<const Pack8*>(zs + (L - 1) * w + (int64_t)(j + r) * C + c);
+    ld8v(prev, y);
+    *reinterpret_cast<uint4*>(prev) = *reinterpret_cast<const uint4*>(zs + (L - 1) * w + (int64_t)(j + r) * C + c);
   }
 #pragma unroll
   for (int k = 0; k < 8; ++k) v[k] += y[k];
-  st8(out + i * 8, v);
+  st8v(out + i * 8, v);
 }
 
 // One block per row, eight channels per thread; the block is a whole number of warps, threads past the last channel
@@ -292,32 +292,32 @@ __global__ void codec_dwconv_ln_kernel(const bf16* __restrict__ z, const bf16* _
   bf16* next = hist + ((p + 1) & 1) * (int64_t)H * C;
   float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, cur[8];
   if (on) {
-    ld8(b + c, acc);
+    ld8v(b + c, acc);
 #pragma unroll
     for (int j = 0; j < kTaps; ++j) {
       const int src = t - (H - j);
       float v[8], wt[8];
       if (src >= 0) {
         float bias[8];
-        ld8(z + ((int64_t)s * T + src) * C + c, v);
-        ld8(zb + (int64_t)(src % r) * C + c, bias);
+        ld8v(z + ((int64_t)s * T + src) * C + c, v);
+        ld8v(zb + (int64_t)(src % r) * C + c, bias);
 #pragma unroll
         for (int k = 0; k < 8; ++k) v[k] = bf16_round(v[k] + bias[k]);
       } else {
-        ld8(old + (int64_t)(H + src) * C + c, v);
+        ld8v(old + (int64_t)(H + src) * C + c, v);
       }
-      ld8(w + (int64_t)j * C + c, wt);
+      ld8v(w + (int64_t)j * C + c, wt);
 #pragma unroll
       for (int k = 0; k < 8; ++k) {
         acc[k] += wt[k] * v[k];
         cur[k] = v[k];
       }
     }
-    st8(xin + g * C + c, cur);
-    if (t + H - T >= 0) st8(next + (int64_t)(t + H - T) * C + c, cur);
+    st8v(xin + g * C + c, cur);
+    if (t + H - T >= 0) st8v(next + (int64_t)(t + H - T) * C + c, cur);
     // with fewer rows per frame than the history holds, the old history's tail moves up
     for (int m = t; m < H - T; m += T)
-      *reinterpret_cast<Pack8*>(next + (int64_t)m * C + c) = *reinterpret_cast<const Pack8*>(old + (int64_t)(m + T) * C + c);
+      *reinterpret_cast<uint4*>(next + (int64_t)m * C + c) = *reinterpret_cast<const uint4*>(old + (int64_t)(m + T) * C + c);
   }
   float sum = 0.f;
 #pragma unroll
@@ -334,11 +334,11 @@ __global__ void codec_dwconv_ln_kernel(const bf16* __restrict__ z, const bf16* _
   const float rstd = rsqrtf(block_add(sq, scratch) / C + eps);
   if (on) {
     float lw[8], lb[8];
-    ld8(ln_w + c, lw);
-    ld8(ln_b + c, lb);
+    ld8v(ln_w + c, lw);
+    ld8v(ln_b + c, lb);
 #pragma unroll
     for (int k = 0; k < 8; ++k) acc[k] = (acc[k] - mean) * rstd * lw[k] + lb[k];
-    st8(out + g * C + c, acc);
+    st8v(out + g * C + c, acc);
   }
 }
 
@@ -365,14 +365,14 @@ __global__ void __launch_bounds__(256)
     const int row = i / per, c = i % per * 8, src = t0 - H + row;
     float v[8];
     if (src < 0) {
-      ld8(old + (int64_t)(H + src) * C + c, v);
+      ld8v(old + (int64_t)(H + src) * C + c, v);
     } else {
-      ld8(x + ((int64_t)s * T + src) * C + c, v);
+      ld8v(x + ((int64_t)s * T + src) * C + c, v);
       bias_snake8(v, bias, alpha, inv_b, c);
 #pragma unroll
       for (int k = 0; k < 8; ++k) v[k] = bf16_round(v[k]);
       // the frame's last six rows are the next history; rows below the tile's own (row < H) belong to the tile before
-      if (src >= T - H && row >= H) st8(next + (int64_t)(src - (T - H)) * C + c, v);
+      if (src >= T - H && row >= H) st8v(next + (int64_t)(src - (T - H)) * C + c, v);
     }
 #pragma unroll
     for (int k = 0; k < 8; ++k) sx[row * ld + c + k] = v[k];

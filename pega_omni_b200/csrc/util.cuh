@@ -47,6 +47,35 @@ __device__ __forceinline__ Pack8 pack8(const float* v) {
 __device__ __forceinline__ void ld8(const bf16* src, float* v) { unpack8(*reinterpret_cast<const Pack8*>(src), v); }
 __device__ __forceinline__ void st8(bf16* dst, const float* v) { *reinterpret_cast<Pack8*>(dst) = pack8(v); }
 
+// The same eight values moved as one 16-byte word: an access through uint4 is a single vector instruction wherever the
+// struct copy above might be split into four.
+__device__ __forceinline__ void unpack8v(const uint4& u, float* v) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = __bfloat1622float2(h[i]);
+    v[2 * i] = f.x;
+    v[2 * i + 1] = f.y;
+  }
+}
+
+__device__ __forceinline__ uint4 pack8v(const float* v) {
+  uint4 u;
+  __nv_bfloat162 t;
+  t = __floats2bfloat162_rn(v[0], v[1]);
+  u.x = *reinterpret_cast<const uint32_t*>(&t);
+  t = __floats2bfloat162_rn(v[2], v[3]);
+  u.y = *reinterpret_cast<const uint32_t*>(&t);
+  t = __floats2bfloat162_rn(v[4], v[5]);
+  u.z = *reinterpret_cast<const uint32_t*>(&t);
+  t = __floats2bfloat162_rn(v[6], v[7]);
+  u.w = *reinterpret_cast<const uint32_t*>(&t);
+  return u;
+}
+
+__device__ __forceinline__ void ld8v(const bf16* src, float* v) { unpack8v(*reinterpret_cast<const uint4*>(src), v); }
+__device__ __forceinline__ void st8v(bf16* dst, const float* v) { *reinterpret_cast<uint4*>(dst) = pack8v(v); }
+
 __device__ __forceinline__ float warp_add(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
