@@ -44,8 +44,6 @@ __device__ __forceinline__ Pack8 pack8(const float* v) {
   return p;
 }
 
-__device__ __forceinline__ void ld8(const bf16* src, float* v) { unpack8(*reinterpret_cast<const Pack8*>(src), v); }
-__device__ __forceinline__ void st8(bf16* dst, const float* v) { *reinterpret_cast<Pack8*>(dst) = pack8(v); }
 
 // The same eight values moved as one 16-byte word: an access through uint4 is a single vector instruction wherever the
 // struct copy above might be split into four.
@@ -75,6 +73,9 @@ __device__ __forceinline__ uint4 pack8v(const float* v) {
 
 __device__ __forceinline__ void ld8v(const bf16* src, float* v) { unpack8v(*reinterpret_cast<const uint4*>(src), v); }
 __device__ __forceinline__ void st8v(bf16* dst, const float* v) { *reinterpret_cast<uint4*>(dst) = pack8v(v); }
+// Eight bf16 at a 16-byte aligned address.
+__device__ __forceinline__ void ld8(const bf16* src, float* v) { ld8v(src, v); }
+__device__ __forceinline__ void st8(bf16* dst, const float* v) { st8v(dst, v); }
 
 __device__ __forceinline__ float warp_add(float v) {
 #pragma unroll

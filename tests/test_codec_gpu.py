@@ -1,0 +1,115 @@
+"""The streaming codec decoder on the GPU, through the C ABI, against the CPU restatement (oracle/codec.py): frame by
+frame against the bf16 streaming oracle, and as a whole against the float64 whole-utterance decoder. The layout follows
+the reference's own waveform test (crates/omni-qwen3-tts/tests/golden.rs:106-162): two streams fed the same frames in
+one batch must agree bit for bit, and a stream that starts later must decode the same audio."""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+from oracle import codec as oc  # noqa: E402
+from pega_omni_b200.codec import CODEC_PRESETS, Codec, codec_random_checkpoint  # noqa: E402
+from pega_omni_b200.model import Denied, OmniError  # noqa: E402
+
+
+def _setup(preset, frames, seed=1):
+    c = CODEC_PRESETS[preset]
+    ck = codec_random_checkpoint(c, 0)
+    codes = np.random.default_rng(seed).integers(0, c.codebook_size, size=(frames, 16)).astype(np.int32)
+    so = oc.StreamOracle(c, oc.fold(ck, c))
+    want = np.stack([so.step(f) for f in codes])
+    return c, ck, codes, want
+
+
+@pytest.mark.parametrize("preset,frames,graphs", [("codec-tiny", 6, False), ("codec-tiny", 80, True),
+                                                  ("codec-mid", 5, True)])
+def test_streams_match_the_oracle(built_lib, preset, frames, graphs):
+    c, ck, codes, want = _setup(preset, frames)
+    ref = oc.whole_utterance(ck, c, codes).reshape(frames, -1)
+    m = Codec(c, ck, max_batch=4, use_graphs=graphs)
+    a, b, late = m.open(), m.open(), m.open()
+    lag = 2
+    got, lagging = [], []
+    for f in range(frames + lag):
+        streams, rows = [], []
+        if f < frames:
+            streams += [a, b]
+            rows += [codes[f], codes[f]]
+        if f >= lag:
+            streams.append(late)
+            rows.append(codes[f - lag])
+        w = m.decode(streams, np.stack(rows))
+        if f < frames:
+            assert np.array_equal(w[0], w[1]), "two streams of the same frames in one batch decode differently"
+            got.append(w[0])
+        if f >= lag:
+            lagging.append(w[-1])
+    got, lagging = np.stack(got), np.stack(lagging)
+    assert a.frames == frames and late.frames == frames
+    assert np.isfinite(got).all() and np.abs(got).max() <= 1.0
+    # bit-equal bf16 values are not expected: the tensor-core GEMMs sum in another order than the oracle's, and one
+    # flipped rounding travels through every later layer. Measured: 29-36 dB against the streaming oracle, and the same
+    # distance from the float64 decoder as the oracle's own (26-28 dB)
+    assert oc.snr_db(got, want) > 25.0
+    assert oc.snr_db(got, ref) > oc.snr_db(want, ref) - 1.5
+    assert oc.snr_db(got[0], want[0]) > 33.0  # the first frame has no rounding history behind it
+    # the lagging stream ran in other batch rows and buckets: same audio up to the same noise
+    assert oc.snr_db(lagging, want) > 25.0
+    m.close()
+
+
+def test_graph_replay_equals_per_op_launches(built_lib):
+    c, ck, codes, _ = _setup("codec-tiny", 5)
+    out = []
+    for graphs in (False, True):
+        m = Codec(c, ck, max_batch=2, use_graphs=graphs)
+        if graphs:
+            m.warmup()
+        s = m.open()
+        out.append(np.stack([m.decode([s], f[None])[0] for f in codes]))
+        ms, launches = m.stats()
+        assert launches > 50 and ms > 0
+        m.close()
+    assert np.array_equal(out[0], out[1])
+
+
+def test_a_reopened_slot_starts_from_silence(built_lib):
+    c, ck, codes, want = _setup("codec-tiny", 3)
+    m = Codec(c, ck, max_batch=1, streams=1, use_graphs=False)
+    s = m.open()
+    first = np.stack([m.decode([s], f[None])[0] for f in codes])
+    with pytest.raises(Denied):
+        m.open()
+    s.close()
+    s = m.open()  # the same slot again: its histories, overlap rows and ring must read as zero
+    again = np.stack([m.decode([s], f[None])[0] for f in codes])
+    assert np.array_equal(first, again)
+    m.close()
+
+
+def test_end_of_speech_and_invalid_codes(built_lib):
+    c, ck, codes, _ = _setup("codec-tiny", 1)
+    m = Codec(c, ck, max_batch=2, use_graphs=False)
+    a, b = m.open(), m.open()
+    eos = codes[0].copy()
+    eos[0] = c.codebook_size + 102   # the talker's end of speech in codebook 0 reads as code 0
+    zero = codes[0].copy()
+    zero[0] = 0
+    w = m.decode([a, b], np.stack([eos, zero]))
+    assert np.array_equal(w[0], w[1])
+    bad = codes[0].copy()
+    bad[3] = c.codebook_size
+    with pytest.raises(OmniError):
+        m.decode([a], bad[None])
+    with pytest.raises(OmniError):
+        m.decode([a, a], np.stack([zero, zero]))
+    assert a.frames == 1  # a refused call advances nothing
+    m.close()
+
+
+def test_unsupported_shapes_are_refused(built_lib):
+    import dataclasses
+    c = dataclasses.replace(CODEC_PRESETS["codec-tiny"], sliding_window=64)
+    with pytest.raises(OmniError) as e:
+        Codec(c, codec_random_checkpoint(c, 0), max_batch=1)
+    assert e.value.status == -5
