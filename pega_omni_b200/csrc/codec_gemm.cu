@@ -28,7 +28,8 @@ constexpr int kConvRows = 128;    // output rows per tile
 constexpr int kConvRing = 200 * 1024;
 constexpr int kConvMaxStages = 8;
 constexpr int kConvThreads = 192; // warp 0 producer, warp 1 MMA issuer, warps 2..5 epilogue
-constexpr size_t kConvSmem = (size_t)kConvRing + 1024 + 256;
+constexpr int kStagePitch = 36;   // floats per row of an epilogue warp's 32 x 32 staging block (16-byte aligned, conflict-free)
+constexpr size_t kConvSmem = (size_t)kConvRing + 1024 + 256 + 4 * 32 * kStagePitch * sizeof(float);
 
 struct ConvArgs {
   bf16* y;
@@ -144,29 +145,28 @@ __global__ void __launch_bounds__(kConvThreads, 1)
     }
     __syncwarp();
   } else {
-    // Epilogue: a thread owns one output row (its TMEM lane; a warp reaches the 32 lanes of quadrant warp % 4) and
-    // walks it 32 channels at a time. What an accumulating GEMM adds to does not depend on the accumulator, so the
-    // row's old values are requested one step ahead: the first step's before the wait for the accumulator.
-    const int quad = warp & 3, m = quad * 32 + lane;
+    // Epilogue. A warp reaches the 32 TMEM lanes of quadrant warp % 4, one output row per thread, and takes the tile 32
+    // channels at a time. A thread's row is 2 * N bytes away from its neighbour's, so storing from that layout would
+    // cost one memory transaction per thread and 16 bytes; instead the 32 x 32 f32 block goes through shared memory
+    // and comes back with four lanes per row (8 channels each), so that a warp instruction covers 8 rows x 64 bytes.
+    // The old values of an accumulating GEMM, the bias and the SnakeBeta parameters are read in that layout too.
+    const int quad = warp & 3;
+    float* stg = reinterpret_cast<float*>(base_ptr + kConvRing + 256) + (warp - 2) * (32 * kStagePitch);
+    const int sub_row = lane >> 2, chunk = lane & 3;
     int use = 0;
     bool alive = true;
     for (int tile = blockIdx.x; tile < a.tiles && alive; tile += gridDim.x, ++use) {
       const int buf = use & 1;
       const int n0 = (tile % a.n_tiles) * a.tn, rt = tile / a.n_tiles;
       const int t0 = (rt % a.t_tiles) * a.TB, s0 = (rt / a.t_tiles) * a.SB;
-      const int s = s0 + m / a.TB, t = t0 + m % a.TB;
-      const bool in_range = s < a.seqs;
-      bf16* row = a.y + ((int64_t)s * a.T + t) * a.N;
       const uint32_t lane_addr = tmem_base + (uint32_t)buf * a.acc_cols + ((uint32_t)(quad * 32) << 16);
-      uint4 ahead[4] = {};
-      auto fetch_old = [&](int c0) {
+      // the four rows this lane stores in every step
+      bf16* rows[4];
 #pragma unroll
-        for (int h = 0; h < 4; ++h) {
-          const int nn = n0 + c0 + 8 * h;
-          if (in_range && c0 + 8 * h < a.tn && nn + 8 <= a.N) ahead[h] = *reinterpret_cast<const uint4*>(row + nn);
-        }
-      };
-      if (a.kind == kConvAccumulate) fetch_old(0);
+      for (int i = 0; i < 4; ++i) {
+        const int m = quad * 32 + 8 * i + sub_row, s = s0 + m / a.TB, t = t0 + m % a.TB;
+        rows[i] = s < a.seqs ? a.y + ((int64_t)s * a.T + t) * a.N : nullptr;
+      }
       alive = mbar_wait(acc_full(buf), (uint32_t)(use >> 1) & 1u, a.err);
       if (!alive) break;
       tc_fence_after_sync();
@@ -181,41 +181,55 @@ __global__ void __launch_bounds__(kConvThreads, 1)
 #pragma unroll
           for (int j = 0; j < 16; ++j) r1[j] = 0u;
         }
-        uint4 old[4];
+        const int nn = n0 + c0 + 8 * chunk;
+        const bool cols_live = c0 + 8 * chunk < a.tn && nn + 8 <= a.N;
+        uint4 old[4] = {};
+        if (a.kind == kConvAccumulate && cols_live) {
 #pragma unroll
-        for (int h = 0; h < 4; ++h) old[h] = ahead[h];
-        if (a.kind == kConvAccumulate && c0 + 32 < a.tn) fetch_old(c0 + 32);
+          for (int i = 0; i < 4; ++i)
+            if (rows[i]) old[i] = *reinterpret_cast<const uint4*>(rows[i] + nn);
+        }
         tmem_ld_fence(r0, r1);
         if (c0 + 32 >= a.tn) {  // the accumulator is in registers: the MMA issuer may start the tile after next
           tc_fence_before_sync();
           __syncwarp();
           if (lane == 0) mbar_arrive(acc_empty(buf));
         }
-        if (!in_range) continue;
+        uint4* mine = reinterpret_cast<uint4*>(stg + lane * kStagePitch);
 #pragma unroll
-        for (int h = 0; h < 4; ++h) {
-          const int nn = n0 + c0 + 8 * h;
-          if (c0 + 8 * h >= a.tn || nn + 8 > a.N) break;
-          float o[8];
-#pragma unroll
-          for (int j = 0; j < 8; ++j) o[j] = __uint_as_float(h < 2 ? r0[8 * h + j] : r1[8 * (h - 2) + j]);
-          if (a.kind == kConvAccumulate) {
-            float prev[8];
-            unpack8v(old[h], prev);
-#pragma unroll
-            for (int j = 0; j < 8; ++j) o[j] += prev[j];
-          } else if (a.kind == kConvBiasSnake) {
-            float b[8];
+        for (int q = 0; q < 4; ++q) {
+          mine[q] = make_uint4(r0[4 * q], r0[4 * q + 1], r0[4 * q + 2], r0[4 * q + 3]);
+          mine[4 + q] = make_uint4(r1[4 * q], r1[4 * q + 1], r1[4 * q + 2], r1[4 * q + 3]);
+        }
+        __syncwarp();
+        if (cols_live) {
+          float b[8], al[8], ib[8];
+          if (a.kind == kConvBiasSnake) {
             ld8v(a.bias + nn, b);
             const float4 a0 = *reinterpret_cast<const float4*>(a.alpha + nn), a1 = *reinterpret_cast<const float4*>(a.alpha + nn + 4);
             const float4 i0 = *reinterpret_cast<const float4*>(a.inv_b + nn), i1 = *reinterpret_cast<const float4*>(a.inv_b + nn + 4);
-            const float al[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
-            const float ib[8] = {i0.x, i0.y, i0.z, i0.w, i1.x, i1.y, i1.z, i1.w};
-#pragma unroll
-            for (int j = 0; j < 8; ++j) o[j] = snake_beta(bf16_round(o[j]) + b[j], al[j], ib[j]);
+            al[0] = a0.x, al[1] = a0.y, al[2] = a0.z, al[3] = a0.w, al[4] = a1.x, al[5] = a1.y, al[6] = a1.z, al[7] = a1.w;
+            ib[0] = i0.x, ib[1] = i0.y, ib[2] = i0.z, ib[3] = i0.w, ib[4] = i1.x, ib[5] = i1.y, ib[6] = i1.z, ib[7] = i1.w;
           }
-          st8v(row + nn, o);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            if (!rows[i]) continue;
+            const float4* src = reinterpret_cast<const float4*>(stg + (8 * i + sub_row) * kStagePitch + 8 * chunk);
+            const float4 lo = src[0], hi = src[1];
+            float o[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+            if (a.kind == kConvAccumulate) {
+              float prev[8];
+              unpack8v(old[i], prev);
+#pragma unroll
+              for (int j = 0; j < 8; ++j) o[j] += prev[j];
+            } else if (a.kind == kConvBiasSnake) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) o[j] = snake_beta(bf16_round(o[j]) + b[j], al[j], ib[j]);
+            }
+            st8v(rows[i] + nn, o);
+          }
         }
+        __syncwarp();  // the block is read out before the next step overwrites it
       }
     }
   }
