@@ -630,6 +630,7 @@ def main():
                     help="talker: the headline Qwen3-TTS tick (default); duplex: the PersonaPlex-7B tick (configs[3]); "
                          "higgs: the Higgs-style 4B step (configs[4])")
     ap.add_argument("--context", type=int, default=3000, help="duplex: KV ring length")
+    ap.add_argument("--no-codec", action="store_true", help="talker: skip the tick + codec decoder arm (with_codec)")
     ap.add_argument("--e2e-waited", action="store_true", help="talker: the end-to-end arm waits on every step (Model.step) "
                     "instead of keeping two steps under way (step_begin / step_end)")
     ap.add_argument("--trace", default=None, help="talker: write the tick kernel's per-phase device timestamps here")
@@ -771,6 +772,42 @@ def main():
     h2d = 4 * (bucket * (1 + 1 + 16 + 16 + 1 + 1) + bucket + 1) + 4 * n * pages_per_seq  # staged front block (approx.)
     d2h = 4 * (bucket * 16 + 1)
 
+    # ---- with the codec decoder behind every tick: what a serving engine runs per 80 ms frame (rank 0 only) ----
+    with_codec = None
+    if rank == 0 and not args.no_codec:
+        from pega_omni_b200.codec import CODEC_PRESETS, Codec, codec_random_checkpoint
+        cc = CODEC_PRESETS["qwen3-tts-12hz"]
+        codec = Codec(cc, codec_random_checkpoint(cc, seed=0), max_batch=n, device=local)
+        codec.warmup()
+        streams = [codec.open() for _ in range(n)]
+        for s_ in seqs:
+            model.release(s_)
+        seqs = [model.open(args.prompt, frames_cap) for _ in range(n)]
+        for i in range(0, n, 32):
+            model.start(list(zip(seqs[i:i + 32], prompts[i:i + 32], d0[i:i + 32])))
+        kc = min(K, 32)
+        out = None
+        tick_ms = codec_ms = 0.0
+        for t in range(W + kc):
+            if t == W:
+                torch.cuda.synchronize()
+                t0 = time.perf_counter()
+            out = model.step_batch(seqs, e2e_draws[t], out)
+            codec.decode(streams, out.codes)
+            if t >= W:
+                tick_ms += model.stats().last_call_gpu_ms
+                codec_ms += codec.stats()[0]
+        torch.cuda.synchronize()
+        wall = time.perf_counter() - t0
+        with_codec = {"ms_per_step": 1e3 * wall / kc, "value": n * kc / wall, "unit": UNIT, "steps": kc,
+                      "device_ms": {"tick": tick_ms / kc, "codec_decoder": codec_ms / kc},
+                      "what": "every step: omni_talker_step (host draws in, codes out), then omni_codec_decode of those "
+                              "codes (1,920 f32 samples per session read back); wall clock, one GPU, the two calls "
+                              "back to back on the host",
+                      "reference_published": "8.27 ms per step at 64 sessions with its codec decoder, of which 1.00 ms "
+                                             "codec (docs/bench.md:156-160 of the reference, other hardware)"}
+        codec.close()
+
     if rank == 0:
         peak, peak_kind = measured_peaks()
         mean_len = float(np.mean(lens)) + 1
@@ -823,6 +860,8 @@ def main():
             "tick_bytes": {"weights": int(weight_bytes), "kv": int(tick_bytes - weight_bytes), "mean_kv_len": mean_len,
                            "folded_at_load": int(cfg.tick_weight_bytes() - weight_bytes)},
         }
+        if with_codec is not None:
+            line["with_codec"] = with_codec
         if not args.no_replay and world == 1:
             model.close()
             torch.cuda.empty_cache()
