@@ -180,6 +180,57 @@ int32_t omni_op_gemm_noalloc(const void* w, int32_t N, int32_t K, const void* x,
                              int32_t splits, const void* bias, int32_t epilogue, void* stream, char* message,
                              size_t message_len);
 
+/* ---- streaming codec decoder: crates/omni-qwen3-tts/kernels/codec.cu, src/codec.rs -------------------------------
+ * A per-stream state is `state + lines[s] * stride` bytes plus the entry's own byte offset; `pos[s]` is the number of
+ * frames stream s has decoded before the call (histories are two halves, frame p reads half p & 1 and writes the
+ * other). Channel counts are multiples of 8. */
+
+/* `codec_rvq` (codec.cu:66-82): out[s] = [book 0 row codes[s][0] | bf16(f32 sum of books 1..15 rows)], books
+ * [16 * book_rows, half]; a codebook-0 code >= book_rows reads as 0. */
+int32_t omni_op_codec_rvq(omni_ops* ctx, const int32_t* codes, const void* books, void* out, int32_t n, int32_t half,
+                          int32_t book_rows);
+/* `codec_add_rms_norm` / `codec_bias_rms_norm` (codec.cu:117-170): v = res + add (add_stride 0: one row for all);
+ * res = bf16(v); out = bf16(v * (rsqrt(mean v^2 + eps) * w)); out may be add. dim a multiple of 256 up to 1024. */
+int32_t omni_op_codec_add_norm(omni_ops* ctx, const void* add, int64_t add_stride, void* res, const void* w, void* out,
+                               int32_t rows, int32_t dim, float eps);
+/* `codec_attention` (codec.cu:177-283): rotary embedding of q and k, k and v into the stream's ring
+ * (K[72][heads * 64] then V, frame p at p % 72), q against the last min(p + 1, 72) frames. qkv [n, 3 * heads * 64]. */
+int32_t omni_op_codec_window_attend(omni_ops* ctx, const void* qkv, void* state, const int32_t* lines, const int32_t* pos,
+                                    int64_t stride, int64_t ring_offset, void* out, int32_t n, int32_t heads, float theta);
+/* `codec_bias_gelu` (codec.cu:84-98), in place; `codec_bias_snake` (codec.cu:100-109). */
+int32_t omni_op_codec_bias_gelu(omni_ops* ctx, void* x, const void* bias, int64_t rows, int32_t cols);
+int32_t omni_op_codec_bias_snake(omni_ops* ctx, const void* x, const void* bias, const float* alpha, const float* inv_b,
+                                 void* out, int64_t rows, int32_t cols);
+/* The input side of `codec_im2col` / `codec_im2col_snake` (codec.cu:291-337) without the im2col matrix:
+ * padded[s][r] = r < H ? history row r : bf16(act(x[s * T + r - H] + bias)), act SnakeBeta when alpha is given; the last
+ * H rows become the next frame's history. `gather_taps` then writes the reference's matrix from it:
+ * col[s * T + t][j * C + c] = padded[s][t + j * dil][c]. */
+int32_t omni_op_codec_stage(omni_ops* ctx, const void* x, const void* bias, const float* alpha, const float* inv_b,
+                            void* state, const int32_t* lines, const int32_t* pos, int64_t stride, int64_t hist_offset,
+                            void* padded, int32_t n, int32_t T, int32_t C, int32_t H);
+int32_t omni_op_codec_gather_taps(omni_ops* ctx, const void* padded, void* col, int32_t n, int32_t T, int32_t C,
+                                  int32_t taps, int32_t dil);
+/* The conv itself as an implicit GEMM on tcgen05 (what `codec_im2col` + the runtime's GEMM compute, codec.rs:60-93):
+ * y[s * T + t][n] (+)= sum over taps j, channels c of padded[s][t + j * dil][c] * w[n][j * C + c]; epilogue 0: store,
+ * 1: y = bf16(y + a), 2: y = bf16(snake(bf16(a) + bias[n])). taps = 1: padded is the dense [n_streams * T, C] input. */
+int32_t omni_op_codec_conv(omni_ops* ctx, const void* w, int32_t N, int32_t C, int32_t taps, int32_t dil,
+                           const void* padded, int32_t T, int32_t n_streams, void* y, int32_t epilogue, const void* bias,
+                           const float* alpha, const float* inv_b);
+/* `codec_col2im` (codec.cu:339-372): transposed conv with kernel 2r, stride r, over z [n, L, 2r * C]. */
+int32_t omni_op_codec_overlap_add(omni_ops* ctx, const void* z, const void* bias, void* state, const int32_t* lines,
+                                  const int32_t* pos, int64_t stride, int64_t prev_offset, void* out, int32_t n, int32_t L,
+                                  int32_t r, int32_t C);
+/* `codec_dwconv_ln` (codec.cu:381-446): xin = bf16(z + zb[row % r]); depthwise 7-tap causal conv; LayerNorm -> out. */
+int32_t omni_op_codec_dwconv_ln(omni_ops* ctx, const void* z, const void* zb, const void* w, const void* b,
+                                const void* ln_w, const void* ln_b, void* state, const int32_t* lines, const int32_t* pos,
+                                int64_t stride, int64_t hist_offset, void* xin, void* out, int32_t n, int32_t T, int32_t r,
+                                int32_t C, float eps);
+/* `codec_conv_out` (codec.cu:455-513): last SnakeBeta, the C -> 1 conv of 7 taps, the clamp; wav f32 [n][T] (the
+ * reference stores the same values as bf16). T a multiple of 64, C a multiple of 32 up to 128. */
+int32_t omni_op_codec_out_conv(omni_ops* ctx, const void* x, const void* bias, const float* alpha, const float* inv_b,
+                               const void* w, const void* wb, void* state, const int32_t* lines, const int32_t* pos,
+                               int64_t stride, int64_t hist_offset, float* wav, int32_t n, int32_t T, int32_t C);
+
 #ifdef __cplusplus
 }
 #endif

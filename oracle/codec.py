@@ -19,6 +19,8 @@ Two decoders over the same checkpoint tensors:
 
 Parity status: UNPINNED against a real checkpoint (none is available offline, and the reference's golden file is not in
 its tree); the two decoders here pin each other (tests/test_codec_oracle.py), and the CUDA path is compared with both.
+The CUDA kernels themselves are also compared one by one with the reference's codec.cu compiled for sm_100a
+(tests/test_codec_ops_gpu.py), which this file takes no part in.
 """
 from __future__ import annotations
 

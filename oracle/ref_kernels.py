@@ -1,8 +1,8 @@
 """The reference's own CUDA kernels, compiled for sm_100a and replayed on the GPU (TEST INFRASTRUCTURE).
 
 build(): when the reference checkout is present, compiles `crates/omni-qwen3/kernels/qwen3.cu`,
-`crates/omni-qwen3-tts/kernels/talker.cu`, `crates/omni-personaplex/kernels/lm.cu` and
-`crates/omni-higgs-audio/kernels/higgs.cu` where they lie (include path
+`crates/omni-qwen3-tts/kernels/talker.cu`, `crates/omni-qwen3-tts/kernels/codec.cu`,
+`crates/omni-personaplex/kernels/lm.cu` and `crates/omni-higgs-audio/kernels/higgs.cu` where they lie (include path
 `crates/omni-kern/kernels`) into
 `oracle/_ref/*.cubin` with the reference's own flags except the architecture
 (crates/omni-qwen3/build.rs:17-27: `nvcc -cubin -O3 -std=c++17`). Sources are never copied.
@@ -30,6 +30,7 @@ SOURCES = {
     "talker": "crates/omni-qwen3-tts/kernels/talker.cu",
     "lm": "crates/omni-personaplex/kernels/lm.cu",
     "higgs": "crates/omni-higgs-audio/kernels/higgs.cu",
+    "codec": "crates/omni-qwen3-tts/kernels/codec.cu",
 }
 
 

@@ -7,6 +7,7 @@
 
 #include "../../include/omni_b200.h"
 #include "../../include/omni_b200_ops.h"
+#include "codec.h"
 #include "gemm.h"
 #include "duplex.h"
 #include "kernels.h"
@@ -316,6 +317,106 @@ int32_t omni_higgs_undelay(const int32_t* rows, int32_t n_rows, int32_t* frames)
   for (int t = 0; t < n; ++t)
     for (int b = 0; b < OMNI_HIGGS_BOOKS; ++b) frames[t * OMNI_HIGGS_BOOKS + b] = rows[(t + b) * OMNI_HIGGS_BOOKS + b];
   return n;
+}
+
+// ---- streaming codec decoder ---------------------------------------------------------------------------------------
+
+int32_t omni_op_codec_rvq(omni_ops* c, const int32_t* codes, const void* books, void* out, int32_t n, int32_t half,
+                          int32_t book_rows) {
+  if (!c || !codes || !books || !out || half % 8) return OMNI_ERR_INVALID;
+  OPS_CUDA(c, launch_codec_rvq(codes, (const bf16*)books, (bf16*)out, n, half, book_rows, c->stream));
+  return OMNI_OK;
+}
+
+int32_t omni_op_codec_add_norm(omni_ops* c, const void* add, int64_t add_stride, void* res, const void* w, void* out,
+                               int32_t rows, int32_t dim, float eps) {
+  if (!c || !add || !res || !w || !out || dim % 256 || dim > 1024) return OMNI_ERR_INVALID;
+  OPS_CUDA(c, launch_codec_add_norm((const bf16*)add, add_stride, (bf16*)res, (const bf16*)w, (bf16*)out, rows, dim, eps,
+                                    c->stream));
+  return OMNI_OK;
+}
+
+int32_t omni_op_codec_window_attend(omni_ops* c, const void* qkv, void* state, const int32_t* lines, const int32_t* pos,
+                                    int64_t stride, int64_t ring_offset, void* out, int32_t n, int32_t heads, float theta) {
+  if (!c || !qkv || !state || !lines || !pos || !out) return OMNI_ERR_INVALID;
+  OPS_CUDA(c, launch_codec_window_attend((const bf16*)qkv, CodecStateRef{(char*)state, lines, pos, stride}, ring_offset,
+                                         (bf16*)out, n, heads, theta, c->stream));
+  return OMNI_OK;
+}
+
+int32_t omni_op_codec_bias_gelu(omni_ops* c, void* x, const void* bias, int64_t rows, int32_t cols) {
+  if (!c || !x || !bias || cols % 8) return OMNI_ERR_INVALID;
+  OPS_CUDA(c, launch_codec_bias_gelu((bf16*)x, (const bf16*)bias, rows, cols, c->stream));
+  return OMNI_OK;
+}
+
+int32_t omni_op_codec_bias_snake(omni_ops* c, const void* x, const void* bias, const float* alpha, const float* inv_b,
+                                 void* out, int64_t rows, int32_t cols) {
+  if (!c || !x || !bias || !alpha || !inv_b || !out || cols % 8) return OMNI_ERR_INVALID;
+  OPS_CUDA(c, launch_codec_bias_snake((const bf16*)x, (const bf16*)bias, alpha, inv_b, (bf16*)out, rows, cols, c->stream));
+  return OMNI_OK;
+}
+
+int32_t omni_op_codec_stage(omni_ops* c, const void* x, const void* bias, const float* alpha, const float* inv_b,
+                            void* state, const int32_t* lines, const int32_t* pos, int64_t stride, int64_t hist_offset,
+                            void* padded, int32_t n, int32_t T, int32_t C, int32_t H) {
+  if (!c || !x || !bias || !state || !lines || !pos || !padded || C % 8 || (alpha != nullptr) != (inv_b != nullptr))
+    return OMNI_ERR_INVALID;
+  OPS_CUDA(c, launch_codec_stage((const bf16*)x, (const bf16*)bias, alpha, inv_b, CodecStateRef{(char*)state, lines, pos, stride},
+                                 hist_offset, (bf16*)padded, n, T, C, H, c->stream));
+  return OMNI_OK;
+}
+
+int32_t omni_op_codec_gather_taps(omni_ops* c, const void* padded, void* col, int32_t n, int32_t T, int32_t C,
+                                  int32_t taps, int32_t dil) {
+  if (!c || !padded || !col || C % 8) return OMNI_ERR_INVALID;
+  OPS_CUDA(c, launch_codec_gather_taps((const bf16*)padded, (bf16*)col, n, T, C, taps, dil, c->stream));
+  return OMNI_OK;
+}
+
+int32_t omni_op_codec_conv(omni_ops* c, const void* w, int32_t N, int32_t C, int32_t taps, int32_t dil, const void* padded,
+                           int32_t T, int32_t n_streams, void* y, int32_t epilogue, const void* bias, const float* alpha,
+                           const float* inv_b) {
+  if (!c || !w || !padded || !y || epilogue < 0 || epilogue > 2) return OMNI_ERR_INVALID;
+  if (epilogue == kConvBiasSnake && (!bias || !alpha || !inv_b)) return OMNI_ERR_INVALID;
+  conv_configure();
+  ConvGemmPlan plan;
+  const int rc = conv_plan(&plan, (const bf16*)w, N, C, taps, dil, (const bf16*)padded, T, n_streams, (bf16*)y, epilogue,
+                           (const bf16*)bias, alpha, inv_b, c->sm_count);
+  if (rc != 0) return c->fail(OMNI_ERR_UNSUPPORTED, "conv plan refused (%d): N=%d C=%d taps=%d T=%d", rc, N, C, taps, T);
+  OPS_CUDA(c, conv_launch(plan, c->err, c->stream));
+  return OMNI_OK;
+}
+
+int32_t omni_op_codec_overlap_add(omni_ops* c, const void* z, const void* bias, void* state, const int32_t* lines,
+                                  const int32_t* pos, int64_t stride, int64_t prev_offset, void* out, int32_t n, int32_t L,
+                                  int32_t r, int32_t C) {
+  if (!c || !z || !bias || !state || !lines || !out || C % 8) return OMNI_ERR_INVALID;
+  OPS_CUDA(c, launch_codec_overlap_add((const bf16*)z, (const bf16*)bias, CodecStateRef{(char*)state, lines, pos, stride},
+                                       prev_offset, (bf16*)out, n, L, r, C, c->stream));
+  return OMNI_OK;
+}
+
+int32_t omni_op_codec_dwconv_ln(omni_ops* c, const void* z, const void* zb, const void* w, const void* b, const void* ln_w,
+                                const void* ln_b, void* state, const int32_t* lines, const int32_t* pos, int64_t stride,
+                                int64_t hist_offset, void* xin, void* out, int32_t n, int32_t T, int32_t r, int32_t C,
+                                float eps) {
+  if (!c || !z || !zb || !w || !b || !ln_w || !ln_b || !state || !lines || !pos || !xin || !out || C % 8 || C > 8192)
+    return OMNI_ERR_INVALID;
+  OPS_CUDA(c, launch_codec_dwconv_ln((const bf16*)z, (const bf16*)zb, (const bf16*)w, (const bf16*)b, (const bf16*)ln_w,
+                                     (const bf16*)ln_b, CodecStateRef{(char*)state, lines, pos, stride}, hist_offset,
+                                     (bf16*)xin, (bf16*)out, n, T, r, C, eps, c->stream));
+  return OMNI_OK;
+}
+
+int32_t omni_op_codec_out_conv(omni_ops* c, const void* x, const void* bias, const float* alpha, const float* inv_b,
+                               const void* w, const void* wb, void* state, const int32_t* lines, const int32_t* pos,
+                               int64_t stride, int64_t hist_offset, float* wav, int32_t n, int32_t T, int32_t C) {
+  if (!c || !x || !bias || !alpha || !inv_b || !w || !wb || !state || !lines || !pos || !wav || T % 64 || C % 32 || C > 128)
+    return OMNI_ERR_INVALID;
+  OPS_CUDA(c, launch_codec_out_conv((const bf16*)x, (const bf16*)bias, alpha, inv_b, (const bf16*)w, (const bf16*)wb,
+                                    CodecStateRef{(char*)state, lines, pos, stride}, hist_offset, wav, n, T, C, c->stream));
+  return OMNI_OK;
 }
 
 }  // extern "C"

@@ -137,6 +137,18 @@ SYMBOLS = {
     "omni_op_lm_advance": (I32, [VP, VP, VP, C.c_int64, VP, VP, VP, VP, VP, I32]),
     "omni_op_higgs_frame_embed": (I32, [VP, VP, VP, C.c_int64, VP, VP, I32, I32, I32]),
     "omni_op_higgs_sample": (I32, [VP, VP, I32, C.c_float, I32, VP, VP, VP, VP, C.c_int64, VP, I32]),
+    "omni_op_codec_rvq": (I32, [VP, VP, VP, VP, I32, I32, I32]),
+    "omni_op_codec_add_norm": (I32, [VP, VP, C.c_int64, VP, VP, VP, I32, I32, C.c_float]),
+    "omni_op_codec_window_attend": (I32, [VP, VP, VP, VP, VP, C.c_int64, C.c_int64, VP, I32, I32, C.c_float]),
+    "omni_op_codec_bias_gelu": (I32, [VP, VP, VP, C.c_int64, I32]),
+    "omni_op_codec_bias_snake": (I32, [VP, VP, VP, VP, VP, VP, C.c_int64, I32]),
+    "omni_op_codec_stage": (I32, [VP, VP, VP, VP, VP, VP, VP, VP, C.c_int64, C.c_int64, VP, I32, I32, I32, I32]),
+    "omni_op_codec_gather_taps": (I32, [VP, VP, VP, I32, I32, I32, I32, I32]),
+    "omni_op_codec_conv": (I32, [VP, VP, I32, I32, I32, I32, VP, I32, I32, VP, I32, VP, VP, VP]),
+    "omni_op_codec_overlap_add": (I32, [VP, VP, VP, VP, VP, VP, C.c_int64, C.c_int64, VP, I32, I32, I32, I32]),
+    "omni_op_codec_dwconv_ln": (I32, [VP, VP, VP, VP, VP, VP, VP, VP, VP, VP, C.c_int64, C.c_int64, VP, VP, I32, I32, I32,
+                                      I32, C.c_float]),
+    "omni_op_codec_out_conv": (I32, [VP, VP, VP, VP, VP, VP, VP, VP, VP, VP, C.c_int64, C.c_int64, VP, I32, I32, I32]),
     "omni_higgs_delay_forced_from": (I32, [P(HiggsDelay)]),
     "omni_higgs_delay_advance": (I32, [P(HiggsDelay), I32]),
     "omni_higgs_undelay": (I32, [P(I32), I32, P(I32)]),

@@ -135,6 +135,58 @@ class Ops:
         self._check(self._lib.omni_op_higgs_sample(self._h, _p(logits), vocab, temperature, top_k, _p(uniforms),
                                                    _p(force), _p(state), _p(lines), stride, _p(codes), rows))
 
+    # ---- streaming codec decoder (state: a byte tensor; lines / pos: int32 tensors, one entry per stream) ----
+    def codec_rvq(self, codes, books, out, book_rows):
+        n, dim = out.shape
+        self._check(self._lib.omni_op_codec_rvq(self._h, _p(codes), _p(books), _p(out), n, dim // 2, book_rows))
+
+    def codec_add_norm(self, add, res, w, out, eps):
+        rows, dim = res.shape
+        stride = 0 if add.dim() == 1 else dim
+        self._check(self._lib.omni_op_codec_add_norm(self._h, _p(add), stride, _p(res), _p(w), _p(out), rows, dim, eps))
+
+    def codec_window_attend(self, qkv, state, lines, pos, stride, ring_offset, out, heads, theta):
+        self._check(self._lib.omni_op_codec_window_attend(self._h, _p(qkv), _p(state), _p(lines), _p(pos), stride,
+                                                          ring_offset, _p(out), qkv.shape[0], heads, theta))
+
+    def codec_bias_gelu(self, x, bias):
+        rows, cols = x.shape
+        self._check(self._lib.omni_op_codec_bias_gelu(self._h, _p(x), _p(bias), rows, cols))
+
+    def codec_bias_snake(self, x, bias, alpha, inv_b, out):
+        rows, cols = x.shape
+        self._check(self._lib.omni_op_codec_bias_snake(self._h, _p(x), _p(bias), _p(alpha), _p(inv_b), _p(out), rows, cols))
+
+    def codec_stage(self, x, bias, alpha, inv_b, state, lines, pos, stride, hist_offset, padded, n, T, H):
+        C = x.shape[-1]
+        self._check(self._lib.omni_op_codec_stage(self._h, _p(x), _p(bias), _p(alpha) if alpha is not None else None,
+                                                  _p(inv_b) if inv_b is not None else None, _p(state), _p(lines), _p(pos),
+                                                  stride, hist_offset, _p(padded), n, T, C, H))
+
+    def codec_gather_taps(self, padded, col, n, T, C, taps, dil):
+        self._check(self._lib.omni_op_codec_gather_taps(self._h, _p(padded), _p(col), n, T, C, taps, dil))
+
+    def codec_conv(self, w, C, taps, dil, padded, T, n, y, epilogue=0, bias=None, alpha=None, inv_b=None):
+        opt = lambda t: _p(t) if t is not None else None
+        self._check(self._lib.omni_op_codec_conv(self._h, _p(w), w.shape[0], C, taps, dil, _p(padded), T, n, _p(y), epilogue,
+                                                 opt(bias), opt(alpha), opt(inv_b)))
+
+    def codec_overlap_add(self, z, bias, state, lines, pos, stride, prev_offset, out, n, L, r, C):
+        self._check(self._lib.omni_op_codec_overlap_add(self._h, _p(z), _p(bias), _p(state), _p(lines), _p(pos), stride,
+                                                        prev_offset, _p(out), n, L, r, C))
+
+    def codec_dwconv_ln(self, z, zb, w, b, ln_w, ln_b, state, lines, pos, stride, hist_offset, xin, out, n, T, r, eps):
+        C = xin.shape[-1]
+        self._check(self._lib.omni_op_codec_dwconv_ln(self._h, _p(z), _p(zb), _p(w), _p(b), _p(ln_w), _p(ln_b), _p(state),
+                                                      _p(lines), _p(pos), stride, hist_offset, _p(xin), _p(out), n, T, r, C,
+                                                      eps))
+
+    def codec_out_conv(self, x, bias, alpha, inv_b, w, wb, state, lines, pos, stride, hist_offset, wav, n, T):
+        C = x.shape[-1]
+        self._check(self._lib.omni_op_codec_out_conv(self._h, _p(x), _p(bias), _p(alpha), _p(inv_b), _p(w), _p(wb),
+                                                     _p(state), _p(lines), _p(pos), stride, hist_offset, _p(wav), n, T, C))
+
+
 def gemm_noalloc(w, x, y, splits=0, bias=None, epilogue=0, stream=None):
     """`omni_op_gemm_noalloc`: the tensor-core GEMM with its split-K scratch inside the library image, for callers
     that cannot allocate device memory (no context object, no cudaMalloc). Waits for the result; raises OpsError
