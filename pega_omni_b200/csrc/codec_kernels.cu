@@ -345,17 +345,19 @@ __global__ void codec_dwconv_ln_kernel(const bf16* __restrict__ z, const bf16* _
 constexpr int kOutTile = 64;  // output samples per block
 
 // A block of 256 per (64 samples, stream): the 70 rows the tile needs are transformed once into shared memory (f32
-// values of their bf16 roundings), then four threads share a sample, each over a quarter of the channels.
+// values of their bf16 roundings). A thread then sums four consecutive samples over a sixteenth of the channels: per
+// channel it reads ten rows and seven weights for 28 multiply-adds, and sixteen lanes reduce. Rows are C + 4 floats
+// apart, so the two row groups a warp reads (four rows apart) fall into opposite halves of the banks.
 __global__ void __launch_bounds__(256)
     codec_out_conv_kernel(const bf16* __restrict__ x, const bf16* __restrict__ bias, const float* __restrict__ alpha,
                           const float* __restrict__ inv_b, const bf16* __restrict__ w, const bf16* __restrict__ wb,
                           CodecStateRef st, int64_t hist_offset, float* __restrict__ wav, int T, int C) {
-  constexpr int H = kTaps - 1;
-  extern __shared__ float out_smem[];
-  float* sx = out_smem;                          // [64 + 6][C + 1]
-  float* sw = out_smem + (kOutTile + H) * (C + 1);  // [7][C]
+  constexpr int H = kTaps - 1, kPer = 4;  // samples per thread
+  extern __shared__ __align__(16) float out_smem[];
+  const int ld = C + 4, per = C / 8;
+  float* sx = out_smem;                        // [64 + 6][C + 4]
+  float* sw = out_smem + (kOutTile + H) * ld;  // [7][C]
   const int s = blockIdx.y, t0 = blockIdx.x * kOutTile, tid = threadIdx.x;
-  const int ld = C + 1, per = C / 8;
   const int p = st.pos[s];
   bf16* hist = slot_ptr(st, s, hist_offset);
   const bf16* old = hist + (p & 1) * (int64_t)H * C;
@@ -374,18 +376,30 @@ __global__ void __launch_bounds__(256)
       // the frame's last six rows are the next history; rows below the tile's own (row < H) belong to the tile before
       if (src >= T - H && row >= H) st8v(next + (int64_t)(src - (T - H)) * C + c, v);
     }
-#pragma unroll
-    for (int k = 0; k < 8; ++k) sx[row * ld + c + k] = v[k];
+    float4* dst = reinterpret_cast<float4*>(sx + row * ld + c);
+    dst[0] = make_float4(v[0], v[1], v[2], v[3]);
+    dst[1] = make_float4(v[4], v[5], v[6], v[7]);
   }
   __syncthreads();
-  const int o = tid >> 2, q = tid & 3;
-  float acc = 0.f;
-  for (int j = 0; j < kTaps; ++j)
-    for (int c = q; c < C; c += 4) acc += sx[(o + j) * ld + c] * sw[j * C + c];
-  acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-  acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-  if (q == 0)
-    wav[(int64_t)s * T + t0 + o] = fminf(1.f, fmaxf(-1.f, bf16_round(acc + __bfloat162float(wb[0]))));
+  const int q = tid & 15, rg = tid >> 4;  // channels q, q + 16, ...; samples rg * 4 .. rg * 4 + 3
+  float acc[kPer] = {0.f, 0.f, 0.f, 0.f};
+  for (int c = q; c < C; c += 16) {
+    float v[kPer + H], wt[kTaps];
+#pragma unroll
+    for (int i = 0; i < kPer + H; ++i) v[i] = sx[(rg * kPer + i) * ld + c];
+#pragma unroll
+    for (int j = 0; j < kTaps; ++j) wt[j] = sw[j * C + c];
+#pragma unroll
+    for (int j = 0; j < kTaps; ++j)
+#pragma unroll
+      for (int o = 0; o < kPer; ++o) acc[o] += v[o + j] * wt[j];
+  }
+#pragma unroll
+  for (int o = 0; o < kPer; ++o)
+#pragma unroll
+    for (int m = 1; m < 16; m <<= 1) acc[o] += __shfl_xor_sync(0xffffffffu, acc[o], m);
+  if (q < kPer)
+    wav[(int64_t)s * T + t0 + rg * kPer + q] = fminf(1.f, fmaxf(-1.f, bf16_round(acc[q] + __bfloat162float(wb[0]))));
 }
 
 inline unsigned blocks_for(int64_t total, int threads) { return (unsigned)((total + threads - 1) / threads); }
@@ -462,7 +476,7 @@ cudaError_t launch_codec_dwconv_ln(const bf16* z, const bf16* zb, const bf16* w,
 cudaError_t launch_codec_out_conv(const bf16* x, const bf16* bias, const float* alpha, const float* inv_b, const bf16* w,
                                   const bf16* wb, CodecStateRef st, int64_t hist_offset, float* wav, int n, int T, int C,
                                   cudaStream_t stream) {
-  const size_t smem = ((size_t)(kOutTile + kTaps - 1) * (C + 1) + (size_t)kTaps * C) * sizeof(float);
+  const size_t smem = ((size_t)(kOutTile + kTaps - 1) * (C + 4) + (size_t)kTaps * C) * sizeof(float);
   codec_out_conv_kernel<<<dim3(T / kOutTile, n), 256, smem, stream>>>(x, bias, alpha, inv_b, w, wb, st, hist_offset, wav,
                                                                       T, C);
   return cudaGetLastError();
