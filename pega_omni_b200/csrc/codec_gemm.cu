@@ -25,11 +25,12 @@ namespace {
 
 constexpr int kConvK = 64;        // channels per k-block: one 128-byte swizzle row
 constexpr int kConvRows = 128;    // output rows per tile
-constexpr int kConvRing = 200 * 1024;
+constexpr int kConvRing = 184 * 1024;
 constexpr int kConvMaxStages = 8;
-constexpr int kConvThreads = 192; // warp 0 producer, warp 1 MMA issuer, warps 2..5 epilogue
+constexpr int kConvEpilogueWarps = 8;  // two per TMEM lane quadrant, each taking every other 32-channel step
+constexpr int kConvThreads = 64 + 32 * kConvEpilogueWarps;  // warp 0 producer, warp 1 MMA issuer, the rest epilogue
 constexpr int kStagePitch = 36;   // floats per row of an epilogue warp's 32 x 32 staging block (16-byte aligned, conflict-free)
-constexpr size_t kConvSmem = (size_t)kConvRing + 1024 + 256 + 4 * 32 * kStagePitch * sizeof(float);
+constexpr size_t kConvSmem = (size_t)kConvRing + 1024 + 256 + kConvEpilogueWarps * 32 * kStagePitch * sizeof(float);
 
 struct ConvArgs {
   bf16* y;
@@ -73,7 +74,7 @@ __global__ void __launch_bounds__(kConvThreads, 1)
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(acc_full(b), 1);
-      mbar_init(acc_empty(b), 4);  // one arrival per epilogue warp
+      mbar_init(acc_empty(b), kConvEpilogueWarps);  // one arrival per epilogue warp
     }
     mbar_init_fence();
     prefetch_tensormap(&xmap);
@@ -150,7 +151,7 @@ __global__ void __launch_bounds__(kConvThreads, 1)
     // cost one memory transaction per thread and 16 bytes; instead the 32 x 32 f32 block goes through shared memory
     // and comes back with four lanes per row (8 channels each), so that a warp instruction covers 8 rows x 64 bytes.
     // The old values of an accumulating GEMM, the bias and the SnakeBeta parameters are read in that layout too.
-    const int quad = warp & 3;
+    const int quad = warp & 3, half = (warp - 2) >> 2;  // this warp's steps: c0 / 32 odd or even
     float* stg = reinterpret_cast<float*>(base_ptr + kConvRing + 256) + (warp - 2) * (32 * kStagePitch);
     const int sub_row = lane >> 2, chunk = lane & 3;
     int use = 0;
@@ -171,7 +172,7 @@ __global__ void __launch_bounds__(kConvThreads, 1)
       if (!alive) break;
       tc_fence_after_sync();
 #pragma unroll 1
-      for (int c0 = 0; c0 < a.tn; c0 += 32) {
+      for (int c0 = 32 * half; c0 < a.tn; c0 += 32 * (kConvEpilogueWarps / 4)) {
         uint32_t r0[16], r1[16];
         const bool second = c0 + 16 < a.tn;  // tn is a multiple of 16: the last step may hold one half only
         tmem_ld16_issue(lane_addr + c0, r0);  // warp-wide: every lane takes part whether or not its row is live
@@ -190,11 +191,6 @@ __global__ void __launch_bounds__(kConvThreads, 1)
             if (rows[i]) old[i] = *reinterpret_cast<const uint4*>(rows[i] + nn);
         }
         tmem_ld_fence(r0, r1);
-        if (c0 + 32 >= a.tn) {  // the accumulator is in registers: the MMA issuer may start the tile after next
-          tc_fence_before_sync();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(acc_empty(buf));
-        }
         uint4* mine = reinterpret_cast<uint4*>(stg + lane * kStagePitch);
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
@@ -231,6 +227,10 @@ __global__ void __launch_bounds__(kConvThreads, 1)
         }
         __syncwarp();  // the block is read out before the next step overwrites it
       }
+      // this warp's part of the accumulator has been read (a warp without a step of its own arrives all the same)
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(acc_empty(buf));
     }
   }
   tc_fence_before_sync();
