@@ -145,8 +145,9 @@ int32_t omni_talker_seq_frames(const omni_seq* seq);
 
 /* Replaces `Model::start` (model.rs:153-177): prefill of `n` fresh sequences
  * (prompt rows concatenated in `text_ids` / `codec_ids`, codec id -1 = none)
- * and their first frame. codes: [n][16] i32. wav: [n][samples_per_frame] or
- * NULL; zero-filled (the waveform decoder is outside this library). */
+ * and their first frame. codes: [n][16] i32. wav: [n][1920] f32 or NULL: the
+ * frames' samples when a codec decoder is attached (omni_talker_attach_codec,
+ * include/omni_b200_codec.h), zero-filled otherwise. */
 int32_t omni_talker_start(omni_talker* m, int32_t n, omni_seq* const* seqs, const int32_t* text_ids,
                           const int32_t* codec_ids, const int32_t* prompt_lens, const omni_draw* draws,
                           int32_t* codes, float* wav);

@@ -6,8 +6,9 @@
  * Replaces the decoder that `codec::build` (crates/omni-qwen3-tts/src/codec.rs:112-448) emits into the tail of the
  * reference model's `first` and `decode` programs, and the kernels those calls launch
  * (crates/omni-qwen3-tts/kernels/codec.cu:66-513). In the reference the decoder shares a sequence's lease with the
- * talker (`Seq`); here it is a model of its own whose stream is opened next to the talker's sequence, and
- * `omni_codec_decode` takes the frame `omni_talker_step` returned. Weight layout transforms and scale folding happen on
+ * talker (`Seq`); here it is a model of its own: either attached to a talker model (`omni_talker_attach_codec`, after
+ * which the talker's calls open, decode and close its streams themselves), or driven by the caller, who opens a stream
+ * next to the talker's sequence and hands `omni_codec_decode` the frame `omni_talker_step` returned. Weight layout transforms and scale folding happen on
  * the host at create, as `build` does at load.
  *
  * One model per GPU per thread; no internal locking; calls are synchronous. All functions return an omni_status
@@ -74,6 +75,14 @@ int32_t omni_codec_warmup(omni_codec* m);
  * Every stream advances by one frame. Streams must be distinct. The rows between n and its bucket run on the padding
  * slot. */
 int32_t omni_codec_decode(omni_codec* m, int32_t n, omni_codec_stream* const* streams, const int32_t* codes, float* wav);
+
+/* Puts the decoder behind a talker model (include/omni_b200.h), as `codec::build` appends it to the reference model's
+ * `first` and `decode` programs: from then on `omni_talker_open` / `omni_talker_close` also take and return a decoder
+ * slot, and `omni_talker_start`, `omni_talker_step` and `omni_talker_step_end` decode the frames they return and fill
+ * `wav` (`Out::wav`, 1,920 samples per sequence) instead of zero-filling it; the streams advance whether or not `wav` is
+ * given. The decoder must give 1,920 samples per frame and take at least the talker's batch; both models must be on
+ * one device. Attach (or detach, with NULL) while no sequence is open. `omni_talker_run_ticks` does not decode. */
+int32_t omni_talker_attach_codec(omni_talker* talker, omni_codec* codec);
 
 /* Samples per frame (the product of every rate). */
 int32_t omni_codec_samples_per_frame(const omni_codec* m);

@@ -19,6 +19,7 @@
 #include <vector>
 
 #include "../../include/omni_b200.h"
+#include "../../include/omni_b200_codec.h"
 #include "gemm.h"
 #include "kernels.h"
 #include "predictor.h"
@@ -126,6 +127,7 @@ struct omni_seq {
   int32_t prompt = 0, frames = 0, cap = 0;
   uint64_t seed = 0;
   bool live = false;
+  omni_codec_stream* audio = nullptr;  // the sequence's slot in the attached codec decoder
 };
 
 constexpr int kTraceMaxPhases = 1024;
@@ -212,8 +214,13 @@ struct omni_talker {
     int32_t* out_host = nullptr;
     cudaEvent_t start = nullptr, done = nullptr;
     int n = 0, launches = 0;
+    std::vector<omni_seq*> seqs;  // with a codec decoder attached: whose frames these are
   } flight[2];
   int flight_first = 0, in_flight = 0;
+  // the codec decoder that turns every frame into samples (omni_talker_attach_codec), or null: `wav` is zero-filled
+  omni_codec* codec = nullptr;
+  std::vector<float> wav_scratch;
+  std::vector<omni_codec_stream*> audio_rows;
 
   int fail(int code, const char* fmt, ...) {
     char buf[512];
@@ -1087,7 +1094,25 @@ void dump_trace(omni_talker* m) {
   fclose(f);
 }
 
-int finish_call(omni_talker* m, int n, int32_t* codes, float* wav) {
+// The frames' audio: with a codec decoder attached every frame of every sequence goes through it (its streams advance
+// whether or not the caller takes the samples); without one `wav` is zero-filled.
+int decode_audio(omni_talker* m, int n, omni_seq* const* seqs, const int32_t* codes, float* wav) {
+  if (!m->codec) {
+    if (wav) memset(wav, 0, (size_t)n * 1920 * sizeof(float));
+    return OMNI_OK;
+  }
+  if (!wav) {
+    m->wav_scratch.resize((size_t)n * 1920);
+    wav = m->wav_scratch.data();
+  }
+  m->audio_rows.resize(n);
+  for (int i = 0; i < n; ++i) m->audio_rows[i] = seqs[i]->audio;
+  const int rc = omni_codec_decode(m->codec, n, m->audio_rows.data(), codes, wav);
+  if (rc != OMNI_OK) return m->fail(rc, "codec decoder: %s", omni_codec_last_error(m->codec));
+  return OMNI_OK;
+}
+
+int finish_call(omni_talker* m, int n, omni_seq* const* seqs, int32_t* codes, float* wav) {
   CUDA_TRY(m, cudaMemcpyAsync(m->out_host, m->codes, ((size_t)m->max_seqs * OMNI_GROUPS + 1) * 4,
                               cudaMemcpyDeviceToHost, m->stream));
   CUDA_TRY(m, cudaEventRecord(m->ev1, m->stream));
@@ -1102,9 +1127,8 @@ int finish_call(omni_talker* m, int n, int32_t* codes, float* wav) {
     return m->fail(OMNI_ERR_DEVICE, "device error word 0x%x (1: barrier wait ran out, 2: index out of range)", err);
   }
   memcpy(codes, m->out_host, (size_t)n * OMNI_GROUPS * 4);
-  if (wav) memset(wav, 0, (size_t)n * 1920 * sizeof(float));
   m->last_n = n;
-  return OMNI_OK;
+  return decode_audio(m, n, seqs, codes, wav);
 }
 
 }  // namespace
@@ -1360,8 +1384,26 @@ int32_t omni_talker_open(omni_talker* m, int32_t prompt_tokens, int32_t max_fram
     m->pages_used -= need;
     return m->fail(OMNI_ERR_CUDA, "clearing the sequence slot: %s", cudaGetErrorString(e));
   }
+  if (m->codec) {  // the decoder's state slot travels with the lease
+    const int rc = omni_codec_open(m->codec, &s->audio);
+    if (rc != OMNI_OK) {
+      for (int32_t p : s->pages) m->free_pages.push_back(p);
+      m->free_lines.push_back(s->line);
+      m->pages_used -= need;
+      return rc == OMNI_DENIED_BUSY ? rc : m->fail(rc, "codec decoder: %s", omni_codec_last_error(m->codec));
+    }
+  }
   *out = s.get();
   m->seqs.push_back(std::move(s));
+  return OMNI_OK;
+}
+
+int32_t omni_talker_attach_codec(omni_talker* m, omni_codec* codec) {
+  if (!m) return OMNI_ERR_INVALID;
+  if (!m->seqs.empty() || m->in_flight > 0) return m->fail(OMNI_ERR_INVALID, "attach or detach the codec decoder while no sequence is open");
+  if (codec && omni_codec_samples_per_frame(codec) != 1920)
+    return m->fail(OMNI_ERR_UNSUPPORTED, "the codec decoder gives %d samples per frame, `wav` rows hold 1920", omni_codec_samples_per_frame(codec));
+  m->codec = codec;
   return OMNI_OK;
 }
 
@@ -1372,6 +1414,7 @@ int32_t omni_talker_close(omni_talker* m, omni_seq* seq) {
   for (size_t i = 0; i < m->seqs.size(); ++i) {
     if (m->seqs[i].get() != seq) continue;
     if (!seq->live) return OMNI_ERR_INVALID;
+    if (seq->audio && m->codec) omni_codec_close(m->codec, seq->audio);
     for (int32_t p : seq->pages) m->free_pages.push_back(p);
     m->free_lines.push_back(seq->line);
     m->pages_used -= (int)seq->pages.size();
@@ -1475,7 +1518,7 @@ int32_t omni_talker_start(omni_talker* m, int32_t n, omni_seq* const* seqs, cons
   TRY(run_program(m, kFirst, b));
   m->launches += prefill_launches;
   m->stats.bucket = b;
-  TRY(finish_call(m, n, codes, wav));
+  TRY(finish_call(m, n, seqs, codes, wav));
   for (int s = 0; s < n; ++s) seqs[s]->frames = 1;
   return OMNI_OK;
 }
@@ -1513,7 +1556,7 @@ int32_t omni_talker_step(omni_talker* m, int32_t n, omni_seq* const* seqs, const
   CUDA_TRY(m, cudaMemcpyAsync(m->in_dev, m->in_host, bytes, cudaMemcpyHostToDevice, m->stream));
   TRY(run_program(m, kDecode, b));
   m->stats.bucket = b;
-  TRY(finish_call(m, n, codes, wav));
+  TRY(finish_call(m, n, seqs, codes, wav));
   for (int s = 0; s < n; ++s) seqs[s]->frames += 1;
   return OMNI_OK;
 }
@@ -1543,6 +1586,7 @@ int32_t omni_talker_step_begin(omni_talker* m, int32_t n, omni_seq* const* seqs,
   CUDA_TRY(m, cudaEventRecord(f.done, m->stream));
   f.n = n;
   f.launches = m->launches;
+  if (m->codec) f.seqs.assign(seqs, seqs + n);
   m->in_flight += 1;
   for (int s = 0; s < n; ++s) seqs[s]->frames += 1;  // the next step_begin computes its positions from these
   return OMNI_OK;
@@ -1569,9 +1613,8 @@ int32_t omni_talker_step_end(omni_talker* m, int32_t* codes, float* wav) {
     return m->fail(OMNI_ERR_DEVICE, "device error word 0x%x (1: barrier wait ran out, 2: index out of range)", err);
   }
   memcpy(codes, f.out_host, (size_t)f.n * OMNI_GROUPS * 4);
-  if (wav) memset(wav, 0, (size_t)f.n * 1920 * sizeof(float));
   m->last_n = f.n;
-  return OMNI_OK;
+  return decode_audio(m, f.n, f.seqs.data(), codes, wav);
 }
 
 int32_t omni_talker_run_ticks(omni_talker* m, int32_t n, omni_seq* const* seqs, int32_t ticks, const omni_draw* draws,

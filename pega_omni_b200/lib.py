@@ -173,6 +173,7 @@ SYMBOLS = {
     "omni_codec_warmup": (I32, [VP]),
     "omni_codec_decode": (I32, [VP, I32, P(VP), P(I32), P(C.c_float)]),
     "omni_codec_stats": (I32, [VP, P(C.c_float), P(I32)]),
+    "omni_talker_attach_codec": (I32, [VP, VP]),
     "omni_duplex_create": (I32, [P(DuplexCfg), P(Tensor), I32, I32, P(VP)]),
     "omni_duplex_destroy": (None, [VP]),
     "omni_duplex_last_error": (C.c_char_p, [VP]),

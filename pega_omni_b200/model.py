@@ -187,6 +187,12 @@ class Model:
         self._check(rc)
         return Seq(self, h, prompt)
 
+    def attach_codec(self, codec) -> None:
+        """Puts a `pega_omni_b200.codec.Codec` behind this model (`omni_talker_attach_codec`): `start` / `step` then
+        return the frames' samples in `Out.wav` as the reference's `first` / `decode` programs do. None detaches."""
+        self._check(self._lib.omni_talker_attach_codec(self._h, codec._m if codec is not None else None))
+        self._codec = codec  # kept alive as long as it is attached
+
     def release(self, seq: Seq) -> None:
         """Dropping a `Seq`: its lease returns to the pool."""
         self._check(self._lib.omni_talker_close(self._h, seq._h))

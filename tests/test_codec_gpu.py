@@ -113,3 +113,44 @@ def test_unsupported_shapes_are_refused(built_lib):
     with pytest.raises(OmniError) as e:
         Codec(c, codec_random_checkpoint(c, 0), max_batch=1)
     assert e.value.status == -5
+
+
+def test_attached_decoder_fills_wav_of_start_and_step(built_lib):
+    """`Out.wav` through the talker's own calls (what the reference's `first` / `decode` programs return): the samples
+    are the ones a decoder of its own gives for the same frames, bit for bit, also through step_begin / step_end."""
+    import dataclasses
+    from pega_omni_b200.config import presets
+    from pega_omni_b200.model import Draw, Limits, Model, Prompt
+    from pega_omni_b200.synthetic import random_checkpoint
+    cfg = presets["tiny128"]()
+    model = Model.load(0, random_checkpoint(cfg, seed=0, device="cuda"), cfg, Limits(max_batch=4, max_tokens=128, kv_gib=0.01))
+    cc = dataclasses.replace(CODEC_PRESETS["codec-mid"], codebook_size=2048)  # 1,920 samples per frame, 2048-entry books
+    ck = codec_random_checkpoint(cc, 0)
+    attached, apart = Codec(cc, ck, max_batch=4, streams=4), Codec(cc, ck, max_batch=4, streams=4)
+    model.attach_codec(attached)
+    rng = np.random.default_rng(3)
+    lens = [9, 14, 11]
+    prompts = [Prompt(list(rng.integers(0, cfg.text_vocab_size, n)), [-1] * n) for n in lens]
+    seqs = [model.open(n, 8) for n in lens]
+    streams = [apart.open() for _ in lens]
+    draws = lambda: [Draw(list(rng.random(16).astype(np.float32))) for _ in lens]
+    out = model.start(list(zip(seqs, prompts, draws())))
+    frames = [(out.codes.copy(), out.wav.copy())]
+    for _ in range(2):
+        out = model.step(list(zip(seqs, draws())))
+        frames.append((out.codes.copy(), out.wav.copy()))
+    model.step_begin(seqs, draws())
+    out = model.step_end(len(seqs))
+    frames.append((out.codes.copy(), out.wav.copy()))
+    for codes, wav in frames:
+        assert np.abs(wav).max() > 0 and np.abs(wav).max() <= 1.0
+        want = apart.decode(streams, codes)
+        assert np.array_equal(wav, want)
+    with pytest.raises(OmniError):
+        model.attach_codec(None)  # sequences are open
+    for s in seqs:
+        model.release(s)
+    model.attach_codec(None)
+    model.close()
+    attached.close()
+    apart.close()
