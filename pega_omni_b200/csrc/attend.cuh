@@ -62,13 +62,13 @@ struct KvBlock {
   static constexpr int LPT = D / 8;           // lanes per key row
   static constexpr int TPI = 32 / LPT;        // key rows per load instruction
   static constexpr int NI = 16 / TPI;         // load instructions per K block
-  Pack8 k[NI];
+  uint4 k[NI];  // loaded as 16-byte words: one request per lane and instruction
   uint2 v[16];
   // `block`: the K rows, then the V rows (global or shared memory)
   __device__ __forceinline__ void load(const bf16* block, int lane) {
     const bf16* vrows = block + 16 * D;
 #pragma unroll
-    for (int c = 0; c < NI; ++c) k[c] = *reinterpret_cast<const Pack8*>(block + (c * 32 + lane) * 8);
+    for (int c = 0; c < NI; ++c) k[c] = *reinterpret_cast<const uint4*>(block + (c * 32 + lane) * 8);
 #pragma unroll
     for (int j = 0; j < 16; ++j) {
       if constexpr (PV == 4)
@@ -99,7 +99,7 @@ __device__ __forceinline__ void page_update(const KvBlock<D>& blk, const float (
 #pragma unroll
   for (int c = 0; c < NI; ++c) {
     float kf[8];
-    unpack8(blk.k[c], kf);
+    unpack8v(blk.k[c], kf);
 #pragma unroll
     for (int g = 0; g < G; ++g) {
       float part = 0.f;

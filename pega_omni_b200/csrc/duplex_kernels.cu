@@ -49,7 +49,7 @@ __global__ void lm_embed_ids_kernel(const int32_t* __restrict__ ids, const int32
       v = 0;
     }
     const int c = threadIdx.x * 8;
-    *reinterpret_cast<Pack8*>(out + r * dim + c) = *reinterpret_cast<const Pack8*>(voices + (int64_t)v * dim + c);
+    *reinterpret_cast<uint4*>(out + r * dim + c) = *reinterpret_cast<const uint4*>(voices + (int64_t)v * dim + c);
     return;
   }
   embed_row(ids + r * kDuplexStreams, t, out + r * dim, dim, err);

@@ -562,7 +562,7 @@ __global__ void __launch_bounds__(kThreads, 1) pred_kernel(const __grid_constant
               const bf16* table = (const bf16*)e.p0;
               bf16* dst = (bf16*)e.q1 + (int64_t)s * a.cfg.next_stride;
               for (int k = ctid * 8; k < e.next_dim; k += kConsumers * 8)
-                *reinterpret_cast<Pack8*>(dst + k) = *reinterpret_cast<const Pack8*>(table + (int64_t)token * e.next_dim + k);
+                *reinterpret_cast<uint4*>(dst + k) = *reinterpret_cast<const uint4*>(table + (int64_t)token * e.next_dim + k);
             }
             ConsumerSync::sync();
           }

@@ -17,8 +17,8 @@ __global__ void gather_kernel(const int32_t* __restrict__ ids, int stride, const
     if (threadIdx.x == 0) raise(err, kErrBadIndex);
     id = 0;
   }
-  *reinterpret_cast<Pack8*>(out + (int64_t)blockIdx.x * dim + c) =
-      *reinterpret_cast<const Pack8*>(table + id * dim + c);
+  *reinterpret_cast<uint4*>(out + (int64_t)blockIdx.x * dim + c) =
+      *reinterpret_cast<const uint4*>(table + id * dim + c);
 }
 
 // `talker_prompt_codec` (talker.cu:55-71): x + bias (+ codec embedding), one rounding.
@@ -96,7 +96,7 @@ __global__ void pred_input_kernel(const bf16* __restrict__ hidden, const bf16* _
     }
     src = codec_emb + (int64_t)id * dim;
   }
-  *reinterpret_cast<Pack8*>(out + ((int64_t)2 * s + blockIdx.y) * dim + c) = *reinterpret_cast<const Pack8*>(src + c);
+  *reinterpret_cast<uint4*>(out + ((int64_t)2 * s + blockIdx.y) * dim + c) = *reinterpret_cast<const uint4*>(src + c);
 }
 
 cudaError_t launch_gather(const int32_t* ids, int stride, const bf16* table, int table_rows, bf16* out, int rows,

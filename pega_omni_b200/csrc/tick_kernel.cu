@@ -795,17 +795,17 @@ __device__ __noinline__ void phase_sample(const Phase& ph, const TickIo& io, con
       const bf16 *table = (const bf16*)ph.src0, *hidden = (const bf16*)ph.src1;
       bf16* dst = (bf16*)ph.dst1;
       for (int i = wtid * 8; i < dim; i += kWorkerThreads * 8) {
-        *reinterpret_cast<Pack8*>(dst + ((int64_t)2 * row) * dim + i) =
-            *reinterpret_cast<const Pack8*>(hidden + (int64_t)row * dim + i);
-        *reinterpret_cast<Pack8*>(dst + ((int64_t)2 * row + 1) * dim + i) =
-            *reinterpret_cast<const Pack8*>(table + (int64_t)token * dim + i);
+        *reinterpret_cast<uint4*>(dst + ((int64_t)2 * row) * dim + i) =
+            *reinterpret_cast<const uint4*>(hidden + (int64_t)row * dim + i);
+        *reinterpret_cast<uint4*>(dst + ((int64_t)2 * row + 1) * dim + i) =
+            *reinterpret_cast<const uint4*>(table + (int64_t)token * dim + i);
       }
     } else if (ph.i8 == kNextCode) {
       const bf16* table = (const bf16*)ph.src0;
       bf16* dst = (bf16*)ph.dst1;
       for (int i = wtid * 8; i < dim; i += kWorkerThreads * 8)
-        *reinterpret_cast<Pack8*>(dst + (int64_t)row * dim + i) =
-            *reinterpret_cast<const Pack8*>(table + (int64_t)token * dim + i);
+        *reinterpret_cast<uint4*>(dst + (int64_t)row * dim + i) =
+            *reinterpret_cast<const uint4*>(table + (int64_t)token * dim + i);
     } else if (ph.i8 == kNextProjected && wtid < kGroupThreads) {
       // the next pass's first attention phase reads the code's q | k | v row (src1, i11 bytes): ask it into L2 now
       if (wtid == 0 && ph.src1) sm100::prefetch_l2((const char*)ph.src1 + (int64_t)token * ph.i11, (uint32_t)ph.i11);
