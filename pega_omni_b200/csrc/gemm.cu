@@ -40,12 +40,8 @@ __global__ void __launch_bounds__(kGemvWarps * 32) gemv_kernel(const bf16* __res
     __syncthreads();
     for (int i = threadIdx.x; i < R * K / 8; i += blockDim.x) {
       const int r = i / (K / 8), c = i % (K / 8) * 8;
-      Pack8 p;
-      if (r0 + r < rows)
-        p = *reinterpret_cast<const Pack8*>(x + (int64_t)(r0 + r) * K + c);
-      else
-        memset(&p, 0, sizeof(p));
-      *reinterpret_cast<Pack8*>(xs + r * K + c) = p;
+      *reinterpret_cast<uint4*>(xs + r * K + c) =
+          r0 + r < rows ? *reinterpret_cast<const uint4*>(x + (int64_t)(r0 + r) * K + c) : make_uint4(0u, 0u, 0u, 0u);
     }
     __syncthreads();
     for (int j = 0; j < cols_per_warp; ++j) {
