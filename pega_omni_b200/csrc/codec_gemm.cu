@@ -153,7 +153,7 @@ __global__ void __launch_bounds__(kConvThreads, 1)
     // cost one memory transaction per thread and 16 bytes; instead the 32 x 32 f32 block goes through shared memory
     // and comes back with four lanes per row (8 channels each), so that a warp instruction covers 8 rows x 64 bytes.
     // The old values of an accumulating GEMM, the bias and the SnakeBeta parameters are read in that layout too.
-    const int quad = warp & 3, half = (warp - 2) >> 2;  // this warp's steps: c0 / 32 = half, half + 3, ...
+    const int quad = warp & 3, turn = (warp - 2) >> 2;  // this warp takes steps turn, turn + 3, ... of 32 channels
     float* stg = reinterpret_cast<float*>(base_ptr + kConvRing + 256) + (warp - 2) * (32 * kStagePitch);
     const int sub_row = lane >> 2, chunk = lane & 3;
     int use = 0;
@@ -174,7 +174,7 @@ __global__ void __launch_bounds__(kConvThreads, 1)
       if (!alive) break;
       tc_fence_after_sync();
 #pragma unroll 1
-      for (int c0 = 32 * half; c0 < a.tn; c0 += 32 * (kConvEpilogueWarps / 4)) {
+      for (int c0 = 32 * turn; c0 < a.tn; c0 += 32 * (kConvEpilogueWarps / 4)) {
         uint32_t r0[16], r1[16];
         const bool second = c0 + 16 < a.tn;  // tn is a multiple of 16: the last step may hold one half only
         tmem_ld16_issue(lane_addr + c0, r0);  // warp-wide: every lane takes part whether or not its row is live

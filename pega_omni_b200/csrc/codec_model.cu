@@ -763,7 +763,7 @@ int32_t omni_codec_warmup(omni_codec* m) {
   buckets.push_back(m->cfg.max_batch);
   for (int b : buckets)
     for (int pass = 0; pass < (m->cfg.use_graphs ? 2 : 1); ++pass) CTRY(decode_rows(m, 0, b, nullptr, nullptr, nullptr));
-  // the padding slot's history must read as zero again for nothing in particular, but keep it defined
+  // the padding slot starts from silence again (its audio is never read; this only keeps its values bounded)
   CCUDA(m, cudaMemsetAsync(m->state + (int64_t)m->pad_line * m->stride, 0, (size_t)m->stride, m->stream));
   return OMNI_OK;
 }
