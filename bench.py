@@ -628,7 +628,8 @@ def main():
     ap.add_argument("--prompt-max", type=int, default=0, help="sweep: prompt lengths uniform in [--prompt, --prompt-max]")
     ap.add_argument("--workload", default="talker", choices=["talker", "duplex", "higgs", "sweep", "attend", "codec"],
                     help="talker: the headline Qwen3-TTS tick (default); duplex: the PersonaPlex-7B tick (configs[3]); "
-                         "higgs: the Higgs-style 4B step (configs[4])")
+                         "higgs: the Higgs-style 4B step (configs[4]); codec: the streaming codec decoder, one frame of every stream per "
+                         "step; sweep: configs[2]; attend: the paged attention kernel alone")
     ap.add_argument("--context", type=int, default=3000, help="duplex: KV ring length")
     ap.add_argument("--no-codec", action="store_true", help="talker: skip the tick + codec decoder arm (with_codec)")
     ap.add_argument("--e2e-waited", action="store_true", help="talker: the end-to-end arm waits on every step (Model.step) "
