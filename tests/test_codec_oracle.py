@@ -77,3 +77,15 @@ def test_config_struct_matches_header(built_lib):
     from pega_omni_b200 import lib as L
     assert C.sizeof(L.CodecCfg) == 120
     assert L.CodecCfg.max_batch.offset == 108 and L.CodecCfg.upsample_rates.offset == 76
+
+
+def test_no_cpu_fallback_without_a_device(built_lib):
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a device is present")
+    from pega_omni_b200.codec import Codec
+    from pega_omni_b200.model import OmniError
+    c = CODEC_PRESETS["codec-tiny"]
+    with pytest.raises(OmniError) as e:
+        Codec(c, codec_random_checkpoint(c, 0), max_batch=1)
+    assert e.value.status == -2  # OMNI_ERR_CUDA: the decoder exists on the GPU only
