@@ -388,6 +388,9 @@ def run_codec(args, rank, world, local):
             "reference_published": "1.0 ms of the reference's 8.27 ms tick at 64 sessions is its codec decoder "
                                    "(docs/bench.md:156-160 of the reference, other hardware)"}))
     model.close()
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
 
 
 def run_duplex(args, rank, world, local):
