@@ -89,3 +89,20 @@ def test_no_cpu_fallback_without_a_device(built_lib):
     with pytest.raises(OmniError) as e:
         Codec(c, codec_random_checkpoint(c, 0), max_batch=1)
     assert e.value.status == -2  # OMNI_ERR_CUDA: the decoder exists on the GPU only
+
+
+def test_codec_entry_points_refuse_null_handles(built_lib):
+    """Argument checks run before anything touches a device, so they hold on a machine without one."""
+    lib = built_lib
+    INVALID = -1
+    assert lib.omni_codec_open(None, None) == INVALID
+    assert lib.omni_codec_close(None, None) == INVALID
+    assert lib.omni_codec_warmup(None) == INVALID
+    assert lib.omni_codec_decode(None, 1, None, None, None) == INVALID
+    assert lib.omni_codec_stats(None, None, None) == INVALID
+    assert lib.omni_codec_stream_frames(None) == -1
+    assert lib.omni_codec_samples_per_frame(None) == -1
+    assert lib.omni_talker_attach_codec(None, None) == INVALID
+    assert lib.omni_codec_last_error(None) == b"null model"
+    assert lib.omni_op_codec_rvq(None, None, None, None, 1, 8, 8) == INVALID
+    assert lib.omni_op_codec_conv(None, None, 8, 8, 1, 1, None, 1, 1, None, 0, None, None, None) == INVALID
